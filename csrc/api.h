@@ -1,0 +1,80 @@
+// Host-callable launchers of every CUDA kernel in this tree (plain C++ signatures, no torch types).
+// All launchers enqueue on `stream` and return immediately; none allocates device memory.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace mt {
+
+// ---- gemm/dense_bf16.cu
+void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+               bool a_mn_major, bool b_mn_major, bool out_f32, bool accumulate, int* status, int num_sms,
+               cudaStream_t stream);
+
+// ---- gemm/grouped_bf16.cu
+// Ragged grouped GEMM: rows of X are grouped by expert (offsets[e]..offsets[e+1]); W is [E, K, N] (b_mn) or
+// [E, N, K] (K-major).  `offsets` is a device int32[E+1] array.
+void grouped_gemm_bf16(const void* X, const void* W, void* Y, const int* offsets, int E, int M_total, int N, int K,
+                       bool w_mn_major, int* status, int num_sms, cudaStream_t stream);
+// Transposed grouped GEMM (per-expert wgrad): dW[e] (+)= X_e^T @ G_e, X [M,K], G [M,N], dW [E,K,N] fp32 or bf16.
+void grouped_wgrad_bf16(const void* X, const void* G, void* dW, const int* offsets, int E, int M_total, int N, int K,
+                        bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream);
+
+// ---- elementwise/rmsnorm.cu
+// y = (x [+ residual]) * rsqrt(mean(.^2) + eps) -> bf16, then * w(bf16-rounded).  If residual_out != null the
+// pre-norm sum is written there (bf16).  rstd (fp32 per row) is saved for backward.
+void rmsnorm_fwd(const void* x, const void* residual, const float* w, void* y, void* residual_out, float* rstd,
+                 int64_t rows, int dim, float eps, cudaStream_t stream);
+// dx = rstd * (w*dy - xhat * mean(xhat * w*dy)) [+ dres];  dw_partial[blocks, dim] holds per-block sums of dy*xhat.
+void rmsnorm_bwd(const void* x, const float* w, const float* rstd, const void* dy, const void* dres, void* dx,
+                 float* dw_partial, int num_partials, int64_t rows, int dim, cudaStream_t stream);
+void rmsnorm_bwd_reduce(const float* dw_partial, int num_partials, int dim, float* dw, bool accumulate,
+                        cudaStream_t stream);
+
+// ---- elementwise/rope.cu
+// In-place rotation of the first rot_dim entries of every head of x [tokens, heads, head_dim] (row pitch
+// `row_stride` elements) by cos/sin tables [max_pos, rot_dim/2]; positions int32[tokens] or null (= t % seq_len).
+void rope_inplace(void* x, const float* cos_t, const float* sin_t, const int* positions, int64_t tokens, int seq_len,
+                  int heads, int head_dim, int rot_dim, int64_t row_stride, bool interleave, bool inverse,
+                  cudaStream_t stream);
+
+// ---- elementwise/swiglu.cu
+// act: 0 silu, 1 gelu(tanh), 2 gelu(erf), 3 relu.  gate/up are column halves [rows, 2*inter] -> out [rows, inter]
+void gated_act_fwd(const void* gate_up, void* out, int64_t rows, int inter, int act, cudaStream_t stream);
+void gated_act_bwd(const void* gate_up, const void* dout, void* dgate_up, int64_t rows, int inter, int act,
+                   cudaStream_t stream);
+
+// ---- elementwise/cross_entropy.cu
+// logits bf16 [rows, V] (row pitch ldl) -> per-row loss, z-loss, lse; overwrites logits with dlogits * grad_scale.
+void cross_entropy_fwd_bwd(void* logits, const int64_t* targets, float* loss, float* zloss, float* lse,
+                           int64_t rows, int V, int64_t ldl, float label_smoothing, float z_weight,
+                           float softcap, float grad_scale, bool write_grad, cudaStream_t stream);
+
+// ---- elementwise/embedding.cu
+void embedding_fwd(const void* table, const int64_t* ids, void* out, int64_t tokens, int dim, float scale,
+                   cudaStream_t stream);
+void embedding_bwd(const void* dout, const int64_t* ids, float* dtable, int64_t tokens, int dim, float scale,
+                   cudaStream_t stream);
+
+// ---- optim/adamw.cu
+// One fused AdamW step over a flat shard: reads grad (bf16 or fp32), updates fp32 master/m/v, writes the bf16
+// compute copy.  grad_scale folds 1/accum and the global-norm clip factor (read from device scalar if non-null).
+void adamw_step(float* master, float* m, float* v, const void* grad, bool grad_f32, void* param_bf16, int64_t n,
+                float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
+                const float* clip_coef, cudaStream_t stream);
+void sumsq(const void* x, bool is_f32, int64_t n, float* out_accum, cudaStream_t stream);
+
+// ---- attention/flash_fwd.cu, flash_bwd.cu
+struct AttnParams {
+  const void* q; const void* k; const void* v; void* o; float* lse;
+  const void* dout; void* dq_accum; void* dk; void* dv; float* delta;
+  int B, S, H, Hkv, dh;
+  int64_t q_row_stride, k_row_stride, v_row_stride, o_row_stride;  // elements between tokens
+  float scale; float softcap; int window;  // window <= 0: none
+  int causal;
+  int* status;
+};
+void flash_attn_fwd(const AttnParams& p, int num_sms, cudaStream_t stream);
+void flash_attn_bwd(const AttnParams& p, int num_sms, cudaStream_t stream);
+
+}  // namespace mt

@@ -1,0 +1,168 @@
+// Python bindings (torch tensors in, raw launchers out).  Shape/dtype/alignment checks live here so the
+// kernels can assume them.  Every function enqueues on the current CUDA stream of the tensors' device.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include "api.h"
+
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int sm_count() {
+  static int n = 0;
+  if (!n) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  return n;
+}
+
+void check_bf16_2d(const torch::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == torch::kBFloat16, name, " must be bf16");
+  TORCH_CHECK(t.dim() == 2, name, " must be 2-D");
+  TORCH_CHECK(t.stride(1) == 1, name, " must have unit inner stride");
+  TORCH_CHECK(t.stride(0) % 8 == 0, name, " row pitch must be a multiple of 8 elements (16 bytes)");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, name, " must be 16-byte aligned");
+}
+
+// C[M,N] (+)= op(A) op(B).  trans_a: A is stored [K,M];  trans_b == false: B is stored [N,K] (K contiguous),
+// trans_b == true: B is stored [K,N].
+void gemm(const torch::Tensor& A, const torch::Tensor& B, torch::Tensor& C, bool a_is_km, bool b_is_kn,
+          bool accumulate, torch::Tensor& status) {
+  check_bf16_2d(A, "A");
+  check_bf16_2d(B, "B");
+  TORCH_CHECK(C.is_cuda() && C.dim() == 2 && C.stride(1) == 1, "C must be 2-D CUDA with unit inner stride");
+  const bool out_f32 = C.scalar_type() == torch::kFloat32;
+  TORCH_CHECK(out_f32 || C.scalar_type() == torch::kBFloat16, "C must be bf16 or fp32");
+  TORCH_CHECK((C.stride(0) * (out_f32 ? 4 : 2)) % 16 == 0, "C row pitch must be a multiple of 16 bytes");
+  const int64_t M = a_is_km ? A.size(1) : A.size(0);
+  const int64_t K = a_is_km ? A.size(0) : A.size(1);
+  const int64_t N = b_is_kn ? B.size(1) : B.size(0);
+  const int64_t Kb = b_is_kn ? B.size(0) : B.size(1);
+  TORCH_CHECK(K == Kb, "contraction sizes differ: ", K, " vs ", Kb);
+  TORCH_CHECK(C.size(0) == M && C.size(1) == N, "C has the wrong shape");
+  c10::cuda::CUDAGuard guard(A.device());
+  mt::gemm_bf16(A.data_ptr(), B.data_ptr(), C.data_ptr(), (int)M, (int)N, (int)K, A.stride(0), B.stride(0),
+                C.stride(0), a_is_km, b_is_kn, out_f32, accumulate, status.data_ptr<int>(), sm_count(), cur_stream());
+}
+
+void rmsnorm_fwd(const torch::Tensor& x, const c10::optional<torch::Tensor>& residual, const torch::Tensor& w,
+                 torch::Tensor& y, const c10::optional<torch::Tensor>& residual_out, torch::Tensor& rstd, double eps) {
+  const int dim = (int)x.size(-1);
+  TORCH_CHECK(dim % 8 == 0, "rmsnorm dim must be a multiple of 8");
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && x.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(w.scalar_type() == torch::kFloat32 && w.numel() == dim);
+  const int64_t rows = x.numel() / dim;
+  c10::cuda::CUDAGuard guard(x.device());
+  mt::rmsnorm_fwd(x.data_ptr(), residual ? residual->data_ptr() : nullptr, w.data_ptr<float>(), y.data_ptr(),
+                  residual_out ? residual_out->data_ptr() : nullptr, rstd.data_ptr<float>(), rows, dim, (float)eps,
+                  cur_stream());
+}
+
+void rmsnorm_bwd(const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& rstd, const torch::Tensor& dy,
+                 const c10::optional<torch::Tensor>& dres, torch::Tensor& dx, torch::Tensor& dw_partial,
+                 torch::Tensor& dw, bool accumulate) {
+  const int dim = (int)x.size(-1);
+  const int64_t rows = x.numel() / dim;
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && dx.is_contiguous());
+  TORCH_CHECK(dw_partial.dim() == 2 && dw_partial.size(1) == dim && dw_partial.scalar_type() == torch::kFloat32);
+  const int parts = (int)dw_partial.size(0);
+  c10::cuda::CUDAGuard guard(x.device());
+  mt::rmsnorm_bwd(x.data_ptr(), w.data_ptr<float>(), rstd.data_ptr<float>(), dy.data_ptr(),
+                  dres ? dres->data_ptr() : nullptr, dx.data_ptr(), dw_partial.data_ptr<float>(), parts, rows, dim,
+                  cur_stream());
+  mt::rmsnorm_bwd_reduce(dw_partial.data_ptr<float>(), parts, dim, dw.data_ptr<float>(), accumulate, cur_stream());
+}
+
+void rope(torch::Tensor& x, const torch::Tensor& cos_t, const torch::Tensor& sin_t,
+          const c10::optional<torch::Tensor>& positions, int64_t seq_len, int64_t heads, int64_t head_dim,
+          int64_t rot_dim, bool interleave, bool inverse) {
+  // x: [tokens, row_stride] view whose first heads*head_dim columns are rotated
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(cos_t.scalar_type() == torch::kFloat32 && cos_t.size(1) == rot_dim / 2);
+  c10::cuda::CUDAGuard guard(x.device());
+  mt::rope_inplace(x.data_ptr(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(),
+                   positions ? positions->data_ptr<int>() : nullptr, x.size(0), (int)seq_len, (int)heads,
+                   (int)head_dim, (int)rot_dim, x.stride(0), interleave, inverse, cur_stream());
+}
+
+void gated_act_fwd(const torch::Tensor& gate_up, torch::Tensor& out, int64_t act) {
+  TORCH_CHECK(gate_up.is_contiguous() && out.is_contiguous());
+  const int inter = (int)out.size(-1);
+  TORCH_CHECK(gate_up.size(-1) == 2 * inter && inter % 8 == 0);
+  c10::cuda::CUDAGuard guard(out.device());
+  mt::gated_act_fwd(gate_up.data_ptr(), out.data_ptr(), out.numel() / inter, inter, (int)act, cur_stream());
+}
+
+void gated_act_bwd(const torch::Tensor& gate_up, const torch::Tensor& dout, torch::Tensor& dgate_up, int64_t act) {
+  TORCH_CHECK(gate_up.is_contiguous() && dout.is_contiguous() && dgate_up.is_contiguous());
+  const int inter = (int)dout.size(-1);
+  c10::cuda::CUDAGuard guard(dout.device());
+  mt::gated_act_bwd(gate_up.data_ptr(), dout.data_ptr(), dgate_up.data_ptr(), dout.numel() / inter, inter, (int)act,
+                    cur_stream());
+}
+
+void cross_entropy(torch::Tensor& logits, const torch::Tensor& targets, torch::Tensor& loss,
+                   const c10::optional<torch::Tensor>& zloss, const c10::optional<torch::Tensor>& lse,
+                   double label_smoothing, double z_weight, double softcap, double grad_scale, bool write_grad) {
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && logits.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(logits.stride(0) % 8 == 0, "logits row pitch must be a multiple of 8");
+  TORCH_CHECK(targets.scalar_type() == torch::kInt64 && targets.is_contiguous());
+  c10::cuda::CUDAGuard guard(logits.device());
+  mt::cross_entropy_fwd_bwd(logits.data_ptr(), targets.data_ptr<int64_t>(), loss.data_ptr<float>(),
+                            zloss ? zloss->data_ptr<float>() : nullptr, lse ? lse->data_ptr<float>() : nullptr,
+                            logits.size(0), (int)logits.size(1), logits.stride(0), (float)label_smoothing,
+                            (float)z_weight, (float)softcap, (float)grad_scale, write_grad, cur_stream());
+}
+
+void embedding_fwd(const torch::Tensor& table, const torch::Tensor& ids, torch::Tensor& out, double scale) {
+  TORCH_CHECK(table.is_contiguous() && out.is_contiguous() && ids.is_contiguous());
+  TORCH_CHECK(table.scalar_type() == torch::kBFloat16 && ids.scalar_type() == torch::kInt64);
+  const int dim = (int)table.size(1);
+  TORCH_CHECK(dim % 8 == 0);
+  c10::cuda::CUDAGuard guard(table.device());
+  mt::embedding_fwd(table.data_ptr(), ids.data_ptr<int64_t>(), out.data_ptr(), ids.numel(), dim, (float)scale,
+                    cur_stream());
+}
+
+void embedding_bwd(const torch::Tensor& dout, const torch::Tensor& ids, torch::Tensor& dtable, double scale) {
+  TORCH_CHECK(dout.is_contiguous() && ids.is_contiguous() && dtable.is_contiguous());
+  TORCH_CHECK(dtable.scalar_type() == torch::kFloat32);
+  const int dim = (int)dtable.size(1);
+  c10::cuda::CUDAGuard guard(dout.device());
+  mt::embedding_bwd(dout.data_ptr(), ids.data_ptr<int64_t>(), dtable.data_ptr<float>(), ids.numel(), dim,
+                    (float)scale, cur_stream());
+}
+
+void adamw_step(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, const torch::Tensor& grad,
+                const c10::optional<torch::Tensor>& param_bf16, double lr, double b1, double b2, double eps, double wd,
+                double bc1, double bc2, double grad_scale, const c10::optional<torch::Tensor>& clip_coef) {
+  TORCH_CHECK(master.is_contiguous() && m.is_contiguous() && v.is_contiguous() && grad.is_contiguous());
+  const bool gf32 = grad.scalar_type() == torch::kFloat32;
+  c10::cuda::CUDAGuard guard(master.device());
+  mt::adamw_step(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr(), gf32,
+                 param_bf16 ? param_bf16->data_ptr() : nullptr, master.numel(), (float)lr, (float)b1, (float)b2,
+                 (float)eps, (float)wd, (float)bc1, (float)bc2, (float)grad_scale,
+                 clip_coef ? clip_coef->data_ptr<float>() : nullptr, cur_stream());
+}
+
+void sumsq(const torch::Tensor& x, torch::Tensor& out) {
+  TORCH_CHECK(x.is_contiguous() && out.scalar_type() == torch::kFloat32);
+  c10::cuda::CUDAGuard guard(x.device());
+  mt::sumsq(x.data_ptr(), x.scalar_type() == torch::kFloat32, x.numel(), out.data_ptr<float>(), cur_stream());
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm, "bf16 tcgen05 GEMM");
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rope", &rope);
+  m.def("gated_act_fwd", &gated_act_fwd);
+  m.def("gated_act_bwd", &gated_act_bwd);
+  m.def("cross_entropy", &cross_entropy);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("adamw_step", &adamw_step);
+  m.def("sumsq", &sumsq);
+}

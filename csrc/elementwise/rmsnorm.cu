@@ -1,0 +1,179 @@
+// RMSNorm forward / backward (bf16 I/O, fp32 math), optional fused residual add.
+// Numerics contract: y = bf16(x * rsqrt(mean(x^2) + eps)) * bf16(w)  (the normalised value is rounded to
+// bf16 before it is scaled, and the product is rounded again).
+// One warp per row, 16-byte vector accesses; the second pass over the row is served from L1.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include "../api.h"
+
+namespace mt {
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+union Pack8 {
+  uint4 u;
+  __nv_bfloat16 h[8];
+};
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                   const float* __restrict__ w, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ res_out,
+                   float* __restrict__ rstd_out, int64_t rows, int dim, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t warp_stride = (int64_t)gridDim.x * kWarpsPerBlock;
+  const int nvec = dim >> 3;
+  for (int64_t row = warp_global; row < rows; row += warp_stride) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * dim);
+    const uint4* rr = res ? reinterpret_cast<const uint4*>(res + row * dim) : nullptr;
+    uint4* ro = res_out ? reinterpret_cast<uint4*>(res_out + row * dim) : nullptr;
+    float ss = 0.f;
+    for (int i = lane; i < nvec; i += 32) {
+      Pack8 a;
+      a.u = xr[i];
+      if (rr) {
+        Pack8 b;
+        b.u = rr[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a.h[j] = __float2bfloat16(__bfloat162float(a.h[j]) + __bfloat162float(b.h[j]));
+        if (ro) ro[i] = a.u;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float f = __bfloat162float(a.h[j]);
+        ss += f * f;
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / dim + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    // second pass: the summed row (when a residual was added) is re-read from res_out, else from x
+    const uint4* src = (rr && ro) ? reinterpret_cast<const uint4*>(res_out + row * dim) : xr;
+    __syncwarp();
+    uint4* yr = reinterpret_cast<uint4*>(y + row * dim);
+    for (int i = lane; i < nvec; i += 32) {
+      Pack8 a;
+      a.u = src[i];
+      if (rr && !ro) {
+        Pack8 b;
+        b.u = rr[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a.h[j] = __float2bfloat16(__bfloat162float(a.h[j]) + __bfloat162float(b.h[j]));
+      }
+      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * i];
+      const float4 w1 = reinterpret_cast<const float4*>(w)[2 * i + 1];
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      Pack8 o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const __nv_bfloat16 n = __float2bfloat16(__bfloat162float(a.h[j]) * rstd);
+        o.h[j] = __float2bfloat16(__bfloat162float(n) * __bfloat162float(__float2bfloat16(wv[j])));
+      }
+      yr[i] = o.u;
+    }
+  }
+}
+
+// dx = rstd * (g - xhat * mean(xhat . g)) with g = w * dy, xhat = x * rstd;  dw += dy * xhat (per block partial).
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, const float* __restrict__ rstd_in,
+                   const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ dres,
+                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int64_t rows, int dim) {
+  extern __shared__ float dw_s[];
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) dw_s[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t warp_stride = (int64_t)gridDim.x * kWarpsPerBlock;
+  const int nvec = dim >> 3;
+  for (int64_t row = warp_global; row < rows; row += warp_stride) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * dim);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + row * dim);
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+    for (int i = lane; i < nvec; i += 32) {
+      Pack8 a, g;
+      a.u = xr[i];
+      g.u = gr[i];
+      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * i];
+      const float4 w1 = reinterpret_cast<const float4*>(w)[2 * i + 1];
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = __bfloat162float(a.h[j]) * rstd;
+        const float gy = __bfloat162float(g.h[j]);
+        dot += xh * gy * wv[j];
+        atomicAdd(&dw_s[i * 8 + j], gy * xh);
+      }
+    }
+    dot = warp_sum(dot) / dim;
+    const uint4* dr = dres ? reinterpret_cast<const uint4*>(dres + row * dim) : nullptr;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + row * dim);
+    for (int i = lane; i < nvec; i += 32) {
+      Pack8 a, g, o;
+      a.u = xr[i];
+      g.u = gr[i];
+      Pack8 r;
+      if (dr) r.u = dr[i];
+      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * i];
+      const float4 w1 = reinterpret_cast<const float4*>(w)[2 * i + 1];
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = __bfloat162float(a.h[j]) * rstd;
+        float d = rstd * (__bfloat162float(g.h[j]) * wv[j] - xh * dot);
+        if (dr) d += __bfloat162float(r.h[j]);
+        o.h[j] = __float2bfloat16(d);
+      }
+      dxr[i] = o.u;
+    }
+  }
+  __syncthreads();
+  float* out = dw_partial + (int64_t)blockIdx.x * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] = dw_s[i];
+}
+
+__global__ void rmsnorm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int dim,
+                                          float* __restrict__ dw, int accumulate) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= dim) return;
+  float s = 0.f;
+  for (int p = 0; p < num_partials; ++p) s += partial[(int64_t)p * dim + i];
+  dw[i] = accumulate ? dw[i] + s : s;
+}
+
+}  // namespace
+
+void rmsnorm_fwd(const void* x, const void* residual, const float* w, void* y, void* residual_out, float* rstd,
+                 int64_t rows, int dim, float eps, cudaStream_t stream) {
+  if (rows == 0) return;
+  int64_t blocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  rmsnorm_fwd_kernel<<<(int)blocks, kWarpsPerBlock * 32, 0, stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, w, (__nv_bfloat16*)y, (__nv_bfloat16*)residual_out,
+      rstd, rows, dim, eps);
+}
+
+void rmsnorm_bwd(const void* x, const float* w, const float* rstd, const void* dy, const void* dres, void* dx,
+                 float* dw_partial, int num_partials, int64_t rows, int dim, cudaStream_t stream) {
+  if (rows == 0) return;
+  rmsnorm_bwd_kernel<<<num_partials, kWarpsPerBlock * 32, dim * sizeof(float), stream>>>(
+      (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx,
+      dw_partial, rows, dim);
+}
+
+void rmsnorm_bwd_reduce(const float* dw_partial, int num_partials, int dim, float* dw, bool accumulate,
+                        cudaStream_t stream) {
+  rmsnorm_bwd_reduce_kernel<<<(dim + 255) / 256, 256, 0, stream>>>(dw_partial, num_partials, dim, dw,
+                                                                   accumulate ? 1 : 0);
+}
+
+}  // namespace mt

@@ -1,0 +1,241 @@
+"""Numerics of the hand-written CUDA kernels against plain PyTorch fp32 references."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ext():
+    from mintext_b200.ops._ext import ext
+
+    return ext()
+
+
+def _status():
+    from mintext_b200.ops._ext import status_word
+
+    return status_word()
+
+
+def _check():
+    from mintext_b200.ops._ext import check_status
+
+    torch.cuda.synchronize()
+    check_status()
+
+
+def _rel_err(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("a_km,b_kn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (384, 512, 320), (200, 136, 72), (1024, 2048, 1024)])
+def test_gemm_layouts(a_km, b_kn, M, N, K):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    ref = a.float() @ b.float()
+    A = a.t().contiguous() if a_km else a
+    B = b if b_kn else b.t().contiguous()
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    _ext().gemm(A, B, c, a_km, b_kn, False, _status())
+    _check()
+    assert _rel_err(c, ref) < 1e-2
+
+
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_gemm_fp32_out_and_accumulate(accumulate):
+    torch.manual_seed(1)
+    M, N, K = 512, 384, 256
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c0 = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    c = c0.clone()
+    _ext().gemm(a, b, c, False, False, accumulate, _status())
+    _check()
+    ref = a.float() @ b.float().t() + (c0 if accumulate else 0)
+    assert _rel_err(c, ref) < 1e-5
+
+
+def test_gemm_bf16_accumulate():
+    torch.manual_seed(2)
+    M, N, K = 256, 256, 512
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c0 = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    c = c0.clone()
+    _ext().gemm(a, b, c, False, False, True, _status())
+    _check()
+    ref = a.float() @ b.float().t() + c0.float()
+    assert _rel_err(c, ref) < 2e-2
+
+
+def test_gemm_strided_views():
+    """Operands and output may be column blocks of wider buffers."""
+    torch.manual_seed(3)
+    M, N, K = 256, 192, 128
+    big_a = torch.randn(M, 3 * K, device="cuda", dtype=torch.bfloat16)
+    a = big_a[:, K:2 * K]
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    big_c = torch.zeros(M, 2 * N + 64, device="cuda", dtype=torch.bfloat16)
+    c = big_c[:, 64:64 + N]
+    _ext().gemm(a, b, c, False, False, False, _status())
+    _check()
+    ref = a.float() @ b.float().t()
+    assert _rel_err(c, ref) < 1e-2
+    assert big_c[:, :64].abs().max().item() == 0
+    assert big_c[:, 64 + N:].abs().max().item() == 0
+
+
+def test_gemm_large_persistent():
+    torch.manual_seed(4)
+    M, N, K = 4096, 4096, 2048
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    _ext().gemm(a, b, c, False, False, False, _status())
+    _check()
+    ref = (a @ b.t()).float()
+    assert _rel_err(c, ref) < 5e-3
+
+
+def test_rmsnorm_fwd_bwd():
+    torch.manual_seed(0)
+    rows, dim = 1000, 2048
+    x = torch.randn(rows, dim, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(rows, dim, device="cuda", dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(dim, device="cuda")).float()
+    y = torch.empty_like(x)
+    res_out = torch.empty_like(x)
+    rstd = torch.empty(rows, device="cuda")
+    e = _ext()
+    e.rmsnorm_fwd(x, res, w, y, res_out, rstd, 1e-5)
+    h = (x.float() + res.float()).bfloat16()
+    assert torch.equal(res_out, h)
+    hf = h.float()
+    ref_rstd = torch.rsqrt(hf.pow(2).mean(-1) + 1e-5)
+    ref = ((hf * ref_rstd[:, None]).bfloat16() * w.bfloat16())
+    assert _rel_err(y, ref) < 1e-2
+    assert torch.allclose(rstd, ref_rstd, rtol=1e-4)
+    # backward vs autograd in fp32
+    dy = torch.randn(rows, dim, device="cuda", dtype=torch.bfloat16)
+    hx = hf.clone().requires_grad_(True)
+    wf = w.clone().requires_grad_(True)
+    yy = hx * torch.rsqrt(hx.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+    yy.backward(dy.float())
+    dx = torch.empty_like(x)
+    parts = torch.empty(64, dim, device="cuda")
+    dw = torch.zeros(dim, device="cuda")
+    e.rmsnorm_bwd(h, w, rstd, dy, None, dx, parts, dw, False)
+    torch.cuda.synchronize()
+    assert _rel_err(dx, hx.grad) < 1e-2
+    assert _rel_err(dw, wf.grad) < 1e-2
+
+
+@pytest.mark.parametrize("interleave", [False, True])
+def test_rope_roundtrip_and_reference(interleave):
+    torch.manual_seed(0)
+    B, S, H, dh, rot = 2, 64, 4, 64, 64
+    x = torch.randn(B * S, H * dh + 32, device="cuda", dtype=torch.bfloat16)
+    x0 = x.clone()
+    inv = 1.0 / (10000 ** (torch.arange(0, rot, 2, device="cuda").float() / rot))
+    ang = torch.arange(S, device="cuda").float()[:, None] * inv[None]
+    cos_t, sin_t = ang.cos().contiguous(), ang.sin().contiguous()
+    e = _ext()
+    e.rope(x, cos_t, sin_t, None, S, H, dh, rot, interleave, False)
+    xr = x0[:, :H * dh].float().view(B, S, H, dh)
+    cos = torch.cat([cos_t, cos_t], -1)[None, :, None, :]
+    sin = torch.cat([sin_t, sin_t], -1)[None, :, None, :]
+    if interleave:
+        p = xr.view(B, S, H, dh // 2, 2)
+        rotx = torch.stack([-p[..., 1], p[..., 0]], -1).reshape(B, S, H, dh)
+    else:
+        rotx = torch.cat([-xr[..., dh // 2:], xr[..., :dh // 2]], -1)
+    ref = xr * cos + rotx * sin
+    assert _rel_err(x[:, :H * dh].view(B, S, H, dh), ref) < 1e-2
+    assert torch.equal(x[:, H * dh:], x0[:, H * dh:])
+    if not interleave:
+        e.rope(x, cos_t, sin_t, None, S, H, dh, rot, interleave, True)
+        assert _rel_err(x[:, :H * dh], x0[:, :H * dh]) < 2e-2
+
+
+@pytest.mark.parametrize("act,fn", [(0, torch.nn.functional.silu), (1, lambda t: torch.nn.functional.gelu(t, approximate="tanh"))])
+def test_gated_act(act, fn):
+    torch.manual_seed(0)
+    rows, inter = 300, 512
+    gu = torch.randn(rows, 2 * inter, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(rows, inter, device="cuda", dtype=torch.bfloat16)
+    e = _ext()
+    e.gated_act_fwd(gu, out, act)
+    g = gu.float().requires_grad_(True)
+    ref = fn(g[:, :inter]) * g[:, inter:]
+    assert _rel_err(out, ref) < 1e-2
+    dout = torch.randn_like(out)
+    ref.backward(dout.float())
+    dgu = torch.empty_like(gu)
+    e.gated_act_bwd(gu, dout, dgu, act)
+    assert _rel_err(dgu, g.grad) < 1e-2
+
+
+@pytest.mark.parametrize("ls,zw", [(0.0, 0.0), (0.1, 1e-3)])
+def test_cross_entropy(ls, zw):
+    torch.manual_seed(0)
+    rows, V = 64, 4104
+    logits = (3 * torch.randn(rows, V, device="cuda")).bfloat16()
+    tgt = torch.randint(0, V, (rows,), device="cuda")
+    lf = logits.float().requires_grad_(True)
+    lse = torch.logsumexp(lf, -1)
+    logp = lf - lse[:, None]
+    nll = -logp.gather(1, tgt[:, None])[:, 0]
+    ref_loss = (1 - ls) * nll - ls * logp.mean(-1)
+    ref_z = zw * lse ** 2
+    (ref_loss + ref_z).mean().backward()
+    loss = torch.empty(rows, device="cuda")
+    z = torch.empty(rows, device="cuda")
+    l2 = logits.clone()
+    _ext().cross_entropy(l2, tgt, loss, z, None, ls, zw, 0.0, 1.0 / rows, True)
+    assert torch.allclose(loss, ref_loss, rtol=1e-3, atol=1e-3)
+    assert torch.allclose(z, ref_z, rtol=1e-3, atol=1e-4)
+    assert _rel_err(l2, lf.grad) < 2e-2
+
+
+def test_embedding_fwd_bwd():
+    torch.manual_seed(0)
+    V, D, T = 1000, 256, 4096
+    table = torch.randn(V, D, device="cuda", dtype=torch.bfloat16)
+    ids = torch.randint(0, V, (T,), device="cuda")
+    out = torch.empty(T, D, device="cuda", dtype=torch.bfloat16)
+    e = _ext()
+    e.embedding_fwd(table, ids, out, 1.0)
+    assert torch.equal(out, table[ids])
+    dout = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+    dt = torch.zeros(V, D, device="cuda")
+    e.embedding_bwd(dout, ids, dt, 1.0)
+    ref = torch.zeros(V, D, device="cuda").index_add_(0, ids, dout.float())
+    assert _rel_err(dt, ref) < 1e-5
+
+
+def test_adamw_and_sumsq():
+    torch.manual_seed(0)
+    n = 100003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ref_p = p.clone()
+    lr, b1, b2, eps, wd = 1e-2, 0.9, 0.95, 1e-8, 0.1
+    e = _ext()
+    rm = torch.zeros(n, device="cuda")
+    rv = torch.zeros(n, device="cuda")
+    for t in range(1, 4):
+        e.adamw_step(p, m, v, g, pb, lr, b1, b2, eps, wd, 1 - b1 ** t, 1 - b2 ** t, 1.0, None)
+        rm = b1 * rm + (1 - b1) * g
+        rv = b2 * rv + (1 - b2) * g * g
+        ref_p = ref_p - lr * ((rm / (1 - b1 ** t)) / ((rv / (1 - b2 ** t)).sqrt() + eps) + wd * ref_p)
+    assert torch.allclose(p, ref_p, rtol=1e-4, atol=1e-5)
+    assert torch.equal(pb, p.bfloat16())
+    out = torch.zeros(1, device="cuda")
+    e.sumsq(g, out)
+    assert torch.allclose(out[0], (g * g).sum(), rtol=1e-3)
