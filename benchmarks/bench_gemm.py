@@ -9,8 +9,12 @@ from __future__ import annotations
 
 import argparse
 import json
+import sys
+from pathlib import Path
 
 import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 
 def _time(fn, flush, iters=10, warmup=3):
