@@ -1,0 +1,247 @@
+"""Headline benchmark: training throughput of the Llama-3.2-1B-shaped model (bf16, global batch 64 x 4096,
+AdamW, synthetic tokens, random init) on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps K --warmup W
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Prints one JSON line (rank 0).  `value` is whole-job tokens/s, device-timed with CUDA events around exactly K
+steps, max over ranks.  `e2e` repeats the measurement through the public engine API with the step's tokens
+copied from pinned host memory and the loss read back to the host every step.
+`--impl reference` reports whether the unmodified reference can run here.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PUBLISHED_TOKENS_PER_SEC_PER_DEVICE = 22800.0  # reference's best published run (TPU v6e-8, Llama-3.2-1B)
+
+
+def llama_1b_config(global_batch: int, seq_len: int, world: int, micro_batch: int, steps: int):
+    from mintext_b200 import MinTextConfig
+
+    per_rank = global_batch // world
+    return MinTextConfig(
+        model_name="llama-3.2-1b", model_type="llama3", num_hidden_layers=16, hidden_size=2048,
+        num_attention_heads=32, num_key_value_heads=8, head_dim=64, intermediate_size=8192, vocab_size=128256,
+        tie_word_embeddings=True, rope_theta=500000.0, rms_norm_eps=1e-5, seq_length=seq_len,
+        per_device_batch_size=micro_batch, gradient_accumulation_steps=max(per_rank // micro_batch, 1),
+        dtype="bfloat16", weight_dtype="float32", optimizer="adamw", learning_rate=3e-4, lr_schedule="cosine",
+        steps=max(steps, 10), remat_policy="none", enable_tensorboard=False, enable_checkpointing=False,
+        ici_fsdp_parallelism=world)
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[tuple[float, float, str]] = []
+        self._stop = threading.Event()
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i",
+                                      str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                parts = [p.strip() for p in out.split(",")]
+                reasons = [n for n, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                              "sw_power_cap"), parts[2:]) if v == "Active"]
+                self.samples.append((float(parts[0]), float(parts[1]), ",".join(reasons)))
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=3)
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        clocks = sorted(s[0] for s in self.samples)
+        reasons = sorted({r for s in self.samples for r in s[2].split(",") if r})
+        return {"sm_mhz": clocks[len(clocks) // 2], "sm_max_mhz": self.samples[0][1], "reasons": reasons,
+                "samples": len(clocks)}
+
+
+def run_reference(args) -> None:
+    """The reference is a JAX program; report why it cannot run when its runtime is absent."""
+    ref = ROOT / "baseline" / "_ref"
+    why = None
+    try:
+        import jax  # noqa: F401
+    except Exception as e:
+        why = f"reference needs jax/flax/optax/orbax/grain which are not installed and cannot be (no index access): {type(e).__name__}"
+    if why is None and not (ref / "mintext").exists():
+        why = "reference package is not installed under baseline/_ref"
+    if why is not None:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}))
+        return
+    # jax present: run the reference's own entry point on the same model/config (never reached on this image)
+    sys.path.insert(0, str(ref))
+    print(json.dumps({"impl": "reference", "unavailable": "reference run path not wired for this image"}))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--global-batch", type=int, default=64)
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--skip-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.engine import TrainEngine, local_batch_rows
+    from mintext_b200.utils.pytree import model_flops_per_token_batch
+
+    warmup = max(args.warmup, 3)
+    cfg = llama_1b_config(args.global_batch, args.seq_len, world, args.micro_batch, args.steps + warmup)
+    model = Transformer(cfg, rngs=0)
+    eng = TrainEngine(model, cfg, device=dev)
+    lo, hi = local_batch_rows(args.global_batch, world, rank)
+    rows = hi - lo
+    n_micro = max(rows // args.micro_batch, 1)
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+
+    def host_batch():
+        t = torch.randint(0, cfg.vocab_size, (rows, args.seq_len), generator=gen, dtype=torch.int64)
+        return t.pin_memory()
+
+    # a pool of distinct batches, each far larger than nothing the L2 could keep between steps: one step streams
+    # > 2.4 GB of weights and tens of GB of activations through a 126 MB L2, so no extra flush is needed
+    dev_batches = [host_batch().to(dev, non_blocking=True) for _ in range(4)]
+
+    def barrier_sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_device(i):
+        tok = dev_batches[i % len(dev_batches)]
+        return eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=n_micro)
+
+    for i in range(warmup):
+        out = step_device(i)
+    barrier_sync()
+    eng.check()
+    launches_before = _count_launch_base(eng)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier_sync()
+        start.record()
+        for i in range(args.steps):
+            out = step_device(i)
+        end.record()
+        barrier_sync()
+    ms = start.elapsed_time(end)
+    eng.check()
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ms_per_step = ms / args.steps
+    tokens_per_step = args.global_batch * args.seq_len
+    value = tokens_per_step / (ms_per_step / 1e3)
+    final_loss = float(out["loss"])
+
+    # end-to-end: pinned host tokens -> device each step, loss read back each step
+    e2e = None
+    if not args.skip_e2e:
+        hosts = [host_batch() for _ in range(4)]
+        for i in range(2):
+            tok = hosts[i % 4].to(dev, non_blocking=True)
+            float(eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=n_micro)["loss"])
+        barrier_sync()
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record()
+        for i in range(args.steps):
+            tok = hosts[i % 4].to(dev, non_blocking=True)
+            o2 = eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=n_micro)
+            final_loss = float(o2["loss"])  # device -> host read of the step's result
+        e2.record()
+        barrier_sync()
+        t2 = torch.tensor([s2.elapsed_time(e2)], device=dev)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        ms2 = float(t2.item()) / args.steps
+        e2e = {"value": tokens_per_step / (ms2 / 1e3), "unit": "tokens/s", "ms_per_step": ms2,
+               "h2d_bytes_per_step": rows * args.seq_len * 8, "d2h_bytes_per_step": 4}
+
+    flops_step = model_flops_per_token_batch(cfg, args.global_batch)
+    tflops_per_gpu = flops_step / (ms_per_step / 1e3) / 1e12 / world
+    if rank == 0:
+        line = {
+            "metric": "train tokens/s (Llama-3.2-1B-shaped, bf16, AdamW)", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": value / (PUBLISHED_TOKENS_PER_SEC_PER_DEVICE * world),
+            "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights", "impl": "own",
+            "tokens_per_sec_per_gpu": value / world, "tflops_per_gpu": tflops_per_gpu,
+            "mfu_vs_nominal_2250": tflops_per_gpu / 2250.0, "final_loss": final_loss,
+            "config": {"model": "llama-3.2-1b-shaped (16L, d2048, 32/8 heads, ffn 8192, vocab 128256, tied)",
+                       "global_batch": args.global_batch, "seq_len": args.seq_len,
+                       "parallelism": f"fsdp{world}" if world > 1 else "single",
+                       "micro_batch": args.micro_batch, "grad_accum_per_rank": n_micro,
+                       "l2": "inputs and weights per step exceed L2 (126 MB) by >20x; no explicit flush"},
+            "clocks": clocks.summary(), "e2e": e2e,
+            "gpu_launches": int(_count_launches(eng, launches_before, args.steps)),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _count_launch_base(eng):
+    from mintext_b200.ops import launch_counter
+
+    return launch_counter.count()
+
+
+def _count_launches(eng, before, steps):
+    from mintext_b200.ops import launch_counter
+
+    return launch_counter.count() - before
+
+
+if __name__ == "__main__":
+    main()

@@ -67,9 +67,11 @@ void sumsq(const void* x, bool is_f32, int64_t n, float* out_accum, cudaStream_t
 // ---- attention/flash_fwd.cu, flash_bwd.cu
 struct AttnParams {
   const void* q; const void* k; const void* v; void* o; float* lse;
-  const void* dout; void* dq_accum; void* dk; void* dv; float* delta;
+  const void* dout; void* dq_accum; void* dq_out; void* dk; void* dv; float* delta;
   int B, S, H, Hkv, dh;
-  int64_t q_row_stride, k_row_stride, v_row_stride, o_row_stride;  // elements between tokens
+  // elements between consecutive tokens of each tensor (heads are packed: head h starts at h*dh)
+  int64_t q_row_stride, k_row_stride, v_row_stride, o_row_stride;
+  int64_t do_row_stride, dq_row_stride, dk_row_stride, dv_row_stride;
   float scale; float softcap; int window;  // window <= 0: none
   int causal;
   int* status;

@@ -1,0 +1,483 @@
+// Flash attention backward for sm_100a (bf16, head_dim 64, grouped-query K/V, causal / sliding window / soft-cap).
+//
+// One CTA = one (batch, kv head, 128-key block).  It keeps K_j and V_j in shared memory and dK_j, dV_j as fp32
+// accumulators in tensor memory while it walks over every query head of the group and every 128-row query
+// block that can see the key block.  Per (query head, query block) five tcgen05 MMAs run:
+//     S^T  = K_j Q_i^T          dP^T = V_j dO_i^T                      (both M=128 keys, N=128 queries, K=dh)
+//     dV  += P^T dO_i           dK  += dS^T Q_i                        (M=128 keys, N=dh, K=128 queries)
+//     dQ_i = dS K_j                                                     (M=128 queries, N=dh, K=128 keys)
+// The score tiles are produced transposed (keys on TMEM lanes) so that P^T and dS^T, written once to swizzled
+// shared memory by the 128 softmax threads (thread = key row), serve as the K-major A operand of dV / dK and,
+// read with an MN-major descriptor, as the A operand of dQ; Q_i and dO_i tiles likewise serve as K-major B of
+// the first pair and MN-major B of the second pair.  dQ partials leave through a per-warp TMA reduce-add into
+// an fp32 accumulator.  A small pre-pass computes delta = rowsum(dO * O) and clears the dQ accumulator; a
+// post-pass converts dQ to bf16.
+// Roles: warps 0-3 softmax/epilogue, warp 4 TMA producer, warp 5 MMA issuer.  All mbarrier waits are bounded.
+#include "../common/ptx.cuh"
+#include "../common/tmap.h"
+#include "../api.h"
+
+namespace mt {
+namespace {
+
+constexpr int BQ = 128;   // query rows per step
+constexpr int BKV = 128;  // keys per CTA
+constexpr int DH = 64;
+constexpr int kThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct BwdCfg {
+  static constexpr int K_BYTES = BKV * DH * 2;      // 16 KB
+  static constexpr int V_BYTES = BKV * DH * 2;
+  static constexpr int Q_BYTES = BQ * DH * 2;       // per stage
+  static constexpr int DO_BYTES = BQ * DH * 2;
+  static constexpr int PT_BYTES = BKV * BQ * 2;     // 32 KB
+  static constexpr int DST_BYTES = BKV * BQ * 2;
+  static constexpr int DQ_STAGE_BYTES = 4 * 2 * 4096;  // per warp: 2 boxes of 32 rows x 128 B
+  static constexpr int STAT_BYTES = 2 * 2 * BQ * 4;    // lse, delta per stage
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + K_BYTES;
+  static constexpr int OFF_Q = OFF_V + V_BYTES;           // 2 stages of (Q | dO)
+  static constexpr int OFF_PT = OFF_Q + 2 * (Q_BYTES + DO_BYTES);
+  static constexpr int OFF_DST = OFF_PT + PT_BYTES;
+  static constexpr int OFF_DQ = OFF_DST + DST_BYTES;
+  static constexpr int OFF_STAT = OFF_DQ + DQ_STAGE_BYTES;
+  static constexpr int OFF_BAR = OFF_STAT + STAT_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384;
+};
+
+struct BwdArgs {
+  int S, H, Hkv, causal, window;
+  float scale, softcap;
+  const float* lse;
+  const float* delta;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                 const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
+                 const __grid_constant__ CUtensorMap tmDV, BwdArgs args) {
+  using C = BwdCfg;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* k_s = smem + C::OFF_K;
+  uint8_t* v_s = smem + C::OFF_V;
+  uint8_t* qdo_s = smem + C::OFF_Q;
+  uint8_t* pt_s = smem + C::OFF_PT;
+  uint8_t* dst_s = smem + C::OFF_DST;
+  uint8_t* dq_s = smem + C::OFF_DQ;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qdo_full = bars + 1;   // [2]
+  uint64_t* qdo_empty = bars + 3;  // [2]
+  uint64_t* st_full = bars + 5;
+  uint64_t* pds_full = bars + 6;
+  uint64_t* mma2_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int j = blockIdx.x;  // key block (small j = most work, scheduled first)
+  const int hk = blockIdx.y;
+  const int b = blockIdx.z;
+  const int G = args.H / args.Hkv;
+  const int nQ = args.S / BQ;
+  const int key0 = j * BKV;
+  const int tok0 = b * args.S;
+  const int i_begin = args.causal ? j : 0;
+  int i_end = nQ;
+  if (args.window > 0) {
+    const int last_q = key0 + BKV - 1 + args.window - 1;  // largest query index that still sees this block
+    i_end = min(nQ, last_q / BQ + 1);
+  }
+  const int n_i = max(i_end - i_begin, 0);
+  const int n_steps = n_i * G;
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0 && args.status) atomicCAS(args.status, 0, MT_ERR_BAD_ARGS);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    mbar_init(st_full, 1);
+    mbar_init(pds_full, 4);
+    mbar_init(mma2_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, C::K_BYTES + C::V_BYTES);
+      tma_load_3d(k_s, &tmK, kv_full, 0, hk, tok0 + key0);
+      tma_load_3d(v_s, &tmV, kv_full, 0, hk, tok0 + key0);
+      for (int t = 0; t < n_steps; ++t) {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        if (!mbar_wait(&qdo_empty[s], ph ^ 1, abort_flag, args.status, MT_ERR_TIMEOUT_EMPTY)) break;
+        const int h = hk * G + t / n_i;
+        const int q0 = (i_begin + t % n_i) * BQ;
+        uint8_t* q_dst = qdo_s + s * (C::Q_BYTES + C::DO_BYTES);
+        mbar_expect_tx(&qdo_full[s], C::Q_BYTES + C::DO_BYTES);
+        tma_load_3d(q_dst, &tmQ, &qdo_full[s], 0, h, tok0 + q0);
+        tma_load_3d(q_dst + C::Q_BYTES, &tmDO, &qdo_full[s], 0, h, tok0 + q0);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BKV, BQ, false, false);     // S^T, dP^T
+      constexpr uint32_t idesc_dkv = make_idesc_bf16(BKV, DH, false, true);    // dV, dK : B = dO / Q as [K=q, N=dh]
+      constexpr uint32_t idesc_dq = make_idesc_bf16(BQ, DH, true, true);       // dQ : A = dS^T read MN-major
+      const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+      const uint32_t pt_addr = smem_u32(pt_s), dst_addr = smem_u32(dst_s);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, MT_ERR_TIMEOUT_FULL);
+      auto issue_scores = [&](int t) {
+        const uint32_t q_addr = smem_u32(qdo_s + (t & 1) * (C::Q_BYTES + C::DO_BYTES));
+        const uint32_t do_addr = q_addr + C::Q_BYTES;
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k)
+          tc_mma_f16(tmem_base + C::COL_ST, make_smem_desc_sw128(k_addr + k * 32, 16, 1024),
+                     make_smem_desc_sw128(q_addr + k * 32, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k)
+          tc_mma_f16(tmem_base + C::COL_DPT, make_smem_desc_sw128(v_addr + k * 32, 16, 1024),
+                     make_smem_desc_sw128(do_addr + k * 32, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+        tc_commit(st_full);
+      };
+      if (ok && n_steps > 0) {
+        ok = mbar_wait(&qdo_full[0], 0, abort_flag, args.status, MT_ERR_TIMEOUT_FULL);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_scores(0);
+        }
+      }
+      for (int t = 0; t < n_steps && ok; ++t) {
+        const int s = t & 1;
+        if (!mbar_wait(pds_full, t & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t q_addr = smem_u32(qdo_s + s * (C::Q_BYTES + C::DO_BYTES));
+        const uint32_t do_addr = q_addr + C::Q_BYTES;
+        // dV += P^T dO ; dK += dS^T Q   (A: [128 keys x 128 queries] K-major in two 64-query atoms)
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k) {
+          const uint32_t aoff = (k >> 2) * (BKV * 128) + (k & 3) * 32;
+          tc_mma_f16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_addr + aoff, 16, 1024),
+                     make_smem_desc_sw128(do_addr + k * (16 * 128), BQ * 128, 1024), idesc_dkv, (t | k) != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k) {
+          const uint32_t aoff = (k >> 2) * (BKV * 128) + (k & 3) * 32;
+          tc_mma_f16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_addr + aoff, 16, 1024),
+                     make_smem_desc_sw128(q_addr + k * (16 * 128), BQ * 128, 1024), idesc_dkv, (t | k) != 0 ? 1u : 0u);
+        }
+        // dQ = dS K : A = dS^T tile read MN-major (M = queries contiguous in 64-wide atoms, K = key rows),
+        //             B = K_j tile read MN-major (N = dh contiguous, K = key rows)
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k)
+          tc_mma_f16(tmem_base + C::COL_DQ, make_smem_desc_sw128(dst_addr + k * (16 * 128), BKV * 128, 1024),
+                     make_smem_desc_sw128(k_addr + k * (16 * 128), BKV * 128, 1024), idesc_dq, k != 0 ? 1u : 0u);
+        tc_commit(&qdo_empty[s]);
+        tc_commit(mma2_done);
+        if (t + 1 < n_steps) {
+          const int s2 = (t + 1) & 1;
+          if (!mbar_wait(&qdo_full[s2], ((t + 1) >> 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          issue_scores(t + 1);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax backward (thread = key row)
+    const int r = threadIdx.x;
+    const int kidx = key0 + r;
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const float sc = args.scale;
+    const float cap = args.softcap;
+    uint8_t* dq_stage = dq_s + warp * (2 * 4096);
+    bool ok = true;
+
+    auto drain_dq = [&](int t_prev) {
+      // dQ partial of step t_prev: TMEM lanes = query rows; this warp owns rows warp*32 .. +31
+      const int h = hk * G + t_prev / n_i;
+      const int q0 = (i_begin + t_prev % n_i) * BQ;
+      if (lane == 0) tma_wait_group_read<0>();
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_row + C::COL_DQ + c * 32, v);
+        tc_wait_ld();
+        uint8_t* srow = dq_stage + c * 4096 + lane * 128;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          uint4 w = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+          *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = w;
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+#pragma unroll
+        for (int c = 0; c < DH / 32; ++c) {
+          asm volatile(
+              "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+              ::"l"(reinterpret_cast<uint64_t>(&tmDQ)), "r"(smem_u32(dq_stage + c * 4096)), "r"(c * 32), "r"(h),
+                "r"(tok0 + q0 + warp * 32)
+              : "memory");
+        }
+        tma_commit_group();
+      }
+    };
+
+    for (int t = 0; t < n_steps && ok; ++t) {
+      const int h = hk * G + t / n_i;
+      const int i = i_begin + t % n_i;
+      const int q0 = i * BQ;
+      // per-query statistics of this step: every warp keeps all 128 (lse, delta) pairs in registers, four per
+      // lane, and broadcasts them with shuffles (no CTA-wide barrier on this path)
+      float lse_r[BQ / 32], delta_r[BQ / 32];
+      {
+        const int64_t sbase = (static_cast<int64_t>(b) * args.H + h) * args.S + q0;
+#pragma unroll
+        for (int c = 0; c < BQ / 32; ++c) {
+          lse_r[c] = args.lse[sbase + c * 32 + lane] * kLog2e;
+          delta_r[c] = args.delta[sbase + c * 32 + lane];
+        }
+      }
+      if (!mbar_wait_warp(st_full, t & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (t > 0) {
+        // previous step's dV/dK/dQ MMAs finished: P^T / dS^T buffers are free and dQ(t-1) can be drained
+        if (!mbar_wait_warp(mma2_done, (t - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after_sync();
+        drain_dq(t - 1);
+      }
+      const bool need_mask = (args.causal && (key0 + BKV - 1 > q0)) ||
+                             (args.window > 0 && (q0 + BQ - 1 - key0 >= args.window));
+#pragma unroll
+      for (int c = 0; c < BQ / 32; ++c) {
+        uint32_t sv[32];
+        uint32_t dv[32];
+        tmem_ld_32x32b_x32(t_row + C::COL_ST + c * 32, sv);
+        tmem_ld_32x32b_x32(t_row + C::COL_DPT + c * 32, dv);
+        tc_wait_ld();
+        float p[32], ds[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int qc = c * 32 + e;
+          float x = __uint_as_float(sv[e]) * sc;
+          float slope = 1.f;
+          if (cap > 0.f) {
+            const float th = tanhf(x / cap);
+            x = cap * th;
+            slope = 1.f - th * th;
+          }
+          const float lse_q = __shfl_sync(0xffffffffu, lse_r[c], e);
+          const float delta_q = __shfl_sync(0xffffffffu, delta_r[c], e);
+          float pe = exp2f(x * kLog2e - lse_q);
+          if (need_mask) {
+            const int qidx = q0 + qc;
+            const bool dead = (args.causal && kidx > qidx) || (args.window > 0 && qidx - kidx >= args.window);
+            if (dead) pe = 0.f;
+          }
+          p[e] = pe;
+          ds[e] = pe * (__uint_as_float(dv[e]) - delta_q) * slope * sc;
+        }
+        uint8_t* prow = pt_s + (c >> 1) * (BKV * 128) + r * 128;
+        uint8_t* drow = dst_s + (c >> 1) * (BKV * 128) + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w, d;
+          w.x = pack_bf16x2(p[8 * g + 0], p[8 * g + 1]);
+          w.y = pack_bf16x2(p[8 * g + 2], p[8 * g + 3]);
+          w.z = pack_bf16x2(p[8 * g + 4], p[8 * g + 5]);
+          w.w = pack_bf16x2(p[8 * g + 6], p[8 * g + 7]);
+          d.x = pack_bf16x2(ds[8 * g + 0], ds[8 * g + 1]);
+          d.y = pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]);
+          d.z = pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]);
+          d.w = pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7]);
+          const int chunk = (c & 1) * 4 + g;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = w;
+          *reinterpret_cast<uint4*>(drow + ((chunk ^ (r & 7)) << 4)) = d;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+    }
+    // tail: last dQ partial, then dK / dV
+    if (ok && n_steps > 0) {
+      ok = mbar_wait_warp(mma2_done, (n_steps - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL);
+      if (ok) {
+        tc_fence_after_sync();
+        drain_dq(n_steps - 1);
+      }
+    }
+    if (ok) {
+      if (lane == 0) tma_wait_group_read<0>();
+      __syncwarp();
+      // dV then dK: this warp's 32 key rows x 64 dims (bf16, one 128-byte row each) through its staging slab
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const int col = which == 0 ? C::COL_DV : C::COL_DK;
+        uint8_t* slab = dq_stage + which * 4096;
+#pragma unroll
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t v[32];
+          if (n_steps > 0) {
+            tmem_ld_32x32b_x32(t_row + col + c * 32, v);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = 0;
+          }
+          uint8_t* srow = slab + lane * 128;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(v[8 * g + 0]), __uint_as_float(v[8 * g + 1]));
+            w.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3]));
+            w.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5]));
+            w.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7]));
+            const int chunk = c * 4 + g;
+            *reinterpret_cast<uint4*>(srow + ((chunk ^ (lane & 7)) << 4)) = w;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_3d(&tmDV, dq_stage, 0, hk, tok0 + key0 + warp * 32);
+        tma_store_3d(&tmDK, dq_stage + 4096, 0, hk, tok0 + key0 + warp * 32);
+        tma_commit_group();
+      }
+    }
+    if (lane == 0) tma_wait_group<0>();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    __syncwarp();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+union Pack8 {
+  uint4 u;
+  __nv_bfloat16 h[8];
+};
+
+// delta[b,h,s] = sum_d dO * O ; also clears the fp32 dQ accumulator.  One warp per (token, head) row of 64.
+__global__ void bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                   float* __restrict__ delta, float* __restrict__ dq_accum, int B, int S, int H,
+                                   int64_t o_stride, int64_t do_stride) {
+  const int64_t rows = static_cast<int64_t>(B) * S * H;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane >> 3;        // 4 rows per warp pass, 8 lanes x 8 elements each
+  const int l8 = lane & 7;
+  for (int64_t row = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 4 + sub; row < rows;
+       row += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5) * 4) {
+    const int64_t tok = row / H;
+    const int h = static_cast<int>(row % H);
+    Pack8 a, g;
+    a.u = *reinterpret_cast<const uint4*>(o + tok * o_stride + h * DH + l8 * 8);
+    g.u = *reinterpret_cast<const uint4*>(dout + tok * do_stride + h * DH + l8 * 8);
+    float s = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s += __bfloat162float(a.h[e]) * __bfloat162float(g.h[e]);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if (l8 == 0) {
+      const int bb = static_cast<int>(tok / S);
+      const int ss = static_cast<int>(tok % S);
+      delta[(static_cast<int64_t>(bb) * H + h) * S + ss] = s;
+    }
+    float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4* dq = reinterpret_cast<float4*>(dq_accum + row * DH + l8 * 8);
+    dq[0] = z;
+    dq[1] = z;
+  }
+}
+
+__global__ void bwd_finish_kernel(const float* __restrict__ dq_accum, __nv_bfloat16* __restrict__ dq, int64_t tokens,
+                                  int H, int64_t dq_stride) {
+  const int64_t total = tokens * H * (DH / 8);
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(idx % (DH / 8));
+    const int64_t th = idx / (DH / 8);
+    const int h = static_cast<int>(th % H);
+    const int64_t tok = th / H;
+    const float4 a = *reinterpret_cast<const float4*>(dq_accum + th * DH + c * 8);
+    const float4 b2 = *reinterpret_cast<const float4*>(dq_accum + th * DH + c * 8 + 4);
+    Pack8 o;
+    o.h[0] = __float2bfloat16(a.x); o.h[1] = __float2bfloat16(a.y);
+    o.h[2] = __float2bfloat16(a.z); o.h[3] = __float2bfloat16(a.w);
+    o.h[4] = __float2bfloat16(b2.x); o.h[5] = __float2bfloat16(b2.y);
+    o.h[6] = __float2bfloat16(b2.z); o.h[7] = __float2bfloat16(b2.w);
+    *reinterpret_cast<uint4*>(dq + tok * dq_stride + h * DH + c * 8) = o.u;
+  }
+}
+
+}  // namespace
+
+// p.dq_accum: fp32 [B*S, H, 64] scratch; p.delta: fp32 [B,H,S] scratch; p.dq_out (bf16) row pitch = q_row_stride.
+void flash_attn_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
+  if (p.dh != DH) throw std::runtime_error("flash_attn_bwd: head_dim must be 64");
+  if (p.S % BQ != 0) throw std::runtime_error("flash_attn_bwd: sequence length must be a multiple of 128");
+  using C = BwdCfg;
+  const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  const uint64_t tokens = static_cast<uint64_t>(p.B) * p.S;
+  bwd_prepare_kernel<<<num_sms * 8, 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(p.o), static_cast<const __nv_bfloat16*>(p.dout), p.delta,
+      static_cast<float*>(p.dq_accum), p.B, p.S, p.H, p.o_row_stride, p.do_row_stride);
+  CUtensorMap tQ = make_tmap_3d(p.q, bf, 2, tokens, p.H, DH, p.q_row_stride, DH, BQ, 1, 64, sw);
+  CUtensorMap tK = make_tmap_3d(p.k, bf, 2, tokens, p.Hkv, DH, p.k_row_stride, DH, BKV, 1, 64, sw);
+  CUtensorMap tV = make_tmap_3d(p.v, bf, 2, tokens, p.Hkv, DH, p.v_row_stride, DH, BKV, 1, 64, sw);
+  CUtensorMap tDO = make_tmap_3d(p.dout, bf, 2, tokens, p.H, DH, p.do_row_stride, DH, BQ, 1, 64, sw);
+  CUtensorMap tDQ = make_tmap_3d(p.dq_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, tokens, p.H, DH,
+                                 static_cast<uint64_t>(p.H) * DH, DH, 32, 1, 32, sw);
+  CUtensorMap tDK = make_tmap_3d(p.dk, bf, 2, tokens, p.Hkv, DH, p.dk_row_stride, DH, 32, 1, 64, sw);
+  CUtensorMap tDV = make_tmap_3d(p.dv, bf, 2, tokens, p.Hkv, DH, p.dv_row_stride, DH, 32, 1, 64, sw);
+  static bool configured = false;
+  if (!configured) {
+    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    configured = true;
+  }
+  BwdArgs a{p.S, p.H, p.Hkv, p.causal, p.window, p.scale, p.softcap, p.lse, p.delta, p.status};
+  dim3 grid(p.S / BKV, p.Hkv, p.B);
+  flash_bwd_kernel<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+  MT_CUDA_CHECK(cudaGetLastError());
+  bwd_finish_kernel<<<num_sms * 8, 256, 0, stream>>>(static_cast<const float*>(p.dq_accum),
+                                                     static_cast<__nv_bfloat16*>(p.dq_out),
+                                                     static_cast<int64_t>(tokens), p.H, p.dq_row_stride);
+  MT_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace mt

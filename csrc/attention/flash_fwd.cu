@@ -1,0 +1,378 @@
+// Causal / sliding-window flash attention forward for sm_100a (bf16, head_dim 64 or 128, grouped-query K/V).
+//
+// One CTA = one (batch, head, 128-query-row block).  Roles:
+//   warps 0-3  softmax      : thread r owns query row r.  Reads S = Q K^T from tensor memory (tcgen05.ld), keeps the
+//                             running max / sum, rescales the O accumulator in TMEM only when some row's max moved,
+//                             writes P (bf16) into 128B-swizzled shared memory as the A operand of the second MMA.
+//   warp 4     TMA producer : Q once, then K/V blocks through a 2-stage ring (non-multicast tile loads).
+//   warp 5     MMA issuer   : S = Q K^T (M=128, N=BN, K=dh) and O += P V (M=128, N=dh, K=BN) with tcgen05.mma,
+//                             accumulators in TMEM (S: BN columns, O: dh columns -> 256 columns per CTA).
+// Two CTAs fit on an SM (112 KB shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the other
+// CTA's MMAs.  Blocks above the causal diagonal / outside the window are never loaded.  Output: O (bf16) by TMA
+// store and the row-wise log-sum-exp (natural log, of the scaled and capped scores) for the backward pass.
+// Every mbarrier wait is bounded; on expiry an error code is recorded and the CTA unwinds.
+#include "../common/ptx.cuh"
+#include "../common/tmap.h"
+#include "../api.h"
+
+namespace mt {
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int kThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int DH>
+struct FwdCfg {
+  static constexpr int BN = (DH == 64) ? 128 : 64;
+  static constexpr int Q_BYTES = BLOCK_M * DH * 2;
+  static constexpr int K_BYTES = BN * DH * 2;
+  static constexpr int V_BYTES = BN * DH * 2;
+  static constexpr int P_BYTES = BLOCK_M * BN * 2;
+  static constexpr int O_STAGE_BYTES = BLOCK_M * DH * 2;  // reuses the P region (+ K stage 0 when larger)
+  static constexpr int SMEM_DATA = Q_BYTES + 2 * (K_BYTES + V_BYTES) + P_BYTES;
+  static constexpr int SMEM_BYTES = SMEM_DATA + 256;
+  static constexpr int TMEM_COLS = 256;
+  static constexpr int S_COL = 0;
+  static constexpr int O_COL = BN;
+  static_assert(BN + DH <= TMEM_COLS, "accumulators must fit the allocation");
+};
+
+struct FwdArgs {
+  int S, H, Hkv, causal, window;
+  float scale, softcap;
+  float* lse;
+  int* status;
+};
+
+template <int DH>
+__global__ void __launch_bounds__(kThreads, 2)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, FwdArgs args) {
+  using C = FwdCfg<DH>;
+  constexpr int BN = C::BN;
+  constexpr int D_ATOMS = DH / 64;   // 64-element (128 B) swizzle atoms along the head dim
+  constexpr int N_ATOMS = BN / 64;   // atoms along the key dim of P
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* q_s = smem;
+  uint8_t* kv_s = q_s + C::Q_BYTES;  // stage s: K at kv_s + s*(K+V), V right after K
+  uint8_t* p_s = kv_s + 2 * (C::K_BYTES + C::V_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + C::P_BYTES);
+  uint64_t* q_full = bars + 0;
+  uint64_t* kv_full = bars + 1;    // [2]
+  uint64_t* kv_empty = bars + 3;   // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_full = bars + 6;
+  uint64_t* pv_done = bars + 7;
+  uint64_t* o_staged = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_qb = args.S / BLOCK_M;
+  const int qb = num_qb - 1 - blockIdx.x;  // heavy (late) blocks first
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hk = h / (args.H / args.Hkv);
+  const int q0 = qb * BLOCK_M;
+  const int tok0 = b * args.S;
+
+  // key-block range of this query block
+  int j_end = args.causal ? (q0 + BLOCK_M + BN - 1) / BN : args.S / BN;
+  if (j_end > args.S / BN) j_end = args.S / BN;
+  int j_begin = 0;
+  if (args.window > 0) {
+    const int first_key = q0 - args.window + 1;
+    if (first_key > 0) j_begin = first_key / BN;
+  }
+  const int n_blocks = j_end - j_begin;
+
+  if ((smem_u32(smem) & 1023u) != 0) {  // swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0 && args.status) atomicCAS(args.status, 0, MT_ERR_BAD_ARGS);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    mbar_init(o_staged, 4);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmO);
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(q_full, C::Q_BYTES);
+#pragma unroll
+      for (int a = 0; a < D_ATOMS; ++a)
+        tma_load_3d(q_s + a * (BLOCK_M * 128), &tmQ, q_full, a * 64, h, tok0 + q0);
+      for (int i = 0; i < n_blocks; ++i) {
+        const int s = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        if (!mbar_wait(&kv_empty[s], ph ^ 1, abort_flag, args.status, MT_ERR_TIMEOUT_EMPTY)) break;
+        uint8_t* k_dst = kv_s + s * (C::K_BYTES + C::V_BYTES);
+        uint8_t* v_dst = k_dst + C::K_BYTES;
+        mbar_expect_tx(&kv_full[s], C::K_BYTES + C::V_BYTES);
+        const int key0 = tok0 + (j_begin + i) * BN;
+#pragma unroll
+        for (int a = 0; a < D_ATOMS; ++a) {
+          tma_load_3d(k_dst + a * (BN * 128), &tmK, &kv_full[s], a * 64, hk, key0);
+          tma_load_3d(v_dst + a * (BN * 128), &tmV, &kv_full[s], a * 64, hk, key0);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(BLOCK_M, BN, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(BLOCK_M, DH, false, true);
+      const uint32_t q_addr = smem_u32(q_s);
+      const uint32_t p_addr = smem_u32(p_s);
+      bool ok = mbar_wait(q_full, 0, abort_flag, args.status, MT_ERR_TIMEOUT_FULL);
+      auto issue_qk = [&](int i) {
+        const uint32_t k_addr = smem_u32(kv_s + (i & 1) * (C::K_BYTES + C::V_BYTES));
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k) {
+          const uint32_t off = (k >> 2) * (BLOCK_M * 128) + (k & 3) * 32;
+          const uint32_t koff = (k >> 2) * (BN * 128) + (k & 3) * 32;
+          tc_mma_f16(tmem_base + C::S_COL, make_smem_desc_sw128(q_addr + off, 16, 1024),
+                     make_smem_desc_sw128(k_addr + koff, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
+        }
+        tc_commit(s_full);
+      };
+      if (ok && n_blocks > 0) {
+        ok = mbar_wait(&kv_full[0], 0, abort_flag, args.status, MT_ERR_TIMEOUT_FULL);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_qk(0);
+        }
+      }
+      for (int i = 0; i < n_blocks && ok; ++i) {
+        const int s = i & 1;
+        // P(i) is in shared memory and O has been rescaled
+        if (!mbar_wait(p_full, i & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(kv_s + s * (C::K_BYTES + C::V_BYTES) + C::K_BYTES);
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+          const uint32_t poff = (k >> 2) * (BLOCK_M * 128) + (k & 3) * 32;
+          tc_mma_f16(tmem_base + C::O_COL, make_smem_desc_sw128(p_addr + poff, 16, 1024),
+                     make_smem_desc_sw128(v_addr + k * (16 * 128), BN * 128, 1024), idesc_pv,
+                     (i | k) != 0 ? 1u : 0u);
+        }
+        tc_commit(&kv_empty[s]);
+        tc_commit(pv_done);
+        if (i + 1 < n_blocks) {
+          const int s2 = (i + 1) & 1;
+          if (!mbar_wait(&kv_full[s2], ((i + 1) >> 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          issue_qk(i + 1);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue (thread = query row)
+    const int r = threadIdx.x;  // 0..127
+    const int q_idx = q0 + r;
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    float m_run = -INFINITY, l_run = 0.f;
+    const float sc = args.scale;
+    const float cap = args.softcap;
+    bool ok = true;
+    for (int i = 0; i < n_blocks && ok; ++i) {
+      const int j = j_begin + i;
+      const int key0 = j * BN;
+      if (!mbar_wait_warp(s_full, i & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after_sync();
+      const bool need_mask = (args.causal && (key0 + BN - 1 > q0)) ||
+                             (args.window > 0 && (key0 <= q0 + BLOCK_M - 1 - args.window));
+      // pass 1: block row max
+      float m_blk = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_row + C::S_COL + c * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float x = __uint_as_float(v[e]) * sc;
+          if (cap > 0.f) x = cap * tanhf(x / cap);
+          if (need_mask) {
+            const int kidx = key0 + c * 32 + e;
+            const bool dead = (args.causal && kidx > q_idx) || (args.window > 0 && q_idx - kidx >= args.window);
+            if (dead) x = -INFINITY;
+          }
+          m_blk = fmaxf(m_blk, x);
+        }
+      }
+      const float m_new = fmaxf(m_run, m_blk);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_use) * kLog2e);
+      // O(i-1) must have landed before P is overwritten or O rescaled
+      if (i > 0) {
+        if (!mbar_wait_warp(pv_done, (i - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+          for (int c = 0; c < DH / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(t_row + C::O_COL + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st_32x32b_x32(t_row + C::O_COL + c * 32, o);
+          }
+          tc_wait_st();
+        }
+      }
+      // pass 2: probabilities -> bf16 -> swizzled shared memory
+      float l_blk = 0.f;
+      const float m_l2 = m_use * kLog2e;
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_row + C::S_COL + c * 32, v);
+        tc_wait_ld();
+        float p[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float x = __uint_as_float(v[e]) * sc;
+          if (cap > 0.f) x = cap * tanhf(x / cap);
+          if (need_mask) {
+            const int kidx = key0 + c * 32 + e;
+            const bool dead = (args.causal && kidx > q_idx) || (args.window > 0 && q_idx - kidx >= args.window);
+            if (dead) x = -INFINITY;
+          }
+          p[e] = exp2f(x * kLog2e - m_l2);
+          l_blk += p[e];
+        }
+        uint8_t* prow = p_s + (c >> 1) * (BLOCK_M * 128) + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack_bf16x2(p[8 * g + 0], p[8 * g + 1]);
+          w.y = pack_bf16x2(p[8 * g + 2], p[8 * g + 3]);
+          w.z = pack_bf16x2(p[8 * g + 4], p[8 * g + 5]);
+          w.w = pack_bf16x2(p[8 * g + 6], p[8 * g + 7]);
+          const int chunk = (c & 1) * 4 + g;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = w;
+        }
+      }
+      l_run = l_run * alpha + l_blk;
+      m_run = m_new;
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // epilogue: O / l -> bf16 -> staging (P region) -> TMA store ; lse
+    if (ok && n_blocks > 0) {
+      ok = mbar_wait_warp(pv_done, (n_blocks - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL);
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      // staging rows are 128 B (64 bf16) per atom; DH=128 uses two atoms: P region (>= 16 KB) + K stage 0
+      uint8_t* stage = (C::P_BYTES >= C::O_STAGE_BYTES) ? p_s : kv_s;
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t o[32];
+        if (n_blocks > 0) {
+          tmem_ld_32x32b_x32(t_row + C::O_COL + c * 32, o);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0;
+        }
+        uint8_t* orow = stage + (c >> 1) * (BLOCK_M * 128) + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(o[8 * g + 0]) * inv_l, __uint_as_float(o[8 * g + 1]) * inv_l);
+          w.y = pack_bf16x2(__uint_as_float(o[8 * g + 2]) * inv_l, __uint_as_float(o[8 * g + 3]) * inv_l);
+          w.z = pack_bf16x2(__uint_as_float(o[8 * g + 4]) * inv_l, __uint_as_float(o[8 * g + 5]) * inv_l);
+          w.w = pack_bf16x2(__uint_as_float(o[8 * g + 6]) * inv_l, __uint_as_float(o[8 * g + 7]) * inv_l);
+          const int chunk = (c & 1) * 4 + g;
+          *reinterpret_cast<uint4*>(orow + ((chunk ^ (r & 7)) << 4)) = w;
+        }
+      }
+      args.lse[(static_cast<int64_t>(b) * args.H + h) * args.S + q_idx] =
+          (l_run > 0.f) ? (m_run + logf(l_run)) : -INFINITY;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_staged);
+      // all four warps staged their rows -> one thread stores the tile (bounded wait, never a bar.sync that a
+      // warp on the error path would skip)
+      if (threadIdx.x == 0 && mbar_wait(o_staged, 0, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) {
+#pragma unroll
+        for (int a = 0; a < D_ATOMS; ++a) tma_store_3d(&tmO, stage + a * (BLOCK_M * 128), a * 64, h, tok0 + q0);
+        tma_commit_group();
+        tma_wait_group<0>();
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    __syncwarp();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+template <int DH>
+void launch_fwd(const AttnParams& p, cudaStream_t stream) {
+  using C = FwdCfg<DH>;
+  const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  const uint64_t tokens = static_cast<uint64_t>(p.B) * p.S;
+  CUtensorMap tQ = make_tmap_3d(p.q, bf, 2, tokens, p.H, DH, p.q_row_stride, DH, BLOCK_M, 1, 64, sw);
+  CUtensorMap tK = make_tmap_3d(p.k, bf, 2, tokens, p.Hkv, DH, p.k_row_stride, DH, C::BN, 1, 64, sw);
+  CUtensorMap tV = make_tmap_3d(p.v, bf, 2, tokens, p.Hkv, DH, p.v_row_stride, DH, C::BN, 1, 64, sw);
+  CUtensorMap tO = make_tmap_3d(p.o, bf, 2, tokens, p.H, DH, p.o_row_stride, DH, BLOCK_M, 1, 64, sw);
+  auto kern = flash_fwd_kernel<DH>;
+  static bool configured = false;
+  if (!configured) {
+    MT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    configured = true;
+  }
+  FwdArgs a{p.S, p.H, p.Hkv, p.causal, p.window, p.scale, p.softcap, p.lse, p.status};
+  dim3 grid(p.S / BLOCK_M, p.H, p.B);
+  kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tO, a);
+  MT_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace
+
+void flash_attn_fwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
+  (void)num_sms;
+  if (p.S % BLOCK_M != 0) throw std::runtime_error("flash_attn_fwd: sequence length must be a multiple of 128");
+  if (p.dh == 64) launch_fwd<64>(p, stream);
+  else if (p.dh == 128) launch_fwd<128>(p, stream);
+  else throw std::runtime_error("flash_attn_fwd: head_dim must be 64 or 128");
+}
+
+}  // namespace mt

@@ -151,6 +151,52 @@ void sumsq(const torch::Tensor& x, torch::Tensor& out) {
   mt::sumsq(x.data_ptr(), x.scalar_type() == torch::kFloat32, x.numel(), out.data_ptr<float>(), cur_stream());
 }
 
+mt::AttnParams attn_params(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, double scale,
+                           bool causal, int64_t window, double softcap, torch::Tensor& status) {
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "q/k/v must be [B,S,H,d]");
+  for (const auto* t : {&q, &k, &v}) {
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kBFloat16, "attention tensors must be CUDA bf16");
+    TORCH_CHECK(t->stride(3) == 1 && t->stride(2) == t->size(3), "heads must be packed along the row");
+    TORCH_CHECK(t->stride(0) == t->stride(1) * t->size(1), "batch must be contiguous in tokens");
+    TORCH_CHECK(t->stride(1) % 8 == 0 && reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0, "16-byte alignment");
+  }
+  mt::AttnParams p{};
+  p.q = q.data_ptr(); p.k = k.data_ptr(); p.v = v.data_ptr();
+  p.B = (int)q.size(0); p.S = (int)q.size(1); p.H = (int)q.size(2); p.Hkv = (int)k.size(2); p.dh = (int)q.size(3);
+  p.q_row_stride = q.stride(1); p.k_row_stride = k.stride(1); p.v_row_stride = v.stride(1);
+  p.scale = (float)scale; p.softcap = (float)softcap; p.window = (int)window; p.causal = causal ? 1 : 0;
+  p.status = status.data_ptr<int>();
+  return p;
+}
+
+void flash_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, torch::Tensor& o,
+               torch::Tensor& lse, double scale, bool causal, int64_t window, double softcap, torch::Tensor& status) {
+  mt::AttnParams p = attn_params(q, k, v, scale, causal, window, softcap, status);
+  TORCH_CHECK(o.is_contiguous() && lse.is_contiguous() && lse.scalar_type() == torch::kFloat32);
+  p.o = o.data_ptr(); p.o_row_stride = o.stride(1); p.lse = lse.data_ptr<float>();
+  c10::cuda::CUDAGuard guard(q.device());
+  mt::flash_attn_fwd(p, sm_count(), cur_stream());
+}
+
+void flash_bwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, const torch::Tensor& o,
+               const torch::Tensor& lse, const torch::Tensor& dout, torch::Tensor& dq, torch::Tensor& dk,
+               torch::Tensor& dv, torch::Tensor& dq_accum, torch::Tensor& delta, double scale, bool causal,
+               int64_t window, double softcap, torch::Tensor& status) {
+  mt::AttnParams p = attn_params(q, k, v, scale, causal, window, softcap, status);
+  TORCH_CHECK(o.is_contiguous() && dout.is_contiguous() && dq.is_contiguous() && dk.is_contiguous() && dv.is_contiguous());
+  TORCH_CHECK(dq_accum.scalar_type() == torch::kFloat32 && dq_accum.numel() == q.numel() && dq_accum.is_contiguous());
+  TORCH_CHECK(delta.scalar_type() == torch::kFloat32 && delta.numel() == lse.numel());
+  p.o = const_cast<void*>(o.data_ptr()); p.o_row_stride = o.stride(1);
+  p.lse = const_cast<float*>(lse.data_ptr<float>());
+  p.dout = dout.data_ptr(); p.do_row_stride = dout.stride(1);
+  p.dq_accum = dq_accum.data_ptr(); p.dq_out = dq.data_ptr(); p.dq_row_stride = dq.stride(1);
+  p.dk = dk.data_ptr(); p.dk_row_stride = dk.stride(1);
+  p.dv = dv.data_ptr(); p.dv_row_stride = dv.stride(1);
+  p.delta = delta.data_ptr<float>();
+  c10::cuda::CUDAGuard guard(q.device());
+  mt::flash_attn_bwd(p, sm_count(), cur_stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -165,4 +211,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_bwd", &embedding_bwd);
   m.def("adamw_step", &adamw_step);
   m.def("sumsq", &sumsq);
+  m.def("flash_fwd", &flash_fwd);
+  m.def("flash_bwd", &flash_bwd);
 }

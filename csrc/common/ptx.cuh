@@ -79,6 +79,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
+// Warp-collective bounded wait: every lane waits, then the warp votes so that all 32 lanes leave with the
+// same answer (the callers go on to execute .sync.aligned instructions and must not diverge).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int code) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ---------------------------------------------------------------- TMA (bulk tensor copies)
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -83,7 +83,7 @@ ce_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ target
     const float xt = cap(__bfloat162float(lr[tgt]), softcap);
     const float nll = lse - xt;
     const float smooth = lse - total.t / V;
-    loss[row] = (1.f - ls) * nll + ls * smooth;
+    loss[row] = (1.f - ls) * nll + ls * smooth + zw * lse * lse;
     if (zloss) zloss[row] = zw * lse * lse;
     if (lse_out) lse_out[row] = lse;
   }

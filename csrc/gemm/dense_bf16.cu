@@ -188,7 +188,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const TileCoord tc = tile_coord(tile, num_m, num_n, BN);
       const int buf = tcount & 1;
       const uint32_t acc_ph = (tcount >> 1) & 1;
-      if (!mbar_wait(&tmem_full[buf], acc_ph, abort_flag, status, MT_ERR_TIMEOUT_TMEM_FULL)) {
+      if (!mbar_wait_warp(&tmem_full[buf], acc_ph, abort_flag, status, MT_ERR_TIMEOUT_TMEM_FULL)) {
         ok = false;
         break;
       }
@@ -254,6 +254,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
+    __syncwarp();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
 }

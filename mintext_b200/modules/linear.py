@@ -1,0 +1,111 @@
+"""Linear projections and the gated MLP (reference: mintext/modules/linear.py).
+
+Kernels keep the reference's parameter-tree shapes: ``in_shape + out_shape`` with the input dims first, e.g.
+``[D, H, dh]`` for a head-expanding projection and ``[H, dh, D]`` for the contracting output projection.  The
+GEMM kernel reads ``[in, out]`` weights directly (MN-major B operand), so no transposed copy is kept.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Sequence
+
+import torch
+from torch import nn
+
+from mintext_b200.ops import functional as F
+from mintext_b200.ops import oracle
+
+
+def _as_tuple(v) -> tuple[int, ...]:
+    return tuple(v) if isinstance(v, (tuple, list)) else (int(v),)
+
+
+def truncated_normal_init(shape: Sequence[int], fan_in: int, generator: torch.Generator | None,
+                          dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Standard normal truncated to [-2, 2], times ``1/sqrt(fan_in)`` with no variance correction
+    (mintext/modules/linear.py:18-30)."""
+    t = torch.empty(tuple(shape), dtype=torch.float32)
+    nn.init.trunc_normal_(t, mean=0.0, std=1.0, a=-2.0, b=2.0, generator=generator)
+    return (t / math.sqrt(max(fan_in, 1))).to(dtype)
+
+
+def fp8_matmul_reference(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Per-tensor dynamically scaled fp8 product: activations to e4m3 with ``448/amax``, weights to e5m2 with
+    ``57344/amax``, fp32 accumulation, rescale (mintext/modules/linear.py:37-57)."""
+    xa = x.float().abs().max().clamp_min(1e-12)
+    wa = w.float().abs().max().clamp_min(1e-12)
+    sx, sw = 448.0 / xa, 57344.0 / wa
+    xq = (x.float() * sx).to(torch.float8_e4m3fn).float()
+    wq = (w.float() * sw).to(torch.float8_e5m2).float()
+    return ((xq @ wq) / (sx * sw)).to(out_dtype)
+
+
+class Linear(nn.Module):
+    """``in_features`` / ``out_features`` may be ints or tuples (head-shaped kernels)."""
+
+    def __init__(self, in_features, out_features, dtype: torch.dtype = torch.float32,
+                 weight_dtype: torch.dtype = torch.float32, kernel_axes: tuple = (), use_bias: bool = False,
+                 kernel_init_fn=None, use_fp8: bool = False, *, rngs: torch.Generator | None = None,
+                 name: str | None = None):
+        super().__init__()
+        self.in_shape = _as_tuple(in_features)
+        self.out_shape = _as_tuple(out_features)
+        self.dtype = dtype
+        self.use_fp8 = use_fp8
+        self.remat_name = name
+        fan_in = math.prod(self.in_shape)
+        shape = self.in_shape + self.out_shape
+        init = kernel_init_fn or truncated_normal_init
+        self.kernel = nn.Parameter(init(shape, fan_in, rngs, weight_dtype))
+        self.kernel.logical_axes = tuple(kernel_axes)
+        if use_bias:
+            self.bias = nn.Parameter(torch.zeros(self.out_shape, dtype=weight_dtype))
+            self.bias.logical_axes = tuple(kernel_axes[len(self.in_shape):])
+        else:
+            self.bias = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        n_in = len(self.in_shape)
+        lead = x.shape[: x.dim() - n_in]
+        fan_in = math.prod(self.in_shape)
+        x2 = x.reshape(*lead, fan_in)
+        w2 = self.kernel.reshape(fan_in, -1) if self.kernel.dim() != 2 else self.kernel
+        if self.use_fp8 and self.kernel.dim() == 2:
+            y = fp8_matmul_reference(x2.reshape(-1, fan_in), w2, self.dtype).reshape(*lead, -1)
+            if self.bias is not None:
+                y = y + self.bias.to(y.dtype).reshape(-1)
+        else:
+            if w2 is not self.kernel and hasattr(self.kernel, "main_grad"):
+                w2.main_grad = self.kernel.main_grad
+            y = F.linear(x2, w2, None if self.bias is None else self.bias.reshape(-1), name=self.remat_name,
+                         dtype=self.dtype)
+        return y.reshape(*lead, *self.out_shape)
+
+
+class MLP(nn.Module):
+    """Gated feed-forward ``down(act(gate(x)) * up(x))`` (mintext/modules/linear.py:174-228).
+
+    ``gate`` and ``up`` are separate parameters (``[D, M]`` each) as in the reference tree.
+    """
+
+    def __init__(self, config, *, rngs: torch.Generator | None = None, mesh=None, intermediate_size: int | None = None):
+        super().__init__()
+        D = config.hidden_size
+        M = intermediate_size or config.intermediate_size
+        dt, wdt = config.torch_dtype, config.torch_weight_dtype
+        self.act_name = config.hidden_activation
+        fp8 = bool(config.use_fp8)
+        self.gate = Linear(D, M, dt, wdt, ("embed", "mlp"), use_fp8=fp8, rngs=rngs, name="mlp_gate_proj")
+        self.up = Linear(D, M, dt, wdt, ("embed", "mlp"), use_fp8=fp8, rngs=rngs, name="mlp_up")
+        self.down = Linear(M, D, dt, wdt, ("mlp", "embed"), use_fp8=fp8, rngs=rngs, name="mlp_down")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.gate.use_fp8:
+            h = oracle.activation(self.act_name)(self.gate(x)) * self.up(x)
+        else:
+            h = F.gate_up_act(x, self.gate.kernel, self.up.kernel, self.act_name, dtype=self.gate.dtype)
+        return self.down(h)
+
+
+ACT2FN = {name: oracle.activation(name) for name in ("silu", "gelu", "gelu_pytorch_tanh", "relu")}

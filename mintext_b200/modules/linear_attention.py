@@ -1,0 +1,88 @@
+"""Gated Delta Rule linear attention (Qwen3-Next GDN; reference: mintext/modules/linear_attention.py)."""
+
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from mintext_b200.ops import oracle
+
+from .linear import Linear
+from .norm import RMSNorm
+
+
+def chunk_gated_delta_rule(q, k, v, beta, g, chunk_size: int = 64):
+    """q,k ``[B,H,S,dk]``, v ``[B,H,S,dv]``, beta,g ``[B,H,S]`` -> ``[B,H,S,dv]`` (fp32)."""
+    from mintext_b200.ops import gdn
+
+    if gdn.cuda_path(q):
+        return gdn.chunk_gated_delta_rule_cuda(q, k, v, beta, g, chunk_size)
+    return oracle.chunk_gated_delta_rule(q, k, v, beta, g, chunk_size)
+
+
+class GatedDeltaRuleAttention(nn.Module):
+    def __init__(self, config, *, rngs=None):
+        super().__init__()
+        self.dtype = dt = config.torch_dtype
+        wdt = config.torch_weight_dtype
+        D = config.hidden_size
+        self.num_k_heads = Hk = config.linear_num_key_heads or config.num_attention_heads
+        self.num_v_heads = Hv = config.linear_num_value_heads or config.num_attention_heads
+        self.key_head_dim = dk = config.linear_key_head_dim
+        self.value_head_dim = dv = config.linear_value_head_dim
+        self.v_heads_per_k_group = Hv // Hk
+        self.chunk_size = 64
+        key_dim, value_dim = Hk * dk, Hv * dv
+        conv_dim = 2 * key_dim + value_dim
+        self.in_proj_qkvz = Linear(D, 2 * key_dim + 2 * value_dim, dt, wdt, ("embed", "mlp"), rngs=rngs)
+        self.in_proj_ba = Linear(D, 2 * Hv, dt, wdt, ("embed", "mlp"), rngs=rngs)
+        ksz = config.linear_conv_kernel_dim
+        self.conv_weight = nn.Parameter((torch.randn(conv_dim, 1, ksz, generator=rngs) * 0.02).to(wdt))
+        self.conv_weight.logical_axes = (None, None, None)
+        self.A_log = nn.Parameter(torch.log(0.5 + torch.rand(Hv, generator=rngs) * 15.5))
+        self.A_log.logical_axes = (None,)
+        self.dt_bias = nn.Parameter(torch.ones(Hv))
+        self.dt_bias.logical_axes = (None,)
+        self.norm = RMSNorm(dv, config.rms_norm_eps, dt)
+        self.out_proj = Linear(value_dim, D, dt, wdt, ("mlp", "embed"), rngs=rngs)
+
+    def _split_qkvz(self, qkvz: torch.Tensor):
+        """HF grouped layout: per key head ``[q(dk) | k(dk) | v(g*dv) | z(g*dv)]``."""
+        B, S, _ = qkvz.shape
+        vg = self.v_heads_per_k_group * self.value_head_dim
+        grouped = qkvz.reshape(B, S, self.num_k_heads, 2 * self.key_head_dim + 2 * vg)
+        q, k, v, z = grouped.split([self.key_head_dim, self.key_head_dim, vg, vg], dim=-1)
+        v = v.reshape(B, S, self.num_v_heads, self.value_head_dim)
+        z = z.reshape(B, S, self.num_v_heads, self.value_head_dim)
+        return q, k, v, z
+
+    def _split_ba(self, ba: torch.Tensor):
+        B, S, _ = ba.shape
+        g = self.v_heads_per_k_group
+        grouped = ba.reshape(B, S, self.num_k_heads, 2 * g)
+        b, a = grouped.split([g, g], dim=-1)
+        return b.reshape(B, S, self.num_v_heads), a.reshape(B, S, self.num_v_heads)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        B, S, _ = x.shape
+        q, k, v, z = self._split_qkvz(self.in_proj_qkvz(x))
+        b_raw, a = self._split_ba(self.in_proj_ba(x))
+        beta = torch.sigmoid(b_raw.float())
+        key_total = self.num_k_heads * self.key_head_dim
+        value_total = self.num_v_heads * self.value_head_dim
+        qkv = torch.cat([q.reshape(B, S, key_total), k.reshape(B, S, key_total), v.reshape(B, S, value_total)], dim=-1)
+        qkv = torch.nn.functional.silu(oracle.causal_conv1d(qkv, self.conv_weight.to(self.dtype)))
+        qc, kc, vc = qkv.split([key_total, key_total, value_total], dim=-1)
+        qh = qc.reshape(B, S, self.num_k_heads, self.key_head_dim)
+        kh = kc.reshape(B, S, self.num_k_heads, self.key_head_dim)
+        vh = vc.reshape(B, S, self.num_v_heads, self.value_head_dim)
+        g = -torch.exp(self.A_log.float()) * torch.nn.functional.softplus(a.float() + self.dt_bias.float())
+        if self.v_heads_per_k_group > 1:
+            qh = qh.repeat_interleave(self.v_heads_per_k_group, dim=2)
+            kh = kh.repeat_interleave(self.v_heads_per_k_group, dim=2)
+        out = chunk_gated_delta_rule(
+            qh.float().transpose(1, 2), kh.float().transpose(1, 2), vh.float().transpose(1, 2),
+            beta.transpose(1, 2), g.transpose(1, 2), chunk_size=self.chunk_size)
+        out = out.transpose(1, 2).to(self.dtype)
+        out = self.norm(out.contiguous()) * torch.nn.functional.silu(z.to(self.dtype))
+        return self.out_proj(out.reshape(B, S, value_total))

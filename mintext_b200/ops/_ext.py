@@ -40,6 +40,10 @@ def _load(name: str):
         spec = importlib.util.spec_from_file_location(name, path)
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
+        if name == "_mt_C":
+            from . import launch_counter
+
+            launch_counter.install(mod)
         _mods[name] = mod
         return mod
 

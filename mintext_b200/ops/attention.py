@@ -1,0 +1,50 @@
+"""Flash-attention front-end: autograd wrapper around the tcgen05 forward / backward kernels."""
+
+from __future__ import annotations
+
+import torch
+
+from ._ext import ext, status_word
+
+
+def flash_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    """The forward kernel covers head dims 64 and 128, the backward kernel 64; training therefore takes the
+    kernel path for bf16, head_dim 64 and sequence lengths that are multiples of 128, anything else the oracle."""
+    if not hasattr(ext(), "flash_fwd"):
+        return False
+    d = q.shape[-1]
+    return (q.dtype == torch.bfloat16 and d == 64 and k.shape[-1] == d and v.shape[-1] == d
+            and q.shape[1] % 128 == 0 and k.shape[1] == q.shape[1] and q.shape[2] % k.shape[2] == 0)
+
+
+class _FlashFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale, causal, window, softcap):
+        B, S, H, d = q.shape
+        o = torch.empty(B, S, H, d, device=q.device, dtype=torch.bfloat16)
+        lse = torch.empty(B, H, S, device=q.device, dtype=torch.float32)
+        ext().flash_fwd(q, k, v, o, lse, float(scale), bool(causal), int(window or 0), float(softcap or 0.0),
+                        status_word(q.device))
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.meta = (float(scale), bool(causal), int(window or 0), float(softcap or 0.0))
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        scale, causal, window, softcap = ctx.meta
+        do = do.contiguous()
+        B, S, H, d = q.shape
+        dq = torch.empty(B, S, H, d, device=q.device, dtype=q.dtype)
+        dk = torch.empty(B, S, k.shape[2], d, device=q.device, dtype=q.dtype)
+        dv = torch.empty(B, S, k.shape[2], d, device=q.device, dtype=q.dtype)
+        dq_accum = torch.empty(B * S, H, d, device=q.device, dtype=torch.float32)  # cleared by the pre-pass
+        delta = torch.empty_like(lse)
+        ext().flash_bwd(q, k, v, o, lse, do, dq, dk, dv, dq_accum, delta, scale, causal, window, softcap,
+                        status_word(q.device))
+        return dq, dk, dv, None, None, None, None
+
+
+def flash_attention(q, k, v, scale, causal=True, window=None, softcap=None):
+    """q ``[B,S,H,d]``, k/v ``[B,S,Hkv,d]`` (any row pitch, unit inner stride) -> ``[B,S,H,d]``."""
+    return _FlashFn.apply(q, k, v, scale, causal, window, softcap)

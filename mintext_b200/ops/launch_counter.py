@@ -1,0 +1,37 @@
+"""Counts launches of this repository's kernels (every call through the extension is one or more launches).
+
+The extension module is wrapped once so that each bound function increments a counter by the number of kernels
+it enqueues; the benchmark reports the difference over its timed region.
+"""
+
+from __future__ import annotations
+
+_LAUNCHES_PER_CALL = {
+    "gemm": 1, "rmsnorm_fwd": 1, "rmsnorm_bwd": 2, "rope": 1, "gated_act_fwd": 1, "gated_act_bwd": 1,
+    "cross_entropy": 1, "embedding_fwd": 1, "embedding_bwd": 1, "adamw_step": 1, "sumsq": 1, "flash_fwd": 1,
+    "flash_bwd": 3,
+}
+_count = 0
+_installed = False
+
+
+def install(mod) -> None:
+    global _installed
+    if _installed:
+        return
+    for name, n in _LAUNCHES_PER_CALL.items():
+        fn = getattr(mod, name, None)
+        if fn is None:
+            continue
+
+        def wrapped(*a, _fn=fn, _n=n, **k):
+            global _count
+            _count += _n
+            return _fn(*a, **k)
+
+        setattr(mod, name, wrapped)
+    _installed = True
+
+
+def count() -> int:
+    return _count

@@ -1,0 +1,301 @@
+"""B200 training engine: flat parameter / gradient storage, sharded fused optimizer, device-timed steps.
+
+Memory plan (sized for 180 GB of HBM3e per GPU): every rank keeps the *whole* bf16 compute copy of the
+parameters resident in one flat buffer (a 1 B model is 2.5 GB, an 8 B model 16 GB), so forward and backward
+never wait for a parameter gather.  What is sharded ``1/N`` over the ``data x fsdp`` ranks is everything that is
+only touched once per step: the fp32 master weights and both Adam moments.  Gradients accumulate in one flat
+fp32 buffer that the wgrad GEMM epilogues add into directly (no per-parameter ``.grad`` tensors, no cast pass).
+
+One optimizer step is then
+  1. reduce-scatter of the flat fp32 gradient (each rank ends up with the sum of its shard),
+  2. the global gradient norm from per-shard sums of squares (one scalar all-reduce),
+  3. the fused AdamW kernel on the shard (clip factor, moments, master update, bf16 cast in one pass),
+  4. all-gather of the updated bf16 shard into every rank's compute buffer.
+With ``fused_collectives`` steps 1 and 3+4 run as this repository's peer-memory kernels (pull-reduce over
+NVLink, update, push to every peer); otherwise they are NCCL reduce-scatter / all-gather around the same AdamW
+kernel.  Small fp32 parameters (norm scales, gate biases ...) are replicated and updated redundantly from
+all-reduced gradients.
+
+The rule for which GPU holds which batch rows: the global batch is split evenly over all ranks of the
+``data`` and ``fsdp`` axes (true FSDP, unlike the reference, which replicates the batch over ``fsdp``).
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from mintext_b200.ops._ext import check_status, ext
+from mintext_b200.optim.optimizer import create_lr_schedule, weight_decay_mask
+
+_ALIGN = 64  # elements; keeps every parameter view 128-byte aligned for TMA
+
+
+@dataclass
+class _Slot:
+    name: str
+    param: torch.nn.Parameter
+    offset: int
+    numel: int
+
+
+class FlatGroup:
+    """Parameters of one kind laid out back to back in flat buffers."""
+
+    def __init__(self, slots: list[_Slot], total: int):
+        self.slots = slots
+        self.total = total
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class TrainEngine:
+    """Owns the device copies of a model's parameters and runs optimizer steps on them.
+
+    ``model`` must have been built on the CPU in ``weight_dtype`` (fp32); the engine moves it to ``device``,
+    re-homes every parameter into the flat buffers and keeps the fp32 values as (sharded) master weights.
+    """
+
+    def __init__(self, model: torch.nn.Module, config, device: torch.device | str = "cuda", group=None):
+        self.config = config
+        self.model = model
+        self.device = torch.device(device)
+        self.group = group
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.schedule = create_lr_schedule(config)
+        self.step_count = 0
+        self.compute_dtype = config.torch_dtype
+        self._build_storage()
+        self.use_fused = bool(config.fused_collectives) and self.world > 1 and config.optimizer == "adamw"
+        self._comm = None
+        if self.use_fused:
+            try:
+                from mintext_b200.parallel.symm import SymmetricOptimizerComm
+
+                self._comm = SymmetricOptimizerComm(self)
+            except Exception as e:  # fall back to the NCCL composition, loudly
+                import logging
+
+                logging.getLogger(__name__).warning("peer-memory optimizer path unavailable (%s); using NCCL", e)
+                self.use_fused = False
+        self._sumsq = torch.zeros(1, device=self.device, dtype=torch.float32)
+        self._clip = torch.ones(1, device=self.device, dtype=torch.float32)
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ storage
+    def _build_storage(self) -> None:
+        cfg = self.config
+        dev = self.device
+        big: list[_Slot] = []
+        small: list[_Slot] = []
+        frozen: list[tuple[str, torch.nn.Parameter]] = []
+        off_b = off_s = 0
+        for name, p in self.model.named_parameters():
+            if not p.requires_grad:
+                frozen.append((name, p))
+                continue
+            is_big = p.dim() >= 2 and p.numel() >= 4096 and "conv_weight" not in name
+            if is_big and self.compute_dtype == torch.bfloat16:
+                big.append(_Slot(name, p, off_b, p.numel()))
+                off_b = _round_up(off_b + p.numel(), _ALIGN)
+            else:
+                small.append(_Slot(name, p, off_s, p.numel()))
+                off_s = _round_up(off_s + p.numel(), _ALIGN)
+        shard_quantum = self.world * 1024
+        total_b = _round_up(max(off_b, 1), shard_quantum)
+        self.big = FlatGroup(big, total_b)
+        self.small = FlatGroup(small, _round_up(max(off_s, 1), _ALIGN))
+        self.shard_size = total_b // self.world
+        lo = self.rank * self.shard_size
+
+        # fp32 master values come from the model's initialisation
+        master_full = torch.zeros(total_b, dtype=torch.float32)
+        for s in big:
+            master_full[s.offset:s.offset + s.numel] = s.param.detach().float().reshape(-1)
+        self.param_flat = self._alloc_symmetric(total_b, torch.bfloat16)
+        self.param_flat.copy_(master_full.to(torch.bfloat16))
+        self.grad_flat = self._alloc_symmetric(total_b, torch.float32)
+        self.grad_flat.zero_()
+        self.master = master_full[lo:lo + self.shard_size].to(dev)
+        self.exp_avg = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
+        self.exp_avg_sq = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
+        self.grad_shard = torch.empty(self.shard_size, device=dev, dtype=torch.float32)
+        # per-element weight decay is uniform over the big group (only the router bias is exempt and it is frozen)
+        for s in big:
+            s.param.data = self.param_flat[s.offset:s.offset + s.numel].view(s.param.shape)
+            s.param.main_grad = self.grad_flat[s.offset:s.offset + s.numel].view(s.param.shape)
+
+        self.small_param = torch.zeros(self.small.total, device=dev, dtype=torch.float32)
+        self.small_grad = torch.zeros(self.small.total, device=dev, dtype=torch.float32)
+        self.small_m = torch.zeros_like(self.small_param)
+        self.small_v = torch.zeros_like(self.small_param)
+        for s in small:
+            self.small_param[s.offset:s.offset + s.numel] = s.param.detach().float().reshape(-1).to(dev)
+            s.param.data = self.small_param[s.offset:s.offset + s.numel].view(s.param.shape)
+            s.param.main_grad = self.small_grad[s.offset:s.offset + s.numel].view(s.param.shape)
+        for _, p in frozen:
+            p.data = p.data.to(dev)
+        for b in self.model.buffers():
+            b.data = b.data.to(dev)
+        self.small_wd = torch.ones(self.small.total, device=dev, dtype=torch.float32)
+        for s in small:
+            if not weight_decay_mask(s.name):
+                self.small_wd[s.offset:s.offset + s.numel] = 0.0
+
+    def _alloc_symmetric(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """Flat buffers live in symmetric (peer-mappable) memory when the peer-memory path may be used."""
+        if self.world > 1 and bool(self.config.fused_collectives):
+            try:
+                import torch.distributed._symmetric_memory as symm
+
+                return symm.empty(numel, dtype=dtype, device=self.device)
+            except Exception:
+                pass
+        return torch.empty(numel, dtype=dtype, device=self.device)
+
+    # ------------------------------------------------------------------ helpers
+    def named_master_parameters(self) -> dict[str, torch.Tensor]:
+        """Full fp32 master tensors by name (gathers the shards; used by checkpointing and tests)."""
+        if self.world > 1:
+            full = torch.empty(self.big.total, device=self.device, dtype=torch.float32)
+            dist.all_gather_into_tensor(full, self.master, group=self.group)
+        else:
+            full = self.master
+        out = {s.name: full[s.offset:s.offset + s.numel].view(s.param.shape).clone() for s in self.big.slots}
+        for s in self.small.slots:
+            out[s.name] = s.param.detach().clone()
+        for n, p in self.model.named_parameters():
+            if n not in out:
+                out[n] = p.detach().clone()
+        return out
+
+    def zero_grad(self) -> None:
+        self.grad_flat.zero_()
+        self.small_grad.zero_()
+
+    def _fold_autograd_grads(self) -> None:
+        """Parameters whose ops returned ordinary autograd gradients: add them into the flat buffers."""
+        for grp in (self.big, self.small):
+            for s in grp.slots:
+                g = s.param.grad
+                if g is not None:
+                    s.param.main_grad.add_(g.to(torch.float32))
+                    s.param.grad = None
+
+    # ------------------------------------------------------------------ step
+    def backward(self, loss: torch.Tensor) -> None:
+        loss.backward()
+        self._fold_autograd_grads()
+
+    def optimizer_step(self, num_micro: int = 1) -> dict:
+        """Reduce gradients, clip, update, re-publish bf16 weights.  Returns device scalars."""
+        cfg = self.config
+        e = ext()
+        W = self.world
+        inv = 1.0 / (num_micro * W)  # micro-batch losses are means over local tokens
+        lr = float(self.schedule(self.step_count))
+        self.step_count += 1
+        t = self.step_count
+        bc1 = 1.0 - cfg.adam_b1 ** t
+        bc2 = 1.0 - cfg.adam_b2 ** t
+
+        # 1. gradient reduction
+        if W > 1:
+            if self.use_fused:
+                self._comm.reduce_scatter_grads(self.grad_shard)
+            else:
+                dist.reduce_scatter_tensor(self.grad_shard, self.grad_flat, group=self.group)
+            dist.all_reduce(self.small_grad, group=self.group)
+            gshard = self.grad_shard
+        else:
+            gshard = self.grad_flat
+        # 2. global norm of the averaged gradient
+        self._sumsq.zero_()
+        e.sumsq(gshard, self._sumsq)
+        if W > 1:
+            dist.all_reduce(self._sumsq, group=self.group)
+        e.sumsq(self.small_grad, self._sumsq)
+        grad_norm = torch.sqrt(self._sumsq) * inv
+        if cfg.gradient_clip_threshold > 0:
+            thr = float(cfg.gradient_clip_threshold)
+            torch.div(thr, torch.clamp(grad_norm, min=thr), out=self._clip)
+        else:
+            self._clip.fill_(1.0)
+        # 3. fused AdamW on the shard (+ 4. publication of the bf16 copy)
+        lo = self.rank * self.shard_size
+        pshard = self.param_flat[lo:lo + self.shard_size]
+        if W > 1 and self.use_fused:
+            self._comm.adamw_and_publish(gshard, lr, bc1, bc2, inv, self._clip)
+        else:
+            e.adamw_step(self.master, self.exp_avg, self.exp_avg_sq, gshard, pshard, lr, cfg.adam_b1, cfg.adam_b2,
+                         cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)
+            if W > 1:
+                dist.all_gather_into_tensor(self.param_flat, pshard, group=self.group)
+        self._small_adamw(lr, bc1, bc2, inv)
+        self.kernel_launches += 4
+        return {"grad_norm": grad_norm, "learning_rate": lr}
+
+    def _small_adamw(self, lr, bc1, bc2, inv) -> None:
+        cfg = self.config
+        g = self.small_grad * (inv * self._clip)
+        self.small_m.mul_(cfg.adam_b1).add_(g, alpha=1 - cfg.adam_b1)
+        self.small_v.mul_(cfg.adam_b2).addcmul_(g, g, value=1 - cfg.adam_b2)
+        upd = (self.small_m / bc1) / ((self.small_v / bc2).sqrt() + cfg.adam_eps)
+        self.small_param.add_(upd + cfg.weight_decay * self.small_wd * self.small_param, alpha=-lr)
+
+    def param_norm(self) -> torch.Tensor:
+        s = torch.zeros(1, device=self.device, dtype=torch.float32)
+        ext().sumsq(self.master, s)
+        if self.world > 1:
+            dist.all_reduce(s, group=self.group)
+        ext().sumsq(self.small_param, s)
+        return torch.sqrt(s)
+
+    def train_step(self, batch: dict, num_micro: int | None = None) -> dict:
+        """``batch`` holds this rank's rows (``[B_local, S]`` token tensors on the device).  Runs ``num_micro``
+        micro-batches (default ``gradient_accumulation_steps``), then one optimizer step."""
+        from mintext_b200.trainer import compute_loss
+
+        cfg = self.config
+        n = num_micro or int(cfg.gradient_accumulation_steps)
+        B = batch["input_tokens"].shape[0]
+        mb = B // n
+        self.zero_grad()
+        loss_sum = torch.zeros((), device=self.device, dtype=torch.float32)
+        counts = None
+        for i in range(n):
+            micro = {k: v[i * mb:(i + 1) * mb] for k, v in batch.items()}
+            loss, aux = compute_loss(None, self.model, cfg, micro)
+            self.backward(loss)
+            loss_sum += loss.detach().float()
+            if aux.get("moe_expert_counts") is not None:
+                counts = aux["moe_expert_counts"] if counts is None else counts + aux["moe_expert_counts"]
+        pnorm = self.param_norm()
+        out = self.optimizer_step(n)
+        loss_mean = loss_sum / n
+        if self.world > 1:
+            dist.all_reduce(loss_mean, group=self.group)
+            loss_mean /= self.world
+            if counts is not None:
+                dist.all_reduce(counts, group=self.group)
+        out.update({"loss": loss_mean, "param_norm": pnorm, "moe_expert_counts": counts, "z_loss": aux["z_loss"]})
+        return out
+
+    def check(self) -> None:
+        """Raise if any kernel recorded a bounded-wait expiry since the last check (synchronises)."""
+        check_status(self.device)
+
+
+def local_batch_rows(global_batch: int, world: int, rank: int) -> tuple[int, int]:
+    """Row range of the global batch that ``rank`` of ``world`` data-parallel ranks processes."""
+    if global_batch % world != 0:
+        raise ValueError(f"global batch {global_batch} is not divisible by {world} ranks")
+    per = global_batch // world
+    return rank * per, (rank + 1) * per

@@ -1,0 +1,185 @@
+"""Loss functions, train / eval steps and the train state (reference: mintext/trainer.py).
+
+This module is the device-agnostic statement of a training step: it works on any model built from
+:mod:`mintext_b200.models` with ordinary autograd and the per-tensor optimizer, which is what the CPU plumbing
+config and the unit tests run.  On B200 the same loss code runs under :class:`mintext_b200.parallel.engine.
+TrainEngine`, which replaces the optimizer step with the fused, sharded kernels.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+from mintext_b200.models.transformer import make_causal_mask
+from mintext_b200.ops import functional as F
+from mintext_b200.ops import oracle
+from mintext_b200.optim import accumulate_gradients, create_lr_schedule, create_optimizer
+
+
+@dataclass
+class TrainState:
+    """``step`` counts optimizer updates; ``params`` is the model's ``{dotted name: Parameter}`` dict (the same
+    tensors the model computes with); ``opt_state`` and ``tx`` belong to the optimizer."""
+
+    step: int
+    params: dict[str, torch.Tensor]
+    opt_state: Any
+    tx: Any
+
+    def state_dict(self) -> dict:
+        return {"step": self.step, "params": self.params, "opt_state": {
+            "count": self.opt_state.count, "mu": self.opt_state.mu, "nu": self.opt_state.nu}}
+
+
+# ------------------------------------------------------------------------------------------ losses
+def cross_entropy_with_z_loss(logits: torch.Tensor, targets: torch.Tensor, label_smoothing: float = 0.0,
+                              z_loss_weight: float = 0.0):
+    """Per-token ``(loss incl. z-loss, z-loss)`` from fp32 log-softmax."""
+    return oracle.cross_entropy(logits, targets, label_smoothing, z_loss_weight)
+
+
+def cross_entropy_loss(logits: torch.Tensor, targets: torch.Tensor, label_smoothing: float = 0.0,
+                       z_loss_weight: float = 0.0):
+    """logits ``[B,S,V]``, targets ``[B,S]`` -> ``(loss [B,S], z_loss [B,S])``."""
+    return oracle.cross_entropy(logits, targets, label_smoothing, z_loss_weight)
+
+
+def chunked_cross_entropy_loss(hidden: torch.Tensor, targets: torch.Tensor, output_proj, num_tiles: int,
+                               label_smoothing: float = 0.0, z_loss_weight: float = 0.0):
+    """Project-and-score ``num_tiles`` token chunks one at a time so the full ``[N,V]`` logits never exist.
+    ``output_proj`` maps ``[n,D] -> [n,V]``."""
+    N = hidden.shape[0]
+    step = N // num_tiles
+    losses, zs = [], []
+    for i in range(num_tiles):
+        sl = slice(i * step, (i + 1) * step if i < num_tiles - 1 else N)
+        l, z = oracle.cross_entropy(output_proj(hidden[sl]), targets[sl], label_smoothing, z_loss_weight)
+        losses.append(l)
+        zs.append(z)
+    return torch.cat(losses), torch.cat(zs)
+
+
+def _l2_norm(tensors) -> torch.Tensor:
+    ts = [t for t in tensors if t is not None]
+    return torch.sqrt(sum((t.detach().float() ** 2).sum() for t in ts))
+
+
+# ------------------------------------------------------------------------------------------ loss
+def compute_loss(params, model, config, batch, loss_scale: float | None = None):
+    """Forward + loss on one batch ``{"input_tokens", "target_tokens"}`` ``[B,S]``.
+
+    Returns ``(loss, aux)`` with ``aux = {loss, z_loss, per_token_loss, moe_expert_counts}``.  The loss is the
+    mean over all ``B*S`` tokens (no padding mask).  ``params`` is accepted for signature parity; the model
+    already computes with those tensors.
+    """
+    tokens, targets = batch["input_tokens"], batch["target_tokens"]
+    B, S = tokens.shape
+    mask = None
+    if config.attn_logit_softcapping is not None and not tokens.is_cuda:
+        mask = make_causal_mask(S).to(tokens.device)
+    fused = F.use_cuda(model.final_norm.scale.new_empty(0, dtype=config.torch_dtype)) and tokens.is_cuda
+    hidden_mode = fused or config.num_vocab_tiles > 1
+    out, aux_list = model(tokens, None, mask, return_hidden=hidden_mode)
+    ntok = B * S
+    scale = loss_scale if loss_scale is not None else 1.0 / ntok
+    if fused:
+        w, is_vd = model.output_weight()
+        per_tok, z = F.linear_cross_entropy(
+            out.reshape(ntok, -1), w, targets.reshape(-1), weight_is_vd=is_vd,
+            label_smoothing=config.label_smoothing, z_loss_weight=config.z_loss_weight,
+            softcap=config.final_logit_softcapping, loss_scale=scale)
+        per_tok, z = per_tok.view(B, S), z.view(B, S)
+        loss = per_tok.sum() * scale
+    elif config.num_vocab_tiles > 1:
+        w, is_vd = model.output_weight()
+        cap = config.final_logit_softcapping
+
+        def proj(h):
+            lg = F.linear_nt(h, w, dtype=config.torch_dtype) if is_vd else F.linear(h, w, dtype=config.torch_dtype)
+            return torch.tanh(lg / cap) * cap if cap is not None else lg
+
+        per_tok, z = chunked_cross_entropy_loss(out.reshape(ntok, -1), targets.reshape(-1), proj,
+                                                config.num_vocab_tiles, config.label_smoothing,
+                                                config.z_loss_weight)
+        per_tok, z = per_tok.view(B, S), z.view(B, S)
+        loss = per_tok.mean()
+    else:
+        per_tok, z = cross_entropy_loss(out, targets, config.label_smoothing, config.z_loss_weight)
+        loss = per_tok.mean()
+    counts = []
+    aux_loss = None
+    for aux in aux_list:
+        if aux is None:
+            continue
+        counts.append(torch.bincount(aux["topk_indices"].reshape(-1), minlength=config.num_experts))
+        if "aux_loss" in aux and config.router_aux_loss_coef > 0:
+            aux_loss = aux["aux_loss"] if aux_loss is None else aux_loss + aux["aux_loss"]
+    if aux_loss is not None:
+        loss = loss + config.router_aux_loss_coef * aux_loss * (scale * ntok)
+    out_aux = {
+        "loss": loss.detach(),
+        "z_loss": z.detach().mean(),
+        "per_token_loss": per_tok.detach(),
+        "moe_expert_counts": torch.stack(counts) if counts else None,
+    }
+    return loss, out_aux
+
+
+# ------------------------------------------------------------------------------------------ steps
+def create_train_state(model, config) -> TrainState:
+    params = dict(model.named_parameters())
+    tx = create_optimizer(config)
+    trainable = {n: p for n, p in params.items() if p.requires_grad}
+    return TrainState(step=0, params=params, opt_state=tx.init(trainable), tx=tx)
+
+
+def train_step(state: TrainState, batch, model, config):
+    """One optimizer update.  Metrics: ``loss``, ``z_loss``, ``learning_rate`` (schedule value at the
+    pre-update step), ``grad_norm`` (before clipping), ``param_norm`` (before the update), ``moe_expert_counts``."""
+    trainable = {n: p for n, p in state.params.items() if p.requires_grad}
+    n_acc = int(config.gradient_accumulation_steps)
+    if n_acc > 1:
+        loss, aux, grads = accumulate_gradients(
+            lambda _p, mb: compute_loss(_p, model, config, mb), trainable, batch, n_acc)
+    else:
+        loss, aux = compute_loss(state.params, model, config, batch)
+        got = torch.autograd.grad(loss, list(trainable.values()), allow_unused=True)
+        grads = dict(zip(trainable, got))
+        loss = loss.detach()
+    grad_norm = _l2_norm(grads.values())
+    param_norm = _l2_norm(state.params.values())
+    lr = create_lr_schedule(config)(state.step)
+    state.tx.update(trainable, grads, state.opt_state, state.step)
+    state.step += 1
+    metrics = {
+        "loss": loss,
+        "z_loss": aux["z_loss"],
+        "learning_rate": lr,
+        "grad_norm": grad_norm,
+        "param_norm": param_norm,
+        "moe_expert_counts": aux.get("moe_expert_counts"),
+    }
+    return state, metrics
+
+
+@torch.no_grad()
+def eval_step(state: TrainState, batch, model, config) -> dict:
+    loss, _ = compute_loss(state.params, model, config, batch)
+    return {"eval_loss": loss.detach()}
+
+
+@torch.no_grad()
+def update_expert_biases(state: TrainState, expert_counts: torch.Tensor | None, config) -> TrainState:
+    """Loss-free balancing: per MoE layer (in layer order) ``bias += rate * sign(mean_count - count)``."""
+    if expert_counts is None:
+        return state
+    rate = config.e_score_correction_bias_update_rate
+    names = sorted((n for n in state.params if n.endswith("e_score_correction_bias")),
+                   key=lambda n: int(n.split(".")[1]))
+    for name, counts in zip(names, expert_counts):
+        c = counts.float()
+        state.params[name].add_(rate * torch.sign(c.mean() - c).to(state.params[name].device))
+    return state

@@ -1,0 +1,54 @@
+"""Step-window profiler (reference: mintext/utils/profiling.py, which wraps jax.profiler).
+
+Traces steps ``[skip_first_n_profiler_steps, skip_first_n_profiler_steps + profiler_steps)`` with
+``torch.profiler`` (CPU + CUDA activities) and writes a Chrome trace under ``<base>/<run>/profiles``.
+"""
+
+from __future__ import annotations
+
+import logging
+from pathlib import Path
+
+logger = logging.getLogger(__name__)
+
+
+class Profiler:
+    def __init__(self, config):
+        self.enabled = bool(config.enable_profiler)
+        self.start_step = int(config.skip_first_n_profiler_steps)
+        self.end_step = self.start_step + int(config.profiler_steps)
+        self.output_dir = str(Path(config.base_output_directory) / config.run_name / "profiles")
+        self.active = False
+        self._prof = None
+
+    def maybe_activate(self, step: int) -> None:
+        if self.enabled and not self.active and step == self.start_step:
+            self._start()
+
+    def maybe_deactivate(self, step: int) -> None:
+        if self.active and step + 1 >= self.end_step:
+            self.stop()
+
+    def _start(self) -> None:
+        import torch
+
+        Path(self.output_dir).mkdir(parents=True, exist_ok=True)
+        acts = [torch.profiler.ProfilerActivity.CPU]
+        if torch.cuda.is_available():
+            acts.append(torch.profiler.ProfilerActivity.CUDA)
+        self._prof = torch.profiler.profile(activities=acts)
+        self._prof.__enter__()
+        self.active = True
+        logger.info("Profiler started, writing to %s", self.output_dir)
+
+    def stop(self) -> None:
+        if not self.active:
+            return
+        self._prof.__exit__(None, None, None)
+        try:
+            self._prof.export_chrome_trace(str(Path(self.output_dir) / "trace.json"))
+        except Exception as e:  # pragma: no cover
+            logger.warning("could not export trace: %s", e)
+        self._prof = None
+        self.active = False
+        logger.info("Profiler stopped")

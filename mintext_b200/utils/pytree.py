@@ -1,0 +1,72 @@
+"""Parameter counting, NaN checks and the analytic FLOP / token accounting used for TFLOP/s and MFU
+(reference: mintext/utils/pytree.py).
+
+The FLOP count deliberately matches the reference's MaxText-style formula term by term (it ignores linear-
+attention layers, sliding windows and shared experts, and prices MLA scores with ``head_dim``), because MFU is
+only comparable when both sides use the same numerator.
+"""
+
+from __future__ import annotations
+
+from typing import Iterable
+
+import torch
+
+
+def _leaves(params) -> Iterable[torch.Tensor]:
+    if isinstance(params, torch.nn.Module):
+        return list(params.parameters())
+    if isinstance(params, dict):
+        out = []
+        for v in params.values():
+            out.extend(_leaves(v) if isinstance(v, (dict, list, tuple)) else [v])
+        return out
+    if isinstance(params, (list, tuple)):
+        return list(params)
+    return [params]
+
+
+def count_params(params) -> int:
+    return sum(int(t.numel()) for t in _leaves(params) if isinstance(t, torch.Tensor))
+
+
+def check_nan(params) -> bool:
+    """True when any leaf holds a NaN or an infinity."""
+    return any(not bool(torch.isfinite(t.float()).all()) for t in _leaves(params) if isinstance(t, torch.Tensor))
+
+
+def model_flops_per_token_batch(config, batch: int) -> float:
+    """Forward+backward FLOPs of one step over ``batch`` sequences of ``seq_length`` tokens."""
+    B, S, D, V, L = batch, config.seq_length, config.hidden_size, config.vocab_size, config.num_hidden_layers
+    H = config.num_attention_heads
+    Hkv = config.num_key_value_heads or H
+    dh = config.head_dim or D // H
+    dense_ffn = 2 * B * S * D * config.intermediate_size * 3
+    if config.num_experts > 0:
+        moe_layers = max(0, L - config.first_k_dense_replace)
+        router = 2 * B * S * D * config.num_experts
+        expert = 2 * B * S * D * config.moe_intermediate_size * 3
+        ffn = dense_ffn * (L - moe_layers) + (router + expert * config.num_experts_per_tok) * moe_layers
+    else:
+        ffn = dense_ffn * L
+    if config.attention_type == "mla":
+        proj = 2 * B * S * (
+            D * config.q_lora_rank + config.q_lora_rank * H * config.qk_head_dim
+            + D * (config.kv_lora_rank + config.qk_rope_head_dim)
+            + config.kv_lora_rank * H * (config.qk_nope_head_dim + config.v_head_dim)
+            + H * config.v_head_dim * D)
+    else:
+        proj = 2 * B * S * D * ((H + 2 * Hkv) * dh + H * dh)
+    scores = 4 * B * S * S * H * dh // 2
+    head = 2 * B * S * D * V
+    return float((ffn + (proj + scores) * L + head) * 3)
+
+
+def calculate_tflops_per_device(config) -> float:
+    """TFLOP per device per optimizer step, assuming each device processes ``per_device_batch_size`` sequences
+    per micro-step."""
+    return model_flops_per_token_batch(config, config.per_device_batch_size) * config.gradient_accumulation_steps / 1e12
+
+
+def calculate_tokens_per_device(config) -> int:
+    return config.per_device_batch_size * config.seq_length * config.gradient_accumulation_steps
