@@ -482,7 +482,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
         V = weight.shape[0] if weight_is_vd else weight.shape[1]
         e = ext()
         st = status_word(hidden.device)
-        need_grad = torch.is_grad_enabled() and (hidden.requires_grad or weight.requires_grad)
+        need_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[1])
         loss = torch.empty(N, device=hidden.device, dtype=torch.float32)
         zloss = torch.empty(N, device=hidden.device, dtype=torch.float32)
         dx = torch.empty_like(hidden) if need_grad else None
