@@ -174,6 +174,7 @@ def main() -> None:
         end.record()
         barrier_sync()
     ms = start.elapsed_time(end)
+    n_launches = _count_launches(eng, launches_before, args.steps)
     eng.check()
     t = torch.tensor([ms], device=dev)
     if world > 1:
@@ -224,7 +225,7 @@ def main() -> None:
                        "micro_batch": args.micro_batch, "grad_accum_per_rank": n_micro,
                        "l2": "inputs and weights per step exceed L2 (126 MB) by >20x; no explicit flush"},
             "clocks": clocks.summary(), "e2e": e2e,
-            "gpu_launches": int(_count_launches(eng, launches_before, args.steps)),
+            "gpu_launches": int(n_launches),
         }
         print(json.dumps(line))
     if world > 1:

@@ -15,6 +15,7 @@
 // Roles: warps 0-3 softmax/epilogue, warp 4 TMA producer, warp 5 MMA issuer.  All mbarrier waits are bounded.
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
+#include <type_traits>
 #include "../api.h"
 
 namespace mt {
@@ -34,7 +35,7 @@ struct BwdCfg {
   static constexpr int PT_BYTES = BKV * BQ * 2;     // 32 KB
   static constexpr int DST_BYTES = BKV * BQ * 2;
   static constexpr int DQ_STAGE_BYTES = 4 * 2 * 4096;  // per warp: 2 boxes of 32 rows x 128 B
-  static constexpr int STAT_BYTES = 2 * 2 * BQ * 4;    // lse, delta per stage
+  static constexpr int STAT_BYTES = 4 * 2 * BQ * 4;    // per softmax warp: lse[128] | delta[128]
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + K_BYTES;
   static constexpr int OFF_Q = OFF_V + V_BYTES;           // 2 stages of (Q | dO)
@@ -56,6 +57,7 @@ struct BwdArgs {
   int* status;
 };
 
+template <bool CAP>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -231,7 +233,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint8_t* srow = dq_stage + c * 4096 + lane * 128;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-          uint4 w = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+          uint4 w = make_uint4(__float_as_uint(__uint_as_float(v[4 * g]) * sc),
+                               __float_as_uint(__uint_as_float(v[4 * g + 1]) * sc),
+                               __float_as_uint(__uint_as_float(v[4 * g + 2]) * sc),
+                               __float_as_uint(__uint_as_float(v[4 * g + 3]) * sc));
           *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = w;
         }
       }
@@ -250,31 +255,24 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     };
 
-    for (int t = 0; t < n_steps && ok; ++t) {
+    // per-query statistics: each warp keeps a private copy of the step's 128 (lse * log2e, delta) pairs in shared
+    // memory (written by its own lanes, read back as 16-byte broadcasts), prefetched one step ahead in registers
+    float* stat = reinterpret_cast<float*>(smem + C::OFF_STAT) + warp * (2 * BQ);
+    auto load_stats = [&](int t, float4& l4, float4& d4) {
       const int h = hk * G + t / n_i;
-      const int i = i_begin + t % n_i;
-      const int q0 = i * BQ;
-      // per-query statistics of this step: every warp keeps all 128 (lse, delta) pairs in registers, four per
-      // lane, and broadcasts them with shuffles (no CTA-wide barrier on this path)
-      float lse_r[BQ / 32], delta_r[BQ / 32];
-      {
-        const int64_t sbase = (static_cast<int64_t>(b) * args.H + h) * args.S + q0;
-#pragma unroll
-        for (int c = 0; c < BQ / 32; ++c) {
-          lse_r[c] = args.lse[sbase + c * 32 + lane] * kLog2e;
-          delta_r[c] = args.delta[sbase + c * 32 + lane];
-        }
-      }
-      if (!mbar_wait_warp(st_full, t & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after_sync();
-      if (t > 0) {
-        // previous step's dV/dK/dQ MMAs finished: P^T / dS^T buffers are free and dQ(t-1) can be drained
-        if (!mbar_wait_warp(mma2_done, (t - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-        tc_fence_after_sync();
-        drain_dq(t - 1);
-      }
-      const bool need_mask = (args.causal && (key0 + BKV - 1 > q0)) ||
-                             (args.window > 0 && (q0 + BQ - 1 - key0 >= args.window));
+      const int q0 = (i_begin + t % n_i) * BQ;
+      const int64_t sbase = (static_cast<int64_t>(b) * args.H + h) * args.S + q0 + lane * 4;
+      l4 = *reinterpret_cast<const float4*>(args.lse + sbase);
+      d4 = *reinterpret_cast<const float4*>(args.delta + sbase);
+    };
+    float4 lse_n = make_float4(0.f, 0.f, 0.f, 0.f), delta_n = lse_n;
+    if (n_steps > 0) load_stats(0, lse_n, delta_n);
+    const float c1 = sc * kLog2e;
+    const float sc_over_cap = CAP ? sc / cap : 0.f;
+    const float cap_l2 = CAP ? cap * kLog2e : 0.f;
+
+    auto score_block = [&](auto mask_tag, int q0) {
+      constexpr bool MASK = decltype(mask_tag)::value;
 #pragma unroll
       for (int c = 0; c < BQ / 32; ++c) {
         uint32_t sv[32];
@@ -284,25 +282,33 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_wait_ld();
         float p[32], ds[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int qc = c * 32 + e;
-          float x = __uint_as_float(sv[e]) * sc;
-          float slope = 1.f;
-          if (cap > 0.f) {
-            const float th = tanhf(x / cap);
-            x = cap * th;
-            slope = 1.f - th * th;
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(stat + c * 32 + e4 * 4);
+          const float4 d4 = *reinterpret_cast<const float4*>(stat + BQ + c * 32 + e4 * 4);
+          const float lq[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float dq4[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int e = e4 * 4 + u;
+            const float x = __uint_as_float(sv[e]);
+            float pe, slope = 1.f;
+            if constexpr (CAP) {
+              const float th = tanhf(x * sc_over_cap);
+              pe = exp2f(fmaf(th, cap_l2, -lq[u]));
+              slope = 1.f - th * th;
+            } else {
+              pe = exp2f(fmaf(x, c1, -lq[u]));
+            }
+            if constexpr (MASK) {
+              const int qidx = q0 + c * 32 + e;
+              const bool dead = (args.causal && kidx > qidx) || (args.window > 0 && qidx - kidx >= args.window);
+              if (dead) pe = 0.f;
+            }
+            p[e] = pe;
+            float d = pe * (__uint_as_float(dv[e]) - dq4[u]);
+            if constexpr (CAP) d *= slope;
+            ds[e] = d;  // the softmax scale is applied once to dK (epilogue) and dQ (drain)
           }
-          const float lse_q = __shfl_sync(0xffffffffu, lse_r[c], e);
-          const float delta_q = __shfl_sync(0xffffffffu, delta_r[c], e);
-          float pe = exp2f(x * kLog2e - lse_q);
-          if (need_mask) {
-            const int qidx = q0 + qc;
-            const bool dead = (args.causal && kidx > qidx) || (args.window > 0 && qidx - kidx >= args.window);
-            if (dead) pe = 0.f;
-          }
-          p[e] = pe;
-          ds[e] = pe * (__uint_as_float(dv[e]) - delta_q) * slope * sc;
         }
         uint8_t* prow = pt_s + (c >> 1) * (BKV * 128) + r * 128;
         uint8_t* drow = dst_s + (c >> 1) * (BKV * 128) + r * 128;
@@ -322,6 +328,30 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           *reinterpret_cast<uint4*>(drow + ((chunk ^ (r & 7)) << 4)) = d;
         }
       }
+    };
+
+    for (int t = 0; t < n_steps && ok; ++t) {
+      const int i = i_begin + t % n_i;
+      const int q0 = i * BQ;
+      // publish this step's statistics to the warp's slab, then prefetch the next step's
+      __syncwarp();
+      reinterpret_cast<float4*>(stat)[lane] =
+          make_float4(lse_n.x * kLog2e, lse_n.y * kLog2e, lse_n.z * kLog2e, lse_n.w * kLog2e);
+      reinterpret_cast<float4*>(stat + BQ)[lane] = delta_n;
+      __syncwarp();
+      if (t + 1 < n_steps) load_stats(t + 1, lse_n, delta_n);
+      if (!mbar_wait_warp(st_full, t & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (t > 0) {
+        // previous step's dV/dK/dQ MMAs finished: P^T / dS^T buffers are free and dQ(t-1) can be drained
+        if (!mbar_wait_warp(mma2_done, (t - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after_sync();
+        drain_dq(t - 1);
+      }
+      const bool need_mask = (args.causal && (key0 + BKV - 1 > q0)) ||
+                             (args.window > 0 && (q0 + BQ - 1 - key0 >= args.window));
+      if (need_mask) score_block(std::true_type{}, q0);
+      else score_block(std::false_type{}, q0);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
@@ -342,6 +372,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const int col = which == 0 ? C::COL_DV : C::COL_DK;
+        const float osc = which == 0 ? 1.f : sc;
         uint8_t* slab = dq_stage + which * 4096;
 #pragma unroll
         for (int c = 0; c < DH / 32; ++c) {
@@ -357,10 +388,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(v[8 * g + 0]), __uint_as_float(v[8 * g + 1]));
-            w.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3]));
-            w.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5]));
-            w.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7]));
+            w.x = pack_bf16x2(__uint_as_float(v[8 * g + 0]) * osc, __uint_as_float(v[8 * g + 1]) * osc);
+            w.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]) * osc, __uint_as_float(v[8 * g + 3]) * osc);
+            w.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]) * osc, __uint_as_float(v[8 * g + 5]) * osc);
+            w.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]) * osc, __uint_as_float(v[8 * g + 7]) * osc);
             const int chunk = c * 4 + g;
             *reinterpret_cast<uint4*>(srow + ((chunk ^ (lane & 7)) << 4)) = w;
           }
@@ -467,12 +498,14 @@ void flash_attn_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
   CUtensorMap tDV = make_tmap_3d(p.dv, bf, 2, tokens, p.Hkv, DH, p.dv_row_stride, DH, 32, 1, 64, sw);
   static bool configured = false;
   if (!configured) {
-    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured = true;
   }
   BwdArgs a{p.S, p.H, p.Hkv, p.causal, p.window, p.scale, p.softcap, p.lse, p.delta, p.status};
   dim3 grid(p.S / BKV, p.Hkv, p.B);
-  flash_bwd_kernel<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+  if (p.softcap > 0.f) flash_bwd_kernel<true><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+  else flash_bwd_kernel<false><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
   MT_CUDA_CHECK(cudaGetLastError());
   bwd_finish_kernel<<<num_sms * 8, 256, 0, stream>>>(static_cast<const float*>(p.dq_accum),
                                                      static_cast<__nv_bfloat16*>(p.dq_out),

@@ -13,6 +13,7 @@
 // Every mbarrier wait is bounded; on expiry an error code is recorded and the CTA unwinds.
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
+#include <type_traits>
 #include "../api.h"
 
 namespace mt {
@@ -45,14 +46,13 @@ struct FwdArgs {
   int* status;
 };
 
-template <int DH>
+template <int DH, bool CAP>
 __global__ void __launch_bounds__(kThreads, 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, FwdArgs args) {
   using C = FwdCfg<DH>;
   constexpr int BN = C::BN;
   constexpr int D_ATOMS = DH / 64;   // 64-element (128 B) swizzle atoms along the head dim
-  constexpr int N_ATOMS = BN / 64;   // atoms along the key dim of P
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_s = smem;
   uint8_t* kv_s = q_s + C::Q_BYTES;  // stage s: K at kv_s + s*(K+V), V right after K
@@ -197,18 +197,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int r = threadIdx.x;  // 0..127
     const int q_idx = q0 + r;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    float m_run = -INFINITY, l_run = 0.f;
-    const float sc = args.scale;
-    const float cap = args.softcap;
+    // running maximum is tracked on the raw scores (scaling and tanh capping are monotone), the running sum on
+    // exp2 of (transformed score - transformed max) in log2 units
+    float m_raw = -INFINITY, M_l2 = -INFINITY, l_run = 0.f;
+    const float c1 = args.scale * kLog2e;
+    const float sc_over_cap = CAP ? args.scale / args.softcap : 0.f;
+    const float cap_l2 = CAP ? args.softcap * kLog2e : 0.f;
     bool ok = true;
-    for (int i = 0; i < n_blocks && ok; ++i) {
-      const int j = j_begin + i;
-      const int key0 = j * BN;
-      if (!mbar_wait_warp(s_full, i & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after_sync();
-      const bool need_mask = (args.causal && (key0 + BN - 1 > q0)) ||
-                             (args.window > 0 && (key0 <= q0 + BLOCK_M - 1 - args.window));
-      // pass 1: block row max
+
+    auto softmax_block = [&](auto mask_tag, int i) -> bool {
+      constexpr bool MASK = decltype(mask_tag)::value;
+      const int key0 = (j_begin + i) * BN;
+      // pass 1: block row max of the raw scores
       float m_blk = -INFINITY;
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
@@ -217,9 +217,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_wait_ld();
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          float x = __uint_as_float(v[e]) * sc;
-          if (cap > 0.f) x = cap * tanhf(x / cap);
-          if (need_mask) {
+          float x = __uint_as_float(v[e]);
+          if constexpr (MASK) {
             const int kidx = key0 + c * 32 + e;
             const bool dead = (args.causal && kidx > q_idx) || (args.window > 0 && q_idx - kidx >= args.window);
             if (dead) x = -INFINITY;
@@ -227,12 +226,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           m_blk = fmaxf(m_blk, x);
         }
       }
-      const float m_new = fmaxf(m_run, m_blk);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_use) * kLog2e);
+      const float m_new = fmaxf(m_raw, m_blk);
+      float M_new;
+      if (m_new == -INFINITY) M_new = 0.f;
+      else M_new = CAP ? cap_l2 * tanhf(m_new * sc_over_cap) : m_new * c1;
+      const float alpha = (m_raw == -INFINITY) ? 0.f : exp2f(M_l2 - M_new);
       // O(i-1) must have landed before P is overwritten or O rescaled
       if (i > 0) {
-        if (!mbar_wait_warp(pv_done, (i - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        if (!mbar_wait_warp(pv_done, (i - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) return false;
         tc_fence_after_sync();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
@@ -249,7 +250,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       // pass 2: probabilities -> bf16 -> swizzled shared memory
       float l_blk = 0.f;
-      const float m_l2 = m_use * kLog2e;
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
@@ -258,15 +258,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         float p[32];
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          float x = __uint_as_float(v[e]) * sc;
-          if (cap > 0.f) x = cap * tanhf(x / cap);
-          if (need_mask) {
+          const float x = __uint_as_float(v[e]);
+          float pe;
+          if constexpr (CAP) pe = exp2f(fmaf(tanhf(x * sc_over_cap), cap_l2, -M_new));
+          else pe = exp2f(fmaf(x, c1, -M_new));
+          if constexpr (MASK) {
             const int kidx = key0 + c * 32 + e;
             const bool dead = (args.causal && kidx > q_idx) || (args.window > 0 && q_idx - kidx >= args.window);
-            if (dead) x = -INFINITY;
+            if (dead) pe = 0.f;
           }
-          p[e] = exp2f(x * kLog2e - m_l2);
-          l_blk += p[e];
+          p[e] = pe;
+          l_blk += pe;
         }
         uint8_t* prow = p_s + (c >> 1) * (BLOCK_M * 128) + r * 128;
 #pragma unroll
@@ -281,12 +283,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       l_run = l_run * alpha + l_blk;
-      m_run = m_new;
+      m_raw = m_new;
+      M_l2 = M_new;
+      return true;
+    };
+
+    for (int i = 0; i < n_blocks && ok; ++i) {
+      const int key0 = (j_begin + i) * BN;
+      if (!mbar_wait_warp(s_full, i & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after_sync();
+      const bool need_mask = (args.causal && (key0 + BN - 1 > q0)) ||
+                             (args.window > 0 && (key0 <= q0 + BLOCK_M - 1 - args.window));
+      ok = need_mask ? softmax_block(std::true_type{}, i) : softmax_block(std::false_type{}, i);
+      if (!ok) break;
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
+    const float m_run = (m_raw == -INFINITY) ? -INFINITY : M_l2 / kLog2e;
     // epilogue: O / l -> bf16 -> staging (P region) -> TMA store ; lse
     if (ok && n_blocks > 0) {
       ok = mbar_wait_warp(pv_done, (n_blocks - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL);
@@ -343,7 +358,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-template <int DH>
+template <int DH, bool CAP>
 void launch_fwd(const AttnParams& p, cudaStream_t stream) {
   using C = FwdCfg<DH>;
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -353,7 +368,7 @@ void launch_fwd(const AttnParams& p, cudaStream_t stream) {
   CUtensorMap tK = make_tmap_3d(p.k, bf, 2, tokens, p.Hkv, DH, p.k_row_stride, DH, C::BN, 1, 64, sw);
   CUtensorMap tV = make_tmap_3d(p.v, bf, 2, tokens, p.Hkv, DH, p.v_row_stride, DH, C::BN, 1, 64, sw);
   CUtensorMap tO = make_tmap_3d(p.o, bf, 2, tokens, p.H, DH, p.o_row_stride, DH, BLOCK_M, 1, 64, sw);
-  auto kern = flash_fwd_kernel<DH>;
+  auto kern = flash_fwd_kernel<DH, CAP>;
   static bool configured = false;
   if (!configured) {
     MT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
@@ -370,8 +385,9 @@ void launch_fwd(const AttnParams& p, cudaStream_t stream) {
 void flash_attn_fwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
   (void)num_sms;
   if (p.S % BLOCK_M != 0) throw std::runtime_error("flash_attn_fwd: sequence length must be a multiple of 128");
-  if (p.dh == 64) launch_fwd<64>(p, stream);
-  else if (p.dh == 128) launch_fwd<128>(p, stream);
+  const bool cap = p.softcap > 0.f;
+  if (p.dh == 64) cap ? launch_fwd<64, true>(p, stream) : launch_fwd<64, false>(p, stream);
+  else if (p.dh == 128) cap ? launch_fwd<128, true>(p, stream) : launch_fwd<128, false>(p, stream);
   else throw std::runtime_error("flash_attn_fwd: head_dim must be 64 or 128");
 }
 

@@ -25,6 +25,8 @@ enum : int {
 
 // About one second at ~2 GHz; a healthy pipeline never waits more than microseconds.
 constexpr long long kMaxWaitCycles = 2000000000LL;
+// Upper bound (ns) a single try_wait may keep the thread suspended; waiting threads then cost no issue slots.
+constexpr uint32_t kSuspendHintNs = 1000000u;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -54,10 +56,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
