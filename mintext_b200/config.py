@@ -118,6 +118,7 @@ class MinTextConfig(BaseModel):
     e_score_correction_bias_update_rate: float = 0.001
     router_type: RouterType = RouterType.sigmoid_group
     router_aux_loss_coef: float = 0.0
+    shared_expert_gate: bool = False  # Qwen3-Next: shared expert output times sigmoid(x @ w_gate)
     moe_use_custom_vjp: bool = True
     moe_mosaic_fusion_group: bool = True
     moe_autotune: bool = False

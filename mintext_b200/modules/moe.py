@@ -88,6 +88,11 @@ class MoEBlock(nn.Module):
                                      intermediate_size=config.moe_intermediate_size * config.n_shared_experts)
         else:
             self.shared_expert = None
+        if self.shared_expert is not None and config.shared_expert_gate:
+            self.shared_expert_gate = Linear(config.hidden_size, 1, config.torch_dtype, config.torch_weight_dtype,
+                                             ("embed", None), rngs=rngs)
+        else:
+            self.shared_expert_gate = None
 
     def forward(self, x: torch.Tensor):
         B, S, D = x.shape
@@ -95,7 +100,10 @@ class MoEBlock(nn.Module):
         idx, w, scores = self.router(flat)
         out = self.experts(flat, idx, w).reshape(B, S, D)
         if self.shared_expert is not None:
-            out = out + self.shared_expert(x)
+            shared = self.shared_expert(x)
+            if self.shared_expert_gate is not None:
+                shared = shared * torch.sigmoid(self.shared_expert_gate(x))
+            out = out + shared
         aux = {"topk_indices": idx, "scores": scores}
         if self.router.last_aux_loss is not None:
             aux["aux_loss"] = self.router.last_aux_loss

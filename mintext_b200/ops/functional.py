@@ -320,7 +320,11 @@ def rope(x: torch.Tensor, positions: torch.Tensor | None, inv_freq: torch.Tensor
     ``default_positions`` says positions are ``arange(S)`` for every sequence, which lets the kernel skip
     the gather."""
     if use_cuda(x) and tables is not None and tables[0].shape[0] >= x.shape[1]:
-        return _RopeFn.apply(x, tables[0], tables[1], None if default_positions else positions, rot_dim, interleave)
+        if interleave:  # bring (2i, 2i+1) pairs to the half layout, then the ordinary rotation applies
+            head = x[..., :rot_dim]
+            head = head.reshape(*head.shape[:-1], -1, 2).transpose(-1, -2).reshape(head.shape)
+            x = head if rot_dim == x.shape[-1] else torch.cat([head, x[..., rot_dim:]], dim=-1)
+        return _RopeFn.apply(x, tables[0], tables[1], None if default_positions else positions, rot_dim, False)
     if positions is None:
         positions = torch.arange(x.shape[1], device=x.device)[None].expand(x.shape[0], -1)
     return oracle.apply_rope(x, positions, inv_freq, attention_factor, rot_dim, interleave)

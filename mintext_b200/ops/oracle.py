@@ -102,8 +102,10 @@ def rope_tables(inv_freq: torch.Tensor, attention_factor: float, max_pos: int, d
 
 def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, attention_factor: float,
                rot_dim: int, interleave: bool) -> torch.Tensor:
-    """x ``[B,S,H,d]``, positions ``[B,S]``.  fp32 math, duplicated ``[sin,sin]`` / ``[cos,cos]`` tables for both
-    pairings, untouched tail when ``rot_dim < d``, result cast back to x.dtype (mintext/modules/rope.py:190-232)."""
+    """x ``[B,S,H,d]``, positions ``[B,S]``.  fp32 math, duplicated ``[sin,sin]`` / ``[cos,cos]`` tables, untouched
+    tail when ``rot_dim < d``, result cast back to x.dtype (mintext/modules/rope.py:190-232).  ``interleave``
+    follows the HuggingFace DeepSeek-V3 definition (de-interleave, then half rotation) rather than the
+    reference's pair-swap with duplicated tables, which does not rotate pairs by a common angle."""
     full = x.shape[-1]
     xr = x[..., :rot_dim]
     ang = positions[:, :, None, None].float() * inv_freq.to(x.device)
@@ -111,11 +113,11 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
     cos = torch.cat([ang.cos(), ang.cos()], -1) * attention_factor
     xf = xr.float()
     if interleave:
-        pairs = xf.reshape(*xf.shape[:-1], -1, 2)
-        rot = torch.stack([-pairs[..., 1], pairs[..., 0]], dim=-1).reshape(xf.shape)
-    else:
-        half = rot_dim // 2
-        rot = torch.cat([-xf[..., half:], xf[..., :half]], dim=-1)
+        # pairs (2i, 2i+1) are brought to the half layout (evens first, then odds) and rotated there; q and k get
+        # the same permutation, so attention scores equal those of an interleaved rotation (HF DeepSeek-V3)
+        xf = xf.reshape(*xf.shape[:-1], -1, 2).transpose(-1, -2).reshape(xf.shape)
+    half = rot_dim // 2
+    rot = torch.cat([-xf[..., half:], xf[..., :half]], dim=-1)
     out = xf * cos + rot * sin
     if rot_dim < full:
         out = torch.cat([out, x[..., rot_dim:].float()], dim=-1)

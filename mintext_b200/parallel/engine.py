@@ -22,6 +22,7 @@ The rule for which GPU holds which batch rows: the global batch is split evenly 
 
 from __future__ import annotations
 
+import json
 import math
 import os
 from dataclasses import dataclass
@@ -291,6 +292,111 @@ class TrainEngine:
     def check(self) -> None:
         """Raise if any kernel recorded a bounded-wait expiry since the last check (synchronises)."""
         check_status(self.device)
+
+    # ------------------------------------------------------------------ evaluation / MoE bias / checkpoints
+    @torch.no_grad()
+    def eval_step(self, batch: dict) -> dict:
+        from mintext_b200.trainer import compute_loss
+
+        loss, _ = compute_loss(None, self.model, self.config, batch)
+        loss = loss.detach().float()
+        if self.world > 1:
+            dist.all_reduce(loss, group=self.group)
+            loss /= self.world
+        return {"eval_loss": loss}
+
+    @torch.no_grad()
+    def update_expert_biases(self, expert_counts: torch.Tensor | None) -> None:
+        """``bias += rate * sign(mean_count - count)`` per MoE layer, counts taken over the global batch."""
+        if expert_counts is None:
+            return
+        rate = self.config.e_score_correction_bias_update_rate
+        names = sorted((n for n, _ in self.model.named_parameters() if n.endswith("e_score_correction_bias")),
+                       key=lambda n: int(n.split(".")[1]))
+        params = dict(self.model.named_parameters())
+        for name, counts in zip(names, expert_counts):
+            c = counts.float()
+            params[name].add_(rate * torch.sign(c.mean() - c))
+
+    params_only_restore = False
+
+    def checkpoint_tree(self) -> dict:
+        """Flat fp32 master / moment buffers are saved as one chunk per rank (``flat_range`` = the rank's slice
+        of the flat layout); small replicated and frozen parameters are saved by name from rank 0."""
+        lo = self.rank * self.shard_size
+        rng = (lo, lo + self.shard_size)
+        suffix = f".{lo}-{lo + self.shard_size}"
+        common = {"writer_rank": self.rank, "flat_range": rng, "flat_total": self.big.total, "suffix": suffix}
+        tree: dict = {
+            "step": self.step_count,
+            "layout/big": {"tensor": json.dumps([[s.name, s.offset, s.numel, list(s.param.shape)] for s in self.big.slots])},
+            "opt_state/flat_master": {"tensor": self.master, **common},
+            "opt_state/flat_exp_avg": {"tensor": self.exp_avg, **common},
+            "opt_state/flat_exp_avg_sq": {"tensor": self.exp_avg_sq, **common},
+        }
+        for s in self.small.slots:
+            tree[f"params/{s.name}"] = s.param.detach()
+            tree[f"opt_state/mu/{s.name}"] = self.small_m[s.offset:s.offset + s.numel].view(s.param.shape)
+            tree[f"opt_state/nu/{s.name}"] = self.small_v[s.offset:s.offset + s.numel].view(s.param.shape)
+        for n, p in self.model.named_parameters():
+            if not p.requires_grad:
+                tree[f"params/{n}"] = p.detach()
+        return tree
+
+    @torch.no_grad()
+    def load_checkpoint_tree(self, read) -> None:
+        lo = self.rank * self.shard_size
+        hi = lo + self.shard_size
+        paths = set(getattr(read, "paths", []))
+        if "opt_state/flat_master" in paths:
+            saved = {row[0]: row for row in json.loads(read("layout/big"))}
+            mine = {s.name: s for s in self.big.slots}
+            same = all(n in saved and saved[n][1] == s.offset and saved[n][2] == s.numel for n, s in mine.items())
+            if not same:
+                raise ValueError("checkpoint parameter layout differs from this model's")
+            self.master.copy_(read("opt_state/flat_master", (lo, hi)))
+            if not self.params_only_restore:
+                self.exp_avg.copy_(read("opt_state/flat_exp_avg", (lo, hi)))
+                self.exp_avg_sq.copy_(read("opt_state/flat_exp_avg_sq", (lo, hi)))
+        else:  # a per-name checkpoint written by the CPU trainer
+            for s in self.big.slots:
+                full = read(f"params/{s.name}").float().reshape(-1)
+                a, b = max(s.offset, lo), min(s.offset + s.numel, hi)
+                if a < b:
+                    self.master[a - lo:b - lo] = full[a - s.offset:b - s.offset].to(self.device)
+        for s in self.small.slots:
+            s.param.copy_(read(f"params/{s.name}").to(self.device))
+            if not self.params_only_restore and f"opt_state/mu/{s.name}" in paths:
+                self.small_m[s.offset:s.offset + s.numel] = read(f"opt_state/mu/{s.name}").reshape(-1).to(self.device)
+                self.small_v[s.offset:s.offset + s.numel] = read(f"opt_state/nu/{s.name}").reshape(-1).to(self.device)
+        for n, p in self.model.named_parameters():
+            if not p.requires_grad and f"params/{n}" in paths:
+                p.copy_(read(f"params/{n}").to(self.device))
+        if not self.params_only_restore:
+            self.step_count = int(read("step"))
+        self._publish_master()
+
+    def _publish_master(self) -> None:
+        """Rebuild the resident bf16 compute copy from the fp32 master shards."""
+        lo = self.rank * self.shard_size
+        pshard = self.param_flat[lo:lo + self.shard_size]
+        pshard.copy_(self.master.to(torch.bfloat16))
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.param_flat, pshard.clone(), group=self.group)
+
+    def reset_step(self) -> None:
+        self.step_count = 0
+        self.exp_avg.zero_()
+        self.exp_avg_sq.zero_()
+        self.small_m.zero_()
+        self.small_v.zero_()
+
+    @torch.no_grad()
+    def refresh_from_model(self) -> None:
+        """Parameters were overwritten in place (e.g. by an HF import into the bf16 views): re-derive the master
+        shards from them."""
+        lo = self.rank * self.shard_size
+        self.master.copy_(self.param_flat[lo:lo + self.shard_size].float())
 
 
 def local_batch_rows(global_batch: int, world: int, rank: int) -> tuple[int, int]:

@@ -1,0 +1,177 @@
+"""Command-line entry point and the training loop (reference: mintext/train.py).
+
+    python -m mintext_b200.train --config configs/base.yml --config configs/models/<model>.yml key=value ...
+    python -m mintext_b200.train --help-config
+
+``--config`` may be repeated; files are merged left to right (each still follows its ``base_config`` chain),
+then ``key=value`` overrides, then ``MINTEXT_<KEY>`` environment variables with the documented priority.
+On a machine with CUDA the loop runs through :class:`mintext_b200.parallel.engine.TrainEngine` (this
+repository's kernels, sharded fused optimizer, device-timed steps); without a GPU it runs the same model through
+the plain-PyTorch path.
+"""
+
+from __future__ import annotations
+
+import argparse
+import logging
+import os
+import sys
+import time
+
+import torch
+
+from mintext_b200.config import MinTextConfig, load_config, parse_cli_overrides, print_help_config
+
+logger = logging.getLogger("mintext_b200.train")
+
+
+def _make_synthetic_batch(config, generator: torch.Generator, batch_rows: int, device) -> dict[str, torch.Tensor]:
+    """Uniform random token ids.  Targets equal the inputs unless ``synthetic_shift_targets`` is set (then the
+    target is the next token), matching the reference's synthetic task by default."""
+    tok = torch.randint(0, config.vocab_size, (batch_rows, config.seq_length), generator=generator, dtype=torch.int64)
+    tgt = tok.roll(-1, dims=1) if config.synthetic_shift_targets else tok
+    if device.type == "cuda":
+        tok, tgt = tok.pin_memory().to(device, non_blocking=True), tgt.pin_memory().to(device, non_blocking=True)
+    return {"input_tokens": tok, "target_tokens": tgt}
+
+
+def _apply_moe_tiling(config, result) -> MinTextConfig:
+    """Copy autotuned grouped-GEMM tilings into the config (kept for parity; tile shapes are fixed by the
+    tcgen05 kernels, so the values are informational)."""
+    return config.model_copy(update={"moe_gate_up_tiling": list(result.gate_up_tiling),
+                                     "moe_down_tiling": list(result.down_tiling)})
+
+
+def train(config: MinTextConfig) -> dict:
+    """Run ``config.steps`` optimizer steps.  Returns the metrics of the last step (floats)."""
+    logging.basicConfig(level=logging.INFO, format="%(asctime)s %(name)s %(message)s")
+    from mintext_b200.checkpoint import (create_checkpoint_manager, maybe_restore_checkpoint, save_checkpoint,
+                                         wait_for_checkpoint)
+    from mintext_b200.parallel import create_sharded_model, initialize_distributed, setup_mesh
+    from mintext_b200.utils import MetricLogger, Profiler
+
+    initialize_distributed(config.jax_distributed_init_timeout)
+    mesh = setup_mesh(config)
+    use_gpu = torch.cuda.is_available() and config.kernel_backend != "oracle"
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_gpu else torch.device("cpu")
+    model = create_sharded_model(config, mesh)
+
+    if use_gpu:
+        from mintext_b200.parallel.engine import TrainEngine
+
+        state = TrainEngine(model, config, device=device)
+    else:
+        from mintext_b200 import trainer
+
+        state = trainer.create_train_state(model, config)
+    metric_logger = MetricLogger(config, params=model)
+    profiler = Profiler(config)
+
+    manager = create_checkpoint_manager(config) if config.enable_checkpointing else None
+    state, start_step = maybe_restore_checkpoint(manager, state, config, model=model)
+
+    if config.moe_autotune and config.num_experts > 0 and use_gpu:
+        from mintext_b200.kernels.autotuner import MoETuningConfig, autotune_moe
+
+        tokens = config.per_device_batch_size * config.seq_length * config.num_experts_per_tok
+        res = autotune_moe(MoETuningConfig(config.num_experts, config.hidden_size, config.moe_intermediate_size,
+                                           tokens, config.dtype), cache_dir=config.moe_autotune_cache_dir or None)
+        config = _apply_moe_tiling(config, res)
+
+    world = mesh.size
+    tp = mesh.shape["tensor"]
+    dp_world = world // tp
+    rows = config.per_device_batch_size * config.gradient_accumulation_steps
+    train_iter = eval_iter = None
+    if config.dataset_type != "synthetic":
+        from mintext_b200.data import create_eval_iterator, create_train_iterator
+
+        train_iter = create_train_iterator(config, mesh)
+        if start_step > 0:
+            train_iter.load_state_dict({"batches_done": start_step})
+        if config.eval_period > 0:
+            eval_iter = create_eval_iterator(config, mesh)
+    rank = int(os.environ.get("RANK", "0"))
+    gen = torch.Generator(device="cpu").manual_seed(config.seed * 1000003 + rank // tp)
+    for _ in range(start_step):  # resume: skip the batches already consumed
+        if train_iter is None:
+            _make_synthetic_batch(config, gen, rows, torch.device("cpu"))
+
+    last = {}
+    ev0 = ev1 = None
+    if use_gpu:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for step in range(start_step, config.steps):
+        profiler.maybe_activate(step)
+        t0 = time.time()
+        if train_iter is not None:
+            nb = next(train_iter)
+            batch = {k: torch.from_numpy(v).long().to(device, non_blocking=True) for k, v in nb.items()}
+        else:
+            batch = _make_synthetic_batch(config, gen, rows, device)
+        if use_gpu:
+            ev0.record()
+            metrics = state.train_step(batch)
+            ev1.record()
+            loss_value = float(metrics["loss"])  # device -> host sync, as the reference blocks on the loss
+            metrics["device_step_ms"] = ev0.elapsed_time(ev1)
+            state.check()
+        else:
+            from mintext_b200 import trainer
+
+            state, metrics = trainer.train_step(state, batch, model, config)
+            loss_value = float(metrics["loss"])
+        step_time = time.time() - t0
+        if config.num_experts > 0 and metrics.get("moe_expert_counts") is not None:
+            if use_gpu:
+                state.update_expert_biases(metrics["moe_expert_counts"])
+            else:
+                from mintext_b200 import trainer
+
+                state = trainer.update_expert_biases(state, metrics["moe_expert_counts"], config)
+        if step % config.log_period == 0 or step == config.steps - 1:
+            metric_logger.log_step(step, metrics, step_time)
+        if eval_iter is not None and config.eval_period > 0 and (step + 1) % config.eval_period == 0:
+            losses = []
+            for _ in range(config.eval_steps):
+                eb = {k: torch.from_numpy(v).long().to(device) for k, v in next(eval_iter).items()}
+                if use_gpu:
+                    losses.append(float(state.eval_step(eb)["eval_loss"]))
+                else:
+                    from mintext_b200 import trainer
+
+                    losses.append(float(trainer.eval_step(state, eb, model, config)["eval_loss"]))
+            logger.info("step=%d eval_loss=%.4f", step, sum(losses) / len(losses))
+        if manager is not None:
+            save_checkpoint(manager, step + 1, state)
+        profiler.maybe_deactivate(step)
+        last = {"loss": loss_value, "step": step, "step_time": step_time,
+                "grad_norm": float(metrics["grad_norm"]), "learning_rate": float(metrics["learning_rate"])}
+    if manager is not None:
+        if config.steps not in manager.all_steps() and config.steps > start_step:
+            save_checkpoint(manager, config.steps, state, force=True)
+        wait_for_checkpoint(manager)
+    profiler.stop()
+    metric_logger.close()
+    if train_iter is not None:
+        train_iter.close()
+    return last
+
+
+def main(argv: list[str] | None = None) -> None:
+    ap = argparse.ArgumentParser(description="mintext_b200 training")
+    ap.add_argument("--config", action="append", default=None, help="YAML config file (repeatable)")
+    ap.add_argument("--help-config", action="store_true", help="print every config field and exit")
+    args, rest = ap.parse_known_args(argv)
+    if args.help_config:
+        print_help_config()
+        return
+    if not args.config:
+        ap.error("--config is required")
+    overrides = parse_cli_overrides(rest)
+    config = load_config(args.config, overrides or None)
+    train(config)
+
+
+if __name__ == "__main__":
+    main()

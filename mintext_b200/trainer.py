@@ -29,9 +29,38 @@ class TrainState:
     opt_state: Any
     tx: Any
 
-    def state_dict(self) -> dict:
-        return {"step": self.step, "params": self.params, "opt_state": {
-            "count": self.opt_state.count, "mu": self.opt_state.mu, "nu": self.opt_state.nu}}
+    params_only_restore: bool = False
+
+    # ---- checkpoint protocol (see mintext_b200.checkpoint.manager)
+    def checkpoint_tree(self) -> dict:
+        tree: dict = {"step": self.step, "opt_state/count": self.opt_state.count}
+        for n, p in self.params.items():
+            tree[f"params/{n}"] = p.detach()
+        for n, t in self.opt_state.mu.items():
+            tree[f"opt_state/mu/{n}"] = t
+        for n, t in self.opt_state.nu.items():
+            tree[f"opt_state/nu/{n}"] = t
+        return tree
+
+    @torch.no_grad()
+    def load_checkpoint_tree(self, read) -> None:
+        for n, p in self.params.items():
+            p.copy_(read(f"params/{n}").to(p.dtype))
+        if self.params_only_restore:
+            return
+        self.step = int(read("step"))
+        self.opt_state.count = int(read("opt_state/count"))
+        for n in self.opt_state.mu:
+            self.opt_state.mu[n].copy_(read(f"opt_state/mu/{n}"))
+        for n in self.opt_state.nu:
+            self.opt_state.nu[n].copy_(read(f"opt_state/nu/{n}"))
+
+    def reset_step(self) -> None:
+        self.step = 0
+        self.opt_state = self.tx.init({n: p for n, p in self.params.items() if p.requires_grad})
+
+    def refresh_from_model(self) -> None:
+        """Parameters are shared with the model, nothing to copy."""
 
 
 # ------------------------------------------------------------------------------------------ losses
