@@ -87,19 +87,20 @@ def run_reference(args) -> None:
     """The reference is a JAX program; report why it cannot run when its runtime is absent."""
     ref = ROOT / "baseline" / "_ref"
     why = None
-    try:
-        import jax  # noqa: F401
-    except Exception as e:
-        why = f"reference needs jax/flax/optax/orbax/grain which are not installed and cannot be (no index access): {type(e).__name__}"
-    if why is None and not (ref / "mintext").exists():
-        why = "reference package is not installed under baseline/_ref"
-    if why is not None:
-        if int(os.environ.get("RANK", "0")) == 0:
-            print(json.dumps({"impl": "reference", "unavailable": why}))
-        return
-    # jax present: run the reference's own entry point on the same model/config (never reached on this image)
-    sys.path.insert(0, str(ref))
-    print(json.dumps({"impl": "reference", "unavailable": "reference run path not wired for this image"}))
+    if not (ref / "mintext").exists():
+        why = "reference package is not installed under baseline/_ref (offline pip install fails: dependency resolution needs the network)"
+    else:
+        sys.path.insert(0, str(ref))
+        try:
+            import mintext  # noqa: F401  (the unmodified reference)
+            import mintext.train  # noqa: F401
+        except Exception as e:
+            why = ("reference installed with --no-deps but cannot be imported: its runtime (jax/flax/optax/orbax/grain/"
+                   f"omegaconf) is not installed and not in the wheelhouse: {type(e).__name__}: {e}")
+    if why is None:
+        why = "reference imported, but no JAX CUDA backend is available to execute it on this image"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:400]}))
 
 
 def main() -> None:

@@ -64,6 +64,20 @@ void adamw_step(float* master, float* m, float* v, const void* grad, bool grad_f
                 const float* clip_coef, cudaStream_t stream);
 void sumsq(const void* x, bool is_f32, int64_t n, float* out_accum, cudaStream_t stream);
 
+// ---- comm/rs_optim.cu : sharded optimizer step over peer memory (pointers of every rank's symmetric buffer)
+constexpr int kMaxPeers = 8;
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+void symm_barrier(const PeerPtrs& flags, int rank, int world, int seq, int* status, cudaStream_t stream);
+// out[0..n) = sum over ranks of grads[r][lo..lo+n) ; *sumsq += |out|^2   (n multiple of 4, lo multiple of 4)
+void grad_pull_reduce(const PeerPtrs& grads, int rank, int world, int64_t lo, int64_t n, float* out, float* sumsq,
+                      cudaStream_t stream);
+// AdamW on the local shard, bf16 result stored to params[r][lo..lo+n) of every rank r   (n multiple of 8)
+void adamw_publish(float* master, float* m, float* v, const float* grad, const PeerPtrs& params, int world, int64_t lo,
+                   int64_t n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                   float grad_scale, const float* clip_coef, cudaStream_t stream);
+
 // ---- attention/flash_fwd.cu, flash_bwd.cu
 struct AttnParams {
   const void* q; const void* k; const void* v; void* o; float* lse;

@@ -197,6 +197,37 @@ void flash_bwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tens
   mt::flash_attn_bwd(p, sm_count(), cur_stream());
 }
 
+mt::PeerPtrs to_peers(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK((int)ptrs.size() <= mt::kMaxPeers, "at most ", mt::kMaxPeers, " peers");
+  mt::PeerPtrs p{};
+  for (size_t i = 0; i < ptrs.size(); ++i) p.p[i] = reinterpret_cast<void*>(ptrs[i]);
+  return p;
+}
+
+void symm_barrier(const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t seq, torch::Tensor& status) {
+  c10::cuda::CUDAGuard guard(status.device());
+  mt::symm_barrier(to_peers(flag_ptrs), (int)rank, (int)flag_ptrs.size(), (int)seq, status.data_ptr<int>(), cur_stream());
+}
+
+void grad_pull_reduce(const std::vector<int64_t>& grad_ptrs, int64_t rank, int64_t lo, torch::Tensor& out,
+                      torch::Tensor& sumsq) {
+  TORCH_CHECK(out.scalar_type() == torch::kFloat32 && out.is_contiguous() && out.numel() % 4 == 0 && lo % 4 == 0);
+  c10::cuda::CUDAGuard guard(out.device());
+  mt::grad_pull_reduce(to_peers(grad_ptrs), (int)rank, (int)grad_ptrs.size(), lo, out.numel(), out.data_ptr<float>(),
+                       sumsq.data_ptr<float>(), cur_stream());
+}
+
+void adamw_publish(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, const torch::Tensor& grad,
+                   const std::vector<int64_t>& param_ptrs, int64_t lo, double lr, double b1, double b2, double eps,
+                   double wd, double bc1, double bc2, double grad_scale, const c10::optional<torch::Tensor>& clip_coef) {
+  TORCH_CHECK(master.numel() % 8 == 0 && lo % 8 == 0 && grad.scalar_type() == torch::kFloat32);
+  c10::cuda::CUDAGuard guard(master.device());
+  mt::adamw_publish(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr<float>(),
+                    to_peers(param_ptrs), (int)param_ptrs.size(), lo, master.numel(), (float)lr, (float)b1, (float)b2,
+                    (float)eps, (float)wd, (float)bc1, (float)bc2, (float)grad_scale,
+                    clip_coef ? clip_coef->data_ptr<float>() : nullptr, cur_stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -211,6 +242,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_bwd", &embedding_bwd);
   m.def("adamw_step", &adamw_step);
   m.def("sumsq", &sumsq);
+  m.def("symm_barrier", &symm_barrier);
+  m.def("grad_pull_reduce", &grad_pull_reduce);
+  m.def("adamw_publish", &adamw_publish);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);
 }

@@ -87,6 +87,7 @@ class TrainEngine:
                 logging.getLogger(__name__).warning("peer-memory optimizer path unavailable (%s); using NCCL", e)
                 self.use_fused = False
         self._sumsq = torch.zeros(1, device=self.device, dtype=torch.float32)
+        self._sumsq_shard = torch.zeros(1, device=self.device, dtype=torch.float32)
         self._clip = torch.ones(1, device=self.device, dtype=torch.float32)
         self.kernel_launches = 0
 
@@ -218,8 +219,11 @@ class TrainEngine:
         else:
             gshard = self.grad_flat
         # 2. global norm of the averaged gradient
-        self._sumsq.zero_()
-        e.sumsq(gshard, self._sumsq)
+        if W > 1 and self.use_fused:
+            self._sumsq.copy_(self._sumsq_shard)  # produced by the pull-reduce kernel
+        else:
+            self._sumsq.zero_()
+            e.sumsq(gshard, self._sumsq)
         if W > 1:
             dist.all_reduce(self._sumsq, group=self.group)
         e.sumsq(self.small_grad, self._sumsq)
