@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include "../api.h"
+#include "rmsnorm_noalloc.h"
+#include <cstdio>
 
 namespace mt {
 namespace {
@@ -177,3 +179,53 @@ void rmsnorm_bwd_reduce(const float* dw_partial, int num_partials, int dim, floa
 }
 
 }  // namespace mt
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free variant (see rmsnorm_noalloc.h).  The per-block partial sums live in this file-scope device
+// array instead of caller-provided memory.  In host code the array's name is only a handle: the device address
+// the kernels need is obtained with cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) float g_rmsnorm_partials[MT_RMSNORM_NOALLOC_PARTIALS * MT_RMSNORM_NOALLOC_MAX_DIM];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_partials_addr[kMaxDevices] = {nullptr};
+
+int fail(char* err, size_t err_len, int code, const char* msg) {
+  if (err && err_len > 0) std::snprintf(err, err_len, "%s", msg);
+  return code;
+}
+}  // namespace
+
+extern "C" int mt_rmsnorm_bwd_noalloc(const void* x, const float* w, const float* rstd, const void* dy,
+                                      const void* dres, void* dx, float* dw, int64_t rows, int dim,
+                                      int accumulate_dw, cudaStream_t stream, char* err, size_t err_len) {
+  if (!x || !w || !rstd || !dy || !dx || !dw) return fail(err, err_len, 1, "mt_rmsnorm_bwd_noalloc: null pointer argument");
+  if (dim <= 0 || dim % 8 != 0) return fail(err, err_len, 2, "mt_rmsnorm_bwd_noalloc: dim must be a positive multiple of 8");
+  if (dim > MT_RMSNORM_NOALLOC_MAX_DIM) {
+    char msg[160];
+    std::snprintf(msg, sizeof(msg), "mt_rmsnorm_bwd_noalloc: dim %d exceeds the built-in scratch limit of %d", dim,
+                  MT_RMSNORM_NOALLOC_MAX_DIM);
+    return fail(err, err_len, 3, msg);
+  }
+  if (rows < 0) return fail(err, err_len, 4, "mt_rmsnorm_bwd_noalloc: negative row count");
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(err, err_len, 5, cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(err, err_len, 6, "mt_rmsnorm_bwd_noalloc: device index out of range");
+  if (g_partials_addr[dev] == nullptr) {  // one-time set-up for this device (current device = dev)
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_rmsnorm_partials);
+    if (e != cudaSuccess) return fail(err, err_len, 7, cudaGetErrorString(e));
+    g_partials_addr[dev] = static_cast<float*>(p);
+  }
+  if (rows == 0) return 0;
+  float* partials = g_partials_addr[dev];
+  mt::rmsnorm_bwd_kernel<<<MT_RMSNORM_NOALLOC_PARTIALS, mt::kWarpsPerBlock * 32, dim * sizeof(float), stream>>>(
+      static_cast<const __nv_bfloat16*>(x), w, rstd, static_cast<const __nv_bfloat16*>(dy),
+      static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx), partials, rows, dim);
+  mt::rmsnorm_bwd_reduce_kernel<<<(dim + 255) / 256, 256, 0, stream>>>(partials, MT_RMSNORM_NOALLOC_PARTIALS, dim, dw,
+                                                                      accumulate_dw ? 1 : 0);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(err, err_len, 8, cudaGetErrorString(e));
+  return 0;
+}
