@@ -38,6 +38,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default="")
     ap.add_argument("--tokens", type=int, default=32768)
+    ap.add_argument("--only", default="", help="run only shapes whose name contains this string")
     args = ap.parse_args()
     from mintext_b200.ops._ext import check_status, ext, status_word
 
@@ -51,6 +52,8 @@ def main():
     ]
     rows = []
     for name, M, N, K in shapes:
+        if args.only and args.only not in name:
+            continue
         x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
         w_kn = torch.randn(K, N, device="cuda", dtype=torch.bfloat16) * 0.02   # [in, out] storage
         dy = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)

@@ -38,6 +38,12 @@ void rope_inplace(void* x, const float* cos_t, const float* sin_t, const int* po
                   int heads, int head_dim, int rot_dim, int64_t row_stride, bool interleave, bool inverse,
                   cudaStream_t stream);
 
+// Half-rotation, out of place (src may equal dst), 16-byte vectors: needs rot_dim % 16 == 0, head_dim % 8 == 0 and
+// 16-byte aligned rows.  Columns past rot_dim are copied through.
+void rope_apply(const void* src, void* dst, const float* cos_t, const float* sin_t, const int* positions,
+                int64_t tokens, int seq_len, int heads, int head_dim, int rot_dim, int64_t src_stride,
+                int64_t dst_stride, bool inverse, cudaStream_t stream);
+
 // ---- elementwise/swiglu.cu
 // act: 0 silu, 1 gelu(tanh), 2 gelu(erf), 3 relu.  gate/up are column halves [rows, 2*inter] -> out [rows, inter]
 void gated_act_fwd(const void* gate_up, void* out, int64_t rows, int inter, int act, cudaStream_t stream);

@@ -85,6 +85,20 @@ void rope(torch::Tensor& x, const torch::Tensor& cos_t, const torch::Tensor& sin
                    (int)head_dim, (int)rot_dim, x.stride(0), interleave, inverse, cur_stream());
 }
 
+void rope_apply(const torch::Tensor& src, torch::Tensor& dst, const torch::Tensor& cos_t, const torch::Tensor& sin_t,
+                const c10::optional<torch::Tensor>& positions, int64_t seq_len, int64_t heads, int64_t head_dim,
+                int64_t rot_dim, bool inverse) {
+  TORCH_CHECK(src.dim() == 2 && dst.dim() == 2 && src.stride(1) == 1 && dst.stride(1) == 1);
+  TORCH_CHECK(src.scalar_type() == torch::kBFloat16 && dst.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(rot_dim % 16 == 0 && head_dim % 8 == 0 && src.stride(0) % 8 == 0 && dst.stride(0) % 8 == 0);
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(src.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(dst.data_ptr()) % 16 == 0);
+  TORCH_CHECK(cos_t.size(1) == rot_dim / 2 && cos_t.is_contiguous() && sin_t.is_contiguous());
+  c10::cuda::CUDAGuard guard(src.device());
+  mt::rope_apply(src.data_ptr(), dst.data_ptr(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(),
+                 positions ? positions->data_ptr<int>() : nullptr, src.size(0), (int)seq_len, (int)heads,
+                 (int)head_dim, (int)rot_dim, src.stride(0), dst.stride(0), inverse, cur_stream());
+}
+
 void gated_act_fwd(const torch::Tensor& gate_up, torch::Tensor& out, int64_t act) {
   TORCH_CHECK(gate_up.is_contiguous() && out.is_contiguous());
   const int inter = (int)out.size(-1);
@@ -235,6 +249,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rope", &rope);
+  m.def("rope_apply", &rope_apply);
   m.def("gated_act_fwd", &gated_act_fwd);
   m.def("gated_act_bwd", &gated_act_bwd);
   m.def("cross_entropy", &cross_entropy);

@@ -143,6 +143,78 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] = dw_s[i];
 }
 
+// Register-resident variant for dim = VPL * 256: every lane owns VPL 16-byte chunks of the row, reads x and dy once,
+// and keeps its slice of the weight gradient in registers across all rows the warp processes (no shared-memory
+// atomics in the row loop); the slices are combined through shared memory once per block at the end.
+template <int VPL>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                       const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
+                       const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                       float* __restrict__ dw_partial, int64_t rows) {
+  constexpr int dim = VPL * 256;
+  extern __shared__ float dw_s[];
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) dw_s[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t warp_stride = (int64_t)gridDim.x * kWarpsPerBlock;
+  float dw_r[VPL * 8];
+#pragma unroll
+  for (int i = 0; i < VPL * 8; ++i) dw_r[i] = 0.f;
+  for (int64_t row = warp_global; row < rows; row += warp_stride) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * dim);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + row * dim);
+    const float rstd = rstd_in[row];
+    Pack8 a[VPL], g[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      a[v].u = xr[v * 32 + lane];
+      g[v].u = gr[v * 32 + lane];
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * (v * 32 + lane)];
+      const float4 w1 = reinterpret_cast<const float4*>(w)[2 * (v * 32 + lane) + 1];
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = __bfloat162float(a[v].h[j]) * rstd;
+        const float gy = __bfloat162float(g[v].h[j]);
+        dot += xh * gy * wv[j];
+        dw_r[v * 8 + j] += gy * xh;
+      }
+    }
+    dot = warp_sum(dot) / dim;
+    const uint4* dr = dres ? reinterpret_cast<const uint4*>(dres + row * dim) : nullptr;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + row * dim);
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * (v * 32 + lane)];
+      const float4 w1 = reinterpret_cast<const float4*>(w)[2 * (v * 32 + lane) + 1];
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      Pack8 r, o;
+      if (dr) r.u = dr[v * 32 + lane];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = __bfloat162float(a[v].h[j]) * rstd;
+        float d = rstd * (__bfloat162float(g[v].h[j]) * wv[j] - xh * dot);
+        if (dr) d += __bfloat162float(r.h[j]);
+        o.h[j] = __float2bfloat16(d);
+      }
+      dxr[v * 32 + lane] = o.u;
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VPL; ++v)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(&dw_s[(v * 32 + lane) * 8 + j], dw_r[v * 8 + j]);
+  __syncthreads();
+  float* out = dw_partial + (int64_t)blockIdx.x * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] = dw_s[i];
+}
+
 __global__ void rmsnorm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int dim,
                                           float* __restrict__ dw, int accumulate) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -167,9 +239,17 @@ void rmsnorm_fwd(const void* x, const void* residual, const float* w, void* y, v
 void rmsnorm_bwd(const void* x, const float* w, const float* rstd, const void* dy, const void* dres, void* dx,
                  float* dw_partial, int num_partials, int64_t rows, int dim, cudaStream_t stream) {
   if (rows == 0) return;
-  rmsnorm_bwd_kernel<<<num_partials, kWarpsPerBlock * 32, dim * sizeof(float), stream>>>(
-      (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx,
-      dw_partial, rows, dim);
+  auto xb = (const __nv_bfloat16*)x;
+  auto gb = (const __nv_bfloat16*)dy;
+  auto rb = (const __nv_bfloat16*)dres;
+  auto ob = (__nv_bfloat16*)dx;
+  const int threads = kWarpsPerBlock * 32;
+  const size_t smem = dim * sizeof(float);
+  if (dim == 2048) rmsnorm_bwd_reg_kernel<8><<<num_partials, threads, smem, stream>>>(xb, w, rstd, gb, rb, ob, dw_partial, rows);
+  else if (dim == 1024) rmsnorm_bwd_reg_kernel<4><<<num_partials, threads, smem, stream>>>(xb, w, rstd, gb, rb, ob, dw_partial, rows);
+  else if (dim == 512) rmsnorm_bwd_reg_kernel<2><<<num_partials, threads, smem, stream>>>(xb, w, rstd, gb, rb, ob, dw_partial, rows);
+  else if (dim == 256) rmsnorm_bwd_reg_kernel<1><<<num_partials, threads, smem, stream>>>(xb, w, rstd, gb, rb, ob, dw_partial, rows);
+  else rmsnorm_bwd_kernel<<<num_partials, threads, smem, stream>>>(xb, w, rstd, gb, rb, ob, dw_partial, rows, dim);
 }
 
 void rmsnorm_bwd_reduce(const float* dw_partial, int num_partials, int dim, float* dw, bool accumulate,

@@ -147,16 +147,28 @@ class DecoderLayer(nn.Module):
             return self.mlp(h)
         return self.mlp(h), None
 
-    def forward(self, x, positions=None, mask=None, default_positions: bool = False):
+    def forward(self, x, positions=None, mask=None, default_positions: bool = False, pending=None,
+                defer_residual: bool = False):
+        """``pending`` is a feed-forward output of the previous layer that has not been added to ``x`` yet: it is
+        folded into this layer's first norm (one pass over memory instead of a separate add).  With
+        ``defer_residual`` the layer likewise returns ``(x, aux, own pending output)`` instead of adding it."""
         if self.use_post_ffw_norm:
+            if pending is not None:
+                x = x + pending
             h = self.post_attn_norm(self._attend(self.pre_attn_norm(x), positions, mask, default_positions))
             x = x + h
             h, aux = self._ffw(self.pre_ffw_norm(x))
             x = x + self.post_ffw_norm(h)
-            return x, aux
-        a = self._attend(self.pre_attn_norm(x), positions, mask, default_positions)
+            return (x, aux, None) if defer_residual else (x, aux)
+        if pending is not None:
+            n, x = self.pre_attn_norm.forward_add(pending, x)
+        else:
+            n = self.pre_attn_norm(x)
+        a = self._attend(n, positions, mask, default_positions)
         h, x = self.post_attn_norm.forward_add(a, x)  # x <- x + a ; h <- norm(x), one pass
         h, aux = self._ffw(h)
+        if defer_residual:
+            return x, aux, h
         return x + h, aux
 
 
@@ -201,10 +213,18 @@ class Transformer(nn.Module):
             positions = torch.arange(tokens.shape[1], device=tokens.device)[None].expand(tokens.shape[0], -1)
         x = F.embedding(self.token_embedder, tokens, dt, self.embedding_scale)
         all_aux = []
+        pending = None
+        fuse = REMAT_POLICIES[self.remat_policy] is None or not torch.is_grad_enabled()
         for layer in self.layers:
-            x, aux = apply_layer_with_remat(layer, x, positions, mask, self.remat_policy, default_positions)
+            if fuse:  # carry the last residual add into the next norm kernel
+                x, aux, pending = layer(x, positions, mask, default_positions, pending=pending, defer_residual=True)
+            else:
+                x, aux = apply_layer_with_remat(layer, x, positions, mask, self.remat_policy, default_positions)
             all_aux.append(aux)
-        x = self.final_norm(x)
+        if pending is not None:
+            x, _ = self.final_norm.forward_add(pending, x)
+        else:
+            x = self.final_norm(x)
         if return_hidden:
             return x, all_aux
         if self.tie_word_embeddings:

@@ -235,6 +235,7 @@ _NORM_PARTIALS = 148 * 2
 class _RMSNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, scale, eps, residual, main_grad):
+        ctx.set_materialize_grads(False)
         ctx.main_grad = main_grad
         shape = x.shape
         dim = shape[-1]
@@ -259,6 +260,9 @@ class _RMSNormFn(torch.autograd.Function):
     def backward(ctx, dy, dh=None):
         h, scale, rstd = ctx.saved_tensors
         dim = h.shape[-1]
+        if dy is None:  # only the summed residual stream was used downstream
+            g = dh if ctx.has_res else None
+            return g, None, None, g, None
         dy2 = dy.reshape(-1, dim).contiguous()
         dx = torch.empty_like(h)
         parts = torch.empty(_NORM_PARTIALS, dim, device=h.device, dtype=torch.float32)
@@ -292,24 +296,43 @@ def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, scale: torch.Tensor, e
 
 # ------------------------------------------------------------------------------------------------ rope
 class _RopeFn(torch.autograd.Function):
+    """Half-rotation RoPE, out of place.  The 16-byte vector kernel is used whenever the layout allows it (rotary
+    width a multiple of 16, packed heads); the scalar in-place kernel on a copy otherwise."""
+
     @staticmethod
     def forward(ctx, x, cos_t, sin_t, positions, rot_dim, interleave):
         B, S, H, d = x.shape
-        out = x.contiguous().clone()
         pos = None
         if positions is not None:
             pos = positions.reshape(-1).to(torch.int32).contiguous()
-        ext().rope(out.view(B * S, H * d), cos_t, sin_t, pos, S, H, d, rot_dim, interleave, False)
+        ctx.set_materialize_grads(False)
         ctx.save_for_backward(cos_t, sin_t, pos if pos is not None else torch.empty(0))
         ctx.meta = (B, S, H, d, rot_dim, interleave, pos is not None)
+        packed = x.stride(3) == 1 and x.stride(2) == d and x.stride(0) == S * x.stride(1)
+        if (not interleave) and rot_dim % 16 == 0 and d % 8 == 0 and packed and x.stride(1) % 8 == 0 \
+                and x.data_ptr() % 16 == 0:
+            out = torch.empty(B, S, H, d, device=x.device, dtype=x.dtype)
+            src = x.as_strided((B * S, H * d), (x.stride(1), 1))
+            ext().rope_apply(src, out.view(B * S, H * d), cos_t, sin_t, pos, S, H, d, rot_dim, False)
+            return out
+        out = x.contiguous().clone()
+        ext().rope(out.view(B * S, H * d), cos_t, sin_t, pos, S, H, d, rot_dim, interleave, False)
         return out
 
     @staticmethod
     def backward(ctx, g):
+        if g is None:
+            return None, None, None, None, None, None
         cos_t, sin_t, pos = ctx.saved_tensors
         B, S, H, d, rot_dim, interleave, has_pos = ctx.meta
-        dx = g.contiguous().clone()
-        ext().rope(dx.view(B * S, H * d), cos_t, sin_t, pos if has_pos else None, S, H, d, rot_dim, interleave, True)
+        p = pos if has_pos else None
+        g = g.contiguous()
+        if (not interleave) and rot_dim % 16 == 0 and d % 8 == 0:
+            dx = torch.empty_like(g)
+            ext().rope_apply(g.view(B * S, H * d), dx.view(B * S, H * d), cos_t, sin_t, p, S, H, d, rot_dim, True)
+            return dx, None, None, None, None, None
+        dx = g.clone()
+        ext().rope(dx.view(B * S, H * d), cos_t, sin_t, p, S, H, d, rot_dim, interleave, True)
         return dx, None, None, None, None, None
 
 
@@ -366,6 +389,7 @@ class _GateUpActFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, wg, wu, act_code, replay_buf, mg_g, mg_u):
+        ctx.set_materialize_grads(False)  # the raw gate/up buffer is an auxiliary output: no zero gradient for it
         T, M = x.shape[0], wg.shape[1]
         if replay_buf is not None:
             buf = replay_buf
