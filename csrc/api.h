@@ -12,12 +12,14 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64
                cudaStream_t stream);
 
 // ---- gemm/grouped_bf16.cu
-// Ragged grouped GEMM: rows of X are grouped by expert (offsets[e]..offsets[e+1]); W is [E, K, N] (b_mn) or
-// [E, N, K] (K-major).  `offsets` is a device int32[E+1] array.
-void grouped_gemm_bf16(const void* X, const void* W, void* Y, const int* offsets, int E, int M_total, int N, int K,
+// Rows of X / Y are grouped by expert: expert e owns rows offsets[e] .. offsets[e+1], every offset a multiple of 128
+// (groups are padded with zero rows).  `offsets` is a device int32[E+1]; M_cap is the allocated row count.
+// Y[rows, N] = X[rows, K] * W[e], W = [E, K, N] (w_mn_major) or [E, N, K] (K-major, the data-gradient product).
+void grouped_gemm_bf16(const void* X, const void* W, void* Y, const int* offsets, int E, int M_cap, int N, int K,
                        bool w_mn_major, int* status, int num_sms, cudaStream_t stream);
-// Transposed grouped GEMM (per-expert wgrad): dW[e] (+)= X_e^T @ G_e, X [M,K], G [M,N], dW [E,K,N] fp32 or bf16.
-void grouped_wgrad_bf16(const void* X, const void* G, void* dW, const int* offsets, int E, int M_total, int N, int K,
+// Per-expert weight gradient: dW[e] (+)= X_e^T @ G_e, X [M_cap, K], G [M_cap, N], dW [E, K, N] fp32 or bf16.
+// Experts without rows are skipped (clear dW beforehand when not accumulating).
+void grouped_wgrad_bf16(const void* X, const void* G, void* dW, const int* offsets, int E, int M_cap, int N, int K,
                         bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream);
 
 // ---- elementwise/rmsnorm.cu

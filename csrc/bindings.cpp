@@ -242,6 +242,37 @@ void adamw_publish(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, co
                     clip_coef ? clip_coef->data_ptr<float>() : nullptr, cur_stream());
 }
 
+void grouped_gemm(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& y, const torch::Tensor& offsets,
+                  bool w_is_ekn, torch::Tensor& status) {
+  // x [M_cap, K] bf16, rows grouped by expert at 128-aligned offsets ; w [E, K, N] (w_is_ekn) or [E, N, K]
+  check_bf16_2d(x, "x");
+  TORCH_CHECK(w.dim() == 3 && w.is_contiguous() && w.scalar_type() == torch::kBFloat16, "w must be contiguous bf16 [E,.,.]");
+  TORCH_CHECK(y.is_contiguous() && y.scalar_type() == torch::kBFloat16 && x.is_contiguous());
+  TORCH_CHECK(offsets.scalar_type() == torch::kInt32 && offsets.is_contiguous() && offsets.numel() == w.size(0) + 1);
+  const int64_t K = x.size(1);
+  const int64_t N = w_is_ekn ? w.size(2) : w.size(1);
+  TORCH_CHECK((w_is_ekn ? w.size(1) : w.size(2)) == K, "contraction sizes differ");
+  TORCH_CHECK(y.size(0) == x.size(0) && y.size(1) == N && x.size(0) % 128 == 0 && K % 8 == 0 && N % 8 == 0);
+  c10::cuda::CUDAGuard guard(x.device());
+  mt::grouped_gemm_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), offsets.data_ptr<int>(), (int)w.size(0),
+                        (int)x.size(0), (int)N, (int)K, w_is_ekn, status.data_ptr<int>(), sm_count(), cur_stream());
+}
+
+void grouped_wgrad(const torch::Tensor& x, const torch::Tensor& g, torch::Tensor& dw, const torch::Tensor& offsets,
+                   bool accumulate, torch::Tensor& status) {
+  check_bf16_2d(x, "x");
+  check_bf16_2d(g, "g");
+  TORCH_CHECK(x.is_contiguous() && g.is_contiguous() && dw.is_contiguous() && dw.dim() == 3);
+  const bool f32 = dw.scalar_type() == torch::kFloat32;
+  TORCH_CHECK(f32 || dw.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(dw.size(1) == x.size(1) && dw.size(2) == g.size(1) && x.size(0) == g.size(0) && x.size(0) % 128 == 0);
+  TORCH_CHECK(offsets.scalar_type() == torch::kInt32 && offsets.numel() == dw.size(0) + 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  mt::grouped_wgrad_bf16(x.data_ptr(), g.data_ptr(), dw.data_ptr(), offsets.data_ptr<int>(), (int)dw.size(0),
+                         (int)x.size(0), (int)g.size(1), (int)x.size(1), f32, accumulate, status.data_ptr<int>(),
+                         sm_count(), cur_stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -260,6 +291,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_barrier", &symm_barrier);
   m.def("grad_pull_reduce", &grad_pull_reduce);
   m.def("adamw_publish", &adamw_publish);
+  m.def("grouped_gemm", &grouped_gemm);
+  m.def("grouped_wgrad", &grouped_wgrad);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);
 }

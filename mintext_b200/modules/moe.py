@@ -64,11 +64,13 @@ class MoEExperts(nn.Module):
 
     def forward(self, x: torch.Tensor, topk_indices: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         """x ``[N,D]`` -> ``[N,D]``: route, grouped GEMM, SwiGLU on the column halves, grouped GEMM, unroute."""
-        rows, sort_idx, sizes = kernels.route(x, topk_indices, self.num_experts)
+        from mintext_b200.ops import moe as moe_ops
+
         gu = self.gate_up_proj if self.gate_up_proj.dtype == self.dtype else self.gate_up_proj.to(self.dtype)
         dn = self.down_proj if self.down_proj.dtype == self.dtype else self.down_proj.to(self.dtype)
-        if gu is self.gate_up_proj and hasattr(gu, "main_grad"):
-            pass
+        if moe_ops.cuda_path(x) and gu is self.gate_up_proj:
+            return moe_ops.experts_forward(x, topk_indices, topk_weights, gu, dn, self.act_name)
+        rows, sort_idx, sizes = kernels.route(x, topk_indices, self.num_experts)
         h = kernels.grouped_matmul_vjp(rows, gu, sizes)
         h = F.gated_act(h, self.act_name)
         y = kernels.grouped_matmul_vjp(h, dn, sizes)

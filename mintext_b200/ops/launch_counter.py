@@ -9,7 +9,7 @@ from __future__ import annotations
 _LAUNCHES_PER_CALL = {
     "gemm": 1, "rmsnorm_fwd": 1, "rmsnorm_bwd": 2, "rope": 1, "gated_act_fwd": 1, "gated_act_bwd": 1,
     "cross_entropy": 1, "embedding_fwd": 1, "embedding_bwd": 1, "adamw_step": 1, "sumsq": 1, "flash_fwd": 1,
-    "flash_bwd": 3, "symm_barrier": 1, "grad_pull_reduce": 1, "adamw_publish": 1,
+    "flash_bwd": 3, "grouped_gemm": 1, "grouped_wgrad": 1, "rope_apply": 1, "symm_barrier": 1, "grad_pull_reduce": 1, "adamw_publish": 1,
 }
 _count = 0
 _installed = False

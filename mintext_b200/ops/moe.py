@@ -1,7 +1,9 @@
-"""CUDA front-ends of the MoE ops (permute, grouped GEMM, transposed grouped GEMM).
+"""CUDA path of the MoE ops: padded expert-contiguous dispatch, tcgen05 grouped GEMMs, weighted combine.
 
-``cuda_path`` gates them: until a tensor is CUDA bf16 (and the backend is not forced to the oracle) the callers
-in :mod:`mintext_b200.kernels` use the plain-PyTorch statements instead.
+The grouped kernels want every expert's rows to start at a multiple of 128, so dispatch writes the ``N*K``
+(token, slot) rows into a buffer where each expert's group is padded with zero rows.  All index arithmetic
+(stable order inside an expert, padded offsets, destinations) stays on the device: the buffer is sized for the
+worst case ``N*K + E*127`` rows, so nothing has to be read back to the host.
 """
 
 from __future__ import annotations
@@ -12,83 +14,127 @@ from . import functional as F
 from . import oracle
 from ._ext import ext, status_word
 
+_PAD = 128
+
 
 def cuda_path(x: torch.Tensor) -> bool:
     return x.is_cuda and x.dtype == torch.bfloat16 and F._backend() != "oracle" and hasattr(ext(), "grouped_gemm")
 
 
-def _offsets(group_sizes: torch.Tensor) -> torch.Tensor:
-    off = torch.zeros(group_sizes.numel() + 1, dtype=torch.int32, device=group_sizes.device)
-    off[1:] = torch.cumsum(group_sizes, 0)
-    return off
+def _cumsum0(v: torch.Tensor) -> torch.Tensor:
+    out = torch.zeros(v.numel() + 1, dtype=torch.int64, device=v.device)
+    out[1:] = torch.cumsum(v, 0)
+    return out
 
 
-class _GroupedFn(torch.autograd.Function):
+def padded_offsets(group_sizes: torch.Tensor):
+    """``(int32 padded offsets [E+1], int64 unpadded offsets [E+1])``."""
+    padded = (group_sizes + (_PAD - 1)) // _PAD * _PAD
+    return _cumsum0(padded).to(torch.int32), _cumsum0(group_sizes)
+
+
+def capacity(rows: int, num_experts: int) -> int:
+    return (rows + num_experts * (_PAD - 1) + _PAD - 1) // _PAD * _PAD
+
+
+def row_destinations(sorted_experts: torch.Tensor, off_p: torch.Tensor, off_u: torch.Tensor) -> torch.Tensor:
+    """Position in the padded buffer of every row of the expert-sorted (unpadded) order."""
+    r = torch.arange(sorted_experts.numel(), device=sorted_experts.device)
+    return off_p.long()[sorted_experts] + (r - off_u[sorted_experts])
+
+
+class _GroupedPaddedFn(torch.autograd.Function):
+    """``y = x @ w[e]`` on a padded, expert-contiguous row buffer (forward, data gradient and weight gradient all
+    run the tcgen05 grouped kernel)."""
+
     @staticmethod
-    def forward(ctx, x, w, group_sizes, main_grad):
-        off = _offsets(group_sizes)
+    def forward(ctx, x, w, off_p, main_grad):
         y = torch.empty(x.shape[0], w.shape[2], device=x.device, dtype=torch.bfloat16)
-        ext().grouped_gemm(x, w, y, off, True, status_word(x.device))
-        ctx.save_for_backward(x, w, off)
+        ext().grouped_gemm(x, w, y, off_p, True, status_word(x.device))
+        ctx.save_for_backward(x, w, off_p)
         ctx.main_grad = main_grad
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w, off = ctx.saved_tensors
+        x, w, off_p = ctx.saved_tensors
         dy = dy.contiguous()
+        st = status_word(x.device)
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dx = torch.empty_like(x)
-            # dy[M,N] . w[e][K,N]^T : w[e] rows are K-major for this product
-            ext().grouped_gemm(dy, w, dx, off, False, status_word(x.device))
+            ext().grouped_gemm(dy, w, dx, off_p, False, st)  # rows of w[e] ([K, N]) are K-major for dy @ w[e]^T
         if ctx.needs_input_grad[1]:
             mg = ctx.main_grad
             if mg is not None:
-                ext().grouped_wgrad(x, dy, mg.view(w.shape), off, True, status_word(x.device))
+                ext().grouped_wgrad(x, dy, mg.view(w.shape), off_p, True, st)
             else:
                 dwf = torch.zeros(w.shape, device=w.device, dtype=torch.float32)
-                ext().grouped_wgrad(x, dy, dwf, off, False, status_word(x.device))
+                ext().grouped_wgrad(x, dy, dwf, off_p, False, st)
                 dw = dwf.to(w.dtype)
         return dx, dw, None, None
 
 
+def grouped_padded(x_p: torch.Tensor, w: torch.Tensor, off_p: torch.Tensor) -> torch.Tensor:
+    return _GroupedPaddedFn.apply(x_p, w, off_p, getattr(w, "main_grad", None))
+
+
+def _pad_rows(x: torch.Tensor, group_sizes: torch.Tensor):
+    E = group_sizes.numel()
+    off_p, off_u = padded_offsets(group_sizes)
+    experts = torch.repeat_interleave(torch.arange(E, device=x.device), group_sizes, output_size=x.shape[0])
+    dest = row_destinations(experts, off_p, off_u)
+    cap = capacity(x.shape[0], E)
+    x_p = torch.zeros(cap, x.shape[1], device=x.device, dtype=x.dtype).index_copy(0, dest, x)
+    return x_p, off_p, dest
+
+
 def grouped_matmul_cuda(x, w, group_sizes):
-    return _GroupedFn.apply(x.contiguous(), w, group_sizes, getattr(w, "main_grad", None))
+    """Public ragged form: rows grouped by expert without padding."""
+    x_p, off_p, dest = _pad_rows(x.contiguous(), group_sizes)
+    return grouped_padded(x_p, w, off_p).index_select(0, dest)
 
 
 def tgmm_cuda(lhs, rhs, group_sizes):
+    l_p, off_p, _ = _pad_rows(lhs.contiguous(), group_sizes)
+    r_p, _, _ = _pad_rows(rhs.contiguous(), group_sizes)
     out = torch.zeros(group_sizes.numel(), lhs.shape[1], rhs.shape[1], device=lhs.device, dtype=torch.float32)
-    ext().grouped_wgrad(lhs.contiguous(), rhs.contiguous(), out, _offsets(group_sizes), False, status_word(lhs.device))
+    ext().grouped_wgrad(l_p, r_p, out, off_p, False, status_word(lhs.device))
     return out.to(lhs.dtype)
 
 
-class _RouteFn(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, tokens, topk_idx, num_experts):
-        N, K = topk_idx.shape
-        flat = topk_idx.reshape(-1)
-        sort_idx = torch.argsort(flat, stable=True)
-        sizes = torch.bincount(flat, minlength=num_experts)
-        src_token = torch.div(sort_idx, K, rounding_mode="floor")
-        rows = tokens.index_select(0, src_token)
-        ctx.save_for_backward(sort_idx)
-        ctx.meta = (N, K)
-        ctx.mark_non_differentiable(sort_idx, sizes)
-        return rows, sort_idx, sizes
-
-    @staticmethod
-    def backward(ctx, drows, _a, _b):
-        (sort_idx,) = ctx.saved_tensors
-        N, K = ctx.meta
-        inv = torch.empty_like(sort_idx)
-        inv[sort_idx] = torch.arange(sort_idx.numel(), device=sort_idx.device)
-        return drows.index_select(0, inv).view(N, K, -1).sum(1), None, None
-
-
 def route_cuda(tokens, topk_idx, num_experts):
-    return _RouteFn.apply(tokens, topk_idx, num_experts)
+    """Reference-shaped ``route`` (unpadded result) for API parity."""
+    N, K = topk_idx.shape
+    flat = topk_idx.reshape(-1)
+    sort_idx = torch.argsort(flat, stable=True)
+    sizes = torch.bincount(flat, minlength=num_experts)
+    rows = tokens.index_select(0, torch.div(sort_idx, K, rounding_mode="floor"))
+    return rows, sort_idx, sizes
 
 
 def unroute_cuda(sorted_out, sort_idx, topk_w, K):
     return oracle.unroute(sorted_out, sort_idx, topk_w, K)
+
+
+def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, gate_up: torch.Tensor,
+                    down: torch.Tensor, act: str) -> torch.Tensor:
+    """Routed-expert MLP for ``x [N, D]``: dispatch into the padded layout, two grouped GEMMs around the gated
+    activation, weighted combine back to token order.  Differentiable end to end."""
+    N, K = topk_idx.shape
+    E = gate_up.shape[0]
+    flat = topk_idx.reshape(-1)
+    sort_idx = torch.argsort(flat, stable=True)             # (token, slot) order kept inside an expert
+    sizes = torch.bincount(flat, minlength=E)
+    off_p, off_u = padded_offsets(sizes)
+    dest = row_destinations(flat[sort_idx], off_p, off_u)   # padded position of every sorted row
+    pos = torch.empty_like(dest)
+    pos[sort_idx] = dest                                     # padded position of flat entry n*K + k
+    cap = capacity(N * K, E)
+    src_token = torch.div(sort_idx, K, rounding_mode="floor")
+    rows = torch.zeros(cap, x.shape[1], device=x.device, dtype=x.dtype).index_copy(0, dest, x.index_select(0, src_token))
+    h = grouped_padded(rows, gate_up, off_p)
+    h = F.gated_act(h, act)
+    y = grouped_padded(h, down, off_p)
+    picked = y.index_select(0, pos).view(N, K, -1)
+    return torch.einsum("nkd,nk->nd", picked, topk_w.to(picked.dtype))
