@@ -86,6 +86,12 @@ void adamw_publish(float* master, float* m, float* v, const float* grad, const P
                    int64_t n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
                    float grad_scale, const float* clip_coef, cudaStream_t stream);
 
+// ---- comm/ep_rows.cu : expert-parallel dispatch (push) / combine (pull) of token rows over peer memory
+void ep_push_rows(const void* src, const int* dst_rank, const int64_t* dst_pos, const PeerPtrs& bufs, int64_t rows,
+                  int dim, int64_t cap_rows, int* overflow, cudaStream_t stream);
+void ep_pull_rows(void* out, const int* src_rank, const int64_t* src_pos, const PeerPtrs& bufs, int64_t rows, int dim,
+                  int64_t cap_rows, cudaStream_t stream);
+
 // ---- attention/flash_fwd.cu, flash_bwd.cu
 struct AttnParams {
   const void* q; const void* k; const void* v; void* o; float* lse;

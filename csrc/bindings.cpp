@@ -273,6 +273,25 @@ void grouped_wgrad(const torch::Tensor& x, const torch::Tensor& g, torch::Tensor
                          sm_count(), cur_stream());
 }
 
+void ep_push_rows(const torch::Tensor& src, const torch::Tensor& dst_rank, const torch::Tensor& dst_pos,
+                  const std::vector<int64_t>& buf_ptrs, int64_t cap_rows, torch::Tensor& overflow) {
+  TORCH_CHECK(src.is_contiguous() && src.scalar_type() == torch::kBFloat16 && src.dim() == 2 && src.size(1) % 8 == 0);
+  TORCH_CHECK(dst_rank.scalar_type() == torch::kInt32 && dst_pos.scalar_type() == torch::kInt64);
+  TORCH_CHECK(dst_rank.numel() == src.size(0) && dst_pos.numel() == src.size(0));
+  c10::cuda::CUDAGuard guard(src.device());
+  mt::ep_push_rows(src.data_ptr(), dst_rank.data_ptr<int>(), dst_pos.data_ptr<int64_t>(), to_peers(buf_ptrs), src.size(0),
+                   (int)src.size(1), cap_rows, overflow.data_ptr<int>(), cur_stream());
+}
+
+void ep_pull_rows(torch::Tensor& out, const torch::Tensor& src_rank, const torch::Tensor& src_pos,
+                  const std::vector<int64_t>& buf_ptrs, int64_t cap_rows) {
+  TORCH_CHECK(out.is_contiguous() && out.scalar_type() == torch::kBFloat16 && out.dim() == 2 && out.size(1) % 8 == 0);
+  TORCH_CHECK(src_rank.scalar_type() == torch::kInt32 && src_pos.scalar_type() == torch::kInt64);
+  c10::cuda::CUDAGuard guard(out.device());
+  mt::ep_pull_rows(out.data_ptr(), src_rank.data_ptr<int>(), src_pos.data_ptr<int64_t>(), to_peers(buf_ptrs), out.size(0),
+                   (int)out.size(1), cap_rows, cur_stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -293,6 +312,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_publish", &adamw_publish);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("grouped_wgrad", &grouped_wgrad);
+  m.def("ep_push_rows", &ep_push_rows);
+  m.def("ep_pull_rows", &ep_pull_rows);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);
 }

@@ -126,6 +126,7 @@ class MinTextConfig(BaseModel):
     moe_gate_up_tiling: list[int] = []
     moe_down_tiling: list[int] = []
     moe_use_fp8: bool = False
+    moe_capacity_factor: float = 2.0  # expert-parallel receive buffers hold this multiple of a rank's own rows
 
     # qwen3-next
     full_attention_interval: int = 4

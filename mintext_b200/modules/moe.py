@@ -48,19 +48,43 @@ class MoERouter(nn.Module):
             self.norm_topk_prob, self.routed_scaling_factor)
 
 
+def _per_expert_init(shape_tail, fan_in, lo, hi, rngs, dtype):
+    """Experts ``lo .. hi`` of a stacked parameter, each drawn from its own generator (seeded from one value taken
+    off the model's stream), so that a rank holding only a slice of the experts initialises exactly the values the
+    unsharded model would have there."""
+    tag = int(torch.randint(0, 2 ** 31 - 1, (1,), generator=rngs))
+    out = torch.empty((hi - lo,) + tuple(shape_tail), dtype=dtype)
+    for e in range(lo, hi):
+        g = torch.Generator().manual_seed((tag + 104729 * e) % (2 ** 63 - 1))
+        out[e - lo] = truncated_normal_init(shape_tail, fan_in, g, dtype)
+    return out
+
+
 class MoEExperts(nn.Module):
+    """Routed experts.  Under expert parallelism (a process-wide :class:`ExpertParallel` context) the module holds
+    only this rank's ``E / ep`` experts and exchanges tokens with the other ranks."""
+
     def __init__(self, config, *, rngs=None):
         super().__init__()
+        from mintext_b200.parallel.ep import current_ep
+
         E, D, I = config.num_experts, config.hidden_size, config.moe_intermediate_size
         self.num_experts = E
         self.dtype = config.torch_dtype
         self.act_name = config.hidden_activation
+        self.ep = current_ep()
+        lo, hi = self.ep.local_expert_range(E) if self.ep is not None else (0, E)
+        self.local_range = (lo, hi)
         wdt = config.torch_weight_dtype
+        rngs = rngs if rngs is not None else torch.Generator().manual_seed(0)
         # the reference's initialiser divides by total // shape[2], i.e. E*D and E*I: the std shrinks with E
-        self.gate_up_proj = nn.Parameter(truncated_normal_init((E, D, 2 * I), E * D, rngs, wdt))
+        self.gate_up_proj = nn.Parameter(_per_expert_init((D, 2 * I), E * D, lo, hi, rngs, wdt))
         self.gate_up_proj.logical_axes = ("exp", "embed", "mlp")
-        self.down_proj = nn.Parameter(truncated_normal_init((E, I, D), E * I, rngs, wdt))
+        self.down_proj = nn.Parameter(_per_expert_init((I, D), E * I, lo, hi, rngs, wdt))
         self.down_proj.logical_axes = ("exp", "mlp", "embed")
+        if self.ep is not None and self.ep.size > 1:
+            self.gate_up_proj.expert_parallel = True
+            self.down_proj.expert_parallel = True
 
     def forward(self, x: torch.Tensor, topk_indices: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         """x ``[N,D]`` -> ``[N,D]``: route, grouped GEMM, SwiGLU on the column halves, grouped GEMM, unroute."""
@@ -68,6 +92,14 @@ class MoEExperts(nn.Module):
 
         gu = self.gate_up_proj if self.gate_up_proj.dtype == self.dtype else self.gate_up_proj.to(self.dtype)
         dn = self.down_proj if self.down_proj.dtype == self.dtype else self.down_proj.to(self.dtype)
+        if self.ep is not None and self.ep.size > 1:
+            from mintext_b200.parallel import ep as ep_mod
+
+            if self.ep.fused and moe_ops.cuda_path(x) and gu is self.gate_up_proj:
+                return ep_mod.experts_forward_peer(self.ep, x, topk_indices, topk_weights, gu, dn, self.act_name,
+                                                   self.num_experts)
+            return ep_mod.experts_forward_collective(self.ep, x, topk_indices, topk_weights, self.gate_up_proj,
+                                                     self.down_proj, self.act_name, self.num_experts, self.dtype)
         if moe_ops.cuda_path(x) and gu is self.gate_up_proj:
             return moe_ops.experts_forward(x, topk_indices, topk_weights, gu, dn, self.act_name)
         rows, sort_idx, sizes = kernels.route(x, topk_indices, self.num_experts)

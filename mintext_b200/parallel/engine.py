@@ -97,6 +97,8 @@ class TrainEngine:
         dev = self.device
         big: list[_Slot] = []
         small: list[_Slot] = []
+        exp: list[_Slot] = []
+        off_e = 0
         frozen: list[tuple[str, torch.nn.Parameter]] = []
         off_b = off_s = 0
         for name, p in self.model.named_parameters():
@@ -104,7 +106,10 @@ class TrainEngine:
                 frozen.append((name, p))
                 continue
             is_big = p.dim() >= 2 and p.numel() >= 4096 and "conv_weight" not in name
-            if is_big and self.compute_dtype == torch.bfloat16:
+            if getattr(p, "expert_parallel", False) and self.compute_dtype == torch.bfloat16:
+                exp.append(_Slot(name, p, off_e, p.numel()))  # this rank's experts: local, not sharded
+                off_e = _round_up(off_e + p.numel(), _ALIGN)
+            elif is_big and self.compute_dtype == torch.bfloat16:
                 big.append(_Slot(name, p, off_b, p.numel()))
                 off_b = _round_up(off_b + p.numel(), _ALIGN)
             else:
@@ -133,6 +138,21 @@ class TrainEngine:
         for s in big:
             s.param.data = self.param_flat[s.offset:s.offset + s.numel].view(s.param.shape)
             s.param.main_grad = self.grad_flat[s.offset:s.offset + s.numel].view(s.param.shape)
+
+        # expert-parallel parameters: every rank owns its experts outright (compute copy, master, moments, grads)
+        self.exp = FlatGroup(exp, _round_up(max(off_e, 4), _ALIGN))
+        if exp:
+            em = torch.zeros(self.exp.total, dtype=torch.float32)
+            for s in exp:
+                em[s.offset:s.offset + s.numel] = s.param.detach().float().reshape(-1)
+            self.exp_master = em.to(dev)
+            self.exp_param = self.exp_master.to(torch.bfloat16)
+            self.exp_grad = torch.zeros(self.exp.total, device=dev, dtype=torch.float32)
+            self.exp_m = torch.zeros_like(self.exp_grad)
+            self.exp_v = torch.zeros_like(self.exp_grad)
+            for s in exp:
+                s.param.data = self.exp_param[s.offset:s.offset + s.numel].view(s.param.shape)
+                s.param.main_grad = self.exp_grad[s.offset:s.offset + s.numel].view(s.param.shape)
 
         self.small_param = torch.zeros(self.small.total, device=dev, dtype=torch.float32)
         self.small_grad = torch.zeros(self.small.total, device=dev, dtype=torch.float32)
@@ -181,10 +201,12 @@ class TrainEngine:
     def zero_grad(self) -> None:
         self.grad_flat.zero_()
         self.small_grad.zero_()
+        if self.exp.slots:
+            self.exp_grad.zero_()
 
     def _fold_autograd_grads(self) -> None:
         """Parameters whose ops returned ordinary autograd gradients: add them into the flat buffers."""
-        for grp in (self.big, self.small):
+        for grp in (self.big, self.small, self.exp):
             for s in grp.slots:
                 g = s.param.grad
                 if g is not None:
@@ -224,6 +246,8 @@ class TrainEngine:
         else:
             self._sumsq.zero_()
             e.sumsq(gshard, self._sumsq)
+        if self.exp.slots:
+            e.sumsq(self.exp_grad, self._sumsq)  # experts are disjoint across ranks: they add to the global norm
         if W > 1:
             dist.all_reduce(self._sumsq, group=self.group)
         e.sumsq(self.small_grad, self._sumsq)
@@ -243,6 +267,9 @@ class TrainEngine:
                          cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)
             if W > 1:
                 dist.all_gather_into_tensor(self.param_flat, pshard, group=self.group)
+        if self.exp.slots:
+            e.adamw_step(self.exp_master, self.exp_m, self.exp_v, self.exp_grad, self.exp_param, lr, cfg.adam_b1,
+                         cfg.adam_b2, cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)
         self._small_adamw(lr, bc1, bc2, inv)
         self.kernel_launches += 4
         return {"grad_norm": grad_norm, "learning_rate": lr}
@@ -258,6 +285,8 @@ class TrainEngine:
     def param_norm(self) -> torch.Tensor:
         s = torch.zeros(1, device=self.device, dtype=torch.float32)
         ext().sumsq(self.master, s)
+        if self.exp.slots:
+            ext().sumsq(self.exp_master, s)
         if self.world > 1:
             dist.all_reduce(s, group=self.group)
         ext().sumsq(self.small_param, s)
@@ -338,6 +367,14 @@ class TrainEngine:
             "opt_state/flat_exp_avg": {"tensor": self.exp_avg, **common},
             "opt_state/flat_exp_avg_sq": {"tensor": self.exp_avg_sq, **common},
         }
+        for s in self.exp.slots:  # rank r holds experts [r*El, (r+1)*El): a contiguous range of the stacked tensor
+            a = self.rank * s.numel
+            meta = {"writer_rank": self.rank, "flat_range": (a, a + s.numel), "flat_total": s.numel * self.world,
+                    "suffix": f".ep{self.rank}"}
+            sl = slice(s.offset, s.offset + s.numel)
+            tree[f"params/{s.name}"] = {"tensor": self.exp_master[sl], **meta}
+            tree[f"opt_state/mu/{s.name}"] = {"tensor": self.exp_m[sl], **meta}
+            tree[f"opt_state/nu/{s.name}"] = {"tensor": self.exp_v[sl], **meta}
         for s in self.small.slots:
             tree[f"params/{s.name}"] = s.param.detach()
             tree[f"opt_state/mu/{s.name}"] = self.small_m[s.offset:s.offset + s.numel].view(s.param.shape)
@@ -368,6 +405,15 @@ class TrainEngine:
                 a, b = max(s.offset, lo), min(s.offset + s.numel, hi)
                 if a < b:
                     self.master[a - lo:b - lo] = full[a - s.offset:b - s.offset].to(self.device)
+        for s in self.exp.slots:
+            a = self.rank * s.numel
+            sl = slice(s.offset, s.offset + s.numel)
+            self.exp_master[sl] = read(f"params/{s.name}", (a, a + s.numel)).reshape(-1).float().to(self.device)
+            if not self.params_only_restore and f"opt_state/mu/{s.name}" in paths:
+                self.exp_m[sl] = read(f"opt_state/mu/{s.name}", (a, a + s.numel)).reshape(-1).to(self.device)
+                self.exp_v[sl] = read(f"opt_state/nu/{s.name}", (a, a + s.numel)).reshape(-1).to(self.device)
+        if self.exp.slots:
+            self.exp_param.copy_(self.exp_master.to(torch.bfloat16))
         for s in self.small.slots:
             s.param.copy_(read(f"params/{s.name}").to(self.device))
             if not self.params_only_restore and f"opt_state/mu/{s.name}" in paths:

@@ -1,0 +1,265 @@
+"""Expert parallelism: experts are distributed over the ranks of an ``expert`` group, tokens travel to them.
+
+Two exchange implementations with identical results:
+
+* **peer-memory path** (CUDA, symmetric memory): a rank computes, entirely on the device, where each of its
+  ``N*K`` (token, slot) rows belongs in the *destination* rank's expert-contiguous, 128-padded input buffer and
+  stores the row there with ``ep_push_rows``; the routing permute and the all-to-all are one pass, there is no
+  host synchronisation and no regrouping on the receiver.  After the grouped GEMMs the expert outputs stay in
+  place and the token's home rank pulls its K rows (``ep_pull_rows``) and reduces them with the routing weights.
+  The backward pass mirrors this (push of output gradients, pull of input gradients).  Buffers hold
+  ``capacity_factor * N*K`` rows; a destination that would overflow is reported through a status flag, never
+  written out of bounds.
+* **collective path** (any backend, also gloo on CPU): all-gather of tokens and routing, every rank serves the
+  slots that chose its experts, reduce-scatter of the partial outputs.  This is the baseline composition and the
+  oracle for the peer-memory path.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+_CURRENT = None
+
+
+def current_ep():
+    """The process-wide expert-parallel context, or None (single-rank experts)."""
+    return _CURRENT
+
+
+def set_current_ep(ctx) -> None:
+    global _CURRENT
+    _CURRENT = ctx
+
+
+class ExpertParallel:
+    def __init__(self, group, device: torch.device, capacity_factor: float = 2.0, fused: bool = True):
+        self.group = group
+        self.size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device(device)
+        self.capacity_factor = capacity_factor
+        self.fused = bool(fused) and self.device.type == "cuda" and self.size <= 8
+        self._bufs = None  # (cap_rows, dim) -> symmetric buffers
+        self.seq = 0
+        self.overflow = None
+
+    def local_expert_range(self, num_experts: int) -> tuple[int, int]:
+        if num_experts % self.size != 0:
+            raise ValueError(f"num_experts ({num_experts}) must be divisible by the expert-parallel size ({self.size})")
+        per = num_experts // self.size
+        return self.rank * per, (self.rank + 1) * per
+
+    # ------------------------------------------------------------------ symmetric buffers
+    def buffers(self, cap_rows: int, dim: int):
+        if self._bufs is not None and self._bufs["cap"] >= cap_rows and self._bufs["dim"] == dim:
+            return self._bufs
+        import torch.distributed._symmetric_memory as symm
+
+        from mintext_b200.ops._ext import status_word
+
+        inb = symm.empty(cap_rows * dim, dtype=torch.bfloat16, device=self.device)
+        outb = symm.empty(cap_rows * dim, dtype=torch.bfloat16, device=self.device)
+        flags = symm.empty(64, dtype=torch.int32, device=self.device)
+        flags.zero_()
+        h_in, h_out, h_fl = (symm.rendezvous(t, self.group) for t in (inb, outb, flags))
+        self._bufs = {
+            "cap": cap_rows, "dim": dim, "in": inb.view(cap_rows, dim), "out": outb.view(cap_rows, dim),
+            "in_ptrs": [int(p) for p in h_in.buffer_ptrs], "out_ptrs": [int(p) for p in h_out.buffer_ptrs],
+            "flag_ptrs": [int(p) for p in h_fl.buffer_ptrs], "handles": (h_in, h_out, h_fl), "flags": flags,
+        }
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.seq = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        status_word(self.device)
+        return self._bufs
+
+    def barrier(self) -> None:
+        from mintext_b200.ops._ext import ext, status_word
+
+        self.seq += 1
+        ext().symm_barrier(self._bufs["flag_ptrs"], self.rank, self.seq, status_word(self.device))
+
+    def check_overflow(self) -> None:
+        if self.overflow is not None and int(self.overflow.item()) != 0:
+            self.overflow.zero_()
+            raise RuntimeError("expert-parallel dispatch overflowed a receive buffer; raise moe capacity_factor")
+
+
+# ------------------------------------------------------------------------------------------ differentiable collectives
+class _AllGatherRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        n = dist.get_world_size(group)
+        out = [torch.empty_like(x) for _ in range(n)]
+        dist.all_gather(out, x.contiguous(), group=group)
+        return torch.cat(out, dim=0)
+
+    @staticmethod
+    def backward(ctx, g):
+        n, r = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        per = g.shape[0] // n
+        return g[r * per:(r + 1) * per], None
+
+
+class _ReduceScatterRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        n, r = dist.get_world_size(group), dist.get_rank(group)
+        x = x.contiguous().clone()
+        dist.all_reduce(x, group=group)
+        per = x.shape[0] // n
+        return x[r * per:(r + 1) * per].clone()
+
+    @staticmethod
+    def backward(ctx, g):
+        n = dist.get_world_size(ctx.group)
+        out = [torch.empty_like(g) for _ in range(n)]
+        dist.all_gather(out, g.contiguous(), group=ctx.group)
+        return torch.cat(out, dim=0), None
+
+
+def experts_forward_collective(ep: ExpertParallel, x, topk_idx, topk_w, gate_up_local, down_local, act: str,
+                               num_experts: int, dtype):
+    """All-gather tokens and routing, serve the slots owned by the local experts, reduce-scatter the outputs."""
+    from mintext_b200 import kernels
+    from mintext_b200.ops import functional as F
+
+    lo, hi = ep.local_expert_range(num_experts)
+    xa = _AllGatherRows.apply(x, ep.group)
+    ia = _AllGatherRows.apply(topk_idx, ep.group)
+    wa = _AllGatherRows.apply(topk_w, ep.group)
+    mine = (ia >= lo) & (ia < hi)                      # [ep*N, K]
+    tok, slot = torch.nonzero(mine, as_tuple=True)     # host sync: acceptable on the baseline path
+    e_local = ia[tok, slot] - lo
+    order = torch.argsort(e_local, stable=True)
+    tok, slot, e_local = tok[order], slot[order], e_local[order]
+    sizes = torch.bincount(e_local, minlength=hi - lo)
+    rows = xa.index_select(0, tok)
+    h = kernels.grouped_matmul_vjp(rows, gate_up_local.to(dtype), sizes)
+    h = F.gated_act(h, act)
+    y = kernels.grouped_matmul_vjp(h, down_local.to(dtype), sizes)
+    y = y * wa[tok, slot].to(y.dtype)[:, None]
+    partial = torch.zeros_like(xa).index_add(0, tok, y)
+    return _ReduceScatterRows.apply(partial, ep.group)
+
+
+# ------------------------------------------------------------------------------------------ peer-memory path
+def _plan(ep: ExpertParallel, topk_idx: torch.Tensor, num_experts: int, cap: int):
+    """Device-side routing plan: for every local (token, slot) row its destination rank and padded position, and
+    the padded offsets of this rank's own experts."""
+    N, K = topk_idx.shape
+    E, R = num_experts, ep.size
+    El = E // R
+    flat = topk_idx.reshape(-1)
+    counts = torch.bincount(flat, minlength=E)
+    all_counts = torch.empty(R, E, dtype=counts.dtype, device=counts.device)
+    dist.all_gather_into_tensor(all_counts, counts, group=ep.group)
+    total = all_counts.sum(0)                                   # rows per global expert
+    padded = (total + 127) // 128 * 128
+    off = torch.zeros(R, El + 1, dtype=torch.int64, device=flat.device)
+    off[:, 1:] = torch.cumsum(padded.view(R, El), dim=1)        # padded offsets inside each destination rank
+    before = torch.cumsum(all_counts, 0) - all_counts           # rows of earlier source ranks, per expert
+    sort_idx = torch.argsort(flat, stable=True)
+    e_sorted = flat[sort_idx]
+    off_u = torch.zeros(E + 1, dtype=torch.int64, device=flat.device)
+    off_u[1:] = torch.cumsum(counts, 0)
+    within = torch.arange(flat.numel(), device=flat.device) - off_u[e_sorted]
+    dst_rank = torch.div(e_sorted, El, rounding_mode="floor")
+    dst_pos = off[dst_rank, e_sorted % El] + before[ep.rank][e_sorted] + within
+    src_token = torch.div(sort_idx, K, rounding_mode="floor")
+    # flat (n, k) order for the combine
+    rank_flat = torch.empty_like(dst_rank)
+    pos_flat = torch.empty_like(dst_pos)
+    rank_flat[sort_idx] = dst_rank
+    pos_flat[sort_idx] = dst_pos
+    return {
+        "src_token": src_token, "dst_rank": dst_rank.to(torch.int32), "dst_pos": dst_pos,
+        "rank_flat": rank_flat.to(torch.int32), "pos_flat": pos_flat,
+        "off_local": off[ep.rank].to(torch.int32).contiguous(), "cap": cap, "N": N, "K": K,
+    }
+
+
+class _Dispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ep, plan):
+        from mintext_b200.ops._ext import ext
+
+        b = ep.buffers(plan["cap"], x.shape[1])
+        rows = x.index_select(0, plan["src_token"])
+        b["in"].zero_()
+        ep.barrier()  # every rank's receive buffer is cleared and no longer read
+        ext().ep_push_rows(rows, plan["dst_rank"], plan["dst_pos"], b["in_ptrs"], b["cap"], ep.overflow)
+        ep.barrier()  # all rows have landed
+        ctx.ep, ctx.plan, ctx.n = ep, plan, x.shape[0]
+        return b["in"][: plan["cap"]].clone()
+
+    @staticmethod
+    def backward(ctx, d_rows):
+        from mintext_b200.ops._ext import ext
+
+        ep, plan = ctx.ep, ctx.plan
+        b = ep.buffers(plan["cap"], d_rows.shape[1])
+        b["out"][: plan["cap"]].copy_(d_rows)
+        ep.barrier()
+        pulled = torch.empty(plan["dst_rank"].numel(), d_rows.shape[1], device=d_rows.device, dtype=d_rows.dtype)
+        ext().ep_pull_rows(pulled, plan["dst_rank"], plan["dst_pos"], b["out_ptrs"], b["cap"])
+        ep.barrier()
+        dx = torch.zeros(ctx.n, d_rows.shape[1], device=d_rows.device, dtype=torch.float32)
+        dx.index_add_(0, plan["src_token"], pulled.float())
+        return dx.to(d_rows.dtype), None, None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y_p, w, ep, plan):
+        from mintext_b200.ops._ext import ext
+
+        b = ep.buffers(plan["cap"], y_p.shape[1])
+        b["out"][: plan["cap"]].copy_(y_p)
+        ep.barrier()
+        N, K = plan["N"], plan["K"]
+        picked = torch.empty(N * K, y_p.shape[1], device=y_p.device, dtype=y_p.dtype)
+        ext().ep_pull_rows(picked, plan["rank_flat"], plan["pos_flat"], b["out_ptrs"], b["cap"])
+        ep.barrier()
+        ctx.save_for_backward(picked, w)
+        ctx.ep, ctx.plan = ep, plan
+        return torch.einsum("nkd,nk->nd", picked.view(N, K, -1), w.to(picked.dtype))
+
+    @staticmethod
+    def backward(ctx, dy):
+        from mintext_b200.ops._ext import ext
+
+        picked, w = ctx.saved_tensors
+        ep, plan = ctx.ep, ctx.plan
+        N, K = plan["N"], plan["K"]
+        d_picked = (dy[:, None, :] * w.to(dy.dtype)[:, :, None]).reshape(N * K, -1).contiguous()
+        dw = torch.einsum("nkd,nd->nk", picked.view(N, K, -1).float(), dy.float()).to(w.dtype)
+        b = ep.buffers(plan["cap"], dy.shape[1])
+        b["in"].zero_()
+        ep.barrier()
+        ext().ep_push_rows(d_picked, plan["rank_flat"], plan["pos_flat"], b["in_ptrs"], b["cap"], ep.overflow)
+        ep.barrier()
+        return b["in"][: plan["cap"]].clone(), dw, None, None
+
+
+def experts_forward_peer(ep: ExpertParallel, x, topk_idx, topk_w, gate_up_local, down_local, act: str,
+                         num_experts: int):
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops import moe as moe_ops
+
+    N, K = topk_idx.shape
+    El = num_experts // ep.size
+    cap = moe_ops.capacity(int(ep.capacity_factor * N * K), El)
+    plan = _plan(ep, topk_idx, num_experts, cap)
+    rows = _Dispatch.apply(x, ep, plan)
+    h = moe_ops.grouped_padded(rows, gate_up_local, plan["off_local"])
+    h = F.gated_act(h, act)
+    y = moe_ops.grouped_padded(h, down_local, plan["off_local"])
+    return _Combine.apply(y, topk_w, ep, plan)

@@ -54,6 +54,11 @@ def train(config: MinTextConfig) -> dict:
     mesh = setup_mesh(config)
     use_gpu = torch.cuda.is_available() and config.kernel_backend != "oracle"
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_gpu else torch.device("cpu")
+    if config.ici_expert_parallelism > 1 and config.num_experts > 0:
+        from mintext_b200.parallel.ep import ExpertParallel, set_current_ep
+
+        set_current_ep(ExpertParallel(mesh.group(("expert",)), device, config.moe_capacity_factor,
+                                      fused=config.fused_collectives))
     model = create_sharded_model(config, mesh)
 
     if use_gpu:

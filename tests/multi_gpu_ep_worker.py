@@ -1,0 +1,62 @@
+"""Worker for the expert-parallel GPU test (one process per GPU): trains a small MoE model with the experts
+distributed over all ranks, once with the peer-memory token exchange and once with the collective exchange."""
+
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+
+def moe_config(fused: bool, ep: int):
+    from mintext_b200 import MinTextConfig
+
+    return MinTextConfig(num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                         intermediate_size=512, vocab_size=1024, seq_length=128, steps=20, learning_rate=1e-3,
+                         num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, n_group=4, topk_group=2,
+                         first_k_dense_replace=1, n_shared_experts=1, enable_tensorboard=False,
+                         enable_checkpointing=False, fused_collectives=fused, ici_expert_parallelism=ep)
+
+
+def main(out_path: str) -> None:
+    rank = int(os.environ["RANK"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.engine import TrainEngine, local_batch_rows
+    from mintext_b200.parallel.ep import ExpertParallel, set_current_ep
+
+    world = dist.get_world_size()
+    g = torch.Generator().manual_seed(7)
+    global_tok = torch.randint(0, 1024, (8, 128), generator=g)
+    lo, hi = local_batch_rows(8, world, rank)
+    tok = global_tok[lo:hi].to(dev)
+    results = {}
+    for name, fused in (("peer", True), ("collective", False)):
+        cfg = moe_config(fused, world)
+        ep = ExpertParallel(dist.group.WORLD, dev, cfg.moe_capacity_factor, fused=fused)
+        set_current_ep(ep)
+        eng = TrainEngine(Transformer(cfg, rngs=0), cfg, device=dev)
+        assert len(eng.exp.slots) == 2, [s.name for s in eng.exp.slots]
+        losses = []
+        for _ in range(5):
+            out = eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=1)
+            losses.append(float(out["loss"]))
+        eng.check()
+        ep.check_overflow()
+        results[name] = {"losses": losses, "grad_norm": float(out["grad_norm"])}
+        set_current_ep(None)
+    if rank == 0:
+        Path(out_path).write_text(json.dumps(results))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1])

@@ -52,6 +52,36 @@ def test_multi_gpu_matches_single_gpu(world, tmp_path):
         assert abs(a - b) < 1e-2 * max(1.0, abs(b))
 
 
+def test_expert_parallel_matches_single_gpu(tmp_path):
+    """Experts distributed over 2 GPUs (peer-memory dispatch/combine and the collective baseline) train exactly
+    like the single-GPU model that holds all experts."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    out = tmp_path / "ep.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29671", str(ROOT / "tests" / "multi_gpu_ep_worker.py"), str(out)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.loads(out.read_text())
+    sys.path.insert(0, str(ROOT / "tests"))
+    from multi_gpu_ep_worker import moe_config
+
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.engine import TrainEngine
+
+    cfg = moe_config(True, 1)
+    eng = TrainEngine(Transformer(cfg, rngs=0), cfg, device="cuda")
+    g = torch.Generator().manual_seed(7)
+    tok = torch.randint(0, 1024, (8, 128), generator=g).cuda()
+    single = [float(eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=1)["loss"]) for _ in range(5)]
+    eng.check()
+    for name in ("peer", "collective"):
+        for a, b in zip(res[name]["losses"], single):
+            assert abs(a - b) < 3e-2, (name, res[name]["losses"], single)
+
+
 def test_barrier_with_absent_peer_times_out_cleanly():
     """Two-rank barrier where nothing ever posts the peer's flag: the wait runs out after about a second, the
     status word records it, and the context stays usable."""
