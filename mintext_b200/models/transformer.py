@@ -211,6 +211,15 @@ class Transformer(nn.Module):
             default_positions = positions is None
         if positions is None:
             positions = torch.arange(tokens.shape[1], device=tokens.device)[None].expand(tokens.shape[0], -1)
+        from mintext_b200.parallel.tp import current_tp
+
+        tp = current_tp()
+        if tp is not None and tp.size > 1:
+            # token-sharded residual stream: this rank embeds (and later scores) rows [lo, hi) of the flat tokens
+            B, S = tokens.shape
+            tp.batch_shape = (B, S)
+            lo, hi = tp.shard(B * S, "tokens per batch")
+            tokens = tokens.reshape(1, B * S)[:, lo:hi]
         x = F.embedding(self.token_embedder, tokens, dt, self.embedding_scale)
         all_aux = []
         pending = None

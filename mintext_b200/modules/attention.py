@@ -39,6 +39,9 @@ class Attention(nn.Module):
         self.attn_logit_softcapping = config.attn_logit_softcapping
         D, H, Hkv, dh = config.hidden_size, config.num_attention_heads, config.num_key_value_heads, config.head_dim
         wdt = config.torch_weight_dtype
+        from mintext_b200.parallel.tp import current_tp
+
+        self.tp = current_tp() if (current_tp() is not None and current_tp().size > 1) else None
         qps = config.query_pre_attn_scalar
         self.scale = (qps if qps is not None else dh) ** -0.5
         q_dim = 2 * dh if use_gate else dh
@@ -50,9 +53,53 @@ class Attention(nn.Module):
         if use_qk_norm:
             self.q_norm = RMSNorm(dh, config.rms_norm_eps, self.dtype)
             self.k_norm = RMSNorm(dh, config.rms_norm_eps, self.dtype)
+        if self.tp is not None:
+            # keep this rank's heads: the full kernels were drawn from the model's stream, so the slices equal
+            # the corresponding heads of the unsharded model
+            qlo, qhi = self.tp.shard(H, "num_attention_heads")
+            klo, khi = self.tp.shard(Hkv, "num_key_value_heads")
+            for lin, (a, b), dim in ((self.query, (qlo, qhi), 1), (self.key, (klo, khi), 1),
+                                     (self.value, (klo, khi), 1), (self.out, (qlo, qhi), 0)):
+                full = lin.kernel.data
+                lin.kernel = nn.Parameter((full[:, a:b] if dim == 1 else full[a:b]).clone().contiguous())
+                lin.kernel.logical_axes = ("embed", "heads", "kv") if dim == 1 else ("heads", "kv", "embed")
+                lin.kernel.tensor_parallel = True
+            self.local_heads, self.local_kv_heads = qhi - qlo, khi - klo
+
+    def _forward_tp(self, x, positions, default_positions):
+        """Token-sharded input ``[1, T/t, D]``: gather tokens into the q/k/v projections of the local heads,
+        attend over the full sequences, scatter the output projection's partial sums back to token shards."""
+        from mintext_b200.parallel import tp as tpm
+
+        tp = self.tp
+        B, S = tp.batch_shape
+        Tl, D = x.shape[-2], x.shape[-1]
+        Hl, Hk, dh = self.local_heads, self.local_kv_heads, self.head_dim
+        qd = 2 * dh if self.use_gate else dh
+        _, (q_raw, k, v) = tpm.column_linear(
+            x.reshape(Tl, D), [self.query.kernel.reshape(D, Hl * qd), self.key.kernel.reshape(D, Hk * dh),
+                               self.value.kernel.reshape(D, Hk * dh)], tp, self.dtype)
+        q_raw, k, v = q_raw.view(B, S, Hl, qd), k.view(B, S, Hk, dh), v.view(B, S, Hk, dh)
+        q, gate = (q_raw.chunk(2, dim=-1) if self.use_gate else (q_raw, None))
+        if self.use_qk_norm:
+            q, k = self.q_norm(q.contiguous()), self.k_norm(k)
+        if positions is None or positions.shape[-1] != S:
+            positions = torch.arange(S, device=x.device)[None].expand(B, -1)
+        q = self.rope(q, positions, default_positions)
+        k = self.rope(k, positions, default_positions)
+        o = F.attention(q, k, v, self.scale, causal=True, window=self.sliding_window,
+                        softcap=self.attn_logit_softcapping)
+        if gate is not None:
+            o = o * torch.sigmoid(gate)
+        y = tpm.row_linear(o.reshape(B * S, Hl * dh), self.out.kernel.reshape(Hl * dh, D), tp, self.dtype)
+        return y.view(1, Tl, D)
 
     def forward(self, x: torch.Tensor, positions: torch.Tensor | None, mask: torch.Tensor | None = None,
                 default_positions: bool = False) -> torch.Tensor:
+        if self.tp is not None:
+            if mask is not None:
+                raise NotImplementedError("explicit attention masks are not supported under tensor parallelism")
+            return self._forward_tp(x, positions, default_positions)
         q_raw = self.query(x)
         k = self.key(x)
         v = self.value(x)

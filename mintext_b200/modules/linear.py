@@ -99,8 +99,26 @@ class MLP(nn.Module):
         self.gate = Linear(D, M, dt, wdt, ("embed", "mlp"), use_fp8=fp8, rngs=rngs, name="mlp_gate_proj")
         self.up = Linear(D, M, dt, wdt, ("embed", "mlp"), use_fp8=fp8, rngs=rngs, name="mlp_up")
         self.down = Linear(M, D, dt, wdt, ("mlp", "embed"), use_fp8=fp8, rngs=rngs, name="mlp_down")
+        from mintext_b200.parallel.tp import current_tp
+
+        self.tp = current_tp() if (current_tp() is not None and current_tp().size > 1) else None
+        if self.tp is not None:
+            lo, hi = self.tp.shard(M, "intermediate_size")
+            for lin, dim in ((self.gate, 1), (self.up, 1), (self.down, 0)):
+                full = lin.kernel.data
+                axes = lin.kernel.logical_axes
+                lin.kernel = nn.Parameter((full[:, lo:hi] if dim == 1 else full[lo:hi]).clone().contiguous())
+                lin.kernel.logical_axes = axes
+                lin.kernel.tensor_parallel = True
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp is not None:
+            from mintext_b200.parallel import tp as tpm
+
+            lead, D = x.shape[:-1], x.shape[-1]
+            _, (g, u) = tpm.column_linear(x.reshape(-1, D), [self.gate.kernel, self.up.kernel], self.tp, self.gate.dtype)
+            h = F.gated_act(torch.cat([g, u], dim=-1), self.act_name)
+            return tpm.row_linear(h, self.down.kernel, self.tp, self.gate.dtype).view(*lead, D)
         if self.gate.use_fp8:
             h = oracle.activation(self.act_name)(self.gate(x)) * self.up(x)
         else:

@@ -63,8 +63,14 @@ class TrainEngine:
     re-homes every parameter into the flat buffers and keeps the fp32 values as (sharded) master weights.
     """
 
-    def __init__(self, model: torch.nn.Module, config, device: torch.device | str = "cuda", group=None):
+    def __init__(self, model: torch.nn.Module, config, device: torch.device | str = "cuda", group=None,
+                 local_reduce_group=None):
+        """``group``: ranks over which replicated parameters are reduced and the optimizer state is sharded
+        (default: all ranks).  ``local_reduce_group``: ranks that hold *the same* slice of the expert- or
+        tensor-parallel parameters (their data-parallel replicas); None when every rank's slice is unique."""
         self.config = config
+        self.local_reduce_group = local_reduce_group
+        self.local_reduce_size = dist.get_world_size(local_reduce_group) if local_reduce_group is not None else 1
         self.model = model
         self.device = torch.device(device)
         self.group = group
@@ -106,7 +112,8 @@ class TrainEngine:
                 frozen.append((name, p))
                 continue
             is_big = p.dim() >= 2 and p.numel() >= 4096 and "conv_weight" not in name
-            if getattr(p, "expert_parallel", False) and self.compute_dtype == torch.bfloat16:
+            if (getattr(p, "expert_parallel", False) or getattr(p, "tensor_parallel", False)) \
+                    and self.compute_dtype == torch.bfloat16:
                 exp.append(_Slot(name, p, off_e, p.numel()))  # this rank's experts: local, not sharded
                 off_e = _round_up(off_e + p.numel(), _ALIGN)
             elif is_big and self.compute_dtype == torch.bfloat16:
@@ -247,7 +254,12 @@ class TrainEngine:
             self._sumsq.zero_()
             e.sumsq(gshard, self._sumsq)
         if self.exp.slots:
-            e.sumsq(self.exp_grad, self._sumsq)  # experts are disjoint across ranks: they add to the global norm
+            # slices are disjoint across ranks up to their data-parallel replicas: count each slice once
+            if self.local_reduce_group is not None:
+                dist.all_reduce(self.exp_grad, group=self.local_reduce_group)
+            tmp = torch.zeros_like(self._sumsq)
+            e.sumsq(self.exp_grad, tmp)
+            self._sumsq.add_(tmp / self.local_reduce_size)
         if W > 1:
             dist.all_reduce(self._sumsq, group=self.group)
         e.sumsq(self.small_grad, self._sumsq)
@@ -286,7 +298,9 @@ class TrainEngine:
         s = torch.zeros(1, device=self.device, dtype=torch.float32)
         ext().sumsq(self.master, s)
         if self.exp.slots:
-            ext().sumsq(self.exp_master, s)
+            tmp = torch.zeros_like(s)
+            ext().sumsq(self.exp_master, tmp)
+            s.add_(tmp / self.local_reduce_size)
         if self.world > 1:
             dist.all_reduce(s, group=self.group)
         ext().sumsq(self.small_param, s)

@@ -1,0 +1,133 @@
+"""Tensor parallelism with token-sharded activations (Megatron-style TP + sequence parallelism).
+
+Inside a tensor-parallel group of ``t`` ranks the residual stream is sharded over tokens: a rank holds rows
+``[r*T/t, (r+1)*T/t)`` of the flattened ``[T, D]`` activations of the group's batch.  A layer's column-parallel
+projections (query/key/value heads, MLP gate/up columns) consume the *gathered* tokens and produce this rank's
+slice of the features; its row-parallel projections (attention output, MLP down) produce partial sums over all
+tokens that are reduce-scattered back to the token shards:
+
+    x_local --norm--> all-gather --> [q|k|v]_local heads --> attention --> out_local --> reduce-scatter --> + x_local
+
+Embedding, norms and the output head are replicated and operate on the local tokens only, so the tensor-parallel
+ranks behave like data-parallel ranks for them (their gradients are reduced over every rank of the job).
+
+``all_gather_tokens`` / ``reduce_scatter_tokens`` are differentiable (each is the other's backward).  On CUDA with
+``fused=True`` the projections call the fused kernels in :mod:`mintext_b200.ops.tp_gemm` (all-gather folded into
+the consuming GEMM, GEMM epilogue scattering partial tiles to their owners); otherwise NCCL / gloo collectives
+around ordinary GEMMs, which is the baseline composition and the oracle.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+_CURRENT = None
+
+
+def current_tp():
+    return _CURRENT
+
+
+def set_current_tp(ctx) -> None:
+    global _CURRENT
+    _CURRENT = ctx
+
+
+class TensorParallel:
+    def __init__(self, group, device, fused: bool = True):
+        self.group = group
+        self.size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device(device)
+        self.fused = bool(fused) and self.device.type == "cuda" and self.size <= 8
+        self._comm = None
+
+    def shard(self, n: int, what: str) -> tuple[int, int]:
+        if n % self.size != 0:
+            raise ValueError(f"{what} ({n}) must be divisible by the tensor-parallel size ({self.size})")
+        per = n // self.size
+        return self.rank * per, (self.rank + 1) * per
+
+    def comm(self):
+        """Peer-memory workspace of the fused kernels (created on first use)."""
+        if self._comm is None:
+            from mintext_b200.ops.tp_gemm import TPWorkspace
+
+            self._comm = TPWorkspace(self)
+        return self._comm
+
+
+class _AllGatherTokens(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        n = dist.get_world_size(group)
+        out = torch.empty((n * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return _reduce_scatter(g.contiguous(), ctx.group), None
+
+
+class _ReduceScatterTokens(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _reduce_scatter(x.contiguous(), group)
+
+    @staticmethod
+    def backward(ctx, g):
+        n = dist.get_world_size(ctx.group)
+        out = torch.empty((n * g.shape[0],) + tuple(g.shape[1:]), dtype=g.dtype, device=g.device)
+        dist.all_gather_into_tensor(out, g.contiguous(), group=ctx.group)
+        return out, None
+
+
+def _reduce_scatter(x: torch.Tensor, group) -> torch.Tensor:
+    n, r = dist.get_world_size(group), dist.get_rank(group)
+    per = x.shape[0] // n
+    if x.is_cuda:
+        out = torch.empty((per,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x, group=group)
+        return out
+    y = x.clone()  # gloo has no reduce-scatter
+    dist.all_reduce(y, group=group)
+    return y[r * per:(r + 1) * per].clone()
+
+
+def all_gather_tokens(x: torch.Tensor, tp: TensorParallel) -> torch.Tensor:
+    """``[T/t, ...] -> [T, ...]`` (rows of rank 0 first)."""
+    return _AllGatherTokens.apply(x, tp.group)
+
+
+def reduce_scatter_tokens(x: torch.Tensor, tp: TensorParallel) -> torch.Tensor:
+    """``[T, ...]`` partial sums on every rank ``-> [T/t, ...]`` complete sums of this rank's rows."""
+    return _ReduceScatterTokens.apply(x, tp.group)
+
+
+def column_linear(x_local: torch.Tensor, weights: list[torch.Tensor], tp: TensorParallel, dtype, names=None):
+    """Gather the token shards once and apply several column-parallel kernels ``[D, out_local...]`` to them.
+    Returns the gathered input (kept for the weight gradients) and one output per kernel."""
+    from mintext_b200.ops import functional as F
+
+    if tp.fused and F.use_cuda(x_local) and all(w.dtype == torch.bfloat16 for w in weights):
+        from mintext_b200.ops import tp_gemm
+
+        return tp_gemm.ag_linear(x_local, weights, tp)
+    xg = all_gather_tokens(x_local, tp)
+    names = names or [None] * len(weights)
+    return xg, [F.linear(xg, w, name=n, dtype=dtype) for w, n in zip(weights, names)]
+
+
+def row_linear(x: torch.Tensor, weight: torch.Tensor, tp: TensorParallel, dtype, name=None) -> torch.Tensor:
+    """Row-parallel projection: ``x [T, in_local] @ W [in_local, D]`` summed over ranks, scattered to token shards."""
+    from mintext_b200.ops import functional as F
+
+    if tp.fused and F.use_cuda(x) and weight.dtype == torch.bfloat16:
+        from mintext_b200.ops import tp_gemm
+
+        return tp_gemm.linear_rs(x, weight, tp)
+    return reduce_scatter_tokens(F.linear(x, weight, name=name, dtype=dtype), tp)

@@ -59,12 +59,21 @@ def train(config: MinTextConfig) -> dict:
 
         set_current_ep(ExpertParallel(mesh.group(("expert",)), device, config.moe_capacity_factor,
                                       fused=config.fused_collectives))
+    local_reduce_group = None
+    if config.ici_tensor_parallelism > 1:
+        from mintext_b200.parallel.tp import TensorParallel, set_current_tp
+
+        if config.num_experts > 0 or config.attention_type == "mla" or "linear_attention" in config.layer_types:
+            raise NotImplementedError("tensor parallelism covers dense MHA/GQA models")
+        set_current_tp(TensorParallel(mesh.group(("tensor",)), device, fused=config.fused_collectives))
+        if mesh.shape["data"] * mesh.shape["fsdp"] > 1:
+            local_reduce_group = mesh.group(("data", "fsdp"))
     model = create_sharded_model(config, mesh)
 
     if use_gpu:
         from mintext_b200.parallel.engine import TrainEngine
 
-        state = TrainEngine(model, config, device=device)
+        state = TrainEngine(model, config, device=device, local_reduce_group=local_reduce_group)
     else:
         from mintext_b200 import trainer
 

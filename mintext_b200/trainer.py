@@ -112,6 +112,13 @@ def compute_loss(params, model, config, batch, loss_scale: float | None = None):
     fused = F.use_cuda(model.final_norm.scale.new_empty(0, dtype=config.torch_dtype)) and tokens.is_cuda
     hidden_mode = fused or config.num_vocab_tiles > 1
     out, aux_list = model(tokens, None, mask, return_hidden=hidden_mode)
+    from mintext_b200.parallel.tp import current_tp
+
+    tp = current_tp()
+    if tp is not None and tp.size > 1:  # the model returned this rank's token shard
+        lo, hi = tp.shard(B * S, "tokens per batch")
+        targets = targets.reshape(1, B * S)[:, lo:hi]
+        B, S = 1, hi - lo
     ntok = B * S
     scale = loss_scale if loss_scale is not None else 1.0 / ntok
     if fused:
