@@ -92,6 +92,16 @@ void ep_push_rows(const void* src, const int* dst_rank, const int64_t* dst_pos, 
 void ep_pull_rows(void* out, const int* src_rank, const int64_t* src_pos, const PeerPtrs& bufs, int64_t rows, int dim,
                   int64_t cap_rows, cudaStream_t stream);
 
+// ---- comm/tp_gemm.cu: tensor-parallel GEMMs fused with their collective (bf16; T tokens over `world` ranks)
+// C[T,N] = gather(shards)[T,K] * op(B); the kernel itself fills `gathered` from the ranks' shards (peer memory)
+// while it computes; `ready` is int[T/128], zeroed by the caller before the call, ready_target = 128*K*2/16384.
+void tp_gemm_ag(const PeerPtrs& shards, void* gathered, const void* B, void* C, int T, int N, int K, int rank, int world,
+                bool b_mn_major, int* ready, int ready_target, int* status, int num_sms, cudaStream_t stream);
+// partial[T,N] = A[T,K] * op(B), rows of rank i stored into staging_slots.p[i] ([T/world, N], peer memory).
+void tp_gemm_rs(const void* A, const void* B, const PeerPtrs& staging_slots, int T, int N, int K, int rank, int world,
+                bool b_mn_major, int* status, int num_sms, cudaStream_t stream);
+void tp_reduce_slots(const void* staging, void* y, int slots, int64_t slot_elems, cudaStream_t stream);
+
 // ---- attention/flash_fwd.cu, flash_bwd.cu
 struct AttnParams {
   const void* q; const void* k; const void* v; void* o; float* lse;

@@ -292,6 +292,42 @@ void ep_pull_rows(torch::Tensor& out, const torch::Tensor& src_rank, const torch
                    (int)out.size(1), cap_rows, cur_stream());
 }
 
+// out[T, N] = gather(shards)[T, K] @ (b_kn ? B[K, N] : B[N, K]^T); fills `gathered` on the way.
+void tp_gemm_ag(const std::vector<int64_t>& shard_ptrs, torch::Tensor& gathered, const torch::Tensor& B, torch::Tensor& out,
+                bool b_kn, int64_t rank, torch::Tensor& ready, torch::Tensor& status) {
+  TORCH_CHECK(gathered.is_contiguous() && B.is_contiguous() && out.is_contiguous());
+  TORCH_CHECK(gathered.scalar_type() == torch::kBFloat16 && B.scalar_type() == torch::kBFloat16 &&
+              out.scalar_type() == torch::kBFloat16);
+  const int64_t T = gathered.size(0), K = gathered.size(1);
+  const int64_t N = b_kn ? B.size(1) : B.size(0);
+  TORCH_CHECK((b_kn ? B.size(0) : B.size(1)) == K && out.size(0) == T && out.size(1) == N);
+  TORCH_CHECK(K % 64 == 0 && N % 8 == 0 && ready.numel() >= T / 128 && ready.scalar_type() == torch::kInt32);
+  c10::cuda::CUDAGuard guard(out.device());
+  mt::tp_gemm_ag(to_peers(shard_ptrs), gathered.data_ptr(), B.data_ptr(), out.data_ptr(), (int)T, (int)N, (int)K, (int)rank,
+                 (int)shard_ptrs.size(), b_kn, ready.data_ptr<int>(), (int)(128 * K * 2 / 16384), status.data_ptr<int>(),
+                 sm_count(), cur_stream());
+}
+
+// Partial products of all T rows; rows owned by rank i land in slot_ptrs[i] (its staging slot for this rank).
+void tp_gemm_rs(const torch::Tensor& A, const torch::Tensor& B, const std::vector<int64_t>& slot_ptrs, bool b_kn,
+                int64_t rank, torch::Tensor& status) {
+  TORCH_CHECK(A.is_contiguous() && B.is_contiguous() && A.scalar_type() == torch::kBFloat16 &&
+              B.scalar_type() == torch::kBFloat16);
+  const int64_t T = A.size(0), K = A.size(1);
+  const int64_t N = b_kn ? B.size(1) : B.size(0);
+  TORCH_CHECK((b_kn ? B.size(0) : B.size(1)) == K && K % 8 == 0 && N % 8 == 0);
+  c10::cuda::CUDAGuard guard(A.device());
+  mt::tp_gemm_rs(A.data_ptr(), B.data_ptr(), to_peers(slot_ptrs), (int)T, (int)N, (int)K, (int)rank, (int)slot_ptrs.size(),
+                 b_kn, status.data_ptr<int>(), sm_count(), cur_stream());
+}
+
+void tp_reduce_slots(const torch::Tensor& staging, torch::Tensor& y) {
+  TORCH_CHECK(staging.is_contiguous() && y.is_contiguous() && staging.scalar_type() == torch::kBFloat16 &&
+              y.scalar_type() == torch::kBFloat16 && y.numel() % 8 == 0 && staging.numel() % y.numel() == 0);
+  c10::cuda::CUDAGuard guard(y.device());
+  mt::tp_reduce_slots(staging.data_ptr(), y.data_ptr(), (int)(staging.numel() / y.numel()), y.numel(), cur_stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -314,6 +350,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_wgrad", &grouped_wgrad);
   m.def("ep_push_rows", &ep_push_rows);
   m.def("ep_pull_rows", &ep_pull_rows);
+  m.def("tp_gemm_ag", &tp_gemm_ag);
+  m.def("tp_gemm_rs", &tp_gemm_rs);
+  m.def("tp_reduce_slots", &tp_reduce_slots);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);
 }

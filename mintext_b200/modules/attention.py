@@ -77,8 +77,8 @@ class Attention(nn.Module):
         Hl, Hk, dh = self.local_heads, self.local_kv_heads, self.head_dim
         qd = 2 * dh if self.use_gate else dh
         _, (q_raw, k, v) = tpm.column_linear(
-            x.reshape(Tl, D), [self.query.kernel.reshape(D, Hl * qd), self.key.kernel.reshape(D, Hk * dh),
-                               self.value.kernel.reshape(D, Hk * dh)], tp, self.dtype)
+            x.reshape(Tl, D), [tpm.as_matrix(self.query.kernel, D), tpm.as_matrix(self.key.kernel, D),
+                               tpm.as_matrix(self.value.kernel, D)], tp, self.dtype)
         q_raw, k, v = q_raw.view(B, S, Hl, qd), k.view(B, S, Hk, dh), v.view(B, S, Hk, dh)
         q, gate = (q_raw.chunk(2, dim=-1) if self.use_gate else (q_raw, None))
         if self.use_qk_norm:
@@ -91,7 +91,7 @@ class Attention(nn.Module):
                         softcap=self.attn_logit_softcapping)
         if gate is not None:
             o = o * torch.sigmoid(gate)
-        y = tpm.row_linear(o.reshape(B * S, Hl * dh), self.out.kernel.reshape(Hl * dh, D), tp, self.dtype)
+        y = tpm.row_linear(o.reshape(B * S, Hl * dh), tpm.as_matrix(self.out.kernel, Hl * dh), tp, self.dtype)
         return y.view(1, Tl, D)
 
     def forward(self, x: torch.Tensor, positions: torch.Tensor | None, mask: torch.Tensor | None = None,

@@ -108,12 +108,29 @@ def reduce_scatter_tokens(x: torch.Tensor, tp: TensorParallel) -> torch.Tensor:
     return _ReduceScatterTokens.apply(x, tp.group)
 
 
+def as_matrix(kernel: torch.Tensor, rows: int) -> torch.Tensor:
+    """2-D ``[rows, -1]`` view of a (possibly head-shaped) kernel that keeps the engine's ``main_grad`` attribute."""
+    if kernel.dim() == 2 and kernel.shape[0] == rows:
+        return kernel
+    w2 = kernel.reshape(rows, -1)
+    if hasattr(kernel, "main_grad"):
+        w2.main_grad = kernel.main_grad
+    return w2
+
+
+def _fusable(tp: TensorParallel, x: torch.Tensor, weights, tokens_local: int, k: int) -> bool:
+    from mintext_b200.ops import functional as F
+
+    return (tp.fused and F.use_cuda(x) and x.dtype == torch.bfloat16 and tokens_local % 128 == 0 and k % 64 == 0
+            and all(w.dtype == torch.bfloat16 and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0 for w in weights))
+
+
 def column_linear(x_local: torch.Tensor, weights: list[torch.Tensor], tp: TensorParallel, dtype, names=None):
     """Gather the token shards once and apply several column-parallel kernels ``[D, out_local...]`` to them.
     Returns the gathered input (kept for the weight gradients) and one output per kernel."""
     from mintext_b200.ops import functional as F
 
-    if tp.fused and F.use_cuda(x_local) and all(w.dtype == torch.bfloat16 for w in weights):
+    if _fusable(tp, x_local, weights, x_local.shape[0], x_local.shape[1]):
         from mintext_b200.ops import tp_gemm
 
         return tp_gemm.ag_linear(x_local, weights, tp)
@@ -126,7 +143,7 @@ def row_linear(x: torch.Tensor, weight: torch.Tensor, tp: TensorParallel, dtype,
     """Row-parallel projection: ``x [T, in_local] @ W [in_local, D]`` summed over ranks, scattered to token shards."""
     from mintext_b200.ops import functional as F
 
-    if tp.fused and F.use_cuda(x) and weight.dtype == torch.bfloat16:
+    if _fusable(tp, x, [weight], x.shape[0] // tp.size, weight.shape[1]):
         from mintext_b200.ops import tp_gemm
 
         return tp_gemm.linear_rs(x, weight, tp)

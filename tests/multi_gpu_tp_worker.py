@@ -1,0 +1,92 @@
+"""Worker for the tensor-parallel GPU test (one process per GPU, all ranks in one tensor-parallel group).
+
+Part 1 compares the fused projections (gather folded into the GEMM, GEMM scattering its tiles) with the NCCL
+composition on random data, values and gradients.  Part 2 trains a small model with both variants."""
+
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+
+def tp_config(fused: bool, tp: int):
+    from mintext_b200 import MinTextConfig
+
+    return MinTextConfig(num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                         intermediate_size=512, vocab_size=1024, seq_length=128, steps=20, learning_rate=1e-3,
+                         enable_tensorboard=False, enable_checkpointing=False, fused_collectives=fused,
+                         ici_tensor_parallelism=tp)
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
+
+
+def op_level(dev, rank, world):
+    from mintext_b200.parallel import tp as tpm
+
+    fused = tpm.TensorParallel(dist.group.WORLD, dev, fused=True)
+    plain = tpm.TensorParallel(dist.group.WORLD, dev, fused=False)
+    g = torch.Generator().manual_seed(100 + rank)
+    Tl, K = 512, 256
+    errs = {}
+    for trial in range(3):  # several calls: exercises the parity double-buffering
+        x = (torch.randn(Tl, K, generator=g) * 0.5).to(dev, torch.bfloat16)
+        gw = torch.Generator().manual_seed(5 + trial)
+        ws = [(torch.randn(K, n, generator=gw) / 16).to(dev, torch.bfloat16) for n in (384, 128)]
+        wo = (torch.randn(384, K, generator=gw) / 16).to(dev, torch.bfloat16)
+        outs = {}
+        for name, ctx in (("fused", fused), ("plain", plain)):
+            xx = x.clone().requires_grad_(True)
+            wl = [w.clone().requires_grad_(True) for w in ws]
+            wol = wo.clone().requires_grad_(True)
+            xg, (a, b) = tpm.column_linear(xx, wl, ctx, torch.bfloat16)
+            y = tpm.row_linear(torch.tanh(a.float()).to(torch.bfloat16), wol, ctx, torch.bfloat16)
+            loss = (y.float() ** 2).sum() + (b.float() ** 2).sum() * 0.1
+            loss.backward()
+            outs[name] = [xg.detach(), a.detach(), b.detach(), y.detach(), xx.grad, wl[0].grad, wl[1].grad, wol.grad]
+        for i, key in enumerate(("gathered", "col0", "col1", "row", "dx", "dw0", "dw1", "dwo")):
+            errs[key] = max(errs.get(key, 0.0), _rel(outs["fused"][i], outs["plain"][i]))
+    return errs
+
+
+def main(out_path: str) -> None:
+    rank = int(os.environ["RANK"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from mintext_b200.models import Transformer
+    from mintext_b200.ops._ext import check_status
+    from mintext_b200.parallel.engine import TrainEngine
+    from mintext_b200.parallel.tp import TensorParallel, set_current_tp
+
+    world = dist.get_world_size()
+    results = {"ops": op_level(dev, rank, world)}
+    check_status(dev)
+    g = torch.Generator().manual_seed(7)
+    tok = torch.randint(0, 1024, (8, 128), generator=g).to(dev)  # one tensor-parallel group: all ranks share the batch
+    for name, fused in (("fused", True), ("nccl", False)):
+        cfg = tp_config(fused, world)
+        set_current_tp(TensorParallel(dist.group.WORLD, dev, fused=fused))
+        eng = TrainEngine(Transformer(cfg, rngs=0), cfg, device=dev)
+        losses = []
+        for _ in range(5):
+            out = eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=1)
+            losses.append(float(out["loss"]))
+        eng.check()
+        results[name] = {"losses": losses, "grad_norm": float(out["grad_norm"])}
+        set_current_tp(None)
+    if rank == 0:
+        Path(out_path).write_text(json.dumps(results))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1])

@@ -98,3 +98,27 @@ def test_barrier_with_absent_peer_times_out_cleanly():
     x = torch.ones(4, device="cuda")
     assert float(x.sum()) == 4.0  # the device still answers
     check_status()  # status was cleared by the raise
+
+
+def test_tensor_parallel_fused_kernels(tmp_path):
+    """Two tensor-parallel GPUs: the gather-in-GEMM and scatter-in-epilogue kernels agree with the NCCL composition
+    (values and gradients), and a model trained either way follows the single-GPU losses."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    out = tmp_path / "tp.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29673", str(ROOT / "tests" / "multi_gpu_tp_worker.py"), str(out)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.loads(out.read_text())
+    assert res["ops"]["gathered"] == 0.0, res["ops"]
+    for key, err in res["ops"].items():
+        assert err < 2e-2, res["ops"]
+    single = _single_gpu_losses()
+    for name in ("fused", "nccl"):
+        for a, b in zip(res[name]["losses"], single):
+            assert abs(a - b) < 3e-2, (name, res[name]["losses"], single)
+    for a, b in zip(res["fused"]["losses"], res["nccl"]["losses"]):
+        assert abs(a - b) < 1e-2
