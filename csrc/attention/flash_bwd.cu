@@ -1,4 +1,5 @@
-// Flash attention backward for sm_100a (bf16, head_dim 64, grouped-query K/V, causal / sliding window / soft-cap).
+// Flash attention backward for sm_100a (bf16, head_dim 64 or 128, grouped-query K/V, causal / sliding window /
+// soft-cap).
 //
 // One CTA = one (batch, kv head, 128-key block).  It keeps K_j and V_j in shared memory and dK_j, dV_j as fp32
 // accumulators in tensor memory while it walks over every query head of the group and every 128-row query
@@ -12,6 +13,10 @@
 // the first pair and MN-major B of the second pair.  dQ partials leave through a per-warp TMA reduce-add into
 // an fp32 accumulator.  A small pre-pass computes delta = rowsum(dO * O) and clears the dQ accumulator; a
 // post-pass converts dQ to bf16.
+// head_dim 128 does not fit five 128-column accumulators into the 512 columns of tensor memory, so it walks the
+// queries in blocks of 64 (S^T, dP^T: N = 64) and produces dQ transposed, dQ_i^T = K_j^T dS^T (M = dh, N = 64
+// queries: the same two shared-memory tiles with the operand roles swapped); the drain transposes it back through
+// the staging slab of the TMA reduce-add.
 // Roles: warps 0-3 softmax/epilogue, warp 4 TMA producer, warp 5 MMA issuer.  All mbarrier waits are bounded.
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
@@ -21,13 +26,14 @@
 namespace mt {
 namespace {
 
-constexpr int BQ = 128;   // query rows per step
 constexpr int BKV = 128;  // keys per CTA
-constexpr int DH = 64;
 constexpr int kThreads = 192;
 constexpr float kLog2e = 1.4426950408889634f;
 
+template <int DH>
 struct BwdCfg {
+  static constexpr int BQ = DH == 64 ? 128 : 64;    // query rows per step
+  static constexpr bool DQ_T = DH != 64;            // dQ accumulated transposed (dh on TMEM lanes)
   static constexpr int K_BYTES = BKV * DH * 2;      // 16 KB
   static constexpr int V_BYTES = BKV * DH * 2;
   static constexpr int Q_BYTES = BQ * DH * 2;       // per stage
@@ -46,7 +52,9 @@ struct BwdCfg {
   static constexpr int OFF_BAR = OFF_STAT + STAT_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384;
+  static constexpr int COL_ST = 0, COL_DPT = BQ, COL_DV = 2 * BQ, COL_DK = 2 * BQ + DH, COL_DQ = 2 * BQ + 2 * DH;
+  static_assert(COL_DQ + (DQ_T ? BQ : DH) <= TMEM_COLS, "tensor memory budget");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
 struct BwdArgs {
@@ -57,13 +65,14 @@ struct BwdArgs {
   int* status;
 };
 
-template <bool CAP>
+template <int DH, bool CAP>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
                  const __grid_constant__ CUtensorMap tmDV, BwdArgs args) {
-  using C = BwdCfg;
+  using C = BwdCfg<DH>;
+  constexpr int BQ = C::BQ;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* k_s = smem + C::OFF_K;
   uint8_t* v_s = smem + C::OFF_V;
@@ -90,7 +99,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int nQ = args.S / BQ;
   const int key0 = j * BKV;
   const int tok0 = b * args.S;
-  const int i_begin = args.causal ? j : 0;
+  const int i_begin = args.causal ? key0 / BQ : 0;
   int i_end = nQ;
   if (args.window > 0) {
     const int last_q = key0 + BKV - 1 + args.window - 1;  // largest query index that still sees this block
@@ -128,8 +137,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(kv_full, C::K_BYTES + C::V_BYTES);
-      tma_load_3d(k_s, &tmK, kv_full, 0, hk, tok0 + key0);
-      tma_load_3d(v_s, &tmV, kv_full, 0, hk, tok0 + key0);
+#pragma unroll
+      for (int x = 0; x < DH / 64; ++x) {  // one 64-wide swizzle atom per load
+        tma_load_3d(k_s + x * (BKV * 128), &tmK, kv_full, x * 64, hk, tok0 + key0);
+        tma_load_3d(v_s + x * (BKV * 128), &tmV, kv_full, x * 64, hk, tok0 + key0);
+      }
       for (int t = 0; t < n_steps; ++t) {
         const int s = t & 1;
         const uint32_t ph = (t >> 1) & 1;
@@ -138,8 +150,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int q0 = (i_begin + t % n_i) * BQ;
         uint8_t* q_dst = qdo_s + s * (C::Q_BYTES + C::DO_BYTES);
         mbar_expect_tx(&qdo_full[s], C::Q_BYTES + C::DO_BYTES);
-        tma_load_3d(q_dst, &tmQ, &qdo_full[s], 0, h, tok0 + q0);
-        tma_load_3d(q_dst + C::Q_BYTES, &tmDO, &qdo_full[s], 0, h, tok0 + q0);
+#pragma unroll
+        for (int x = 0; x < DH / 64; ++x) {
+          tma_load_3d(q_dst + x * (BQ * 128), &tmQ, &qdo_full[s], x * 64, h, tok0 + q0);
+          tma_load_3d(q_dst + C::Q_BYTES + x * (BQ * 128), &tmDO, &qdo_full[s], x * 64, h, tok0 + q0);
+        }
       }
     }
   } else if (warp == 5) {
@@ -147,7 +162,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BKV, BQ, false, false);     // S^T, dP^T
       constexpr uint32_t idesc_dkv = make_idesc_bf16(BKV, DH, false, true);    // dV, dK : B = dO / Q as [K=q, N=dh]
-      constexpr uint32_t idesc_dq = make_idesc_bf16(BQ, DH, true, true);       // dQ : A = dS^T read MN-major
+      constexpr uint32_t idesc_dq = C::DQ_T ? make_idesc_bf16(DH, BQ, true, true)   // dQ^T : A = K_j read MN-major
+                                            : make_idesc_bf16(BQ, DH, true, true);  // dQ : A = dS^T read MN-major
       const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
       const uint32_t pt_addr = smem_u32(pt_s), dst_addr = smem_u32(dst_s);
       bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, MT_ERR_TIMEOUT_FULL);
@@ -156,12 +172,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t do_addr = q_addr + C::Q_BYTES;
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k)
-          tc_mma_f16(tmem_base + C::COL_ST, make_smem_desc_sw128(k_addr + k * 32, 16, 1024),
-                     make_smem_desc_sw128(q_addr + k * 32, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+          tc_mma_f16(tmem_base + C::COL_ST,
+                     make_smem_desc_sw128(k_addr + (k >> 2) * (BKV * 128) + (k & 3) * 32, 16, 1024),
+                     make_smem_desc_sw128(q_addr + (k >> 2) * (BQ * 128) + (k & 3) * 32, 16, 1024), idesc_s,
+                     k != 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k)
-          tc_mma_f16(tmem_base + C::COL_DPT, make_smem_desc_sw128(v_addr + k * 32, 16, 1024),
-                     make_smem_desc_sw128(do_addr + k * 32, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+          tc_mma_f16(tmem_base + C::COL_DPT,
+                     make_smem_desc_sw128(v_addr + (k >> 2) * (BKV * 128) + (k & 3) * 32, 16, 1024),
+                     make_smem_desc_sw128(do_addr + (k >> 2) * (BQ * 128) + (k & 3) * 32, 16, 1024), idesc_s,
+                     k != 0 ? 1u : 0u);
         tc_commit(st_full);
       };
       if (ok && n_steps > 0) {
@@ -193,9 +213,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // dQ = dS K : A = dS^T tile read MN-major (M = queries contiguous in 64-wide atoms, K = key rows),
         //             B = K_j tile read MN-major (N = dh contiguous, K = key rows)
 #pragma unroll
-        for (int k = 0; k < BKV / 16; ++k)
-          tc_mma_f16(tmem_base + C::COL_DQ, make_smem_desc_sw128(dst_addr + k * (16 * 128), BKV * 128, 1024),
-                     make_smem_desc_sw128(k_addr + k * (16 * 128), BKV * 128, 1024), idesc_dq, k != 0 ? 1u : 0u);
+        for (int k = 0; k < BKV / 16; ++k) {
+          const uint64_t d_ds = make_smem_desc_sw128(dst_addr + k * (16 * 128), BKV * 128, 1024);
+          const uint64_t d_k = make_smem_desc_sw128(k_addr + k * (16 * 128), BKV * 128, 1024);
+          if (C::DQ_T) tc_mma_f16(tmem_base + C::COL_DQ, d_k, d_ds, idesc_dq, k != 0 ? 1u : 0u);
+          else tc_mma_f16(tmem_base + C::COL_DQ, d_ds, d_k, idesc_dq, k != 0 ? 1u : 0u);
+        }
         tc_commit(&qdo_empty[s]);
         tc_commit(mma2_done);
         if (t + 1 < n_steps) {
@@ -220,35 +243,51 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     bool ok = true;
 
     auto drain_dq = [&](int t_prev) {
-      // dQ partial of step t_prev: TMEM lanes = query rows; this warp owns rows warp*32 .. +31
       const int h = hk * G + t_prev / n_i;
       const int q0 = (i_begin + t_prev % n_i) * BQ;
       if (lane == 0) tma_wait_group_read<0>();
       __syncwarp();
+      if constexpr (!C::DQ_T) {
+        // dQ partial: TMEM lanes = query rows; this warp owns rows warp*32 .. +31, boxes of 32 dims
 #pragma unroll
-      for (int c = 0; c < DH / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_row + C::COL_DQ + c * 32, v);
-        tc_wait_ld();
-        uint8_t* srow = dq_stage + c * 4096 + lane * 128;
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_row + C::COL_DQ + c * 32, v);
+          tc_wait_ld();
+          uint8_t* srow = dq_stage + c * 4096 + lane * 128;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          uint4 w = make_uint4(__float_as_uint(__uint_as_float(v[4 * g]) * sc),
-                               __float_as_uint(__uint_as_float(v[4 * g + 1]) * sc),
-                               __float_as_uint(__uint_as_float(v[4 * g + 2]) * sc),
-                               __float_as_uint(__uint_as_float(v[4 * g + 3]) * sc));
-          *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = w;
+          for (int g = 0; g < 8; ++g) {
+            uint4 w = make_uint4(__float_as_uint(__uint_as_float(v[4 * g]) * sc),
+                                 __float_as_uint(__uint_as_float(v[4 * g + 1]) * sc),
+                                 __float_as_uint(__uint_as_float(v[4 * g + 2]) * sc),
+                                 __float_as_uint(__uint_as_float(v[4 * g + 3]) * sc));
+            *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = w;
+          }
+        }
+      } else {
+        // dQ^T partial: TMEM lanes = head dims (this warp owns dims warp*32 .. +31), columns = 64 queries.
+        // Each box of the reduce-add is [32 queries x 32 dims]: lane d writes element d of every query row.
+#pragma unroll
+        for (int c = 0; c < BQ / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_row + C::COL_DQ + c * 32, v);
+          tc_wait_ld();
+          uint8_t* box = dq_stage + c * 4096 + (lane & 3) * 4;
+#pragma unroll
+          for (int q = 0; q < 32; ++q)
+            *reinterpret_cast<float*>(box + q * 128 + (((lane >> 2) ^ (q & 7)) << 4)) = __uint_as_float(v[q]) * sc;
         }
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
 #pragma unroll
-        for (int c = 0; c < DH / 32; ++c) {
+        for (int c = 0; c < 2; ++c) {
+          const int x = C::DQ_T ? warp * 32 : c * 32;
+          const int tok = tok0 + q0 + (C::DQ_T ? c * 32 : warp * 32);
           asm volatile(
               "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
-              ::"l"(reinterpret_cast<uint64_t>(&tmDQ)), "r"(smem_u32(dq_stage + c * 4096)), "r"(c * 32), "r"(h),
-                "r"(tok0 + q0 + warp * 32)
+              ::"l"(reinterpret_cast<uint64_t>(&tmDQ)), "r"(smem_u32(dq_stage + c * 4096)), "r"(x), "r"(h), "r"(tok)
               : "memory");
         }
         tma_commit_group();
@@ -261,9 +300,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto load_stats = [&](int t, float4& l4, float4& d4) {
       const int h = hk * G + t / n_i;
       const int q0 = (i_begin + t % n_i) * BQ;
-      const int64_t sbase = (static_cast<int64_t>(b) * args.H + h) * args.S + q0 + lane * 4;
-      l4 = *reinterpret_cast<const float4*>(args.lse + sbase);
-      d4 = *reinterpret_cast<const float4*>(args.delta + sbase);
+      if (lane * 4 < BQ) {
+        const int64_t sbase = (static_cast<int64_t>(b) * args.H + h) * args.S + q0 + lane * 4;
+        l4 = *reinterpret_cast<const float4*>(args.lse + sbase);
+        d4 = *reinterpret_cast<const float4*>(args.delta + sbase);
+      }
     };
     float4 lse_n = make_float4(0.f, 0.f, 0.f, 0.f), delta_n = lse_n;
     if (n_steps > 0) load_stats(0, lse_n, delta_n);
@@ -335,9 +376,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int q0 = i * BQ;
       // publish this step's statistics to the warp's slab, then prefetch the next step's
       __syncwarp();
-      reinterpret_cast<float4*>(stat)[lane] =
-          make_float4(lse_n.x * kLog2e, lse_n.y * kLog2e, lse_n.z * kLog2e, lse_n.w * kLog2e);
-      reinterpret_cast<float4*>(stat + BQ)[lane] = delta_n;
+      if (lane * 4 < BQ) {
+        reinterpret_cast<float4*>(stat)[lane] =
+            make_float4(lse_n.x * kLog2e, lse_n.y * kLog2e, lse_n.z * kLog2e, lse_n.w * kLog2e);
+        reinterpret_cast<float4*>(stat + BQ)[lane] = delta_n;
+      }
       __syncwarp();
       if (t + 1 < n_steps) load_stats(t + 1, lse_n, delta_n);
       if (!mbar_wait_warp(st_full, t & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
@@ -368,41 +411,49 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (ok) {
       if (lane == 0) tma_wait_group_read<0>();
       __syncwarp();
-      // dV then dK: this warp's 32 key rows x 64 dims (bf16, one 128-byte row each) through its staging slab
+      // dV then dK: this warp's 32 key rows x DH dims (bf16) through its staging slab, one 64-dim box (32 rows of
+      // 128 bytes) at a time; the slab holds two boxes
+      int boxes = 0;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const int col = which == 0 ? C::COL_DV : C::COL_DK;
         const float osc = which == 0 ? 1.f : sc;
-        uint8_t* slab = dq_stage + which * 4096;
 #pragma unroll
-        for (int c = 0; c < DH / 32; ++c) {
-          uint32_t v[32];
-          if (n_steps > 0) {
-            tmem_ld_32x32b_x32(t_row + col + c * 32, v);
-            tc_wait_ld();
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = 0;
+        for (int half = 0; half < DH / 64; ++half, ++boxes) {
+          if (boxes >= 2) {  // slab full: wait until the earlier boxes have been read out
+            if (lane == 0) tma_wait_group_read<0>();
+            __syncwarp();
           }
-          uint8_t* srow = slab + lane * 128;
+          uint8_t* slab = dq_stage + (boxes & 1) * 4096;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(v[8 * g + 0]) * osc, __uint_as_float(v[8 * g + 1]) * osc);
-            w.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]) * osc, __uint_as_float(v[8 * g + 3]) * osc);
-            w.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]) * osc, __uint_as_float(v[8 * g + 5]) * osc);
-            w.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]) * osc, __uint_as_float(v[8 * g + 7]) * osc);
-            const int chunk = c * 4 + g;
-            *reinterpret_cast<uint4*>(srow + ((chunk ^ (lane & 7)) << 4)) = w;
+          for (int c = 0; c < 2; ++c) {
+            uint32_t v[32];
+            if (n_steps > 0) {
+              tmem_ld_32x32b_x32(t_row + col + half * 64 + c * 32, v);
+              tc_wait_ld();
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) v[e] = 0;
+            }
+            uint8_t* srow = slab + lane * 128;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(v[8 * g + 0]) * osc, __uint_as_float(v[8 * g + 1]) * osc);
+              w.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]) * osc, __uint_as_float(v[8 * g + 3]) * osc);
+              w.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]) * osc, __uint_as_float(v[8 * g + 5]) * osc);
+              w.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]) * osc, __uint_as_float(v[8 * g + 7]) * osc);
+              const int chunk = c * 4 + g;
+              *reinterpret_cast<uint4*>(srow + ((chunk ^ (lane & 7)) << 4)) = w;
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(which == 0 ? &tmDV : &tmDK, slab, half * 64, hk, tok0 + key0 + warp * 32);
+            tma_commit_group();
           }
         }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        tma_store_3d(&tmDV, dq_stage, 0, hk, tok0 + key0 + warp * 32);
-        tma_store_3d(&tmDK, dq_stage + 4096, 0, hk, tok0 + key0 + warp * 32);
-        tma_commit_group();
       }
     }
     if (lane == 0) tma_wait_group<0>();
@@ -422,16 +473,19 @@ union Pack8 {
   __nv_bfloat16 h[8];
 };
 
-// delta[b,h,s] = sum_d dO * O ; also clears the fp32 dQ accumulator.  One warp per (token, head) row of 64.
+// delta[b,h,s] = sum_d dO * O ; also clears the fp32 dQ accumulator.  DH/8 lanes per (token, head) row.
+template <int DH>
 __global__ void bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                    float* __restrict__ delta, float* __restrict__ dq_accum, int B, int S, int H,
                                    int64_t o_stride, int64_t do_stride) {
+  constexpr int LPR = DH / 8;          // lanes per row, 8 elements each
+  constexpr int RPW = 32 / LPR;        // rows per warp pass
   const int64_t rows = static_cast<int64_t>(B) * S * H;
   const int lane = threadIdx.x & 31;
-  const int sub = lane >> 3;        // 4 rows per warp pass, 8 lanes x 8 elements each
-  const int l8 = lane & 7;
-  for (int64_t row = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 4 + sub; row < rows;
-       row += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5) * 4) {
+  const int sub = lane / LPR;
+  const int l8 = lane % LPR;
+  for (int64_t row = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW + sub; row < rows;
+       row += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5) * RPW) {
     const int64_t tok = row / H;
     const int h = static_cast<int>(row % H);
     Pack8 a, g;
@@ -440,9 +494,8 @@ __global__ void bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const __
     float s = 0.f;
 #pragma unroll
     for (int e = 0; e < 8; ++e) s += __bfloat162float(a.h[e]) * __bfloat162float(g.h[e]);
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
+#pragma unroll
+    for (int m = 1; m < LPR; m <<= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
     if (l8 == 0) {
       const int bb = static_cast<int>(tok / S);
       const int ss = static_cast<int>(tok % S);
@@ -455,6 +508,7 @@ __global__ void bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const __
   }
 }
 
+template <int DH>
 __global__ void bwd_finish_kernel(const float* __restrict__ dq_accum, __nv_bfloat16* __restrict__ dq, int64_t tokens,
                                   int H, int64_t dq_stride) {
   const int64_t total = tokens * H * (DH / 8);
@@ -475,17 +529,14 @@ __global__ void bwd_finish_kernel(const float* __restrict__ dq_accum, __nv_bfloa
   }
 }
 
-}  // namespace
-
-// p.dq_accum: fp32 [B*S, H, 64] scratch; p.delta: fp32 [B,H,S] scratch; p.dq_out (bf16) row pitch = q_row_stride.
-void flash_attn_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
-  if (p.dh != DH) throw std::runtime_error("flash_attn_bwd: head_dim must be 64");
-  if (p.S % BQ != 0) throw std::runtime_error("flash_attn_bwd: sequence length must be a multiple of 128");
-  using C = BwdCfg;
+template <int DH>
+void launch_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
+  using C = BwdCfg<DH>;
+  constexpr int BQ = C::BQ;
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
   const uint64_t tokens = static_cast<uint64_t>(p.B) * p.S;
-  bwd_prepare_kernel<<<num_sms * 8, 256, 0, stream>>>(
+  bwd_prepare_kernel<DH><<<num_sms * 8, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(p.o), static_cast<const __nv_bfloat16*>(p.dout), p.delta,
       static_cast<float*>(p.dq_accum), p.B, p.S, p.H, p.o_row_stride, p.do_row_stride);
   CUtensorMap tQ = make_tmap_3d(p.q, bf, 2, tokens, p.H, DH, p.q_row_stride, DH, BQ, 1, 64, sw);
@@ -498,19 +549,31 @@ void flash_attn_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
   CUtensorMap tDV = make_tmap_3d(p.dv, bf, 2, tokens, p.Hkv, DH, p.dv_row_stride, DH, 32, 1, 64, sw);
   static bool configured = false;
   if (!configured) {
-    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<DH, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<DH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured = true;
   }
   BwdArgs a{p.S, p.H, p.Hkv, p.causal, p.window, p.scale, p.softcap, p.lse, p.delta, p.status};
   dim3 grid(p.S / BKV, p.Hkv, p.B);
-  if (p.softcap > 0.f) flash_bwd_kernel<true><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
-  else flash_bwd_kernel<false><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+  if (p.softcap > 0.f)
+    flash_bwd_kernel<DH, true><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+  else
+    flash_bwd_kernel<DH, false><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
   MT_CUDA_CHECK(cudaGetLastError());
-  bwd_finish_kernel<<<num_sms * 8, 256, 0, stream>>>(static_cast<const float*>(p.dq_accum),
-                                                     static_cast<__nv_bfloat16*>(p.dq_out),
-                                                     static_cast<int64_t>(tokens), p.H, p.dq_row_stride);
+  bwd_finish_kernel<DH><<<num_sms * 8, 256, 0, stream>>>(static_cast<const float*>(p.dq_accum),
+                                                         static_cast<__nv_bfloat16*>(p.dq_out),
+                                                         static_cast<int64_t>(tokens), p.H, p.dq_row_stride);
   MT_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace
+
+// p.dq_accum: fp32 [B*S, H, dh] scratch; p.delta: fp32 [B,H,S] scratch; p.dq_out (bf16) row pitch = q_row_stride.
+void flash_attn_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
+  if (p.S % 128 != 0) throw std::runtime_error("flash_attn_bwd: sequence length must be a multiple of 128");
+  if (p.dh == 64) launch_bwd<64>(p, num_sms, stream);
+  else if (p.dh == 128) launch_bwd<128>(p, num_sms, stream);
+  else throw std::runtime_error("flash_attn_bwd: head_dim must be 64 or 128");
 }
 
 }  // namespace mt

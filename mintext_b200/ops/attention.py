@@ -8,12 +8,12 @@ from ._ext import ext, status_word
 
 
 def flash_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
-    """The forward kernel covers head dims 64 and 128, the backward kernel 64; training therefore takes the
-    kernel path for bf16, head_dim 64 and sequence lengths that are multiples of 128, anything else the oracle."""
+    """Forward and backward kernels cover head dims 64 and 128: the kernel path takes bf16 tensors with those head
+    dims and sequence lengths that are multiples of 128, anything else goes to the oracle."""
     if not hasattr(ext(), "flash_fwd"):
         return False
     d = q.shape[-1]
-    return (q.dtype == torch.bfloat16 and d == 64 and k.shape[-1] == d and v.shape[-1] == d
+    return (q.dtype == torch.bfloat16 and d in (64, 128) and k.shape[-1] == d and v.shape[-1] == d
             and q.shape[1] % 128 == 0 and k.shape[1] == q.shape[1] and q.shape[2] % k.shape[2] == 0)
 
 

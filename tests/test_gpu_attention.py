@@ -61,6 +61,17 @@ def test_flash_bwd_multi_block_gqa():
     _run(2, 512, 4, 2, 64)
 
 
+def test_flash_bwd_dh128():
+    _run(1, 128, 1, 1, 128)
+    _run(2, 512, 4, 2, 128)
+
+
+def test_flash_bwd_dh128_window_and_softcap():
+    _run(1, 512, 2, 1, 128, window=200)
+    _run(1, 256, 2, 2, 128, softcap=30.0)
+    _run(1, 256, 2, 1, 128, causal=False)
+
+
 def test_flash_window_and_softcap():
     _run(1, 512, 2, 1, 64, window=200)
     _run(1, 256, 2, 2, 64, softcap=30.0)
