@@ -102,6 +102,24 @@ void tp_gemm_rs(const void* A, const void* B, const PeerPtrs& staging_slots, int
                 bool b_mn_major, int* status, int num_sms, cudaStream_t stream);
 void tp_reduce_slots(const void* staging, void* y, int slots, int64_t slot_elems, cudaStream_t stream);
 
+// ---- moe/route.cu
+void router_sigmoid_group(const void* logits, bool logits_bf16, const float* bias, float* scores, int64_t* topk_idx,
+                          float* topk_w, int N, int E, int top_k, int n_group, int topk_group, bool norm, float scaling,
+                          cudaStream_t stream);
+void router_softmax_topk(const void* logits, bool logits_bf16, float* probs, int64_t* topk_idx, float* topk_w, int N,
+                         int E, int top_k, bool norm, float scaling, cudaStream_t stream);
+void router_bwd(bool softmax, const float* scores, const int64_t* topk_idx, const float* dw, const float* dscores,
+                float* dlogits, int N, int E, int top_k, bool norm, float scaling, cudaStream_t stream);
+int moe_sort_chunks(int M);
+// experts: int64[M] expert of every flat (token, slot) entry; chunk_counts: int[moe_sort_chunks(M) * E] scratch;
+// sizes int64[E]; off_p int[E+1] (128-padded); pos int64[M]; src int[cap] (entry at each padded row, -1 = padding).
+void moe_sort(const int64_t* experts, int M, int E, int64_t cap, int* chunk_counts, int64_t* sizes, int* off_p,
+              int64_t* pos, int* src, cudaStream_t stream);
+void moe_gather_rows(const void* x, const int* src, const float* w, void* rows, int64_t cap, int K, int D,
+                     cudaStream_t stream);
+void moe_combine_rows(const void* y, const int64_t* pos, const float* w, void* out, const void* g, float* dw, int N,
+                      int K, int D, cudaStream_t stream);
+
 // ---- attention/flash_fwd.cu, flash_bwd.cu
 struct AttnParams {
   const void* q; const void* k; const void* v; void* o; float* lse;

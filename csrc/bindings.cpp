@@ -292,6 +292,90 @@ void ep_pull_rows(torch::Tensor& out, const torch::Tensor& src_rank, const torch
                    (int)out.size(1), cap_rows, cur_stream());
 }
 
+// -> (topk_idx int64 [N,K], topk_w fp32 [N,K], scores fp32 [N,E]); kind 0 = sigmoid / group-limited, 1 = softmax
+std::vector<torch::Tensor> moe_router(const torch::Tensor& logits, const c10::optional<torch::Tensor>& bias, int64_t kind,
+                                      int64_t top_k, int64_t n_group, int64_t topk_group, bool norm, double scaling) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous());
+  TORCH_CHECK(logits.scalar_type() == torch::kBFloat16 || logits.scalar_type() == torch::kFloat32);
+  const int64_t N = logits.size(0), E = logits.size(1);
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto f32 = logits.options().dtype(torch::kFloat32);
+  auto scores = torch::empty({N, E}, f32);
+  auto idx = torch::empty({N, top_k}, logits.options().dtype(torch::kInt64));
+  auto w = torch::empty({N, top_k}, f32);
+  const bool bf = logits.scalar_type() == torch::kBFloat16;
+  if (kind == 0) {
+    TORCH_CHECK(bias && bias->scalar_type() == torch::kFloat32 && bias->numel() == E);
+    mt::router_sigmoid_group(logits.data_ptr(), bf, bias->data_ptr<float>(), scores.data_ptr<float>(),
+                             idx.data_ptr<int64_t>(), w.data_ptr<float>(), (int)N, (int)E, (int)top_k, (int)n_group,
+                             (int)topk_group, norm, (float)scaling, cur_stream());
+  } else {
+    mt::router_softmax_topk(logits.data_ptr(), bf, scores.data_ptr<float>(), idx.data_ptr<int64_t>(), w.data_ptr<float>(),
+                            (int)N, (int)E, (int)top_k, norm, (float)scaling, cur_stream());
+  }
+  return {idx, w, scores};
+}
+
+torch::Tensor moe_router_bwd(const torch::Tensor& scores, const torch::Tensor& idx, const c10::optional<torch::Tensor>& dw,
+                             const c10::optional<torch::Tensor>& dscores, int64_t kind, bool norm, double scaling) {
+  const int64_t N = scores.size(0), E = scores.size(1), K = idx.size(1);
+  TORCH_CHECK(scores.is_contiguous() && idx.is_contiguous());
+  TORCH_CHECK(!dw || (dw->is_contiguous() && dw->scalar_type() == torch::kFloat32));
+  TORCH_CHECK(!dscores || (dscores->is_contiguous() && dscores->scalar_type() == torch::kFloat32));
+  c10::cuda::CUDAGuard guard(scores.device());
+  auto dlogits = torch::empty({N, E}, scores.options());
+  mt::router_bwd(kind == 1, scores.data_ptr<float>(), idx.data_ptr<int64_t>(), dw ? dw->data_ptr<float>() : nullptr,
+                 dscores ? dscores->data_ptr<float>() : nullptr, dlogits.data_ptr<float>(), (int)N, (int)E, (int)K, norm,
+                 (float)scaling, cur_stream());
+  return dlogits;
+}
+
+// -> (sizes int64 [E], off_p int32 [E+1], pos int64 [M], src int32 [cap])
+std::vector<torch::Tensor> moe_sort(const torch::Tensor& experts, int64_t E, int64_t cap) {
+  TORCH_CHECK(experts.is_cuda() && experts.is_contiguous() && experts.scalar_type() == torch::kInt64 && E <= 4096);
+  const int64_t M = experts.numel();
+  c10::cuda::CUDAGuard guard(experts.device());
+  auto i32 = experts.options().dtype(torch::kInt32);
+  auto chunk_counts = torch::empty({std::max<int64_t>(mt::moe_sort_chunks((int)M), 1) * E}, i32);
+  auto sizes = torch::empty({E}, experts.options());
+  auto off_p = torch::empty({E + 1}, i32);
+  auto pos = torch::empty({M}, experts.options());
+  auto src = torch::empty({cap}, i32);
+  mt::moe_sort(experts.data_ptr<int64_t>(), (int)M, (int)E, cap, chunk_counts.data_ptr<int>(), sizes.data_ptr<int64_t>(),
+               off_p.data_ptr<int>(), pos.data_ptr<int64_t>(), src.data_ptr<int>(), cur_stream());
+  return {sizes, off_p, pos, src};
+}
+
+torch::Tensor moe_gather_rows(const torch::Tensor& x, const torch::Tensor& src, const c10::optional<torch::Tensor>& w,
+                              int64_t K) {
+  TORCH_CHECK(x.is_contiguous() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.size(1) % 8 == 0);
+  TORCH_CHECK(src.scalar_type() == torch::kInt32 && src.is_contiguous());
+  TORCH_CHECK(!w || (w->scalar_type() == torch::kFloat32 && w->is_contiguous()));
+  c10::cuda::CUDAGuard guard(x.device());
+  auto rows = torch::empty({src.numel(), x.size(1)}, x.options());
+  mt::moe_gather_rows(x.data_ptr(), src.data_ptr<int>(), w ? w->data_ptr<float>() : nullptr, rows.data_ptr(), src.numel(),
+                      (int)K, (int)x.size(1), cur_stream());
+  return rows;
+}
+
+// -> (out [N, D] bf16 or undefined, dw [N, K] fp32 or undefined)
+std::vector<torch::Tensor> moe_combine_rows(const torch::Tensor& y, const torch::Tensor& pos,
+                                            const c10::optional<torch::Tensor>& w, int64_t N, int64_t K, bool want_out,
+                                            const c10::optional<torch::Tensor>& g) {
+  TORCH_CHECK(y.is_contiguous() && y.scalar_type() == torch::kBFloat16 && y.size(1) % 8 == 0);
+  TORCH_CHECK(pos.scalar_type() == torch::kInt64 && pos.is_contiguous() && pos.numel() == N * K);
+  TORCH_CHECK(!w || (w->scalar_type() == torch::kFloat32 && w->is_contiguous() && w->numel() == N * K));
+  TORCH_CHECK(!g || (g->scalar_type() == torch::kBFloat16 && g->is_contiguous() && g->size(0) == N && g->size(1) == y.size(1)));
+  c10::cuda::CUDAGuard guard(y.device());
+  torch::Tensor out, dw;
+  if (want_out) out = torch::empty({N, y.size(1)}, y.options());
+  if (g) dw = torch::empty({N, K}, y.options().dtype(torch::kFloat32));
+  mt::moe_combine_rows(y.data_ptr(), pos.data_ptr<int64_t>(), w ? w->data_ptr<float>() : nullptr,
+                       want_out ? out.data_ptr() : nullptr, g ? g->data_ptr() : nullptr,
+                       g ? dw.data_ptr<float>() : nullptr, (int)N, (int)K, (int)y.size(1), cur_stream());
+  return {out, dw};
+}
+
 // out[T, N] = gather(shards)[T, K] @ (b_kn ? B[K, N] : B[N, K]^T); fills `gathered` on the way.
 void tp_gemm_ag(const std::vector<int64_t>& shard_ptrs, torch::Tensor& gathered, const torch::Tensor& B, torch::Tensor& out,
                 bool b_kn, int64_t rank, torch::Tensor& ready, torch::Tensor& status) {
@@ -350,6 +434,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_wgrad", &grouped_wgrad);
   m.def("ep_push_rows", &ep_push_rows);
   m.def("ep_pull_rows", &ep_pull_rows);
+  m.def("moe_router", &moe_router);
+  m.def("moe_router_bwd", &moe_router_bwd);
+  m.def("moe_sort", &moe_sort);
+  m.def("moe_gather_rows", &moe_gather_rows);
+  m.def("moe_combine_rows", &moe_combine_rows);
   m.def("tp_gemm_ag", &tp_gemm_ag);
   m.def("tp_gemm_rs", &tp_gemm_rs);
   m.def("tp_reduce_slots", &tp_reduce_slots);

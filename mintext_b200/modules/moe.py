@@ -37,13 +37,17 @@ class MoERouter(nn.Module):
 
     def forward(self, x: torch.Tensor):
         """x ``[N, D]`` -> (topk_indices ``[N,K]``, topk_weights ``[N,K]`` fp32, scores ``[N,E]`` fp32)."""
+        from mintext_b200.ops import moe as moe_ops
+
         logits = self.gate(x)
+        impl = moe_ops if moe_ops.router_cuda_path(logits, self.num_experts, self.num_experts_per_tok,
+                                                   self.n_group) else oracle
         if self.router_type == "softmax_topk":
-            idx, w, probs, aux = oracle.router_softmax_topk(logits, self.num_experts_per_tok, self.norm_topk_prob)
+            idx, w, probs, aux = impl.router_softmax_topk(logits, self.num_experts_per_tok, self.norm_topk_prob)
             self.last_aux_loss = aux
             return idx, w, probs
         self.last_aux_loss = None
-        return oracle.router_sigmoid_group(
+        return impl.router_sigmoid_group(
             logits, self.e_score_correction_bias, self.num_experts_per_tok, self.n_group, self.topk_group,
             self.norm_topk_prob, self.routed_scaling_factor)
 

@@ -117,24 +117,114 @@ def unroute_cuda(sorted_out, sort_idx, topk_w, K):
     return oracle.unroute(sorted_out, sort_idx, topk_w, K)
 
 
+class _RouterFn(torch.autograd.Function):
+    """Router kernels (``csrc/moe/route.cu``): ``kind`` 0 = sigmoid scores with group-limited top-k and selection
+    bias (mintext/modules/moe.py:52-103), 1 = softmax top-k.  Returns ``(indices, weights fp32, scores fp32)``."""
+
+    @staticmethod
+    def forward(ctx, logits, bias, kind, top_k, n_group, topk_group, norm, scaling):
+        idx, w, scores = ext().moe_router(logits, bias, kind, top_k, n_group, topk_group, norm, scaling)
+        ctx.save_for_backward(scores, idx)
+        ctx.meta = (kind, norm, scaling, logits.dtype)
+        ctx.mark_non_differentiable(idx)
+        ctx.set_materialize_grads(False)
+        return idx, w, scores
+
+    @staticmethod
+    def backward(ctx, _didx, dw, dscores):
+        scores, idx = ctx.saved_tensors
+        kind, norm, scaling, dtype = ctx.meta
+        if dw is None and dscores is None:
+            return (None,) * 8
+        dw = None if dw is None else dw.float().contiguous()
+        dscores = None if dscores is None else dscores.float().contiguous()
+        dlogits = ext().moe_router_bwd(scores, idx, dw, dscores, kind, norm, scaling)
+        return dlogits.to(dtype), None, None, None, None, None, None, None
+
+
+def router_cuda_path(logits: torch.Tensor, num_experts: int, top_k: int, n_group: int) -> bool:
+    return (logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32) and F._backend() != "oracle"
+            and hasattr(ext(), "moe_router") and num_experts <= 512 and top_k <= 16 and n_group <= 32)
+
+
+def router_sigmoid_group(logits, bias, top_k, n_group, topk_group, norm_topk_prob, scaling):
+    return _RouterFn.apply(logits.contiguous(), bias.float(), 0, int(top_k), int(n_group), int(topk_group),
+                           bool(norm_topk_prob), float(scaling))
+
+
+def router_softmax_topk(logits, top_k, norm_topk_prob, scaling: float = 1.0):
+    """``(indices, weights, probs, aux)``; the Switch-style auxiliary loss ``E * sum_e f_e P_e`` is formed from the
+    kernel's outputs (a histogram and a column mean)."""
+    idx, w, probs = _RouterFn.apply(logits.contiguous(), None, 1, int(top_k), 0, 0, bool(norm_topk_prob), float(scaling))
+    N, E = probs.shape
+    f = torch.bincount(idx.reshape(-1), minlength=E).float() / (N * top_k)
+    aux = E * (f * probs.mean(0)).sum()
+    return idx, w, probs, aux
+
+
+class _DispatchFn(torch.autograd.Function):
+    """Token rows into the padded expert-contiguous layout; backward sums the K row gradients of a token."""
+
+    @staticmethod
+    def forward(ctx, x, src, pos, K):
+        ctx.save_for_backward(pos)
+        ctx.meta = (x.shape[0], K)
+        return ext().moe_gather_rows(x, src, None, K)
+
+    @staticmethod
+    def backward(ctx, drows):
+        (pos,) = ctx.saved_tensors
+        N, K = ctx.meta
+        dx, _ = ext().moe_combine_rows(drows.contiguous(), pos, None, N, K, True, None)
+        return dx, None, None, None
+
+
+class _CombineFn(torch.autograd.Function):
+    """``out[n] = sum_k w[n,k] * y[pos[n,k]]``; backward scatters ``w * dout`` back to the padded rows and forms
+    ``dw[n,k] = <y[pos[n,k]], dout[n]>``."""
+
+    @staticmethod
+    def forward(ctx, y, w, pos, src, K):
+        N = w.shape[0]
+        w32 = w.float().contiguous()
+        ctx.save_for_backward(y, w32, pos, src)
+        ctx.meta = (N, K, w.dtype)
+        out, _ = ext().moe_combine_rows(y, pos, w32, N, K, True, None)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        y, w32, pos, src = ctx.saved_tensors
+        N, K, wdt = ctx.meta
+        dout = dout.contiguous()
+        dy = dw = None
+        if ctx.needs_input_grad[0]:
+            dy = ext().moe_gather_rows(dout, src, w32.reshape(-1), K)
+        if ctx.needs_input_grad[1]:
+            _, dw = ext().moe_combine_rows(y, pos, None, N, K, False, dout)
+            dw = dw.to(wdt)
+        return dy, dw, None, None, None
+
+
+def sort_by_expert(topk_idx: torch.Tensor, num_experts: int):
+    """Stable counting sort of the ``N*K`` (token, slot) entries by expert, on the device.  Returns
+    ``(sizes int64 [E], padded offsets int32 [E+1], pos int64 [N*K], src int32 [capacity])`` where ``pos`` is the
+    padded row of every entry and ``src`` the entry held by every padded row (-1 for padding)."""
+    flat = topk_idx.reshape(-1).contiguous()
+    cap = capacity(flat.numel(), num_experts)
+    return ext().moe_sort(flat, num_experts, cap)
+
+
 def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, gate_up: torch.Tensor,
                     down: torch.Tensor, act: str) -> torch.Tensor:
-    """Routed-expert MLP for ``x [N, D]``: dispatch into the padded layout, two grouped GEMMs around the gated
-    activation, weighted combine back to token order.  Differentiable end to end."""
+    """Routed-expert MLP for ``x [N, D]``: counting-sort dispatch into the padded layout, two grouped GEMMs around
+    the gated activation, weighted combine back to token order.  Differentiable end to end; every step is a kernel
+    of this package."""
     N, K = topk_idx.shape
     E = gate_up.shape[0]
-    flat = topk_idx.reshape(-1)
-    sort_idx = torch.argsort(flat, stable=True)             # (token, slot) order kept inside an expert
-    sizes = torch.bincount(flat, minlength=E)
-    off_p, off_u = padded_offsets(sizes)
-    dest = row_destinations(flat[sort_idx], off_p, off_u)   # padded position of every sorted row
-    pos = torch.empty_like(dest)
-    pos[sort_idx] = dest                                     # padded position of flat entry n*K + k
-    cap = capacity(N * K, E)
-    src_token = torch.div(sort_idx, K, rounding_mode="floor")
-    rows = torch.zeros(cap, x.shape[1], device=x.device, dtype=x.dtype).index_copy(0, dest, x.index_select(0, src_token))
+    sizes, off_p, pos, src = sort_by_expert(topk_idx, E)
+    rows = _DispatchFn.apply(x.contiguous(), src, pos, K)
     h = grouped_padded(rows, gate_up, off_p)
     h = F.gated_act(h, act)
     y = grouped_padded(h, down, off_p)
-    picked = y.index_select(0, pos).view(N, K, -1)
-    return torch.einsum("nkd,nk->nd", picked, topk_w.to(picked.dtype))
+    return _CombineFn.apply(y, topk_w, pos, src, K)

@@ -87,3 +87,100 @@ def test_moe_model_trains_with_engine():
     eng.check()
     assert out["moe_expert_counts"].shape == (1, 8)
     assert losses[-1] < losses[1] - 0.3, losses
+
+
+@pytest.mark.parametrize("E,K,n_group,topk_group,norm", [(64, 6, 8, 3, True), (256, 8, 8, 4, True), (8, 2, 1, 1, False),
+                                                         (128, 8, 4, 2, False)])
+def test_router_sigmoid_group_kernel_matches_oracle(E, K, n_group, topk_group, norm):
+    from mintext_b200.ops import moe as moe_ops
+    from mintext_b200.ops import oracle
+
+    torch.manual_seed(1)
+    N = 777
+    logits = (torch.randn(N, E, device="cuda") * 2).requires_grad_(True)
+    bias = torch.randn(E, device="cuda") * 0.1
+    idx, w, scores = moe_ops.router_sigmoid_group(logits, bias, K, n_group, topk_group, norm, 2.5)
+    lr = logits.detach().clone().requires_grad_(True)
+    idx_r, w_r, scores_r = oracle.router_sigmoid_group(lr, bias, K, n_group, topk_group, norm, 2.5)
+    _check()
+    assert (idx == idx_r).float().mean().item() > 0.999  # fast-math sigmoid may flip a near tie
+    same = (idx == idx_r).all(dim=1)
+    assert torch.allclose(w[same], w_r[same], atol=1e-5, rtol=1e-4)
+    assert torch.allclose(scores, scores_r, atol=1e-6, rtol=1e-5)
+    gw, gs = torch.randn_like(w), torch.randn_like(scores) * 0.1
+    (w * gw).sum().add((scores * gs).sum()).backward()
+    ((w_r * gw).sum() + (scores_r * gs).sum()).backward()
+    _check()
+    assert torch.allclose(logits.grad[same], lr.grad[same], atol=1e-5, rtol=1e-3)
+
+
+def test_router_softmax_kernel_matches_oracle():
+    from mintext_b200.ops import moe as moe_ops
+    from mintext_b200.ops import oracle
+
+    torch.manual_seed(2)
+    N, E, K = 500, 128, 8
+    logits = torch.randn(N, E, device="cuda").bfloat16().requires_grad_(True)
+    idx, w, probs, aux = moe_ops.router_softmax_topk(logits, K, True)
+    lr = logits.detach().clone().requires_grad_(True)
+    idx_r, w_r, probs_r, aux_r = oracle.router_softmax_topk(lr, K, True)
+    _check()
+    same = (idx == idx_r).all(dim=1)
+    assert same.float().mean().item() > 0.99
+    assert torch.allclose(w[same], w_r[same], atol=1e-5, rtol=1e-4)
+    assert torch.allclose(probs, probs_r, atol=1e-6, rtol=1e-4)
+    assert abs(float(aux) - float(aux_r)) < 1e-4
+    gw = torch.randn_like(w)
+    ((w * gw).sum() + aux * 3.0).backward()
+    ((w_r * gw).sum() + aux_r * 3.0).backward()
+    _check()
+    assert _rel(logits.grad[same], lr.grad[same]) < 2e-2  # bf16 gradients
+
+
+@pytest.mark.parametrize("N,K,E", [(1000, 2, 8), (4096, 8, 128), (3, 1, 4), (5000, 4, 640)])
+def test_counting_sort_dispatch_matches_stable_argsort(N, K, E):
+    from mintext_b200.ops import moe as moe_ops
+
+    torch.manual_seed(3)
+    idx = torch.randint(0, E, (N, K), device="cuda")
+    if E > 4:
+        idx[idx == 1] = 2  # an empty expert
+    sizes, off_p, pos, src = moe_ops.sort_by_expert(idx, E)
+    _check()
+    flat = idx.reshape(-1)
+    assert torch.equal(sizes, torch.bincount(flat, minlength=E))
+    ref_off_p, ref_off_u = moe_ops.padded_offsets(sizes)
+    assert torch.equal(off_p, ref_off_p)
+    order = torch.argsort(flat, stable=True)
+    dest = moe_ops.row_destinations(flat[order], ref_off_p, ref_off_u)
+    ref_pos = torch.empty_like(dest)
+    ref_pos[order] = dest
+    assert torch.equal(pos, ref_pos)
+    live = src >= 0
+    assert int(live.sum()) == N * K
+    assert torch.equal(pos[src[live].long()], torch.nonzero(live).squeeze(1))
+
+
+def test_dispatch_combine_kernels_and_grads():
+    from mintext_b200.ops import moe as moe_ops
+
+    torch.manual_seed(4)
+    N, K, E, D = 512, 4, 16, 256
+    idx = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(N)])
+    x = torch.randn(N, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.rand(N, K, device="cuda", requires_grad=True)
+    sizes, off_p, pos, src = moe_ops.sort_by_expert(idx, E)
+    rows = moe_ops._DispatchFn.apply(x, src, pos, K)
+    out = moe_ops._CombineFn.apply(rows * 1.0, w, pos, src, K)  # identity experts: out[n] = sum_k w[n,k] x[n]
+    _check()
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().clone().requires_grad_(True)
+    ref = xr * wr.sum(1, keepdim=True)
+    assert _rel(out, ref) < 1e-2
+    assert float(rows[src < 0].abs().max()) == 0.0
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref.backward(g.float())
+    _check()
+    assert _rel(x.grad, xr.grad) < 2e-2
+    assert _rel(w.grad, wr.grad) < 2e-2
