@@ -102,6 +102,11 @@ void tp_gemm_rs(const void* A, const void* B, const PeerPtrs& staging_slots, int
                 bool b_mn_major, int* status, int num_sms, cudaStream_t stream);
 void tp_reduce_slots(const void* staging, void* y, int slots, int64_t slot_elems, cudaStream_t stream);
 
+// ---- elementwise/conv1d.cu: depth-wise causal conv1d + SiLU (x, y, dy, dx: bf16 [B,S,C]; w: bf16 [C,K]; dw: fp32 [C,K], added to)
+void conv1d_silu_fwd(const void* x, const void* w, void* y, int B, int S, int C, int K, cudaStream_t stream);
+void conv1d_silu_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, int B, int S, int C, int K,
+                     cudaStream_t stream);
+
 // ---- moe/route.cu
 void router_sigmoid_group(const void* logits, bool logits_bf16, const float* bias, float* scores, int64_t* topk_idx,
                           float* topk_w, int N, int E, int top_k, int n_group, int topk_group, bool norm, float scaling,

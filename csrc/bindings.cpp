@@ -292,6 +292,27 @@ void ep_pull_rows(torch::Tensor& out, const torch::Tensor& src_rank, const torch
                    (int)out.size(1), cap_rows, cur_stream());
 }
 
+torch::Tensor conv1d_silu_fwd(const torch::Tensor& x, const torch::Tensor& w) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 3 && x.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(w.is_contiguous() && w.scalar_type() == torch::kBFloat16 && w.numel() % x.size(2) == 0);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = torch::empty_like(x);
+  mt::conv1d_silu_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), (int)x.size(0), (int)x.size(1), (int)x.size(2),
+                      (int)(w.numel() / x.size(2)), cur_stream());
+  return y;
+}
+
+// -> (dx bf16 [B,S,C], dw fp32 shaped like w)
+std::vector<torch::Tensor> conv1d_silu_bwd(const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& dy) {
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && w.is_contiguous() && dy.scalar_type() == torch::kBFloat16);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto dx = torch::empty_like(x);
+  auto dw = torch::zeros(w.sizes(), w.options().dtype(torch::kFloat32));
+  mt::conv1d_silu_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), dx.data_ptr(), dw.data_ptr<float>(), (int)x.size(0),
+                      (int)x.size(1), (int)x.size(2), (int)(w.numel() / x.size(2)), cur_stream());
+  return {dx, dw};
+}
+
 // -> (topk_idx int64 [N,K], topk_w fp32 [N,K], scores fp32 [N,E]); kind 0 = sigmoid / group-limited, 1 = softmax
 std::vector<torch::Tensor> moe_router(const torch::Tensor& logits, const c10::optional<torch::Tensor>& bias, int64_t kind,
                                       int64_t top_k, int64_t n_group, int64_t topk_group, bool norm, double scaling) {
@@ -434,6 +455,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_wgrad", &grouped_wgrad);
   m.def("ep_push_rows", &ep_push_rows);
   m.def("ep_pull_rows", &ep_pull_rows);
+  m.def("conv1d_silu_fwd", &conv1d_silu_fwd);
+  m.def("conv1d_silu_bwd", &conv1d_silu_bwd);
   m.def("moe_router", &moe_router);
   m.def("moe_router_bwd", &moe_router_bwd);
   m.def("moe_sort", &moe_sort);

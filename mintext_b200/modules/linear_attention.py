@@ -5,6 +5,7 @@ from __future__ import annotations
 import torch
 from torch import nn
 
+from mintext_b200.ops import functional as F
 from mintext_b200.ops import oracle
 
 from .linear import Linear
@@ -71,7 +72,8 @@ class GatedDeltaRuleAttention(nn.Module):
         key_total = self.num_k_heads * self.key_head_dim
         value_total = self.num_v_heads * self.value_head_dim
         qkv = torch.cat([q.reshape(B, S, key_total), k.reshape(B, S, key_total), v.reshape(B, S, value_total)], dim=-1)
-        qkv = torch.nn.functional.silu(oracle.causal_conv1d(qkv, self.conv_weight.to(self.dtype)))
+        qkv = F.causal_conv1d_silu(qkv, self.conv_weight if self.conv_weight.dtype == self.dtype
+                                   else self.conv_weight.to(self.dtype))
         qc, kc, vc = qkv.split([key_total, key_total, value_total], dim=-1)
         qh = qc.reshape(B, S, self.num_k_heads, self.key_head_dim)
         kh = kc.reshape(B, S, self.num_k_heads, self.key_head_dim)

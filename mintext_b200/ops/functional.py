@@ -131,6 +131,30 @@ def checkpoint_name(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
+# ------------------------------------------------------------------------------------------------ conv1d + SiLU
+class _Conv1dSiluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return ext().conv1d_silu_fwd(x, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dx, dw = ext().conv1d_silu_bwd(x, w, dy.contiguous())
+        return dx, dw.to(w.dtype)
+
+
+def causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``silu(depth-wise causal conv1d(x))``: x ``[B,S,C]``, weight ``[C,1,K]`` (mintext/modules/linear_attention.py:17-40
+    followed by the activation of :123-131)."""
+    C, K = weight.shape[0], weight.shape[-1]
+    if (use_cuda(x) and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and C % 8 == 0 and 2 <= K <= 4
+            and hasattr(ext(), "conv1d_silu_fwd")):
+        return _Conv1dSiluFn.apply(x.contiguous(), weight.contiguous())
+    return torch.nn.functional.silu(oracle.causal_conv1d(x, weight.to(x.dtype)))
+
+
 # ------------------------------------------------------------------------------------------------ linear
 def _gemm(a, b, c, a_km, b_kn, accumulate=False):
     ext().gemm(a, b, c, a_km, b_kn, accumulate, status_word(a.device))

@@ -124,6 +124,9 @@ class TrainEngine:
                 off_s = _round_up(off_s + p.numel(), _ALIGN)
         shard_quantum = self.world * 1024
         total_b = _round_up(max(off_b, 1), shard_quantum)
+        self.use_muon = cfg.optimizer == "muon"
+        if self.use_muon and self.world > 1 and big:
+            total_b = self._matrix_aligned_layout(big)
         self.big = FlatGroup(big, total_b)
         self.small = FlatGroup(small, _round_up(max(off_s, 1), _ALIGN))
         self.shard_size = total_b // self.world
@@ -177,6 +180,21 @@ class TrainEngine:
         for s in small:
             if not weight_decay_mask(s.name):
                 self.small_wd[s.offset:s.offset + s.numel] = 0.0
+
+    def _matrix_aligned_layout(self, big: list) -> int:
+        """Muon orthogonalises whole matrices, so under Muon no parameter may straddle two optimizer shards:
+        parameters are packed greedily (largest first) into one bin per rank, a bin being that rank's contiguous
+        shard of the flat buffers.  Returns the flat total (``world`` bins of the largest bin's size)."""
+        loads = [0] * self.world
+        placed: list[tuple[_Slot, int, int]] = []
+        for s in sorted(big, key=lambda t: -t.numel):
+            b = min(range(self.world), key=lambda i: loads[i])
+            placed.append((s, b, loads[b]))
+            loads[b] = _round_up(loads[b] + s.numel, _ALIGN)
+        bin_size = _round_up(max(loads), 1024)
+        for s, b, off in placed:
+            s.offset = b * bin_size + off
+        return bin_size * self.world
 
     def _alloc_symmetric(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         """Flat buffers live in symmetric (peer-mappable) memory when the peer-memory path may be used."""
@@ -272,19 +290,67 @@ class TrainEngine:
         # 3. fused AdamW on the shard (+ 4. publication of the bf16 copy)
         lo = self.rank * self.shard_size
         pshard = self.param_flat[lo:lo + self.shard_size]
-        if W > 1 and self.use_fused:
+        if self.use_muon:
+            self._muon_group(self.big.slots, lo, lo + self.shard_size, self.master, self.exp_avg, self.exp_avg_sq,
+                             gshard, pshard, lr, bc1, bc2, inv, t)
+            if W > 1:
+                dist.all_gather_into_tensor(self.param_flat, pshard, group=self.group)
+        elif W > 1 and self.use_fused:
             self._comm.adamw_and_publish(gshard, lr, bc1, bc2, inv, self._clip)
         else:
             e.adamw_step(self.master, self.exp_avg, self.exp_avg_sq, gshard, pshard, lr, cfg.adam_b1, cfg.adam_b2,
                          cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)
             if W > 1:
                 dist.all_gather_into_tensor(self.param_flat, pshard, group=self.group)
-        if self.exp.slots:
+        if self.exp.slots and self.use_muon:
+            self._muon_group(self.exp.slots, 0, self.exp.total, self.exp_master, self.exp_m, self.exp_v, self.exp_grad,
+                             self.exp_param, lr, bc1, bc2, inv, t)
+        elif self.exp.slots:
             e.adamw_step(self.exp_master, self.exp_m, self.exp_v, self.exp_grad, self.exp_param, lr, cfg.adam_b1,
                          cfg.adam_b2, cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)
         self._small_adamw(lr, bc1, bc2, inv)
         self.kernel_launches += 4
         return {"grad_norm": grad_norm, "learning_rate": lr}
+
+    def _muon_group(self, slots, lo, hi, master, mom, second, grad, param_out, lr, bc1, bc2, inv, t) -> None:
+        """Muon for the matrices, AdamW for everything else, over the slots held in ``[lo, hi)`` of a flat group
+        (mintext/optim/optimizer.py:117-168: Nesterov momentum with optax's bias correction, Newton-Schulz,
+        shape-dependent scale, decoupled weight decay)."""
+        import math
+
+        from mintext_b200.ops import muon as muon_ops
+        from mintext_b200.optim.optimizer import muon_matrix_view
+
+        cfg = self.config
+        e = ext()
+        beta = cfg.muon_beta
+        for s in slots:
+            if s.offset < lo or s.offset + s.numel > hi:
+                continue
+            a = s.offset - lo
+            view = muon_matrix_view(s.name, tuple(s.param.shape))
+            if view is None:
+                n = min(_round_up(s.numel, _ALIGN), hi - s.offset)  # the padding behind a slot has zero gradients
+                sl = slice(a, a + n)
+                e.adamw_step(master[sl], mom[sl], second[sl], grad[sl], param_out[sl], lr, cfg.adam_b1, cfg.adam_b2,
+                             cfg.adam_eps, cfg.weight_decay if weight_decay_mask(s.name) else 0.0, bc1, bc2, inv,
+                             self._clip)
+                continue
+            sl = slice(a, a + s.numel)
+            b, r, c = view
+            g = grad[sl] * (inv * self._clip)
+            mu = mom[sl]
+            mu.mul_(beta).add_(g, alpha=1 - beta)
+            mu_hat = mu * (beta / (1 - beta ** (t + 1))) + g * ((1 - beta) / (1 - beta ** t))
+            upd = muon_ops.newton_schulz(mu_hat.view(b, r, c), cfg.muon_newton_schulz_steps).reshape(-1)
+            if cfg.muon_consistent_rms is not None:
+                scale = math.sqrt(max(r, c)) * float(cfg.muon_consistent_rms)
+            else:
+                scale = math.sqrt(max(1.0, r / c))
+            wd = cfg.weight_decay if weight_decay_mask(s.name) else 0.0
+            w = master[sl]
+            w.add_(upd * scale + wd * w, alpha=-lr)
+            param_out[sl].copy_(w)
 
     def _small_adamw(self, lr, bc1, bc2, inv) -> None:
         cfg = self.config

@@ -86,3 +86,63 @@ def test_remat_policies_give_same_gradients(policy):
     for a, b in zip(grads["none"][1], grads[policy][1]):
         if a is not None:
             assert torch.allclose(a.float(), b.float(), rtol=2e-2, atol=2e-3)
+
+
+def test_newton_schulz_kernel_path_matches_fp32_oracle():
+    from mintext_b200.ops import muon as muon_ops
+    from mintext_b200.ops import oracle
+    from mintext_b200.ops._ext import check_status
+
+    torch.manual_seed(0)
+    for shape in [(1, 256, 512), (1, 512, 256), (2, 128, 128)]:
+        x = torch.randn(*shape, device="cuda")
+        got = muon_ops.newton_schulz(x, 5)
+        ref = oracle.newton_schulz(x, 5)
+        torch.cuda.synchronize()
+        check_status()
+        rel = ((got - ref).norm() / ref.norm()).item()
+        assert rel < 3e-2, (shape, rel)
+
+
+def test_engine_muon_follows_cpu_muon_trainer():
+    """The engine's Muon step (Newton-Schulz on the tcgen05 GEMM, bf16) tracks the fp32 reference optimizer."""
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.engine import TrainEngine
+
+    cfg = _cfg(optimizer="muon", learning_rate=2e-3)
+    tok = torch.randint(0, cfg.vocab_size, (4, cfg.seq_length), generator=torch.Generator().manual_seed(5))
+    batch = {"input_tokens": tok, "target_tokens": tok}
+    cpu_cfg = _cfg(optimizer="muon", learning_rate=2e-3, dtype="float32", weight_dtype="float32")
+    cpu_model = Transformer(cpu_cfg, rngs=0)
+    state = trainer.create_train_state(cpu_model, cpu_cfg)
+    ref = []
+    for _ in range(4):
+        state, metrics = trainer.train_step(state, batch, cpu_model, cpu_cfg)
+        ref.append(float(metrics["loss"]))
+    eng = TrainEngine(Transformer(cfg, rngs=0), cfg, device="cuda")
+    gb = {k: v.cuda() for k, v in batch.items()}
+    got = [float(eng.train_step(gb, num_micro=1)["loss"]) for _ in range(4)]
+    eng.check()
+    assert got[-1] < got[0], got
+    for a, b in zip(got, ref):
+        assert abs(a - b) < 0.1, (got, ref)
+
+
+def test_causal_conv1d_silu_kernel():
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops import oracle
+
+    torch.manual_seed(0)
+    for (B, S, C, K) in [(2, 100, 256, 4), (1, 33, 64, 3), (3, 64, 512, 2)]:
+        x = torch.randn(B, S, C, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        w = (torch.randn(C, 1, K, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+        y = F.causal_conv1d_silu(x, w)
+        xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+        ref = torch.nn.functional.silu(oracle.causal_conv1d(xr, wr))
+        assert ((y.float() - ref).norm() / ref.norm()).item() < 1e-2
+        g = torch.randn_like(y)
+        y.backward(g)
+        ref.backward(g.float())
+        assert ((x.grad.float() - xr.grad).norm() / xr.grad.norm()).item() < 2e-2
+        assert ((w.grad.float() - wr.grad).norm() / wr.grad.norm()).item() < 2e-2

@@ -14,14 +14,14 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
 
-def _single_gpu_losses():
+def _single_gpu_losses(optimizer="adamw"):
     from mintext_b200 import MinTextConfig
     from mintext_b200.models import Transformer
     from mintext_b200.parallel.engine import TrainEngine
 
     cfg = MinTextConfig(num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                         intermediate_size=512, vocab_size=1024, seq_length=128, steps=20, learning_rate=1e-3,
-                        enable_tensorboard=False, enable_checkpointing=False)
+                        enable_tensorboard=False, enable_checkpointing=False, optimizer=optimizer)
     eng = TrainEngine(Transformer(cfg, rngs=0), cfg, device="cuda")
     g = torch.Generator().manual_seed(7)
     tok = torch.randint(0, 1024, (8, 128), generator=g).cuda()
@@ -50,6 +50,8 @@ def test_multi_gpu_matches_single_gpu(world, tmp_path):
         assert abs(a - b) < 5e-3
     for a, b in zip(res["fused"]["grad_norms"], res["nccl"]["grad_norms"]):
         assert abs(a - b) < 1e-2 * max(1.0, abs(b))
+    for a, b in zip(res["muon"]["losses"], _single_gpu_losses("muon")):  # Muon with matrix-aligned shards
+        assert abs(a - b) < 3e-2, (res["muon"]["losses"],)
 
 
 def test_expert_parallel_matches_single_gpu(tmp_path):
