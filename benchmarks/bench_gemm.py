@@ -39,6 +39,7 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--tokens", type=int, default=32768)
     ap.add_argument("--only", default="", help="run only shapes whose name contains this string")
+    ap.add_argument("--fp8", action="store_true", help="time the FP8 GEMM instead (ratio is against cuBLAS bf16)")
     args = ap.parse_args()
     from mintext_b200.ops._ext import check_status, ext, status_word
 
@@ -70,6 +71,15 @@ def main():
             # wgrad    dW += x^T @ dy     : A = x stored [contraction=M, K] -> MN-major, B = dy stored [M, N]
             "wgrad": (lambda: e.gemm(x, dy, dw, True, True, True, st), lambda: torch.matmul(x.t(), dy, out=dw_b)),
         }
+        if args.fp8:  # FP8 GEMM alone (pre-quantised operands) and the whole fp8 linear (amax + quantise + GEMM)
+            xq, _, sx = e.fp8_quantize(x, False, True, False)
+            _, wqt, sw = e.fp8_quantize(w_kn, True, False, True)
+            cases = {
+                "fp8_gemm": (lambda: e.gemm_fp8(xq, wqt, False, True, sx, sw, st), lambda: torch.matmul(x, w_kn, out=y)),
+                "fp8_linear": (lambda: e.gemm_fp8(e.fp8_quantize(x, False, True, False)[0],
+                                                  e.fp8_quantize(w_kn, True, False, True)[1], False, True, sx, sw, st),
+                               lambda: torch.matmul(x, w_kn, out=y)),
+            }
         for kind, (mine, ref) in cases.items():
             t_mine = _time(mine, flush)
             t_ref = _time(ref, flush)

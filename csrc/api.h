@@ -102,6 +102,15 @@ void tp_gemm_rs(const void* A, const void* B, const PeerPtrs& staging_slots, int
                 bool b_mn_major, int* status, int num_sms, cudaStream_t stream);
 void tp_reduce_slots(const void* staging, void* y, int slots, int64_t slot_elems, cudaStream_t stream);
 
+// ---- gemm/fp8_gemm.cu: per-tensor-scaled FP8 GEMM (both operands K-major) and its quantisation kernels
+void fp8_amax(const void* x_bf16, int64_t n, float* amax, cudaStream_t stream);
+// scale[0] = (e5m2 ? 57344 : 448) / amax[0]; q [R,C] and / or qt [C,R] (either may be null) = fp8(x * scale)
+void fp8_quantize(const void* x_bf16, const float* amax, float* scale, void* q, void* qt, int R, int C, bool e5m2,
+                  cudaStream_t stream);
+// C[M,N] bf16 = A[M,K] * B[N,K]^T / (scale_a[0] * scale_b[0])
+void gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, bool a_e5m2, bool b_e5m2, const float* scale_a,
+              const float* scale_b, int* status, int num_sms, cudaStream_t stream);
+
 // ---- elementwise/conv1d.cu: depth-wise causal conv1d + SiLU (x, y, dy, dx: bf16 [B,S,C]; w: bf16 [C,K]; dw: fp32 [C,K], added to)
 void conv1d_silu_fwd(const void* x, const void* w, void* y, int B, int S, int C, int K, cudaStream_t stream);
 void conv1d_silu_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, int B, int S, int C, int K,

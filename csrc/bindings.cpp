@@ -292,6 +292,35 @@ void ep_pull_rows(torch::Tensor& out, const torch::Tensor& src_rank, const torch
                    (int)out.size(1), cap_rows, cur_stream());
 }
 
+// -> (q uint8 [R,C] or undefined, qt uint8 [C,R] or undefined, scale fp32 [1])
+std::vector<torch::Tensor> fp8_quantize(const torch::Tensor& x, bool e5m2, bool want_q, bool want_qt) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto f32 = x.options().dtype(torch::kFloat32);
+  auto u8 = x.options().dtype(torch::kUInt8);
+  auto amax = torch::empty({1}, f32);
+  auto scale = torch::empty({1}, f32);
+  torch::Tensor q, qt;
+  if (want_q) q = torch::empty({x.size(0), x.size(1)}, u8);
+  if (want_qt) qt = torch::empty({x.size(1), x.size(0)}, u8);
+  mt::fp8_amax(x.data_ptr(), x.numel(), amax.data_ptr<float>(), cur_stream());
+  mt::fp8_quantize(x.data_ptr(), amax.data_ptr<float>(), scale.data_ptr<float>(), want_q ? q.data_ptr() : nullptr,
+                   want_qt ? qt.data_ptr() : nullptr, (int)x.size(0), (int)x.size(1), e5m2, cur_stream());
+  return {q, qt, scale};
+}
+
+// out[M,N] bf16 = a[M,K] . b[N,K]^T / (scale_a * scale_b), 8-bit float operands
+torch::Tensor gemm_fp8(const torch::Tensor& a, const torch::Tensor& b, bool a_e5m2, bool b_e5m2, const torch::Tensor& scale_a,
+                       const torch::Tensor& scale_b, torch::Tensor& status) {
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && a.scalar_type() == torch::kUInt8 && b.scalar_type() == torch::kUInt8);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1) && a.size(1) % 16 == 0 && b.size(0) % 8 == 0);
+  c10::cuda::CUDAGuard guard(a.device());
+  auto out = torch::empty({a.size(0), b.size(0)}, a.options().dtype(torch::kBFloat16));
+  mt::gemm_fp8(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)a.size(0), (int)b.size(0), (int)a.size(1), a_e5m2, b_e5m2,
+               scale_a.data_ptr<float>(), scale_b.data_ptr<float>(), status.data_ptr<int>(), sm_count(), cur_stream());
+  return out;
+}
+
 torch::Tensor conv1d_silu_fwd(const torch::Tensor& x, const torch::Tensor& w) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 3 && x.scalar_type() == torch::kBFloat16);
   TORCH_CHECK(w.is_contiguous() && w.scalar_type() == torch::kBFloat16 && w.numel() % x.size(2) == 0);
@@ -455,6 +484,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_wgrad", &grouped_wgrad);
   m.def("ep_push_rows", &ep_push_rows);
   m.def("ep_pull_rows", &ep_pull_rows);
+  m.def("fp8_quantize", &fp8_quantize);
+  m.def("gemm_fp8", &gemm_fp8);
   m.def("conv1d_silu_fwd", &conv1d_silu_fwd);
   m.def("conv1d_silu_bwd", &conv1d_silu_bwd);
   m.def("moe_router", &moe_router);

@@ -71,7 +71,11 @@ class Linear(nn.Module):
         fan_in = math.prod(self.in_shape)
         x2 = x.reshape(*lead, fan_in)
         w2 = self.kernel.reshape(fan_in, -1) if self.kernel.dim() != 2 else self.kernel
-        if self.use_fp8 and self.kernel.dim() == 2:
+        if self.use_fp8 and self.kernel.dim() == 2 and F.fp8_kernel_path(x2, w2):
+            y = F.linear_fp8(x2, w2)
+            if self.bias is not None:
+                y = y + self.bias.to(y.dtype).reshape(-1)
+        elif self.use_fp8 and self.kernel.dim() == 2:
             y = fp8_matmul_reference(x2.reshape(-1, fan_in), w2, self.dtype).reshape(*lead, -1)
             if self.bias is not None:
                 y = y + self.bias.to(y.dtype).reshape(-1)

@@ -217,6 +217,55 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, n
     return y.reshape(*lead, w2.shape[1])
 
 
+class _LinearFp8Fn(torch.autograd.Function):
+    """``y = x @ W`` on the FP8 tensor-core path with per-tensor dynamic scales: activations e4m3 (448/amax), weights
+    e5m2 (57344/amax) as in mintext/modules/linear.py:37-57.  The data gradient also runs in FP8 (output gradient
+    quantised to e5m2); the weight gradient stays a bf16 GEMM accumulating in fp32."""
+
+    @staticmethod
+    def forward(ctx, x, w, main_grad):
+        e, st = ext(), status_word(x.device)
+        xq, _, sx = e.fp8_quantize(x, False, True, False)
+        wq, wqt, sw = e.fp8_quantize(w, True, True, True)   # [K,N] for the data gradient, [N,K] for the forward
+        ctx.save_for_backward(x, wq, sw)
+        ctx.main_grad, ctx.wmeta = main_grad, (w.shape, w.dtype, w.device)
+        return e.gemm_fp8(xq, wqt, False, True, sx, sw, st)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, wq, sw = ctx.saved_tensors
+        e, st = ext(), status_word(x.device)
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dyq, _, sdy = e.fp8_quantize(dy, True, True, False)
+            dx = e.gemm_fp8(dyq, wq, True, True, sdy, sw, st)   # dy [T,N] . W [K,N]^T
+        if ctx.needs_input_grad[1]:
+            shape, wdt, dev = ctx.wmeta
+            mg = ctx.main_grad
+            if mg is not None:
+                _gemm(x, dy, mg.view(shape), True, True, accumulate=True)
+            else:
+                dw = torch.empty(shape, device=dev, dtype=torch.float32)
+                dw = _gemm(x, dy, dw, True, True).to(wdt)
+        return dx, dw, None
+
+
+def fp8_kernel_path(x: torch.Tensor, w2: torch.Tensor) -> bool:
+    return (use_cuda(x) and x.dtype == torch.bfloat16 and w2.dtype == torch.bfloat16 and hasattr(ext(), "gemm_fp8")
+            and w2.shape[0] % 16 == 0 and w2.shape[1] % 16 == 0)
+
+
+def linear_fp8(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x[..., K] @ w[K, N]`` through the FP8 GEMM (callers check :func:`fp8_kernel_path`)."""
+    lead, K = x.shape[:-1], w.shape[0]
+    x2 = x.reshape(-1, K)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = _LinearFp8Fn.apply(x2, w, getattr(w, "main_grad", None))
+    return y.reshape(*lead, w.shape[1])
+
+
 class _LinearNTFn(torch.autograd.Function):
     """y[T,N] = x[T,K] @ W[N,K]^T (tied-embedding logits: the table is [vocab, hidden])."""
 

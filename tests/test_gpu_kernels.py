@@ -239,3 +239,33 @@ def test_adamw_and_sumsq():
     out = torch.zeros(1, device="cuda")
     e.sumsq(g, out)
     assert torch.allclose(out[0], (g * g).sum(), rtol=1e-3)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (384, 272, 1040), (128, 4096, 2048)])
+def test_fp8_gemm_matches_dequantised_reference(M, N, K):
+    """Per-tensor-scaled FP8 GEMM (e4m3 activations, e5m2 weights) against the fp32 product of the same quantised
+    values; forward and the FP8 data gradient."""
+    from mintext_b200.modules.linear import fp8_matmul_reference
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops._ext import check_status
+
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(K, N, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    y = F.linear_fp8(x, w)
+    ref = fp8_matmul_reference(x.detach(), w.detach(), torch.float32)
+    torch.cuda.synchronize()
+    check_status()
+    rel = ((y.float() - ref).norm() / ref.norm()).item()
+    assert rel < 1e-2, rel
+    full = x.detach().float() @ w.detach().float()
+    corr = torch.corrcoef(torch.stack([y.float().flatten(), full.flatten()]))[0, 1].item()
+    assert corr > 0.99, corr
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    check_status()
+    dx_ref = dy.float() @ w.detach().float().t()
+    dw_ref = x.detach().float().t() @ dy.float()
+    assert ((x.grad.float() - dx_ref).norm() / dx_ref.norm()).item() < 0.15   # two e5m2 operands
+    assert ((w.grad.float() - dw_ref).norm() / dw_ref.norm()).item() < 1e-2
