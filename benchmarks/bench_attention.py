@@ -1,7 +1,7 @@
 """Micro-benchmark of the flash-attention kernels (forward and backward), causal, bf16.
 
 Usage: python benchmarks/bench_attention.py [--B 8 --S 4096 --H 32 --Hkv 8 --d 64] [--iters 5] [--fwd-only]
-FLOPs counted: forward 4*B*S^2*H*d/2 (causal), backward 2.5x that.  CUDA events, 3 warm-up runs.
+FLOPs counted: forward 2*B*S^2*H*(d+dv)/2 (causal), backward 2.5x that.  CUDA events, 3 warm-up runs.
 """
 
 from __future__ import annotations
@@ -18,7 +18,7 @@ sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 def main():
     ap = argparse.ArgumentParser()
-    for k, v in (("B", 8), ("S", 4096), ("H", 32), ("Hkv", 8), ("d", 64), ("iters", 5)):
+    for k, v in (("B", 8), ("S", 4096), ("H", 32), ("Hkv", 8), ("d", 64), ("dv", 0), ("iters", 5)):
         ap.add_argument(f"--{k}", type=int, default=v)
     ap.add_argument("--fwd-only", action="store_true")
     a = ap.parse_args()
@@ -27,9 +27,10 @@ def main():
 
     q = torch.randn(a.B, a.S, a.H, a.d, device="cuda", dtype=torch.bfloat16, requires_grad=not a.fwd_only)
     k = torch.randn(a.B, a.S, a.Hkv, a.d, device="cuda", dtype=torch.bfloat16, requires_grad=not a.fwd_only)
-    v = torch.randn(a.B, a.S, a.Hkv, a.d, device="cuda", dtype=torch.bfloat16, requires_grad=not a.fwd_only)
-    do = torch.randn(a.B, a.S, a.H, a.d, device="cuda", dtype=torch.bfloat16)
-    flops_f = 4.0 * a.B * a.S * a.S * a.H * a.d / 2
+    dv = a.dv or a.d
+    v = torch.randn(a.B, a.S, a.Hkv, dv, device="cuda", dtype=torch.bfloat16, requires_grad=not a.fwd_only)
+    do = torch.randn(a.B, a.S, a.H, dv, device="cuda", dtype=torch.bfloat16)
+    flops_f = 2.0 * a.B * a.S * a.S * a.H * (a.d + dv) / 2
 
     def timeit(fn, n):
         for _ in range(3):
@@ -44,7 +45,7 @@ def main():
         return s.elapsed_time(e) / n
 
     t_f = timeit(lambda: flash_attention(q, k, v, a.d ** -0.5), a.iters)
-    out = {"B": a.B, "S": a.S, "H": a.H, "Hkv": a.Hkv, "d": a.d, "fwd_ms": round(t_f, 3),
+    out = {"B": a.B, "S": a.S, "H": a.H, "Hkv": a.Hkv, "d": a.d, "dv": dv, "fwd_ms": round(t_f, 3),
            "fwd_tflops": round(flops_f / t_f / 1e9, 1)}
     if not a.fwd_only:
         def fb():

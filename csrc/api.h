@@ -139,6 +139,7 @@ struct AttnParams {
   const void* q; const void* k; const void* v; void* o; float* lse;
   const void* dout; void* dq_accum; void* dq_out; void* dk; void* dv; float* delta;
   int B, S, H, Hkv, dh;
+  int dv_dim = 0;  // value / output head dim when it differs from the query / key head dim `dh` (0: same)
   // elements between consecutive tokens of each tensor (heads are packed: head h starts at h*dh)
   int64_t q_row_stride, k_row_stride, v_row_stride, o_row_stride;
   int64_t do_row_stride, dq_row_stride, dk_row_stride, dv_row_stride;

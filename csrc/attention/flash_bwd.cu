@@ -16,7 +16,9 @@
 // head_dim 128 does not fit five 128-column accumulators into the 512 columns of tensor memory, so it walks the
 // queries in blocks of 64 (S^T, dP^T: N = 64) and produces dQ transposed, dQ_i^T = K_j^T dS^T (M = dh, N = 64
 // queries: the same two shared-memory tiles with the operand roles swapped); the drain transposes it back through
-// the staging slab of the TMA reduce-add.
+// the staging slab of the TMA reduce-add.  The multi-head-latent shape (192-wide queries / keys, 128-wide values)
+// uses 32-query steps; its dQ^T needs 192 lanes, so it is produced as two M = 128 groups over head dims 0..127 and
+// 64..191 (the second one's upper 64 lanes are the new dims), each 64 columns wide (the upper 32 are never read).
 // Roles: warps 0-3 softmax/epilogue, warp 4 TMA producer, warp 5 MMA issuer.  All mbarrier waits are bounded.
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
@@ -30,16 +32,18 @@ constexpr int BKV = 128;  // keys per CTA
 constexpr int kThreads = 192;
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int DH>
+template <int DQK, int DV>
 struct BwdCfg {
-  static constexpr int BQ = DH == 64 ? 128 : 64;    // query rows per step
-  static constexpr bool DQ_T = DH != 64;            // dQ accumulated transposed (dh on TMEM lanes)
-  static constexpr int K_BYTES = BKV * DH * 2;      // 16 KB
-  static constexpr int V_BYTES = BKV * DH * 2;
-  static constexpr int Q_BYTES = BQ * DH * 2;       // per stage
-  static constexpr int DO_BYTES = BQ * DH * 2;
-  static constexpr int PT_BYTES = BKV * BQ * 2;     // 32 KB
-  static constexpr int DST_BYTES = BKV * BQ * 2;
+  static constexpr int BQ = DQK == 64 ? 128 : (DQK == 128 ? 64 : 32);  // query rows per step
+  static constexpr bool DQ_T = DQK != 64;           // dQ accumulated transposed (head dims on TMEM lanes)
+  static constexpr int DQ_GROUPS = DQK == 192 ? 2 : 1;
+  static constexpr int DQ_N = BQ < 64 ? 64 : BQ;    // columns per dQ^T group (one full 64-wide MN-major atom)
+  static constexpr int K_BYTES = BKV * DQK * 2;
+  static constexpr int V_BYTES = BKV * DV * 2;
+  static constexpr int Q_BYTES = BQ * DQK * 2;      // per stage
+  static constexpr int DO_BYTES = BQ * DV * 2;
+  static constexpr int PT_BYTES = BKV * DQ_N * 2;   // rows of P^T / dS^T are at least one 128-byte span
+  static constexpr int DST_BYTES = BKV * DQ_N * 2;
   static constexpr int DQ_STAGE_BYTES = 4 * 2 * 4096;  // per warp: 2 boxes of 32 rows x 128 B
   static constexpr int STAT_BYTES = 4 * 2 * BQ * 4;    // per softmax warp: lse[128] | delta[128]
   static constexpr int OFF_K = 0;
@@ -52,8 +56,9 @@ struct BwdCfg {
   static constexpr int OFF_BAR = OFF_STAT + STAT_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int COL_ST = 0, COL_DPT = BQ, COL_DV = 2 * BQ, COL_DK = 2 * BQ + DH, COL_DQ = 2 * BQ + 2 * DH;
-  static_assert(COL_DQ + (DQ_T ? BQ : DH) <= TMEM_COLS, "tensor memory budget");
+  static constexpr int COL_ST = 0, COL_DPT = BQ, COL_DV = 2 * BQ, COL_DK = 2 * BQ + DV, COL_DQ = 2 * BQ + DV + DQK;
+  static_assert(COL_DQ + (DQ_T ? DQ_GROUPS * DQ_N : DQK) <= TMEM_COLS, "tensor memory budget");
+  static_assert(DQ_GROUPS * (BQ / 32) <= 2 || !DQ_T, "the dQ staging slab holds two boxes per warp");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -65,13 +70,13 @@ struct BwdArgs {
   int* status;
 };
 
-template <int DH, bool CAP>
+template <int DQK, int DV, bool CAP>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
                  const __grid_constant__ CUtensorMap tmDV, BwdArgs args) {
-  using C = BwdCfg<DH>;
+  using C = BwdCfg<DQK, DV>;
   constexpr int BQ = C::BQ;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* k_s = smem + C::OFF_K;
@@ -138,10 +143,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0) {
       mbar_expect_tx(kv_full, C::K_BYTES + C::V_BYTES);
 #pragma unroll
-      for (int x = 0; x < DH / 64; ++x) {  // one 64-wide swizzle atom per load
+      for (int x = 0; x < DQK / 64; ++x)  // one 64-wide swizzle atom per load
         tma_load_3d(k_s + x * (BKV * 128), &tmK, kv_full, x * 64, hk, tok0 + key0);
-        tma_load_3d(v_s + x * (BKV * 128), &tmV, kv_full, x * 64, hk, tok0 + key0);
-      }
+#pragma unroll
+      for (int x = 0; x < DV / 64; ++x) tma_load_3d(v_s + x * (BKV * 128), &tmV, kv_full, x * 64, hk, tok0 + key0);
       for (int t = 0; t < n_steps; ++t) {
         const int s = t & 1;
         const uint32_t ph = (t >> 1) & 1;
@@ -151,19 +156,21 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint8_t* q_dst = qdo_s + s * (C::Q_BYTES + C::DO_BYTES);
         mbar_expect_tx(&qdo_full[s], C::Q_BYTES + C::DO_BYTES);
 #pragma unroll
-        for (int x = 0; x < DH / 64; ++x) {
+        for (int x = 0; x < DQK / 64; ++x)
           tma_load_3d(q_dst + x * (BQ * 128), &tmQ, &qdo_full[s], x * 64, h, tok0 + q0);
+#pragma unroll
+        for (int x = 0; x < DV / 64; ++x)
           tma_load_3d(q_dst + C::Q_BYTES + x * (BQ * 128), &tmDO, &qdo_full[s], x * 64, h, tok0 + q0);
-        }
       }
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BKV, BQ, false, false);     // S^T, dP^T
-      constexpr uint32_t idesc_dkv = make_idesc_bf16(BKV, DH, false, true);    // dV, dK : B = dO / Q as [K=q, N=dh]
-      constexpr uint32_t idesc_dq = C::DQ_T ? make_idesc_bf16(DH, BQ, true, true)   // dQ^T : A = K_j read MN-major
-                                            : make_idesc_bf16(BQ, DH, true, true);  // dQ : A = dS^T read MN-major
+      constexpr uint32_t idesc_dv = make_idesc_bf16(BKV, DV, false, true);     // dV : B = dO as [K=q, N=dv]
+      constexpr uint32_t idesc_dk = make_idesc_bf16(BKV, DQK, false, true);    // dK : B = Q as [K=q, N=dqk]
+      constexpr uint32_t idesc_dq = C::DQ_T ? make_idesc_bf16(128, C::DQ_N, true, true)  // dQ^T : A = K_j read MN-major
+                                            : make_idesc_bf16(BQ, DQK, true, true);      // dQ : A = dS^T read MN-major
       const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
       const uint32_t pt_addr = smem_u32(pt_s), dst_addr = smem_u32(dst_s);
       bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, MT_ERR_TIMEOUT_FULL);
@@ -171,13 +178,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t q_addr = smem_u32(qdo_s + (t & 1) * (C::Q_BYTES + C::DO_BYTES));
         const uint32_t do_addr = q_addr + C::Q_BYTES;
 #pragma unroll
-        for (int k = 0; k < DH / 16; ++k)
+        for (int k = 0; k < DQK / 16; ++k)
           tc_mma_f16(tmem_base + C::COL_ST,
                      make_smem_desc_sw128(k_addr + (k >> 2) * (BKV * 128) + (k & 3) * 32, 16, 1024),
                      make_smem_desc_sw128(q_addr + (k >> 2) * (BQ * 128) + (k & 3) * 32, 16, 1024), idesc_s,
                      k != 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < DH / 16; ++k)
+        for (int k = 0; k < DV / 16; ++k)
           tc_mma_f16(tmem_base + C::COL_DPT,
                      make_smem_desc_sw128(v_addr + (k >> 2) * (BKV * 128) + (k & 3) * 32, 16, 1024),
                      make_smem_desc_sw128(do_addr + (k >> 2) * (BQ * 128) + (k & 3) * 32, 16, 1024), idesc_s,
@@ -202,22 +209,29 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int k = 0; k < BQ / 16; ++k) {
           const uint32_t aoff = (k >> 2) * (BKV * 128) + (k & 3) * 32;
           tc_mma_f16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_addr + aoff, 16, 1024),
-                     make_smem_desc_sw128(do_addr + k * (16 * 128), BQ * 128, 1024), idesc_dkv, (t | k) != 0 ? 1u : 0u);
+                     make_smem_desc_sw128(do_addr + k * (16 * 128), BQ * 128, 1024), idesc_dv, (t | k) != 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < BQ / 16; ++k) {
           const uint32_t aoff = (k >> 2) * (BKV * 128) + (k & 3) * 32;
           tc_mma_f16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_addr + aoff, 16, 1024),
-                     make_smem_desc_sw128(q_addr + k * (16 * 128), BQ * 128, 1024), idesc_dkv, (t | k) != 0 ? 1u : 0u);
+                     make_smem_desc_sw128(q_addr + k * (16 * 128), BQ * 128, 1024), idesc_dk, (t | k) != 0 ? 1u : 0u);
         }
         // dQ = dS K : A = dS^T tile read MN-major (M = queries contiguous in 64-wide atoms, K = key rows),
         //             B = K_j tile read MN-major (N = dh contiguous, K = key rows)
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
           const uint64_t d_ds = make_smem_desc_sw128(dst_addr + k * (16 * 128), BKV * 128, 1024);
-          const uint64_t d_k = make_smem_desc_sw128(k_addr + k * (16 * 128), BKV * 128, 1024);
-          if (C::DQ_T) tc_mma_f16(tmem_base + C::COL_DQ, d_k, d_ds, idesc_dq, k != 0 ? 1u : 0u);
-          else tc_mma_f16(tmem_base + C::COL_DQ, d_ds, d_k, idesc_dq, k != 0 ? 1u : 0u);
+          if (C::DQ_T) {
+#pragma unroll
+            for (int g = 0; g < C::DQ_GROUPS; ++g)  // group g covers head dims 64g .. 64g+127
+              tc_mma_f16(tmem_base + C::COL_DQ + g * C::DQ_N,
+                         make_smem_desc_sw128(k_addr + g * (BKV * 128) + k * (16 * 128), BKV * 128, 1024), d_ds, idesc_dq,
+                         k != 0 ? 1u : 0u);
+          } else {
+            tc_mma_f16(tmem_base + C::COL_DQ, d_ds, make_smem_desc_sw128(k_addr + k * (16 * 128), BKV * 128, 1024),
+                       idesc_dq, k != 0 ? 1u : 0u);
+          }
         }
         tc_commit(&qdo_empty[s]);
         tc_commit(mma2_done);
@@ -250,7 +264,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if constexpr (!C::DQ_T) {
         // dQ partial: TMEM lanes = query rows; this warp owns rows warp*32 .. +31, boxes of 32 dims
 #pragma unroll
-        for (int c = 0; c < DH / 32; ++c) {
+        for (int c = 0; c < DQK / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32b_x32(t_row + C::COL_DQ + c * 32, v);
           tc_wait_ld();
@@ -264,33 +278,45 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = w;
           }
         }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+          for (int c = 0; c < DQK / 32; ++c)
+            tma_reduce_add_3d(&tmDQ, dq_stage + c * 4096, c * 32, h, tok0 + q0 + warp * 32);
+          tma_commit_group();
+        }
       } else {
-        // dQ^T partial: TMEM lanes = head dims (this warp owns dims warp*32 .. +31), columns = 64 queries.
+        // dQ^T partial: TMEM lanes = head dims (group g: dims 64g + warp*32 + lane), columns = queries.
         // Each box of the reduce-add is [32 queries x 32 dims]: lane d writes element d of every query row.
+        int box = 0;
 #pragma unroll
-        for (int c = 0; c < BQ / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(t_row + C::COL_DQ + c * 32, v);
-          tc_wait_ld();
-          uint8_t* box = dq_stage + c * 4096 + (lane & 3) * 4;
+        for (int g = 0; g < C::DQ_GROUPS; ++g) {
+          if (g > 0 && warp < 2) continue;  // lanes 0..63 of a later group repeat dims of the previous one
 #pragma unroll
-          for (int q = 0; q < 32; ++q)
-            *reinterpret_cast<float*>(box + q * 128 + (((lane >> 2) ^ (q & 7)) << 4)) = __uint_as_float(v[q]) * sc;
+          for (int c = 0; c < BQ / 32; ++c, ++box) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(t_row + C::COL_DQ + g * C::DQ_N + c * 32, v);
+            tc_wait_ld();
+            uint8_t* bx = dq_stage + box * 4096 + (lane & 3) * 4;
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              *reinterpret_cast<float*>(bx + q * 128 + (((lane >> 2) ^ (q & 7)) << 4)) = __uint_as_float(v[q]) * sc;
+          }
         }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          box = 0;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int x = C::DQ_T ? warp * 32 : c * 32;
-          const int tok = tok0 + q0 + (C::DQ_T ? c * 32 : warp * 32);
-          asm volatile(
-              "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
-              ::"l"(reinterpret_cast<uint64_t>(&tmDQ)), "r"(smem_u32(dq_stage + c * 4096)), "r"(x), "r"(h), "r"(tok)
-              : "memory");
+          for (int g = 0; g < C::DQ_GROUPS; ++g) {
+            if (g > 0 && warp < 2) continue;
+#pragma unroll
+            for (int c = 0; c < BQ / 32; ++c, ++box)
+              tma_reduce_add_3d(&tmDQ, dq_stage + box * 4096, 64 * g + warp * 32, h, tok0 + q0 + c * 32);
+          }
+          tma_commit_group();
         }
-        tma_commit_group();
       }
     };
 
@@ -419,7 +445,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int col = which == 0 ? C::COL_DV : C::COL_DK;
         const float osc = which == 0 ? 1.f : sc;
 #pragma unroll
-        for (int half = 0; half < DH / 64; ++half, ++boxes) {
+        for (int half = 0; half < (which == 0 ? DV : DQK) / 64; ++half, ++boxes) {
           if (boxes >= 2) {  // slab full: wait until the earlier boxes have been read out
             if (lane == 0) tma_wait_group_read<0>();
             __syncwarp();
@@ -473,13 +499,15 @@ union Pack8 {
   __nv_bfloat16 h[8];
 };
 
-// delta[b,h,s] = sum_d dO * O ; also clears the fp32 dQ accumulator.  DH/8 lanes per (token, head) row.
-template <int DH>
+// delta[b,h,s] = sum_d dO * O over the DV value dims; also clears the fp32 dQ accumulator row (DQK floats).
+// DV/8 lanes per (token, head) row.
+template <int DQK, int DV>
 __global__ void bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                    float* __restrict__ delta, float* __restrict__ dq_accum, int B, int S, int H,
                                    int64_t o_stride, int64_t do_stride) {
-  constexpr int LPR = DH / 8;          // lanes per row, 8 elements each
+  constexpr int LPR = DV / 8;          // lanes per row, 8 elements each
   constexpr int RPW = 32 / LPR;        // rows per warp pass
+  constexpr int ZPL = DQK / LPR;       // dQ floats cleared per lane (8 or 12)
   const int64_t rows = static_cast<int64_t>(B) * S * H;
   const int lane = threadIdx.x & 31;
   const int sub = lane / LPR;
@@ -489,8 +517,8 @@ __global__ void bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const __
     const int64_t tok = row / H;
     const int h = static_cast<int>(row % H);
     Pack8 a, g;
-    a.u = *reinterpret_cast<const uint4*>(o + tok * o_stride + h * DH + l8 * 8);
-    g.u = *reinterpret_cast<const uint4*>(dout + tok * do_stride + h * DH + l8 * 8);
+    a.u = *reinterpret_cast<const uint4*>(o + tok * o_stride + h * DV + l8 * 8);
+    g.u = *reinterpret_cast<const uint4*>(dout + tok * do_stride + h * DV + l8 * 8);
     float s = 0.f;
 #pragma unroll
     for (int e = 0; e < 8; ++e) s += __bfloat162float(a.h[e]) * __bfloat162float(g.h[e]);
@@ -502,9 +530,9 @@ __global__ void bwd_prepare_kernel(const __nv_bfloat16* __restrict__ o, const __
       delta[(static_cast<int64_t>(bb) * H + h) * S + ss] = s;
     }
     float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4* dq = reinterpret_cast<float4*>(dq_accum + row * DH + l8 * 8);
-    dq[0] = z;
-    dq[1] = z;
+    float4* dq = reinterpret_cast<float4*>(dq_accum + row * DQK + l8 * ZPL);
+#pragma unroll
+    for (int e = 0; e < ZPL / 4; ++e) dq[e] = z;
   }
 }
 
@@ -529,51 +557,53 @@ __global__ void bwd_finish_kernel(const float* __restrict__ dq_accum, __nv_bfloa
   }
 }
 
-template <int DH>
+template <int DQK, int DV>
 void launch_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
-  using C = BwdCfg<DH>;
+  using C = BwdCfg<DQK, DV>;
   constexpr int BQ = C::BQ;
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
   const uint64_t tokens = static_cast<uint64_t>(p.B) * p.S;
-  bwd_prepare_kernel<DH><<<num_sms * 8, 256, 0, stream>>>(
+  bwd_prepare_kernel<DQK, DV><<<num_sms * 8, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(p.o), static_cast<const __nv_bfloat16*>(p.dout), p.delta,
       static_cast<float*>(p.dq_accum), p.B, p.S, p.H, p.o_row_stride, p.do_row_stride);
-  CUtensorMap tQ = make_tmap_3d(p.q, bf, 2, tokens, p.H, DH, p.q_row_stride, DH, BQ, 1, 64, sw);
-  CUtensorMap tK = make_tmap_3d(p.k, bf, 2, tokens, p.Hkv, DH, p.k_row_stride, DH, BKV, 1, 64, sw);
-  CUtensorMap tV = make_tmap_3d(p.v, bf, 2, tokens, p.Hkv, DH, p.v_row_stride, DH, BKV, 1, 64, sw);
-  CUtensorMap tDO = make_tmap_3d(p.dout, bf, 2, tokens, p.H, DH, p.do_row_stride, DH, BQ, 1, 64, sw);
-  CUtensorMap tDQ = make_tmap_3d(p.dq_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, tokens, p.H, DH,
-                                 static_cast<uint64_t>(p.H) * DH, DH, 32, 1, 32, sw);
-  CUtensorMap tDK = make_tmap_3d(p.dk, bf, 2, tokens, p.Hkv, DH, p.dk_row_stride, DH, 32, 1, 64, sw);
-  CUtensorMap tDV = make_tmap_3d(p.dv, bf, 2, tokens, p.Hkv, DH, p.dv_row_stride, DH, 32, 1, 64, sw);
+  CUtensorMap tQ = make_tmap_3d(p.q, bf, 2, tokens, p.H, DQK, p.q_row_stride, DQK, BQ, 1, 64, sw);
+  CUtensorMap tK = make_tmap_3d(p.k, bf, 2, tokens, p.Hkv, DQK, p.k_row_stride, DQK, BKV, 1, 64, sw);
+  CUtensorMap tV = make_tmap_3d(p.v, bf, 2, tokens, p.Hkv, DV, p.v_row_stride, DV, BKV, 1, 64, sw);
+  CUtensorMap tDO = make_tmap_3d(p.dout, bf, 2, tokens, p.H, DV, p.do_row_stride, DV, BQ, 1, 64, sw);
+  CUtensorMap tDQ = make_tmap_3d(p.dq_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, tokens, p.H, DQK,
+                                 static_cast<uint64_t>(p.H) * DQK, DQK, 32, 1, 32, sw);
+  CUtensorMap tDK = make_tmap_3d(p.dk, bf, 2, tokens, p.Hkv, DQK, p.dk_row_stride, DQK, 32, 1, 64, sw);
+  CUtensorMap tDV = make_tmap_3d(p.dv, bf, 2, tokens, p.Hkv, DV, p.dv_row_stride, DV, 32, 1, 64, sw);
   static bool configured = false;
   if (!configured) {
-    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<DH, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<DH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<DQK, DV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<DQK, DV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured = true;
   }
   BwdArgs a{p.S, p.H, p.Hkv, p.causal, p.window, p.scale, p.softcap, p.lse, p.delta, p.status};
   dim3 grid(p.S / BKV, p.Hkv, p.B);
   if (p.softcap > 0.f)
-    flash_bwd_kernel<DH, true><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+    flash_bwd_kernel<DQK, DV, true><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
   else
-    flash_bwd_kernel<DH, false><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+    flash_bwd_kernel<DQK, DV, false><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
   MT_CUDA_CHECK(cudaGetLastError());
-  bwd_finish_kernel<DH><<<num_sms * 8, 256, 0, stream>>>(static_cast<const float*>(p.dq_accum),
-                                                         static_cast<__nv_bfloat16*>(p.dq_out),
-                                                         static_cast<int64_t>(tokens), p.H, p.dq_row_stride);
+  bwd_finish_kernel<DQK><<<num_sms * 8, 256, 0, stream>>>(static_cast<const float*>(p.dq_accum),
+                                                          static_cast<__nv_bfloat16*>(p.dq_out),
+                                                          static_cast<int64_t>(tokens), p.H, p.dq_row_stride);
   MT_CUDA_CHECK(cudaGetLastError());
 }
 
 }  // namespace
 
-// p.dq_accum: fp32 [B*S, H, dh] scratch; p.delta: fp32 [B,H,S] scratch; p.dq_out (bf16) row pitch = q_row_stride.
+// p.dq_accum: fp32 [B*S, H, dh] scratch; p.delta: fp32 [B,H,S] scratch; p.dq_out (bf16) row pitch = dq_row_stride.
 void flash_attn_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
   if (p.S % 128 != 0) throw std::runtime_error("flash_attn_bwd: sequence length must be a multiple of 128");
-  if (p.dh == 64) launch_bwd<64>(p, num_sms, stream);
-  else if (p.dh == 128) launch_bwd<128>(p, num_sms, stream);
-  else throw std::runtime_error("flash_attn_bwd: head_dim must be 64 or 128");
+  const int dv = p.dv_dim > 0 ? p.dv_dim : p.dh;
+  if (p.dh == 64 && dv == 64) launch_bwd<64, 64>(p, num_sms, stream);
+  else if (p.dh == 128 && dv == 128) launch_bwd<128, 128>(p, num_sms, stream);
+  else if (p.dh == 192 && dv == 128) launch_bwd<192, 128>(p, num_sms, stream);
+  else throw std::runtime_error("flash_attn_bwd: head dims must be 64, 128 or 192/128");
 }
 
 }  // namespace mt

@@ -1,4 +1,5 @@
-// Causal / sliding-window flash attention forward for sm_100a (bf16, head_dim 64 or 128, grouped-query K/V).
+// Causal / sliding-window flash attention forward for sm_100a (bf16, head_dim 64 or 128, grouped-query K/V; also
+// the multi-head-latent shape with 192-wide queries/keys and 128-wide values).
 //
 // One CTA = one (batch, head, 128-query-row block).  Roles:
 //   warps 0-3  softmax      : thread r owns query row r.  Reads S = Q K^T from tensor memory (tcgen05.ld), keeps the
@@ -23,20 +24,21 @@ constexpr int BLOCK_M = 128;
 constexpr int kThreads = 192;
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int DH>
+template <int DQK, int DV>
 struct FwdCfg {
-  static constexpr int BN = (DH == 64) ? 128 : 64;
-  static constexpr int Q_BYTES = BLOCK_M * DH * 2;
-  static constexpr int K_BYTES = BN * DH * 2;
-  static constexpr int V_BYTES = BN * DH * 2;
+  static constexpr int BN = (DQK == 64) ? 128 : 64;
+  static constexpr int Q_BYTES = BLOCK_M * DQK * 2;
+  static constexpr int K_BYTES = BN * DQK * 2;
+  static constexpr int V_BYTES = BN * DV * 2;
   static constexpr int P_BYTES = BLOCK_M * BN * 2;
-  static constexpr int O_STAGE_BYTES = BLOCK_M * DH * 2;  // reuses the P region (+ K stage 0 when larger)
+  static constexpr int O_STAGE_BYTES = BLOCK_M * DV * 2;  // reuses the P region, or the K/V ring when larger
   static constexpr int SMEM_DATA = Q_BYTES + 2 * (K_BYTES + V_BYTES) + P_BYTES;
   static constexpr int SMEM_BYTES = SMEM_DATA + 256;
   static constexpr int TMEM_COLS = 256;
   static constexpr int S_COL = 0;
   static constexpr int O_COL = BN;
-  static_assert(BN + DH <= TMEM_COLS, "accumulators must fit the allocation");
+  static_assert(BN + DV <= TMEM_COLS, "accumulators must fit the allocation");
+  static_assert(O_STAGE_BYTES <= P_BYTES || O_STAGE_BYTES <= 2 * (K_BYTES + V_BYTES), "output staging");
 };
 
 struct FwdArgs {
@@ -46,13 +48,14 @@ struct FwdArgs {
   int* status;
 };
 
-template <int DH, bool CAP>
+template <int DQK, int DV, bool CAP>
 __global__ void __launch_bounds__(kThreads, 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, FwdArgs args) {
-  using C = FwdCfg<DH>;
+  using C = FwdCfg<DQK, DV>;
   constexpr int BN = C::BN;
-  constexpr int D_ATOMS = DH / 64;   // 64-element (128 B) swizzle atoms along the head dim
+  constexpr int QK_ATOMS = DQK / 64;  // 64-element (128 B) swizzle atoms along the head dims
+  constexpr int V_ATOMS = DV / 64;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_s = smem;
   uint8_t* kv_s = q_s + C::Q_BYTES;  // stage s: K at kv_s + s*(K+V), V right after K
@@ -123,7 +126,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0) {
       mbar_expect_tx(q_full, C::Q_BYTES);
 #pragma unroll
-      for (int a = 0; a < D_ATOMS; ++a)
+      for (int a = 0; a < QK_ATOMS; ++a)
         tma_load_3d(q_s + a * (BLOCK_M * 128), &tmQ, q_full, a * 64, h, tok0 + q0);
       for (int i = 0; i < n_blocks; ++i) {
         const int s = i & 1;
@@ -134,24 +137,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_expect_tx(&kv_full[s], C::K_BYTES + C::V_BYTES);
         const int key0 = tok0 + (j_begin + i) * BN;
 #pragma unroll
-        for (int a = 0; a < D_ATOMS; ++a) {
-          tma_load_3d(k_dst + a * (BN * 128), &tmK, &kv_full[s], a * 64, hk, key0);
-          tma_load_3d(v_dst + a * (BN * 128), &tmV, &kv_full[s], a * 64, hk, key0);
-        }
+        for (int a = 0; a < QK_ATOMS; ++a) tma_load_3d(k_dst + a * (BN * 128), &tmK, &kv_full[s], a * 64, hk, key0);
+#pragma unroll
+        for (int a = 0; a < V_ATOMS; ++a) tma_load_3d(v_dst + a * (BN * 128), &tmV, &kv_full[s], a * 64, hk, key0);
       }
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(BLOCK_M, BN, false, false);
-      constexpr uint32_t idesc_pv = make_idesc_bf16(BLOCK_M, DH, false, true);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(BLOCK_M, DV, false, true);
       const uint32_t q_addr = smem_u32(q_s);
       const uint32_t p_addr = smem_u32(p_s);
       bool ok = mbar_wait(q_full, 0, abort_flag, args.status, MT_ERR_TIMEOUT_FULL);
       auto issue_qk = [&](int i) {
         const uint32_t k_addr = smem_u32(kv_s + (i & 1) * (C::K_BYTES + C::V_BYTES));
 #pragma unroll
-        for (int k = 0; k < DH / 16; ++k) {
+        for (int k = 0; k < DQK / 16; ++k) {
           const uint32_t off = (k >> 2) * (BLOCK_M * 128) + (k & 3) * 32;
           const uint32_t koff = (k >> 2) * (BN * 128) + (k & 3) * 32;
           tc_mma_f16(tmem_base + C::S_COL, make_smem_desc_sw128(q_addr + off, 16, 1024),
@@ -237,7 +239,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_after_sync();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-          for (int c = 0; c < DH / 32; ++c) {
+          for (int c = 0; c < DV / 32; ++c) {
             uint32_t o[32];
             tmem_ld_32x32b_x32(t_row + C::O_COL + c * 32, o);
             tc_wait_ld();
@@ -309,10 +311,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (ok) {
       tc_fence_after_sync();
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      // staging rows are 128 B (64 bf16) per atom; DH=128 uses two atoms: P region (>= 16 KB) + K stage 0
+      // staging rows are 128 B (64 bf16) per atom: the P region when it is large enough, else the K/V ring
       uint8_t* stage = (C::P_BYTES >= C::O_STAGE_BYTES) ? p_s : kv_s;
 #pragma unroll
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = 0; c < DV / 32; ++c) {
         uint32_t o[32];
         if (n_blocks > 0) {
           tmem_ld_32x32b_x32(t_row + C::O_COL + c * 32, o);
@@ -342,7 +344,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // warp on the error path would skip)
       if (threadIdx.x == 0 && mbar_wait(o_staged, 0, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) {
 #pragma unroll
-        for (int a = 0; a < D_ATOMS; ++a) tma_store_3d(&tmO, stage + a * (BLOCK_M * 128), a * 64, h, tok0 + q0);
+        for (int a = 0; a < V_ATOMS; ++a) tma_store_3d(&tmO, stage + a * (BLOCK_M * 128), a * 64, h, tok0 + q0);
         tma_commit_group();
         tma_wait_group<0>();
       }
@@ -358,17 +360,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-template <int DH, bool CAP>
+template <int DQK, int DV, bool CAP>
 void launch_fwd(const AttnParams& p, cudaStream_t stream) {
-  using C = FwdCfg<DH>;
+  using C = FwdCfg<DQK, DV>;
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
   const uint64_t tokens = static_cast<uint64_t>(p.B) * p.S;
-  CUtensorMap tQ = make_tmap_3d(p.q, bf, 2, tokens, p.H, DH, p.q_row_stride, DH, BLOCK_M, 1, 64, sw);
-  CUtensorMap tK = make_tmap_3d(p.k, bf, 2, tokens, p.Hkv, DH, p.k_row_stride, DH, C::BN, 1, 64, sw);
-  CUtensorMap tV = make_tmap_3d(p.v, bf, 2, tokens, p.Hkv, DH, p.v_row_stride, DH, C::BN, 1, 64, sw);
-  CUtensorMap tO = make_tmap_3d(p.o, bf, 2, tokens, p.H, DH, p.o_row_stride, DH, BLOCK_M, 1, 64, sw);
-  auto kern = flash_fwd_kernel<DH, CAP>;
+  CUtensorMap tQ = make_tmap_3d(p.q, bf, 2, tokens, p.H, DQK, p.q_row_stride, DQK, BLOCK_M, 1, 64, sw);
+  CUtensorMap tK = make_tmap_3d(p.k, bf, 2, tokens, p.Hkv, DQK, p.k_row_stride, DQK, C::BN, 1, 64, sw);
+  CUtensorMap tV = make_tmap_3d(p.v, bf, 2, tokens, p.Hkv, DV, p.v_row_stride, DV, C::BN, 1, 64, sw);
+  CUtensorMap tO = make_tmap_3d(p.o, bf, 2, tokens, p.H, DV, p.o_row_stride, DV, BLOCK_M, 1, 64, sw);
+  auto kern = flash_fwd_kernel<DQK, DV, CAP>;
   static bool configured = false;
   if (!configured) {
     MT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
@@ -386,9 +388,11 @@ void flash_attn_fwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
   (void)num_sms;
   if (p.S % BLOCK_M != 0) throw std::runtime_error("flash_attn_fwd: sequence length must be a multiple of 128");
   const bool cap = p.softcap > 0.f;
-  if (p.dh == 64) cap ? launch_fwd<64, true>(p, stream) : launch_fwd<64, false>(p, stream);
-  else if (p.dh == 128) cap ? launch_fwd<128, true>(p, stream) : launch_fwd<128, false>(p, stream);
-  else throw std::runtime_error("flash_attn_fwd: head_dim must be 64 or 128");
+  const int dv = p.dv_dim > 0 ? p.dv_dim : p.dh;
+  if (p.dh == 64 && dv == 64) cap ? launch_fwd<64, 64, true>(p, stream) : launch_fwd<64, 64, false>(p, stream);
+  else if (p.dh == 128 && dv == 128) cap ? launch_fwd<128, 128, true>(p, stream) : launch_fwd<128, 128, false>(p, stream);
+  else if (p.dh == 192 && dv == 128) cap ? launch_fwd<192, 128, true>(p, stream) : launch_fwd<192, 128, false>(p, stream);
+  else throw std::runtime_error("flash_attn_fwd: head dims must be 64, 128 or 192/128");
 }
 
 }  // namespace mt

@@ -177,6 +177,8 @@ mt::AttnParams attn_params(const torch::Tensor& q, const torch::Tensor& k, const
   mt::AttnParams p{};
   p.q = q.data_ptr(); p.k = k.data_ptr(); p.v = v.data_ptr();
   p.B = (int)q.size(0); p.S = (int)q.size(1); p.H = (int)q.size(2); p.Hkv = (int)k.size(2); p.dh = (int)q.size(3);
+  p.dv_dim = (int)v.size(3);
+  TORCH_CHECK(k.size(3) == q.size(3), "q and k head dims differ");
   p.q_row_stride = q.stride(1); p.k_row_stride = k.stride(1); p.v_row_stride = v.stride(1);
   p.scale = (float)scale; p.softcap = (float)softcap; p.window = (int)window; p.causal = causal ? 1 : 0;
   p.status = status.data_ptr<int>();
@@ -198,7 +200,8 @@ void flash_bwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tens
                int64_t window, double softcap, torch::Tensor& status) {
   mt::AttnParams p = attn_params(q, k, v, scale, causal, window, softcap, status);
   TORCH_CHECK(o.is_contiguous() && dout.is_contiguous() && dq.is_contiguous() && dk.is_contiguous() && dv.is_contiguous());
-  TORCH_CHECK(dq_accum.scalar_type() == torch::kFloat32 && dq_accum.numel() == q.numel() && dq_accum.is_contiguous());
+  TORCH_CHECK(dq_accum.scalar_type() == torch::kFloat32 && dq_accum.numel() == q.size(0) * q.size(1) * q.size(2) * q.size(3) &&
+              dq_accum.is_contiguous());
   TORCH_CHECK(delta.scalar_type() == torch::kFloat32 && delta.numel() == lse.numel());
   p.o = const_cast<void*>(o.data_ptr()); p.o_row_stride = o.stride(1);
   p.lse = const_cast<float*>(lse.data_ptr<float>());

@@ -10,7 +10,7 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
-def _run(B, S, H, Hkv, d, causal=True, window=None, softcap=None, grad=True):
+def _run(B, S, H, Hkv, d, causal=True, window=None, softcap=None, grad=True, dv=None):
     from mintext_b200.ops import oracle
     from mintext_b200.ops._ext import check_status
     from mintext_b200.ops.attention import flash_attention
@@ -18,7 +18,7 @@ def _run(B, S, H, Hkv, d, causal=True, window=None, softcap=None, grad=True):
     torch.manual_seed(0)
     q = torch.randn(B, S, H, d, device="cuda", dtype=torch.bfloat16, requires_grad=grad)
     k = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.bfloat16, requires_grad=grad)
-    v = torch.randn(B, S, Hkv, d, device="cuda", dtype=torch.bfloat16, requires_grad=grad)
+    v = torch.randn(B, S, Hkv, dv or d, device="cuda", dtype=torch.bfloat16, requires_grad=grad)
     scale = d ** -0.5
     o = flash_attention(q, k, v, scale, causal, window, softcap)
     qf, kf, vf = (t.detach().float().requires_grad_(grad) for t in (q, k, v))
@@ -70,6 +70,17 @@ def test_flash_bwd_dh128_window_and_softcap():
     _run(1, 512, 2, 1, 128, window=200)
     _run(1, 256, 2, 2, 128, softcap=30.0)
     _run(1, 256, 2, 1, 128, causal=False)
+
+
+def test_flash_mla_shape_fwd():
+    _run(1, 256, 2, 2, 192, grad=False, dv=128)
+    _run(2, 512, 4, 4, 192, causal=False, grad=False, dv=128)
+
+
+def test_flash_mla_shape_bwd():
+    _run(1, 128, 1, 1, 192, dv=128)
+    _run(2, 512, 4, 4, 192, dv=128)
+    _run(1, 384, 2, 2, 192, causal=False, dv=128)
 
 
 def test_flash_window_and_softcap():
