@@ -60,7 +60,8 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int accumulate, int* status) {
+                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int accumulate, int splits,
+                 int* status) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -79,6 +80,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_n = (N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (K + BK - 1) / BK;
+  // split-K (only with the accumulating epilogue): work item w = split * num_tiles + tile covers k-blocks
+  // [split * num_kb / splits, (split + 1) * num_kb / splits)
+  const int num_items = num_tiles * splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -109,9 +113,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(tile, num_m, num_n, BN);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int split = item / num_tiles;
+        const TileCoord tc = tile_coord(item - split * num_tiles, num_m, num_n, BN);
+        const int kb_lo = static_cast<int>(static_cast<int64_t>(split) * num_kb / splits);
+        const int kb_hi = static_cast<int>(static_cast<int64_t>(split + 1) * num_kb / splits);
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, status, MT_ERR_TIMEOUT_EMPTY)) {
@@ -144,7 +151,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int it = 0;
       int tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++tcount) {
+        const int split = item / num_tiles;
+        const int kb_lo = static_cast<int>(static_cast<int64_t>(split) * num_kb / splits);
+        const int kb_hi = static_cast<int>(static_cast<int64_t>(split + 1) * num_kb / splits);
         const int buf = tcount & 1;
         const uint32_t acc_ph = (tcount >> 1) & 1;
         if (!mbar_wait(&tmem_empty[buf], acc_ph ^ 1, abort_flag, status, MT_ERR_TIMEOUT_TMEM_EMPTY)) {
@@ -153,7 +163,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, status, MT_ERR_TIMEOUT_FULL)) {
@@ -169,7 +179,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                      : make_smem_desc_sw128(a_addr + k * (UMMA_K * 2), 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc_sw128(b_addr + k * (UMMA_K * 128), BK * 128, 1024)
                                      : make_smem_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
-            tc_mma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            tc_mma_f16(d_tmem, da, db, idesc, ((kb - kb_lo) | k) != 0 ? 1u : 0u);
           }
           tc_commit(&empty_bar[s]);  // slot reusable once these MMAs have read it
         }
@@ -184,8 +194,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int tcount = 0;
     int nstores = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
-      const TileCoord tc = tile_coord(tile, num_m, num_n, BN);
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++tcount) {
+      const TileCoord tc = tile_coord(item % num_tiles, num_m, num_n, BN);
       const int buf = tcount & 1;
       const uint32_t acc_ph = (tcount >> 1) & 1;
       if (!mbar_wait_warp(&tmem_full[buf], acc_ph, abort_flag, status, MT_ERR_TIMEOUT_TMEM_FULL)) {
@@ -270,8 +280,27 @@ void launch_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensor
     configured = true;
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tA, tB, tC, M, N, K, accumulate ? 1 : 0, status);
+  // Split K when the tiles fill the last wave badly and the epilogue adds into C anyway (weight gradients:
+  // few tiles, long K).  Each split pays one more pass of the fp32 tile through the reduce-add epilogue.
+  int splits = 1;
+  if (OUT_F32 && accumulate) {
+    const int num_kb = (K + BK - 1) / BK;
+    auto eff = [&](int s) {
+      const int items = tiles * s;
+      return static_cast<double>(items) / (static_cast<double>((items + num_sms - 1) / num_sms) * num_sms);
+    };
+    double best = eff(1);
+    for (int s = 2; s <= 4; ++s) {
+      if (num_kb / s < 16) break;
+      if (eff(s) > best + 0.08) {
+        best = eff(s);
+        splits = s;
+      }
+    }
+  }
+  const int items = tiles * splits;
+  const int grid = items < num_sms ? items : num_sms;
+  kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tA, tB, tC, M, N, K, accumulate ? 1 : 0, splits, status);
   MT_CUDA_CHECK(cudaGetLastError());
 }
 

@@ -58,6 +58,20 @@ def test_gemm_fp32_out_and_accumulate(accumulate):
     assert _rel_err(c, ref) < 1e-5
 
 
+def test_gemm_weight_gradient_layout_with_split_k():
+    """x^T dy accumulated into fp32 with few output tiles and a long contraction: the launcher splits K."""
+    torch.manual_seed(3)
+    T, Kin, Nout = 4096 + 64, 2048, 3072   # 16 x 12 tiles on 148 SMs -> three K slices (of unequal length)
+    x = torch.randn(T, Kin, device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn(T, Nout, device="cuda", dtype=torch.bfloat16)
+    c0 = torch.randn(Kin, Nout, device="cuda", dtype=torch.float32)
+    c = c0.clone()
+    _ext().gemm(x, dy, c, True, True, True, _status())
+    _check()
+    ref = x.float().t() @ dy.float() + c0
+    assert _rel_err(c, ref) < 1e-4
+
+
 def test_gemm_bf16_accumulate():
     torch.manual_seed(2)
     M, N, K = 256, 256, 512
