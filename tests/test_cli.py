@@ -1,0 +1,73 @@
+"""The training loop end to end through the public entry points (CPU plumbing path): config files + overrides,
+synthetic batches, metric logging, checkpoints on the save interval, resume."""
+
+import json
+from pathlib import Path
+
+import pytest
+
+from mintext_b200.config import load_config
+from mintext_b200.train import main, train
+
+ROOT = Path(__file__).resolve().parents[1]
+TINY = [str(ROOT / "configs" / "base.yml"), str(ROOT / "configs" / "models" / "test-tiny.yml")]
+
+
+def _cfg(tmp_path, **kw):
+    over = dict(steps=4, seq_length=32, per_device_batch_size=2, enable_tensorboard=False, log_period=1,
+                checkpoint_dir=str(tmp_path / "ckpt"), enable_checkpointing=True, checkpoint_period=2,
+                dtype="float32", weight_dtype="float32", kernel_backend="oracle", learning_rate=1e-3)
+    over.update(kw)
+    return load_config(TINY, over)
+
+
+def test_train_loop_checkpoints_and_resumes(tmp_path):
+    last = train(_cfg(tmp_path))
+    assert last["step"] == 3 and last["loss"] == last["loss"]
+    saved = sorted(int(p.name) for p in (tmp_path / "ckpt").iterdir() if p.name.isdigit())
+    assert 4 in saved and 2 in saved, saved
+    # a longer run from the same directory starts at the saved step and ends at its own last step
+    last2 = train(_cfg(tmp_path, steps=6))
+    assert last2["step"] == 5
+    saved = sorted(int(p.name) for p in (tmp_path / "ckpt").iterdir() if p.name.isdigit())
+    assert 6 in saved
+
+
+def test_resumed_run_equals_uninterrupted_run(tmp_path):
+    import shutil
+
+    full = train(_cfg(tmp_path, steps=6, checkpoint_period=3))
+    shutil.rmtree(tmp_path / "ckpt" / "6")  # as if the run had stopped after the step-3 checkpoint
+    resumed = train(_cfg(tmp_path, steps=6, checkpoint_period=3))
+    assert abs(full["loss"] - resumed["loss"]) < 1e-5, (full, resumed)
+
+
+def test_cli_main_with_overrides(tmp_path, capsys):
+    main(["--config", TINY[0], "--config", TINY[1], "steps=2", "seq_length=16", "enable_tensorboard=false",
+          "enable_checkpointing=false", "kernel_backend=oracle", "dtype=float32", "weight_dtype=float32",
+          f"log_dir={tmp_path}"])
+    main(["--help-config"])
+    assert "learning_rate" in capsys.readouterr().out
+
+
+@pytest.mark.parametrize("model", ["deepseek-v3-4l", "qwen3-next-80b-a3b", "gemma-3-4b"])
+def test_model_configs_shrink_and_train(tmp_path, model):
+    """The shipped model configs, shrunk by overrides, run through the loop (MoE bias update included)."""
+    paths = [str(ROOT / "configs" / "base.yml"), str(ROOT / "configs" / "models" / f"{model}.yml")]
+    over = dict(steps=2, seq_length=16, per_device_batch_size=1, num_hidden_layers=2, hidden_size=64, vocab_size=128,
+                num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=128,
+                enable_tensorboard=False, enable_checkpointing=False, dtype="float32", weight_dtype="float32",
+                kernel_backend="oracle", ici_expert_parallelism=1, ici_tensor_parallelism=1, ici_fsdp_parallelism=1,
+                ici_data_parallelism=1)
+    cfg0 = load_config(paths, None)
+    if cfg0.num_experts > 0:
+        over.update(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, n_group=1, topk_group=1,
+                    first_k_dense_replace=min(1, cfg0.first_k_dense_replace))
+    if cfg0.attention_type == "mla":
+        over.update(q_lora_rank=16, kv_lora_rank=16, qk_nope_head_dim=8, qk_rope_head_dim=4, v_head_dim=8)
+    if model.startswith("qwen3-next"):
+        over.update(linear_key_head_dim=8, linear_value_head_dim=8, linear_num_key_heads=2, linear_num_value_heads=4)
+    if model.startswith("gemma"):
+        over.update(sliding_window=8)
+    last = train(load_config(paths, over))
+    assert last["loss"] == last["loss"]
