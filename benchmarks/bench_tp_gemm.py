@@ -79,6 +79,29 @@ def main():
             rows.append({"op": name, "tp": t, "tokens": T, "hidden": D, "ffn_local": Fl, "fused_ms": round(ms_f, 4),
                          "nccl_ms": round(ms_p, 4), "speedup": round(ms_p / ms_f, 3), "roofline_ms": round(floor_ms, 4),
                          "fused_frac_of_roofline": round(floor_ms / ms_f, 3)})
+    # fully sharded weight (FSDP): gather of W [D, F] folded into x @ W, vs all_gather_into_tensor + GEMM
+    from mintext_b200.ops import tp_gemm
+    from mintext_b200.ops._ext import ext, status_word
+
+    Ff = args.ffn
+    w_full = (torch.randn(D, Ff, device=dev) * 0.02).bfloat16()
+    sw = tp_gemm.ShardedWeight(w_full, dist.group.WORLD, dev)
+    xs = torch.randn(Tl, D, device=dev).bfloat16()
+    wbuf = torch.empty(D, Ff, device=dev, dtype=torch.bfloat16)
+    ybuf = torch.empty(Tl, Ff, device=dev, dtype=torch.bfloat16)
+
+    def nccl_path():
+        dist.all_gather_into_tensor(wbuf, sw.shard.detach())
+        ext().gemm(xs, wbuf, ybuf, False, True, False, status_word(dev))
+
+    with torch.no_grad():
+        ms_f = _time(lambda: tp_gemm.fsdp_linear(xs, sw), dev)
+        ms_p = _time(nccl_path, dev)
+    flops, link_bytes = 2.0 * Tl * D * Ff, (t - 1) * (D // t) * Ff * 2
+    floor_ms = max(flops / (args.gemm_tflops * 1e12), link_bytes / (args.link_gbs * 1e9)) * 1e3
+    rows.append({"op": "FSDP weight all-gather -> GEMM (MLP up, full width)", "tp": t, "tokens": Tl, "hidden": D,
+                 "ffn_local": Ff, "fused_ms": round(ms_f, 4), "nccl_ms": round(ms_p, 4), "speedup": round(ms_p / ms_f, 3),
+                 "roofline_ms": round(floor_ms, 4), "fused_frac_of_roofline": round(floor_ms / ms_f, 3)})
     check_status(dev)
     if rank == 0:
         for r in rows:

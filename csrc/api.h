@@ -94,13 +94,17 @@ void ep_pull_rows(void* out, const int* src_rank, const int64_t* src_pos, const 
 
 // ---- comm/tp_gemm.cu: tensor-parallel GEMMs fused with their collective (bf16; T tokens over `world` ranks)
 // C[T,N] = gather(shards)[T,K] * op(B); the kernel itself fills `gathered` from the ranks' shards (peer memory)
-// while it computes; `ready` is int[T/128], zeroed by the caller before the call, ready_target = 128*K*2/16384.
+// while it computes; `ready` is int[T/128], zeroed by the caller before the call, ready_target = 128*K*2/8192.
 void tp_gemm_ag(const PeerPtrs& shards, void* gathered, const void* B, void* C, int T, int N, int K, int rank, int world,
                 bool b_mn_major, int* ready, int ready_target, int* status, int num_sms, cudaStream_t stream);
 // partial[T,N] = A[T,K] * op(B), rows of rank i stored into staging_slots.p[i] ([T/world, N], peer memory).
 void tp_gemm_rs(const void* A, const void* B, const PeerPtrs& staging_slots, int T, int N, int K, int rank, int world,
                 bool b_mn_major, int* status, int num_sms, cudaStream_t stream);
 void tp_reduce_slots(const void* staging, void* y, int slots, int64_t slot_elems, cudaStream_t stream);
+// C[T,N] = A[T,K] * W[K,N] with W sharded over ranks by rows of K (w_shards: each rank's [K/world, N] shard in
+// symmetric memory); the kernel assembles W in `w_full` while it computes.  ready: int[K/64], zeroed by the caller.
+void fsdp_gemm_agw(const void* A, const PeerPtrs& w_shards, void* w_full, void* C, int T, int N, int K, int rank,
+                   int world, int* ready, int* status, int num_sms, cudaStream_t stream);
 
 // ---- gemm/fp8_gemm.cu: per-tensor-scaled FP8 GEMM (both operands K-major) and its quantisation kernels
 void fp8_amax(const void* x_bf16, int64_t n, float* amax, cudaStream_t stream);

@@ -441,7 +441,7 @@ void tp_gemm_ag(const std::vector<int64_t>& shard_ptrs, torch::Tensor& gathered,
   TORCH_CHECK(K % 64 == 0 && N % 8 == 0 && ready.numel() >= T / 128 && ready.scalar_type() == torch::kInt32);
   c10::cuda::CUDAGuard guard(out.device());
   mt::tp_gemm_ag(to_peers(shard_ptrs), gathered.data_ptr(), B.data_ptr(), out.data_ptr(), (int)T, (int)N, (int)K, (int)rank,
-                 (int)shard_ptrs.size(), b_kn, ready.data_ptr<int>(), (int)(128 * K * 2 / 16384), status.data_ptr<int>(),
+                 (int)shard_ptrs.size(), b_kn, ready.data_ptr<int>(), (int)(128 * K * 2 / 8192), status.data_ptr<int>(),
                  sm_count(), cur_stream());
 }
 
@@ -456,6 +456,20 @@ void tp_gemm_rs(const torch::Tensor& A, const torch::Tensor& B, const std::vecto
   c10::cuda::CUDAGuard guard(A.device());
   mt::tp_gemm_rs(A.data_ptr(), B.data_ptr(), to_peers(slot_ptrs), (int)T, (int)N, (int)K, (int)rank, (int)slot_ptrs.size(),
                  b_kn, status.data_ptr<int>(), sm_count(), cur_stream());
+}
+
+// out[T,N] = a[T,K] @ W[K,N], W gathered inside the kernel from the ranks' row shards into w_full
+void fsdp_gemm_agw(const torch::Tensor& a, const std::vector<int64_t>& shard_ptrs, torch::Tensor& w_full, torch::Tensor& out,
+                   int64_t rank, torch::Tensor& ready, torch::Tensor& status) {
+  TORCH_CHECK(a.is_contiguous() && w_full.is_contiguous() && out.is_contiguous());
+  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w_full.scalar_type() == torch::kBFloat16 &&
+              out.scalar_type() == torch::kBFloat16);
+  const int64_t T = a.size(0), K = a.size(1), N = w_full.size(1);
+  TORCH_CHECK(w_full.size(0) == K && out.size(0) == T && out.size(1) == N && ready.numel() >= K / 64 &&
+              ready.scalar_type() == torch::kInt32);
+  c10::cuda::CUDAGuard guard(a.device());
+  mt::fsdp_gemm_agw(a.data_ptr(), to_peers(shard_ptrs), w_full.data_ptr(), out.data_ptr(), (int)T, (int)N, (int)K, (int)rank,
+                    (int)shard_ptrs.size(), ready.data_ptr<int>(), status.data_ptr<int>(), sm_count(), cur_stream());
 }
 
 void tp_reduce_slots(const torch::Tensor& staging, torch::Tensor& y) {
@@ -499,6 +513,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tp_gemm_ag", &tp_gemm_ag);
   m.def("tp_gemm_rs", &tp_gemm_rs);
   m.def("tp_reduce_slots", &tp_reduce_slots);
+  m.def("fsdp_gemm_agw", &fsdp_gemm_agw);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);
 }

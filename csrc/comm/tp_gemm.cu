@@ -2,8 +2,8 @@
 //
 // MODE_AG  all-gather -> GEMM.  C[T, N] = G[T, K] * op(B), where G is the concatenation of every rank's token
 //          shard [T/t, K].  The shards live in symmetric memory; G is a local buffer this kernel fills itself:
-//          a seventh warp in every CTA pulls 16 KB pieces of the shards (peers' and its own) with bulk TMA copies
-//          (peer global -> shared -> local global, three in flight per CTA) and counts finished pieces per
+//          a seventh warp in every CTA pulls 8 KB pieces of the shards (peers' and its own) with bulk TMA copies
+//          (peer global -> shared -> local global, two in flight per CTA) and counts finished pieces per
 //          128-row block; the TMA producer warp of the GEMM waits (bounded) for a row block's count before it
 //          loads A tiles from it.  Tiles are visited starting with this rank's own rows, so the tensor cores
 //          work on local data while remote rows are still crossing NVLink.  G stays behind for the caller
@@ -12,6 +12,10 @@
 //          output tile straight into the staging slot [source rank] of the rank that owns those rows (TMA store
 //          to peer memory), so when the kernel ends the partial tiles are already scattered; a small local kernel
 //          (tp_reduce_slots) adds the t slots.
+// MODE_AGB all-gather of a sharded *weight* -> GEMM (fully-sharded data parallelism).  C[T, N] = A[T, K] * W[K, N] with
+//          W sharded over ranks by rows of K.  The gather warps assemble the full W in a local buffer exactly as
+//          above; the producer waits per 64-row k-block of W and walks the k-blocks starting with this rank's own
+//          shard, so the main loop starts at once and the remote rows arrive underneath it.
 // No multicast loads anywhere; remote traffic is bulk / tensor TMA without multicast and ordinary stores.
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
@@ -24,14 +28,21 @@ constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
 constexpr int kEpiWarps = 4;
 constexpr int kThreads = 32 * (3 + kEpiWarps);  // TMA, MMA, 4 epilogue, copy
 constexpr int kEpiStageBytes = 4096;
-constexpr int kStages = 3;
-constexpr int kPieceBytes = 16384;
-constexpr int kCopySlots = 3;
+constexpr int kPieceBytes = 8192;  // granularity of the readiness counters
+enum { MODE_AG = 0, MODE_RS = 1, MODE_AGB = 2 };
 
+// Shared-memory split per mode: the token gather moves (t-1)/t of the activations and gets a deep copy ring at the
+// price of one pipeline stage; the weight gather is small next to its GEMM and keeps four stages; the scattering
+// GEMM has no ring at all.
+template <int MODE>
 struct TCfg {
+  static constexpr int kStages = MODE == MODE_AG ? 3 : 4;
+  static constexpr int kEpiBufs = MODE == MODE_RS ? 2 : 1;   // staging buffers per epilogue warp
+  static constexpr int kCopyBytes = MODE == MODE_AG ? 16384 : 8192;  // bytes per bulk copy (multiple of the piece)
+  static constexpr int kCopySlots = MODE == MODE_AG ? 4 : (MODE == MODE_AGB ? 2 : 0);
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int EPI_BYTES = kEpiWarps * 2 * kEpiStageBytes;
-  static constexpr int COPY_BYTES = kCopySlots * kPieceBytes;
+  static constexpr int EPI_BYTES = kEpiWarps * kEpiBufs * kEpiStageBytes;
+  static constexpr int COPY_BYTES = kCopySlots * kCopyBytes;
   static constexpr int OFF_EPI = kStages * STAGE_BYTES;
   static constexpr int OFF_COPY = OFF_EPI + EPI_BYTES;
   static constexpr int OFF_BAR = OFF_COPY + COPY_BYTES;
@@ -49,10 +60,12 @@ struct TpArgs {
   int rank, world;
   int rows_per_rank;      // T / t (multiple of 128)
   // MODE_AG
-  const void* shard[kMaxPeers];  // every rank's [T/t, K] shard (symmetric memory)
-  void* gathered;                // local [T, K]
-  int* ready;                    // local int[T/128], pieces landed per row block, monotonically increasing
-  int ready_target;              // value a row block's counter has once this call's pieces are in
+  const void* shard[kMaxPeers];  // every rank's shard of the gathered operand (symmetric memory)
+  void* gathered;                // local buffer for the whole gathered operand
+  int* ready;                    // local counters, one per block of the gathered operand: 8 KB pieces landed
+  int ready_target;              // value a block's counter has once this call's pieces are in
+  int64_t rank_bytes;            // bytes of one rank's shard
+  int64_t block_bytes;           // bytes per readiness block (128 token rows of A, or 64 k-rows of W)
   int* status;
 };
 
@@ -77,8 +90,6 @@ __device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint3
 }
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
-enum { MODE_AG = 0, MODE_RS = 1 };
-
 // Tile order: groups of 8 column tiles, rows fastest inside a group, rows rotated so that `row_rot` comes first.
 __device__ __forceinline__ void tile_coord(int tile, int num_m, int num_n, int row_rot, int& m_idx, int& n_idx) {
   const int per_group = 8 * num_m;
@@ -94,7 +105,11 @@ template <int MODE, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CMaps tmC, const TpArgs a) {
-  using C = TCfg;
+  using C = TCfg<MODE>;
+  constexpr int kStages = C::kStages;
+  constexpr int kEpiBufs = C::kEpiBufs;
+  constexpr int kCopySlots = C::kCopySlots;
+  constexpr int kCopyBytes = C::kCopyBytes;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0 && a.status) atomicCAS(a.status, 0, MT_ERR_BAD_ARGS);
@@ -118,7 +133,8 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int num_tiles = num_m * num_n;
   const int num_kb = (a.K + BK - 1) / BK;
   const int blocks_per_rank = a.rows_per_rank / BM;
-  const int row_rot = a.rank * blocks_per_rank;  // this rank's rows first
+  const int row_rot = MODE == MODE_AGB ? 0 : a.rank * blocks_per_rank;  // this rank's rows first
+  const int kb_rot = MODE == MODE_AGB ? a.rank * (num_kb / a.world) : 0;  // this rank's k-blocks first
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -149,6 +165,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       int it = 0;
       bool ok = true;
+      bool all_ready = false;  // MODE_AGB: every k-block has been seen complete (after this CTA's first tile)
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_idx, n_idx;
         tile_coord(tile, num_m, num_n, row_rot, m_idx, n_idx);
@@ -168,7 +185,23 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           fence_proxy_async_all();
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kbi = 0; kbi < num_kb; ++kbi, ++it) {
+          const int kb = (kbi + kb_rot) % num_kb;
+          if (MODE == MODE_AGB && !all_ready) {  // this k-block of the weight must have been gathered
+            if (ld_acquire_gpu(a.ready + kb) < a.ready_target) {
+              const long long t0 = clock64();
+              while (ld_acquire_gpu(a.ready + kb) < a.ready_target) {
+                if (*abort_flag || clock64() - t0 > kMaxWaitCycles) {
+                  *abort_flag = 1;
+                  if (a.status) atomicCAS(a.status, 0, MT_ERR_TIMEOUT_FLAG);
+                  ok = false;
+                  break;
+                }
+              }
+              if (!ok) break;
+            }
+            fence_proxy_async_all();
+          }
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, a.status, MT_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -184,6 +217,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tma_load_2d(b_dst, &tmB, &full_bar[s], kb * BK, n_idx * BN);
           }
         }
+        all_ready = true;
       }
     }
   } else if (warp == 1) {
@@ -197,7 +231,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!mbar_wait(&tmem_empty[buf], ((tcount >> 1) & 1) ^ 1, abort_flag, a.status, MT_ERR_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {  // kb counts loop steps here; the producer chose the k order
           const int s = it % kStages;
           if (!mbar_wait(&full_bar[s], (it / kStages) & 1, abort_flag, a.status, MT_ERR_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after_sync();
@@ -218,7 +252,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else if (warp < 2 + kEpiWarps) {
     // ------------------------------------------------------------ epilogue (bf16 out)
     const int q = warp & 3;
-    uint8_t* stage0 = epi_base + (warp - 2) * 2 * kEpiStageBytes;
+    uint8_t* stage0 = epi_base + (warp - 2) * kEpiBufs * kEpiStageBytes;
     int tcount = 0, nstores = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
       int m_idx, n_idx;
@@ -237,8 +271,8 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int c = 0; c < BN / 64; ++c) {
         const int col0 = n_idx * BN + c * 64;
         if (col0 >= a.N) break;
-        uint8_t* sbuf = stage0 + (nstores & 1) * kEpiStageBytes;
-        if (lane == 0) tma_wait_group_read<1>();
+        uint8_t* sbuf = stage0 + (nstores % kEpiBufs) * kEpiStageBytes;
+        if (lane == 0) tma_wait_group_read<kEpiBufs - 1>();
         __syncwarp();
         uint8_t* srow = sbuf + lane * 128;
 #pragma unroll
@@ -270,67 +304,65 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     if (lane == 0) tma_wait_group<0>();
   } else {
-    // ------------------------------------------------------------ gather warp (MODE_AG): bulk copies of shard pieces
-    if (MODE == MODE_AG && lane == 0) {
-      const int64_t rank_bytes = static_cast<int64_t>(a.rows_per_rank) * a.K * 2;
-      const int64_t pieces_per_rank = rank_bytes / kPieceBytes;
-      const int64_t total = pieces_per_rank * a.world;
-      const int64_t block_bytes = static_cast<int64_t>(BM) * a.K * 2;  // one 128-row block
-      int issued = 0;          // pieces whose load has been issued by this CTA
-      int stored = 0;          // pieces whose store has been issued
-      int signalled = 0;       // pieces counted into `ready`
-      int64_t mine[kCopySlots];  // global piece index per slot
-      auto piece_of = [&](int n) -> int64_t {  // n-th piece of this CTA, own rank's region first
-        const int64_t i = static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(n) * gridDim.x;
-        return (i + static_cast<int64_t>(a.rank) * pieces_per_rank) % total;
-      };
-      auto signal = [&](int64_t piece) {
-        const int64_t byte = (piece % pieces_per_rank) * kPieceBytes + (piece / pieces_per_rank) * rank_bytes;
-        red_release_gpu_add(a.ready + static_cast<int>(byte / block_bytes), 1);
-      };
-      const int n_mine = static_cast<int>((total - blockIdx.x + gridDim.x - 1) / gridDim.x);
-      int64_t pending_signal[2] = {-1, -1};
-      bool ok = true;
-      for (int n = 0; n < n_mine + (kCopySlots - 1) && ok; ++n) {
-        if (n < n_mine) {
-          const int s = n % kCopySlots;
-          // slot s was last used by piece n - kCopySlots whose store was issued in the previous iteration
-          tma_wait_group_read<0>();
-          const int64_t p = piece_of(n);
-          mine[s] = p;
-          const int src_rank = static_cast<int>(p / pieces_per_rank);
-          const uint8_t* src = static_cast<const uint8_t*>(a.shard[src_rank]) + (p % pieces_per_rank) * kPieceBytes;
-          mbar_expect_tx(&copy_bar[s], kPieceBytes);
-          bulk_g2s(copy_base + s * kPieceBytes, src, kPieceBytes, &copy_bar[s]);
-          ++issued;
-        }
-        const int d = n - (kCopySlots - 1);  // piece whose data should have arrived by now
-        if (d >= 0 && d < n_mine) {
-          const int s = d % kCopySlots;
-          if (!mbar_wait(&copy_bar[s], (d / kCopySlots) & 1, abort_flag, a.status, MT_ERR_TIMEOUT_FULL)) { ok = false; break; }
-          const int64_t p = mine[s];
-          uint8_t* dst = static_cast<uint8_t*>(a.gathered) + (p / pieces_per_rank) * rank_bytes +
-                         (p % pieces_per_rank) * kPieceBytes;
-          bulk_s2g(dst, copy_base + s * kPieceBytes, kPieceBytes);
-          tma_commit_group();
-          ++stored;
-          // the store issued one step earlier has completed once at most one group is pending
-          if (pending_signal[0] >= 0) {
-            tma_wait_group<1>();
-            fence_proxy_async_all();
-            signal(pending_signal[0]);
-            ++signalled;
+    // ------------------------------------------------------------ gather warp: bulk copies of the shards
+    if constexpr (MODE == MODE_AG || MODE == MODE_AGB) {
+      if (lane == 0) {
+        constexpr int kUnitPieces = kCopyBytes / kPieceBytes;
+        const int64_t rank_bytes = a.rank_bytes;
+        const int64_t units_per_rank = rank_bytes / kCopyBytes;
+        const int64_t total = units_per_rank * a.world;
+        const int64_t block_bytes = a.block_bytes;
+        int64_t mine[kCopySlots];  // copy unit held by each slot
+        auto unit_of = [&](int n) -> int64_t {  // n-th unit of this CTA, own rank's region first
+          const int64_t i = static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(n) * gridDim.x;
+          return (i + static_cast<int64_t>(a.rank) * units_per_rank) % total;
+        };
+        auto offset_of = [&](int64_t u) -> int64_t {
+          return (u / units_per_rank) * rank_bytes + (u % units_per_rank) * kCopyBytes;
+        };
+        auto signal = [&](int64_t u) {
+          red_release_gpu_add(a.ready + static_cast<int>(offset_of(u) / block_bytes), kUnitPieces);
+        };
+        const int n_mine = static_cast<int>((total - blockIdx.x + gridDim.x - 1) / gridDim.x);
+        int64_t pending_signal = -1;
+        bool ok = true;
+        for (int n = 0; n < n_mine + (kCopySlots - 1) && ok; ++n) {
+          if (n < n_mine) {
+            const int s = n % kCopySlots;
+            // slot s was last used by unit n - kCopySlots, whose store was issued in the previous iteration
+            tma_wait_group_read<0>();
+            const int64_t u = unit_of(n);
+            mine[s] = u;
+            const uint8_t* src =
+                static_cast<const uint8_t*>(a.shard[u / units_per_rank]) + (u % units_per_rank) * kCopyBytes;
+            mbar_expect_tx(&copy_bar[s], kCopyBytes);
+            bulk_g2s(copy_base + s * kCopyBytes, src, kCopyBytes, &copy_bar[s]);
           }
-          pending_signal[0] = p;
+          const int d = n - (kCopySlots - 1);  // unit whose data should have arrived by now
+          if (d >= 0 && d < n_mine) {
+            const int s = d % kCopySlots;
+            if (!mbar_wait(&copy_bar[s], (d / kCopySlots) & 1, abort_flag, a.status, MT_ERR_TIMEOUT_FULL)) {
+              ok = false;
+              break;
+            }
+            const int64_t u = mine[s];
+            bulk_s2g(static_cast<uint8_t*>(a.gathered) + offset_of(u), copy_base + s * kCopyBytes, kCopyBytes);
+            tma_commit_group();
+            // the store issued one step earlier has completed once at most one group is pending
+            if (pending_signal >= 0) {
+              tma_wait_group<1>();
+              fence_proxy_async_all();
+              signal(pending_signal);
+            }
+            pending_signal = u;
+          }
+        }
+        tma_wait_group<0>();
+        if (ok && pending_signal >= 0) {
+          fence_proxy_async_all();
+          signal(pending_signal);
         }
       }
-      tma_wait_group<0>();
-      if (ok && pending_signal[0] >= 0) {
-        fence_proxy_async_all();
-        signal(pending_signal[0]);
-        ++signalled;
-      }
-      (void)issued; (void)stored; (void)signalled;
     }
   }
 
@@ -368,14 +400,15 @@ template <int MODE, bool B_MN>
 void launch(const CUtensorMap& tA, const CUtensorMap& tB, const CMaps& tC, const TpArgs& a, int num_sms,
             cudaStream_t stream) {
   auto kern = tp_gemm_kernel<MODE, B_MN>;
+  using Cf = TCfg<MODE>;
   static bool configured = false;
   if (!configured) {
-    MT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TCfg::SMEM_BYTES));
+    MT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::SMEM_BYTES));
     configured = true;
   }
   const int tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, kThreads, TCfg::SMEM_BYTES, stream>>>(tA, tB, tC, a);
+  kern<<<grid, kThreads, Cf::SMEM_BYTES, stream>>>(tA, tB, tC, a);
   MT_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -386,7 +419,7 @@ void tp_gemm_ag(const PeerPtrs& shards, void* gathered, const void* B, void* Cou
                 cudaStream_t stream) {
   const int rows_per_rank = T / world;
   if (T % (world * BM) != 0) throw std::runtime_error("tp_gemm_ag: tokens per rank must be a multiple of 128");
-  if ((static_cast<int64_t>(BM) * K * 2) % kPieceBytes != 0) throw std::runtime_error("tp_gemm_ag: K must be a multiple of 64");
+  if (K % 64 != 0) throw std::runtime_error("tp_gemm_ag: K must be a multiple of 64");
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
   CUtensorMap tA = make_tmap_2d(gathered, bf, 2, T, K, K, BM, BK, sw);
@@ -397,6 +430,8 @@ void tp_gemm_ag(const PeerPtrs& shards, void* gathered, const void* B, void* Cou
   a.M = T; a.N = N; a.K = K; a.rank = rank; a.world = world; a.rows_per_rank = rows_per_rank;
   for (int i = 0; i < world; ++i) a.shard[i] = shards.p[i];
   a.gathered = gathered; a.ready = ready; a.ready_target = ready_target; a.status = status;
+  a.rank_bytes = static_cast<int64_t>(rows_per_rank) * K * 2;
+  a.block_bytes = static_cast<int64_t>(BM) * K * 2;
   if (b_mn_major) launch<MODE_AG, true>(tA, tB, tC, a, num_sms, stream);
   else launch<MODE_AG, false>(tA, tB, tC, a, num_sms, stream);
 }
@@ -416,6 +451,27 @@ void tp_gemm_rs(const void* A, const void* B, const PeerPtrs& staging_slots, int
   a.M = T; a.N = N; a.K = K; a.rank = rank; a.world = world; a.rows_per_rank = rows_per_rank; a.status = status;
   if (b_mn_major) launch<MODE_RS, true>(tA, tB, tC, a, num_sms, stream);
   else launch<MODE_RS, false>(tA, tB, tC, a, num_sms, stream);
+}
+
+void fsdp_gemm_agw(const void* A, const PeerPtrs& w_shards, void* w_full, void* Cout, int T, int N, int K, int rank,
+                   int world, int* ready, int* status, int num_sms, cudaStream_t stream) {
+  if (K % (world * BK) != 0) throw std::runtime_error("fsdp_gemm_agw: K must be a multiple of 64 * world");
+  if ((static_cast<int64_t>(BK) * N * 2) % kPieceBytes != 0 || (static_cast<int64_t>(K / world) * N * 2) % kPieceBytes != 0)
+    throw std::runtime_error("fsdp_gemm_agw: N must be a multiple of 128");
+  const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  CUtensorMap tA = make_tmap_2d(A, bf, 2, T, K, K, BM, BK, sw);
+  CUtensorMap tB = make_tmap_2d(w_full, bf, 2, K, N, N, BK, 64, sw);
+  CMaps tC{};
+  tC.m[0] = make_tmap_2d(Cout, bf, 2, T, N, N, 32, 64, sw);
+  TpArgs a{};
+  a.M = T; a.N = N; a.K = K; a.rank = rank; a.world = world; a.rows_per_rank = BM;  // unused by this mode
+  for (int i = 0; i < world; ++i) a.shard[i] = w_shards.p[i];
+  a.gathered = w_full; a.ready = ready; a.status = status;
+  a.rank_bytes = static_cast<int64_t>(K / world) * N * 2;
+  a.block_bytes = static_cast<int64_t>(BK) * N * 2;
+  a.ready_target = static_cast<int>(a.block_bytes / kPieceBytes);
+  launch<MODE_AGB, true>(tA, tB, tC, a, num_sms, stream);
 }
 
 void tp_reduce_slots(const void* staging, void* y, int slots, int64_t slot_elems, cudaStream_t stream) {

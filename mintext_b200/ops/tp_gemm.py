@@ -193,3 +193,63 @@ def linear_rs(x: torch.Tensor, weight: torch.Tensor, tp) -> torch.Tensor:
     ws = tp.comm()
     x2 = x if x.is_contiguous() else x.contiguous()
     return _LinearRSFn.apply(x2, weight, ws, getattr(weight, "main_grad", None))
+
+
+# ---------------------------------------------------------------------------------------------- sharded weights
+class ShardedWeight:
+    """A ``[K, N]`` kernel stored 1/world per rank (rows ``[r*K/w, (r+1)*K/w)``) in symmetric memory, for fully
+    sharded data parallelism without a resident full copy.  ``fsdp_linear`` gathers it inside the GEMM kernel:
+    the gather warps pull the peers' rows over NVLink while the main loop starts on this rank's own k-blocks.
+
+    The reference gets this overlap from XLA's async all-gather + latency-hiding scheduler
+    (mintext/utils/xla_flags.py:15-31) on ``fsdp``-sharded kernels (mintext/distributed/sharding.py:33-47)."""
+
+    def __init__(self, full: torch.Tensor, group, device):
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        K, N = full.shape
+        if K % (64 * self.world) != 0 or N % 128 != 0:
+            raise ValueError("ShardedWeight needs K % (64 * world) == 0 and N % 128 == 0")
+        self.shape = (K, N)
+        self.device = torch.device(device)
+        rows = K // self.world
+        self.shard = symm.empty((rows, N), dtype=torch.bfloat16, device=self.device)
+        self.shard.copy_(full[self.rank * rows:(self.rank + 1) * rows].to(self.device, torch.bfloat16))
+        self.shard.requires_grad_(True)
+        self._handle = symm.rendezvous(self.shard, group)
+        self.ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        self.ready = torch.zeros(K // 64, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)  # every shard is in place; callers barrier again after they update shards
+
+
+class _FsdpLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, shard, sw):
+        K, N = sw.shape
+        w_full = torch.empty(K, N, dtype=torch.bfloat16, device=x.device)
+        y = torch.empty(x.shape[0], N, dtype=torch.bfloat16, device=x.device)
+        sw.ready.zero_()
+        ext().fsdp_gemm_agw(x, sw.ptrs, w_full, y, sw.rank, sw.ready, status_word(x.device))
+        ctx.save_for_backward(x, w_full)
+        ctx.sw = sw
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w_full = ctx.saved_tensors
+        sw = ctx.sw
+        dy = dy.contiguous()
+        dx = _gemm(dy, w_full, torch.empty_like(x), False, False)
+        dw_full = _gemm(x, dy, torch.empty(sw.shape, dtype=torch.float32, device=x.device), True, True)
+        dw = torch.empty(sw.shape[0] // sw.world, sw.shape[1], dtype=torch.float32, device=x.device)
+        dist.reduce_scatter_tensor(dw, dw_full, group=sw.group)
+        return dx, dw.to(torch.bfloat16), None
+
+
+def fsdp_linear(x: torch.Tensor, sw: ShardedWeight) -> torch.Tensor:
+    """``x [T, K] @ W [K, N]`` with ``W`` all-gathered from its row shards inside the GEMM kernel."""
+    x2 = x if x.is_contiguous() else x.contiguous()
+    return _FsdpLinearFn.apply(x2, sw.shard, sw)

@@ -52,6 +52,28 @@ def op_level(dev, rank, world):
             outs[name] = [xg.detach(), a.detach(), b.detach(), y.detach(), xx.grad, wl[0].grad, wl[1].grad, wol.grad]
         for i, key in enumerate(("gathered", "col0", "col1", "row", "dx", "dw0", "dw1", "dwo")):
             errs[key] = max(errs.get(key, 0.0), _rel(outs["fused"][i], outs["plain"][i]))
+    # fully sharded weight: gather inside the GEMM vs an explicit all-gather + matmul
+    from mintext_b200.ops import tp_gemm
+
+    gw = torch.Generator().manual_seed(11)
+    K, N, T = 256 * world, 384, 640
+    w = (torch.randn(K, N, generator=gw) / 16).to(torch.bfloat16)
+    sw = tp_gemm.ShardedWeight(w, dist.group.WORLD, dev)
+    for trial in range(2):
+        x = (torch.randn(T, K, generator=g) * 0.5).to(dev, torch.bfloat16).requires_grad_(True)
+        y = tp_gemm.fsdp_linear(x, sw)
+        (y.float() ** 2).sum().backward()
+        xr = x.detach().clone().requires_grad_(True)
+        wr = w.to(dev).float().requires_grad_(True)
+        yr = xr.float() @ wr
+        (yr ** 2).sum().backward()
+        dwr = wr.grad.clone()
+        dist.all_reduce(dwr)
+        rows = K // world
+        errs["fsdp_y"] = max(errs.get("fsdp_y", 0.0), _rel(y, yr))
+        errs["fsdp_dx"] = max(errs.get("fsdp_dx", 0.0), _rel(x.grad, xr.grad))
+        errs["fsdp_dw"] = max(errs.get("fsdp_dw", 0.0), _rel(sw.shard.grad, dwr[rank * rows:(rank + 1) * rows]))
+        sw.shard.grad = None
     return errs
 
 

@@ -118,6 +118,7 @@ def test_tensor_parallel_fused_kernels(tmp_path):
     assert res["ops"]["gathered"] == 0.0, res["ops"]
     for key, err in res["ops"].items():
         assert err < 2e-2, res["ops"]
+    assert "fsdp_y" in res["ops"]  # weight all-gather folded into the GEMM (fully sharded parameters)
     single = _single_gpu_losses()
     for name in ("fused", "nccl"):
         for a, b in zip(res[name]["losses"], single):
