@@ -17,8 +17,8 @@ sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 def tp_config(fused: bool, tp: int):
     from mintext_b200 import MinTextConfig
 
-    return MinTextConfig(num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
-                         intermediate_size=512, vocab_size=1024, seq_length=128, steps=20, learning_rate=1e-3,
+    return MinTextConfig(num_hidden_layers=2, hidden_size=512, num_attention_heads=8, num_key_value_heads=8, head_dim=64,
+                         intermediate_size=1024, vocab_size=1024, seq_length=128, steps=20, learning_rate=1e-3,
                          enable_tensorboard=False, enable_checkpointing=False, fused_collectives=fused,
                          ici_tensor_parallelism=tp)
 
@@ -91,6 +91,7 @@ def main(out_path: str) -> None:
     world = dist.get_world_size()
     results = {"ops": op_level(dev, rank, world)}
     check_status(dev)
+    assert results["ops"]["gathered"] == 0.0 and all(v < 2e-2 for v in results["ops"].values()), results["ops"]
     g = torch.Generator().manual_seed(7)
     tok = torch.randint(0, 1024, (8, 128), generator=g).to(dev)  # one tensor-parallel group: all ranks share the batch
     for name, fused in (("fused", True), ("nccl", False)):

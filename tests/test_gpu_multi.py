@@ -119,7 +119,17 @@ def test_tensor_parallel_fused_kernels(tmp_path):
     for key, err in res["ops"].items():
         assert err < 2e-2, res["ops"]
     assert "fsdp_y" in res["ops"]  # weight all-gather folded into the GEMM (fully sharded parameters)
-    single = _single_gpu_losses()
+    sys.path.insert(0, str(ROOT / "tests"))
+    from multi_gpu_tp_worker import tp_config
+
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.engine import TrainEngine
+
+    cfg = tp_config(True, 1)
+    eng = TrainEngine(Transformer(cfg, rngs=0), cfg, device="cuda")
+    tok = torch.randint(0, 1024, (8, 128), generator=torch.Generator().manual_seed(7)).cuda()
+    single = [float(eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=1)["loss"]) for _ in range(5)]
+    eng.check()
     for name in ("fused", "nccl"):
         for a, b in zip(res[name]["losses"], single):
             assert abs(a - b) < 3e-2, (name, res[name]["losses"], single)
