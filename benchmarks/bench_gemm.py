@@ -39,6 +39,7 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--tokens", type=int, default=32768)
     ap.add_argument("--only", default="", help="run only shapes whose name contains this string")
+    ap.add_argument("--pair", action="store_true", help="time the CTA-pair (cta_group::2) kernel next to the 1-CTA one")
     ap.add_argument("--fp8", action="store_true", help="time the FP8 GEMM instead (ratio is against cuBLAS bf16)")
     args = ap.parse_args()
     from mintext_b200.ops._ext import check_status, ext, status_word
@@ -71,6 +72,14 @@ def main():
             # wgrad    dW += x^T @ dy     : A = x stored [contraction=M, K] -> MN-major, B = dy stored [M, N]
             "wgrad": (lambda: e.gemm(x, dy, dw, True, True, True, st), lambda: torch.matmul(x.t(), dy, out=dw_b)),
         }
+        if args.pair:  # CTA-pair kernel (cta_group::2) on the forward / data-gradient layouts
+            cases = {
+                "fwd_pair": (lambda: e.gemm_pair(x, w_kn, y, True, st), lambda: torch.matmul(x, w_kn, out=y)),
+                "fwd_1cta": (lambda: e.gemm(x, w_kn, y, False, True, False, st), lambda: torch.matmul(x, w_kn, out=y)),
+                "dgrad_pair": (lambda: e.gemm_pair(dy, w_kn, dx, False, st), lambda: torch.matmul(dy, w_kn.t(), out=dx)),
+                "dgrad_1cta": (lambda: e.gemm(dy, w_kn, dx, False, False, False, st),
+                               lambda: torch.matmul(dy, w_kn.t(), out=dx)),
+            }
         if args.fp8:  # FP8 GEMM alone (pre-quantised operands) and the whole fp8 linear (amax + quantise + GEMM)
             xq, _, sx = e.fp8_quantize(x, False, True, False)
             _, wqt, sw = e.fp8_quantize(w_kn, True, False, True)

@@ -295,6 +295,18 @@ void ep_pull_rows(torch::Tensor& out, const torch::Tensor& src_rank, const torch
                    (int)out.size(1), cap_rows, cur_stream());
 }
 
+// c[M,N] = a[M,K] @ (b_kn ? b[K,N] : b[N,K]^T) on CTA pairs (bf16 in / out)
+void gemm_pair(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& c, bool b_kn, torch::Tensor& status) {
+  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16 && c.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && c.stride(1) == 1);
+  const int64_t M = a.size(0), K = a.size(1), N = b_kn ? b.size(1) : b.size(0);
+  TORCH_CHECK((b_kn ? b.size(0) : b.size(1)) == K && c.size(0) == M && c.size(1) == N);
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && c.stride(0) % 8 == 0 && K % 8 == 0 && N % 8 == 0);
+  c10::cuda::CUDAGuard guard(a.device());
+  mt::gemm_bf16_pair(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0), c.stride(0),
+                     b_kn, status.data_ptr<int>(), sm_count(), cur_stream());
+}
+
 // -> (q uint8 [R,C] or undefined, qt uint8 [C,R] or undefined, scale fp32 [1])
 std::vector<torch::Tensor> fp8_quantize(const torch::Tensor& x, bool e5m2, bool want_q, bool want_qt) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16);
@@ -501,6 +513,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_wgrad", &grouped_wgrad);
   m.def("ep_push_rows", &ep_push_rows);
   m.def("ep_pull_rows", &ep_pull_rows);
+  m.def("gemm_pair", &gemm_pair);
   m.def("fp8_quantize", &fp8_quantize);
   m.def("gemm_fp8", &gemm_fp8);
   m.def("conv1d_silu_fwd", &conv1d_silu_fwd);

@@ -1,0 +1,321 @@
+// Dense bf16 GEMM on CTA pairs (tcgen05 cta_group::2):  C[M,N] = A[M,K] * op(B), bf16 out, fp32 accumulate.
+//
+// Two CTAs of a 2-CTA cluster (two SMs of one TPC) work on one 256x256 output tile.  Each CTA stages its own 128
+// rows of A and its own 128 columns of B per k-block (32 KB per stage instead of the 48 KB a lone CTA needs for a
+// 128x256 tile, so the ring is six deep and the L2 -> shared-memory traffic per FLOP drops by a third); one thread of
+// the leader CTA issues tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 16), which reads A from each CTA's own
+// shared memory and the two halves of B from both, and accumulates 128 rows x 256 columns into each CTA's own
+// tensor memory.  Protocol:
+//   * both producers wait on their own `empty` barrier and issue TMA loads whose completion bytes land on the
+//     LEADER's `full` barrier (cta_group::2 load form with the peer bit of the barrier address cleared);
+//     the leader's producer posts the expected byte count of both CTAs;
+//   * the leader's MMA thread waits on `full`, issues the MMAs, and commits with a cluster-wide arrive on both CTAs'
+//     `empty` barriers (tcgen05.commit .multicast::cluster: an mbarrier arrive, not a data multicast) and, after
+//     the last k-block, on both CTAs' `tmem_full`;
+//   * the epilogue warps of both CTAs drain their own TMEM half and arrive on the leader's `tmem_empty` (remote
+//     mbarrier arrive for the follower).
+// No TMA load uses multicast.  Every wait is bounded; the only unbounded synchronisation is the pair of cluster
+// barriers at start and end, which every thread reaches on every path.
+#include "../common/ptx.cuh"
+#include "../common/tmap.h"
+#include "../api.h"
+
+namespace mt {
+namespace {
+
+constexpr int BM = 128;        // rows per CTA (256 per pair)
+constexpr int BN = 256;        // columns per pair tile; each CTA stages BN/2 columns of B
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kEpiWarps = 4;
+constexpr int kThreads = 32 * (2 + kEpiWarps);
+constexpr int kEpiStageBytes = 4096;
+constexpr int kStages = 6;
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address -> rank 0
+
+struct PCfg {
+  static constexpr int A_BYTES = BM * BK * 2;           // 16 KB
+  static constexpr int B_BYTES = (BN / 2) * BK * 2;     // 16 KB
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_BYTES = kEpiWarps * 2 * kEpiStageBytes;
+  static constexpr int OFF_EPI = kStages * STAGE_BYTES;
+  static constexpr int OFF_BAR = OFF_EPI + EPI_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA tile load of a CTA pair: data into this CTA's shared memory, completion bytes on the barrier at the same
+// offset in CTA rank 0.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar) & kPeerBitMask), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+  const uint32_t z = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(z)
+      : "memory");
+}
+// mbarrier arrive on the barrier at the same offset in both CTAs once this thread's MMAs have completed.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(mask)
+      : "memory");
+}
+// arrive on the barrier at the same offset in CTA rank 0 of the cluster
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, 0;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+      ::"r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// Pair-tile order: groups of 8 column tiles, rows fastest inside a group.
+__device__ __forceinline__ void tile_coord(int tile, int num_m, int num_n, int& m_idx, int& n_idx) {
+  const int per_group = 8 * num_m;
+  const int group = tile / per_group;
+  const int first_n = group * 8;
+  const int gsize = min(8, num_n - first_n);
+  const int local = tile - group * per_group;
+  m_idx = local / gsize;
+  n_idx = first_n + local % gsize;
+}
+
+template <bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int* status) {
+  using C = PCfg;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* epi_base = smem + C::OFF_EPI;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint64_t* full_bar = bars;                   // [kStages]  used in the leader only
+  uint64_t* empty_bar = bars + kStages;        // [kStages]  one per CTA
+  uint64_t* tmem_full = bars + 2 * kStages;    // [2]        one per CTA
+  uint64_t* tmem_empty = tmem_full + 2;        // [2]        used in the leader only (8 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_m = (M + 2 * BM - 1) / (2 * BM);
+  const int num_n = (N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + BK - 1) / BK;
+  const bool aligned = (smem_u32(smem) & 1023u) == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 2 * kEpiWarps);
+    }
+    *abort_flag = aligned ? 0 : 1;
+    if (!aligned && status) atomicCAS(status, 0, MT_ERR_BAD_ARGS);
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    prefetch_tmap(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrive or load completion
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (one per CTA)
+    if (lane == 0 && aligned) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int m_idx, n_idx;
+        tile_coord(tile, num_m, num_n, m_idx, n_idx);
+        const int row0 = m_idx * (2 * BM) + rank * BM;          // this CTA's rows of A
+        const int col0 = n_idx * BN + rank * (BN / 2);          // this CTA's columns of B
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, status, MT_ERR_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + s * C::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + C::A_BYTES;
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);  // bytes of both CTAs
+          const int k0 = kb * BK;
+          tma_load_2d_pair(a_dst, &tmA, &full_bar[s], k0, row0);
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int a = 0; a < (BN / 2) / 64; ++a)
+              tma_load_2d_pair(b_dst + a * (BK * 128), &tmB, &full_bar[s], col0 + a * 64, k0);
+          } else {
+            tma_load_2d_pair(b_dst, &tmB, &full_bar[s], k0, col0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && leader && aligned) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, false, B_MN);
+      int it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
+        const int buf = tcount & 1;
+        if (!mbar_wait(&tmem_empty[buf], ((tcount >> 1) & 1) ^ 1, abort_flag, status, MT_ERR_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          if (!mbar_wait(&full_bar[s], (it / kStages) & 1, abort_flag, status, MT_ERR_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc_sw128(a_addr + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(b_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                                     : make_smem_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
+            tc_mma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit_pair(&empty_bar[s]);  // both CTAs' slots reusable once these MMAs have read them
+        }
+        if (ok) tc_commit_pair(&tmem_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    uint8_t* stage0 = epi_base + (warp - 2) * 2 * kEpiStageBytes;
+    int tcount = 0, nstores = 0;
+    for (int tile = pair; tile < num_tiles && aligned; tile += num_pairs, ++tcount) {
+      int m_idx, n_idx;
+      tile_coord(tile, num_m, num_n, m_idx, n_idx);
+      const int buf = tcount & 1;
+      if (!mbar_wait_warp(&tmem_full[buf], (tcount >> 1) & 1, abort_flag, status, MT_ERR_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after_sync();
+      const int row0 = m_idx * (2 * BM) + rank * BM + q * 32;
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      for (int c = 0; c < BN / 64; ++c) {
+        const int col0 = n_idx * BN + c * 64;
+        if (col0 >= N) break;
+        uint8_t* sbuf = stage0 + (nstores & 1) * kEpiStageBytes;
+        if (lane == 0) tma_wait_group_read<1>();
+        __syncwarp();
+        uint8_t* srow = sbuf + lane * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_lane + c * 64 + h * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            *reinterpret_cast<uint4*>(srow + (((h * 4 + j) ^ (lane & 7)) << 4)) = v;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (row0 < M) tma_store_2d(&tmC, sbuf, col0, row0);
+          tma_commit_group();
+        }
+        ++nstores;
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&tmem_empty[buf]);  // this warp has drained its part of the accumulator
+    }
+    if (lane == 0) tma_wait_group<0>();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer may still be signalling this CTA's barriers or reading its shared memory
+  if (warp == 1) {
+    tc_fence_after_sync();
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+  }
+}
+
+template <bool B_MN>
+void launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, int M, int N, int K, int* status,
+                 int num_sms, cudaStream_t stream) {
+  auto kern = gemm_bf16_pair_kernel<B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    MT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PCfg::SMEM_BYTES));
+    configured = true;
+  }
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  const int pairs = tiles < num_sms / 2 ? tiles : num_sms / 2;
+  kern<<<2 * pairs, kThreads, PCfg::SMEM_BYTES, stream>>>(tA, tB, tC, M, N, K, status);
+  MT_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace
+
+// A: [M,K] row pitch lda (K-major).  B: K-major [N,K] (ldb) or MN-major [K,N] (ldb).  C: bf16 [M,N] row pitch ldc.
+void gemm_bf16_pair(const void* A, const void* B, void* Cout, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                    bool b_mn_major, int* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return;
+  const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  CUtensorMap tA = make_tmap_2d(A, bf, 2, M, K, lda, BM, BK, sw);
+  CUtensorMap tB = b_mn_major ? make_tmap_2d(B, bf, 2, K, N, ldb, BK, 64, sw) : make_tmap_2d(B, bf, 2, N, K, ldb, BN / 2, BK, sw);
+  CUtensorMap tC = make_tmap_2d(Cout, bf, 2, M, N, ldc, 32, 64, sw);
+  if (b_mn_major) launch_pair<true>(tA, tB, tC, M, N, K, status, num_sms, stream);
+  else launch_pair<false>(tA, tB, tC, M, N, K, status, num_sms, stream);
+}
+
+}  // namespace mt

@@ -58,6 +58,21 @@ def test_gemm_fp32_out_and_accumulate(accumulate):
     assert _rel_err(c, ref) < 1e-5
 
 
+@pytest.mark.parametrize("M,N,K,b_kn", [(256, 256, 64, False), (512, 768, 320, True), (384, 520, 1024, False),
+                                         (4096, 2048, 2048, True)])
+def test_gemm_on_cta_pairs(M, N, K, b_kn):
+    """cta_group::2 kernel (256x256 tiles on two SMs) against the fp32 product, ragged edges included."""
+    torch.manual_seed(4)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    B = b.t().contiguous() if b_kn else b
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    _ext().gemm_pair(a, B, c, b_kn, _status())
+    _check()
+    assert _rel_err(c, ref) < 1e-2
+
+
 def test_gemm_weight_gradient_layout_with_split_k():
     """x^T dy accumulated into fp32 with few output tiles and a long contraction: the launcher splits K."""
     torch.manual_seed(3)
