@@ -75,10 +75,8 @@ def main():
         if args.pair:  # CTA-pair kernel (cta_group::2) on the forward / data-gradient layouts
             cases = {
                 "fwd_pair": (lambda: e.gemm_pair(x, w_kn, y, True, st), lambda: torch.matmul(x, w_kn, out=y)),
-                "fwd_1cta": (lambda: e.gemm(x, w_kn, y, False, True, False, st), lambda: torch.matmul(x, w_kn, out=y)),
+                "wgrad_auto": (lambda: e.gemm(x, dy, dw, True, True, True, st), lambda: torch.matmul(x.t(), dy, out=dw_b)),
                 "dgrad_pair": (lambda: e.gemm_pair(dy, w_kn, dx, False, st), lambda: torch.matmul(dy, w_kn.t(), out=dx)),
-                "dgrad_1cta": (lambda: e.gemm(dy, w_kn, dx, False, False, False, st),
-                               lambda: torch.matmul(dy, w_kn.t(), out=dx)),
             }
         if args.fp8:  # FP8 GEMM alone (pre-quantised operands) and the whole fp8 linear (amax + quantise + GEMM)
             xq, _, sx = e.fp8_quantize(x, False, True, False)

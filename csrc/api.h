@@ -106,9 +106,10 @@ void tp_reduce_slots(const void* staging, void* y, int slots, int64_t slot_elems
 void fsdp_gemm_agw(const void* A, const PeerPtrs& w_shards, void* w_full, void* C, int T, int N, int K, int rank,
                    int world, int* ready, int* status, int num_sms, cudaStream_t stream);
 
-// ---- gemm/dense_bf16_2cta.cu: the same product on CTA pairs (tcgen05 cta_group::2, 256x256 tiles); A K-major, bf16 out
+// ---- gemm/dense_bf16_2cta.cu: the same product on CTA pairs (tcgen05 cta_group::2, 256x256 tiles), same operand rules
 void gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-                    bool b_mn_major, int* status, int num_sms, cudaStream_t stream);
+                    bool a_mn_major, bool b_mn_major, bool out_f32, bool accumulate, int* status, int num_sms,
+                    cudaStream_t stream);
 
 // ---- gemm/fp8_gemm.cu: per-tensor-scaled FP8 GEMM (both operands K-major) and its quantisation kernels
 void fp8_amax(const void* x_bf16, int64_t n, float* amax, cudaStream_t stream);

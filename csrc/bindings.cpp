@@ -304,7 +304,7 @@ void gemm_pair(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& c,
   TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && c.stride(0) % 8 == 0 && K % 8 == 0 && N % 8 == 0);
   c10::cuda::CUDAGuard guard(a.device());
   mt::gemm_bf16_pair(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0), c.stride(0),
-                     b_kn, status.data_ptr<int>(), sm_count(), cur_stream());
+                     false, b_kn, false, false, status.data_ptr<int>(), sm_count(), cur_stream());
 }
 
 // -> (q uint8 [R,C] or undefined, qt uint8 [C,R] or undefined, scale fp32 [1])

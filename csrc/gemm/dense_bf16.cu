@@ -13,6 +13,7 @@
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
 #include "../api.h"
+#include <cstdlib>
 
 namespace mt {
 namespace {
@@ -330,6 +331,15 @@ void gemm_bf16(const void* A, const void* B, void* Cout, int M, int N, int K, in
                int64_t ldc, bool a_mn_major, bool b_mn_major, bool out_f32, bool accumulate, int* status,
                int num_sms, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return;
+  // Two-SM tiles (256x256 per CTA pair) wherever a whole pair tile is useful; the single-CTA kernel keeps narrow
+  // outputs and short row counts.  MT_GEMM_SINGLE_CTA=1 forces the single-CTA kernel (for comparisons).
+  static const bool single_only = [] {
+    const char* e = std::getenv("MT_GEMM_SINGLE_CTA");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (!single_only && M > 128 && N > 128)
+    return gemm_bf16_pair(A, B, Cout, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, out_f32, accumulate, status,
+                          num_sms, stream);
   const int BN = (N <= 128) ? 128 : 256;
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;

@@ -1,4 +1,5 @@
-// Dense bf16 GEMM on CTA pairs (tcgen05 cta_group::2):  C[M,N] = A[M,K] * op(B), bf16 out, fp32 accumulate.
+// Dense bf16 GEMM on CTA pairs (tcgen05 cta_group::2):  C[M,N] (+)= op(A) * op(B), fp32 accumulation, bf16 or fp32
+// out, each operand K-major or MN-major, optional split-K with the accumulating (TMA reduce-add) epilogue.
 //
 // Two CTAs of a 2-CTA cluster (two SMs of one TPC) work on one 256x256 output tile.  Each CTA stages its own 128
 // rows of A and its own 128 columns of B per k-block (32 KB per stage instead of the 48 KB a lone CTA needs for a
@@ -110,10 +111,11 @@ __device__ __forceinline__ void tile_coord(int tile, int num_m, int num_n, int& 
   n_idx = first_n + local % gsize;
 }
 
-template <bool B_MN>
+template <bool A_MN, bool B_MN, bool OUT_F32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int* status) {
+                      const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int accumulate, int splits,
+                      int* status) {
   using C = PCfg;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* epi_base = smem + C::OFF_EPI;
@@ -135,6 +137,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int num_n = (N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (K + BK - 1) / BK;
+  const int num_items = num_tiles * splits;  // split-K: item = split * num_tiles + tile
   const bool aligned = (smem_u32(smem) & 1023u) == 0;
 
   if (threadIdx.x == 0) {
@@ -168,12 +171,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     if (lane == 0 && aligned) {
       int it = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      for (int item = pair; item < num_items && ok; item += num_pairs) {
+        const int split = item / num_tiles;
         int m_idx, n_idx;
-        tile_coord(tile, num_m, num_n, m_idx, n_idx);
+        tile_coord(item - split * num_tiles, num_m, num_n, m_idx, n_idx);
         const int row0 = m_idx * (2 * BM) + rank * BM;          // this CTA's rows of A
         const int col0 = n_idx * BN + rank * (BN / 2);          // this CTA's columns of B
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb_lo = static_cast<int>(static_cast<int64_t>(split) * num_kb / splits);
+        const int kb_hi = static_cast<int>(static_cast<int64_t>(split + 1) * num_kb / splits);
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, status, MT_ERR_TIMEOUT_EMPTY)) {
@@ -184,7 +190,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           uint8_t* b_dst = a_dst + C::A_BYTES;
           if (leader) mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);  // bytes of both CTAs
           const int k0 = kb * BK;
-          tma_load_2d_pair(a_dst, &tmA, &full_bar[s], k0, row0);
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int a = 0; a < BM / 64; ++a) tma_load_2d_pair(a_dst + a * (BK * 128), &tmA, &full_bar[s], row0 + a * 64, k0);
+          } else {
+            tma_load_2d_pair(a_dst, &tmA, &full_bar[s], k0, row0);
+          }
           if constexpr (B_MN) {
 #pragma unroll
             for (int a = 0; a < (BN / 2) / 64; ++a)
@@ -198,15 +209,18 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && leader && aligned) {
-      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, false, B_MN);
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
       int it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
+      for (int item = pair; item < num_items && ok; item += num_pairs, ++tcount) {
+        const int split = item / num_tiles;
+        const int kb_lo = static_cast<int>(static_cast<int64_t>(split) * num_kb / splits);
+        const int kb_hi = static_cast<int>(static_cast<int64_t>(split + 1) * num_kb / splits);
         const int buf = tcount & 1;
         if (!mbar_wait(&tmem_empty[buf], ((tcount >> 1) & 1) ^ 1, abort_flag, status, MT_ERR_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % kStages;
           if (!mbar_wait(&full_bar[s], (it / kStages) & 1, abort_flag, status, MT_ERR_TIMEOUT_FULL)) {
             ok = false;
@@ -217,10 +231,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           const uint32_t b_addr = a_addr + C::A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = make_smem_desc_sw128(a_addr + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t da = A_MN ? make_smem_desc_sw128(a_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                                     : make_smem_desc_sw128(a_addr + k * (UMMA_K * 2), 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc_sw128(b_addr + k * (UMMA_K * 128), BK * 128, 1024)
                                      : make_smem_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
-            tc_mma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            tc_mma_f16_pair(d_tmem, da, db, idesc, ((kb - kb_lo) | k) != 0 ? 1u : 0u);
           }
           tc_commit_pair(&empty_bar[s]);  // both CTAs' slots reusable once these MMAs have read them
         }
@@ -230,42 +245,57 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
     const int q = warp & 3;
+    constexpr int COLS = OUT_F32 ? 32 : 64;  // columns per 128-byte staging row
     uint8_t* stage0 = epi_base + (warp - 2) * 2 * kEpiStageBytes;
     int tcount = 0, nstores = 0;
-    for (int tile = pair; tile < num_tiles && aligned; tile += num_pairs, ++tcount) {
+    for (int item = pair; item < num_items && aligned; item += num_pairs, ++tcount) {
       int m_idx, n_idx;
-      tile_coord(tile, num_m, num_n, m_idx, n_idx);
+      tile_coord(item % num_tiles, num_m, num_n, m_idx, n_idx);
       const int buf = tcount & 1;
       if (!mbar_wait_warp(&tmem_full[buf], (tcount >> 1) & 1, abort_flag, status, MT_ERR_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after_sync();
       const int row0 = m_idx * (2 * BM) + rank * BM + q * 32;
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-      for (int c = 0; c < BN / 64; ++c) {
-        const int col0 = n_idx * BN + c * 64;
+      for (int c = 0; c < BN / COLS; ++c) {
+        const int col0 = n_idx * BN + c * COLS;
         if (col0 >= N) break;
         uint8_t* sbuf = stage0 + (nstores & 1) * kEpiStageBytes;
         if (lane == 0) tma_wait_group_read<1>();
         __syncwarp();
         uint8_t* srow = sbuf + lane * 128;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        if constexpr (OUT_F32) {
           uint32_t r[32];
-          tmem_ld_32x32b_x32(t_lane + c * 64 + h * 32, r);
+          tmem_ld_32x32b_x32(t_lane + c * 32, r);
           tc_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-            *reinterpret_cast<uint4*>(srow + (((h * 4 + j) ^ (lane & 7)) << 4)) = v;
+          for (int j = 0; j < 8; ++j) {
+            uint4 v = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            *reinterpret_cast<uint4*>(srow + ((j ^ (lane & 7)) << 4)) = v;
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_lane + c * 64 + h * 32, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              *reinterpret_cast<uint4*>(srow + (((h * 4 + j) ^ (lane & 7)) << 4)) = v;
+            }
           }
         }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (row0 < M) tma_store_2d(&tmC, sbuf, col0, row0);
+          if (row0 < M) {
+            if (accumulate) tma_reduce_add_2d(&tmC, sbuf, col0, row0);
+            else tma_store_2d(&tmC, sbuf, col0, row0);
+          }
           tma_commit_group();
         }
         ++nstores;
@@ -288,34 +318,66 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 }
 
-template <bool B_MN>
-void launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, int M, int N, int K, int* status,
-                 int num_sms, cudaStream_t stream) {
-  auto kern = gemm_bf16_pair_kernel<B_MN>;
+template <bool A_MN, bool B_MN, bool OUT_F32>
+void launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, int M, int N, int K, bool accumulate,
+                 int* status, int num_sms, cudaStream_t stream) {
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, OUT_F32>;
   static bool configured = false;
   if (!configured) {
     MT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PCfg::SMEM_BYTES));
     configured = true;
   }
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
-  const int pairs = tiles < num_sms / 2 ? tiles : num_sms / 2;
-  kern<<<2 * pairs, kThreads, PCfg::SMEM_BYTES, stream>>>(tA, tB, tC, M, N, K, status);
+  const int max_pairs = num_sms / 2;
+  // split K when the pair tiles fill the last wave badly and the epilogue adds into C anyway (weight gradients)
+  int splits = 1;
+  if (OUT_F32 && accumulate) {
+    const int num_kb = (K + BK - 1) / BK;
+    auto eff = [&](int sp) {
+      const int items = tiles * sp;
+      return static_cast<double>(items) / (static_cast<double>((items + max_pairs - 1) / max_pairs) * max_pairs);
+    };
+    double best = eff(1);
+    for (int sp = 2; sp <= 6; ++sp) {
+      if (num_kb / sp < 16) break;
+      if (eff(sp) > best + 0.08) {
+        best = eff(sp);
+        splits = sp;
+      }
+    }
+  }
+  const int items = tiles * splits;
+  const int pairs = items < max_pairs ? items : max_pairs;
+  kern<<<2 * pairs, kThreads, PCfg::SMEM_BYTES, stream>>>(tA, tB, tC, M, N, K, accumulate ? 1 : 0, splits, status);
   MT_CUDA_CHECK(cudaGetLastError());
 }
 
 }  // namespace
 
-// A: [M,K] row pitch lda (K-major).  B: K-major [N,K] (ldb) or MN-major [K,N] (ldb).  C: bf16 [M,N] row pitch ldc.
+// A: K-major [M,K] or MN-major [K,M] (row pitch lda); B: K-major [N,K] or MN-major [K,N] (ldb); C: [M,N] (ldc), bf16
+// or fp32; accumulate -> C += result (TMA element-wise add).
 void gemm_bf16_pair(const void* A, const void* B, void* Cout, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-                    bool b_mn_major, int* status, int num_sms, cudaStream_t stream) {
+                    bool a_mn_major, bool b_mn_major, bool out_f32, bool accumulate, int* status, int num_sms,
+                    cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return;
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
-  CUtensorMap tA = make_tmap_2d(A, bf, 2, M, K, lda, BM, BK, sw);
+  CUtensorMap tA = a_mn_major ? make_tmap_2d(A, bf, 2, K, M, lda, BK, 64, sw) : make_tmap_2d(A, bf, 2, M, K, lda, BM, BK, sw);
   CUtensorMap tB = b_mn_major ? make_tmap_2d(B, bf, 2, K, N, ldb, BK, 64, sw) : make_tmap_2d(B, bf, 2, N, K, ldb, BN / 2, BK, sw);
-  CUtensorMap tC = make_tmap_2d(Cout, bf, 2, M, N, ldc, 32, 64, sw);
-  if (b_mn_major) launch_pair<true>(tA, tB, tC, M, N, K, status, num_sms, stream);
-  else launch_pair<false>(tA, tB, tC, M, N, K, status, num_sms, stream);
+  CUtensorMap tC = out_f32 ? make_tmap_2d(Cout, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, 32, sw)
+                           : make_tmap_2d(Cout, bf, 2, M, N, ldc, 32, 64, sw);
+#define MT_PAIR_CASE(AM, BMJ, F32)                                \
+  if (a_mn_major == AM && b_mn_major == BMJ && out_f32 == F32)    \
+    return launch_pair<AM, BMJ, F32>(tA, tB, tC, M, N, K, accumulate, status, num_sms, stream);
+  MT_PAIR_CASE(false, false, false)
+  MT_PAIR_CASE(false, true, false)
+  MT_PAIR_CASE(true, false, false)
+  MT_PAIR_CASE(true, true, false)
+  MT_PAIR_CASE(false, false, true)
+  MT_PAIR_CASE(false, true, true)
+  MT_PAIR_CASE(true, false, true)
+  MT_PAIR_CASE(true, true, true)
+#undef MT_PAIR_CASE
 }
 
 }  // namespace mt
