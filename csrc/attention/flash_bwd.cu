@@ -19,7 +19,9 @@
 // the staging slab of the TMA reduce-add.  The multi-head-latent shape (192-wide queries / keys, 128-wide values)
 // uses 32-query steps; its dQ^T needs 192 lanes, so it is produced as two M = 128 groups over head dims 0..127 and
 // 64..191 (the second one's upper 64 lanes are the new dims), each 64 columns wide (the upper 32 are never read).
-// Roles: warps 0-3 softmax/epilogue, warp 4 TMA producer, warp 5 MMA issuer.  All mbarrier waits are bounded.
+// Roles: eight softmax / epilogue warps (two per 32-key lane quarter of tensor memory, each taking half of the step's
+// query columns, so that every scheduler has two of them to overlap latencies; four for the 32-query MLA steps),
+// then one TMA producer warp and one MMA issuer warp.  All mbarrier waits are bounded.
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
 #include <type_traits>
@@ -29,7 +31,6 @@ namespace mt {
 namespace {
 
 constexpr int BKV = 128;  // keys per CTA
-constexpr int kThreads = 192;
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int DQK, int DV>
@@ -44,8 +45,12 @@ struct BwdCfg {
   static constexpr int DO_BYTES = BQ * DV * 2;
   static constexpr int PT_BYTES = BKV * DQ_N * 2;   // rows of P^T / dS^T are at least one 128-byte span
   static constexpr int DST_BYTES = BKV * DQ_N * 2;
-  static constexpr int DQ_STAGE_BYTES = 4 * 2 * 4096;  // per warp: 2 boxes of 32 rows x 128 B
-  static constexpr int STAT_BYTES = 4 * 2 * BQ * 4;    // per softmax warp: lse[128] | delta[128]
+  static constexpr int SOFT_WARPS = BQ >= 64 ? 8 : 4;
+  static constexpr int GROUPS = SOFT_WARPS / 4;        // column halves per key-row quarter
+  static constexpr int THREADS = 32 * (SOFT_WARPS + 2);
+  static constexpr int DQ_STAGE_BYTES = 4 * 2 * 4096;  // eight boxes of 32 rows x 128 B, shared out over the warps
+  static constexpr int SLAB_BYTES = DQ_STAGE_BYTES / SOFT_WARPS;
+  static constexpr int STAT_BYTES = SOFT_WARPS * 2 * BQ * 4;  // per softmax warp: lse[BQ] | delta[BQ]
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + K_BYTES;
   static constexpr int OFF_Q = OFF_V + V_BYTES;           // 2 stages of (Q | dO)
@@ -71,7 +76,7 @@ struct BwdArgs {
 };
 
 template <int DQK, int DV, bool CAP>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((BwdCfg<DQK, DV>::THREADS), 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
@@ -124,12 +129,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&qdo_empty[s], 1);
     }
     mbar_init(st_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, C::SOFT_WARPS);
     mbar_init(mma2_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) {
+  constexpr int kTmaWarp = C::SOFT_WARPS, kMmaWarp = C::SOFT_WARPS + 1;
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -138,7 +144,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(kv_full, C::K_BYTES + C::V_BYTES);
@@ -163,7 +169,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tma_load_3d(q_dst + C::Q_BYTES + x * (BQ * 128), &tmDO, &qdo_full[s], x * 64, h, tok0 + q0);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BKV, BQ, false, false);     // S^T, dP^T
@@ -248,12 +254,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------------ softmax backward (thread = key row)
-    const int r = threadIdx.x;
+    const int wq = warp & 3;    // lane quarter of tensor memory = 32-key block of this warp
+    const int grp = warp >> 2;  // which part of the step's query columns (and of the drain / epilogue boxes)
+    const int r = wq * 32 + lane;
     const int kidx = key0 + r;
-    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(wq * 32) << 16);
     const float sc = args.scale;
     const float cap = args.softcap;
-    uint8_t* dq_stage = dq_s + warp * (2 * 4096);
+    uint8_t* dq_stage = dq_s + warp * C::SLAB_BYTES;
     bool ok = true;
 
     auto drain_dq = [&](int t_prev) {
@@ -265,10 +273,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // dQ partial: TMEM lanes = query rows; this warp owns rows warp*32 .. +31, boxes of 32 dims
 #pragma unroll
         for (int c = 0; c < DQK / 32; ++c) {
+          if (C::GROUPS == 2 && c != grp) continue;  // one box per warp
           uint32_t v[32];
           tmem_ld_32x32b_x32(t_row + C::COL_DQ + c * 32, v);
           tc_wait_ld();
-          uint8_t* srow = dq_stage + c * 4096 + lane * 128;
+          uint8_t* srow = dq_stage + (C::GROUPS == 2 ? 0 : c * 4096) + lane * 128;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             uint4 w = make_uint4(__float_as_uint(__uint_as_float(v[4 * g]) * sc),
@@ -282,8 +291,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         __syncwarp();
         if (lane == 0) {
 #pragma unroll
-          for (int c = 0; c < DQK / 32; ++c)
-            tma_reduce_add_3d(&tmDQ, dq_stage + c * 4096, c * 32, h, tok0 + q0 + warp * 32);
+          for (int c = 0; c < DQK / 32; ++c) {
+            if (C::GROUPS == 2 && c != grp) continue;
+            tma_reduce_add_3d(&tmDQ, dq_stage + (C::GROUPS == 2 ? 0 : c * 4096), c * 32, h, tok0 + q0 + wq * 32);
+          }
           tma_commit_group();
         }
       } else {
@@ -292,13 +303,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         int box = 0;
 #pragma unroll
         for (int g = 0; g < C::DQ_GROUPS; ++g) {
-          if (g > 0 && warp < 2) continue;  // lanes 0..63 of a later group repeat dims of the previous one
+          if (g > 0 && wq < 2) continue;  // lanes 0..63 of a later group repeat dims of the previous one
 #pragma unroll
           for (int c = 0; c < BQ / 32; ++c, ++box) {
+            if (C::GROUPS == 2 && c != grp) continue;  // one box per warp
             uint32_t v[32];
             tmem_ld_32x32b_x32(t_row + C::COL_DQ + g * C::DQ_N + c * 32, v);
             tc_wait_ld();
-            uint8_t* bx = dq_stage + box * 4096 + (lane & 3) * 4;
+            uint8_t* bx = dq_stage + (C::GROUPS == 2 ? 0 : box * 4096) + (lane & 3) * 4;
 #pragma unroll
             for (int q = 0; q < 32; ++q)
               *reinterpret_cast<float*>(bx + q * 128 + (((lane >> 2) ^ (q & 7)) << 4)) = __uint_as_float(v[q]) * sc;
@@ -310,10 +322,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           box = 0;
 #pragma unroll
           for (int g = 0; g < C::DQ_GROUPS; ++g) {
-            if (g > 0 && warp < 2) continue;
+            if (g > 0 && wq < 2) continue;
 #pragma unroll
-            for (int c = 0; c < BQ / 32; ++c, ++box)
-              tma_reduce_add_3d(&tmDQ, dq_stage + box * 4096, 64 * g + warp * 32, h, tok0 + q0 + c * 32);
+            for (int c = 0; c < BQ / 32; ++c, ++box) {
+              if (C::GROUPS == 2 && c != grp) continue;
+              tma_reduce_add_3d(&tmDQ, dq_stage + (C::GROUPS == 2 ? 0 : box * 4096), 64 * g + wq * 32, h,
+                                tok0 + q0 + c * 32);
+            }
           }
           tma_commit_group();
         }
@@ -341,7 +356,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto score_block = [&](auto mask_tag, int q0) {
       constexpr bool MASK = decltype(mask_tag)::value;
 #pragma unroll
-      for (int c = 0; c < BQ / 32; ++c) {
+      for (int cc = 0; cc < (BQ / 32) / C::GROUPS; ++cc) {
+        const int c = grp * ((BQ / 32) / C::GROUPS) + cc;  // this warp's share of the query columns
         uint32_t sv[32];
         uint32_t dv[32];
         tmem_ld_32x32b_x32(t_row + C::COL_ST + c * 32, sv);
@@ -439,18 +455,21 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       __syncwarp();
       // dV then dK: this warp's 32 key rows x DH dims (bf16) through its staging slab, one 64-dim box (32 rows of
       // 128 bytes) at a time; the slab holds two boxes
+      // with eight warps the first group writes dV and the second dK, each through its one-box slab
+      constexpr int kSlabBoxes = C::SLAB_BYTES / 4096;
       int boxes = 0;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
+        if (C::GROUPS == 2 && which != grp) continue;
         const int col = which == 0 ? C::COL_DV : C::COL_DK;
         const float osc = which == 0 ? 1.f : sc;
 #pragma unroll
         for (int half = 0; half < (which == 0 ? DV : DQK) / 64; ++half, ++boxes) {
-          if (boxes >= 2) {  // slab full: wait until the earlier boxes have been read out
+          if (boxes >= kSlabBoxes) {  // slab full: wait until the earlier boxes have been read out
             if (lane == 0) tma_wait_group_read<0>();
             __syncwarp();
           }
-          uint8_t* slab = dq_stage + (boxes & 1) * 4096;
+          uint8_t* slab = dq_stage + (boxes % kSlabBoxes) * 4096;
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             uint32_t v[32];
@@ -476,7 +495,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(which == 0 ? &tmDV : &tmDK, slab, half * 64, hk, tok0 + key0 + warp * 32);
+            tma_store_3d(which == 0 ? &tmDV : &tmDK, slab, half * 64, hk, tok0 + key0 + wq * 32);
             tma_commit_group();
           }
         }
@@ -487,7 +506,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after_sync();
     __syncwarp();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -584,9 +603,9 @@ void launch_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
   BwdArgs a{p.S, p.H, p.Hkv, p.causal, p.window, p.scale, p.softcap, p.lse, p.delta, p.status};
   dim3 grid(p.S / BKV, p.Hkv, p.B);
   if (p.softcap > 0.f)
-    flash_bwd_kernel<DQK, DV, true><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+    flash_bwd_kernel<DQK, DV, true><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
   else
-    flash_bwd_kernel<DQK, DV, false><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+    flash_bwd_kernel<DQK, DV, false><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
   MT_CUDA_CHECK(cudaGetLastError());
   bwd_finish_kernel<DQK><<<num_sms * 8, 256, 0, stream>>>(static_cast<const float*>(p.dq_accum),
                                                           static_cast<__nv_bfloat16*>(p.dq_out),
