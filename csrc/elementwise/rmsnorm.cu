@@ -215,6 +215,84 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] = dw_s[i];
 }
 
+// Column-owner variant for dim = 8 * blockDim.x (dim a multiple of 256, at most 8192): a block walks rows R at a time,
+// every thread owns the same 8 columns of every row, so its slice of the weight gradient stays in 8 registers with
+// no atomics, 2R 16-byte loads per thread are in flight, and the register count stays low enough for several
+// blocks per SM.  The per-row dot product is a block reduction (warp shuffle, then one shared-memory exchange per
+// R rows, double-buffered so one __syncthreads per iteration suffices).
+template <int R, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_bwd_col_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                       const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
+                       const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                       float* __restrict__ dw_partial, int64_t rows, int dim) {
+  __shared__ float part[2][R][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int vec = threadIdx.x;  // this thread's 16-byte chunk of every row
+  const float4 w0 = reinterpret_cast<const float4*>(w)[2 * vec];
+  const float4 w1 = reinterpret_cast<const float4*>(w)[2 * vec + 1];
+  const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+  float dw_r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const float inv_dim = 1.f / dim;
+  const int vecs_per_row = dim >> 3;
+  int it = 0;
+  for (int64_t row0 = (int64_t)blockIdx.x * R; row0 < rows; row0 += (int64_t)gridDim.x * R, ++it) {
+    Pack8 a[R], g[R];
+    float rs[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int64_t row = row0 + r;
+      if (row < rows) {
+        a[r].u = reinterpret_cast<const uint4*>(x)[row * vecs_per_row + vec];
+        g[r].u = reinterpret_cast<const uint4*>(dy)[row * vecs_per_row + vec];
+        rs[r] = rstd_in[row];
+      } else {
+        a[r].u = make_uint4(0, 0, 0, 0);
+        g[r].u = make_uint4(0, 0, 0, 0);
+        rs[r] = 0.f;
+      }
+    }
+    float dot[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float d = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = __bfloat162float(a[r].h[j]) * rs[r];
+        const float gy = __bfloat162float(g[r].h[j]);
+        d = fmaf(xh * gy, wv[j], d);
+        dw_r[j] = fmaf(gy, xh, dw_r[j]);
+      }
+      d = warp_sum(d);
+      if (lane == 0) part[it & 1][r][warp] = d;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float d = lane < nwarps ? part[it & 1][r][lane] : 0.f;
+      dot[r] = warp_sum(d) * inv_dim;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int64_t row = row0 + r;
+      if (row >= rows) continue;
+      Pack8 rr, o;
+      if (dres) rr.u = reinterpret_cast<const uint4*>(dres)[row * vecs_per_row + vec];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = __bfloat162float(a[r].h[j]) * rs[r];
+        float d = rs[r] * (__bfloat162float(g[r].h[j]) * wv[j] - xh * dot[r]);
+        if (dres) d += __bfloat162float(rr.h[j]);
+        o.h[j] = __float2bfloat16(d);
+      }
+      reinterpret_cast<uint4*>(dx)[row * vecs_per_row + vec] = o.u;
+    }
+  }
+  float* out = dw_partial + (int64_t)blockIdx.x * dim + vec * 8;
+  reinterpret_cast<float4*>(out)[0] = make_float4(dw_r[0], dw_r[1], dw_r[2], dw_r[3]);
+  reinterpret_cast<float4*>(out)[1] = make_float4(dw_r[4], dw_r[5], dw_r[6], dw_r[7]);
+}
+
 __global__ void rmsnorm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int dim,
                                           float* __restrict__ dw, int accumulate) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -245,7 +323,10 @@ void rmsnorm_bwd(const void* x, const float* w, const float* rstd, const void* d
   auto ob = (__nv_bfloat16*)dx;
   const int threads = kWarpsPerBlock * 32;
   const size_t smem = dim * sizeof(float);
-  if (dim == 2048) rmsnorm_bwd_reg_kernel<8><<<num_partials, threads, smem, stream>>>(xb, w, rstd, gb, rb, ob, dw_partial, rows);
+  if (dim % 256 == 0 && dim >= 1024 && dim <= 4096)  // up to 512 threads: four rows in flight per thread
+    rmsnorm_bwd_col_kernel<4, 512><<<num_partials, dim / 8, 0, stream>>>(xb, w, rstd, gb, rb, ob, dw_partial, rows, dim);
+  else if (dim % 256 == 0 && dim > 4096 && dim <= 8192)
+    rmsnorm_bwd_col_kernel<2, 1024><<<num_partials, dim / 8, 0, stream>>>(xb, w, rstd, gb, rb, ob, dw_partial, rows, dim);
   else if (dim == 1024) rmsnorm_bwd_reg_kernel<4><<<num_partials, threads, smem, stream>>>(xb, w, rstd, gb, rb, ob, dw_partial, rows);
   else if (dim == 512) rmsnorm_bwd_reg_kernel<2><<<num_partials, threads, smem, stream>>>(xb, w, rstd, gb, rb, ob, dw_partial, rows);
   else if (dim == 256) rmsnorm_bwd_reg_kernel<1><<<num_partials, threads, smem, stream>>>(xb, w, rstd, gb, rb, ob, dw_partial, rows);
@@ -300,11 +381,9 @@ extern "C" int mt_rmsnorm_bwd_noalloc(const void* x, const float* w, const float
   }
   if (rows == 0) return 0;
   float* partials = g_partials_addr[dev];
-  mt::rmsnorm_bwd_kernel<<<MT_RMSNORM_NOALLOC_PARTIALS, mt::kWarpsPerBlock * 32, dim * sizeof(float), stream>>>(
-      static_cast<const __nv_bfloat16*>(x), w, rstd, static_cast<const __nv_bfloat16*>(dy),
-      static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx), partials, rows, dim);
-  mt::rmsnorm_bwd_reduce_kernel<<<(dim + 255) / 256, 256, 0, stream>>>(partials, MT_RMSNORM_NOALLOC_PARTIALS, dim, dw,
-                                                                      accumulate_dw ? 1 : 0);
+  // same kernel selection as the ordinary entry point (bit-identical dx), with the built-in partial-sum array
+  mt::rmsnorm_bwd(x, w, rstd, dy, dres, dx, partials, MT_RMSNORM_NOALLOC_PARTIALS, rows, dim, stream);
+  mt::rmsnorm_bwd_reduce(partials, MT_RMSNORM_NOALLOC_PARTIALS, dim, dw, accumulate_dw != 0, stream);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(err, err_len, 8, cudaGetErrorString(e));
   return 0;
