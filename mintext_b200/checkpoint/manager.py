@@ -32,6 +32,10 @@ _NP_OF = {torch.float32: np.float32, torch.float64: np.float64, torch.float16: n
           torch.bfloat16: np.uint16}
 
 
+class CheckpointCorrupt(RuntimeError):
+    """A committed checkpoint whose files do not match its metadata."""
+
+
 def _rank() -> int:
     import torch.distributed as dist
 
@@ -210,10 +214,28 @@ class CheckpointManager:
             shutil.rmtree(self.directory / str(s), ignore_errors=True)
 
     # ---------------------------------------------------------------- restore
+    def verify(self, step: int) -> None:
+        """Raise :class:`CheckpointCorrupt` unless every file the step's metadata names exists with exactly the size
+        its shape and dtype imply (a truncated or partly copied checkpoint must not be loaded)."""
+        leaf_dir = self.directory / str(step) / "default"
+        try:
+            with open(leaf_dir / "_METADATA") as f:
+                meta = json.load(f)
+        except (OSError, ValueError) as e:
+            raise CheckpointCorrupt(f"step {step}: unreadable metadata ({e})") from e
+        for path, info in meta.items():
+            for leaf in info.get("chunks", [info] if "file" in info else []):
+                want = int(np.prod(leaf["shape"], dtype=np.int64)) * np.dtype(_NP_OF[getattr(torch, leaf["dtype"])]).itemsize
+                f = leaf_dir / leaf["file"]
+                have = f.stat().st_size if f.exists() else -1
+                if have != want:
+                    raise CheckpointCorrupt(f"step {step}: '{path}' file {leaf['file']} has {have} bytes, expected {want}")
+
     def restore(self, step: int, state) -> None:
         leaf_dir = self.directory / str(step) / "default"
         if not (self.directory / str(step) / _COMMIT).exists():
             raise FileNotFoundError(f"No committed checkpoint for step {step} in {self.directory}")
+        self.verify(step)
         with open(leaf_dir / "_METADATA") as f:
             meta = json.load(f)
 
@@ -278,9 +300,17 @@ def maybe_restore_checkpoint(manager: CheckpointManager | None, state, config, m
     or parameters only with ``load_params_only`` -> step 0); (3) ``load_hf_checkpoint`` (parameters, step 0);
     (4) start from scratch.  Returns ``(state, start_step)``."""
     if manager is not None and manager.latest_step() is not None:
-        state, step = restore_checkpoint(manager, state)
-        logger.info("Resuming from step %d", step)
-        return state, step
+        # newest first; a step whose files are damaged is skipped in favour of the one before it
+        for step in reversed(manager.all_steps()):
+            try:
+                manager.verify(step)
+            except CheckpointCorrupt as e:
+                logger.warning("Skipping damaged checkpoint: %s", e)
+                continue
+            state, step = restore_checkpoint(manager, state, step)
+            logger.info("Resuming from step %d", step)
+            return state, step
+        raise CheckpointCorrupt(f"every checkpoint in {manager.directory} is damaged")
     if config.load_checkpoint:
         src = CheckpointManager(config.load_checkpoint, read_only=True)
         step = src.latest_step()

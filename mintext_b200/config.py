@@ -220,6 +220,11 @@ class MinTextConfig(BaseModel):
     dcn_tensor_parallelism: int = 1
     num_slices: int = 1
     jax_distributed_init_timeout: int = 300
+    # failure detection (none of this exists in the reference): peer heartbeats over the job's store, checked before
+    # every step (0 = off), and what to do with a NaN / Inf loss: ignore | skip | abort
+    heartbeat_interval: float = 0.0
+    heartbeat_timeout: float = 60.0
+    nan_policy: str = "ignore"
     logical_axis_rules: list[tuple[str, str | None]] = []
     fused_collectives: bool = True  # peer-memory kernels for the sharded optimizer step; False: NCCL composition
 

@@ -392,13 +392,22 @@ class TrainEngine:
             if aux.get("moe_expert_counts") is not None:
                 counts = aux["moe_expert_counts"] if counts is None else counts + aux["moe_expert_counts"]
         pnorm = self.param_norm()
-        out = self.optimizer_step(n)
         loss_mean = loss_sum / n
         if self.world > 1:
             dist.all_reduce(loss_mean, group=self.group)
             loss_mean /= self.world
             if counts is not None:
                 dist.all_reduce(counts, group=self.group)
+        if cfg.nan_policy != "ignore":
+            from mintext_b200.parallel.health import apply_nan_policy
+
+            # the all-reduced loss is the same on every rank, so all ranks take the same decision
+            if apply_nan_policy(cfg.nan_policy, float(loss_mean), self.step_count):
+                self.zero_grad()
+                return {"loss": loss_mean, "param_norm": pnorm, "moe_expert_counts": None, "z_loss": aux["z_loss"],
+                        "grad_norm": torch.full((), float("nan"), device=self.device),
+                        "learning_rate": float(self.schedule(self.step_count)), "skipped": True}
+        out = self.optimizer_step(n)
         out.update({"loss": loss_mean, "param_norm": pnorm, "moe_expert_counts": counts, "z_loss": aux["z_loss"]})
         return out
 

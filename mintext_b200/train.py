@@ -111,12 +111,23 @@ def train(config: MinTextConfig) -> dict:
         if train_iter is None:
             _make_synthetic_batch(config, gen, rows, torch.device("cpu"))
 
+    heartbeat = None
+    if config.heartbeat_interval > 0 and world > 1:
+        import torch.distributed as dist
+
+        from mintext_b200.parallel.health import Heartbeat
+
+        heartbeat = Heartbeat(dist.distributed_c10d._get_default_store(), rank, world, config.heartbeat_interval,
+                              config.heartbeat_timeout)
+        heartbeat.wait_all_alive(config.jax_distributed_init_timeout)
     last = {}
     ev0 = ev1 = None
     if use_gpu:
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for step in range(start_step, config.steps):
         profiler.maybe_activate(step)
+        if heartbeat is not None:
+            heartbeat.check()  # a dead peer becomes an exception here, not a hang in the step's first collective
         t0 = time.time()
         if train_iter is not None:
             nb = next(train_iter)
@@ -165,6 +176,8 @@ def train(config: MinTextConfig) -> dict:
         if config.steps not in manager.all_steps() and config.steps > start_step:
             save_checkpoint(manager, config.steps, state, force=True)
         wait_for_checkpoint(manager)
+    if heartbeat is not None:
+        heartbeat.close()
     profiler.stop()
     metric_logger.close()
     if train_iter is not None:

@@ -188,9 +188,16 @@ def train_step(state: TrainState, batch, model, config):
     grad_norm = _l2_norm(grads.values())
     param_norm = _l2_norm(state.params.values())
     lr = create_lr_schedule(config)(state.step)
-    state.tx.update(trainable, grads, state.opt_state, state.step)
-    state.step += 1
+    skipped = False
+    if getattr(config, "nan_policy", "ignore") != "ignore":
+        from mintext_b200.parallel.health import apply_nan_policy
+
+        skipped = apply_nan_policy(config.nan_policy, float(loss), state.step)
+    if not skipped:
+        state.tx.update(trainable, grads, state.opt_state, state.step)
+        state.step += 1
     metrics = {
+        "skipped": skipped,
         "loss": loss,
         "z_loss": aux["z_loss"],
         "learning_rate": lr,
