@@ -23,6 +23,7 @@ from mintext_b200.modules.mla import MLAttention
 from mintext_b200.modules.moe import MoEBlock
 from mintext_b200.modules.norm import RMSNorm
 from mintext_b200.ops import functional as F
+from mintext_b200.utils.profiling import nvtx_range
 from mintext_b200.ops.oracle import causal_mask
 
 _QKV = frozenset({"query_proj", "key_proj", "value_proj"})
@@ -224,11 +225,12 @@ class Transformer(nn.Module):
         all_aux = []
         pending = None
         fuse = REMAT_POLICIES[self.remat_policy] is None or not torch.is_grad_enabled()
-        for layer in self.layers:
-            if fuse:  # carry the last residual add into the next norm kernel
-                x, aux, pending = layer(x, positions, mask, default_positions, pending=pending, defer_residual=True)
-            else:
-                x, aux = apply_layer_with_remat(layer, x, positions, mask, self.remat_policy, default_positions)
+        for li, layer in enumerate(self.layers):
+            with nvtx_range(f"layer{li}"):
+                if fuse:  # carry the last residual add into the next norm kernel
+                    x, aux, pending = layer(x, positions, mask, default_positions, pending=pending, defer_residual=True)
+                else:
+                    x, aux = apply_layer_with_remat(layer, x, positions, mask, self.remat_policy, default_positions)
             all_aux.append(aux)
         if pending is not None:
             x, _ = self.final_norm.forward_add(pending, x)

@@ -32,6 +32,7 @@ import torch.distributed as dist
 
 from mintext_b200.ops._ext import check_status, ext
 from mintext_b200.optim.optimizer import create_lr_schedule, weight_decay_mask
+from mintext_b200.utils.profiling import nvtx_range
 
 _ALIGN = 64  # elements; keeps every parameter view 128-byte aligned for TMA
 
@@ -407,7 +408,8 @@ class TrainEngine:
                 return {"loss": loss_mean, "param_norm": pnorm, "moe_expert_counts": None, "z_loss": aux["z_loss"],
                         "grad_norm": torch.full((), float("nan"), device=self.device),
                         "learning_rate": float(self.schedule(self.step_count)), "skipped": True}
-        out = self.optimizer_step(n)
+        with nvtx_range("optimizer_step"):
+            out = self.optimizer_step(n)
         out.update({"loss": loss_mean, "param_norm": pnorm, "moe_expert_counts": counts, "z_loss": aux["z_loss"]})
         return out
 

@@ -11,6 +11,32 @@ from pathlib import Path
 
 logger = logging.getLogger(__name__)
 
+_NVTX = False
+
+
+class nvtx_range:
+    """NVTX range around a model region (per decoder layer, loss, optimizer step), emitted only while the profiler
+    window is open on a CUDA device so that the steady-state loop pays nothing."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self.on = False
+
+    def __enter__(self):
+        if _NVTX:
+            import torch
+
+            torch.cuda.nvtx.range_push(self.name)
+            self.on = True
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            import torch
+
+            torch.cuda.nvtx.range_pop()
+        return False
+
 
 class Profiler:
     def __init__(self, config):
@@ -39,6 +65,8 @@ class Profiler:
         self._prof = torch.profiler.profile(activities=acts)
         self._prof.__enter__()
         self.active = True
+        global _NVTX
+        _NVTX = torch.cuda.is_available()
         logger.info("Profiler started, writing to %s", self.output_dir)
 
     def stop(self) -> None:
@@ -51,4 +79,6 @@ class Profiler:
             logger.warning("could not export trace: %s", e)
         self._prof = None
         self.active = False
+        global _NVTX
+        _NVTX = False
         logger.info("Profiler stopped")

@@ -135,3 +135,36 @@ def test_tensor_parallel_fused_kernels(tmp_path):
             assert abs(a - b) < 3e-2, (name, res[name]["losses"], single)
     for a, b in zip(res["fused"]["losses"], res["nccl"]["losses"]):
         assert abs(a - b) < 1e-2
+
+
+def test_checkpoint_saved_on_two_gpus_restores_on_one(tmp_path):
+    """Resharding: the flat optimizer state written as one chunk per rank by a 2-GPU run restores into a 1-GPU
+    engine (a different shard layout), and training continues with the same losses."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    out = tmp_path / "ck.json"
+    ckpt = tmp_path / "ckpt"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29675", str(ROOT / "tests" / "multi_gpu_ckpt_worker.py"),
+           str(ckpt), str(out)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.loads(out.read_text())
+    sys.path.insert(0, str(ROOT / "tests"))
+    from multi_gpu_ckpt_worker import ckpt_config, global_batch
+
+    from mintext_b200.checkpoint.manager import create_checkpoint_manager, maybe_restore_checkpoint
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.engine import TrainEngine
+
+    cfg = ckpt_config(str(ckpt))
+    eng = TrainEngine(Transformer(cfg, rngs=123), cfg, device="cuda")  # different init: everything must come from disk
+    eng, step = maybe_restore_checkpoint(create_checkpoint_manager(cfg), eng, cfg)
+    assert step == 3 and eng.step_count == 3
+    tok = global_batch().cuda()
+    got = [float(eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=1)["loss"]) for _ in range(3)]
+    eng.check()
+    for a, b in zip(got, res["after"]):
+        assert abs(a - b) < 2e-2, (got, res["after"])
