@@ -125,6 +125,15 @@ void conv1d_silu_fwd(const void* x, const void* w, void* y, int B, int S, int C,
 void conv1d_silu_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, int B, int S, int C, int K,
                      cudaStream_t stream);
 
+// ---- gdn/gdn_scan.cu: inter-chunk state recurrence of the chunked Gated Delta Rule (fp32, chunk length 64).
+// Per (batch*head, chunk): W, QG, KD [64, dk]; U, O, dO, dU [64, dv]; M [64, 64]; GL scalar; Sstart [dk, dv].
+bool gdn_scan_supported(int dk, int dv);
+void gdn_scan_fwd(const float* W, const float* U, const float* QG, const float* M, const float* KD, const float* GL,
+                  float* O, float* Sstart, int BH, int C, int dk, int dv, cudaStream_t stream);
+void gdn_scan_bwd(const float* W, const float* U, const float* QG, const float* M, const float* KD, const float* GL,
+                  const float* Sstart, const float* dO, float* dW, float* dU, float* dQG, float* dM, float* dKD,
+                  float* dGL, int BH, int C, int dk, int dv, cudaStream_t stream);
+
 // ---- moe/route.cu
 void router_sigmoid_group(const void* logits, bool logits_bf16, const float* bias, float* scores, int64_t* topk_idx,
                           float* topk_w, int N, int E, int top_k, int n_group, int topk_group, bool norm, float scaling,

@@ -336,6 +336,38 @@ torch::Tensor gemm_fp8(const torch::Tensor& a, const torch::Tensor& b, bool a_e5
   return out;
 }
 
+// W, QG, KD [BH, C, 64, dk]; U [BH, C, 64, dv]; M [BH, C, 64, 64]; GL [BH, C]  ->  (O [BH, C, 64, dv], Sstart [BH, C, dk, dv])
+std::vector<torch::Tensor> gdn_scan_fwd(const torch::Tensor& W, const torch::Tensor& U, const torch::Tensor& QG,
+                                        const torch::Tensor& M, const torch::Tensor& KD, const torch::Tensor& GL) {
+  for (const auto* t : {&W, &U, &QG, &M, &KD, &GL})
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == torch::kFloat32, "gdn_scan wants contiguous fp32");
+  const int64_t BH = W.size(0), C = W.size(1), dk = W.size(3), dv = U.size(3);
+  TORCH_CHECK(W.size(2) == 64 && M.size(2) == 64 && M.size(3) == 64 && mt::gdn_scan_supported((int)dk, (int)dv));
+  c10::cuda::CUDAGuard guard(W.device());
+  auto O = torch::empty_like(U);
+  auto S = torch::empty({BH, C, dk, dv}, W.options());
+  mt::gdn_scan_fwd(W.data_ptr<float>(), U.data_ptr<float>(), QG.data_ptr<float>(), M.data_ptr<float>(), KD.data_ptr<float>(),
+                   GL.data_ptr<float>(), O.data_ptr<float>(), S.data_ptr<float>(), (int)BH, (int)C, (int)dk, (int)dv,
+                   cur_stream());
+  return {O, S};
+}
+
+// -> (dW, dU, dQG, dM, dKD, dGL)
+std::vector<torch::Tensor> gdn_scan_bwd(const torch::Tensor& W, const torch::Tensor& U, const torch::Tensor& QG,
+                                        const torch::Tensor& M, const torch::Tensor& KD, const torch::Tensor& GL,
+                                        const torch::Tensor& S, const torch::Tensor& dO) {
+  TORCH_CHECK(dO.is_contiguous() && dO.scalar_type() == torch::kFloat32 && S.is_contiguous());
+  const int64_t BH = W.size(0), C = W.size(1), dk = W.size(3), dv = U.size(3);
+  c10::cuda::CUDAGuard guard(W.device());
+  auto dW = torch::zeros_like(W), dQG = torch::zeros_like(QG), dKD = torch::zeros_like(KD), dM = torch::zeros_like(M),
+       dGL = torch::zeros_like(GL), dU = torch::empty_like(U);
+  mt::gdn_scan_bwd(W.data_ptr<float>(), U.data_ptr<float>(), QG.data_ptr<float>(), M.data_ptr<float>(), KD.data_ptr<float>(),
+                   GL.data_ptr<float>(), S.data_ptr<float>(), dO.data_ptr<float>(), dW.data_ptr<float>(), dU.data_ptr<float>(),
+                   dQG.data_ptr<float>(), dM.data_ptr<float>(), dKD.data_ptr<float>(), dGL.data_ptr<float>(), (int)BH, (int)C,
+                   (int)dk, (int)dv, cur_stream());
+  return {dW, dU, dQG, dM, dKD, dGL};
+}
+
 torch::Tensor conv1d_silu_fwd(const torch::Tensor& x, const torch::Tensor& w) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 3 && x.scalar_type() == torch::kBFloat16);
   TORCH_CHECK(w.is_contiguous() && w.scalar_type() == torch::kBFloat16 && w.numel() % x.size(2) == 0);
@@ -516,6 +548,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_pair", &gemm_pair);
   m.def("fp8_quantize", &fp8_quantize);
   m.def("gemm_fp8", &gemm_fp8);
+  m.def("gdn_scan_fwd", &gdn_scan_fwd);
+  m.def("gdn_scan_bwd", &gdn_scan_bwd);
   m.def("conv1d_silu_fwd", &conv1d_silu_fwd);
   m.def("conv1d_silu_bwd", &conv1d_silu_bwd);
   m.def("moe_router", &moe_router);

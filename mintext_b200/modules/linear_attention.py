@@ -16,7 +16,7 @@ def chunk_gated_delta_rule(q, k, v, beta, g, chunk_size: int = 64):
     """q,k ``[B,H,S,dk]``, v ``[B,H,S,dv]``, beta,g ``[B,H,S]`` -> ``[B,H,S,dv]`` (fp32)."""
     from mintext_b200.ops import gdn
 
-    if gdn.cuda_path(q):
+    if gdn.cuda_path(q, v, chunk_size):
         return gdn.chunk_gated_delta_rule_cuda(q, k, v, beta, g, chunk_size)
     return oracle.chunk_gated_delta_rule(q, k, v, beta, g, chunk_size)
 
