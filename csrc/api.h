@@ -21,6 +21,11 @@ void grouped_gemm_bf16(const void* X, const void* W, void* Y, const int* offsets
 // Experts without rows are skipped (clear dW beforehand when not accumulating).
 void grouped_wgrad_bf16(const void* X, const void* G, void* dW, const int* offsets, int E, int M_cap, int N, int K,
                         bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream);
+// the same two products on CTA pairs (gemm/grouped_bf16_2cta.cu); the functions above route to these by default
+void grouped_gemm_bf16_pair(const void* X, const void* W, void* Y, const int* offsets, int E, int M_cap, int N, int K,
+                            bool w_mn_major, int* status, int num_sms, cudaStream_t stream);
+void grouped_wgrad_bf16_pair(const void* X, const void* G, void* dW, const int* offsets, int E, int M_cap, int N, int K,
+                             bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream);
 
 // ---- elementwise/rmsnorm.cu
 // y = (x [+ residual]) * rsqrt(mean(.^2) + eps) -> bf16, then * w(bf16-rounded).  If residual_out != null the

@@ -13,9 +13,18 @@
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
 #include "../api.h"
+#include <cstdlib>
 
 namespace mt {
 namespace {
+
+bool single_cta_only() {  // MT_GEMM_SINGLE_CTA=1 keeps the single-CTA kernels (for comparisons)
+  static const bool v = [] {
+    const char* e = std::getenv("MT_GEMM_SINGLE_CTA");
+    return e != nullptr && e[0] == '1';
+  }();
+  return v;
+}
 
 constexpr int BM = 128;
 constexpr int BN = 256;
@@ -297,6 +306,8 @@ void configure(Kern k) {
 void grouped_gemm_bf16(const void* X, const void* W, void* Y, const int* offsets, int E, int M_cap, int N, int K,
                        bool w_mn_major, int* status, int num_sms, cudaStream_t stream) {
   if (M_cap <= 0 || E <= 0) return;
+  if (!single_cta_only() && N > 128 && E <= 256)
+    return grouped_gemm_bf16_pair(X, W, Y, offsets, E, M_cap, N, K, w_mn_major, status, num_sms, stream);
   if (E > kMaxExperts) throw std::runtime_error("grouped_gemm_bf16: too many experts");
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
@@ -321,6 +332,8 @@ void grouped_gemm_bf16(const void* X, const void* W, void* Y, const int* offsets
 void grouped_wgrad_bf16(const void* X, const void* G, void* dW, const int* offsets, int E, int M_cap, int N, int K,
                         bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream) {
   if (M_cap <= 0 || E <= 0) return;
+  if (!single_cta_only() && N > 128 && K > 128 && E <= 256)
+    return grouped_wgrad_bf16_pair(X, G, dW, offsets, E, M_cap, N, K, out_f32, accumulate, status, num_sms, stream);
   if (E > kMaxExperts) throw std::runtime_error("grouped_wgrad_bf16: too many experts");
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
