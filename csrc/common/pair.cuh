@@ -32,6 +32,16 @@ __device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_d, uint64_t desc_a
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(z)
       : "memory");
 }
+__device__ __forceinline__ void tc_mma_f8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  const uint32_t z = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(z)
+      : "memory");
+}
 // mbarrier arrive on the barrier at the same offset in both CTAs once this thread's MMAs have completed.
 __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
   const uint16_t mask = 3;

@@ -10,8 +10,10 @@
 // e4m3 with 448/amax, weights to e5m2 with 57344/amax.
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
+#include "../common/pair.cuh"
 #include "../api.h"
 #include <cuda_fp8.h>
+#include <cstdlib>
 
 namespace mt {
 namespace {
@@ -199,6 +201,184 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 }
 
+
+// ---------------------------------------------------------------------------------------- CTA-pair version
+// Same product on a 2-CTA cluster (tcgen05 cta_group::2): 256x256 tile per pair, each CTA stages 128 rows of A and
+// 128 rows of B (32 KB per stage, six stages); protocol as in dense_bf16_2cta.cu.
+constexpr int kPairStages = 6;
+struct FPCfg {
+  static constexpr int A_BYTES = BM * BK, B_BYTES = (BN / 2) * BK, STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_BYTES = kEpiWarps * 2 * kEpiStageBytes;
+  static constexpr int OFF_EPI = kPairStages * STAGE_BYTES;
+  static constexpr int OFF_BAR = OFF_EPI + EPI_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int a_fmt, int b_fmt,
+                     const float* __restrict__ scale_a, const float* __restrict__ scale_b, int* status) {
+  using C = FPCfg;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* epi_base = smem + C::OFF_EPI;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint64_t* full_bar = bars;                        // leader only
+  uint64_t* empty_bar = bars + kPairStages;         // per CTA
+  uint64_t* tmem_full = bars + 2 * kPairStages;     // per CTA
+  uint64_t* tmem_empty = tmem_full + 2;             // leader only (8 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_m = (M + 2 * BM - 1) / (2 * BM);
+  const int num_n = (N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + BK - 1) / BK;
+  const bool aligned = (smem_u32(smem) & 1023u) == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 2 * kEpiWarps);
+    }
+    *abort_flag = aligned ? 0 : 1;
+    if (!aligned && status) atomicCAS(status, 0, MT_ERR_BAD_ARGS);
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    prefetch_tmap(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0 && aligned) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int m_idx, n_idx;
+        tile_coord(tile, num_m, num_n, m_idx, n_idx);
+        const int row0 = m_idx * (2 * BM) + rank * BM;
+        const int col0 = n_idx * BN + rank * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kPairStages;
+          if (!mbar_wait(&empty_bar[s], ((it / kPairStages) & 1) ^ 1, abort_flag, status, MT_ERR_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + s * C::STAGE_BYTES;
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);
+          tma_load_2d_pair(a_dst, &tmA, &full_bar[s], kb * BK, row0);
+          tma_load_2d_pair(a_dst + C::A_BYTES, &tmB, &full_bar[s], kb * BK, col0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader && aligned) {
+      const uint32_t idesc = make_idesc_f8(2 * BM, BN, a_fmt, b_fmt);
+      int it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
+        const int buf = tcount & 1;
+        if (!mbar_wait(&tmem_empty[buf], ((tcount >> 1) & 1) ^ 1, abort_flag, status, MT_ERR_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kPairStages;
+          if (!mbar_wait(&full_bar[s], (it / kPairStages) & 1, abort_flag, status, MT_ERR_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tc_mma_f8_pair(d_tmem, make_smem_desc_sw128(a_addr + k * UMMA_K, 16, 1024),
+                           make_smem_desc_sw128(b_addr + k * UMMA_K, 16, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit_pair(&empty_bar[s]);
+        }
+        if (ok) tc_commit_pair(&tmem_full[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint8_t* stage0 = epi_base + (warp - 2) * 2 * kEpiStageBytes;
+    const float out_scale = 1.f / (scale_a[0] * scale_b[0]);
+    int tcount = 0, nstores = 0;
+    for (int tile = pair; tile < num_tiles && aligned; tile += num_pairs, ++tcount) {
+      int m_idx, n_idx;
+      tile_coord(tile, num_m, num_n, m_idx, n_idx);
+      const int buf = tcount & 1;
+      if (!mbar_wait_warp(&tmem_full[buf], (tcount >> 1) & 1, abort_flag, status, MT_ERR_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after_sync();
+      const int row0 = m_idx * (2 * BM) + rank * BM + q * 32;
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      for (int c = 0; c < BN / 64; ++c) {
+        const int col0 = n_idx * BN + c * 64;
+        if (col0 >= N) break;
+        uint8_t* sbuf = stage0 + (nstores & 1) * kEpiStageBytes;
+        if (lane == 0) tma_wait_group_read<1>();
+        __syncwarp();
+        uint8_t* srow = sbuf + lane * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_lane + c * 64 + h * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]) * out_scale, __uint_as_float(r[8 * j + 1]) * out_scale);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * out_scale, __uint_as_float(r[8 * j + 3]) * out_scale);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * out_scale, __uint_as_float(r[8 * j + 5]) * out_scale);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * out_scale, __uint_as_float(r[8 * j + 7]) * out_scale);
+            *reinterpret_cast<uint4*>(srow + (((h * 4 + j) ^ (lane & 7)) << 4)) = v;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (row0 < M) tma_store_2d(&tmC, sbuf, col0, row0);
+          tma_commit_group();
+        }
+        ++nstores;
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&tmem_empty[buf]);
+    }
+    if (lane == 0) tma_wait_group<0>();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+  }
+}
+
 // ---------------------------------------------------------------------------------------- quantisation
 __global__ void amax_kernel(const __nv_bfloat16* __restrict__ x, int64_t n, float* __restrict__ amax) {
   float m = 0.f;
@@ -307,8 +487,26 @@ void gemm_fp8(const void* A, const void* B, void* Cout, int M, int N, int K, boo
   const auto u8 = CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
   CUtensorMap tA = make_tmap_2d(A, u8, 1, M, K, K, BM, BK, sw);
-  CUtensorMap tB = make_tmap_2d(B, u8, 1, N, K, K, BN, BK, sw);
   CUtensorMap tC = make_tmap_2d(Cout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, N, 32, 64, sw);
+  static const bool single_only = [] {
+    const char* e = std::getenv("MT_GEMM_SINGLE_CTA");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (!single_only && M > 128 && N > 128) {  // CTA pairs: each CTA loads half of the B tile
+    CUtensorMap tBh = make_tmap_2d(B, u8, 1, N, K, K, BN / 2, BK, sw);
+    static bool pair_configured = false;
+    if (!pair_configured) {
+      MT_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FPCfg::SMEM_BYTES));
+      pair_configured = true;
+    }
+    const int ptiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    const int pairs = ptiles < num_sms / 2 ? ptiles : num_sms / 2;
+    gemm_fp8_pair_kernel<<<2 * pairs, kThreads, FPCfg::SMEM_BYTES, stream>>>(tA, tBh, tC, M, N, K, a_e5m2 ? 1 : 0,
+                                                                            b_e5m2 ? 1 : 0, scale_a, scale_b, status);
+    MT_CUDA_CHECK(cudaGetLastError());
+    return;
+  }
+  CUtensorMap tB = make_tmap_2d(B, u8, 1, N, K, K, BN, BK, sw);
   static bool configured = false;
   if (!configured) {
     MT_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FCfg::SMEM_BYTES));

@@ -123,7 +123,10 @@ class MLP(nn.Module):
             _, (g, u) = tpm.column_linear(x.reshape(-1, D), [self.gate.kernel, self.up.kernel], self.tp, self.gate.dtype)
             h = F.gated_act(torch.cat([g, u], dim=-1), self.act_name)
             return tpm.row_linear(h, self.down.kernel, self.tp, self.gate.dtype).view(*lead, D)
-        if self.gate.use_fp8:
+        if self.gate.use_fp8 and self.act_name in oracle.ACT_CODES and \
+                F.fp8_kernel_path(x.reshape(-1, x.shape[-1]), self.gate.kernel):
+            h = F.gate_up_act_fp8(x, self.gate.kernel, self.up.kernel, self.act_name)
+        elif self.gate.use_fp8:
             h = oracle.activation(self.act_name)(self.gate(x)) * self.up(x)
         else:
             h = F.gate_up_act(x, self.gate.kernel, self.up.kernel, self.act_name, dtype=self.gate.dtype)

@@ -500,6 +500,58 @@ class _GateUpActFn(torch.autograd.Function):
         return dx, grads[0], grads[1], None, None, None, None
 
 
+class _GateUpActFp8Fn(torch.autograd.Function):
+    """FP8 version of the gated MLP front half: the activations are quantised once (e4m3), gate and up kernels are
+    quantised together (e5m2, one scale) so that ``x @ [Wg | Wu]`` is a single FP8 GEMM writing the ``[T, 2M]``
+    buffer the activation kernel reads, and the data gradient is a single FP8 GEMM over the ``2M`` columns; the
+    weight gradients stay bf16 GEMMs accumulating in fp32."""
+
+    @staticmethod
+    def forward(ctx, x, wg, wu, act_code, mg_g, mg_u):
+        e, st = ext(), status_word(x.device)
+        T, M = x.shape[0], wg.shape[1]
+        xq, _, sx = e.fp8_quantize(x, False, True, False)
+        wcat = torch.cat([wg, wu], dim=1)                      # [K, 2M]
+        wq, wqt, sw = e.fp8_quantize(wcat, True, True, True)   # [K, 2M] for the data gradient, [2M, K] for forward
+        buf = e.gemm_fp8(xq, wqt, False, True, sx, sw, st)     # [T, 2M]
+        out = torch.empty(T, M, device=x.device, dtype=torch.bfloat16)
+        e.gated_act_fwd(buf, out, act_code)
+        ctx.save_for_backward(x, buf, wq, sw)
+        ctx.meta = (act_code, mg_g, mg_u, wg.shape, wg.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, buf, wq, sw = ctx.saved_tensors
+        act_code, mg_g, mg_u, wshape, wdt = ctx.meta
+        e, st = ext(), status_word(x.device)
+        M = wshape[1]
+        dgu = torch.empty_like(buf)
+        e.gated_act_bwd(buf, dout.contiguous(), dgu, act_code)
+        dgq, _, sdg = e.fp8_quantize(dgu, True, True, False)
+        dx = e.gemm_fp8(dgq, wq, True, True, sdg, sw, st)      # dgu [T, 2M] . [Wg | Wu][K, 2M]^T
+        grads = []
+        for d, mg in ((dgu[:, :M], mg_g), (dgu[:, M:], mg_u)):
+            if mg is not None:
+                _gemm(x, d, mg.view(wshape), True, True, accumulate=True)
+                grads.append(None)
+            else:
+                dw = torch.empty(wshape, device=x.device, dtype=torch.float32)
+                grads.append(_gemm(x, d, dw, True, True).to(wdt))
+        return dx, grads[0], grads[1], None, None, None
+
+
+def gate_up_act_fp8(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, act: str) -> torch.Tensor:
+    """``act(x @ wg) * (x @ wu)`` through the FP8 GEMM (callers check :func:`fp8_kernel_path`)."""
+    lead, K = x.shape[:-1], wg.shape[0]
+    x2 = x.reshape(-1, K)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    out = _GateUpActFp8Fn.apply(x2, wg, wu, oracle.ACT_CODES[act], getattr(wg, "main_grad", None),
+                                getattr(wu, "main_grad", None))
+    return out.reshape(*lead, wg.shape[1])
+
+
 def gate_up_act(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, act: str, dtype: torch.dtype | None = None,
                 name: str = "mlp_gate_up") -> torch.Tensor:
     """Gated MLP front half, ``act(x @ wg) * (x @ wu)`` (mintext/modules/linear.py:218-225)."""

@@ -298,3 +298,28 @@ def test_fp8_gemm_matches_dequantised_reference(M, N, K):
     dw_ref = x.detach().float().t() @ dy.float()
     assert ((x.grad.float() - dx_ref).norm() / dx_ref.norm()).item() < 0.15   # two e5m2 operands
     assert ((w.grad.float() - dw_ref).norm() / dw_ref.norm()).item() < 1e-2
+
+
+def test_fp8_gated_mlp_front_half_matches_bf16_path():
+    """One FP8 GEMM for gate|up plus the activation kernel, against the bf16 kernels (values and gradients)."""
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops._ext import check_status
+
+    torch.manual_seed(5)
+    T, K, M = 512, 256, 384
+    x = torch.randn(T, K, device="cuda").bfloat16().requires_grad_(True)
+    wg = (torch.randn(K, M, device="cuda") * 0.06).bfloat16().requires_grad_(True)
+    wu = (torch.randn(K, M, device="cuda") * 0.06).bfloat16().requires_grad_(True)
+    h8 = F.gate_up_act_fp8(x, wg, wu, "silu")
+    g = torch.randn_like(h8)
+    h8.backward(g)
+    got = [h8.detach(), x.grad.clone(), wg.grad.clone(), wu.grad.clone()]
+    x.grad = wg.grad = wu.grad = None
+    h16 = F.gate_up_act(x, wg, wu, "silu")
+    h16.backward(g)
+    torch.cuda.synchronize()
+    check_status()
+    ref = [h16.detach(), x.grad, wg.grad, wu.grad]
+    # e5m2 weights keep two mantissa bits: the comparison is against the bf16 path, not against an exact FP8 oracle
+    for name, a, b, tol in zip(("h", "dx", "dwg", "dwu"), got, ref, (0.12, 0.25, 0.12, 0.12)):
+        assert _rel_err(a, b) < tol, (name, _rel_err(a, b))
