@@ -14,7 +14,7 @@
 namespace mt {
 namespace {
 
-constexpr int kRun = 32;       // tokens per thread run
+constexpr int kRun = 16;       // tokens per thread run
 constexpr int kWarps = 8;      // runs per block
 
 union Pack8 {
@@ -67,6 +67,7 @@ __global__ void conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, cons
       for (int i = 0; i < 8; ++i) win[j + 1][i] = 0.f;
   }
   const int s_end = min(s0 + kRun, S);
+#pragma unroll 4
   for (int s = s0; s < s_end; ++s) {
 #pragma unroll
     for (int j = 0; j < K - 1; ++j)
@@ -127,6 +128,7 @@ __global__ void conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, cons
     }
     const int s_run_end = min(s0 + kRun, S);
     const int s_last = s_run_end + (K - 1);  // dpre is needed K-1 tokens past the run for the run's last dx
+#pragma unroll 2
     for (int s = s0; s < s_last; ++s) {
 #pragma unroll
       for (int j = K - 1; j > 0; --j)
