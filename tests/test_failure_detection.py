@@ -135,3 +135,25 @@ def test_damaged_checkpoint_is_skipped_for_the_previous_one(tmp_path):
     (tmp_path / "1" / "default" / "_METADATA").write_text("{not json")
     with pytest.raises(CheckpointCorrupt):
         maybe_restore_checkpoint(mgr, trainer.create_train_state(Transformer(cfg, rngs=1), cfg), cfg)
+
+
+def _train_with_heartbeat_worker(rank, world):
+    import os
+    from pathlib import Path
+
+    from mintext_b200.config import load_config
+    from mintext_b200.train import train
+
+    root = Path(__file__).resolve().parents[1]
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    cfg = load_config([str(root / "configs" / "base.yml"), str(root / "configs" / "models" / "test-tiny.yml")],
+                      dict(steps=3, seq_length=16, per_device_batch_size=2, enable_tensorboard=False,
+                           enable_checkpointing=False, dtype="float32", weight_dtype="float32", kernel_backend="oracle",
+                           heartbeat_interval=0.05, heartbeat_timeout=5.0, nan_policy="abort",
+                           ici_fsdp_parallelism=world))
+    return train(cfg)["loss"]
+
+
+def test_training_loop_runs_with_heartbeats_on_gloo_ranks():
+    res = run_ranks(_train_with_heartbeat_worker, 2, 29643)
+    assert all(v == v for v in res.values())
