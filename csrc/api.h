@@ -172,5 +172,8 @@ struct AttnParams {
 };
 void flash_attn_fwd(const AttnParams& p, int num_sms, cudaStream_t stream);
 void flash_attn_bwd(const AttnParams& p, int num_sms, cudaStream_t stream);
+// main kernel of the head_dim-64 backward with pipelined 64-query steps (attention/flash_bwd_pipe64.cu); called by
+// flash_attn_bwd between its pre- and post-pass
+void flash_bwd_pipe64_main(const AttnParams& p, cudaStream_t stream);
 
 }  // namespace mt

@@ -26,6 +26,7 @@
 #include "../common/tmap.h"
 #include <type_traits>
 #include "../api.h"
+#include <cstdlib>
 
 namespace mt {
 namespace {
@@ -602,10 +603,18 @@ void launch_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
   }
   BwdArgs a{p.S, p.H, p.Hkv, p.causal, p.window, p.scale, p.softcap, p.lse, p.delta, p.status};
   dim3 grid(p.S / BKV, p.Hkv, p.B);
-  if (p.softcap > 0.f)
-    flash_bwd_kernel<DQK, DV, true><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
-  else
-    flash_bwd_kernel<DQK, DV, false><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+  static const bool pipelined = [] {  // MT_ATTN_BWD_PIPELINED=1 selects the software-pipelined head_dim-64 kernel
+    const char* e = std::getenv("MT_ATTN_BWD_PIPELINED");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (DQK == 64 && DV == 64 && pipelined) {
+    flash_bwd_pipe64_main(p, stream);  // software-pipelined 64-query steps (flash_bwd_pipe64.cu)
+  } else {
+    if (p.softcap > 0.f)
+      flash_bwd_kernel<DQK, DV, true><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+    else
+      flash_bwd_kernel<DQK, DV, false><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+  }
   MT_CUDA_CHECK(cudaGetLastError());
   bwd_finish_kernel<DQK><<<num_sms * 8, 256, 0, stream>>>(static_cast<const float*>(p.dq_accum),
                                                           static_cast<__nv_bfloat16*>(p.dq_out),
