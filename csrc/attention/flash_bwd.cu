@@ -603,9 +603,9 @@ void launch_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
   }
   BwdArgs a{p.S, p.H, p.Hkv, p.causal, p.window, p.scale, p.softcap, p.lse, p.delta, p.status};
   dim3 grid(p.S / BKV, p.Hkv, p.B);
-  static const bool pipelined = [] {  // MT_ATTN_BWD_PIPELINED=1 selects the software-pipelined head_dim-64 kernel
+  static const bool pipelined = [] {  // MT_ATTN_BWD_PIPELINED=0 falls back to the 128-query-step kernel for head_dim 64
     const char* e = std::getenv("MT_ATTN_BWD_PIPELINED");
-    return e != nullptr && e[0] == '1';
+    return e == nullptr || e[0] != '0';
   }();
   if (DQK == 64 && DV == 64 && pipelined) {
     flash_bwd_pipe64_main(p, stream);  // software-pipelined 64-query steps (flash_bwd_pipe64.cu)
