@@ -150,6 +150,8 @@ flash_bwd_pipe64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       constexpr uint32_t idesc_g = make_idesc_bf16(BKV, DH, false, true);    // dV, dK : B = dO / Q as [K = q, N = dh]
       constexpr uint32_t idesc_q = make_idesc_bf16(BQ, DH, true, true);      // dQ : M = 64 queries, A = dS^T MN-major
       const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+      const uint64_t dk_km = make_smem_desc_sw128(k_addr, 16, 1024), dv_km = make_smem_desc_sw128(v_addr, 16, 1024);
+      const uint64_t dk_mn = make_smem_desc_sw128(k_addr, BKV * 128, 1024);
       bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, MT_ERR_TIMEOUT_FULL);
       auto issue_scores = [&](int t) -> bool {
         const int s = t % kQStages;
@@ -158,14 +160,14 @@ flash_bwd_pipe64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         const uint32_t q_addr = smem_u32(qdo_s + s * C::QDO_BYTES);
         const uint32_t do_addr = q_addr + C::Q_BYTES;
         const uint32_t col = (t & 1) * BQ;
+        // descriptors differ only in their 16-byte-granular start address (low bits): one add per MMA
+        const uint64_t dq = make_smem_desc_sw128(q_addr, 16, 1024), ddo = make_smem_desc_sw128(do_addr, 16, 1024);
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k)
-          tc_mma_f16(tmem_base + C::COL_ST + col, make_smem_desc_sw128(k_addr + k * 32, 16, 1024),
-                     make_smem_desc_sw128(q_addr + k * 32, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+          tc_mma_f16(tmem_base + C::COL_ST + col, dk_km + k * 2, dq + k * 2, idesc_s, k != 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k)
-          tc_mma_f16(tmem_base + C::COL_DPT + col, make_smem_desc_sw128(v_addr + k * 32, 16, 1024),
-                     make_smem_desc_sw128(do_addr + k * 32, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+          tc_mma_f16(tmem_base + C::COL_DPT + col, dv_km + k * 2, ddo + k * 2, idesc_s, k != 0 ? 1u : 0u);
         tc_commit(&st_full[t & 1]);
         return true;
       };
@@ -186,18 +188,18 @@ flash_bwd_pipe64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         const uint32_t do_addr = q_addr + C::Q_BYTES;
         const uint32_t pt_addr = smem_u32(pt_s + bsel * C::PT_BYTES);
         const uint32_t dst_addr = smem_u32(dst_s + bsel * C::PT_BYTES);
+        const uint64_t dpt = make_smem_desc_sw128(pt_addr, 16, 1024), dds = make_smem_desc_sw128(dst_addr, 16, 1024);
+        const uint64_t ddo_mn = make_smem_desc_sw128(do_addr, BQ * 128, 1024), dq_mn = make_smem_desc_sw128(q_addr, BQ * 128, 1024);
+        const uint64_t dds_mn = make_smem_desc_sw128(dst_addr, BKV * 128, 1024);
 #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k)  // dV += P^T dO : contraction over the 64 queries
-          tc_mma_f16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_addr + k * 32, 16, 1024),
-                     make_smem_desc_sw128(do_addr + k * (16 * 128), BQ * 128, 1024), idesc_g, (t | k) != 0 ? 1u : 0u);
+        for (int k = 0; k < BQ / 16; ++k)  // dV += P^T dO : contraction over the 64 queries (16 rows = 2048 B per step)
+          tc_mma_f16(tmem_base + C::COL_DV, dpt + k * 2, ddo_mn + k * 128, idesc_g, (t | k) != 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < BQ / 16; ++k)  // dK += dS^T Q
-          tc_mma_f16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_addr + k * 32, 16, 1024),
-                     make_smem_desc_sw128(q_addr + k * (16 * 128), BQ * 128, 1024), idesc_g, (t | k) != 0 ? 1u : 0u);
+          tc_mma_f16(tmem_base + C::COL_DK, dds + k * 2, dq_mn + k * 128, idesc_g, (t | k) != 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k)  // dQ = dS K : contraction over the 128 keys, M = 64 queries
-          tc_mma_f16(tmem_base + C::COL_DQ + bsel * DH, make_smem_desc_sw128(dst_addr + k * (16 * 128), BKV * 128, 1024),
-                     make_smem_desc_sw128(k_addr + k * (16 * 128), BKV * 128, 1024), idesc_q, k != 0 ? 1u : 0u);
+          tc_mma_f16(tmem_base + C::COL_DQ + bsel * DH, dds_mn + k * 128, dk_mn + k * 128, idesc_q, k != 0 ? 1u : 0u);
         tc_commit(&qdo_empty[s]);
         tc_commit(&mma2_done[bsel]);
       }
