@@ -1,5 +1,5 @@
-// Flash attention backward for sm_100a (bf16, head_dim 64 or 128, grouped-query K/V, causal / sliding window /
-// soft-cap).
+// Flash attention backward for sm_100a (bf16, head_dim 64, 128 or 256, the 192/128 multi-head-latent shape,
+// grouped-query K/V, causal / sliding window / soft-cap).
 //
 // One CTA = one (batch, kv head, 128-key block).  It keeps K_j and V_j in shared memory and dK_j, dV_j as fp32
 // accumulators in tensor memory while it walks over every query head of the group and every 128-row query
@@ -19,6 +19,8 @@
 // the staging slab of the TMA reduce-add.  The multi-head-latent shape (192-wide queries / keys, 128-wide values)
 // uses 32-query steps; its dQ^T needs 192 lanes, so it is produced as two M = 128 groups over head dims 0..127 and
 // 64..191 (the second one's upper 64 lanes are the new dims), each 64 columns wide (the upper 32 are never read).
+// head_dim 256 also uses 32-query steps and two dQ^T groups (dims 0..127, 128..255), and runs as two launches: one
+// that forms P^T and accumulates dV, one that forms dS^T and accumulates dK and dQ (see BwdCfg).
 // Roles: eight softmax / epilogue warps (two per 32-key lane quarter of tensor memory, each taking half of the step's
 // query columns, so that every scheduler has two of them to overlap latencies; four for the 32-query MLA steps),
 // then one TMA producer warp and one MMA issuer warp.  All mbarrier waits are bounded.
@@ -34,22 +36,29 @@ namespace {
 constexpr int BKV = 128;  // keys per CTA
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int DQK, int DV>
+// PASS: 0 = every gradient in one launch; 1 = dV only; 2 = dK and dQ only.  head_dim 256 runs as passes 1 and 2:
+// dK and dV alone (256 fp32 columns each) would fill tensor memory, and K, V, Q and dO tiles together leave no room
+// for both score staging buffers in shared memory.
+template <int DQK, int DV, int PASS = 0>
 struct BwdCfg {
+  static constexpr bool HAS_DV = PASS != 2;         // P^T staged, dV accumulated
+  static constexpr bool HAS_DK = PASS != 1;         // V loaded, dP^T / dS^T formed, dK and dQ accumulated
   static constexpr int BQ = DQK == 64 ? 128 : (DQK == 128 ? 64 : 32);  // query rows per step
   static constexpr bool DQ_T = DQK != 64;           // dQ accumulated transposed (head dims on TMEM lanes)
-  static constexpr int DQ_GROUPS = DQK == 192 ? 2 : 1;
+  static constexpr int DQ_GROUPS = DQK >= 192 ? 2 : 1;
+  static constexpr int DQ_GROUP_DIMS = DQK == 192 ? 64 : 128;  // first head dim of group g = g * DQ_GROUP_DIMS
   static constexpr int DQ_N = BQ < 64 ? 64 : BQ;    // columns per dQ^T group (one full 64-wide MN-major atom)
   static constexpr int K_BYTES = BKV * DQK * 2;
-  static constexpr int V_BYTES = BKV * DV * 2;
+  static constexpr int V_BYTES = HAS_DK ? BKV * DV * 2 : 0;
   static constexpr int Q_BYTES = BQ * DQK * 2;      // per stage
   static constexpr int DO_BYTES = BQ * DV * 2;
-  static constexpr int PT_BYTES = BKV * DQ_N * 2;   // rows of P^T / dS^T are at least one 128-byte span
-  static constexpr int DST_BYTES = BKV * DQ_N * 2;
+  static constexpr int PT_BYTES = HAS_DV ? BKV * DQ_N * 2 : 0;   // rows of P^T / dS^T are at least one 128-byte span
+  static constexpr int DST_BYTES = HAS_DK ? BKV * DQ_N * 2 : 0;
   static constexpr int SOFT_WARPS = BQ >= 64 ? 8 : 4;
   static constexpr int GROUPS = SOFT_WARPS / 4;        // column halves per key-row quarter
   static constexpr int THREADS = 32 * (SOFT_WARPS + 2);
-  static constexpr int DQ_STAGE_BYTES = 4 * 2 * 4096;  // eight boxes of 32 rows x 128 B, shared out over the warps
+  // boxes of 32 rows x 128 B, shared out over the warps: eight, or four where shared memory is short
+  static constexpr int DQ_STAGE_BYTES = (DQK == 256 && PASS == 2) ? 4 * 4096 : 4 * 2 * 4096;
   static constexpr int SLAB_BYTES = DQ_STAGE_BYTES / SOFT_WARPS;
   static constexpr int STAT_BYTES = SOFT_WARPS * 2 * BQ * 4;  // per softmax warp: lse[BQ] | delta[BQ]
   static constexpr int OFF_K = 0;
@@ -62,9 +71,10 @@ struct BwdCfg {
   static constexpr int OFF_BAR = OFF_STAT + STAT_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int COL_ST = 0, COL_DPT = BQ, COL_DV = 2 * BQ, COL_DK = 2 * BQ + DV, COL_DQ = 2 * BQ + DV + DQK;
-  static_assert(COL_DQ + (DQ_T ? DQ_GROUPS * DQ_N : DQK) <= TMEM_COLS, "tensor memory budget");
-  static_assert(DQ_GROUPS * (BQ / 32) <= 2 || !DQ_T, "the dQ staging slab holds two boxes per warp");
+  static constexpr int COL_ST = 0, COL_DPT = BQ, COL_DV = 2 * BQ, COL_DK = COL_DV + (HAS_DV ? DV : 0),
+                       COL_DQ = COL_DK + (HAS_DK ? DQK : 0);
+  static_assert(COL_DQ + (!HAS_DK ? 0 : (DQ_T ? DQ_GROUPS * DQ_N : DQK)) <= TMEM_COLS, "tensor memory budget");
+  static_assert(DQK != 256 || PASS != 0, "head_dim 256 runs as two passes");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -76,13 +86,13 @@ struct BwdArgs {
   int* status;
 };
 
-template <int DQK, int DV, bool CAP>
-__global__ void __launch_bounds__((BwdCfg<DQK, DV>::THREADS), 1)
+template <int DQK, int DV, bool CAP, int PASS = 0>
+__global__ void __launch_bounds__((BwdCfg<DQK, DV, PASS>::THREADS), 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
                  const __grid_constant__ CUtensorMap tmDV, BwdArgs args) {
-  using C = BwdCfg<DQK, DV>;
+  using C = BwdCfg<DQK, DV, PASS>;
   constexpr int BQ = C::BQ;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* k_s = smem + C::OFF_K;
@@ -152,8 +162,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int x = 0; x < DQK / 64; ++x)  // one 64-wide swizzle atom per load
         tma_load_3d(k_s + x * (BKV * 128), &tmK, kv_full, x * 64, hk, tok0 + key0);
+      if constexpr (C::HAS_DK) {
 #pragma unroll
-      for (int x = 0; x < DV / 64; ++x) tma_load_3d(v_s + x * (BKV * 128), &tmV, kv_full, x * 64, hk, tok0 + key0);
+        for (int x = 0; x < DV / 64; ++x) tma_load_3d(v_s + x * (BKV * 128), &tmV, kv_full, x * 64, hk, tok0 + key0);
+      }
       for (int t = 0; t < n_steps; ++t) {
         const int s = t & 1;
         const uint32_t ph = (t >> 1) & 1;
@@ -190,12 +202,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                      make_smem_desc_sw128(k_addr + (k >> 2) * (BKV * 128) + (k & 3) * 32, 16, 1024),
                      make_smem_desc_sw128(q_addr + (k >> 2) * (BQ * 128) + (k & 3) * 32, 16, 1024), idesc_s,
                      k != 0 ? 1u : 0u);
+        if constexpr (C::HAS_DK) {
 #pragma unroll
-        for (int k = 0; k < DV / 16; ++k)
-          tc_mma_f16(tmem_base + C::COL_DPT,
-                     make_smem_desc_sw128(v_addr + (k >> 2) * (BKV * 128) + (k & 3) * 32, 16, 1024),
-                     make_smem_desc_sw128(do_addr + (k >> 2) * (BQ * 128) + (k & 3) * 32, 16, 1024), idesc_s,
-                     k != 0 ? 1u : 0u);
+          for (int k = 0; k < DV / 16; ++k)
+            tc_mma_f16(tmem_base + C::COL_DPT,
+                       make_smem_desc_sw128(v_addr + (k >> 2) * (BKV * 128) + (k & 3) * 32, 16, 1024),
+                       make_smem_desc_sw128(do_addr + (k >> 2) * (BQ * 128) + (k & 3) * 32, 16, 1024), idesc_s,
+                       k != 0 ? 1u : 0u);
+        }
         tc_commit(st_full);
       };
       if (ok && n_steps > 0) {
@@ -212,29 +226,34 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t q_addr = smem_u32(qdo_s + s * (C::Q_BYTES + C::DO_BYTES));
         const uint32_t do_addr = q_addr + C::Q_BYTES;
         // dV += P^T dO ; dK += dS^T Q   (A: [128 keys x 128 queries] K-major in two 64-query atoms)
+        if constexpr (C::HAS_DV) {
 #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k) {
-          const uint32_t aoff = (k >> 2) * (BKV * 128) + (k & 3) * 32;
-          tc_mma_f16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_addr + aoff, 16, 1024),
-                     make_smem_desc_sw128(do_addr + k * (16 * 128), BQ * 128, 1024), idesc_dv, (t | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < BQ / 16; ++k) {
+            const uint32_t aoff = (k >> 2) * (BKV * 128) + (k & 3) * 32;
+            tc_mma_f16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_addr + aoff, 16, 1024),
+                       make_smem_desc_sw128(do_addr + k * (16 * 128), BQ * 128, 1024), idesc_dv, (t | k) != 0 ? 1u : 0u);
+          }
         }
+        if constexpr (C::HAS_DK) {
 #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k) {
-          const uint32_t aoff = (k >> 2) * (BKV * 128) + (k & 3) * 32;
-          tc_mma_f16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_addr + aoff, 16, 1024),
-                     make_smem_desc_sw128(q_addr + k * (16 * 128), BQ * 128, 1024), idesc_dk, (t | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < BQ / 16; ++k) {
+            const uint32_t aoff = (k >> 2) * (BKV * 128) + (k & 3) * 32;
+            tc_mma_f16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_addr + aoff, 16, 1024),
+                       make_smem_desc_sw128(q_addr + k * (16 * 128), BQ * 128, 1024), idesc_dk, (t | k) != 0 ? 1u : 0u);
+          }
         }
         // dQ = dS K : A = dS^T tile read MN-major (M = queries contiguous in 64-wide atoms, K = key rows),
         //             B = K_j tile read MN-major (N = dh contiguous, K = key rows)
 #pragma unroll
-        for (int k = 0; k < BKV / 16; ++k) {
+        for (int k = 0; k < (C::HAS_DK ? BKV / 16 : 0); ++k) {
           const uint64_t d_ds = make_smem_desc_sw128(dst_addr + k * (16 * 128), BKV * 128, 1024);
           if (C::DQ_T) {
 #pragma unroll
-            for (int g = 0; g < C::DQ_GROUPS; ++g)  // group g covers head dims 64g .. 64g+127
+            for (int g = 0; g < C::DQ_GROUPS; ++g)  // group g covers head dims g * DQ_GROUP_DIMS .. + 127
               tc_mma_f16(tmem_base + C::COL_DQ + g * C::DQ_N,
-                         make_smem_desc_sw128(k_addr + g * (BKV * 128) + k * (16 * 128), BKV * 128, 1024), d_ds, idesc_dq,
-                         k != 0 ? 1u : 0u);
+                         make_smem_desc_sw128(k_addr + g * (C::DQ_GROUP_DIMS / 64) * (BKV * 128) + k * (16 * 128),
+                                              BKV * 128, 1024),
+                         d_ds, idesc_dq, k != 0 ? 1u : 0u);
           } else {
             tc_mma_f16(tmem_base + C::COL_DQ, d_ds, make_smem_desc_sw128(k_addr + k * (16 * 128), BKV * 128, 1024),
                        idesc_dq, k != 0 ? 1u : 0u);
@@ -301,37 +320,35 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       } else {
         // dQ^T partial: TMEM lanes = head dims (group g: dims 64g + warp*32 + lane), columns = queries.
         // Each box of the reduce-add is [32 queries x 32 dims]: lane d writes element d of every query row.
+        constexpr int kSlabBoxes = C::SLAB_BYTES / 4096;
         int box = 0;
 #pragma unroll
         for (int g = 0; g < C::DQ_GROUPS; ++g) {
-          if (g > 0 && wq < 2) continue;  // lanes 0..63 of a later group repeat dims of the previous one
+          // overlapping groups (192 dims): lanes 0..63 of the later group repeat dims of the previous one
+          if (g > 0 && C::DQ_GROUP_DIMS < 128 && wq < 2) continue;
 #pragma unroll
-          for (int c = 0; c < BQ / 32; ++c, ++box) {
+          for (int c = 0; c < BQ / 32; ++c) {
             if (C::GROUPS == 2 && c != grp) continue;  // one box per warp
+            if (box >= kSlabBoxes) {  // slab full: the earlier boxes must have been read out
+              if (lane == 0) tma_wait_group_read<0>();
+              __syncwarp();
+            }
             uint32_t v[32];
             tmem_ld_32x32b_x32(t_row + C::COL_DQ + g * C::DQ_N + c * 32, v);
             tc_wait_ld();
-            uint8_t* bx = dq_stage + (C::GROUPS == 2 ? 0 : box * 4096) + (lane & 3) * 4;
+            uint8_t* slab = dq_stage + (box % kSlabBoxes) * 4096;
+            uint8_t* bx = slab + (lane & 3) * 4;
 #pragma unroll
             for (int q = 0; q < 32; ++q)
               *reinterpret_cast<float*>(bx + q * 128 + (((lane >> 2) ^ (q & 7)) << 4)) = __uint_as_float(v[q]) * sc;
-          }
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          box = 0;
-#pragma unroll
-          for (int g = 0; g < C::DQ_GROUPS; ++g) {
-            if (g > 0 && wq < 2) continue;
-#pragma unroll
-            for (int c = 0; c < BQ / 32; ++c, ++box) {
-              if (C::GROUPS == 2 && c != grp) continue;
-              tma_reduce_add_3d(&tmDQ, dq_stage + (C::GROUPS == 2 ? 0 : box * 4096), 64 * g + wq * 32, h,
-                                tok0 + q0 + c * 32);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_3d(&tmDQ, slab, C::DQ_GROUP_DIMS * g + wq * 32, h, tok0 + q0 + c * 32);
+              tma_commit_group();
             }
+            ++box;
           }
-          tma_commit_group();
         }
       }
     };
@@ -362,7 +379,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t sv[32];
         uint32_t dv[32];
         tmem_ld_32x32b_x32(t_row + C::COL_ST + c * 32, sv);
-        tmem_ld_32x32b_x32(t_row + C::COL_DPT + c * 32, dv);
+        if constexpr (C::HAS_DK) tmem_ld_32x32b_x32(t_row + C::COL_DPT + c * 32, dv);
         tc_wait_ld();
         float p[32], ds[32];
 #pragma unroll
@@ -389,27 +406,34 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               if (dead) pe = 0.f;
             }
             p[e] = pe;
-            float d = pe * (__uint_as_float(dv[e]) - dq4[u]);
-            if constexpr (CAP) d *= slope;
-            ds[e] = d;  // the softmax scale is applied once to dK (epilogue) and dQ (drain)
+            if constexpr (C::HAS_DK) {
+              float d = pe * (__uint_as_float(dv[e]) - dq4[u]);
+              if constexpr (CAP) d *= slope;
+              ds[e] = d;  // the softmax scale is applied once to dK (epilogue) and dQ (drain)
+            }
           }
         }
         uint8_t* prow = pt_s + (c >> 1) * (BKV * 128) + r * 128;
         uint8_t* drow = dst_s + (c >> 1) * (BKV * 128) + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          uint4 w, d;
-          w.x = pack_bf16x2(p[8 * g + 0], p[8 * g + 1]);
-          w.y = pack_bf16x2(p[8 * g + 2], p[8 * g + 3]);
-          w.z = pack_bf16x2(p[8 * g + 4], p[8 * g + 5]);
-          w.w = pack_bf16x2(p[8 * g + 6], p[8 * g + 7]);
-          d.x = pack_bf16x2(ds[8 * g + 0], ds[8 * g + 1]);
-          d.y = pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]);
-          d.z = pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]);
-          d.w = pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7]);
           const int chunk = (c & 1) * 4 + g;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = w;
-          *reinterpret_cast<uint4*>(drow + ((chunk ^ (r & 7)) << 4)) = d;
+          if constexpr (C::HAS_DV) {
+            uint4 w;
+            w.x = pack_bf16x2(p[8 * g + 0], p[8 * g + 1]);
+            w.y = pack_bf16x2(p[8 * g + 2], p[8 * g + 3]);
+            w.z = pack_bf16x2(p[8 * g + 4], p[8 * g + 5]);
+            w.w = pack_bf16x2(p[8 * g + 6], p[8 * g + 7]);
+            *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = w;
+          }
+          if constexpr (C::HAS_DK) {
+            uint4 d;
+            d.x = pack_bf16x2(ds[8 * g + 0], ds[8 * g + 1]);
+            d.y = pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]);
+            d.z = pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]);
+            d.w = pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7]);
+            *reinterpret_cast<uint4*>(drow + ((chunk ^ (r & 7)) << 4)) = d;
+          }
         }
       }
     };
@@ -432,7 +456,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // previous step's dV/dK/dQ MMAs finished: P^T / dS^T buffers are free and dQ(t-1) can be drained
         if (!mbar_wait_warp(mma2_done, (t - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after_sync();
-        drain_dq(t - 1);
+        if constexpr (C::HAS_DK) drain_dq(t - 1);
       }
       const bool need_mask = (args.causal && (key0 + BKV - 1 > q0)) ||
                              (args.window > 0 && (q0 + BQ - 1 - key0 >= args.window));
@@ -448,7 +472,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = mbar_wait_warp(mma2_done, (n_steps - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL);
       if (ok) {
         tc_fence_after_sync();
-        drain_dq(n_steps - 1);
+        if constexpr (C::HAS_DK) drain_dq(n_steps - 1);
       }
     }
     if (ok) {
@@ -462,6 +486,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         if (C::GROUPS == 2 && which != grp) continue;
+        if ((which == 0 && !C::HAS_DV) || (which == 1 && !C::HAS_DK)) continue;
         const int col = which == 0 ? C::COL_DV : C::COL_DK;
         const float osc = which == 0 ? 1.f : sc;
 #pragma unroll
@@ -577,9 +602,26 @@ __global__ void bwd_finish_kernel(const float* __restrict__ dq_accum, __nv_bfloa
   }
 }
 
+template <int DQK, int DV, int PASS>
+void launch_pass(const CUtensorMap& tQ, const CUtensorMap& tK, const CUtensorMap& tV, const CUtensorMap& tDO,
+                 const CUtensorMap& tDQ, const CUtensorMap& tDK, const CUtensorMap& tDV, const BwdArgs& a, dim3 grid,
+                 bool cap, cudaStream_t stream) {
+  using C = BwdCfg<DQK, DV, PASS>;
+  static bool configured = false;
+  if (!configured) {
+    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<DQK, DV, false, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<DQK, DV, true, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    configured = true;
+  }
+  if (cap)
+    flash_bwd_kernel<DQK, DV, true, PASS><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+  else
+    flash_bwd_kernel<DQK, DV, false, PASS><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+}
+
 template <int DQK, int DV>
 void launch_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
-  using C = BwdCfg<DQK, DV>;
+  using C = BwdCfg<DQK, DV, DQK == 256 ? 1 : 0>;  // tile sizes are the same in every pass
   constexpr int BQ = C::BQ;
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
@@ -595,12 +637,6 @@ void launch_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
                                  static_cast<uint64_t>(p.H) * DQK, DQK, 32, 1, 32, sw);
   CUtensorMap tDK = make_tmap_3d(p.dk, bf, 2, tokens, p.Hkv, DQK, p.dk_row_stride, DQK, 32, 1, 64, sw);
   CUtensorMap tDV = make_tmap_3d(p.dv, bf, 2, tokens, p.Hkv, DV, p.dv_row_stride, DV, 32, 1, 64, sw);
-  static bool configured = false;
-  if (!configured) {
-    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<DQK, DV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    MT_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<DQK, DV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    configured = true;
-  }
   BwdArgs a{p.S, p.H, p.Hkv, p.causal, p.window, p.scale, p.softcap, p.lse, p.delta, p.status};
   dim3 grid(p.S / BKV, p.Hkv, p.B);
   static const bool pipelined = [] {  // MT_ATTN_BWD_PIPELINED=0 falls back to the 128-query-step kernel for head_dim 64
@@ -609,11 +645,11 @@ void launch_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
   }();
   if (DQK == 64 && DV == 64 && pipelined) {
     flash_bwd_pipe64_main(p, stream);  // software-pipelined 64-query steps (flash_bwd_pipe64.cu)
+  } else if constexpr (DQK == 256) {
+    launch_pass<DQK, DV, 1>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a, grid, p.softcap > 0.f, stream);
+    launch_pass<DQK, DV, 2>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a, grid, p.softcap > 0.f, stream);
   } else {
-    if (p.softcap > 0.f)
-      flash_bwd_kernel<DQK, DV, true><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
-    else
-      flash_bwd_kernel<DQK, DV, false><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a);
+    launch_pass<DQK, DV, 0>(tQ, tK, tV, tDO, tDQ, tDK, tDV, a, grid, p.softcap > 0.f, stream);
   }
   MT_CUDA_CHECK(cudaGetLastError());
   bwd_finish_kernel<DQK><<<num_sms * 8, 256, 0, stream>>>(static_cast<const float*>(p.dq_accum),
@@ -631,7 +667,8 @@ void flash_attn_bwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
   if (p.dh == 64 && dv == 64) launch_bwd<64, 64>(p, num_sms, stream);
   else if (p.dh == 128 && dv == 128) launch_bwd<128, 128>(p, num_sms, stream);
   else if (p.dh == 192 && dv == 128) launch_bwd<192, 128>(p, num_sms, stream);
-  else throw std::runtime_error("flash_attn_bwd: head dims must be 64, 128 or 192/128");
+  else if (p.dh == 256 && dv == 256) launch_bwd<256, 256>(p, num_sms, stream);
+  else throw std::runtime_error("flash_attn_bwd: head dims must be 64, 128, 256 or 192/128");
 }
 
 }  // namespace mt

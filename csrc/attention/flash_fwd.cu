@@ -1,4 +1,4 @@
-// Causal / sliding-window flash attention forward for sm_100a (bf16, head_dim 64 or 128, grouped-query K/V; also
+// Causal / sliding-window flash attention forward for sm_100a (bf16, head_dim 64, 128 or 256, grouped-query K/V; also
 // the multi-head-latent shape with 192-wide queries/keys and 128-wide values).
 //
 // One CTA = one (batch, head, 128-query-row block).  Roles:
@@ -34,7 +34,7 @@ struct FwdCfg {
   static constexpr int O_STAGE_BYTES = BLOCK_M * DV * 2;  // reuses the P region, or the K/V ring when larger
   static constexpr int SMEM_DATA = Q_BYTES + 2 * (K_BYTES + V_BYTES) + P_BYTES;
   static constexpr int SMEM_BYTES = SMEM_DATA + 256;
-  static constexpr int TMEM_COLS = 256;
+  static constexpr int TMEM_COLS = BN + DV <= 256 ? 256 : 512;  // head_dim 256: one CTA per SM, all of tensor memory
   static constexpr int S_COL = 0;
   static constexpr int O_COL = BN;
   static_assert(BN + DV <= TMEM_COLS, "accumulators must fit the allocation");
@@ -392,7 +392,8 @@ void flash_attn_fwd(const AttnParams& p, int num_sms, cudaStream_t stream) {
   if (p.dh == 64 && dv == 64) cap ? launch_fwd<64, 64, true>(p, stream) : launch_fwd<64, 64, false>(p, stream);
   else if (p.dh == 128 && dv == 128) cap ? launch_fwd<128, 128, true>(p, stream) : launch_fwd<128, 128, false>(p, stream);
   else if (p.dh == 192 && dv == 128) cap ? launch_fwd<192, 128, true>(p, stream) : launch_fwd<192, 128, false>(p, stream);
-  else throw std::runtime_error("flash_attn_fwd: head dims must be 64, 128 or 192/128");
+  else if (p.dh == 256 && dv == 256) cap ? launch_fwd<256, 256, true>(p, stream) : launch_fwd<256, 256, false>(p, stream);
+  else throw std::runtime_error("flash_attn_fwd: head dims must be 64, 128, 256 or 192/128");
 }
 
 }  // namespace mt

@@ -8,13 +8,13 @@ from ._ext import ext, status_word
 
 
 def flash_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
-    """Forward and backward kernels cover head dims 64 and 128 and the multi-head-latent shape (192-wide queries and
-    keys, 128-wide values): the kernel path takes bf16 tensors of those shapes with sequence lengths that are
+    """Forward and backward kernels cover head dims 64, 128 and 256 and the multi-head-latent shape (192-wide queries
+    and keys, 128-wide values): the kernel path takes bf16 tensors of those shapes with sequence lengths that are
     multiples of 128, anything else goes to the oracle."""
     if not hasattr(ext(), "flash_fwd"):
         return False
     d, dv = q.shape[-1], v.shape[-1]
-    return (q.dtype == torch.bfloat16 and (d, dv) in ((64, 64), (128, 128), (192, 128)) and k.shape[-1] == d
+    return (q.dtype == torch.bfloat16 and (d, dv) in ((64, 64), (128, 128), (256, 256), (192, 128)) and k.shape[-1] == d
             and q.shape[1] % 128 == 0 and k.shape[1] == q.shape[1] and q.shape[2] % k.shape[2] == 0)
 
 

@@ -83,6 +83,21 @@ def test_flash_mla_shape_bwd():
     _run(1, 384, 2, 2, 192, causal=False, dv=128)
 
 
+def test_flash_fwd_dh256():
+    _run(1, 128, 1, 1, 256, grad=False)
+    _run(2, 512, 4, 2, 256, grad=False)
+    _run(1, 256, 2, 1, 256, causal=False, grad=False)
+
+
+def test_flash_bwd_dh256():
+    """head_dim 256 (Gemma 3) runs the backward as a dV pass and a dK / dQ pass."""
+    _run(1, 128, 1, 1, 256)
+    _run(2, 512, 4, 2, 256)
+    _run(1, 512, 2, 1, 256, window=200)
+    _run(1, 256, 2, 2, 256, softcap=30.0)
+    _run(1, 256, 2, 1, 256, causal=False)
+
+
 def test_flash_window_and_softcap():
     _run(1, 512, 2, 1, 64, window=200)
     _run(1, 256, 2, 2, 64, softcap=30.0)
