@@ -483,13 +483,26 @@ class TrainEngine:
         if "opt_state/flat_master" in paths:
             saved = {row[0]: row for row in json.loads(read("layout/big"))}
             mine = {s.name: s for s in self.big.slots}
-            same = all(n in saved and saved[n][1] == s.offset and saved[n][2] == s.numel for n, s in mine.items())
-            if not same:
-                raise ValueError("checkpoint parameter layout differs from this model's")
-            self.master.copy_(read("opt_state/flat_master", (lo, hi)))
+            for n, s in mine.items():
+                if n not in saved or saved[n][2] != s.numel:
+                    raise ValueError(f"checkpoint has no parameter '{n}' of {s.numel} elements")
+            same = all(saved[n][1] == s.offset for n, s in mine.items())
+            kinds = [("opt_state/flat_master", self.master)]
             if not self.params_only_restore:
-                self.exp_avg.copy_(read("opt_state/flat_exp_avg", (lo, hi)))
-                self.exp_avg_sq.copy_(read("opt_state/flat_exp_avg_sq", (lo, hi)))
+                kinds += [("opt_state/flat_exp_avg", self.exp_avg), ("opt_state/flat_exp_avg_sq", self.exp_avg_sq)]
+            if same:
+                for path, dst in kinds:
+                    dst.copy_(read(path, (lo, hi)))
+            else:
+                # the flat layout depends on the optimizer and the rank count (Muon packs whole matrices per rank):
+                # look every parameter up by name in the saved layout and copy the part this rank holds
+                for s in self.big.slots:
+                    a, b = max(s.offset, lo), min(s.offset + s.numel, hi)
+                    if a >= b:
+                        continue
+                    so = saved[s.name][1]
+                    for path, dst in kinds:
+                        dst[a - lo:b - lo] = read(path, (so + a - s.offset, so + b - s.offset)).to(self.device)
         else:  # a per-name checkpoint written by the CPU trainer
             for s in self.big.slots:
                 full = read(f"params/{s.name}").float().reshape(-1)

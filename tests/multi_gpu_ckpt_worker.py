@@ -12,10 +12,10 @@ import torch.distributed as dist
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 
-def ckpt_config(ckpt_dir: str):
+def ckpt_config(ckpt_dir: str, optimizer: str = "adamw"):
     from mintext_b200 import MinTextConfig
 
-    return MinTextConfig(num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+    return MinTextConfig(optimizer=optimizer, num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                          intermediate_size=512, vocab_size=1024, seq_length=128, steps=20, learning_rate=1e-3,
                          enable_tensorboard=False, enable_checkpointing=True, checkpoint_dir=ckpt_dir,
                          checkpoint_period=1, async_checkpointing=False)
@@ -25,7 +25,7 @@ def global_batch():
     return torch.randint(0, 1024, (8, 128), generator=torch.Generator().manual_seed(7))
 
 
-def main(ckpt_dir: str, out_path: str) -> None:
+def main(ckpt_dir: str, out_path: str, optimizer: str = "adamw") -> None:
     rank = int(os.environ["RANK"])
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -36,7 +36,7 @@ def main(ckpt_dir: str, out_path: str) -> None:
     from mintext_b200.parallel.engine import TrainEngine, local_batch_rows
 
     world = dist.get_world_size()
-    cfg = ckpt_config(ckpt_dir)
+    cfg = ckpt_config(ckpt_dir, optimizer)
     eng = TrainEngine(Transformer(cfg, rngs=0), cfg, device=dev)
     lo, hi = local_batch_rows(8, world, rank)
     tok = global_batch()[lo:hi].to(dev)
@@ -55,4 +55,4 @@ def main(ckpt_dir: str, out_path: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1], sys.argv[2])
+    main(*sys.argv[1:4])

@@ -137,9 +137,11 @@ def test_tensor_parallel_fused_kernels(tmp_path):
         assert abs(a - b) < 1e-2
 
 
-def test_checkpoint_saved_on_two_gpus_restores_on_one(tmp_path):
+@pytest.mark.parametrize("optimizer", ["adamw", "muon"])
+def test_checkpoint_saved_on_two_gpus_restores_on_one(tmp_path, optimizer):
     """Resharding: the flat optimizer state written as one chunk per rank by a 2-GPU run restores into a 1-GPU
-    engine (a different shard layout), and training continues with the same losses."""
+    engine (a different shard layout; under Muon also a different packing of the parameters into the flat
+    buffer), and training continues with the same losses."""
     world = 2
     if torch.cuda.device_count() < world:
         pytest.skip("needs 2 GPUs")
@@ -148,7 +150,7 @@ def test_checkpoint_saved_on_two_gpus_restores_on_one(tmp_path):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29675", str(ROOT / "tests" / "multi_gpu_ckpt_worker.py"),
-           str(ckpt), str(out)]
+           str(ckpt), str(out), optimizer]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     res = json.loads(out.read_text())
@@ -159,7 +161,7 @@ def test_checkpoint_saved_on_two_gpus_restores_on_one(tmp_path):
     from mintext_b200.models import Transformer
     from mintext_b200.parallel.engine import TrainEngine
 
-    cfg = ckpt_config(str(ckpt))
+    cfg = ckpt_config(str(ckpt), optimizer)
     eng = TrainEngine(Transformer(cfg, rngs=123), cfg, device="cuda")  # different init: everything must come from disk
     eng, step = maybe_restore_checkpoint(create_checkpoint_manager(cfg), eng, cfg)
     assert step == 3 and eng.step_count == 3
