@@ -28,7 +28,8 @@ sys.path.insert(0, str(ROOT))
 PUBLISHED_TOKENS_PER_SEC_PER_DEVICE = 22800.0  # reference's best published run (TPU v6e-8, Llama-3.2-1B)
 
 
-def llama_1b_config(global_batch: int, seq_len: int, world: int, micro_batch: int, steps: int, fp8_mlp: bool = False):
+def llama_1b_config(global_batch: int, seq_len: int, world: int, micro_batch: int, steps: int, fp8_mlp: bool = False,
+                    fp8_recipe: str = "per_tensor"):
     from mintext_b200 import MinTextConfig
 
     per_rank = global_batch // world
@@ -39,7 +40,7 @@ def llama_1b_config(global_batch: int, seq_len: int, world: int, micro_batch: in
         per_device_batch_size=micro_batch, gradient_accumulation_steps=max(per_rank // micro_batch, 1),
         dtype="bfloat16", weight_dtype="float32", optimizer="adamw", learning_rate=3e-4, lr_schedule="cosine",
         steps=max(steps, 10), remat_policy="none", enable_tensorboard=False, enable_checkpointing=False,
-        ici_fsdp_parallelism=world, use_fp8=fp8_mlp)
+        ici_fsdp_parallelism=world, use_fp8=fp8_mlp, fp8_recipe=fp8_recipe)
 
 
 class ClockSampler:
@@ -115,6 +116,8 @@ def main() -> None:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--fp8-mlp", action="store_true",
                     help="side measurement, not the headline: MLP projections through the FP8 GEMM (per-tensor scales)")
+    ap.add_argument("--fp8-recipe", choices=("per_tensor", "mx_block"), default="per_tensor",
+                    help="with --fp8-mlp: per-tensor scales (e4m3 / e5m2) or MXFP8 block scales (e4m3, one scale per 32)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -138,7 +141,8 @@ def main() -> None:
     from mintext_b200.utils.pytree import model_flops_per_token_batch
 
     warmup = max(args.warmup, 3)
-    cfg = llama_1b_config(args.global_batch, args.seq_len, world, args.micro_batch, args.steps + warmup, args.fp8_mlp)
+    cfg = llama_1b_config(args.global_batch, args.seq_len, world, args.micro_batch, args.steps + warmup, args.fp8_mlp,
+                          args.fp8_recipe)
     model = Transformer(cfg, rngs=0)
     eng = TrainEngine(model, cfg, device=dev)
     lo, hi = local_batch_rows(args.global_batch, world, rank)
@@ -219,7 +223,7 @@ def main() -> None:
             "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong",
             "vs_baseline": value / (PUBLISHED_TOKENS_PER_SEC_PER_DEVICE * world),
-            "dtype": "bf16 (fp8 e4m3/e5m2 MLP projections)" if args.fp8_mlp else "bf16", "data": "synthetic uniform-random token ids, random-init weights", "impl": "own",
+            "dtype": ("bf16 (mxfp8 MLP projections)" if args.fp8_recipe == "mx_block" else "bf16 (fp8 e4m3/e5m2 MLP projections)") if args.fp8_mlp else "bf16", "data": "synthetic uniform-random token ids, random-init weights", "impl": "own",
             "tokens_per_sec_per_gpu": value / world, "tflops_per_gpu": tflops_per_gpu,
             "mfu_vs_nominal_2250": tflops_per_gpu / 2250.0, "final_loss": final_loss,
             "config": {"model": "llama-3.2-1b-shaped (16L, d2048, 32/8 heads, ffn 8192, vocab 128256, tied)",

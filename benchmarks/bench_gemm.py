@@ -41,6 +41,7 @@ def main():
     ap.add_argument("--only", default="", help="run only shapes whose name contains this string")
     ap.add_argument("--pair", action="store_true", help="time the CTA-pair (cta_group::2) kernel next to the 1-CTA one")
     ap.add_argument("--fp8", action="store_true", help="time the FP8 GEMM instead (ratio is against cuBLAS bf16)")
+    ap.add_argument("--mxfp8", action="store_true", help="time the block-scaled FP8 GEMM instead (ratio against cuBLAS bf16)")
     args = ap.parse_args()
     from mintext_b200.ops._ext import check_status, ext, status_word
 
@@ -86,6 +87,19 @@ def main():
                 "fp8_linear": (lambda: e.gemm_fp8(e.fp8_quantize(x, False, True, False)[0],
                                                   e.fp8_quantize(w_kn, True, False, True)[1], False, True, sx, sw, st),
                                lambda: torch.matmul(x, w_kn, out=y)),
+            }
+        if args.mxfp8:  # block-scaled FP8 GEMM alone (pre-quantised operands) and with both quantisations
+            xq, xs, _, _ = e.mxfp8_quantize(x, True, False, False, False)
+            _, _, wqt, wst = e.mxfp8_quantize(w_kn, False, False, True, True)
+
+            def mx_linear():
+                a, sa, _, _ = e.mxfp8_quantize(x, True, False, False, False)
+                _, _, b, sb = e.mxfp8_quantize(w_kn, False, False, True, True)
+                return e.gemm_mxfp8(a, sa, b, sb, st)
+
+            cases = {
+                "mxfp8_gemm": (lambda: e.gemm_mxfp8(xq, xs, wqt, wst, st), lambda: torch.matmul(x, w_kn, out=y)),
+                "mxfp8_linear": (mx_linear, lambda: torch.matmul(x, w_kn, out=y)),
             }
         for kind, (mine, ref) in cases.items():
             t_mine = _time(mine, flush)

@@ -116,6 +116,13 @@ void gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, 
                     bool a_mn_major, bool b_mn_major, bool out_f32, bool accumulate, int* status, int num_sms,
                     cudaStream_t stream);
 
+// ---- gemm/mxfp8_gemm.cu: block-scaled FP8 (e4m3 elements, one UE8M0 scale per 32 elements along K)
+int64_t mxfp8_sf_bytes(int rows, int K, bool b_operand);
+void mxfp8_quantize(const void* x_bf16, int R, int C, void* q, void* sf, bool q_b_operand, void* qt, void* sft,
+                    bool qt_b_operand, cudaStream_t stream);
+void gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K, int* status,
+                int num_sms, cudaStream_t stream);
+
 // ---- gemm/fp8_gemm.cu: per-tensor-scaled FP8 GEMM (both operands K-major) and its quantisation kernels
 void fp8_amax(const void* x_bf16, int64_t n, float* amax, cudaStream_t stream);
 // scale[0] = (e5m2 ? 57344 : 448) / amax[0]; q [R,C] and / or qt [C,R] (either may be null) = fp8(x * scale)

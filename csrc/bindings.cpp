@@ -336,6 +336,42 @@ torch::Tensor gemm_fp8(const torch::Tensor& a, const torch::Tensor& b, bool a_e5
   return out;
 }
 
+// x [R,C] bf16 -> (q [R,C], sf, qt [C,R], sft): e4m3 elements with UE8M0 scales per 32 elements along the last dim
+// of q / qt; scale buffers are tiled for the GEMM's A (128-row tiles) or B (192-row tiles) operand.
+std::vector<torch::Tensor> mxfp8_quantize(const torch::Tensor& x, bool want_q, bool q_b_operand, bool want_qt,
+                                          bool qt_b_operand) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto u8 = x.options().dtype(torch::kUInt8);
+  const int R = (int)x.size(0), C = (int)x.size(1);
+  torch::Tensor q, sf, qt, sft;
+  if (want_q) {
+    q = torch::empty({R, C}, u8);
+    sf = torch::zeros({mt::mxfp8_sf_bytes(R, C, q_b_operand)}, u8);
+  }
+  if (want_qt) {
+    qt = torch::empty({C, R}, u8);
+    sft = torch::zeros({mt::mxfp8_sf_bytes(C, R, qt_b_operand)}, u8);
+  }
+  mt::mxfp8_quantize(x.data_ptr(), R, C, want_q ? q.data_ptr() : nullptr, want_q ? sf.data_ptr() : nullptr, q_b_operand,
+                     want_qt ? qt.data_ptr() : nullptr, want_qt ? sft.data_ptr() : nullptr, qt_b_operand, cur_stream());
+  return {q, sf, qt, sft};
+}
+
+// out[M,N] bf16 = a[M,K] . b[N,K]^T with the block scales applied by the tensor core
+torch::Tensor gemm_mxfp8(const torch::Tensor& a, const torch::Tensor& sfa, const torch::Tensor& b, const torch::Tensor& sfb,
+                         torch::Tensor& status) {
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && a.scalar_type() == torch::kUInt8 && b.scalar_type() == torch::kUInt8);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1) && a.size(1) % 128 == 0 && b.size(0) % 8 == 0);
+  TORCH_CHECK(sfa.numel() == mt::mxfp8_sf_bytes((int)a.size(0), (int)a.size(1), false), "A scales: wrong tiling");
+  TORCH_CHECK(sfb.numel() == mt::mxfp8_sf_bytes((int)b.size(0), (int)b.size(1), true), "B scales: wrong tiling");
+  c10::cuda::CUDAGuard guard(a.device());
+  auto out = torch::empty({a.size(0), b.size(0)}, a.options().dtype(torch::kBFloat16));
+  mt::gemm_mxfp8(a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), out.data_ptr(), (int)a.size(0), (int)b.size(0),
+                 (int)a.size(1), status.data_ptr<int>(), sm_count(), cur_stream());
+  return out;
+}
+
 // W, QG, KD [BH, C, 64, dk]; U [BH, C, 64, dv]; M [BH, C, 64, 64]; GL [BH, C]  ->  (O [BH, C, 64, dv], Sstart [BH, C, dk, dv])
 std::vector<torch::Tensor> gdn_scan_fwd(const torch::Tensor& W, const torch::Tensor& U, const torch::Tensor& QG,
                                         const torch::Tensor& M, const torch::Tensor& KD, const torch::Tensor& GL) {
@@ -548,6 +584,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_pair", &gemm_pair);
   m.def("fp8_quantize", &fp8_quantize);
   m.def("gemm_fp8", &gemm_fp8);
+  m.def("mxfp8_quantize", &mxfp8_quantize);
+  m.def("gemm_mxfp8", &gemm_mxfp8);
   m.def("gdn_scan_fwd", &gdn_scan_fwd);
   m.def("gdn_scan_bwd", &gdn_scan_bwd);
   m.def("conv1d_silu_fwd", &conv1d_silu_fwd);

@@ -41,18 +41,36 @@ def fp8_matmul_reference(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtyp
     return ((xq @ wq) / (sx * sw)).to(out_dtype)
 
 
+def mxfp8_matmul_reference(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Block-scaled fp8 product ``x[T,K] @ w[K,N]``: both operands to e4m3 with one power-of-two scale per 32
+    elements along K (the smallest that brings the block within +-448), fp32 accumulation.  Torch statement of
+    what csrc/gemm/mxfp8_gemm.cu computes; used where the kernel path is unavailable."""
+    def qdq(t: torch.Tensor) -> torch.Tensor:  # blocks along the last dim
+        r, k = t.shape
+        pad = (-k) % 32
+        tf = torch.nn.functional.pad(t.float(), (0, pad)).view(r, -1, 32)
+        amax = tf.abs().amax(-1, keepdim=True)
+        e = torch.ceil(torch.log2(amax.clamp_min(2.0 ** -120) / 448.0)).clamp(-127, 127)
+        scale = torch.exp2(e)
+        q = (tf / scale).clamp(-448, 448).to(torch.float8_e4m3fn).float() * scale
+        return q.view(r, -1)[:, :k]
+
+    return (qdq(x) @ qdq(w.t()).t()).to(out_dtype)
+
+
 class Linear(nn.Module):
     """``in_features`` / ``out_features`` may be ints or tuples (head-shaped kernels)."""
 
     def __init__(self, in_features, out_features, dtype: torch.dtype = torch.float32,
                  weight_dtype: torch.dtype = torch.float32, kernel_axes: tuple = (), use_bias: bool = False,
                  kernel_init_fn=None, use_fp8: bool = False, *, rngs: torch.Generator | None = None,
-                 name: str | None = None):
+                 name: str | None = None, fp8_recipe: str = "per_tensor"):
         super().__init__()
         self.in_shape = _as_tuple(in_features)
         self.out_shape = _as_tuple(out_features)
         self.dtype = dtype
         self.use_fp8 = use_fp8
+        self.fp8_recipe = str(fp8_recipe)
         self.remat_name = name
         fan_in = math.prod(self.in_shape)
         shape = self.in_shape + self.out_shape
@@ -71,7 +89,14 @@ class Linear(nn.Module):
         fan_in = math.prod(self.in_shape)
         x2 = x.reshape(*lead, fan_in)
         w2 = self.kernel.reshape(fan_in, -1) if self.kernel.dim() != 2 else self.kernel
-        if self.use_fp8 and self.kernel.dim() == 2 and F.fp8_kernel_path(x2, w2):
+        if self.use_fp8 and self.kernel.dim() == 2 and self.fp8_recipe == "mx_block":
+            if F.mxfp8_kernel_path(x2, w2):
+                y = F.linear_mxfp8(x2, w2)
+            else:
+                y = mxfp8_matmul_reference(x2.reshape(-1, fan_in), w2, self.dtype).reshape(*lead, -1)
+            if self.bias is not None:
+                y = y + self.bias.to(y.dtype).reshape(-1)
+        elif self.use_fp8 and self.kernel.dim() == 2 and F.fp8_kernel_path(x2, w2):
             y = F.linear_fp8(x2, w2)
             if self.bias is not None:
                 y = y + self.bias.to(y.dtype).reshape(-1)
@@ -100,9 +125,10 @@ class MLP(nn.Module):
         dt, wdt = config.torch_dtype, config.torch_weight_dtype
         self.act_name = config.hidden_activation
         fp8 = bool(config.use_fp8)
-        self.gate = Linear(D, M, dt, wdt, ("embed", "mlp"), use_fp8=fp8, rngs=rngs, name="mlp_gate_proj")
-        self.up = Linear(D, M, dt, wdt, ("embed", "mlp"), use_fp8=fp8, rngs=rngs, name="mlp_up")
-        self.down = Linear(M, D, dt, wdt, ("mlp", "embed"), use_fp8=fp8, rngs=rngs, name="mlp_down")
+        rec = str(getattr(config, "fp8_recipe", "per_tensor"))
+        self.gate = Linear(D, M, dt, wdt, ("embed", "mlp"), use_fp8=fp8, rngs=rngs, name="mlp_gate_proj", fp8_recipe=rec)
+        self.up = Linear(D, M, dt, wdt, ("embed", "mlp"), use_fp8=fp8, rngs=rngs, name="mlp_up", fp8_recipe=rec)
+        self.down = Linear(M, D, dt, wdt, ("mlp", "embed"), use_fp8=fp8, rngs=rngs, name="mlp_down", fp8_recipe=rec)
         from mintext_b200.parallel.tp import current_tp
 
         self.tp = current_tp() if (current_tp() is not None and current_tp().size > 1) else None
@@ -123,7 +149,15 @@ class MLP(nn.Module):
             _, (g, u) = tpm.column_linear(x.reshape(-1, D), [self.gate.kernel, self.up.kernel], self.tp, self.gate.dtype)
             h = F.gated_act(torch.cat([g, u], dim=-1), self.act_name)
             return tpm.row_linear(h, self.down.kernel, self.tp, self.gate.dtype).view(*lead, D)
-        if self.gate.use_fp8 and self.act_name in oracle.ACT_CODES and \
+        if self.gate.use_fp8 and self.gate.fp8_recipe == "mx_block":
+            x2 = x.reshape(-1, x.shape[-1])
+            if self.act_name in oracle.ACT_CODES and F.mxfp8_kernel_path(x2, self.gate.kernel):
+                # one block-scaled GEMM for gate|up (the activation is quantised once), then the gated-act kernel
+                gu = F.linear_mxfp8(x, torch.cat([self.gate.kernel, self.up.kernel], dim=1))
+                h = F.gated_act(gu, self.act_name)
+            else:
+                h = oracle.activation(self.act_name)(self.gate(x)) * self.up(x)
+        elif self.gate.use_fp8 and self.act_name in oracle.ACT_CODES and \
                 F.fp8_kernel_path(x.reshape(-1, x.shape[-1]), self.gate.kernel):
             h = F.gate_up_act_fp8(x, self.gate.kernel, self.up.kernel, self.act_name)
         elif self.gate.use_fp8:

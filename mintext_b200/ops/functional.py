@@ -266,6 +266,57 @@ def linear_fp8(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return y.reshape(*lead, w.shape[1])
 
 
+class _LinearMxfp8Fn(torch.autograd.Function):
+    """``y = x @ W`` with MXFP8 operands: e4m3 elements with one power-of-two scale per 32 elements along the
+    contraction, applied inside the tensor core (csrc/gemm/mxfp8_gemm.cu).  Forward and data gradient run in 8
+    bits (each operand quantised along the dimension its product contracts); the weight gradient stays a bf16 GEMM
+    accumulating in fp32, as on the per-tensor FP8 path (mintext/modules/linear.py:37-57 for the layer semantics)."""
+
+    @staticmethod
+    def forward(ctx, x, w, main_grad):
+        e, st = ext(), status_word(x.device)
+        xq, xs, _, _ = e.mxfp8_quantize(x, True, False, False, False)
+        # w is [K, N]: the forward contracts K (transposed copy [N, K]), the data gradient contracts N (w as stored)
+        wq, ws, wqt, wst = e.mxfp8_quantize(w, True, True, True, True)
+        ctx.save_for_backward(x, wq, ws)
+        ctx.main_grad, ctx.wmeta = main_grad, (w.shape, w.dtype, w.device)
+        return e.gemm_mxfp8(xq, xs, wqt, wst, st)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, wq, ws = ctx.saved_tensors
+        e, st = ext(), status_word(x.device)
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dyq, dys, _, _ = e.mxfp8_quantize(dy, True, False, False, False)
+            dx = e.gemm_mxfp8(dyq, dys, wq, ws, st)   # dy [T,N] . W [K,N]^T
+        if ctx.needs_input_grad[1]:
+            shape, wdt, dev = ctx.wmeta
+            mg = ctx.main_grad
+            if mg is not None:
+                _gemm(x, dy, mg.view(shape), True, True, accumulate=True)
+            else:
+                dw = torch.empty(shape, device=dev, dtype=torch.float32)
+                dw = _gemm(x, dy, dw, True, True).to(wdt)
+        return dx, dw, None
+
+
+def mxfp8_kernel_path(x: torch.Tensor, w2: torch.Tensor) -> bool:
+    return (use_cuda(x) and x.dtype == torch.bfloat16 and w2.dtype == torch.bfloat16 and hasattr(ext(), "gemm_mxfp8")
+            and w2.shape[0] % 128 == 0 and w2.shape[1] % 128 == 0)
+
+
+def linear_mxfp8(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x[..., K] @ w[K, N]`` through the block-scaled FP8 GEMM (callers check :func:`mxfp8_kernel_path`)."""
+    lead, K = x.shape[:-1], w.shape[0]
+    x2 = x.reshape(-1, K)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = _LinearMxfp8Fn.apply(x2, w, getattr(w, "main_grad", None))
+    return y.reshape(*lead, w.shape[1])
+
+
 class _LinearNTFn(torch.autograd.Function):
     """y[T,N] = x[T,K] @ W[N,K]^T (tied-embedding logits: the table is [vocab, hidden])."""
 

@@ -300,6 +300,79 @@ def test_fp8_gemm_matches_dequantised_reference(M, N, K):
     assert ((w.grad.float() - dw_ref).norm() / dw_ref.norm()).item() < 1e-2
 
 
+def _mx_dequant(q, sf, tile_rows):
+    """Decode e4m3 elements and their UE8M0 block scales (512-byte atoms of 32 lanes x 16 bytes per 128 rows of a
+    tile and 128-element k-block, tile-relative rows)."""
+    R, K = q.shape
+    atoms = (tile_rows + 127) // 128
+    rows = torch.arange(R, device=q.device)[:, None]
+    g = torch.arange(K // 32, device=q.device)[None, :]
+    tile, rr = rows // tile_rows, rows % tile_rows
+    off = ((tile * (K // 128) + (g >> 2)) * atoms + (rr >> 7)) * 512 + (rr & 31) * 16 + ((rr & 127) >> 5) * 4 + (g & 3)
+    scale = torch.exp2(sf[off].float() - 127.0)
+    return (q.view(torch.float8_e4m3fn).float().view(R, K // 32, 32) * scale[:, :, None]).view(R, K)
+
+
+def test_mxfp8_quantise_blocks_and_transposed_copy():
+    from mintext_b200.ops._ext import ext
+
+    torch.manual_seed(0)
+    x = (torch.randn(384, 512, device="cuda") * torch.logspace(-3, 2, 512, device="cuda")).bfloat16()
+    q, sf, qt, sft = ext().mxfp8_quantize(x, True, False, True, True)
+    xd = _mx_dequant(q, sf, 128)
+    assert ((xd - x.float()).norm() / x.float().norm()).item() < 0.04
+    # every block uses the e4m3 range: the largest magnitude of a block lands in (224, 448] after scaling
+    blk = x.float().view(384, 16, 32).abs().amax(-1)
+    qmax = q.view(torch.float8_e4m3fn).float().abs().view(384, 16, 32).amax(-1)
+    assert (qmax[blk > 0] > 223).all() and (qmax <= 448).all()
+    # the transposed copy equals quantising x^T along its rows
+    q2, sf2, _, _ = ext().mxfp8_quantize(x.t().contiguous(), True, True, False, False)
+    assert torch.equal(qt, q2) and torch.equal(sft, sf2)
+    assert torch.allclose(_mx_dequant(qt, sft, 192), _mx_dequant(q2, sf2, 192))
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 192, 128), (384, 1000, 512), (1024, 2048, 2048), (2000, 776, 384)])
+def test_mxfp8_gemm_matches_dequantised_reference(M, N, K):
+    """Block-scaled FP8 GEMM against the fp32 product of the same de-quantised operands."""
+    from mintext_b200.ops._ext import check_status, ext, status_word
+
+    torch.manual_seed(0)
+    x = (torch.randn(M, K, device="cuda") * torch.logspace(-2, 1, K, device="cuda")).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    e = ext()
+    xq, xs, _, _ = e.mxfp8_quantize(x, True, False, False, False)
+    wq, ws, _, _ = e.mxfp8_quantize(w, True, True, False, False)
+    y = e.gemm_mxfp8(xq, xs, wq, ws, status_word(x.device))
+    torch.cuda.synchronize()
+    check_status()
+    ref = _mx_dequant(xq, xs, 128) @ _mx_dequant(wq, ws, 192).t()
+    rel = ((y.float() - ref).norm() / ref.norm()).item()
+    assert rel < 1e-2, rel
+    full = x.float() @ w.float().t()
+    assert ((y.float() - full).norm() / full.norm()).item() < 0.06
+
+
+def test_mxfp8_linear_forward_and_gradients():
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops._ext import check_status
+
+    torch.manual_seed(0)
+    x = torch.randn(512, 384, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(384, 640, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    assert F.mxfp8_kernel_path(x, w)
+    y = F.linear_mxfp8(x, w)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    check_status()
+    full = x.detach().float() @ w.detach().float()
+    assert ((y.float() - full).norm() / full.norm()).item() < 0.06
+    dx_ref = dy.float() @ w.detach().float().t()
+    dw_ref = x.detach().float().t() @ dy.float()
+    assert ((x.grad.float() - dx_ref).norm() / dx_ref.norm()).item() < 0.06
+    assert ((w.grad.float() - dw_ref).norm() / dw_ref.norm()).item() < 1e-2
+
+
 def test_fp8_gated_mlp_front_half_matches_bf16_path():
     """One FP8 GEMM for gate|up plus the activation kernel, against the bf16 kernels (values and gradients)."""
     from mintext_b200.ops import functional as F
@@ -323,3 +396,30 @@ def test_fp8_gated_mlp_front_half_matches_bf16_path():
     # e5m2 weights keep two mantissa bits: the comparison is against the bf16 path, not against an exact FP8 oracle
     for name, a, b, tol in zip(("h", "dx", "dwg", "dwu"), got, ref, (0.12, 0.25, 0.12, 0.12)):
         assert _rel_err(a, b) < tol, (name, _rel_err(a, b))
+
+
+def test_mxfp8_mlp_matches_bf16_mlp():
+    """The MLP with ``fp8_recipe=mx_block`` (one block-scaled GEMM for gate|up, block-scaled down projection and
+    data gradients) against the same module on the bf16 kernels."""
+    from mintext_b200 import MinTextConfig
+    from mintext_b200.modules.linear import MLP
+    from mintext_b200.ops._ext import check_status
+
+    def build(**kw):
+        c = MinTextConfig(hidden_size=256, intermediate_size=512, dtype="bfloat16", weight_dtype="bfloat16", **kw)
+        return MLP(c, rngs=torch.Generator().manual_seed(3)).cuda()
+
+    torch.manual_seed(1)
+    x = torch.randn(4, 128, 256, device="cuda").bfloat16()
+    outs = []
+    for kw in ({}, {"use_fp8": True, "fp8_recipe": "mx_block"}):
+        m = build(**kw)
+        xi = x.clone().requires_grad_(True)
+        y = m(xi)
+        y.backward(torch.ones_like(y) * 0.01)
+        outs.append((y.detach(), xi.grad, m.gate.kernel.grad, m.down.kernel.grad))
+    torch.cuda.synchronize()
+    check_status()
+    for name, a, b in zip(("y", "dx", "dw_gate", "dw_down"), outs[1], outs[0]):
+        assert a is not None and _rel_err(a, b) < 0.08, (name, _rel_err(a, b))
+

@@ -313,3 +313,17 @@ def test_fp8_matmul_correlates_with_exact():
     assert corr > 0.95
     c = cfg(use_fp8=True)
     assert torch.isfinite(MLP(c, rngs=gen())(torch.randn(2, 4, c.hidden_size))).all()
+
+
+def test_mxfp8_matmul_reference_is_close_to_exact():
+    """Block scaling (one power-of-two scale per 32 elements) keeps the product within a few percent even when
+    the columns of the activation differ by orders of magnitude, where one per-tensor scale would flush them."""
+    from mintext_b200.modules.linear import mxfp8_matmul_reference
+
+    x = torch.randn(64, 128) * torch.logspace(-3, 2, 128)
+    w = torch.randn(128, 96) * 0.05
+    a = mxfp8_matmul_reference(x, w, torch.float32)
+    b = x @ w
+    assert ((a - b).norm() / b.norm()).item() < 0.05
+    c = cfg(use_fp8=True, fp8_recipe="mx_block")
+    assert torch.isfinite(MLP(c, rngs=gen())(torch.randn(2, 4, c.hidden_size))).all()
