@@ -24,6 +24,10 @@ void grouped_wgrad_bf16(const void* X, const void* G, void* dW, const int* offse
 // the same two products on CTA pairs (gemm/grouped_bf16_2cta.cu); the functions above route to these by default
 void grouped_gemm_bf16_pair(const void* X, const void* W, void* Y, const int* offsets, int E, int M_cap, int N, int K,
                             bool w_mn_major, int* status, int num_sms, cudaStream_t stream);
+// Forward product whose output row r goes to the address row_dst[r] (possibly in a peer GPU's memory; 0 = dropped)
+void grouped_gemm_scatter_bf16_pair(const void* X, const void* W, const unsigned long long* row_dst, const int* offsets,
+                                    int E, int M_cap, int N, int K, bool w_mn_major, int* status, int num_sms,
+                                    cudaStream_t stream);
 void grouped_wgrad_bf16_pair(const void* X, const void* G, void* dW, const int* offsets, int E, int M_cap, int N, int K,
                              bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream);
 

@@ -261,6 +261,24 @@ void grouped_gemm(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor&
                         (int)x.size(0), (int)N, (int)K, w_is_ekn, status.data_ptr<int>(), sm_count(), cur_stream());
 }
 
+// Expert GEMM fused with a row scatter: output row r is written to the byte address row_dst[r] (int64; 0 drops the
+// row), which may lie in a peer GPU's symmetric buffer.  Rows are N bf16 wide.
+void grouped_gemm_scatter(const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& row_dst,
+                          const torch::Tensor& offsets, bool w_is_ekn, torch::Tensor& status) {
+  check_bf16_2d(x, "x");
+  TORCH_CHECK(w.dim() == 3 && w.is_contiguous() && w.scalar_type() == torch::kBFloat16 && x.is_contiguous());
+  TORCH_CHECK(row_dst.scalar_type() == torch::kInt64 && row_dst.is_contiguous() && row_dst.numel() == x.size(0));
+  TORCH_CHECK(offsets.scalar_type() == torch::kInt32 && offsets.is_contiguous() && offsets.numel() == w.size(0) + 1);
+  const int64_t K = x.size(1);
+  const int64_t N = w_is_ekn ? w.size(2) : w.size(1);
+  TORCH_CHECK((w_is_ekn ? w.size(1) : w.size(2)) == K && x.size(0) % 128 == 0 && K % 8 == 0 && N % 8 == 0 && N > 128);
+  c10::cuda::CUDAGuard guard(x.device());
+  mt::grouped_gemm_scatter_bf16_pair(x.data_ptr(), w.data_ptr(),
+                                     reinterpret_cast<const unsigned long long*>(row_dst.data_ptr<int64_t>()),
+                                     offsets.data_ptr<int>(), (int)w.size(0), (int)x.size(0), (int)N, (int)K, w_is_ekn,
+                                     status.data_ptr<int>(), sm_count(), cur_stream());
+}
+
 void grouped_wgrad(const torch::Tensor& x, const torch::Tensor& g, torch::Tensor& dw, const torch::Tensor& offsets,
                    bool accumulate, torch::Tensor& status) {
   check_bf16_2d(x, "x");
@@ -579,6 +597,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_publish", &adamw_publish);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("grouped_wgrad", &grouped_wgrad);
+  m.def("grouped_gemm_scatter", &grouped_gemm_scatter);
   m.def("ep_push_rows", &ep_push_rows);
   m.def("ep_pull_rows", &ep_pull_rows);
   m.def("gemm_pair", &gemm_pair);

@@ -7,6 +7,11 @@
 //              expert; the follower still feeds the pair MMA (with rows of whatever follows) but stores nothing.
 //              Tiles are enumerated per expert through a prefix sum of ceil(blocks / 2) built in shared memory.
 //   MODE_WGRAD dW[e][K, N] (+)= X_e^T * G_e with 256 x 256 tiles of dW[e]; contraction over the expert's rows.
+//   SCATTER    (forward only) the epilogue does not store the tile: every output row is written, 128 contiguous bytes
+//              per group of eight lanes, to the address `row_dst[row]` - a row of a buffer in another GPU's (or this
+//              GPU's) memory - and rows whose entry is 0 (padding) are dropped.  This is the expert GEMM fused with
+//              the combine (or dispatch-gradient) all-to-all of expert parallelism: the rows travel over NVLink while
+//              later tiles are still being multiplied.  Plain peer stores; the consumer reads after a barrier.
 // Barrier protocol, bounded waits and the absence of multicast loads are as in the dense pair kernel.
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
@@ -76,11 +81,12 @@ __device__ __forceinline__ Tile decode_tile(int tile, const int* offs, const int
   return t;
 }
 
-template <int MODE, bool B_MN, bool OUT_F32>
+template <int MODE, bool B_MN, bool OUT_F32, bool SCATTER = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 grouped_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const int* __restrict__ offsets, int E, int N, int K,
-                    int accumulate, int* status) {
+                    int accumulate, int* status, const unsigned long long* __restrict__ row_dst = nullptr) {
+  static_assert(!SCATTER || (MODE == MODE_FWD && !OUT_F32), "row scatter is a forward, bf16 epilogue");
   using C = GPCfg;
   constexpr bool A_MN = (MODE == MODE_WGRAD);
   constexpr bool BMN = (MODE == MODE_WGRAD) ? true : B_MN;
@@ -222,11 +228,17 @@ grouped_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int row0 = t.row0 + rank * BM + q * 32;
       const bool rows_live = row0 < t.row_end;  // forward: the follower's half may lie beyond the expert's rows
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      unsigned long long my_dst = 0;  // SCATTER: lane l holds the destination of row row0 + l
+      if constexpr (SCATTER) {
+        if (rows_live) my_dst = row_dst[row0 + lane];
+      }
       for (int c = 0; c < BN / COLS && rows_live; ++c) {
         const int col0 = t.n0 + c * COLS;
         if (col0 >= N) break;
         uint8_t* sbuf = stage0 + (nstores & 1) * kEpiStageBytes;
-        if (lane == 0) tma_wait_group_read<1>();
+        if constexpr (!SCATTER) {
+          if (lane == 0) tma_wait_group_read<1>();
+        }
         __syncwarp();
         uint8_t* srow = sbuf + lane * 128;
         if constexpr (OUT_F32) {
@@ -254,13 +266,28 @@ grouped_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (MODE == MODE_FWD) tma_store_2d(&tmC, sbuf, col0, row0);
-          else if (accumulate) tma_reduce_add_3d(&tmC, sbuf, col0, row0, t.e);
-          else tma_store_3d(&tmC, sbuf, col0, row0, t.e);
-          tma_commit_group();
+        if constexpr (SCATTER) {
+          __syncwarp();
+          // read the staged 32 x 128-byte chunk back row-wise: eight lanes carry one row's 128 contiguous bytes
+          const int ch = lane & 7;
+          const bool col_ok = col0 + ch * 8 < N;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3);
+            const unsigned long long dst = __shfl_sync(0xffffffffu, my_dst, rr);
+            const uint4 v = *reinterpret_cast<const uint4*>(sbuf + rr * 128 + ((ch ^ (rr & 7)) << 4));
+            if (dst != 0 && col_ok)
+              *reinterpret_cast<uint4*>(dst + static_cast<unsigned long long>(col0 + ch * 8) * 2) = v;
+          }
+        } else {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (MODE == MODE_FWD) tma_store_2d(&tmC, sbuf, col0, row0);
+            else if (accumulate) tma_reduce_add_3d(&tmC, sbuf, col0, row0, t.e);
+            else tma_store_3d(&tmC, sbuf, col0, row0, t.e);
+            tma_commit_group();
+          }
         }
         ++nstores;
       }
@@ -310,6 +337,33 @@ void grouped_gemm_bf16_pair(const void* X, const void* W, void* Y, const int* of
     grouped_pair_kernel<MODE_FWD, true, false><<<grid, kThreads, GPCfg::SMEM_BYTES, stream>>>(tA, tB, tC, offsets, E, N, K, 0, status);
   else
     grouped_pair_kernel<MODE_FWD, false, false><<<grid, kThreads, GPCfg::SMEM_BYTES, stream>>>(tA, tB, tC, offsets, E, N, K, 0, status);
+  MT_CUDA_CHECK(cudaGetLastError());
+}
+
+// Same product, but output row r is written to the address row_dst[r] (0 = drop the row) instead of Y; the addresses
+// may point into peer-mapped memory of other GPUs.  `row_dst` has M_cap entries; every destination row holds N bf16.
+void grouped_gemm_scatter_bf16_pair(const void* X, const void* W, const unsigned long long* row_dst, const int* offsets,
+                                    int E, int M_cap, int N, int K, bool w_mn_major, int* status, int num_sms,
+                                    cudaStream_t stream) {
+  if (M_cap <= 0 || E <= 0) return;
+  if (E > kMaxExperts) throw std::runtime_error("grouped_gemm_scatter_bf16_pair: too many experts");
+  if (N % 8 != 0) throw std::runtime_error("grouped_gemm_scatter_bf16_pair: N must be a multiple of 8");
+  const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  CUtensorMap tA = make_tmap_2d(X, bf, 2, M_cap, K, K, BM, BK, sw);
+  CUtensorMap tB = w_mn_major ? make_tmap_3d(W, bf, 2, E, K, N, (uint64_t)K * N, N, 1, BK, 64, sw)
+                              : make_tmap_3d(W, bf, 2, E, N, K, (uint64_t)N * K, K, 1, BN / 2, BK, sw);
+  static bool configured = false;
+  if (!configured) {
+    configure(grouped_pair_kernel<MODE_FWD, true, false, true>);
+    configure(grouped_pair_kernel<MODE_FWD, false, false, true>);
+    configured = true;
+  }
+  const int grid = (num_sms / 2) * 2;
+  if (w_mn_major)
+    grouped_pair_kernel<MODE_FWD, true, false, true><<<grid, kThreads, GPCfg::SMEM_BYTES, stream>>>(tA, tB, tA, offsets, E, N, K, 0, status, row_dst);
+  else
+    grouped_pair_kernel<MODE_FWD, false, false, true><<<grid, kThreads, GPCfg::SMEM_BYTES, stream>>>(tA, tB, tA, offsets, E, N, K, 0, status, row_dst);
   MT_CUDA_CHECK(cudaGetLastError());
 }
 

@@ -63,11 +63,15 @@ class ExpertParallel:
         outb = symm.empty(cap_rows * dim, dtype=torch.bfloat16, device=self.device)
         flags = symm.empty(64, dtype=torch.int32, device=self.device)
         flags.zero_()
-        h_in, h_out, h_fl = (symm.rendezvous(t, self.group) for t in (inb, outb, flags))
+        # one 16-byte record per received row: (sender rank + 1, the row's flat (token, slot) index, 0, 0)
+        tagb = symm.empty(cap_rows * 8, dtype=torch.bfloat16, device=self.device)
+        h_in, h_out, h_fl, h_tag = (symm.rendezvous(t, self.group) for t in (inb, outb, flags, tagb))
         self._bufs = {
             "cap": cap_rows, "dim": dim, "in": inb.view(cap_rows, dim), "out": outb.view(cap_rows, dim),
             "in_ptrs": [int(p) for p in h_in.buffer_ptrs], "out_ptrs": [int(p) for p in h_out.buffer_ptrs],
-            "flag_ptrs": [int(p) for p in h_fl.buffer_ptrs], "handles": (h_in, h_out, h_fl), "flags": flags,
+            "flag_ptrs": [int(p) for p in h_fl.buffer_ptrs], "handles": (h_in, h_out, h_fl, h_tag), "flags": flags,
+            "tag": tagb.view(cap_rows, 8), "tag_ptrs": [int(p) for p in h_tag.buffer_ptrs],
+            "out_ptr_table": torch.tensor([int(p) for p in h_out.buffer_ptrs], dtype=torch.int64, device=self.device),
         }
         self.overflow = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.seq = 0
@@ -180,25 +184,48 @@ def _plan(ep: ExpertParallel, topk_idx: torch.Tensor, num_experts: int, cap: int
     rank_flat[sort_idx] = dst_rank
     pos_flat[sort_idx] = dst_pos
     return {
-        "src_token": src_token, "dst_rank": dst_rank.to(torch.int32), "dst_pos": dst_pos,
+        "src_token": src_token, "sort_idx": sort_idx, "dst_rank": dst_rank.to(torch.int32), "dst_pos": dst_pos,
         "rank_flat": rank_flat.to(torch.int32), "pos_flat": pos_flat,
         "off_local": off[ep.rank].to(torch.int32).contiguous(), "cap": cap, "N": N, "K": K,
     }
 
 
+def _dispatch_rows(x, ep, plan):
+    """Forward half of the dispatch: push this rank's (token, slot) rows and their return addresses to the expert
+    ranks; returns this rank's expert-contiguous, 128-padded input rows."""
+    from mintext_b200.ops._ext import ext
+
+    b = ep.buffers(plan["cap"], x.shape[1])
+    rows = x.index_select(0, plan["src_token"])
+    b["in"].zero_()
+    b["tag"].zero_()
+    ep.barrier()  # every rank's receive buffer is cleared and no longer read
+    ext().ep_push_rows(rows, plan["dst_rank"], plan["dst_pos"], b["in_ptrs"], b["cap"], ep.overflow)
+    # the rows' return addresses travel with them: the fused expert-GEMM + combine kernel writes its output rows
+    # straight back to (sender rank, flat index)
+    tags = torch.zeros(rows.shape[0], 4, dtype=torch.int32, device=x.device)
+    tags[:, 0] = ep.rank + 1
+    tags[:, 1] = plan["sort_idx"].to(torch.int32)          # flat (token, slot) index: where the combine wants it
+    tags[:, 2] = torch.arange(rows.shape[0], device=x.device, dtype=torch.int32)  # expert-sorted index (dispatch grad)
+    ext().ep_push_rows(tags.view(torch.bfloat16), plan["dst_rank"], plan["dst_pos"], b["tag_ptrs"], b["cap"],
+                       ep.overflow)
+    ep.barrier()  # all rows have landed
+    plan["tags"] = b["tag"][: plan["cap"]].view(torch.int32).clone()
+    return b["in"][: plan["cap"]].clone()
+
+
+def _return_addresses(b, tags: torch.Tensor, column: int, dim: int) -> torch.Tensor:
+    """Byte address, in the sender's receive buffer, of the row that each padded local row answers (0 = padding)."""
+    home = tags[:, 0].long()
+    dst = b["out_ptr_table"][(home - 1).clamp_min(0)] + tags[:, column].long() * (dim * 2)
+    return torch.where(home > 0, dst, torch.zeros_like(dst)).contiguous()
+
+
 class _Dispatch(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, ep, plan):
-        from mintext_b200.ops._ext import ext
-
-        b = ep.buffers(plan["cap"], x.shape[1])
-        rows = x.index_select(0, plan["src_token"])
-        b["in"].zero_()
-        ep.barrier()  # every rank's receive buffer is cleared and no longer read
-        ext().ep_push_rows(rows, plan["dst_rank"], plan["dst_pos"], b["in_ptrs"], b["cap"], ep.overflow)
-        ep.barrier()  # all rows have landed
         ctx.ep, ctx.plan, ctx.n = ep, plan, x.shape[0]
-        return b["in"][: plan["cap"]].clone()
+        return _dispatch_rows(x, ep, plan)
 
     @staticmethod
     def backward(ctx, d_rows):
@@ -249,6 +276,110 @@ class _Combine(torch.autograd.Function):
         return b["in"][: plan["cap"]].clone(), dw, None, None
 
 
+class _GroupedCombine(torch.autograd.Function):
+    """Down projection of the local experts fused with the combine all-to-all: ONE kernel multiplies the expert
+    tiles and writes every output row from its epilogue straight into the home rank's receive buffer over NVLink
+    (csrc/gemm/grouped_bf16_2cta.cu, SCATTER), so the transfer overlaps the remaining tiles; the home rank then
+    reduces its K rows per token with the routing weights.  Backward: push of the weighted output gradients to the
+    expert ranks, then the grouped data- and weight-gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, h, w, topk_w, main_grad, ep, plan):
+        from mintext_b200.ops._ext import ext, status_word
+
+        D = w.shape[2]
+        N, K = plan["N"], plan["K"]
+        b = ep.buffers(plan["cap"], D)
+        row_dst = _return_addresses(b, plan["tags"], 1, D)
+        ep.barrier()  # nobody still reads its receive buffer from an earlier layer
+        ext().grouped_gemm_scatter(h, w, row_dst, plan["off_local"], True, status_word(h.device))
+        ep.barrier()  # every rank's rows have landed
+        picked = b["out"][: N * K].clone()
+        ctx.save_for_backward(h, w, picked, topk_w)
+        ctx.ep, ctx.plan, ctx.main_grad = ep, plan, main_grad
+        return torch.einsum("nkd,nk->nd", picked.view(N, K, -1), topk_w.to(picked.dtype))
+
+    @staticmethod
+    def backward(ctx, dy):
+        from mintext_b200.ops._ext import ext, status_word
+
+        h, w, picked, topk_w = ctx.saved_tensors
+        ep, plan = ctx.ep, ctx.plan
+        N, K = plan["N"], plan["K"]
+        st = status_word(h.device)
+        d_picked = (dy[:, None, :] * topk_w.to(dy.dtype)[:, :, None]).reshape(N * K, -1).contiguous()
+        dtw = torch.einsum("nkd,nd->nk", picked.view(N, K, -1).float(), dy.float()).to(topk_w.dtype)
+        b = ep.buffers(plan["cap"], dy.shape[1])
+        b["in"].zero_()
+        ep.barrier()
+        ext().ep_push_rows(d_picked, plan["rank_flat"], plan["pos_flat"], b["in_ptrs"], b["cap"], ep.overflow)
+        ep.barrier()
+        dy_p = b["in"][: plan["cap"]].clone()
+        dh = torch.empty_like(h)
+        ext().grouped_gemm(dy_p, w, dh, plan["off_local"], False, st)
+        dw = None
+        if ctx.main_grad is not None:
+            ext().grouped_wgrad(h, dy_p, ctx.main_grad.view(w.shape), plan["off_local"], True, st)
+        else:
+            dwf = torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+            ext().grouped_wgrad(h, dy_p, dwf, plan["off_local"], False, st)
+            dw = dwf.to(w.dtype)
+        return dh, dw, dtw, None, None, None
+
+
+class _DispatchGrouped(torch.autograd.Function):
+    """Dispatch + first expert projection.  Forward: peer-store dispatch, then the grouped GEMM.  Backward: the
+    grouped data-gradient GEMM fused with the dispatch-gradient all-to-all - its epilogue writes every gradient row
+    straight back to the rank the token came from (same SCATTER kernel as the fused combine)."""
+
+    @staticmethod
+    def forward(ctx, x, w, main_grad, ep, plan):
+        from mintext_b200.ops._ext import ext, status_word
+
+        rows = _dispatch_rows(x, ep, plan)
+        y = torch.empty(rows.shape[0], w.shape[2], device=x.device, dtype=torch.bfloat16)
+        ext().grouped_gemm(rows, w, y, plan["off_local"], True, status_word(x.device))
+        ctx.save_for_backward(rows, w)
+        ctx.ep, ctx.plan, ctx.main_grad, ctx.n = ep, plan, main_grad, x.shape[0]
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from mintext_b200.ops._ext import ext, status_word
+
+        rows, w = ctx.saved_tensors
+        ep, plan = ctx.ep, ctx.plan
+        st = status_word(rows.device)
+        dy = dy.contiguous()
+        D = rows.shape[1]
+        dw = None
+        if ctx.main_grad is not None:
+            ext().grouped_wgrad(rows, dy, ctx.main_grad.view(w.shape), plan["off_local"], True, st)
+        else:
+            dwf = torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+            ext().grouped_wgrad(rows, dy, dwf, plan["off_local"], False, st)
+            dw = dwf.to(w.dtype)
+        b = ep.buffers(plan["cap"], D)
+        row_dst = _return_addresses(b, plan["tags"], 2, D)
+        ep.barrier()  # nobody still reads its receive buffer
+        ext().grouped_gemm_scatter(dy, w, row_dst, plan["off_local"], False, st)  # dy @ w[e]^T, rows sent home
+        ep.barrier()
+        R = plan["dst_rank"].numel()
+        dx = torch.zeros(ctx.n, D, device=dy.device, dtype=torch.float32)
+        dx.index_add_(0, plan["src_token"], b["out"][:R].float())
+        return dx.to(dy.dtype), dw, None, None, None
+
+
+def _fused_combine_ok(ep: ExpertParallel, plan, down_local) -> bool:
+    import os
+
+    from mintext_b200.ops._ext import ext
+
+    return (os.environ.get("MT_EP_FUSED_COMBINE", "1") != "0" and hasattr(ext(), "grouped_gemm_scatter")
+            and down_local.dtype == torch.bfloat16 and down_local.shape[2] > 128 and down_local.shape[2] % 8 == 0
+            and down_local.shape[0] <= 256 and plan["N"] * plan["K"] <= plan["cap"])
+
+
 def experts_forward_peer(ep: ExpertParallel, x, topk_idx, topk_w, gate_up_local, down_local, act: str,
                          num_experts: int):
     from mintext_b200.ops import functional as F
@@ -258,8 +389,14 @@ def experts_forward_peer(ep: ExpertParallel, x, topk_idx, topk_w, gate_up_local,
     El = num_experts // ep.size
     cap = moe_ops.capacity(int(ep.capacity_factor * N * K), El)
     plan = _plan(ep, topk_idx, num_experts, cap)
-    rows = _Dispatch.apply(x, ep, plan)
-    h = moe_ops.grouped_padded(rows, gate_up_local, plan["off_local"])
+    fused = _fused_combine_ok(ep, plan, down_local)
+    if fused and x.shape[1] > 128 and x.dtype == torch.bfloat16:
+        h = _DispatchGrouped.apply(x.contiguous(), gate_up_local, getattr(gate_up_local, "main_grad", None), ep, plan)
+    else:
+        rows = _Dispatch.apply(x, ep, plan)
+        h = moe_ops.grouped_padded(rows, gate_up_local, plan["off_local"])
     h = F.gated_act(h, act)
+    if fused:
+        return _GroupedCombine.apply(h.contiguous(), down_local, topk_w, getattr(down_local, "main_grad", None), ep, plan)
     y = moe_ops.grouped_padded(h, down_local, plan["off_local"])
     return _Combine.apply(y, topk_w, ep, plan)

@@ -25,6 +25,13 @@ class Heartbeat:
                  prefix: str = "mt_hb"):
         self.store, self.rank, self.world = store, rank, world
         self.interval_s, self.timeout_s, self.prefix = float(interval_s), float(timeout_s), prefix
+        # A store client is one socket: the publishing thread gets its own connection (Store.clone) where the store
+        # supports it, and a lock serialises the two users otherwise.
+        self._lock = threading.Lock()
+        try:
+            self._pub_store = store.clone()
+        except Exception:
+            self._pub_store = store
         self._stop = threading.Event()
         self._beat = 0
         self._seen: dict[int, tuple[int, float]] = {}
@@ -37,7 +44,8 @@ class Heartbeat:
 
     def _publish(self) -> None:
         self._beat += 1
-        self.store.set(self._key(self.rank), str(self._beat))
+        with self._lock:
+            self._pub_store.set(self._key(self.rank), str(self._beat))
 
     def _run(self) -> None:
         while not self._stop.wait(self.interval_s):
@@ -54,7 +62,8 @@ class Heartbeat:
             if r == self.rank:
                 continue
             try:
-                beat = int(self.store.get(self._key(r)).decode()) if self.store.check([self._key(r)]) else 0
+                with self._lock:
+                    beat = int(self.store.get(self._key(r)).decode()) if self.store.check([self._key(r)]) else 0
             except Exception as e:
                 raise PeerFailure(f"rank {self.rank}: heartbeat store unreachable ({e})") from e
             last = self._seen.get(r)
@@ -69,7 +78,8 @@ class Heartbeat:
         """Block until every peer has published at least once (start-up), or raise after ``deadline_s``."""
         t0 = time.monotonic()
         while True:
-            missing = [r for r in range(self.world) if r != self.rank and not self.store.check([self._key(r)])]
+            with self._lock:
+                missing = [r for r in range(self.world) if r != self.rank and not self.store.check([self._key(r)])]
             if not missing:
                 return
             if time.monotonic() - t0 > deadline_s:

@@ -177,6 +177,10 @@ def train(config: MinTextConfig) -> dict:
             save_checkpoint(manager, config.steps, state, force=True)
         wait_for_checkpoint(manager)
     if heartbeat is not None:
+        # ranks that finish early must not take the store down under a peer that is still checking it
+        import torch.distributed as dist
+
+        dist.barrier()
         heartbeat.close()
     profiler.stop()
     metric_logger.close()

@@ -38,7 +38,10 @@ def main(out_path: str) -> None:
     lo, hi = local_batch_rows(8, world, rank)
     tok = global_tok[lo:hi].to(dev)
     results = {}
-    for name, fused in (("peer", True), ("collective", False)):
+    # "peer": dispatch by peer stores, down projection fused with the combine all-to-all (one kernel);
+    # "peer_unfused": the same exchange with the combine as a separate pull kernel; "collective": NCCL baseline
+    for name, fused, fuse_combine in (("peer", True, "1"), ("peer_unfused", True, "0"), ("collective", False, "1")):
+        os.environ["MT_EP_FUSED_COMBINE"] = fuse_combine
         cfg = moe_config(fused, world)
         ep = ExpertParallel(dist.group.WORLD, dev, cfg.moe_capacity_factor, fused=fused)
         set_current_ep(ep)

@@ -184,3 +184,32 @@ def test_dispatch_combine_kernels_and_grads():
     _check()
     assert _rel(x.grad, xr.grad) < 2e-2
     assert _rel(w.grad, wr.grad) < 2e-2
+
+
+def test_grouped_gemm_with_row_scatter_epilogue():
+    """The expert GEMM whose epilogue writes every output row to a per-row address (the fused combine of expert
+    parallelism), here into a local buffer through a random permutation with some rows dropped."""
+    from mintext_b200.ops._ext import check_status, ext, status_word
+
+    torch.manual_seed(0)
+    E, K, N = 5, 192, 320
+    sizes = torch.tensor([128, 384, 0, 256, 128])
+    off = torch.zeros(E + 1, dtype=torch.int32)
+    off[1:] = torch.cumsum(sizes, 0)
+    M = int(off[-1])
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(E, K, N, device="cuda") * 0.05).bfloat16()
+    off = off.cuda()
+    y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ext().grouped_gemm(x, w, y, off, True, status_word())
+    perm = torch.randperm(M, device="cuda")
+    keep = torch.rand(M, device="cuda") > 0.2
+    out = torch.full((M, N), 7.0, device="cuda", dtype=torch.bfloat16)
+    dst = torch.where(keep, out.data_ptr() + perm * (N * 2), torch.zeros_like(perm)).contiguous()
+    ext().grouped_gemm_scatter(x, w, dst, off, True, status_word())
+    torch.cuda.synchronize()
+    check_status()
+    want = torch.full_like(out, 7.0)
+    want[perm[keep]] = y[keep]
+    assert torch.equal(out, want)
+

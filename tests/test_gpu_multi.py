@@ -79,7 +79,7 @@ def test_expert_parallel_matches_single_gpu(tmp_path):
     tok = torch.randint(0, 1024, (8, 128), generator=g).cuda()
     single = [float(eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=1)["loss"]) for _ in range(5)]
     eng.check()
-    for name in ("peer", "collective"):
+    for name in ("peer", "peer_unfused", "collective"):
         for a, b in zip(res[name]["losses"], single):
             assert abs(a - b) < 3e-2, (name, res[name]["losses"], single)
 
