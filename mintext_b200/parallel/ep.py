@@ -205,8 +205,7 @@ def _dispatch_rows(x, ep, plan):
     # straight back to (sender rank, flat index)
     tags = torch.zeros(rows.shape[0], 4, dtype=torch.int32, device=x.device)
     tags[:, 0] = ep.rank + 1
-    tags[:, 1] = plan["sort_idx"].to(torch.int32)          # flat (token, slot) index: where the combine wants it
-    tags[:, 2] = torch.arange(rows.shape[0], device=x.device, dtype=torch.int32)  # expert-sorted index (dispatch grad)
+    tags[:, 1] = plan["sort_idx"].to(torch.int32)          # flat (token, slot) index: where the row goes home to
     ext().ep_push_rows(tags.view(torch.bfloat16), plan["dst_rank"], plan["dst_pos"], b["tag_ptrs"], b["cap"],
                        ep.overflow)
     ep.barrier()  # all rows have landed
@@ -293,6 +292,7 @@ class _GroupedCombine(torch.autograd.Function):
         row_dst = _return_addresses(b, plan["tags"], 1, D)
         ep.barrier()  # nobody still reads its receive buffer from an earlier layer
         ext().grouped_gemm_scatter(h, w, row_dst, plan["off_local"], True, status_word(h.device))
+        ep.fused_combines = getattr(ep, "fused_combines", 0) + 1
         ep.barrier()  # every rank's rows have landed
         picked = b["out"][: N * K].clone()
         ctx.save_for_backward(h, w, picked, topk_w)
@@ -360,14 +360,15 @@ class _DispatchGrouped(torch.autograd.Function):
             ext().grouped_wgrad(rows, dy, dwf, plan["off_local"], False, st)
             dw = dwf.to(w.dtype)
         b = ep.buffers(plan["cap"], D)
-        row_dst = _return_addresses(b, plan["tags"], 2, D)
+        # rows go home to their flat (token, slot) position, so a token's K gradient rows are adjacent and the
+        # reduction over slots needs no atomics
+        row_dst = _return_addresses(b, plan["tags"], 1, D)
         ep.barrier()  # nobody still reads its receive buffer
         ext().grouped_gemm_scatter(dy, w, row_dst, plan["off_local"], False, st)  # dy @ w[e]^T, rows sent home
         ep.barrier()
-        R = plan["dst_rank"].numel()
-        dx = torch.zeros(ctx.n, D, device=dy.device, dtype=torch.float32)
-        dx.index_add_(0, plan["src_token"], b["out"][:R].float())
-        return dx.to(dy.dtype), dw, None, None, None
+        N, K = plan["N"], plan["K"]
+        dx = b["out"][: N * K].view(N, K, D).sum(dim=1, dtype=torch.float32).to(dy.dtype)
+        return dx, dw, None, None, None
 
 
 def _fused_combine_ok(ep: ExpertParallel, plan, down_local) -> bool:

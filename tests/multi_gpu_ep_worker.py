@@ -53,6 +53,8 @@ def main(out_path: str) -> None:
             losses.append(float(out["loss"]))
         eng.check()
         ep.check_overflow()
+        if fused:  # the fused expert-GEMM + combine kernel ran exactly where it was asked for
+            assert (getattr(ep, "fused_combines", 0) > 0) == (fuse_combine == "1"), (name, getattr(ep, "fused_combines", 0))
         results[name] = {"losses": losses, "grad_norm": float(out["grad_norm"])}
         set_current_ep(None)
     if rank == 0:
