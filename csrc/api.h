@@ -100,6 +100,9 @@ void ep_push_rows(const void* src, const int* dst_rank, const int64_t* dst_pos, 
                   int dim, int64_t cap_rows, int* overflow, cudaStream_t stream);
 void ep_pull_rows(void* out, const int* src_rank, const int64_t* src_pos, const PeerPtrs& bufs, int64_t rows, int dim,
                   int64_t cap_rows, cudaStream_t stream);
+// out[r] = scale[r] (or 1) * row at byte address row_src[r] (peer-mapped or local), zero row where the address is 0
+void ep_gather_rows(void* out, const unsigned long long* row_src, const float* row_scale, int64_t rows, int dim,
+                    cudaStream_t stream);
 
 // ---- comm/tp_gemm.cu: tensor-parallel GEMMs fused with their collective (bf16; T tokens over `world` ranks)
 // C[T,N] = gather(shards)[T,K] * op(B); the kernel itself fills `gathered` from the ranks' shards (peer memory)

@@ -313,6 +313,17 @@ void ep_pull_rows(torch::Tensor& out, const torch::Tensor& src_rank, const torch
                    (int)out.size(1), cap_rows, cur_stream());
 }
 
+// out [R, D] bf16; row_src int64 [R] byte addresses (0 = zero row); row_scale fp32 [R] or an empty tensor
+void ep_gather_rows(torch::Tensor& out, const torch::Tensor& row_src, const torch::Tensor& row_scale) {
+  TORCH_CHECK(out.is_contiguous() && out.scalar_type() == torch::kBFloat16 && out.dim() == 2 && out.size(1) % 8 == 0);
+  TORCH_CHECK(row_src.scalar_type() == torch::kInt64 && row_src.is_contiguous() && row_src.numel() == out.size(0));
+  const bool scaled = row_scale.numel() > 0;
+  if (scaled) TORCH_CHECK(row_scale.scalar_type() == torch::kFloat32 && row_scale.is_contiguous() && row_scale.numel() == out.size(0));
+  c10::cuda::CUDAGuard guard(out.device());
+  mt::ep_gather_rows(out.data_ptr(), reinterpret_cast<const unsigned long long*>(row_src.data_ptr<int64_t>()),
+                     scaled ? row_scale.data_ptr<float>() : nullptr, out.size(0), (int)out.size(1), cur_stream());
+}
+
 // c[M,N] = a[M,K] @ (b_kn ? b[K,N] : b[N,K]^T) on CTA pairs (bf16 in / out)
 void gemm_pair(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& c, bool b_kn, torch::Tensor& status) {
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16 && c.scalar_type() == torch::kBFloat16);
@@ -600,6 +611,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm_scatter", &grouped_gemm_scatter);
   m.def("ep_push_rows", &ep_push_rows);
   m.def("ep_pull_rows", &ep_pull_rows);
+  m.def("ep_gather_rows", &ep_gather_rows);
   m.def("gemm_pair", &gemm_pair);
   m.def("fp8_quantize", &fp8_quantize);
   m.def("gemm_fp8", &gemm_fp8);

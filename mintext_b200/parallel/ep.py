@@ -72,6 +72,7 @@ class ExpertParallel:
             "flag_ptrs": [int(p) for p in h_fl.buffer_ptrs], "handles": (h_in, h_out, h_fl, h_tag), "flags": flags,
             "tag": tagb.view(cap_rows, 8), "tag_ptrs": [int(p) for p in h_tag.buffer_ptrs],
             "out_ptr_table": torch.tensor([int(p) for p in h_out.buffer_ptrs], dtype=torch.int64, device=self.device),
+            "in_ptr_table": torch.tensor([int(p) for p in h_in.buffer_ptrs], dtype=torch.int64, device=self.device),
         }
         self.overflow = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.seq = 0
@@ -191,26 +192,35 @@ def _plan(ep: ExpertParallel, topk_idx: torch.Tensor, num_experts: int, cap: int
 
 
 def _dispatch_rows(x, ep, plan):
-    """Forward half of the dispatch: push this rank's (token, slot) rows and their return addresses to the expert
-    ranks; returns this rank's expert-contiguous, 128-padded input rows."""
+    """Forward half of the dispatch.  Every rank publishes its tokens in its symmetric buffer and sends each expert
+    rank one 16-byte record per routed (token, slot): (sender + 1, flat (token, slot) index, token row, routing
+    weight).  The expert rank then pulls the rows it was promised with one table-driven gather that also lays them
+    out expert-contiguous and 128-padded (zero rows in the padding).  Returns those rows; the records stay in
+    ``plan["tags"]`` as the rows' return addresses."""
     from mintext_b200.ops._ext import ext
 
-    b = ep.buffers(plan["cap"], x.shape[1])
-    rows = x.index_select(0, plan["src_token"])
-    b["in"].zero_()
-    b["tag"].zero_()
-    ep.barrier()  # every rank's receive buffer is cleared and no longer read
-    ext().ep_push_rows(rows, plan["dst_rank"], plan["dst_pos"], b["in_ptrs"], b["cap"], ep.overflow)
-    # the rows' return addresses travel with them: the fused expert-GEMM + combine kernel writes its output rows
-    # straight back to (sender rank, flat index)
-    tags = torch.zeros(rows.shape[0], 4, dtype=torch.int32, device=x.device)
+    N, D = x.shape
+    b = ep.buffers(plan["cap"], D)
+    R = plan["dst_rank"].numel()
+    tags = torch.empty(R, 4, dtype=torch.int32, device=x.device)
     tags[:, 0] = ep.rank + 1
-    tags[:, 1] = plan["sort_idx"].to(torch.int32)          # flat (token, slot) index: where the row goes home to
-    ext().ep_push_rows(tags.view(torch.bfloat16), plan["dst_rank"], plan["dst_pos"], b["tag_ptrs"], b["cap"],
-                       ep.overflow)
-    ep.barrier()  # all rows have landed
-    plan["tags"] = b["tag"][: plan["cap"]].view(torch.int32).clone()
-    return b["in"][: plan["cap"]].clone()
+    tags[:, 1] = plan["sort_idx"].to(torch.int32)
+    tags[:, 2] = plan["src_token"].to(torch.int32)
+    tags[:, 3] = plan["w_sorted"].view(torch.int32)
+    ep.barrier()  # nobody still reads this rank's buffers from an earlier exchange
+    b["in"][:N].copy_(x)
+    b["tag"].zero_()
+    ep.barrier()  # tokens published, record buffers cleared everywhere
+    ext().ep_push_rows(tags.view(torch.bfloat16), plan["dst_rank"], plan["dst_pos"], b["tag_ptrs"], b["cap"], ep.overflow)
+    ep.barrier()  # records have landed
+    got = b["tag"][: plan["cap"]].view(torch.int32).clone()
+    plan["tags"] = got
+    home = got[:, 0].long()
+    src = b["in_ptr_table"][(home - 1).clamp_min(0)] + got[:, 2].long() * (D * 2)
+    rows = torch.empty(plan["cap"], D, device=x.device, dtype=x.dtype)
+    ext().ep_gather_rows(rows, torch.where(home > 0, src, torch.zeros_like(src)).contiguous(), torch.empty(0, device=x.device))
+    ep.barrier()  # every rank has its rows: the token buffers may be reused
+    return rows
 
 
 def _return_addresses(b, tags: torch.Tensor, column: int, dim: int) -> torch.Tensor:
@@ -307,14 +317,21 @@ class _GroupedCombine(torch.autograd.Function):
         ep, plan = ctx.ep, ctx.plan
         N, K = plan["N"], plan["K"]
         st = status_word(h.device)
-        d_picked = (dy[:, None, :] * topk_w.to(dy.dtype)[:, :, None]).reshape(N * K, -1).contiguous()
+        D = dy.shape[1]
         dtw = torch.einsum("nkd,nd->nk", picked.view(N, K, -1).float(), dy.float()).to(topk_w.dtype)
-        b = ep.buffers(plan["cap"], dy.shape[1])
-        b["in"].zero_()
-        ep.barrier()
-        ext().ep_push_rows(d_picked, plan["rank_flat"], plan["pos_flat"], b["in_ptrs"], b["cap"], ep.overflow)
-        ep.barrier()
-        dy_p = b["in"][: plan["cap"]].clone()
+        b = ep.buffers(plan["cap"], D)
+        # the expert ranks pull dy[token] * routing weight for each of their rows (weights came with the dispatch
+        # records), so the weighted [N*K, D] gradient is never materialised on the home rank
+        tags = plan["tags"]
+        home = tags[:, 0].long()
+        src = b["in_ptr_table"][(home - 1).clamp_min(0)] + torch.div(tags[:, 1], K, rounding_mode="floor").long() * (D * 2)
+        ep.barrier()  # nobody still reads this rank's token buffer
+        b["in"][:N].copy_(dy)
+        ep.barrier()  # every rank's output gradient is published
+        dy_p = torch.empty(plan["cap"], D, device=dy.device, dtype=dy.dtype)
+        ext().ep_gather_rows(dy_p, torch.where(home > 0, src, torch.zeros_like(src)).contiguous(),
+                             tags[:, 3].contiguous().view(torch.float32))
+        ep.barrier()  # all pulls done: the buffers may be reused
         dh = torch.empty_like(h)
         ext().grouped_gemm(dy_p, w, dh, plan["off_local"], False, st)
         dw = None
@@ -390,6 +407,7 @@ def experts_forward_peer(ep: ExpertParallel, x, topk_idx, topk_w, gate_up_local,
     El = num_experts // ep.size
     cap = moe_ops.capacity(int(ep.capacity_factor * N * K), El)
     plan = _plan(ep, topk_idx, num_experts, cap)
+    plan["w_sorted"] = topk_w.detach().reshape(-1)[plan["sort_idx"]].float().contiguous()
     fused = _fused_combine_ok(ep, plan, down_local)
     if fused and x.shape[1] > 128 and x.dtype == torch.bfloat16:
         h = _DispatchGrouped.apply(x.contiguous(), gate_up_local, getattr(gate_up_local, "main_grad", None), ep, plan)
