@@ -245,9 +245,7 @@ flash_bwd_pipe64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         uint8_t* srow = box + lane * 128;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-          uint4 w = make_uint4(__float_as_uint(__uint_as_float(v[4 * g]) * sc), __float_as_uint(__uint_as_float(v[4 * g + 1]) * sc),
-                               __float_as_uint(__uint_as_float(v[4 * g + 2]) * sc), __float_as_uint(__uint_as_float(v[4 * g + 3]) * sc));
-          *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = w;
+          *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
         }
       }
       fence_proxy_async_smem();
@@ -300,9 +298,10 @@ flash_bwd_pipe64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             if (dead) pe = 0.f;
           }
           p[e] = pe;
-          float d = pe * (__uint_as_float(dv[e]) - dq4[u]);
+          // dS carries the softmax scale: (dP - delta) * scale is one FMA against the pre-scaled delta
+          float d = pe * fmaf(__uint_as_float(dv[e]), sc, -dq4[u]);
           if constexpr (CAP) d *= slope;
-          ds[e] = d;  // the softmax scale is applied once to dK (epilogue) and dQ (drain)
+          ds[e] = d;
         }
       }
       uint8_t* prow = pt_s + bsel * C::PT_BYTES + r * 128;
@@ -331,7 +330,8 @@ flash_bwd_pipe64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       if (lane * 4 < BQ) {
         reinterpret_cast<float4*>(stat)[lane] =
             make_float4(lse_n.x * kLog2e, lse_n.y * kLog2e, lse_n.z * kLog2e, lse_n.w * kLog2e);
-        reinterpret_cast<float4*>(stat + BQ)[lane] = delta_n;
+        reinterpret_cast<float4*>(stat + BQ)[lane] =
+            make_float4(delta_n.x * sc, delta_n.y * sc, delta_n.z * sc, delta_n.w * sc);
       }
       __syncwarp();
       if (t + 1 < n_steps) load_stats(t + 1, lse_n, delta_n);
@@ -369,7 +369,7 @@ flash_bwd_pipe64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       __syncwarp();
       // dV (first warp group) and dK (second): this warp's 32 key rows x 64 dims as one 4 KB box
       const int col = grp == 0 ? C::COL_DV : C::COL_DK;
-      const float osc = grp == 0 ? 1.f : sc;
+      constexpr float osc = 1.f;  // dS already carries the softmax scale
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
