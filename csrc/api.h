@@ -60,6 +60,11 @@ void rope_apply(const void* src, void* dst, const float* cos_t, const float* sin
 void gated_act_fwd(const void* gate_up, void* out, int64_t rows, int inter, int act, cudaStream_t stream);
 void gated_act_bwd(const void* gate_up, const void* dout, void* dgate_up, int64_t rows, int inter, int act,
                    cudaStream_t stream);
+// out = x * f(gate), f = sigmoid (mode 0) or silu (mode 1); x / gate rows at pitches xs / gs elements
+void gate_mul_fwd(const void* x, const void* gate, void* out, int64_t rows, int dim, int64_t xs, int64_t gs, int mode,
+                  cudaStream_t stream);
+void gate_mul_bwd(const void* x, const void* gate, const void* dout, void* dx, void* dgate, int64_t rows, int dim,
+                  int64_t xs, int64_t gs, int mode, cudaStream_t stream);
 
 // ---- elementwise/cross_entropy.cu
 // logits bf16 [rows, V] (row pitch ldl) -> per-row loss, z-loss, lse; overwrites logits with dlogits * grad_scale.

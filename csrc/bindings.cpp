@@ -115,6 +115,38 @@ void gated_act_bwd(const torch::Tensor& gate_up, const torch::Tensor& dout, torc
                     cur_stream());
 }
 
+static void check_gate_rows(const torch::Tensor& t, const char* what) {
+  TORCH_CHECK(t.dim() == 2 && t.scalar_type() == torch::kBFloat16 && t.stride(1) == 1 && t.stride(0) % 8 == 0 &&
+                  t.size(1) % 8 == 0 && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0,
+              what, ": want bf16 rows of a multiple of 8 elements at a 16-byte-aligned pitch");
+}
+
+// out[rows, dim] = x * f(gate); x and gate are 2-D views whose rows may be strided (mode 0 sigmoid, 1 silu)
+torch::Tensor gate_mul_fwd(const torch::Tensor& x, const torch::Tensor& gate, int64_t mode) {
+  check_gate_rows(x, "x");
+  check_gate_rows(gate, "gate");
+  TORCH_CHECK(x.sizes() == gate.sizes());
+  c10::cuda::CUDAGuard guard(x.device());
+  auto out = torch::empty({x.size(0), x.size(1)}, x.options());
+  mt::gate_mul_fwd(x.data_ptr(), gate.data_ptr(), out.data_ptr(), x.size(0), (int)x.size(1), x.stride(0), gate.stride(0),
+                   (int)mode, cur_stream());
+  return out;
+}
+
+// -> (dx, dgate), both contiguous [rows, dim]
+std::vector<torch::Tensor> gate_mul_bwd(const torch::Tensor& x, const torch::Tensor& gate, const torch::Tensor& dout,
+                                        int64_t mode) {
+  check_gate_rows(x, "x");
+  check_gate_rows(gate, "gate");
+  TORCH_CHECK(dout.is_contiguous() && dout.scalar_type() == torch::kBFloat16 && dout.sizes() == x.sizes());
+  c10::cuda::CUDAGuard guard(x.device());
+  auto dx = torch::empty({x.size(0), x.size(1)}, x.options());
+  auto dg = torch::empty({x.size(0), x.size(1)}, x.options());
+  mt::gate_mul_bwd(x.data_ptr(), gate.data_ptr(), dout.data_ptr(), dx.data_ptr(), dg.data_ptr(), x.size(0), (int)x.size(1),
+                   x.stride(0), gate.stride(0), (int)mode, cur_stream());
+  return {dx, dg};
+}
+
 void cross_entropy(torch::Tensor& logits, const torch::Tensor& targets, torch::Tensor& loss,
                    const c10::optional<torch::Tensor>& zloss, const c10::optional<torch::Tensor>& lse,
                    double label_smoothing, double z_weight, double softcap, double grad_scale, bool write_grad) {
@@ -598,6 +630,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_apply", &rope_apply);
   m.def("gated_act_fwd", &gated_act_fwd);
   m.def("gated_act_bwd", &gated_act_bwd);
+  m.def("gate_mul_fwd", &gate_mul_fwd);
+  m.def("gate_mul_bwd", &gate_mul_bwd);
   m.def("cross_entropy", &cross_entropy);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);

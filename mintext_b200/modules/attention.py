@@ -90,7 +90,7 @@ class Attention(nn.Module):
         o = F.attention(q, k, v, self.scale, causal=True, window=self.sliding_window,
                         softcap=self.attn_logit_softcapping)
         if gate is not None:
-            o = o * torch.sigmoid(gate)
+            o = F.gate_mul(o, gate, "sigmoid")
         y = tpm.row_linear(o.reshape(B * S, Hl * dh), tpm.as_matrix(self.out.kernel, Hl * dh), tp, self.dtype)
         return y.view(1, Tl, D)
 
@@ -124,5 +124,5 @@ class Attention(nn.Module):
                             softcap=self.attn_logit_softcapping)
         o = F.checkpoint_name(o, "context")
         if gate is not None:
-            o = o * torch.sigmoid(gate)
+            o = F.gate_mul(o, gate, "sigmoid")
         return self.out(o)

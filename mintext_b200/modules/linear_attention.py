@@ -86,5 +86,5 @@ class GatedDeltaRuleAttention(nn.Module):
             qh.float().transpose(1, 2), kh.float().transpose(1, 2), vh.float().transpose(1, 2),
             beta.transpose(1, 2), g.transpose(1, 2), chunk_size=self.chunk_size)
         out = out.transpose(1, 2).to(self.dtype)
-        out = self.norm(out.contiguous()) * torch.nn.functional.silu(z.to(self.dtype))
+        out = F.gate_mul(self.norm(out.contiguous()), z.to(self.dtype), "silu")
         return self.out_proj(out.reshape(B, S, value_total))

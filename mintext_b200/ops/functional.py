@@ -506,6 +506,50 @@ def gated_act(gate_up: torch.Tensor, act: str) -> torch.Tensor:
     return oracle.gated_act(gate_up, act)
 
 
+_GATE_MODES = {"sigmoid": 0, "silu": 1}
+
+
+def _rows_view(t: torch.Tensor, dim: int) -> torch.Tensor:
+    """``t`` as 2-D rows of its last dimension without copying when its leading dims collapse (a column block of a
+    fused projection does); otherwise a contiguous copy."""
+    try:
+        return t.view(-1, dim)
+    except RuntimeError:
+        return t.reshape(-1, dim)
+
+
+class _GateMulFn(torch.autograd.Function):
+    """``x * f(gate)`` in one pass (f = sigmoid: attention output gate; f = silu: gate after the GDN head norm)."""
+
+    @staticmethod
+    def forward(ctx, x, gate, mode):
+        d = x.shape[-1]
+        x2, g2 = _rows_view(x, d), _rows_view(gate, d)
+        out = ext().gate_mul_fwd(x2, g2, mode)
+        ctx.save_for_backward(x2, g2)
+        ctx.mode, ctx.shape = mode, x.shape
+        return out.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2, g2 = ctx.saved_tensors
+        dx, dg = ext().gate_mul_bwd(x2, g2, dout.reshape(x2.shape).contiguous(), ctx.mode)
+        return dx.view(ctx.shape), dg.view(ctx.shape), None
+
+
+def gate_mul(x: torch.Tensor, gate: torch.Tensor, kind: str) -> torch.Tensor:
+    """``x * sigmoid(gate)`` or ``x * silu(gate)`` (``kind``), gate possibly a strided column block."""
+    d = x.shape[-1]
+    if (use_cuda(x, gate) and x.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and x.shape == gate.shape
+            and d % 8 == 0 and hasattr(ext(), "gate_mul_fwd")):
+        g2 = _rows_view(gate, d)
+        x2 = _rows_view(x, d)
+        if g2.stride(0) % 8 == 0 and x2.stride(0) % 8 == 0 and g2.data_ptr() % 16 == 0 and x2.data_ptr() % 16 == 0:
+            return _GateMulFn.apply(x, gate, _GATE_MODES[kind])
+    f = torch.sigmoid(gate) if kind == "sigmoid" else torch.nn.functional.silu(gate)
+    return x * f.to(x.dtype)
+
+
 class _GateUpActFn(torch.autograd.Function):
     """``act(x @ Wg) * (x @ Wu)``: both projections write the column halves of one ``[T, 2M]`` buffer (strided
     GEMM outputs), the activation kernel reads it once; backward mirrors this with strided dgrad / wgrad

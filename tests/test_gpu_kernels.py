@@ -423,3 +423,29 @@ def test_mxfp8_mlp_matches_bf16_mlp():
     for name, a, b in zip(("y", "dx", "dw_gate", "dw_down"), outs[1], outs[0]):
         assert a is not None and _rel_err(a, b) < 0.08, (name, _rel_err(a, b))
 
+
+@pytest.mark.parametrize("kind", ["sigmoid", "silu"])
+def test_gate_mul_matches_torch_with_strided_gate(kind):
+    """x * f(gate) with the gate a column block of a wider projection (no copy), values and both gradients."""
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops._ext import check_status
+
+    torch.manual_seed(0)
+    B, S, H, dh = 2, 96, 4, 64
+    proj = torch.randn(B, S, H, 2 * dh, device="cuda").bfloat16().requires_grad_(True)
+    x = torch.randn(B, S, H, dh, device="cuda").bfloat16().requires_grad_(True)
+    _, gate = proj.chunk(2, dim=-1)
+    y = F.gate_mul(x, gate, kind)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    check_status()
+    xf, pf = x.detach().float().requires_grad_(True), proj.detach().float().requires_grad_(True)
+    gf = pf.chunk(2, dim=-1)[1]
+    ref = xf * (torch.sigmoid(gf) if kind == "sigmoid" else torch.nn.functional.silu(gf))
+    ref.backward(dy.float())
+    assert _rel_err(y, ref) < 1e-2
+    assert _rel_err(x.grad, xf.grad) < 1e-2
+    assert _rel_err(proj.grad[..., dh:], pf.grad[..., dh:]) < 1e-2
+    assert proj.grad[..., :dh].abs().max() == 0
+
