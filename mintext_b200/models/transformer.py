@@ -124,6 +124,17 @@ class DecoderLayer(nn.Module):
             self.pre_ffw_norm = RMSNorm(D, eps, dt)
             self.post_ffw_norm = RMSNorm(D, eps, dt)
         self.is_linear = layer_type == "linear_attention"
+        self.has_moe = config.num_experts > 0 and layer_idx >= config.first_k_dense_replace
+        # Under tensor parallelism the dense attention and MLP shard their weights; sub-layers without a sharded
+        # kernel path are built unsharded and computed in full on every rank of the group (parallel/tp.py).
+        from mintext_b200.parallel import tp as tpm
+
+        tp = tpm.current_tp()
+        tp_on = tp is not None and tp.size > 1
+        self.attn_replicated = tp_on and (self.is_linear or config.attention_type == "mla")
+        self.mlp_replicated = tp_on and self.has_moe
+        if self.attn_replicated:
+            tpm.set_current_tp(None)
         if self.is_linear:
             self.attention = GatedDeltaRuleAttention(config, rngs=rngs)
         elif config.attention_type == "mla":
@@ -135,15 +146,29 @@ class DecoderLayer(nn.Module):
                 config, rngs=rngs, mesh=mesh, use_qk_norm=config.use_qk_norm, sliding_window=sliding,
                 use_gate=(config.model_type == "qwen3_next" and layer_type == "full_attention"),
                 rope_local_theta=local_theta)
-        self.has_moe = config.num_experts > 0 and layer_idx >= config.first_k_dense_replace
+        tpm.set_current_tp(None if self.mlp_replicated else tp)
         self.mlp = MoEBlock(config, rngs=rngs) if self.has_moe else MLP(config, rngs=rngs, mesh=mesh)
+        tpm.set_current_tp(tp)
+        if self.attn_replicated:
+            tpm.mark_replicated(self.attention)
+        if self.mlp_replicated:
+            tpm.mark_replicated(self.mlp)
 
     def _attend(self, h, positions, mask, default_positions):
+        if self.attn_replicated:
+            from mintext_b200.parallel import tp as tpm
+
+            fn = self.attention if self.is_linear else (lambda t: self.attention(t, positions, mask, default_positions))
+            return tpm.run_replicated(fn, h, tpm.current_tp())[0]
         if self.is_linear:
             return self.attention(h)
         return self.attention(h, positions, mask, default_positions)
 
     def _ffw(self, h):
+        if self.mlp_replicated:
+            from mintext_b200.parallel import tp as tpm
+
+            return tpm.run_replicated(self.mlp, h, tpm.current_tp())
         if self.has_moe:
             return self.mlp(h)
         return self.mlp(h), None

@@ -256,6 +256,16 @@ class TrainEngine:
         bc1 = 1.0 - cfg.adam_b1 ** t
         bc2 = 1.0 - cfg.adam_b2 ** t
 
+        # sub-layers that every rank of a tensor-parallel group computes in full hold identical gradients there
+        # (of the group's summed loss): divide by the group size so that the cross-rank sum counts them once
+        from mintext_b200.parallel.tp import current_tp
+
+        tp = current_tp()
+        if tp is not None and tp.size > 1:
+            for grp in (self.big, self.small):
+                for s in grp.slots:
+                    if getattr(s.param, "tp_replicated_compute", False):
+                        s.param.main_grad.mul_(1.0 / tp.size)
         # 1. gradient reduction
         if W > 1:
             if self.use_fused:

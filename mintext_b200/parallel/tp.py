@@ -72,6 +72,63 @@ class _AllGatherTokens(torch.autograd.Function):
         return _reduce_scatter(g.contiguous(), ctx.group), None
 
 
+class _GatherForReplicated(torch.autograd.Function):
+    """All-gather of the token shards in front of a sub-layer that every rank of the group computes in full (it has
+    no sharded kernel path).  The full computation back-propagates the gradient of the *sum* of the ranks' losses,
+    the same on every rank, so the backward is just this rank's rows - no reduction."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        out = torch.empty((tp.size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=tp.group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        n = g.shape[0] // ctx.tp.size
+        return g[ctx.tp.rank * n:(ctx.tp.rank + 1) * n].contiguous(), None
+
+
+class _SliceFromReplicated(torch.autograd.Function):
+    """This rank's token rows of a replicated sub-layer's output; backward gathers every rank's output gradient so
+    that the replicated backward sees all of them."""
+
+    @staticmethod
+    def forward(ctx, y, tp):
+        ctx.tp = tp
+        n = y.shape[0] // tp.size
+        return y[tp.rank * n:(tp.rank + 1) * n].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        tp = ctx.tp
+        out = torch.empty((tp.size * g.shape[0],) + tuple(g.shape[1:]), dtype=g.dtype, device=g.device)
+        dist.all_gather_into_tensor(out, g.contiguous(), group=tp.group)
+        return out, None
+
+
+def run_replicated(fn, h: torch.Tensor, tp: "TensorParallel"):
+    """Run ``fn`` (a sub-layer without a tensor-parallel kernel path: multi-head-latent attention, Gated Delta Rule,
+    mixture of experts) on the whole ``[B, S, D]`` batch on every rank of the group and return this rank's token
+    rows of its output (plus ``fn``'s auxiliary output, if it returns a pair).  The parameters of such a sub-layer
+    carry ``tp_replicated_compute``: their gradients are identical on all ranks of the group and the engine divides
+    them by the group size before the cross-rank sum."""
+    B, S = tp.batch_shape
+    D = h.shape[-1]
+    full = _GatherForReplicated.apply(h.reshape(-1, D), tp).view(B, S, D)
+    out = fn(full)
+    aux = None
+    if isinstance(out, tuple):
+        out, aux = out
+    return _SliceFromReplicated.apply(out.reshape(B * S, -1), tp).view(1, -1, out.shape[-1]), aux
+
+
+def mark_replicated(module: torch.nn.Module) -> None:
+    for p in module.parameters():
+        p.tp_replicated_compute = True
+
+
 class _ReduceScatterTokens(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):

@@ -63,8 +63,9 @@ def train(config: MinTextConfig) -> dict:
     if config.ici_tensor_parallelism > 1:
         from mintext_b200.parallel.tp import TensorParallel, set_current_tp
 
-        if config.num_experts > 0 or config.attention_type == "mla" or "linear_attention" in config.layer_types:
-            raise NotImplementedError("tensor parallelism covers dense MHA/GQA models")
+        if config.ici_expert_parallelism > 1:
+            raise NotImplementedError("expert parallelism and tensor parallelism cannot be combined: experts are "
+                                      "computed in full on every rank of a tensor-parallel group")
         set_current_tp(TensorParallel(mesh.group(("tensor",)), device, fused=config.fused_collectives))
         if mesh.shape["data"] * mesh.shape["fsdp"] > 1:
             local_reduce_group = mesh.group(("data", "fsdp"))

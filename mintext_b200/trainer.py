@@ -154,7 +154,14 @@ def compute_loss(params, model, config, batch, loss_scale: float | None = None):
         if "aux_loss" in aux and config.router_aux_loss_coef > 0:
             aux_loss = aux["aux_loss"] if aux_loss is None else aux_loss + aux["aux_loss"]
     if aux_loss is not None:
-        loss = loss + config.router_aux_loss_coef * aux_loss * (scale * ntok)
+        # under tensor parallelism the router runs on the whole batch on every rank of the group while the token
+        # loss is this rank's share; the engine averages the ranks' gradients, so the replicated term counts
+        # group-size times here
+        from mintext_b200.parallel.tp import current_tp
+
+        tp = current_tp()
+        rep = float(tp.size) if (tp is not None and tp.size > 1) else 1.0
+        loss = loss + config.router_aux_loss_coef * aux_loss * (scale * ntok) * rep
     out_aux = {
         "loss": loss.detach(),
         "z_loss": z.detach().mean(),

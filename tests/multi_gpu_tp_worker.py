@@ -14,10 +14,23 @@ import torch.distributed as dist
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 
-def tp_config(fused: bool, tp: int):
+MIXED = {  # families whose attention / feed-forward has no sharded path: computed in full on every rank
+    "deepseek": dict(model_type="deepseek_v3", attention_type="mla", q_lora_rank=128, kv_lora_rank=128,
+                     qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, num_experts=8, num_experts_per_tok=2,
+                     moe_intermediate_size=128, n_group=4, topk_group=2, first_k_dense_replace=1, n_shared_experts=1),
+    "qwen3_next": dict(model_type="qwen3_next", use_qk_norm=True, full_attention_interval=2, partial_rotary_factor=0.25,
+                       linear_key_head_dim=64, linear_value_head_dim=64, linear_num_key_heads=2,
+                       linear_num_value_heads=4, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
+                       n_group=1, topk_group=1, first_k_dense_replace=0, router_type="softmax_topk",
+                       shared_expert_gate=True, n_shared_experts=1, router_aux_loss_coef=0.01),
+}
+
+
+def tp_config(fused: bool, tp: int, kind: str = "dense"):
     from mintext_b200 import MinTextConfig
 
-    return MinTextConfig(num_hidden_layers=2, hidden_size=512, num_attention_heads=8, num_key_value_heads=8, head_dim=64,
+    extra = MIXED.get(kind, {})
+    return MinTextConfig(**extra, num_hidden_layers=2, hidden_size=512, num_attention_heads=8, num_key_value_heads=8, head_dim=64,
                          intermediate_size=1024, vocab_size=1024, seq_length=128, steps=20, learning_rate=1e-3,
                          enable_tensorboard=False, enable_checkpointing=False, fused_collectives=fused,
                          ici_tensor_parallelism=tp)
@@ -77,7 +90,7 @@ def op_level(dev, rank, world):
     return errs
 
 
-def main(out_path: str) -> None:
+def main(out_path: str, kind: str = "dense") -> None:
     rank = int(os.environ["RANK"])
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -89,13 +102,15 @@ def main(out_path: str) -> None:
     from mintext_b200.parallel.tp import TensorParallel, set_current_tp
 
     world = dist.get_world_size()
-    results = {"ops": op_level(dev, rank, world)}
-    check_status(dev)
-    assert results["ops"]["gathered"] == 0.0 and all(v < 2e-2 for v in results["ops"].values()), results["ops"]
+    results = {}
+    if kind == "dense":
+        results["ops"] = op_level(dev, rank, world)
+        check_status(dev)
+        assert results["ops"]["gathered"] == 0.0 and all(v < 2e-2 for v in results["ops"].values()), results["ops"]
     g = torch.Generator().manual_seed(7)
     tok = torch.randint(0, 1024, (8, 128), generator=g).to(dev)  # one tensor-parallel group: all ranks share the batch
-    for name, fused in (("fused", True), ("nccl", False)):
-        cfg = tp_config(fused, world)
+    for name, fused in (("fused", True), ("nccl", False)) if kind == "dense" else (("fused", True),):
+        cfg = tp_config(fused, world, kind)
         set_current_tp(TensorParallel(dist.group.WORLD, dev, fused=fused))
         eng = TrainEngine(Transformer(cfg, rngs=0), cfg, device=dev)
         losses = []
@@ -112,4 +127,4 @@ def main(out_path: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1])
+    main(*sys.argv[1:3])

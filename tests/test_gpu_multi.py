@@ -137,6 +137,37 @@ def test_tensor_parallel_fused_kernels(tmp_path):
         assert abs(a - b) < 1e-2
 
 
+@pytest.mark.parametrize("kind", ["deepseek", "qwen3_next"])
+def test_tensor_parallel_with_replicated_sublayers_matches_single_gpu(tmp_path, kind):
+    """Families whose attention (multi-head latent, Gated Delta Rule) or feed-forward (mixture of experts) has no
+    sharded path train under tensor parallelism with those sub-layers computed in full on every rank; the dense
+    attention / MLP layers between them stay sharded.  Losses follow the single-GPU run."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    out = tmp_path / "tp.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29677", str(ROOT / "tests" / "multi_gpu_tp_worker.py"), str(out),
+           kind]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.loads(out.read_text())
+    sys.path.insert(0, str(ROOT / "tests"))
+    from multi_gpu_tp_worker import tp_config
+
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.engine import TrainEngine
+
+    cfg = tp_config(True, 1, kind)
+    eng = TrainEngine(Transformer(cfg, rngs=0), cfg, device="cuda")
+    tok = torch.randint(0, 1024, (8, 128), generator=torch.Generator().manual_seed(7)).cuda()
+    single = [float(eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=1)["loss"]) for _ in range(5)]
+    eng.check()
+    for a, b in zip(res["fused"]["losses"], single):
+        assert abs(a - b) < 5e-2, (res["fused"]["losses"], single)
+
+
 @pytest.mark.parametrize("optimizer", ["adamw", "muon"])
 def test_checkpoint_saved_on_two_gpus_restores_on_one(tmp_path, optimizer):
     """Resharding: the flat optimizer state written as one chunk per rank by a 2-GPU run restores into a 1-GPU
