@@ -2,9 +2,11 @@
 // the multi-head-latent shape with 192-wide queries/keys and 128-wide values).
 //
 // One CTA = one (batch, head, 128-query-row block).  Roles:
-//   warps 0-3  softmax      : thread r owns query row r.  Reads S = Q K^T from tensor memory (tcgen05.ld), keeps the
-//                             running max / sum, rescales the O accumulator in TMEM only when some row's max moved,
-//                             writes P (bf16) into 128B-swizzled shared memory as the A operand of the second MMA.
+//   warps 0-3  softmax      : thread r owns query row r.  Reads S = Q K^T from tensor memory (tcgen05.ld) ONCE per
+//                             block: probabilities are formed against a lazily updated reference (any value within
+//                             2^12 of the row maximum keeps bf16 / fp32 in range), the row maximum is tracked on the
+//                             side, and only when a row outgrows the reference is O rescaled in TMEM and the block
+//                             redone.  P (bf16) goes to 128B-swizzled shared memory as the A operand of the second MMA.
 //   warp 4     TMA producer : Q once, then K/V blocks through a 2-stage ring (non-multicast tile loads).
 //   warp 5     MMA issuer   : S = Q K^T (M=128, N=BN, K=dh) and O += P V (M=128, N=dh, K=BN) with tcgen05.mma,
 //                             accumulators in TMEM (S: BN columns, O: dh columns -> 256 columns per CTA).
@@ -207,52 +209,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float cap_l2 = CAP ? args.softcap * kLog2e : 0.f;
     bool ok = true;
 
-    auto softmax_block = [&](auto mask_tag, int i) -> bool {
+    // One pass over a score block: probabilities relative to the reference `M_ref` (log2 units) -> bf16 -> swizzled
+    // shared memory; returns their sum and, with TRACK, the block's raw row maximum.
+    auto exp_pass = [&](auto mask_tag, auto track_tag, int i, float M_ref, float& m_blk) -> float {
       constexpr bool MASK = decltype(mask_tag)::value;
+      constexpr bool TRACK = decltype(track_tag)::value;
       const int key0 = (j_begin + i) * BN;
-      // pass 1: block row max of the raw scores
-      float m_blk = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_row + C::S_COL + c * 32, v);
-        tc_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float x = __uint_as_float(v[e]);
-          if constexpr (MASK) {
-            const int kidx = key0 + c * 32 + e;
-            const bool dead = (args.causal && kidx > q_idx) || (args.window > 0 && q_idx - kidx >= args.window);
-            if (dead) x = -INFINITY;
-          }
-          m_blk = fmaxf(m_blk, x);
-        }
-      }
-      const float m_new = fmaxf(m_raw, m_blk);
-      float M_new;
-      if (m_new == -INFINITY) M_new = 0.f;
-      else M_new = CAP ? cap_l2 * tanhf(m_new * sc_over_cap) : m_new * c1;
-      const float alpha = (m_raw == -INFINITY) ? 0.f : exp2f(M_l2 - M_new);
-      // O(i-1) must have landed before P is overwritten or O rescaled
-      if (i > 0) {
-        if (!mbar_wait_warp(pv_done, (i - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) return false;
-        tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll
-          for (int c = 0; c < DV / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(t_row + C::O_COL + c * 32, o);
-            tc_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tmem_st_32x32b_x32(t_row + C::O_COL + c * 32, o);
-          }
-          tc_wait_st();
-        }
-      }
-      // pass 2: probabilities -> bf16 -> swizzled shared memory
       float l_blk = 0.f;
-#pragma unroll
+      constexpr int kUnroll = BN == 128 ? 2 : 1;  // measured: more unrolling spills, less exposes the load latency
+#pragma unroll kUnroll
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(t_row + C::S_COL + c * 32, v);
@@ -262,12 +227,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int e = 0; e < 32; ++e) {
           const float x = __uint_as_float(v[e]);
           float pe;
-          if constexpr (CAP) pe = exp2f(fmaf(tanhf(x * sc_over_cap), cap_l2, -M_new));
-          else pe = exp2f(fmaf(x, c1, -M_new));
+          if constexpr (CAP) pe = exp2f(fmaf(tanhf(x * sc_over_cap), cap_l2, -M_ref));
+          else pe = exp2f(fmaf(x, c1, -M_ref));
           if constexpr (MASK) {
             const int kidx = key0 + c * 32 + e;
             const bool dead = (args.causal && kidx > q_idx) || (args.window > 0 && q_idx - kidx >= args.window);
             if (dead) pe = 0.f;
+            if constexpr (TRACK) m_blk = fmaxf(m_blk, dead ? -INFINITY : x);
+          } else {
+            if constexpr (TRACK) m_blk = fmaxf(m_blk, x);
           }
           p[e] = pe;
           l_blk += pe;
@@ -284,6 +252,71 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = w;
         }
       }
+      return l_blk;
+    };
+
+    // The softmax reference M_l2 only has to keep the exponentials in range (bf16 and fp32 share the exponent width),
+    // not to equal the running maximum.  After the first block a block is therefore processed in ONE pass against the
+    // current reference while its maximum is tracked on the side; only when some row of the warp outgrows the
+    // reference by more than kSlack (log2 units), or had no live key so far, the reference moves, O is rescaled
+    // and the block's probabilities are recomputed.
+    constexpr float kSlack = 12.f;
+    auto softmax_block = [&](auto mask_tag, int i) -> bool {
+      constexpr bool MASK = decltype(mask_tag)::value;
+      const int key0 = (j_begin + i) * BN;
+      float m_blk = -INFINITY;
+      if (i > 0) {
+        // O(i-1) has landed (its MMAs precede this block's score MMA): P may be overwritten and O rescaled
+        if (!mbar_wait_warp(pv_done, (i - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) return false;
+        tc_fence_after_sync();
+        const float l_blk = exp_pass(mask_tag, std::true_type{}, i, M_l2, m_blk);
+        bool grow = false;
+        if (m_blk != -INFINITY) {
+          const float t_blk = CAP ? cap_l2 * tanhf(m_blk * sc_over_cap) : m_blk * c1;
+          grow = (m_raw == -INFINITY) || (t_blk - M_l2 > kSlack);
+        }
+        if (!__any_sync(0xffffffffu, grow)) {
+          l_run += l_blk;
+          return true;
+        }
+      } else {
+        // first block: row maximum of the raw scores
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_row + C::S_COL + c * 32, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            float x = __uint_as_float(v[e]);
+            if constexpr (MASK) {
+              const int kidx = key0 + c * 32 + e;
+              const bool dead = (args.causal && kidx > q_idx) || (args.window > 0 && q_idx - kidx >= args.window);
+              if (dead) x = -INFINITY;
+            }
+            m_blk = fmaxf(m_blk, x);
+          }
+        }
+      }
+      const float m_new = fmaxf(m_raw, m_blk);
+      float M_new;
+      if (m_new == -INFINITY) M_new = 0.f;
+      else M_new = CAP ? cap_l2 * tanhf(m_new * sc_over_cap) : m_new * c1;
+      const float alpha = (m_raw == -INFINITY) ? 0.f : exp2f(M_l2 - M_new);
+      if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+        for (int c = 0; c < DV / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(t_row + C::O_COL + c * 32, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st_32x32b_x32(t_row + C::O_COL + c * 32, o);
+        }
+        tc_wait_st();
+      }
+      float unused = 0.f;
+      const float l_blk = exp_pass(mask_tag, std::false_type{}, i, M_new, unused);
       l_run = l_run * alpha + l_blk;
       m_raw = m_new;
       M_l2 = M_new;
