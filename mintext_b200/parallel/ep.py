@@ -157,13 +157,19 @@ def experts_forward_collective(ep: ExpertParallel, x, topk_idx, topk_w, gate_up_
 
 # ------------------------------------------------------------------------------------------ peer-memory path
 def _plan(ep: ExpertParallel, topk_idx: torch.Tensor, num_experts: int, cap: int):
-    """Device-side routing plan: for every local (token, slot) row its destination rank and padded position, and
-    the padded offsets of this rank's own experts."""
+    """Device-side routing plan, in flat (token, slot) order: for every local entry its destination rank and its
+    row in that rank's expert-contiguous, 128-padded buffer, plus the padded offsets of this rank's own experts.
+    The per-expert counts and the stable rank of every entry inside its expert come from the counting-sort kernel
+    (no host synchronisation); the only collective is the all-gather of the counts."""
+    from mintext_b200.ops import moe as moe_ops
+    from mintext_b200.ops._ext import ext
+
     N, K = topk_idx.shape
     E, R = num_experts, ep.size
     El = E // R
-    flat = topk_idx.reshape(-1)
-    counts = torch.bincount(flat, minlength=E)
+    flat = topk_idx.reshape(-1).contiguous()
+    counts, off_l, pos_l, _ = ext().moe_sort(flat, E, moe_ops.capacity(flat.numel(), E))
+    within = pos_l - off_l.long()[flat]                         # stable rank of the entry among its expert's entries
     all_counts = torch.empty(R, E, dtype=counts.dtype, device=counts.device)
     dist.all_gather_into_tensor(all_counts, counts, group=ep.group)
     total = all_counts.sum(0)                                   # rows per global expert
@@ -171,22 +177,13 @@ def _plan(ep: ExpertParallel, topk_idx: torch.Tensor, num_experts: int, cap: int
     off = torch.zeros(R, El + 1, dtype=torch.int64, device=flat.device)
     off[:, 1:] = torch.cumsum(padded.view(R, El), dim=1)        # padded offsets inside each destination rank
     before = torch.cumsum(all_counts, 0) - all_counts           # rows of earlier source ranks, per expert
-    sort_idx = torch.argsort(flat, stable=True)
-    e_sorted = flat[sort_idx]
-    off_u = torch.zeros(E + 1, dtype=torch.int64, device=flat.device)
-    off_u[1:] = torch.cumsum(counts, 0)
-    within = torch.arange(flat.numel(), device=flat.device) - off_u[e_sorted]
-    dst_rank = torch.div(e_sorted, El, rounding_mode="floor")
-    dst_pos = off[dst_rank, e_sorted % El] + before[ep.rank][e_sorted] + within
-    src_token = torch.div(sort_idx, K, rounding_mode="floor")
-    # flat (n, k) order for the combine
-    rank_flat = torch.empty_like(dst_rank)
-    pos_flat = torch.empty_like(dst_pos)
-    rank_flat[sort_idx] = dst_rank
-    pos_flat[sort_idx] = dst_pos
+    dst_rank = torch.div(flat, El, rounding_mode="floor")
+    dst_pos = off[dst_rank, flat % El] + before[ep.rank][flat] + within
+    idx = torch.arange(flat.numel(), device=flat.device)
+    dst_rank32 = dst_rank.to(torch.int32)
     return {
-        "src_token": src_token, "sort_idx": sort_idx, "dst_rank": dst_rank.to(torch.int32), "dst_pos": dst_pos,
-        "rank_flat": rank_flat.to(torch.int32), "pos_flat": pos_flat,
+        "src_token": torch.div(idx, K, rounding_mode="floor"), "sort_idx": idx, "dst_rank": dst_rank32, "dst_pos": dst_pos,
+        "rank_flat": dst_rank32, "pos_flat": dst_pos,
         "off_local": off[ep.rank].to(torch.int32).contiguous(), "cap": cap, "N": N, "K": K,
     }
 
@@ -307,7 +304,9 @@ class _GroupedCombine(torch.autograd.Function):
         picked = b["out"][: N * K].clone()
         ctx.save_for_backward(h, w, picked, topk_w)
         ctx.ep, ctx.plan, ctx.main_grad = ep, plan, main_grad
-        return torch.einsum("nkd,nk->nd", picked.view(N, K, -1), topk_w.to(picked.dtype))
+        # weighted sum of each token's K adjacent rows (row-reduction kernel of the single-GPU path, identity index)
+        out, _ = ext().moe_combine_rows(picked, plan["sort_idx"], topk_w.detach().float().contiguous(), N, K, True, None)
+        return out
 
     @staticmethod
     def backward(ctx, dy):
@@ -318,7 +317,9 @@ class _GroupedCombine(torch.autograd.Function):
         N, K = plan["N"], plan["K"]
         st = status_word(h.device)
         D = dy.shape[1]
-        dtw = torch.einsum("nkd,nd->nk", picked.view(N, K, -1).float(), dy.float()).to(topk_w.dtype)
+        dy = dy.contiguous()
+        _, dtw = ext().moe_combine_rows(picked, plan["sort_idx"], None, N, K, False, dy)
+        dtw = dtw.to(topk_w.dtype)
         b = ep.buffers(plan["cap"], D)
         # the expert ranks pull dy[token] * routing weight for each of their rows (weights came with the dispatch
         # records), so the weighted [N*K, D] gradient is never materialised on the home rank
