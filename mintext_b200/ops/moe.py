@@ -157,7 +157,7 @@ def router_softmax_topk(logits, top_k, norm_topk_prob, scaling: float = 1.0):
     kernel's outputs (a histogram and a column mean)."""
     idx, w, probs = _RouterFn.apply(logits.contiguous(), None, 1, int(top_k), 0, 0, bool(norm_topk_prob), float(scaling))
     N, E = probs.shape
-    f = torch.bincount(idx.reshape(-1), minlength=E).float() / (N * top_k)
+    f = oracle.histogram(idx, E).float() / (N * top_k)
     aux = E * (f * probs.mean(0)).sum()
     return idx, w, probs, aux
 

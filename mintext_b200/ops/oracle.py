@@ -38,6 +38,13 @@ def activation(name: str):
     return table[name]
 
 
+def histogram(indices: torch.Tensor, bins: int) -> torch.Tensor:
+    """Occurrences of ``0..bins-1`` in ``indices`` (int64).  Unlike ``torch.bincount`` this never copies a size back
+    to the host, so the launching thread keeps running ahead of the device."""
+    flat = indices.reshape(-1)
+    return torch.zeros(bins, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
+
+
 ACT_CODES = {"silu": 0, "gelu_pytorch_tanh": 1, "gelu": 2, "relu": 3}
 
 

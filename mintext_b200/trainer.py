@@ -150,7 +150,7 @@ def compute_loss(params, model, config, batch, loss_scale: float | None = None):
     for aux in aux_list:
         if aux is None:
             continue
-        counts.append(torch.bincount(aux["topk_indices"].reshape(-1), minlength=config.num_experts))
+        counts.append(oracle.histogram(aux["topk_indices"], config.num_experts))
         if "aux_loss" in aux and config.router_aux_loss_coef > 0:
             aux_loss = aux["aux_loss"] if aux_loss is None else aux_loss + aux["aux_loss"]
     if aux_loss is not None:
