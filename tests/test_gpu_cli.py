@@ -43,7 +43,12 @@ def test_single_gpu_cli_checkpoint_and_resume(tmp_path):
 @pytest.mark.parametrize("extra", [["ici_tensor_parallelism=2"],
                                    ["ici_expert_parallelism=2", "num_experts=4", "num_experts_per_tok=2",
                                     "moe_intermediate_size=128", "n_group=1", "topk_group=1", "first_k_dense_replace=1",
-                                    "model_type=deepseek_v3", "attention_type=mha"]])
+                                    "model_type=deepseek_v3", "attention_type=mha"],
+                                   # tensor parallelism around sub-layers that run replicated (MLA, experts)
+                                   ["ici_tensor_parallelism=2", "num_experts=4", "num_experts_per_tok=2",
+                                    "moe_intermediate_size=128", "n_group=1", "topk_group=1", "first_k_dense_replace=1",
+                                    "model_type=deepseek_v3", "attention_type=mla", "q_lora_rank=64", "kv_lora_rank=64",
+                                    "qk_nope_head_dim=128", "qk_rope_head_dim=64", "v_head_dim=128"]])
 def test_two_gpu_cli_tensor_and_expert_parallel(tmp_path, extra):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
