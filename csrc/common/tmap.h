@@ -21,6 +21,14 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 inline EncodeTiledFn get_encode_tiled() {
+  // The encoder is a driver-API call and needs a context current in the calling thread.  A thread that has only
+  // ever been handed cached device memory (an autograd worker whose first operation is one of these GEMMs) has
+  // none yet: the runtime binds the primary context lazily on its first runtime call, so make one here.
+  thread_local bool context_bound = false;
+  if (!context_bound) {
+    MT_CUDA_CHECK(cudaFree(nullptr));
+    context_bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;

@@ -53,7 +53,7 @@ def build_cuda(verbose: bool = False) -> Path:
 
 def build_io(verbose: bool = False) -> Path | None:
     """Host-only C++ runtime (data index builders, mmap reader, async checkpoint writer)."""
-    src = sorted(str(p) for p in (CSRC / "io").glob("*.cpp"))
+    src = sorted(str(p) for p in (CSRC / "io").glob("*.cpp") if p.name != "io_selftest.cpp")  # that one has a main()
     if not src:
         return None
     from torch.utils import cpp_extension
