@@ -81,3 +81,98 @@ def test_gated_act_random_shapes(rows, i8, act, seed):
     ref.backward(dy.float())
     assert _rel(y, ref) < 1e-2
     assert _rel(gu.grad, gr.grad) < 2e-2
+
+
+@settings(**SETTINGS)
+@given(b=st.integers(1, 2), s128=st.integers(1, 5), hkv=st.integers(1, 3), group=st.integers(1, 3),
+       shape=st.sampled_from([(64, 64), (128, 128), (256, 256), (192, 128)]), causal=st.booleans(),
+       window=st.sampled_from([None, 96, 200]), softcap=st.sampled_from([None, 30.0]), seed=st.integers(0, 1000))
+def test_attention_random_shapes(b, s128, hkv, group, shape, causal, window, softcap, seed):
+    from mintext_b200.ops import oracle
+    from mintext_b200.ops._ext import check_status
+    from mintext_b200.ops.attention import flash_attention
+
+    d, dv = shape
+    S, H = 128 * s128, hkv * group
+    if window is not None and not causal:
+        window = None
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.randn(b, S, H, d, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    k = torch.randn(b, S, hkv, d, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    v = torch.randn(b, S, hkv, dv, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    scale = d ** -0.5
+    o = flash_attention(q, k, v, scale, causal, window, softcap)
+    do = torch.randn(o.shape, device="cuda", generator=g).bfloat16()
+    o.backward(do)
+    torch.cuda.synchronize()
+    check_status()
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = oracle.attention(qf, kf, vf, scale, causal, window, softcap)
+    ref.backward(do.float())
+    assert _rel(o, ref) < 2e-2
+    assert _rel(v.grad, vf.grad) < 3e-2
+    assert _rel(k.grad, kf.grad) < 3e-2
+    assert _rel(q.grad, qf.grad) < 3e-2
+
+
+@settings(**SETTINGS)
+@given(sizes=st.lists(st.integers(0, 300), min_size=1, max_size=9), k8=st.integers(1, 40), n8=st.integers(1, 60),
+       seed=st.integers(0, 1000))
+def test_grouped_matmul_random_groups(sizes, k8, n8, seed):
+    from mintext_b200.ops import moe as moe_ops
+    from mintext_b200.ops._ext import check_status
+
+    if sum(sizes) == 0:
+        sizes = sizes[:-1] + [5]
+    K, N, E = 8 * k8, 8 * n8, len(sizes)
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    M = sum(sizes)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(E, K, N, device="cuda", generator=g) * K ** -0.5).bfloat16()
+    gs = torch.tensor(sizes, device="cuda")
+    y = moe_ops.grouped_matmul_cuda(x, w, gs)
+    dw = moe_ops.tgmm_cuda(x, y, gs)
+    torch.cuda.synchronize()
+    check_status()
+    ref = torch.zeros(M, N, device="cuda")
+    dw_ref = torch.zeros(E, K, N, device="cuda")
+    r0 = 0
+    for e, n in enumerate(sizes):
+        ref[r0:r0 + n] = x[r0:r0 + n].float() @ w[e].float()
+        dw_ref[e] = x[r0:r0 + n].float().t() @ y[r0:r0 + n].float()
+        r0 += n
+    assert _rel(y, ref) < 1e-2
+    assert _rel(dw, dw_ref) < 2e-2
+
+
+@settings(**SETTINGS)
+@given(n=st.integers(1, 600), d8=st.integers(1, 40), v=st.integers(9, 3000), is_vd=st.booleans(),
+       ls=st.sampled_from([0.0, 0.1]), zw=st.sampled_from([0.0, 1e-3]), cap=st.sampled_from([None, 30.0]),
+       seed=st.integers(0, 1000))
+def test_linear_cross_entropy_random_shapes(n, d8, v, is_vd, ls, zw, cap, seed):
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops import oracle
+    from mintext_b200.ops._ext import check_status
+
+    d = 8 * d8
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    h = torch.randn(n, d, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    w = (torch.randn((v, d) if is_vd else (d, v), device="cuda", generator=g) * d ** -0.5).bfloat16().requires_grad_(True)
+    if not is_vd and v % 8 != 0:
+        return  # [hidden, vocab] storage needs a 16-byte row pitch
+    t = torch.randint(0, v, (n,), device="cuda", generator=g)
+    scale = 1.0 / n
+    per_tok, z = F.linear_cross_entropy(h, w, t, weight_is_vd=is_vd, label_smoothing=ls, z_loss_weight=zw, softcap=cap,
+                                        chunk_rows=256, loss_scale=scale)
+    (per_tok.sum() * scale).backward()
+    torch.cuda.synchronize()
+    check_status()
+    hf, wf = h.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    logits = hf @ (wf.t() if is_vd else wf)
+    if cap is not None:
+        logits = torch.tanh(logits / cap) * cap
+    ref, _ = oracle.cross_entropy(logits, t, ls, zw)
+    (ref.sum() * scale).backward()
+    assert _rel(per_tok, ref) < 2e-2
+    assert _rel(h.grad, hf.grad) < 4e-2
+    assert _rel(w.grad, wf.grad) < 4e-2
