@@ -176,3 +176,61 @@ def test_linear_cross_entropy_random_shapes(n, d8, v, is_vd, ls, zw, cap, seed):
     assert _rel(per_tok, ref) < 2e-2
     assert _rel(h.grad, hf.grad) < 4e-2
     assert _rel(w.grad, wf.grad) < 4e-2
+
+
+@settings(**SETTINGS)
+@given(n=st.integers(16, 400), e=st.integers(2, 12), topk=st.integers(1, 2), d8=st.integers(4, 40), i8=st.integers(2, 30),
+       seed=st.integers(0, 1000))
+def test_routed_experts_random_shapes(n, e, topk, d8, i8, seed):
+    """Counting-sort dispatch, grouped GEMMs, gated activation and weighted combine against the dense per-token sum."""
+    from mintext_b200.ops import moe as moe_ops
+    from mintext_b200.ops._ext import check_status
+
+    D, I = 8 * d8, 8 * i8
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(n, D, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    gu = (torch.randn(e, D, 2 * I, device="cuda", generator=g) * D ** -0.5).bfloat16().requires_grad_(True)
+    dn = (torch.randn(e, I, D, device="cuda", generator=g) * I ** -0.5).bfloat16().requires_grad_(True)
+    scores = torch.rand(n, e, device="cuda", generator=g)
+    w, idx = torch.topk(scores, topk, dim=-1)
+    w = w.bfloat16().requires_grad_(True)
+    y = moe_ops.experts_forward(x, idx, w, gu, dn, "silu")
+    dy = torch.randn(n, D, device="cuda", generator=g).bfloat16()
+    y.backward(dy)
+    torch.cuda.synchronize()
+    check_status()
+    xf, guf, dnf, wf = (t.detach().float().requires_grad_(True) for t in (x, gu, dn, w))
+    ref = torch.zeros(n, D, device="cuda")
+    for k in range(topk):
+        h = torch.einsum("nd,ndi->ni", xf, guf[idx[:, k]])
+        h = torch.nn.functional.silu(h[:, :I]) * h[:, I:]
+        ref = ref + wf[:, k:k + 1] * torch.einsum("ni,nid->nd", h, dnf[idx[:, k]])
+    ref.backward(dy.float())
+    assert _rel(y, ref) < 2e-2
+    assert _rel(x.grad, xf.grad) < 3e-2
+    assert _rel(w.grad, wf.grad) < 6e-2   # each entry is one dot product of bf16-rounded rows: cancellation
+    assert _rel(gu.grad, guf.grad) < 3e-2
+    assert _rel(dn.grad, dnf.grad) < 3e-2
+
+
+@settings(**SETTINGS)
+@given(m=st.integers(1, 700), n8=st.integers(1, 120), k128=st.integers(1, 6), seed=st.integers(0, 1000))
+def test_mxfp8_gemm_random_shapes(m, n8, k128, seed):
+    """Block-scaled GEMM on ragged M / N (partial 128-row and 192-column tiles) against the product of the
+    de-quantised operands."""
+    from tests.test_gpu_kernels import _mx_dequant
+
+    from mintext_b200.ops._ext import check_status, ext, status_word
+
+    n, k = 8 * n8, 128 * k128
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = (torch.randn(m, k, device="cuda", generator=g) * torch.logspace(-2, 1, k, device="cuda")).bfloat16()
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).bfloat16()
+    e = ext()
+    xq, xs, _, _ = e.mxfp8_quantize(x, True, False, False, False)
+    wq, ws, _, _ = e.mxfp8_quantize(w, True, True, False, False)
+    y = e.gemm_mxfp8(xq, xs, wq, ws, status_word(x.device))
+    torch.cuda.synchronize()
+    check_status()
+    ref = _mx_dequant(xq, xs, 128) @ _mx_dequant(wq, ws, 192).t()
+    assert _rel(y, ref) < 1e-2
