@@ -57,3 +57,86 @@ def test_tensor_parallel_matches_single_process():
             dim = next(i for i, (a, b) in enumerate(zip(parts[0].shape, g.shape)) if a != b)
             got = torch.cat(parts, dim=dim) / world
         assert torch.allclose(got, g, atol=2e-5), name
+
+
+MIXED = {
+    "deepseek": dict(model_type="deepseek_v3", attention_type="mla", q_lora_rank=16, kv_lora_rank=16, qk_nope_head_dim=8,
+                     qk_rope_head_dim=8, v_head_dim=8, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=16,
+                     n_group=2, topk_group=1, first_k_dense_replace=1, n_shared_experts=1),
+    "qwen3_next": dict(model_type="qwen3_next", use_qk_norm=True, full_attention_interval=2, partial_rotary_factor=0.5,
+                       linear_key_head_dim=8, linear_value_head_dim=8, linear_num_key_heads=2, linear_num_value_heads=4,
+                       num_experts=4, num_experts_per_tok=2, moe_intermediate_size=16, n_group=1, topk_group=1,
+                       first_k_dense_replace=0, router_type="softmax_topk", shared_expert_gate=True, n_shared_experts=1,
+                       router_aux_loss_coef=0.05),
+}
+
+
+def _mixed_cfg(kind):
+    return MinTextConfig(dtype="float32", vocab_size=64, num_hidden_layers=2, hidden_size=32, num_attention_heads=4,
+                         num_key_value_heads=2, intermediate_size=64, seq_length=16, **MIXED[kind])
+
+
+def _mixed_worker(rank, world, kind):
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.tp import TensorParallel, set_current_tp
+
+    set_current_tp(TensorParallel(dist.group.WORLD, torch.device("cpu"), fused=False))
+    try:
+        cfg = _mixed_cfg(kind)
+        m = Transformer(cfg, rngs=0)
+        loss, _ = trainer.compute_loss(None, m, cfg, _batch())
+        named = [(n, p) for n, p in m.named_parameters() if p.requires_grad]
+        grads = torch.autograd.grad(loss, [p for _, p in named], allow_unused=True)
+        rep = {n for n, p in named if getattr(p, "tp_replicated_compute", False)}
+        return float(loss), {n: (g.clone() if g is not None else None) for (n, _), g in zip(named, grads)}, rep
+    finally:
+        set_current_tp(None)
+
+
+def _deepseek_worker(rank, world):
+    return _mixed_worker(rank, world, "deepseek")
+
+
+def _qwen3_next_worker(rank, world):
+    return _mixed_worker(rank, world, "qwen3_next")
+
+
+def _check_mixed(kind, worker, port):
+    """Sub-layers without a sharded path (MLA, Gated Delta Rule, experts) run in full on every rank: their gradients
+    are the same on all ranks and count once after the 1/tp scaling the engine applies; everything else follows the
+    token-sharded rules.  Together they give the single-process gradient of mean loss (+ auxiliary loss)."""
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+
+    world = 2
+    res = run_ranks(worker, world, port)
+    cfg = _mixed_cfg(kind)
+    m = Transformer(cfg, rngs=0)
+    loss, _ = trainer.compute_loss(None, m, cfg, _batch())
+    named = [(n, p) for n, p in m.named_parameters() if p.requires_grad]
+    ref = dict(zip([n for n, _ in named], torch.autograd.grad(loss, [p for _, p in named], allow_unused=True)))
+    replicated = res[0][2]
+    assert replicated, "some sub-layer should have been computed replicated"
+    for name, g in ref.items():
+        parts = [res[r][1][name] for r in range(world)]
+        if g is None:
+            assert all(p is None for p in parts), name
+            continue
+        if name in replicated:
+            assert torch.allclose(parts[0], parts[1], atol=1e-5), name      # identical on every rank
+            got = sum(parts) / world / world                                 # engine: 1/tp, then the mean over ranks
+        elif parts[0].shape == g.shape:
+            got = sum(parts) / world
+        else:
+            dim = next(i for i, (a, b) in enumerate(zip(parts[0].shape, g.shape)) if a != b)
+            got = torch.cat(parts, dim=dim) / world
+        assert torch.allclose(got, g, atol=5e-5), (name, (got - g).abs().max())
+
+
+def test_tensor_parallel_with_replicated_mla_and_experts():
+    _check_mixed("deepseek", _deepseek_worker, 29633)
+
+
+def test_tensor_parallel_with_replicated_gdn_experts_and_aux_loss():
+    _check_mixed("qwen3_next", _qwen3_next_worker, 29635)
