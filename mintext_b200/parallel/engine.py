@@ -399,7 +399,7 @@ class TrainEngine:
             micro = {k: v[i * mb:(i + 1) * mb] for k, v in batch.items()}
             loss, aux = compute_loss(None, self.model, cfg, micro)
             self.backward(loss)
-            loss_sum += loss.detach().float()
+            loss_sum += aux["loss"].float()
             if aux.get("moe_expert_counts") is not None:
                 counts = aux["moe_expert_counts"] if counts is None else counts + aux["moe_expert_counts"]
         pnorm = self.param_norm()

@@ -161,9 +161,13 @@ def compute_loss(params, model, config, batch, loss_scale: float | None = None):
 
         tp = current_tp()
         rep = float(tp.size) if (tp is not None and tp.size > 1) else 1.0
-        loss = loss + config.router_aux_loss_coef * aux_loss * (scale * ntok) * rep
+        term = config.router_aux_loss_coef * aux_loss * (scale * ntok)
+        reported = (loss + term).detach()          # what a single process would report
+        loss = loss + term * rep
+    else:
+        reported = loss.detach()
     out_aux = {
-        "loss": loss.detach(),
+        "loss": reported,
         "z_loss": z.detach().mean(),
         "per_token_loss": per_tok.detach(),
         "moe_expert_counts": torch.stack(counts) if counts else None,

@@ -124,7 +124,23 @@ def _worker(rank, world, port, fn, ret):
         dist.destroy_process_group()
 
 
+def _usable_port(port: int) -> int:
+    """``port`` if it can be bound right now, else a free one (a rerun shortly after another may find the
+    rendezvous port of the previous run still in TIME_WAIT)."""
+    import socket
+
+    for candidate in (port, 0):
+        with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+            try:
+                s.bind(("127.0.0.1", candidate))
+                return s.getsockname()[1]
+            except OSError:
+                continue
+    return port
+
+
 def run_ranks(fn, world, port):
+    port = _usable_port(port)
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, port, fn, ret), nprocs=world, join=True)
