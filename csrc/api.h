@@ -127,6 +127,9 @@ void fsdp_gemm_agw(const void* A, const PeerPtrs& w_shards, void* w_full, void* 
 void gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                     bool a_mn_major, bool b_mn_major, bool out_f32, bool accumulate, int* status, int num_sms,
                     cudaStream_t stream);
+// Gated-MLP front half in one pair GEMM: GU[:, :I] = X Wg, GU[:, I:] = X Wu, H = act(gate) * up  (I % 128 == 0)
+void gemm_gate_up_act_pair(const void* X, const void* Wg, const void* Wu, void* GU, void* H, int T, int I, int K,
+                           int64_t ldx, int act, int* status, int num_sms, cudaStream_t stream);
 
 // ---- gemm/mxfp8_gemm.cu: block-scaled FP8 (e4m3 elements, one UE8M0 scale per 32 elements along K)
 int64_t mxfp8_sf_bytes(int rows, int K, bool b_operand);

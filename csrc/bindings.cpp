@@ -356,6 +356,22 @@ void ep_gather_rows(torch::Tensor& out, const torch::Tensor& row_src, const torc
                      scaled ? row_scale.data_ptr<float>() : nullptr, out.size(0), (int)out.size(1), cur_stream());
 }
 
+// gu [T, 2I] <- [x wg | x wu], h [T, I] <- act(x wg) * (x wu); wg, wu [K, I] contiguous bf16
+void gemm_gate_up_act(const torch::Tensor& x, const torch::Tensor& wg, const torch::Tensor& wu, torch::Tensor& gu,
+                      torch::Tensor& h, int64_t act, torch::Tensor& status) {
+  check_bf16_2d(x, "x");
+  TORCH_CHECK(x.stride(1) == 1 && x.stride(0) % 8 == 0);
+  TORCH_CHECK(wg.is_contiguous() && wu.is_contiguous() && wg.dim() == 2 && wg.sizes() == wu.sizes());
+  TORCH_CHECK(wg.scalar_type() == torch::kBFloat16 && wu.scalar_type() == torch::kBFloat16);
+  const int64_t T = x.size(0), K = x.size(1), I = wg.size(1);
+  TORCH_CHECK(wg.size(0) == K && I % 128 == 0 && K % 8 == 0);
+  TORCH_CHECK(gu.is_contiguous() && h.is_contiguous() && gu.scalar_type() == torch::kBFloat16 && h.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(gu.size(0) == T && gu.size(1) == 2 * I && h.size(0) == T && h.size(1) == I);
+  c10::cuda::CUDAGuard guard(x.device());
+  mt::gemm_gate_up_act_pair(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), gu.data_ptr(), h.data_ptr(), (int)T, (int)I, (int)K,
+                            x.stride(0), (int)act, status.data_ptr<int>(), sm_count(), cur_stream());
+}
+
 // c[M,N] = a[M,K] @ (b_kn ? b[K,N] : b[N,K]^T) on CTA pairs (bf16 in / out)
 void gemm_pair(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& c, bool b_kn, torch::Tensor& status) {
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16 && c.scalar_type() == torch::kBFloat16);
@@ -647,6 +663,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ep_pull_rows", &ep_pull_rows);
   m.def("ep_gather_rows", &ep_gather_rows);
   m.def("gemm_pair", &gemm_pair);
+  m.def("gemm_gate_up_act", &gemm_gate_up_act);
   m.def("fp8_quantize", &fp8_quantize);
   m.def("gemm_fp8", &gemm_fp8);
   m.def("mxfp8_quantize", &mxfp8_quantize);

@@ -550,6 +550,14 @@ def gate_mul(x: torch.Tensor, gate: torch.Tensor, kind: str) -> torch.Tensor:
     return x * f.to(x.dtype)
 
 
+def _fused_gate_up(x, wg, wu, T: int, M: int) -> bool:
+    import os
+
+    return (os.environ.get("MT_FUSED_GATE_UP", "1") != "0" and hasattr(ext(), "gemm_gate_up_act") and M % 128 == 0
+            and T > 128 and x.shape[1] % 8 == 0 and wg.is_contiguous() and wu.is_contiguous() and x.stride(1) == 1
+            and x.stride(0) % 8 == 0)
+
+
 class _GateUpActFn(torch.autograd.Function):
     """``act(x @ Wg) * (x @ Wu)``: both projections write the column halves of one ``[T, 2M]`` buffer (strided
     GEMM outputs), the activation kernel reads it once; backward mirrors this with strided dgrad / wgrad
@@ -563,6 +571,15 @@ class _GateUpActFn(torch.autograd.Function):
             buf = replay_buf
         else:
             buf = torch.empty(T, 2 * M, device=x.device, dtype=torch.bfloat16)
+            if _fused_gate_up(x, wg, wu, T, M):
+                # one CTA-pair GEMM whose accumulator holds [gate | up] for the same output columns and whose
+                # epilogue also writes act(gate) * up: no separate activation kernel, no re-read of the buffer
+                out = torch.empty(T, M, device=x.device, dtype=torch.bfloat16)
+                ext().gemm_gate_up_act(x, wg, wu, buf, out, act_code, status_word(x.device))
+                ctx.save_for_backward(x, wg, wu, buf)
+                ctx.meta = (act_code, mg_g, mg_u)
+                ctx.mark_non_differentiable(buf)
+                return out, buf
             _gemm(x, wg, buf[:, :M], False, True)
             _gemm(x, wu, buf[:, M:], False, True)
         out = torch.empty(T, M, device=x.device, dtype=torch.bfloat16)

@@ -449,3 +449,34 @@ def test_gate_mul_matches_torch_with_strided_gate(kind):
     assert _rel_err(proj.grad[..., dh:], pf.grad[..., dh:]) < 1e-2
     assert proj.grad[..., :dh].abs().max() == 0
 
+
+
+@pytest.mark.parametrize("T,K,I,act", [(384, 256, 256, "silu"), (1000, 192, 128, "gelu_pytorch_tanh"), (2048, 512, 1024, "silu")])
+def test_fused_gate_up_act_gemm_matches_separate_kernels(T, K, I, act, monkeypatch):
+    """One CTA-pair GEMM producing [gate | up] and act(gate) * up from its epilogue, against the two GEMMs plus the
+    activation kernel (values of both outputs, and the gradients that flow through either path)."""
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops._ext import check_status
+
+    torch.manual_seed(2)
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    wg = (torch.randn(K, I, device="cuda") * K ** -0.5).bfloat16()
+    wu = (torch.randn(K, I, device="cuda") * K ** -0.5).bfloat16()
+    dy = torch.randn(T, I, device="cuda").bfloat16()
+    res = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("MT_FUSED_GATE_UP", mode)
+        xi, g, u = (t.clone().requires_grad_(True) for t in (x, wg, wu))
+        h = F.gate_up_act(xi, g, u, act)
+        h.backward(dy)
+        res[mode] = (h.detach(), xi.grad, g.grad, u.grad)
+    torch.cuda.synchronize()
+    check_status()
+    ref = oracle_h = None
+    xf = x.float()
+    gf, uf = xf @ wg.float(), xf @ wu.float()
+    from mintext_b200.ops import oracle
+    oracle_h = oracle.activation(act)(gf) * uf
+    assert _rel_err(res["1"][0], oracle_h) < 1e-2
+    for name, a, b in zip(("h", "dx", "dwg", "dwu"), res["1"], res["0"]):
+        assert _rel_err(a, b) < 1e-2, (name, _rel_err(a, b))
