@@ -130,6 +130,9 @@ void gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, 
 // Gated-MLP front half in one pair GEMM: GU[:, :I] = X Wg, GU[:, I:] = X Wu, H = act(gate) * up  (I % 128 == 0)
 void gemm_gate_up_act_pair(const void* X, const void* Wg, const void* Wu, void* GU, void* H, int T, int I, int K,
                            int64_t ldx, int act, int* status, int num_sms, cudaStream_t stream);
+// dGU[:, :I] = (dY Wd^T) * U * act'(G), dGU[:, I:] = (dY Wd^T) * act(G)  with G | U the halves of GU  (I % 256 == 0)
+void gemm_gated_bwd_pair(const void* dY, const void* Wd, const void* GU, void* dGU, int T, int I, int D, int64_t ldy,
+                         int act, int* status, int num_sms, cudaStream_t stream);
 
 // ---- gemm/mxfp8_gemm.cu: block-scaled FP8 (e4m3 elements, one UE8M0 scale per 32 elements along K)
 int64_t mxfp8_sf_bytes(int rows, int K, bool b_operand);

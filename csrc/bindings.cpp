@@ -372,6 +372,21 @@ void gemm_gate_up_act(const torch::Tensor& x, const torch::Tensor& wg, const tor
                             x.stride(0), (int)act, status.data_ptr<int>(), sm_count(), cur_stream());
 }
 
+// dgu [T, 2I] <- [(dy wd^T) * up * act'(gate) | (dy wd^T) * act(gate)], gate | up = halves of gu; wd [I, D]
+void gemm_gated_bwd(const torch::Tensor& dy, const torch::Tensor& wd, const torch::Tensor& gu, torch::Tensor& dgu,
+                    int64_t act, torch::Tensor& status) {
+  check_bf16_2d(dy, "dy");
+  TORCH_CHECK(dy.stride(1) == 1 && dy.stride(0) % 8 == 0);
+  TORCH_CHECK(wd.is_contiguous() && wd.dim() == 2 && wd.scalar_type() == torch::kBFloat16);
+  const int64_t T = dy.size(0), D = dy.size(1), I = wd.size(0);
+  TORCH_CHECK(wd.size(1) == D && I % 256 == 0 && D % 8 == 0);
+  TORCH_CHECK(gu.is_contiguous() && dgu.is_contiguous() && gu.scalar_type() == torch::kBFloat16 && dgu.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(gu.size(0) == T && gu.size(1) == 2 * I && dgu.sizes() == gu.sizes());
+  c10::cuda::CUDAGuard guard(dy.device());
+  mt::gemm_gated_bwd_pair(dy.data_ptr(), wd.data_ptr(), gu.data_ptr(), dgu.data_ptr(), (int)T, (int)I, (int)D, dy.stride(0),
+                          (int)act, status.data_ptr<int>(), sm_count(), cur_stream());
+}
+
 // c[M,N] = a[M,K] @ (b_kn ? b[K,N] : b[N,K]^T) on CTA pairs (bf16 in / out)
 void gemm_pair(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& c, bool b_kn, torch::Tensor& status) {
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16 && c.scalar_type() == torch::kBFloat16);
@@ -664,6 +679,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ep_gather_rows", &ep_gather_rows);
   m.def("gemm_pair", &gemm_pair);
   m.def("gemm_gate_up_act", &gemm_gate_up_act);
+  m.def("gemm_gated_bwd", &gemm_gated_bwd);
   m.def("fp8_quantize", &fp8_quantize);
   m.def("gemm_fp8", &gemm_fp8);
   m.def("mxfp8_quantize", &mxfp8_quantize);

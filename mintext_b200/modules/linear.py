@@ -163,6 +163,9 @@ class MLP(nn.Module):
         elif self.gate.use_fp8:
             h = oracle.activation(self.act_name)(self.gate(x)) * self.up(x)
         else:
+            if self.down.bias is None and F.gated_mlp_path(x, self.gate.kernel, self.up.kernel, self.down.kernel,
+                                                           self.act_name):
+                return F.gated_mlp(x, self.gate.kernel, self.up.kernel, self.down.kernel, self.act_name)
             h = F.gate_up_act(x, self.gate.kernel, self.up.kernel, self.act_name, dtype=self.gate.dtype)
         return self.down(h)
 

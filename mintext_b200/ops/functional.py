@@ -664,6 +664,80 @@ def gate_up_act_fp8(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, act: st
     return out.reshape(*lead, wg.shape[1])
 
 
+class _GatedMlpFn(torch.autograd.Function):
+    """Whole gated MLP ``(act(x Wg) * (x Wu)) Wd`` as one autograd node, so that the backward can run the down
+    projection's data-gradient GEMM with the activation backward in its epilogue (csrc/gemm/gated_bwd_2cta.cu): the
+    gradient of the hidden activation never reaches memory.  Forward: the fused gate/up GEMM, then the down GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, wg, wu, wd, act_code, mg_g, mg_u, mg_d):
+        T, I = x.shape[0], wg.shape[1]
+        st = status_word(x.device)
+        buf = torch.empty(T, 2 * I, device=x.device, dtype=torch.bfloat16)
+        h = torch.empty(T, I, device=x.device, dtype=torch.bfloat16)
+        ext().gemm_gate_up_act(x, wg, wu, buf, h, act_code, st)
+        y = torch.empty(T, wd.shape[1], device=x.device, dtype=torch.bfloat16)
+        _gemm(h, wd, y, False, True)
+        ctx.save_for_backward(x, wg, wu, wd, buf, h)
+        ctx.meta = (act_code, mg_g, mg_u, mg_d)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, wg, wu, wd, buf, h = ctx.saved_tensors
+        act_code, mg_g, mg_u, mg_d = ctx.meta
+        I = wg.shape[1]
+        dy = dy.contiguous()
+        dgu = torch.empty_like(buf)
+        ext().gemm_gated_bwd(dy, wd, buf, dgu, act_code, status_word(x.device))
+        grads = []
+        if mg_d is not None:
+            _gemm(h, dy, mg_d.view(wd.shape), True, True, accumulate=True)
+            dwd = None
+        else:
+            dwd = torch.empty(wd.shape, device=wd.device, dtype=torch.float32)
+            dwd = _gemm(h, dy, dwd, True, True).to(wd.dtype)
+        dg, du = dgu[:, :I], dgu[:, I:]
+        dx = torch.empty_like(x)
+        _gemm(dg, wg, dx, False, False)
+        _gemm(du, wu, dx, False, False, accumulate=True)
+        for d, w, mg in ((dg, wg, mg_g), (du, wu, mg_u)):
+            if mg is not None:
+                _gemm(x, d, mg.view(w.shape), True, True, accumulate=True)
+                grads.append(None)
+            else:
+                dw = torch.empty(w.shape, device=w.device, dtype=torch.float32)
+                grads.append(_gemm(x, d, dw, True, True).to(w.dtype))
+        return dx, grads[0], grads[1], dwd, None, None, None, None
+
+
+def gated_mlp_path(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, wd: torch.Tensor, act: str) -> bool:
+    """The single-node gated MLP applies to bf16 CUDA tensors outside rematerialisation, with the intermediate
+    width a multiple of 256 and more than one row tile."""
+    import os
+
+    if not (use_cuda(x) and _remat() is None and act in oracle.ACT_CODES and hasattr(ext(), "gemm_gated_bwd")):
+        return False
+    if os.environ.get("MT_FUSED_GATE_UP", "1") == "0":
+        return False
+    K, I = wg.shape
+    rows = x.numel() // max(x.shape[-1], 1)
+    return (wg.dtype == torch.bfloat16 and wu.dtype == torch.bfloat16 and wd.dtype == torch.bfloat16 and wg.dim() == 2
+            and wd.dim() == 2 and wd.shape[0] == I and I % 256 == 0 and K % 8 == 0 and wd.shape[1] % 8 == 0 and rows > 128
+            and wg.is_contiguous() and wu.is_contiguous() and wd.is_contiguous())
+
+
+def gated_mlp(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, wd: torch.Tensor, act: str) -> torch.Tensor:
+    """``(act(x @ wg) * (x @ wu)) @ wd`` (mintext/modules/linear.py:218-228); callers check :func:`gated_mlp_path`."""
+    lead, K = x.shape[:-1], wg.shape[0]
+    x2 = x.reshape(-1, K)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = _GatedMlpFn.apply(x2, wg, wu, wd, oracle.ACT_CODES[act], getattr(wg, "main_grad", None),
+                          getattr(wu, "main_grad", None), getattr(wd, "main_grad", None))
+    return y.reshape(*lead, wd.shape[1])
+
+
 def gate_up_act(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, act: str, dtype: torch.dtype | None = None,
                 name: str = "mlp_gate_up") -> torch.Tensor:
     """Gated MLP front half, ``act(x @ wg) * (x @ wu)`` (mintext/modules/linear.py:218-225)."""

@@ -480,3 +480,30 @@ def test_fused_gate_up_act_gemm_matches_separate_kernels(T, K, I, act, monkeypat
     assert _rel_err(res["1"][0], oracle_h) < 1e-2
     for name, a, b in zip(("h", "dx", "dwg", "dwu"), res["1"], res["0"]):
         assert _rel_err(a, b) < 1e-2, (name, _rel_err(a, b))
+
+
+@pytest.mark.parametrize("T,D,I,act", [(512, 256, 512, "silu"), (1000, 192, 256, "gelu_pytorch_tanh"), (2048, 512, 1024, "silu")])
+def test_gated_mlp_single_node_matches_separate_kernels(T, D, I, act, monkeypatch):
+    """The whole gated MLP as one autograd node (fused gate/up GEMM forward; down-projection data gradient with the
+    activation backward in its epilogue) against the chain of separate GEMMs and activation kernels."""
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops._ext import check_status
+
+    torch.manual_seed(4)
+    x = torch.randn(T, D, device="cuda").bfloat16()
+    wg = (torch.randn(D, I, device="cuda") * D ** -0.5).bfloat16()
+    wu = (torch.randn(D, I, device="cuda") * D ** -0.5).bfloat16()
+    wd = (torch.randn(I, D, device="cuda") * I ** -0.5).bfloat16()
+    dy = torch.randn(T, D, device="cuda").bfloat16()
+    res = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("MT_FUSED_GATE_UP", mode)
+        xi, g, u, d = (t.clone().requires_grad_(True) for t in (x, wg, wu, wd))
+        assert F.gated_mlp_path(xi, g, u, d, act) == (mode == "1")
+        y = F.gated_mlp(xi, g, u, d, act) if mode == "1" else F.linear(F.gate_up_act(xi, g, u, act), d)
+        y.backward(dy)
+        res[mode] = (y.detach(), xi.grad, g.grad, u.grad, d.grad)
+    torch.cuda.synchronize()
+    check_status()
+    for name, a, b in zip(("y", "dx", "dwg", "dwu", "dwd"), res["1"], res["0"]):
+        assert _rel_err(a, b) < 1.5e-2, (name, _rel_err(a, b))
