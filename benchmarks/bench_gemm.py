@@ -2,7 +2,7 @@
 Llama-3.2-1B and Llama-3-8B configs (forward, dgrad, wgrad layouts).
 
 Timing: CUDA events, 3 warm-up runs, L2 flushed between timed runs by writing a 256 MB buffer.
-Usage: python benchmarks/bench_gemm.py [--out gpurun_out/gemm_bench.json]
+Usage: python benchmarks/bench_gemm.py [--out gemm_bench.json]
 """
 
 from __future__ import annotations
