@@ -234,3 +234,105 @@ def test_mxfp8_gemm_random_shapes(m, n8, k128, seed):
     check_status()
     ref = _mx_dequant(xq, xs, 128) @ _mx_dequant(wq, ws, 192).t()
     assert _rel(y, ref) < 1e-2
+
+
+@settings(**SETTINGS)
+@given(b=st.integers(1, 3), s=st.integers(1, 300), h=st.integers(1, 6), d=st.sampled_from([32, 64, 128, 192, 256]),
+       frac=st.sampled_from([1.0, 0.5, 0.25]), default=st.booleans(), seed=st.integers(0, 1000))
+def test_rope_random_shapes(b, s, h, d, frac, default, seed):
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops import oracle
+    from mintext_b200.ops._ext import check_status
+
+    rot = int(d * frac) // 2 * 2
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(b, s, h, d, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, rot, 2, device="cuda").float() / rot))
+    tables = oracle.rope_tables(inv_freq, 1.0, 512, device="cuda")
+    if default:
+        pos = torch.arange(s, device="cuda")[None].expand(b, -1)
+    else:
+        pos = torch.randint(0, 512, (b, s), device="cuda", generator=g)
+    y = F.rope(x, pos, inv_freq, 1.0, rot, False, tables=tables, default_positions=default)
+    dy = torch.randn(y.shape, device="cuda", generator=g).bfloat16()
+    y.backward(dy)
+    torch.cuda.synchronize()
+    check_status()
+    xf = x.detach().float().requires_grad_(True)
+    ref = oracle.apply_rope(xf, pos, inv_freq, 1.0, rot, False)
+    ref.backward(dy.float())
+    assert _rel(y, ref) < 1e-2
+    assert _rel(x.grad, xf.grad) < 1e-2
+
+
+@settings(**SETTINGS)
+@given(b=st.integers(1, 3), s=st.integers(1, 200), c8=st.integers(1, 64), k=st.integers(2, 4), seed=st.integers(0, 1000))
+def test_conv1d_silu_random_shapes(b, s, c8, k, seed):
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops import oracle
+    from mintext_b200.ops._ext import check_status
+
+    c = 8 * c8
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(b, s, c, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    w = (torch.randn(c, 1, k, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True)
+    y = F.causal_conv1d_silu(x, w)
+    dy = torch.randn(y.shape, device="cuda", generator=g).bfloat16()
+    y.backward(dy)
+    torch.cuda.synchronize()
+    check_status()
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.silu(oracle.causal_conv1d(xr, wr))
+    ref.backward(dy.float())
+    assert _rel(y, ref) < 1e-2
+    assert _rel(x.grad, xr.grad) < 2e-2
+    assert _rel(w.grad, wr.grad) < 3e-2
+
+
+@settings(**SETTINGS)
+@given(n=st.integers(1, 500), v=st.integers(2, 4000), d8=st.integers(1, 64), scale=st.sampled_from([None, 8.0]),
+       seed=st.integers(0, 1000))
+def test_embedding_random_shapes(n, v, d8, scale, seed):
+    from mintext_b200.ops import functional as F
+    from mintext_b200.ops._ext import check_status
+
+    d = 8 * d8
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    table = torch.randn(v, d, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    ids = torch.randint(0, v, (2, n), device="cuda", generator=g)
+    y = F.embedding(table, ids, torch.bfloat16, scale)
+    dy = torch.randn(y.shape, device="cuda", generator=g).bfloat16()
+    y.backward(dy)
+    torch.cuda.synchronize()
+    check_status()
+    tf = table.detach().float().requires_grad_(True)
+    ref = tf[ids] * (scale if scale is not None else 1.0)
+    ref.backward(dy.float())
+    assert _rel(y, ref) < 1e-2
+    assert _rel(table.grad, tf.grad) < 2e-2
+
+
+@settings(**SETTINGS)
+@given(b=st.integers(1, 2), h=st.integers(1, 3), s=st.integers(1, 260), dk=st.sampled_from([64, 128]),
+       dv=st.sampled_from([32, 64, 128]), seed=st.integers(0, 1000))
+def test_gated_delta_rule_random_shapes(b, h, s, dk, dv, seed):
+    from mintext_b200.ops import gdn, oracle
+    from mintext_b200.ops._ext import check_status
+
+    g_ = torch.Generator(device="cuda").manual_seed(seed)
+    q, k = (torch.randn(b, h, s, dk, device="cuda", generator=g_).requires_grad_(True) for _ in range(2))
+    v = torch.randn(b, h, s, dv, device="cuda", generator=g_).requires_grad_(True)
+    beta = torch.rand(b, h, s, device="cuda", generator=g_).requires_grad_(True)
+    gl = (-torch.rand(b, h, s, device="cuda", generator=g_) * 0.5).requires_grad_(True)
+    assert gdn.cuda_path(q, v, 64)
+    o = gdn.chunk_gated_delta_rule_cuda(q, k, v, beta, gl)
+    do = torch.randn(o.shape, device="cuda", generator=g_)
+    o.backward(do)
+    torch.cuda.synchronize()
+    check_status()
+    ins = [t.detach().clone().requires_grad_(True) for t in (q, k, v, beta, gl)]
+    ref = oracle.chunk_gated_delta_rule(*ins)
+    ref.backward(do)
+    assert _rel(o, ref) < 1e-3
+    for name, a, r in zip("qkvbg", (q, k, v, beta, gl), ins):
+        assert _rel(a.grad, r.grad) < 5e-3, name
