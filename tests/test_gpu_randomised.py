@@ -336,3 +336,42 @@ def test_gated_delta_rule_random_shapes(b, h, s, dk, dv, seed):
     assert _rel(o, ref) < 1e-3
     for name, a, r in zip("qkvbg", (q, k, v, beta, gl), ins):
         assert _rel(a.grad, r.grad) < 5e-3, name
+
+
+@settings(**SETTINGS)
+@given(n=st.integers(1, 700), groups=st.sampled_from([1, 2, 4, 8]), per=st.sampled_from([2, 4, 16, 32]),
+       topk=st.integers(1, 8), norm=st.booleans(), softmax=st.booleans(), seed=st.integers(0, 1000))
+def test_routers_random_shapes(n, groups, per, topk, norm, softmax, seed):
+    """Both router kernels against the oracle: same experts, weights, scores, auxiliary loss and logit gradients."""
+    from mintext_b200.ops import moe as moe_ops
+    from mintext_b200.ops import oracle
+    from mintext_b200.ops._ext import check_status
+
+    E = groups * per
+    topk_group = max(groups // 2, 1)
+    topk = min(topk, topk_group * per)
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    logits = (torch.randn(n, E, device="cuda", generator=g) * 2).requires_grad_(True)
+    bias = torch.randn(E, device="cuda", generator=g) * 0.1
+    ref_in = logits.detach().clone().requires_grad_(True)
+    if softmax:
+        idx, w, probs, aux = moe_ops.router_softmax_topk(logits, topk, norm, 1.5)
+        ridx, rw, rprobs, raux = oracle.router_softmax_topk(ref_in, topk, norm, 1.5)
+    else:
+        idx, w, probs = moe_ops.router_sigmoid_group(logits, bias, topk, groups, topk_group, norm, 2.5)
+        ridx, rw, rprobs = oracle.router_sigmoid_group(ref_in, bias, topk, groups, topk_group, norm, 2.5)
+        aux = raux = None
+    dw = torch.randn(w.shape, device="cuda", generator=g)
+    loss = (w.float() * dw).sum() + (aux if aux is not None else 0.0)
+    rloss = (rw.float() * dw).sum() + (raux if raux is not None else 0.0)
+    loss.backward()
+    rloss.backward()
+    torch.cuda.synchronize()
+    check_status()
+    assert torch.equal(idx.long().sort(-1)[0], ridx.long().sort(-1)[0])
+    order, rorder = idx.long().argsort(-1), ridx.long().argsort(-1)
+    assert torch.allclose(w.float().gather(1, order), rw.float().gather(1, rorder), atol=1e-5, rtol=1e-4)
+    assert torch.allclose(probs.float(), rprobs.float(), atol=1e-5)
+    if aux is not None:
+        assert abs(float(aux) - float(raux)) < 1e-4
+    assert _rel(logits.grad, ref_in.grad) < 1e-3
