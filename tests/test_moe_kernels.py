@@ -129,3 +129,16 @@ def test_autotuner_candidates_and_cache(tmp_path):
     assert r2.gate_up_tiling == r.gate_up_tiling
     other = MoETuningConfig(num_experts=8, hidden_size=32, moe_intermediate_size=16, num_tokens=64, dtype="float32")
     assert _cache_key(other) != _cache_key(tc)
+
+
+def test_histogram_matches_bincount():
+    """The sync-free expert histogram used on the training path equals ``torch.bincount(..., minlength=E)``."""
+    import torch
+
+    from mintext_b200.ops import oracle
+
+    g = torch.Generator().manual_seed(0)
+    for shape, bins in (((7, 3), 5), ((1000, 8), 128), ((1, 1), 4)):
+        idx = torch.randint(0, bins, shape, generator=g)
+        assert torch.equal(oracle.histogram(idx, bins), torch.bincount(idx.reshape(-1), minlength=bins))
+    assert torch.equal(oracle.histogram(torch.zeros(0, dtype=torch.long), 3), torch.zeros(3, dtype=torch.long))
