@@ -1,5 +1,9 @@
 """Headline benchmark: training throughput of the Llama-3.2-1B-shaped model (bf16, global batch 64 x 4096,
-AdamW, synthetic tokens, random init) on N GPUs of one node.
+AdamW, synthetic tokens, random init) on N GPUs of one node.  ``--model`` selects the other benchmark models
+(`llama8b`: Llama-3-8B-shaped, FSDP 4 x TP 2, MXFP8 MLP GEMMs, 32 x 8192; `qwen3moe`: Qwen3-30B-A3B-shaped, EP 8,
+32 x 4096; `dsv3`: DeepSeek-V3-shaped 4-layer MLA + MoE, EP 8, 16 x 4096), each read from
+``configs/benchmarks/*.yml`` and set up exactly as ``python -m mintext_b200.train`` sets it up; ``--set key=value``
+overrides config keys (e.g. a smaller expert count for a run on fewer GPUs).
 
     python bench.py --gpus 1 --steps K --warmup W
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
@@ -41,6 +45,39 @@ def llama_1b_config(global_batch: int, seq_len: int, world: int, micro_batch: in
         dtype="bfloat16", weight_dtype="float32", optimizer="adamw", learning_rate=3e-4, lr_schedule="cosine",
         steps=max(steps, 10), remat_policy="none", enable_tensorboard=False, enable_checkpointing=False,
         ici_fsdp_parallelism=world, use_fp8=fp8_mlp, fp8_recipe=fp8_recipe)
+
+
+BENCH_MODELS = {
+    # name: (config file, global batch in sequences, metric label, model description)
+    "llama8b": ("llama-3-8b-b200.yml", 32, "train tokens/s (Llama-3-8B-shaped, FSDP x TP, AdamW)",
+                "llama-3-8b-shaped (32L, d4096, 32/8 heads, ffn 14336, vocab 128256)"),
+    "qwen3moe": ("qwen3-30b-a3b-b200.yml", 32, "train tokens/s (Qwen3-30B-A3B-shaped MoE, EP + FSDP, AdamW)",
+                 "qwen3-30b-a3b-shaped (48L, d2048, 32/4 heads, 128 experts top-8, moe ffn 768, vocab 151936)"),
+    "dsv3": ("deepseek-v3-4l-b200.yml", 16, "train tokens/s (DeepSeek-V3-shaped 4-layer MLA+MoE, EP + FSDP, AdamW)",
+             "deepseek-v3-shaped 4 layers (d7168, MLA 128 heads, 256 experts top-8 + 1 shared, moe ffn 2048)"),
+}
+
+
+def yaml_config(name: str, world: int, global_batch: int | None, seq_len: int | None, micro_batch: int | None,
+                steps: int, overrides: list[str]):
+    """Config of one of the non-headline benchmark models with the batch split worked out for ``world`` ranks."""
+    from mintext_b200.config import load_config, parse_cli_overrides
+
+    yml, gb, _, _ = BENCH_MODELS[name]
+    o = parse_cli_overrides(overrides) if overrides else {}
+    if seq_len:
+        o["seq_length"] = seq_len
+    if micro_batch:
+        o["per_device_batch_size"] = micro_batch
+    o.update({"steps": max(steps, 10), "enable_tensorboard": False, "enable_checkpointing": False})
+    cfg = load_config(ROOT / "configs" / "benchmarks" / yml, o)
+    gb = global_batch or gb
+    tp = max(int(cfg.ici_tensor_parallelism), 1)
+    dp = world // tp
+    if gb % dp != 0 or (gb // dp) % cfg.per_device_batch_size != 0:
+        raise SystemExit(f"global batch {gb} does not split into {dp} data-parallel ranks x micro-batches of "
+                         f"{cfg.per_device_batch_size}")
+    return cfg.model_copy(update={"gradient_accumulation_steps": gb // dp // cfg.per_device_batch_size}), gb
 
 
 class ClockSampler:
@@ -110,9 +147,11 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
-    ap.add_argument("--global-batch", type=int, default=64)
-    ap.add_argument("--seq-len", type=int, default=4096)
-    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--model", default="llama1b", choices=["llama1b"] + sorted(BENCH_MODELS))
+    ap.add_argument("--global-batch", type=int, default=None)
+    ap.add_argument("--seq-len", type=int, default=None)
+    ap.add_argument("--micro-batch", type=int, default=None)
+    ap.add_argument("--set", nargs="*", default=[], metavar="KEY=VALUE", help="config overrides (not for llama1b)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--fp8-mlp", action="store_true",
                     help="side measurement, not the headline: MLP projections through the FP8 GEMM (per-tensor scales)")
@@ -141,14 +180,35 @@ def main() -> None:
     from mintext_b200.utils.pytree import model_flops_per_token_batch
 
     warmup = max(args.warmup, 3)
-    cfg = llama_1b_config(args.global_batch, args.seq_len, world, args.micro_batch, args.steps + warmup, args.fp8_mlp,
-                          args.fp8_recipe)
-    model = Transformer(cfg, rngs=0)
-    eng = TrainEngine(model, cfg, device=dev)
-    lo, hi = local_batch_rows(args.global_batch, world, rank)
+    if args.model == "llama1b":
+        args.global_batch = args.global_batch or 64
+        args.seq_len = args.seq_len or 4096
+        args.micro_batch = args.micro_batch or 8
+        cfg = llama_1b_config(args.global_batch, args.seq_len, world, args.micro_batch, args.steps + warmup,
+                              args.fp8_mlp, args.fp8_recipe)
+        model = Transformer(cfg, rngs=0)
+        eng = TrainEngine(model, cfg, device=dev)
+        tp = 1
+        metric = "train tokens/s (Llama-3.2-1B-shaped, bf16, AdamW)"
+        model_desc = "llama-3.2-1b-shaped (16L, d2048, 32/8 heads, ffn 8192, vocab 128256, tied)"
+        parallelism = f"fsdp{world}" if world > 1 else "single"
+    else:
+        from mintext_b200.train import setup_training
+
+        cfg, args.global_batch = yaml_config(args.model, world, args.global_batch, args.seq_len, args.micro_batch,
+                                             args.steps + warmup, args.set)
+        args.seq_len, args.micro_batch = cfg.seq_length, cfg.per_device_batch_size
+        mesh, model, eng, _, _ = setup_training(cfg)
+        tp = mesh.shape["tensor"]
+        _, _, metric, model_desc = BENCH_MODELS[args.model]
+        parallelism = "x".join(f"{k}{v}" for k, v in (("fsdp", mesh.shape["data"] * mesh.shape["fsdp"]), ("tp", tp),
+                                                       ("ep", mesh.shape["expert"])) if v > 1) or "single"
+        if cfg.use_fp8:
+            args.fp8_mlp, args.fp8_recipe = True, str(cfg.fp8_recipe)
+    lo, hi = local_batch_rows(args.global_batch, world // tp, rank // tp)  # a tensor-parallel group shares its rows
     rows = hi - lo
     n_micro = max(rows // args.micro_batch, 1)
-    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank // tp)
 
     def host_batch():
         t = torch.randint(0, cfg.vocab_size, (rows, args.seq_len), generator=gen, dtype=torch.int64)
@@ -165,7 +225,7 @@ def main() -> None:
 
     def step_device(i):
         tok = dev_batches[i % len(dev_batches)]
-        return eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=n_micro)
+        return eng.train_step({"input_tokens": tok, "target_tokens": tok.roll(-1, dims=1)}, num_micro=n_micro)
 
     for i in range(warmup):
         out = step_device(i)
@@ -198,13 +258,14 @@ def main() -> None:
         hosts = [host_batch() for _ in range(4)]
         for i in range(2):
             tok = hosts[i % 4].to(dev, non_blocking=True)
-            float(eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=n_micro)["loss"])
+            float(eng.train_step({"input_tokens": tok, "target_tokens": tok.roll(-1, dims=1)},
+                                 num_micro=n_micro)["loss"])
         barrier_sync()
         s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s2.record()
         for i in range(args.steps):
             tok = hosts[i % 4].to(dev, non_blocking=True)
-            o2 = eng.train_step({"input_tokens": tok, "target_tokens": tok}, num_micro=n_micro)
+            o2 = eng.train_step({"input_tokens": tok, "target_tokens": tok.roll(-1, dims=1)}, num_micro=n_micro)
             final_loss = float(o2["loss"])  # device -> host read of the step's result
         e2.record()
         barrier_sync()
@@ -215,20 +276,27 @@ def main() -> None:
         e2e = {"value": tokens_per_step / (ms2 / 1e3), "unit": "tokens/s", "ms_per_step": ms2,
                "h2d_bytes_per_step": rows * args.seq_len * 8, "d2h_bytes_per_step": 4}
 
+    free_b, total_b = torch.cuda.mem_get_info(dev)  # includes symmetric-memory and NCCL buffers
+    peak = torch.tensor([max(torch.cuda.max_memory_reserved(dev), total_b - free_b) / 2 ** 30], device=dev)
+    if world > 1:
+        dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+    peak_gb = round(float(peak.item()), 2)
     flops_step = model_flops_per_token_batch(cfg, args.global_batch)
     tflops_per_gpu = flops_step / (ms_per_step / 1e3) / 1e12 / world
     if rank == 0:
         line = {
-            "metric": "train tokens/s (Llama-3.2-1B-shaped, bf16, AdamW)", "value": value, "unit": "tokens/s",
+            "metric": metric, "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": value / (PUBLISHED_TOKENS_PER_SEC_PER_DEVICE * world),
+            # the reference publishes a number for the Llama-3.2-1B run only
+            "vs_baseline": value / (PUBLISHED_TOKENS_PER_SEC_PER_DEVICE * world) if args.model == "llama1b" else None,
             "dtype": ("bf16 (mxfp8 MLP projections)" if args.fp8_recipe == "mx_block" else "bf16 (fp8 e4m3/e5m2 MLP projections)") if args.fp8_mlp else "bf16", "data": "synthetic uniform-random token ids, random-init weights", "impl": "own",
             "tokens_per_sec_per_gpu": value / world, "tflops_per_gpu": tflops_per_gpu,
             "mfu_vs_nominal_2250": tflops_per_gpu / 2250.0, "final_loss": final_loss,
-            "config": {"model": "llama-3.2-1b-shaped (16L, d2048, 32/8 heads, ffn 8192, vocab 128256, tied)",
+            "peak_memory_gb": peak_gb,
+            "config": {"model": model_desc,
                        "global_batch": args.global_batch, "seq_len": args.seq_len,
-                       "parallelism": f"fsdp{world}" if world > 1 else "single",
+                       "parallelism": parallelism, "remat_policy": str(cfg.remat_policy),
                        "micro_batch": args.micro_batch, "grad_accum_per_rank": n_micro,
                        "l2": "inputs and weights per step exceed L2 (126 MB) by >20x; no explicit flush"},
             "clocks": clocks.summary(), "e2e": e2e,

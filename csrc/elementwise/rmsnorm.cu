@@ -7,6 +7,7 @@
 #include <cstdint>
 #include "../api.h"
 #include "rmsnorm_noalloc.h"
+#include <atomic>
 #include <cstdio>
 
 namespace mt {
@@ -349,7 +350,9 @@ static __device__ __align__(256) float g_rmsnorm_partials[MT_RMSNORM_NOALLOC_PAR
 
 namespace {
 constexpr int kMaxDevices = 64;
-float* g_partials_addr[kMaxDevices] = {nullptr};
+// Written once per device with the same value by whichever host thread gets there first; atomic so that first
+// calls from several threads do not race on the slot (relaxed order suffices: the value itself is all that is read).
+std::atomic<float*> g_partials_addr[kMaxDevices];
 
 int fail(char* err, size_t err_len, int code, const char* msg) {
   if (err && err_len > 0) std::snprintf(err, err_len, "%s", msg);
@@ -360,7 +363,8 @@ int fail(char* err, size_t err_len, int code, const char* msg) {
 extern "C" int mt_rmsnorm_bwd_noalloc(const void* x, const float* w, const float* rstd, const void* dy,
                                       const void* dres, void* dx, float* dw, int64_t rows, int dim,
                                       int accumulate_dw, cudaStream_t stream, char* err, size_t err_len) {
-  if (!x || !w || !rstd || !dy || !dx || !dw) return fail(err, err_len, 1, "mt_rmsnorm_bwd_noalloc: null pointer argument");
+  if (!w || !dw || (rows > 0 && (!x || !rstd || !dy || !dx)))  // an empty [0, dim] operand may have no address
+    return fail(err, err_len, 1, "mt_rmsnorm_bwd_noalloc: null pointer argument");
   if (dim <= 0 || dim % 8 != 0) return fail(err, err_len, 2, "mt_rmsnorm_bwd_noalloc: dim must be a positive multiple of 8");
   if (dim > MT_RMSNORM_NOALLOC_MAX_DIM) {
     char msg[160];
@@ -373,14 +377,21 @@ extern "C" int mt_rmsnorm_bwd_noalloc(const void* x, const float* w, const float
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(err, err_len, 5, cudaGetErrorString(e));
   if (dev < 0 || dev >= kMaxDevices) return fail(err, err_len, 6, "mt_rmsnorm_bwd_noalloc: device index out of range");
-  if (g_partials_addr[dev] == nullptr) {  // one-time set-up for this device (current device = dev)
+  float* partials = g_partials_addr[dev].load(std::memory_order_relaxed);
+  if (partials == nullptr) {  // one-time set-up for this device (current device = dev)
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_rmsnorm_partials);
     if (e != cudaSuccess) return fail(err, err_len, 7, cudaGetErrorString(e));
-    g_partials_addr[dev] = static_cast<float*>(p);
+    partials = static_cast<float*>(p);
+    g_partials_addr[dev].store(partials, std::memory_order_relaxed);
   }
-  if (rows == 0) return 0;
-  float* partials = g_partials_addr[dev];
+  if (rows == 0) {
+    // a sum over no rows: dw is zero (or left as it is when accumulating); reducing zero partial rows writes that
+    mt::rmsnorm_bwd_reduce(partials, 0, dim, dw, accumulate_dw != 0, stream);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(err, err_len, 8, cudaGetErrorString(e));
+    return 0;
+  }
   // same kernel selection as the ordinary entry point (bit-identical dx), with the built-in partial-sum array
   mt::rmsnorm_bwd(x, w, rstd, dy, dres, dx, partials, MT_RMSNORM_NOALLOC_PARTIALS, rows, dim, stream);
   mt::rmsnorm_bwd_reduce(partials, MT_RMSNORM_NOALLOC_PARTIALS, dim, dw, accumulate_dw != 0, stream);

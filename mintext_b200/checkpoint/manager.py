@@ -2,7 +2,10 @@
 
 Layout on disk: ``<checkpoint_dir>/<step>/default/`` holds one raw little-endian file per leaf of the state
 tree (``step``, ``params/<dotted name>``, ``opt_state/...``), named by the leaf path with ``/`` -> ``__``, plus
-``_METADATA`` (JSON: path -> dtype, shape, file, optional flat-chunk range) and, once everything is on disk,
+``_METADATA`` (JSON: path -> dtype, shape, file; a flat buffer saved by several ranks lists ``chunks`` with their
+element ranges, a tensor- or expert-parallel parameter lists ``shards`` with the dimension it is split along, the
+shard's index and the shard count, so that a restore under another parallel degree reassembles it along that
+dimension) and, once everything is on disk,
 ``<step>/_CHECKPOINT_METADATA`` as the commit marker; a step without the marker is ignored (a crash mid-save
 never yields a loadable half checkpoint).  Saves snapshot device tensors into pinned host memory and hand the
 buffers to background writer threads (C++ when the native runtime is built), so training continues while files
@@ -109,6 +112,7 @@ class CheckpointManager:
         self.read_only = read_only
         self._writer = None
         self._inflight: list[tuple[int, Path]] = []
+        self._pending_meta: dict | None = None
         if not read_only and _rank() == 0:
             self.directory.mkdir(parents=True, exist_ok=True)
 
@@ -161,6 +165,9 @@ class CheckpointManager:
                 info["flat_total"] = int(entry["flat_total"])
             if "flat_range" in entry:
                 meta.setdefault(path, {"chunks": []})["chunks"].append(info)
+            elif "shard" in entry:
+                info["shard"] = [int(v) for v in entry["shard"]]
+                meta.setdefault(path, {"shards": []})["shards"].append(info)
             else:
                 meta[path] = info
             if writer_rank is not None and writer_rank != _rank():
@@ -178,9 +185,10 @@ class CheckpointManager:
             merged: dict[str, dict] = {}
             for m in gathered:
                 for k, v in m.items():
-                    if "chunks" in v:
-                        merged.setdefault(k, {"chunks": []})["chunks"].extend(
-                            c for c in v["chunks"] if c not in merged[k]["chunks"])
+                    if "chunks" in v or "shards" in v:
+                        kind = "chunks" if "chunks" in v else "shards"
+                        merged.setdefault(k, {kind: []})[kind].extend(
+                            c for c in v[kind] if c not in merged[k][kind])
                     else:
                         merged[k] = v
             meta = merged
@@ -191,18 +199,42 @@ class CheckpointManager:
         return True
 
     def wait_until_finished(self) -> None:
+        """Block until the save in flight is on disk and committed.  A write error on any rank fails the save on
+        every rank: nothing is committed, the step's directory is removed, and all ranks raise together (a rank
+        that raised alone would leave its peers waiting in the barrier)."""
+        error: Exception | None = None
         if self._writer is not None:
-            self._writer.wait()
+            try:
+                self._writer.wait()
+            except Exception as e:
+                error = e
         if not self._inflight:
+            if error is not None:
+                raise error
             return
-        _barrier()  # every rank's files are on disk
-        for step, step_dir in self._inflight:
+        ok = error is None
+        if _world() > 1:
+            import torch.distributed as dist
+
+            flags = [None] * _world()
+            dist.all_gather_object(flags, ok)
+            ok = all(flags)
+        inflight, self._inflight, meta, self._pending_meta = self._inflight, [], self._pending_meta, None
+        if not ok:
+            if _rank() == 0:
+                for _, step_dir in inflight:
+                    shutil.rmtree(step_dir, ignore_errors=True)
+            _barrier()
+            steps = [s for s, _ in inflight]
+            if error is not None:
+                raise RuntimeError(f"checkpoint write failed for step(s) {steps}; nothing was committed") from error
+            raise RuntimeError(f"checkpoint write failed on another rank for step(s) {steps}; nothing was committed")
+        for step, step_dir in inflight:
             if _rank() == 0:
                 with open(step_dir / "default" / "_METADATA", "w") as f:
-                    json.dump(self._pending_meta, f)
+                    json.dump(meta, f)
                 with open(step_dir / _COMMIT, "w") as f:
                     json.dump({"step": step, "world_size": _world()}, f)
-        self._inflight = []
         _barrier()
         self._apply_retention()
 
@@ -224,7 +256,7 @@ class CheckpointManager:
         except (OSError, ValueError) as e:
             raise CheckpointCorrupt(f"step {step}: unreadable metadata ({e})") from e
         for path, info in meta.items():
-            for leaf in info.get("chunks", [info] if "file" in info else []):
+            for leaf in info.get("chunks", info.get("shards", [info] if "file" in info else [])):
                 want = int(np.prod(leaf["shape"], dtype=np.int64)) * np.dtype(_NP_OF[getattr(torch, leaf["dtype"])]).itemsize
                 f = leaf_dir / leaf["file"]
                 have = f.stat().st_size if f.exists() else -1
@@ -247,24 +279,45 @@ class CheckpointManager:
                 t = t.view(torch.bfloat16)
             return t.reshape(info["shape"])
 
-        def read(path: str, flat_range: tuple[int, int] | None = None):
+        def read(path: str, flat_range: tuple[int, int] | None = None, shard: tuple[int, int, int] | None = None):
+            """``flat_range``: element range of a flat buffer saved in per-rank chunks.  ``shard = (dim, index,
+            count)``: the caller holds slice ``index`` of ``count`` along ``dim``; the saved entry may be whole or
+            split into any number of shards along the same dimension."""
             if path not in meta:
                 raise KeyError(f"checkpoint has no entry '{path}'")
             info = meta[path]
             if "scalar" in info:
                 return info["scalar"]
-            if "chunks" not in info:
-                return read_file(info)
-            # flat buffer saved as per-rank chunks: assemble the requested range from the chunks that overlap it
-            lo, hi = flat_range if flat_range is not None else (0, info["chunks"][0]["flat_total"])
-            first = info["chunks"][0]
-            out = torch.zeros(hi - lo, dtype=getattr(torch, first["dtype"]))
-            for c in info["chunks"]:
-                a, b = c["flat_range"]
-                s, e = max(a, lo), min(b, hi)
-                if s < e:
-                    out[s - lo:e - lo] = read_file(c)[s - a:e - a]
-            return out
+            if "shards" in info:
+                parts = sorted(info["shards"], key=lambda c: c["shard"][1])
+                dim, _, count = parts[0]["shard"]
+                if len(parts) != count or any(c["shard"][0] != dim or c["shard"][2] != count for c in parts):
+                    raise CheckpointCorrupt(f"step {step}: '{path}' has {len(parts)} of {count} shards")
+                if shard is not None and shard[0] != dim:
+                    raise ValueError(f"'{path}' was saved split along dim {dim}, requested along dim {shard[0]}")
+                if shard is not None and shard[2] == count:
+                    return read_file(parts[shard[1]])
+                full = torch.cat([read_file(c) for c in parts], dim=dim)
+            elif "chunks" not in info:
+                full = read_file(info)
+            else:
+                # flat buffer saved as per-rank chunks: assemble the requested range from the chunks that overlap it
+                lo, hi = flat_range if flat_range is not None else (0, info["chunks"][0]["flat_total"])
+                first = info["chunks"][0]
+                out = torch.zeros(hi - lo, dtype=getattr(torch, first["dtype"]))
+                for c in info["chunks"]:
+                    a, b = c["flat_range"]
+                    s, e = max(a, lo), min(b, hi)
+                    if s < e:
+                        out[s - lo:e - lo] = read_file(c)[s - a:e - a]
+                return out
+            if shard is None:
+                return full
+            dim, idx, cnt = shard
+            if full.shape[dim] % cnt != 0:
+                raise ValueError(f"'{path}' dim {dim} ({full.shape[dim]}) does not split into {cnt} shards")
+            per = full.shape[dim] // cnt
+            return full.narrow(dim, idx * per, per).contiguous()
 
         read.paths = list(meta.keys())  # type: ignore[attr-defined]
         state.load_checkpoint_tree(read)

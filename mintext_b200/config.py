@@ -197,6 +197,9 @@ class MinTextConfig(BaseModel):
     use_fp8: bool = False
     fp8_recipe: Fp8Recipe = Fp8Recipe.per_tensor
     kernel_backend: str = "auto"  # auto | cuda | oracle
+    # draw the initial weights on the GPU (seeded from `seed`); "auto": when the model has more than 2e9 parameters,
+    # where host-side sampling by every rank would take minutes and tens of GB of host memory per process
+    init_weights_on_device: str = "auto"  # auto | true | false
 
     # data
     dataset_type: DatasetType = DatasetType.synthetic

@@ -97,16 +97,22 @@ class BatchIterator:
         self._threads: list[threading.Thread] = []
         self._stop = threading.Event()
         self._perm_cache: dict[int, np.ndarray] = {}
+        self._perm_lock = threading.Lock()
 
     # position -> sample id ------------------------------------------------------------
     def _epoch_perm(self, epoch: int) -> np.ndarray:
-        if epoch not in self._perm_cache:
-            n = len(self.source)
-            ids = np.arange(n)
-            if self.shuffle:
-                np.random.RandomState((self.seed + 1000003 * epoch) % (2 ** 31)).shuffle(ids)
-            self._perm_cache = {epoch: ids}
-        return self._perm_cache[epoch]
+        """Sample order of one epoch.  Prefetch workers straddle an epoch boundary, so the two most recent epochs
+        stay cached and the array itself is returned under the lock (never looked up again after an eviction)."""
+        with self._perm_lock:
+            ids = self._perm_cache.get(epoch)
+            if ids is None:
+                ids = np.arange(len(self.source))
+                if self.shuffle:
+                    np.random.RandomState((self.seed + 1000003 * epoch) % (2 ** 31)).shuffle(ids)
+                keep = {e: v for e, v in self._perm_cache.items() if abs(e - epoch) <= 1}
+                keep[epoch] = ids
+                self._perm_cache = keep
+            return ids
 
     def _sample_ids(self, batch_index: int) -> list[int]:
         per_epoch = (len(self.source) // (self.world * self.batch_size)) * self.world * self.batch_size
@@ -134,7 +140,10 @@ class BatchIterator:
                 with self._lock:
                     b = self._next_to_schedule
                     self._next_to_schedule += 1
-                batch = self._make_batch(b)
+                try:
+                    batch = self._make_batch(b)
+                except BaseException as exc:  # handed to the consumer: a dead worker must not become a silent hang
+                    batch = exc
                 while not self._stop.is_set():
                     try:
                         self._q.put((b, batch), timeout=0.1)
@@ -163,9 +172,17 @@ class BatchIterator:
                 self._start()
             want = self.batches_done
             while want not in self._pending:
-                b, data = self._q.get()
+                try:
+                    b, data = self._q.get(timeout=1.0)
+                except queue.Empty:
+                    if not any(t.is_alive() for t in self._threads):
+                        raise RuntimeError(f"data workers exited before producing batch {want}")
+                    continue
                 self._pending[b] = data
             batch = self._pending.pop(want)
+            if isinstance(batch, BaseException):
+                self.close()
+                raise RuntimeError(f"data worker failed while building batch {want}") from batch
         self.batches_done += 1
         return batch
 

@@ -17,7 +17,7 @@ import torch
 from torch import nn
 
 from mintext_b200.modules.attention import Attention
-from mintext_b200.modules.linear import MLP, Linear
+from mintext_b200.modules.linear import MLP, Linear, normal_init
 from mintext_b200.modules.linear_attention import GatedDeltaRuleAttention
 from mintext_b200.modules.mla import MLAttention
 from mintext_b200.modules.moe import MoEBlock
@@ -212,7 +212,7 @@ class Transformer(nn.Module):
         dt, wdt = config.torch_dtype, config.torch_weight_dtype
         self.embedding_scale = float(config.hidden_size) ** 0.5 if config.scale_embeddings else None
         V, D = config.vocab_size, config.hidden_size
-        self.token_embedder = nn.Parameter((torch.randn(V, D, generator=rngs) * 0.02).to(wdt))
+        self.token_embedder = nn.Parameter(normal_init((V, D), 0.02, rngs, wdt))
         self.token_embedder.logical_axes = ("vocab", "embed")
         self.layers = nn.ModuleList(
             [DecoderLayer(config, i, rngs=rngs, mesh=mesh) for i in range(config.num_hidden_layers)])

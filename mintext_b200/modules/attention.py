@@ -64,6 +64,7 @@ class Attention(nn.Module):
                 lin.kernel = nn.Parameter((full[:, a:b] if dim == 1 else full[a:b]).clone().contiguous())
                 lin.kernel.logical_axes = ("embed", "heads", "kv") if dim == 1 else ("heads", "kv", "embed")
                 lin.kernel.tensor_parallel = True
+                lin.kernel.shard_spec = (dim, self.tp.rank, self.tp.size)
             self.local_heads, self.local_kv_heads = qhi - qlo, khi - klo
 
     def _forward_tp(self, x, positions, default_positions):

@@ -21,10 +21,54 @@ def _as_tuple(v) -> tuple[int, ...]:
     return tuple(v) if isinstance(v, (tuple, list)) else (int(v),)
 
 
+_INIT_DEVICE: torch.device | None = None
+
+
+class init_on_device:
+    """While active, parameter initialisers draw their values on ``device`` instead of the host.
+
+    Building a multi-billion-parameter model on the host costs minutes of single-threaded sampling and, with one
+    process per GPU, eight host copies of the weights; on the GPU the same tensors appear in milliseconds and only
+    the slices a rank keeps stay allocated.  Device streams are seeded from the model's host generator (one draw per
+    tensor), so a given seed still names one set of weights - though not the set the host path draws."""
+
+    def __init__(self, device):
+        self.device = torch.device(device) if device is not None else None
+
+    def __enter__(self):
+        global _INIT_DEVICE
+        self._prev = _INIT_DEVICE
+        _INIT_DEVICE = self.device if (self.device is not None and self.device.type == "cuda") else None
+        return self
+
+    def __exit__(self, *exc):
+        global _INIT_DEVICE
+        _INIT_DEVICE = self._prev
+
+
+def _device_generator(generator: torch.Generator | None) -> torch.Generator:
+    seed = int(torch.randint(0, 2 ** 31 - 1, (1,), generator=generator)) if generator is not None else 0
+    return torch.Generator(device=_INIT_DEVICE).manual_seed(seed)
+
+
+def normal_init(shape: Sequence[int], std: float, generator: torch.Generator | None,
+                dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``N(0, std^2)`` values (embedding tables, convolution taps)."""
+    if _INIT_DEVICE is not None:
+        t = torch.empty(tuple(shape), dtype=torch.float32, device=_INIT_DEVICE)
+        t.normal_(0.0, std, generator=_device_generator(generator))
+        return t.to(dtype)
+    return (torch.randn(tuple(shape), generator=generator) * std).to(dtype)
+
+
 def truncated_normal_init(shape: Sequence[int], fan_in: int, generator: torch.Generator | None,
                           dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """Standard normal truncated to [-2, 2], times ``1/sqrt(fan_in)`` with no variance correction
     (mintext/modules/linear.py:18-30)."""
+    if _INIT_DEVICE is not None:
+        t = torch.empty(tuple(shape), dtype=torch.float32, device=_INIT_DEVICE)
+        nn.init.trunc_normal_(t, mean=0.0, std=1.0, a=-2.0, b=2.0, generator=_device_generator(generator))
+        return t.mul_(1.0 / math.sqrt(max(fan_in, 1))).to(dtype)
     t = torch.empty(tuple(shape), dtype=torch.float32)
     nn.init.trunc_normal_(t, mean=0.0, std=1.0, a=-2.0, b=2.0, generator=generator)
     return (t / math.sqrt(max(fan_in, 1))).to(dtype)
@@ -140,12 +184,22 @@ class MLP(nn.Module):
                 lin.kernel = nn.Parameter((full[:, lo:hi] if dim == 1 else full[lo:hi]).clone().contiguous())
                 lin.kernel.logical_axes = axes
                 lin.kernel.tensor_parallel = True
+                lin.kernel.shard_spec = (dim, self.tp.rank, self.tp.size)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp is not None:
             from mintext_b200.parallel import tp as tpm
 
             lead, D = x.shape[:-1], x.shape[-1]
+            x2 = x.reshape(-1, D)
+            if self.gate.use_fp8 and self.gate.fp8_recipe == "mx_block" and self.act_name in oracle.ACT_CODES \
+                    and F.mxfp8_kernel_path(x2, self.gate.kernel) and F.mxfp8_kernel_path(x2, self.down.kernel):
+                # block-scaled FP8 on the rank's column / row slices: the gathered tokens are quantised once for
+                # gate|up; the collectives around the two GEMMs are the group's all-gather and reduce-scatter
+                xg = tpm.all_gather_tokens(x2, self.tp)
+                gu = F.linear_mxfp8(xg, torch.cat([self.gate.kernel, self.up.kernel], dim=1))
+                h = F.gated_act(gu, self.act_name)
+                return tpm.reduce_scatter_tokens(F.linear_mxfp8(h, self.down.kernel), self.tp).view(*lead, D)
             _, (g, u) = tpm.column_linear(x.reshape(-1, D), [self.gate.kernel, self.up.kernel], self.tp, self.gate.dtype)
             h = F.gated_act(torch.cat([g, u], dim=-1), self.act_name)
             return tpm.row_linear(h, self.down.kernel, self.tp, self.gate.dtype).view(*lead, D)

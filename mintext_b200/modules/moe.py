@@ -57,10 +57,13 @@ def _per_expert_init(shape_tail, fan_in, lo, hi, rngs, dtype):
     off the model's stream), so that a rank holding only a slice of the experts initialises exactly the values the
     unsharded model would have there."""
     tag = int(torch.randint(0, 2 ** 31 - 1, (1,), generator=rngs))
-    out = torch.empty((hi - lo,) + tuple(shape_tail), dtype=dtype)
+    out = None
     for e in range(lo, hi):
         g = torch.Generator().manual_seed((tag + 104729 * e) % (2 ** 63 - 1))
-        out[e - lo] = truncated_normal_init(shape_tail, fan_in, g, dtype)
+        w = truncated_normal_init(shape_tail, fan_in, g, dtype)
+        if out is None:  # on whichever device the initialiser draws
+            out = torch.empty((hi - lo,) + tuple(shape_tail), dtype=dtype, device=w.device)
+        out[e - lo] = w
     return out
 
 
@@ -89,6 +92,7 @@ class MoEExperts(nn.Module):
         if self.ep is not None and self.ep.size > 1:
             self.gate_up_proj.expert_parallel = True
             self.down_proj.expert_parallel = True
+            self.gate_up_proj.shard_spec = self.down_proj.shard_spec = (0, self.ep.rank, self.ep.size)
 
     def forward(self, x: torch.Tensor, topk_indices: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         """x ``[N,D]`` -> ``[N,D]``: route, grouped GEMM, SwiGLU on the column halves, grouped GEMM, unroute."""

@@ -99,6 +99,17 @@ def muon_matrix_view(name: str, shape: tuple[int, ...]) -> tuple[int, int, int] 
     return None
 
 
+def muon_shape_scale(fan_in: int, fan_out: int, consistent_rms: float | None = None) -> float:
+    """Factor applied to an orthogonalised ``[fan_in, fan_out]`` update: ``sqrt(max(1, fan_out / fan_in))`` (the
+    update of a matrix that widens its input is scaled up, one that narrows it is left alone), or
+    ``consistent_rms * sqrt(max(fan_in, fan_out))`` when a target RMS is configured.  The reference gets this from
+    ``optax.contrib.muon`` with the reduction axis first and the output axis last
+    (mintext/optim/optimizer.py:92-150)."""
+    if consistent_rms is not None:
+        return math.sqrt(max(fan_in, fan_out)) * float(consistent_rms)
+    return math.sqrt(max(1.0, fan_out / fan_in))
+
+
 def global_norm(tensors) -> torch.Tensor:
     ts = [t for t in tensors if t is not None]
     if not ts:
@@ -160,11 +171,9 @@ class Optimizer:
                 mu.mul_(beta).add_(g, alpha=1 - beta)
                 # Nesterov look-ahead with optax's bias correction of both terms
                 mu_hat = (beta * mu / (1 - beta ** (t + 1))) + ((1 - beta) * g / (1 - beta ** t))
-                upd = oracle.newton_schulz(mu_hat.reshape(b, r, c), cfg.muon_newton_schulz_steps).reshape(p.shape)
-                if cfg.muon_consistent_rms is not None:
-                    scale = math.sqrt(max(r, c)) * float(cfg.muon_consistent_rms)
-                else:
-                    scale = math.sqrt(max(1.0, r / c))
+                upd = oracle.newton_schulz(mu_hat.reshape(b, r, c), cfg.muon_newton_schulz_steps,
+                                           cfg.adam_eps).reshape(p.shape)
+                scale = muon_shape_scale(r, c, cfg.muon_consistent_rms)
                 pf.add_(upd * scale + wd * pf, alpha=-lr)
             if pf is not p:
                 p.copy_(pf)

@@ -133,36 +133,43 @@ class TrainEngine:
         self.shard_size = total_b // self.world
         lo = self.rank * self.shard_size
 
-        # fp32 master values come from the model's initialisation
-        master_full = torch.zeros(total_b, dtype=torch.float32)
-        for s in big:
-            master_full[s.offset:s.offset + s.numel] = s.param.detach().float().reshape(-1)
+        # fp32 master values come from the model's initialisation.  Parameters are consumed one at a time (they may
+        # already live on the device): the bf16 compute copy and this rank's slice of the fp32 master are filled
+        # from a parameter, then its own storage is released by re-pointing it at the flat buffer.
         self.param_flat = self._alloc_symmetric(total_b, torch.bfloat16)
-        self.param_flat.copy_(master_full.to(torch.bfloat16))
+        self.param_flat.zero_()
         self.grad_flat = self._alloc_symmetric(total_b, torch.float32)
         self.grad_flat.zero_()
-        self.master = master_full[lo:lo + self.shard_size].to(dev)
+        self.master = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
         self.exp_avg = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
         self.exp_avg_sq = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
         self.grad_shard = torch.empty(self.shard_size, device=dev, dtype=torch.float32)
+        hi = lo + self.shard_size
         # per-element weight decay is uniform over the big group (only the router bias is exempt and it is frozen)
         for s in big:
+            src = s.param.detach().reshape(-1)
+            self.param_flat[s.offset:s.offset + s.numel].copy_(src)
+            a, b = max(s.offset, lo), min(s.offset + s.numel, hi)
+            if a < b:
+                self.master[a - lo:b - lo].copy_(src[a - s.offset:b - s.offset])
+            del src
             s.param.data = self.param_flat[s.offset:s.offset + s.numel].view(s.param.shape)
             s.param.main_grad = self.grad_flat[s.offset:s.offset + s.numel].view(s.param.shape)
 
         # expert-parallel parameters: every rank owns its experts outright (compute copy, master, moments, grads)
         self.exp = FlatGroup(exp, _round_up(max(off_e, 4), _ALIGN))
         if exp:
-            em = torch.zeros(self.exp.total, dtype=torch.float32)
+            self.exp_master = torch.zeros(self.exp.total, device=dev, dtype=torch.float32)
+            self.exp_param = torch.zeros(self.exp.total, device=dev, dtype=torch.bfloat16)
             for s in exp:
-                em[s.offset:s.offset + s.numel] = s.param.detach().float().reshape(-1)
-            self.exp_master = em.to(dev)
-            self.exp_param = self.exp_master.to(torch.bfloat16)
+                sl = slice(s.offset, s.offset + s.numel)
+                self.exp_master[sl].copy_(s.param.detach().reshape(-1))
+                self.exp_param[sl].copy_(self.exp_master[sl])
+                s.param.data = self.exp_param[sl].view(s.param.shape)
             self.exp_grad = torch.zeros(self.exp.total, device=dev, dtype=torch.float32)
             self.exp_m = torch.zeros_like(self.exp_grad)
             self.exp_v = torch.zeros_like(self.exp_grad)
             for s in exp:
-                s.param.data = self.exp_param[s.offset:s.offset + s.numel].view(s.param.shape)
                 s.param.main_grad = self.exp_grad[s.offset:s.offset + s.numel].view(s.param.shape)
 
         self.small_param = torch.zeros(self.small.total, device=dev, dtype=torch.float32)
@@ -327,10 +334,8 @@ class TrainEngine:
         """Muon for the matrices, AdamW for everything else, over the slots held in ``[lo, hi)`` of a flat group
         (mintext/optim/optimizer.py:117-168: Nesterov momentum with optax's bias correction, Newton-Schulz,
         shape-dependent scale, decoupled weight decay)."""
-        import math
-
         from mintext_b200.ops import muon as muon_ops
-        from mintext_b200.optim.optimizer import muon_matrix_view
+        from mintext_b200.optim.optimizer import muon_matrix_view, muon_shape_scale
 
         cfg = self.config
         e = ext()
@@ -353,11 +358,8 @@ class TrainEngine:
             mu = mom[sl]
             mu.mul_(beta).add_(g, alpha=1 - beta)
             mu_hat = mu * (beta / (1 - beta ** (t + 1))) + g * ((1 - beta) / (1 - beta ** t))
-            upd = muon_ops.newton_schulz(mu_hat.view(b, r, c), cfg.muon_newton_schulz_steps).reshape(-1)
-            if cfg.muon_consistent_rms is not None:
-                scale = math.sqrt(max(r, c)) * float(cfg.muon_consistent_rms)
-            else:
-                scale = math.sqrt(max(1.0, r / c))
+            upd = muon_ops.newton_schulz(mu_hat.view(b, r, c), cfg.muon_newton_schulz_steps, cfg.adam_eps).reshape(-1)
+            scale = muon_shape_scale(r, c, cfg.muon_consistent_rms)
             wd = cfg.weight_decay if weight_decay_mask(s.name) else 0.0
             w = master[sl]
             w.add_(upd * scale + wd * w, alpha=-lr)
@@ -468,14 +470,17 @@ class TrainEngine:
             "opt_state/flat_exp_avg": {"tensor": self.exp_avg, **common},
             "opt_state/flat_exp_avg_sq": {"tensor": self.exp_avg_sq, **common},
         }
-        for s in self.exp.slots:  # rank r holds experts [r*El, (r+1)*El): a contiguous range of the stacked tensor
-            a = self.rank * s.numel
-            meta = {"writer_rank": self.rank, "flat_range": (a, a + s.numel), "flat_total": s.numel * self.world,
-                    "suffix": f".ep{self.rank}"}
+        # expert- / tensor-parallel parameters: this rank's slice along the parameter's shard dimension; of the
+        # data-parallel replicas that hold the same slice only the first writes it
+        first_replica = self.local_reduce_group is None or dist.get_rank(self.local_reduce_group) == 0
+        for s in self.exp.slots:
+            dim, idx, cnt = getattr(s.param, "shard_spec", (0, self.rank, self.world))
+            meta = {"writer_rank": self.rank if first_replica else -1, "shard": (int(dim), int(idx), int(cnt)),
+                    "suffix": f".shard{idx}of{cnt}"}
             sl = slice(s.offset, s.offset + s.numel)
-            tree[f"params/{s.name}"] = {"tensor": self.exp_master[sl], **meta}
-            tree[f"opt_state/mu/{s.name}"] = {"tensor": self.exp_m[sl], **meta}
-            tree[f"opt_state/nu/{s.name}"] = {"tensor": self.exp_v[sl], **meta}
+            tree[f"params/{s.name}"] = {"tensor": self.exp_master[sl].view(s.param.shape), **meta}
+            tree[f"opt_state/mu/{s.name}"] = {"tensor": self.exp_m[sl].view(s.param.shape), **meta}
+            tree[f"opt_state/nu/{s.name}"] = {"tensor": self.exp_v[sl].view(s.param.shape), **meta}
         for s in self.small.slots:
             tree[f"params/{s.name}"] = s.param.detach()
             tree[f"opt_state/mu/{s.name}"] = self.small_m[s.offset:s.offset + s.numel].view(s.param.shape)
@@ -520,12 +525,12 @@ class TrainEngine:
                 if a < b:
                     self.master[a - lo:b - lo] = full[a - s.offset:b - s.offset].to(self.device)
         for s in self.exp.slots:
-            a = self.rank * s.numel
+            spec = tuple(getattr(s.param, "shard_spec", (0, self.rank, self.world)))
             sl = slice(s.offset, s.offset + s.numel)
-            self.exp_master[sl] = read(f"params/{s.name}", (a, a + s.numel)).reshape(-1).float().to(self.device)
+            self.exp_master[sl] = read(f"params/{s.name}", shard=spec).reshape(-1).float().to(self.device)
             if not self.params_only_restore and f"opt_state/mu/{s.name}" in paths:
-                self.exp_m[sl] = read(f"opt_state/mu/{s.name}", (a, a + s.numel)).reshape(-1).to(self.device)
-                self.exp_v[sl] = read(f"opt_state/nu/{s.name}", (a, a + s.numel)).reshape(-1).to(self.device)
+                self.exp_m[sl] = read(f"opt_state/mu/{s.name}", shard=spec).reshape(-1).to(self.device)
+                self.exp_v[sl] = read(f"opt_state/nu/{s.name}", shard=spec).reshape(-1).to(self.device)
         if self.exp.slots:
             self.exp_param.copy_(self.exp_master.to(torch.bfloat16))
         for s in self.small.slots:

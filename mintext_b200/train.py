@@ -42,18 +42,30 @@ def _apply_moe_tiling(config, result) -> MinTextConfig:
                                      "moe_down_tiling": list(result.down_tiling)})
 
 
-def train(config: MinTextConfig) -> dict:
-    """Run ``config.steps`` optimizer steps.  Returns the metrics of the last step (floats)."""
-    logging.basicConfig(level=logging.INFO, format="%(asctime)s %(name)s %(message)s")
-    from mintext_b200.checkpoint import (create_checkpoint_manager, maybe_restore_checkpoint, save_checkpoint,
-                                         wait_for_checkpoint)
+def _device_init_wanted(config) -> bool:
+    mode = str(config.init_weights_on_device).lower()
+    if mode in ("true", "1", "yes"):
+        return True
+    if mode in ("false", "0", "no"):
+        return False
+    from mintext_b200.utils.pytree import estimate_param_count
+
+    return estimate_param_count(config) > 2e9
+
+
+def setup_training(config: MinTextConfig):
+    """Everything between a config and the first step: join the process group, build the mesh, install the
+    expert- / tensor-parallel contexts the modules consult while they are constructed, build the model and hand it
+    to the engine (GPU) or the plain-PyTorch train state (CPU).  Returns ``(mesh, model, state, device, use_gpu)``;
+    ``bench.py`` calls this too, so a benchmarked model is set up exactly as a trained one."""
     from mintext_b200.parallel import create_sharded_model, initialize_distributed, setup_mesh
-    from mintext_b200.utils import MetricLogger, Profiler
 
     initialize_distributed(config.jax_distributed_init_timeout)
     mesh = setup_mesh(config)
     use_gpu = torch.cuda.is_available() and config.kernel_backend != "oracle"
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_gpu else torch.device("cpu")
+    if use_gpu:
+        torch.cuda.set_device(device)
     if config.ici_expert_parallelism > 1 and config.num_experts > 0:
         from mintext_b200.parallel.ep import ExpertParallel, set_current_ep
 
@@ -69,8 +81,12 @@ def train(config: MinTextConfig) -> dict:
         set_current_tp(TensorParallel(mesh.group(("tensor",)), device, fused=config.fused_collectives))
         if mesh.shape["data"] * mesh.shape["fsdp"] > 1:
             local_reduce_group = mesh.group(("data", "fsdp"))
-    model = create_sharded_model(config, mesh)
-
+    elif config.ici_expert_parallelism > 1 and config.num_experts > 0:
+        dp = mesh.shape["data"] * mesh.shape["fsdp"]
+        if dp > config.ici_expert_parallelism:
+            local_reduce_group = _expert_replica_group(mesh, config.ici_expert_parallelism)
+    init_device = device if (use_gpu and _device_init_wanted(config)) else None
+    model = create_sharded_model(config, mesh, init_device=init_device)
     if use_gpu:
         from mintext_b200.parallel.engine import TrainEngine
 
@@ -79,6 +95,37 @@ def train(config: MinTextConfig) -> dict:
         from mintext_b200 import trainer
 
         state = trainer.create_train_state(model, config)
+    return mesh, model, state, device, use_gpu
+
+
+def _expert_replica_group(mesh, ep: int):
+    """Ranks that hold the same experts: one from every expert-parallel block of the batch-sharding ranks."""
+    import torch.distributed as dist
+
+    rank = dist.get_rank()
+    mine = None
+    seen = set()
+    for r in range(mesh.size):
+        dp = mesh.ranks_along(("data", "fsdp"), r)
+        pos = dp.index(r) % ep
+        members = tuple(dp[pos::ep])
+        if members in seen:
+            continue
+        seen.add(members)
+        g = dist.new_group(list(members))
+        if rank in members:
+            mine = g
+    return mine
+
+
+def train(config: MinTextConfig) -> dict:
+    """Run ``config.steps`` optimizer steps.  Returns the metrics of the last step (floats)."""
+    logging.basicConfig(level=logging.INFO, format="%(asctime)s %(name)s %(message)s")
+    from mintext_b200.checkpoint import (create_checkpoint_manager, maybe_restore_checkpoint, save_checkpoint,
+                                         wait_for_checkpoint)
+    from mintext_b200.utils import MetricLogger, Profiler
+
+    mesh, model, state, device, use_gpu = setup_training(config)
     metric_logger = MetricLogger(config, params=model)
     profiler = Profiler(config)
 

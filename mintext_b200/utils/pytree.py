@@ -62,6 +62,31 @@ def model_flops_per_token_batch(config, batch: int) -> float:
     return float((ffn + (proj + scores) * L + head) * 3)
 
 
+def estimate_param_count(config) -> float:
+    """Approximate number of parameters of the model a config describes (embedding, projections, feed-forward
+    weights; norms and biases ignored).  Used to pick host- or device-side initialisation before anything is built."""
+    D, V, L = config.hidden_size, config.vocab_size, config.num_hidden_layers
+    H = config.num_attention_heads
+    Hkv = config.num_key_value_heads or H
+    dh = config.head_dim or D // H
+    if config.attention_type == "mla":
+        attn = (D * config.q_lora_rank + config.q_lora_rank * H * config.qk_head_dim
+                + D * (config.kv_lora_rank + config.qk_rope_head_dim)
+                + config.kv_lora_rank * H * (config.qk_nope_head_dim + config.v_head_dim) + H * config.v_head_dim * D)
+    else:
+        attn = D * (H + 2 * Hkv) * dh + H * dh * D
+    dense = 3 * D * config.intermediate_size
+    if config.num_experts > 0:
+        moe_layers = max(0, L - config.first_k_dense_replace)
+        moe = D * config.num_experts + 3 * D * config.moe_intermediate_size * (
+            config.num_experts + config.n_shared_experts)
+        ffn = dense * (L - moe_layers) + moe * moe_layers
+    else:
+        ffn = dense * L
+    emb = V * D * (1 if config.tie_word_embeddings else 2)
+    return float(emb + attn * L + ffn)
+
+
 def calculate_tflops_per_device(config) -> float:
     """TFLOP per device per optimizer step, assuming each device processes ``per_device_batch_size`` sequences
     per micro-step."""

@@ -262,3 +262,96 @@ def test_parity_gemma3(tmp_path):
                   scale_embeddings=True, sliding_window=8, sliding_window_pattern=2,
                   hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True, rope_theta=1e6, rope_local_theta=1e4,
                   rms_norm_eps=1e-6), "Gemma3ForCausalLM", tmp_path, atol=2e-3)
+
+
+# ------------------------------------------------------------------ sharded entries and failing writers
+class _ShardedState:
+    """Stand-in for an engine whose ``w`` is column-split over ``count`` tensor-parallel ranks and whose ``e`` is
+    split along dim 0 (experts)."""
+
+    FULL_W = torch.arange(6 * 8, dtype=torch.float32).reshape(6, 8)
+    FULL_E = torch.arange(4 * 3 * 2, dtype=torch.float32).reshape(4, 3, 2)
+
+    def __init__(self, index, count, rank):
+        self.index, self.count, self.rank = index, count, rank
+        self.w = torch.zeros(6, 8 // count)
+        self.e = torch.zeros(4 // count, 3, 2)
+
+    def fill(self):
+        self.w = self.FULL_W.chunk(self.count, 1)[self.index].contiguous()
+        self.e = self.FULL_E.chunk(self.count, 0)[self.index].contiguous()
+
+    def checkpoint_tree(self):
+        def meta(dim):
+            return {"writer_rank": self.rank, "shard": (dim, self.index, self.count),
+                    "suffix": f".shard{self.index}of{self.count}"}
+        return {"step": 1, "params/w": {"tensor": self.w, **meta(1)}, "params/e": {"tensor": self.e, **meta(0)}}
+
+    def load_checkpoint_tree(self, read):
+        self.w = read("params/w", shard=(1, self.index, self.count))
+        self.e = read("params/e", shard=(0, self.index, self.count))
+
+
+def _save_two_shards(rank, world, directory):
+    from mintext_b200.checkpoint.manager import CheckpointManager
+
+    st = _ShardedState(rank, world, rank)
+    st.fill()
+    m = CheckpointManager(directory, enable_async=False)
+    assert m.save(1, st, force=True)
+    back = _ShardedState(rank, world, rank)
+    m.restore(1, back)
+    return bool(torch.equal(back.w, st.w) and torch.equal(back.e, st.e))
+
+
+def test_tensor_parallel_shards_restore_under_another_degree(tmp_path):
+    """Saved by two ranks split along their shard dimensions; restored whole (degree 1) and in four shards."""
+    import functools
+
+    from mintext_b200.checkpoint.manager import CheckpointManager
+    from tests.test_sharding import run_ranks
+
+    out = run_ranks(functools.partial(_save_two_shards, directory=str(tmp_path)), 2, 29641)
+    assert out == {0: True, 1: True}
+    m = CheckpointManager(str(tmp_path), read_only=True)
+    one = _ShardedState(0, 1, 0)
+    m.restore(1, one)
+    assert torch.equal(one.w, _ShardedState.FULL_W) and torch.equal(one.e, _ShardedState.FULL_E)
+    for i in range(4):
+        q = _ShardedState(i, 4, 0)
+        m.restore(1, q)
+        assert torch.equal(q.w, _ShardedState.FULL_W.chunk(4, 1)[i]) and torch.equal(q.e, _ShardedState.FULL_E[i:i + 1])
+    meta = json.loads((tmp_path / "1" / "default" / "_METADATA").read_text())
+    assert [c["shard"] for c in meta["params/w"]["shards"]] == [[1, 0, 2], [1, 1, 2]]
+
+
+def test_failed_background_write_commits_nothing(tmp_path, monkeypatch):
+    from mintext_b200.checkpoint import manager as mgr_mod
+
+    class _FailingWriter:
+        failed = False
+
+        def submit(self, path, host):
+            pass
+
+        def wait(self):
+            if not self.failed:  # like the real writers: an error is reported once, then cleared
+                self.failed = True
+                raise OSError("disk full")
+
+    c = MinTextConfig(num_hidden_layers=1, hidden_size=32, num_attention_heads=2, intermediate_size=64, vocab_size=64,
+                      seq_length=8, dtype="float32", checkpoint_dir=str(tmp_path), checkpoint_period=1,
+                      async_checkpointing=True, enable_tensorboard=False)
+    state = trainer.create_train_state(Transformer(c, rngs=0), c)
+    m = create_checkpoint_manager(c)
+    monkeypatch.setattr(mgr_mod, "_make_writer", lambda: _FailingWriter())
+    assert m.save(1, state)
+    with pytest.raises(RuntimeError, match="nothing was committed"):
+        m.wait_until_finished()
+    assert m.all_steps() == [] and not (tmp_path / "1").exists()
+    m.wait_until_finished()          # the failed save is gone: nothing left to commit, no error
+    assert m.all_steps() == []
+    m._writer = None
+    monkeypatch.undo()
+    assert m.save(1, state) and (m.wait_until_finished() or True)
+    assert m.all_steps() == [1]

@@ -125,6 +125,43 @@ def test_shipped_configs_load():
         assert c.num_hidden_layers >= 1, f
 
 
+def test_benchmark_configs_build_an_eight_gpu_mesh():
+    """Every shipped benchmark config must give a valid mesh on the eight ranks it is written for."""
+    from pathlib import Path
+
+    from mintext_b200.parallel.mesh import create_mesh
+
+    root = Path(__file__).resolve().parents[1] / "configs" / "benchmarks"
+    files = sorted(root.glob("*.yml"))
+    assert len(files) >= 4
+    for f in files:
+        c = load_config(f)
+        m = create_mesh(c, devices=list(range(8)))
+        assert m.size == 8, f
+        assert (m.shape["data"] * m.shape["fsdp"]) % m.shape["expert"] == 0, f
+        if c.num_experts > 0:
+            assert m.shape["expert"] == 8 and c.num_experts % 8 == 0, f
+            assert len(m.expert_group_ranks(3)) == 8
+    c = load_config(root / "llama-3-8b-b200.yml")
+    assert c.use_fp8 and str(c.fp8_recipe) == "mx_block" and c.ici_tensor_parallelism == 2
+
+
+def test_bench_model_configs_split_the_batch():
+    import importlib.util
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("bench", Path(__file__).resolve().parents[1] / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for name, (yml, gb, _, _) in bench.BENCH_MODELS.items():
+        cfg, got = bench.yaml_config(name, 8, None, None, None, 6, [])
+        tp = cfg.ici_tensor_parallelism
+        assert got == gb
+        assert cfg.gradient_accumulation_steps * cfg.per_device_batch_size * (8 // tp) == gb, name
+    cfg, _ = bench.yaml_config("qwen3moe", 2, 8, None, None, 6, ["num_experts=32", "ici_expert_parallelism=2"])
+    assert cfg.num_experts == 32 and cfg.ici_expert_parallelism == 2
+
+
 def test_layer_type_generation():
     assert MinTextConfig(model_type="qwen3_next", num_hidden_layers=8).layer_types.count("full_attention") == 2
     g = MinTextConfig(model_type="gemma3", num_hidden_layers=12).layer_types

@@ -193,3 +193,43 @@ def test_rank_sharding_is_disjoint(mmap_path, tmp_path):
     ia = sum((a._sample_ids(i) for i in range(5)), [])
     ib = sum((b._sample_ids(i) for i in range(5)), [])
     assert not set(ia) & set(ib) and len(set(ia)) == 10
+
+
+class _ArraySource:
+    """Tiny in-memory source: sample ``i`` is ``seq_len + 1`` tokens all equal to ``i``."""
+
+    def __init__(self, n, seq_len=4, fail_at=None):
+        self.n, self.seq_len, self.fail_at = n, seq_len, fail_at
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i):
+        if self.fail_at is not None and i == self.fail_at:
+            raise OSError(f"cannot read sample {i}")
+        return {"tokens": np.full(self.seq_len + 1, i, dtype=np.int32)}
+
+
+def test_prefetch_workers_cross_epoch_boundaries_in_order():
+    from mintext_b200.data.pipeline import BatchIterator
+
+    src = _ArraySource(10)
+    serial = BatchIterator(src, 2, 7, True, workers=0)
+    threaded = BatchIterator(src, 2, 7, True, workers=4, buffer_size=8)
+    try:
+        for _ in range(40):  # 5 batches per epoch: eight epoch boundaries
+            a, b = next(serial), next(threaded)
+            assert np.array_equal(a["input_tokens"], b["input_tokens"])
+    finally:
+        threaded.close()
+
+
+def test_worker_exception_reaches_the_consumer():
+    from mintext_b200.data.pipeline import BatchIterator
+
+    it = BatchIterator(_ArraySource(8, fail_at=5), 2, 0, False, workers=3, buffer_size=8)
+    with pytest.raises(RuntimeError, match="data worker failed") as info:
+        for _ in range(8):
+            next(it)
+    assert isinstance(info.value.__cause__, OSError)
+    it.close()

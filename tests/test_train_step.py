@@ -127,6 +127,35 @@ def test_newton_schulz_orthogonalises():
     assert oracle.newton_schulz(torch.randn(3, 48, 16)).shape == (3, 48, 16)
 
 
+def test_muon_update_of_a_widening_kernel_by_hand():
+    """First Muon step on an [in=8, out=32] kernel, written out with plain tensor algebra (no shared helper):
+    bias-corrected Nesterov momentum equals the gradient at t=1, five quintic iterations on the wide orientation,
+    update scaled by sqrt(max(1, out/in)) = 2, decoupled weight decay.  The narrowing [32, 8] kernel gets scale 1."""
+    torch.manual_seed(3)
+    c = cfg(optimizer="muon", learning_rate=0.05, gradient_clip_threshold=0.0, weight_decay=0.1, lr_schedule="linear",
+            warmup_steps_fraction=0.0, lr_final_fraction=1.0, muon_beta=0.95, muon_newton_schulz_steps=5)
+    for shape, scale in (((8, 32), 2.0), ((32, 8), 1.0)):
+        name = "layers.0.mlp.gate.kernel"
+        w0 = torch.randn(shape)
+        g = torch.randn(shape)
+        p = {name: w0.clone()}
+        opt = create_optimizer(c)
+        st = opt.init(p)
+        opt.update(p, {name: g}, st, 0)
+        beta = 0.95
+        mu = (1 - beta) * g
+        mu_hat = beta * mu / (1 - beta ** 2) + (1 - beta) * g / (1 - beta)
+        x = mu_hat if shape[0] <= shape[1] else mu_hat.t()
+        x = x / (torch.sqrt((x * x).sum()) + c.adam_eps)
+        for _ in range(5):
+            a = x @ x.t()
+            x = 3.4445 * x + (-4.7750 * a + 2.0315 * (a @ a)) @ x
+        o = x if shape[0] <= shape[1] else x.t()
+        lr = float(opt.schedule(0))
+        want = w0 - lr * (scale * o + 0.1 * w0)
+        assert torch.allclose(p[name], want, atol=1e-5), shape
+
+
 @pytest.mark.parametrize("optimizer", ["adamw", "muon"])
 def test_loss_decreases_on_a_fixed_batch(optimizer):
     c = cfg(optimizer=optimizer, learning_rate=3e-3 if optimizer == "adamw" else 2e-2)

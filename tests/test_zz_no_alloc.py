@@ -38,8 +38,8 @@ def _reference(x, w, rstd, dy, dres):
     return dx, dw
 
 
-def _call(fn, x, w, rstd, dy, dres, accumulate=0, dw=None):
-    dx = torch.empty_like(x)
+def _call(fn, x, w, rstd, dy, dres, accumulate=0, dw=None, dx=None):
+    dx = torch.empty_like(x) if dx is None else dx
     dw = torch.zeros(x.shape[1], device="cuda") if dw is None else dw
     err = ctypes.create_string_buffer(256)
     stream = torch.cuda.current_stream().cuda_stream
@@ -51,18 +51,25 @@ def _call(fn, x, w, rstd, dy, dres, accumulate=0, dw=None):
 def test_no_alloc_entry_point_matches_ordinary_one_twice():
     fn = _lib()
     torch.manual_seed(0)
-    before = None
     for call, (rows, dim) in enumerate([(777, 2048), (1500, 4096)]):
         x = torch.randn(rows, dim, device="cuda", dtype=torch.bfloat16)
         dy = torch.randn(rows, dim, device="cuda", dtype=torch.bfloat16)
         dres = torch.randn(rows, dim, device="cuda", dtype=torch.bfloat16) if call == 1 else None
         w = (1 + 0.1 * torch.randn(dim, device="cuda")).float()
         rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-5)
+        # outputs exist before the call, so anything that appears on the device during it was allocated by it:
+        # neither torch's caching allocator nor the driver (free memory of the device) may move
+        dx = torch.empty_like(x)
+        dw = torch.zeros(dim, device="cuda")
+        if call == 0:
+            assert _call(fn, x, w, rstd, dy, dres, dw=dw, dx=dx)[0] == 0  # first call on the device: address look-up
         torch.cuda.synchronize()
-        if before is None:
-            before = torch.cuda.memory_allocated()
-        rc, msg, dx, dw = _call(fn, x, w, rstd, dy, dres)
+        allocated, reserved, free = torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.mem_get_info()[0]
+        rc, msg, dx, dw = _call(fn, x, w, rstd, dy, dres, dw=dw, dx=dx)
+        torch.cuda.synchronize()
         assert rc == 0, msg
+        assert torch.cuda.memory_allocated() == allocated and torch.cuda.memory_reserved() == reserved
+        assert torch.cuda.mem_get_info()[0] >= free, "device memory shrank during an allocation-free call"
         ref_dx, ref_dw = _reference(x, w, rstd, dy, dres)
         torch.cuda.synchronize()
         assert torch.equal(dx, ref_dx)
@@ -87,3 +94,19 @@ def test_no_alloc_entry_point_accumulates_and_rejects_oversize():
     assert rc != 0 and "exceeds the built-in scratch limit" in msg
     rc, msg, _, _ = _call(fn, x[:, :1020].contiguous(), w[:1020].contiguous(), rstd, dy[:, :1020].contiguous(), None)
     assert rc != 0 and "multiple of 8" in msg
+
+
+def test_no_alloc_entry_point_with_no_rows_writes_the_empty_sum():
+    fn = _lib()
+    dim = 512
+    x = torch.empty(0, dim, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(dim, device="cuda")
+    rstd = torch.empty(0, device="cuda")
+    stale = torch.full((dim,), 7.0, device="cuda")
+    rc, msg, _, dw = _call(fn, x, w, rstd, x, None, accumulate=0, dw=stale.clone())
+    torch.cuda.synchronize()
+    assert rc == 0, msg
+    assert torch.count_nonzero(dw).item() == 0            # a sum over zero rows
+    rc, msg, _, dw = _call(fn, x, w, rstd, x, None, accumulate=1, dw=stale.clone())
+    torch.cuda.synchronize()
+    assert rc == 0 and torch.equal(dw, stale)             # accumulating nothing leaves dw alone
