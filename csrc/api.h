@@ -72,6 +72,11 @@ void cross_entropy_fwd_bwd(void* logits, const int64_t* targets, float* loss, fl
                            int64_t rows, int V, int64_t ldl, float label_smoothing, float z_weight,
                            float softcap, float grad_scale, bool write_grad, cudaStream_t stream);
 
+// ---- elementwise/threefry.cu
+// out[i] = randint element (start + i) of the stream keyed by the two split keys (a0,a1) and (b0,b1), in [0, span)
+void threefry_randint(int64_t* out, int64_t count, uint32_t a0, uint32_t a1, uint32_t b0, uint32_t b1, uint64_t start,
+                      uint32_t span, cudaStream_t stream);
+
 // ---- elementwise/embedding.cu
 void embedding_fwd(const void* table, const int64_t* ids, void* out, int64_t tokens, int dim, float scale,
                    cudaStream_t stream);

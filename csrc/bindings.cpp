@@ -160,6 +160,14 @@ void cross_entropy(torch::Tensor& logits, const torch::Tensor& targets, torch::T
                             (float)z_weight, (float)softcap, (float)grad_scale, write_grad, cur_stream());
 }
 
+void threefry_randint(torch::Tensor& out, int64_t a0, int64_t a1, int64_t b0, int64_t b1, int64_t start, int64_t span) {
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == torch::kInt64);
+  TORCH_CHECK(span > 0 && span <= 0xFFFFFFFFll && start >= 0);
+  c10::cuda::CUDAGuard guard(out.device());
+  mt::threefry_randint(out.data_ptr<int64_t>(), out.numel(), (uint32_t)a0, (uint32_t)a1, (uint32_t)b0, (uint32_t)b1,
+                       (uint64_t)start, (uint32_t)span, cur_stream());
+}
+
 void embedding_fwd(const torch::Tensor& table, const torch::Tensor& ids, torch::Tensor& out, double scale) {
   TORCH_CHECK(table.is_contiguous() && out.is_contiguous() && ids.is_contiguous());
   TORCH_CHECK(table.scalar_type() == torch::kBFloat16 && ids.scalar_type() == torch::kInt64);
@@ -664,6 +672,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gate_mul_fwd", &gate_mul_fwd);
   m.def("gate_mul_bwd", &gate_mul_bwd);
   m.def("cross_entropy", &cross_entropy);
+  m.def("threefry_randint", &threefry_randint);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("adamw_step", &adamw_step);

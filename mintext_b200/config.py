@@ -200,6 +200,9 @@ class MinTextConfig(BaseModel):
     # draw the initial weights on the GPU (seeded from `seed`); "auto": when the model has more than 2e9 parameters,
     # where host-side sampling by every rank would take minutes and tens of GB of host memory per process
     init_weights_on_device: str = "auto"  # auto | true | false
+    # synthetic batches: "threefry" = counter-based stream keyed by `seed`, split once per step, every rank writing
+    # its own rows of the global batch on the device; "torch" = the host generator (one stream per data-parallel rank)
+    synthetic_rng: str = "threefry"
 
     # data
     dataset_type: DatasetType = DatasetType.synthetic

@@ -35,6 +35,41 @@ def _make_synthetic_batch(config, generator: torch.Generator, batch_rows: int, d
     return {"input_tokens": tok, "target_tokens": tgt}
 
 
+class _SyntheticStream:
+    """Source of the synthetic batches of one data-parallel rank (``synthetic_rng``).  With the counter-based
+    generator the key is split once per step and the rank draws rows ``[dp_rank * rows, (dp_rank + 1) * rows)`` of
+    the step's global batch directly on its device; ``skip`` advances past the steps a resumed run has consumed."""
+
+    def __init__(self, config, rows: int, dp_rank: int, device):
+        from mintext_b200.utils import threefry
+
+        self.config, self.rows, self.dp_rank, self.device = config, rows, dp_rank, device
+        self.counter_based = str(config.synthetic_rng) == "threefry"
+        self.key = threefry.key(config.seed)
+        self.gen = torch.Generator(device="cpu").manual_seed(config.seed * 1000003 + dp_rank)
+
+    def skip(self, steps: int) -> None:
+        from mintext_b200.utils import threefry
+
+        for _ in range(steps):
+            if self.counter_based:
+                self.key = threefry.split(self.key)[0]
+            else:
+                _make_synthetic_batch(self.config, self.gen, self.rows, torch.device("cpu"))
+
+    def next(self) -> dict[str, torch.Tensor]:
+        if not self.counter_based:
+            return _make_synthetic_batch(self.config, self.gen, self.rows, self.device)
+        from mintext_b200.utils import threefry
+
+        self.key, batch_key = threefry.split(self.key)
+        cfg = self.config
+        tok = threefry.randint_rows(batch_key, self.dp_rank * self.rows, self.rows, cfg.seq_length, cfg.vocab_size,
+                                    self.device)
+        tgt = tok.roll(-1, dims=1) if cfg.synthetic_shift_targets else tok
+        return {"input_tokens": tok, "target_tokens": tgt}
+
+
 def _apply_moe_tiling(config, result) -> MinTextConfig:
     """Copy autotuned grouped-GEMM tilings into the config (kept for parity; tile shapes are fixed by the
     tcgen05 kernels, so the values are informational)."""
@@ -154,10 +189,9 @@ def train(config: MinTextConfig) -> dict:
         if config.eval_period > 0:
             eval_iter = create_eval_iterator(config, mesh)
     rank = int(os.environ.get("RANK", "0"))
-    gen = torch.Generator(device="cpu").manual_seed(config.seed * 1000003 + rank // tp)
-    for _ in range(start_step):  # resume: skip the batches already consumed
-        if train_iter is None:
-            _make_synthetic_batch(config, gen, rows, torch.device("cpu"))
+    synthetic = _SyntheticStream(config, rows, rank // tp, device)
+    if train_iter is None:
+        synthetic.skip(start_step)  # resume: past the batches already consumed
 
     heartbeat = None
     if config.heartbeat_interval > 0 and world > 1:
@@ -181,7 +215,7 @@ def train(config: MinTextConfig) -> dict:
             nb = next(train_iter)
             batch = {k: torch.from_numpy(v).long().to(device, non_blocking=True) for k, v in nb.items()}
         else:
-            batch = _make_synthetic_batch(config, gen, rows, device)
+            batch = synthetic.next()
         if use_gpu:
             ev0.record()
             metrics = state.train_step(batch)

@@ -507,3 +507,13 @@ def test_gated_mlp_single_node_matches_separate_kernels(T, D, I, act, monkeypatc
     check_status()
     for name, a, b in zip(("y", "dx", "dwg", "dwu", "dwd"), res["1"], res["0"]):
         assert _rel_err(a, b) < 1.5e-2, (name, _rel_err(a, b))
+
+
+def test_threefry_randint_kernel_equals_the_tensor_path():
+    from mintext_b200.utils import threefry as tf
+
+    for seed, (row_lo, rows, cols, span) in enumerate([(0, 4, 128, 128256), (5, 3, 100, 17), (2 ** 20, 2, 4096, 151936)]):
+        k = tf.key(seed + 11)
+        got = tf.randint_rows(k, row_lo, rows, cols, span, device="cuda", use_kernel=True)
+        want = tf.randint_rows(k, row_lo, rows, cols, span, device="cpu", use_kernel=False)
+        assert got.dtype == torch.int64 and torch.equal(got.cpu(), want)
