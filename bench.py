@@ -276,6 +276,14 @@ def main() -> None:
         e2e = {"value": tokens_per_step / (ms2 / 1e3), "unit": "tokens/s", "ms_per_step": ms2,
                "h2d_bytes_per_step": rows * args.seq_len * 8, "d2h_bytes_per_step": 4}
 
+    from mintext_b200.parallel.ep import current_ep
+
+    dropped = None  # routed rows that exceeded an expert rank's receive capacity (whole run, all ranks)
+    if current_ep() is not None:
+        d = torch.tensor([current_ep().dropped_rows()], device=dev, dtype=torch.int64)
+        if world > 1:
+            dist.all_reduce(d)
+        dropped = int(d.item())
     free_b, total_b = torch.cuda.mem_get_info(dev)  # includes symmetric-memory and NCCL buffers
     peak = torch.tensor([max(torch.cuda.max_memory_reserved(dev), total_b - free_b) / 2 ** 30], device=dev)
     if world > 1:
@@ -293,7 +301,7 @@ def main() -> None:
             "dtype": ("bf16 (mxfp8 MLP projections)" if args.fp8_recipe == "mx_block" else "bf16 (fp8 e4m3/e5m2 MLP projections)") if args.fp8_mlp else "bf16", "data": "synthetic uniform-random token ids, random-init weights", "impl": "own",
             "tokens_per_sec_per_gpu": value / world, "tflops_per_gpu": tflops_per_gpu,
             "mfu_vs_nominal_2250": tflops_per_gpu / 2250.0, "final_loss": final_loss,
-            "peak_memory_gb": peak_gb,
+            "peak_memory_gb": peak_gb, "moe_dropped_rows": dropped,
             "config": {"model": model_desc,
                        "global_batch": args.global_batch, "seq_len": args.seq_len,
                        "parallelism": parallelism, "remat_policy": str(cfg.remat_policy),

@@ -100,6 +100,12 @@ void symm_barrier(const PeerPtrs& flags, int rank, int world, int seq, int* stat
 // out[0..n) = sum over ranks of grads[r][lo..lo+n) ; *sumsq += |out|^2   (n multiple of 4, lo multiple of 4)
 void grad_pull_reduce(const PeerPtrs& grads, int rank, int world, int64_t lo, int64_t n, float* out, float* sumsq,
                       cudaStream_t stream);
+// One bucket of the same reduction, with the readiness handshake folded in (see comm/rs_optim.cu).  `flags` are the
+// ranks' int[world * kBucketSlots] tables; `lo`/`n` select this rank's slice of the bucket in the flat buffers; the
+// consumed source elements are cleared.  `blocks` caps the grid (<= 0: a full-device grid).
+constexpr int kBucketSlots = 1024;
+void grad_pull_bucket(const PeerPtrs& grads, const PeerPtrs& flags, int rank, int world, int bucket, int seq, int64_t lo,
+                      int64_t n, float* out, bool accumulate, int blocks, int* status, cudaStream_t stream);
 // AdamW on the local shard, bf16 result stored to params[r][lo..lo+n) of every rank r   (n multiple of 8)
 void adamw_publish(float* master, float* m, float* v, const float* grad, const PeerPtrs& params, int world, int64_t lo,
                    int64_t n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
@@ -113,6 +119,15 @@ void ep_pull_rows(void* out, const int* src_rank, const int64_t* src_pos, const 
 // out[r] = scale[r] (or 1) * row at byte address row_src[r] (peer-mapped or local), zero row where the address is 0
 void ep_gather_rows(void* out, const unsigned long long* row_src, const float* row_scale, int64_t rows, int dim,
                     cudaStream_t stream);
+// Routing plan of the peer-memory expert exchange (comm/ep_rows.cu).  Count tables are int[2][kMaxPeers][ep_count_slots()]
+// in symmetric memory.
+int ep_count_slots();
+void ep_push_counts(const int64_t* counts, const PeerPtrs& tables, int rank, int R, int E, int parity, cudaStream_t stream);
+void ep_plan(const int64_t* flat, const int64_t* pos_l, const int* off_l, const float* w, const int* table, int rank, int R,
+             int E, int El, int64_t cap, int K, int64_t NK, int* dst_rank, int64_t* dst_pos, int64_t* home_pos,
+             int* off_local, int* tags, unsigned long long* dropped, cudaStream_t stream);
+void ep_resolve(const int* tags, const PeerPtrs& in_bufs, const PeerPtrs& out_bufs, int64_t cap, int64_t row_bytes,
+                unsigned long long* row_src, unsigned long long* row_dst, float* scale, cudaStream_t stream);
 
 // ---- comm/tp_gemm.cu: tensor-parallel GEMMs fused with their collective (bf16; T tokens over `world` ranks)
 // C[T,N] = gather(shards)[T,K] * op(B); the kernel itself fills `gathered` from the ranks' shards (peer memory)

@@ -274,6 +274,19 @@ void grad_pull_reduce(const std::vector<int64_t>& grad_ptrs, int64_t rank, int64
                        sumsq.data_ptr<float>(), cur_stream());
 }
 
+void grad_pull_bucket(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& flag_ptrs, int64_t rank,
+                      int64_t bucket, int64_t seq, int64_t lo, torch::Tensor& out, bool accumulate, int64_t blocks,
+                      torch::Tensor& status) {
+  TORCH_CHECK(out.scalar_type() == torch::kFloat32 && out.is_contiguous() && out.numel() % 4 == 0 && lo % 4 == 0);
+  TORCH_CHECK(grad_ptrs.size() == flag_ptrs.size() && bucket >= 0 && bucket < mt::kBucketSlots);
+  c10::cuda::CUDAGuard guard(out.device());
+  mt::grad_pull_bucket(to_peers(grad_ptrs), to_peers(flag_ptrs), (int)rank, (int)grad_ptrs.size(), (int)bucket, (int)seq,
+                       lo, out.numel(), out.data_ptr<float>(), accumulate, (int)blocks, status.data_ptr<int>(),
+                       cur_stream());
+}
+
+int64_t bucket_flag_slots() { return mt::kBucketSlots; }
+
 void adamw_publish(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, const torch::Tensor& grad,
                    const std::vector<int64_t>& param_ptrs, int64_t lo, double lr, double b1, double b2, double eps,
                    double wd, double bc1, double bc2, double grad_scale, const c10::optional<torch::Tensor>& clip_coef) {
@@ -592,6 +605,59 @@ torch::Tensor moe_gather_rows(const torch::Tensor& x, const torch::Tensor& src, 
 }
 
 // -> (out [N, D] bf16 or undefined, dw [N, K] fp32 or undefined)
+void ep_push_counts(const torch::Tensor& counts, const std::vector<int64_t>& table_ptrs, int64_t rank, int64_t parity) {
+  TORCH_CHECK(counts.is_cuda() && counts.is_contiguous() && counts.scalar_type() == torch::kInt64);
+  TORCH_CHECK(counts.numel() <= mt::ep_count_slots() && (parity == 0 || parity == 1));
+  c10::cuda::CUDAGuard guard(counts.device());
+  mt::ep_push_counts(counts.data_ptr<int64_t>(), to_peers(table_ptrs), (int)rank, (int)table_ptrs.size(),
+                     (int)counts.numel(), (int)parity, cur_stream());
+}
+
+// -> (dst_rank int32 [NK], dst_pos int64 [NK], home_pos int64 [NK], off_local int32 [El+1], tags int32 [NK, 4])
+std::vector<torch::Tensor> ep_plan(const torch::Tensor& flat, const torch::Tensor& pos_l, const torch::Tensor& off_l,
+                                   const torch::Tensor& w, const torch::Tensor& table, int64_t parity, int64_t rank,
+                                   int64_t R, int64_t E, int64_t cap, int64_t K, torch::Tensor& dropped) {
+  TORCH_CHECK(flat.is_contiguous() && flat.scalar_type() == torch::kInt64 && pos_l.is_contiguous() &&
+              pos_l.scalar_type() == torch::kInt64 && pos_l.numel() == flat.numel());
+  TORCH_CHECK(off_l.scalar_type() == torch::kInt32 && off_l.is_contiguous() && off_l.numel() >= E);
+  TORCH_CHECK(w.scalar_type() == torch::kFloat32 && w.is_contiguous() && w.numel() == flat.numel());
+  TORCH_CHECK(table.scalar_type() == torch::kInt32 && table.is_contiguous() &&
+              table.numel() >= 2 * mt::kMaxPeers * mt::ep_count_slots());
+  TORCH_CHECK(E % R == 0 && E <= mt::ep_count_slots() && R <= mt::kMaxPeers && dropped.scalar_type() == torch::kInt64);
+  c10::cuda::CUDAGuard guard(flat.device());
+  const int64_t NK = flat.numel(), El = E / R;
+  auto i32 = flat.options().dtype(torch::kInt32);
+  auto dst_rank = torch::empty({NK}, i32);
+  auto dst_pos = torch::empty({NK}, flat.options());
+  auto home_pos = torch::empty({NK}, flat.options());
+  auto off_local = torch::empty({El + 1}, i32);
+  auto tags = torch::empty({NK, 4}, i32);
+  mt::ep_plan(flat.data_ptr<int64_t>(), pos_l.data_ptr<int64_t>(), off_l.data_ptr<int>(), w.data_ptr<float>(),
+              table.data_ptr<int>() + parity * mt::kMaxPeers * mt::ep_count_slots(), (int)rank, (int)R, (int)E, (int)El, cap,
+              (int)K, NK, dst_rank.data_ptr<int>(), dst_pos.data_ptr<int64_t>(), home_pos.data_ptr<int64_t>(),
+              off_local.data_ptr<int>(), tags.data_ptr<int>(),
+              reinterpret_cast<unsigned long long*>(dropped.data_ptr<int64_t>()), cur_stream());
+  return {dst_rank, dst_pos, home_pos, off_local, tags};
+}
+
+// tags int32 [cap, 4] -> (row_src int64 [cap], row_dst int64 [cap], scale fp32 [cap])
+std::vector<torch::Tensor> ep_resolve(const torch::Tensor& tags, const std::vector<int64_t>& in_ptrs,
+                                      const std::vector<int64_t>& out_ptrs, int64_t row_bytes) {
+  TORCH_CHECK(tags.is_cuda() && tags.is_contiguous() && tags.scalar_type() == torch::kInt32 && tags.dim() == 2 &&
+              tags.size(1) == 4 && in_ptrs.size() == out_ptrs.size());
+  c10::cuda::CUDAGuard guard(tags.device());
+  const int64_t cap = tags.size(0);
+  auto i64 = tags.options().dtype(torch::kInt64);
+  auto row_src = torch::empty({cap}, i64), row_dst = torch::empty({cap}, i64);
+  auto scale = torch::empty({cap}, tags.options().dtype(torch::kFloat32));
+  mt::ep_resolve(tags.data_ptr<int>(), to_peers(in_ptrs), to_peers(out_ptrs), cap, row_bytes,
+                 reinterpret_cast<unsigned long long*>(row_src.data_ptr<int64_t>()),
+                 reinterpret_cast<unsigned long long*>(row_dst.data_ptr<int64_t>()), scale.data_ptr<float>(), cur_stream());
+  return {row_src, row_dst, scale};
+}
+
+int64_t ep_count_slots() { return mt::ep_count_slots(); }
+
 std::vector<torch::Tensor> moe_combine_rows(const torch::Tensor& y, const torch::Tensor& pos,
                                             const c10::optional<torch::Tensor>& w, int64_t N, int64_t K, bool want_out,
                                             const c10::optional<torch::Tensor>& g) {
@@ -679,6 +745,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sumsq", &sumsq);
   m.def("symm_barrier", &symm_barrier);
   m.def("grad_pull_reduce", &grad_pull_reduce);
+  m.def("grad_pull_bucket", &grad_pull_bucket);
+  m.def("bucket_flag_slots", &bucket_flag_slots);
   m.def("adamw_publish", &adamw_publish);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("grouped_wgrad", &grouped_wgrad);
@@ -702,6 +770,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_sort", &moe_sort);
   m.def("moe_gather_rows", &moe_gather_rows);
   m.def("moe_combine_rows", &moe_combine_rows);
+  m.def("ep_push_counts", &ep_push_counts);
+  m.def("ep_plan", &ep_plan);
+  m.def("ep_resolve", &ep_resolve);
+  m.def("ep_count_slots", &ep_count_slots);
   m.def("tp_gemm_ag", &tp_gemm_ag);
   m.def("tp_gemm_rs", &tp_gemm_rs);
   m.def("tp_reduce_slots", &tp_reduce_slots);

@@ -5,6 +5,13 @@
 //   grad_pull_reduce    reduce-scatter by pulling: this rank reads its shard range from every rank's flat fp32
 //                       gradient buffer with plain peer loads (its own copy included), sums in a fixed rank order,
 //                       keeps the sum locally and accumulates its sum of squares for the global-norm clip.
+//   grad_pull_bucket    the same reduction for one bucket of the flat buffer, launched on a side stream while the
+//                       backward pass is still running: the kernel first posts "my gradients for bucket b are
+//                       final" (a sequence number) into every peer's flag table, waits (bounded) until every peer
+//                       has posted the same, then pulls and sums its slice of the bucket from all ranks and
+//                       stores zeros back into the slices it has consumed, so that no separate clearing pass over the
+//                       gradient buffers is needed.  Runs on a capped grid so that it hides under the backward
+//                       kernels instead of competing with them.
 //   adamw_publish       fused AdamW on the shard (clip factor, moments, fp32 master) whose bf16 result is written
 //                       straight into the shard's slot of every rank's resident parameter buffer (peer stores),
 //                       i.e. the update and the parameter all-gather are one kernel.
@@ -72,6 +79,46 @@ __global__ void grad_pull_reduce_kernel(PeerPtrs grads, int rank, int world, int
   }
 }
 
+// flags: per rank an int[world * kBucketSlots] table in symmetric memory; entry [src * kBucketSlots + bucket] of rank d
+// is the last sequence number rank src posted for that bucket.
+__global__ void grad_pull_bucket_kernel(PeerPtrs grads, PeerPtrs flags, int rank, int world, int bucket, int seq,
+                                        int64_t lo, int64_t n, float* __restrict__ out, int accumulate, int* status) {
+  __shared__ int give_up;
+  if (threadIdx.x == 0) give_up = 0;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int peer = threadIdx.x;
+    if (blockIdx.x == 0) {
+      __threadfence_system();  // this rank's gradient writes (earlier kernels of the stream) before the post
+      st_release_sys(reinterpret_cast<int*>(flags.p[peer]) + rank * kBucketSlots + bucket, seq);
+    }
+    const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + peer * kBucketSlots + bucket;
+    const long long t0 = clock64();
+    while (ld_acquire_sys(mine) < seq) {
+      if (clock64() - t0 > kMaxWaitCycles) {
+        if (status) atomicCAS(status, 0, MT_ERR_TIMEOUT_FLAG);
+        give_up = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (give_up) return;  // nothing is read or cleared: the host sees the status word
+  const int64_t nvec = n >> 2;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 s = accumulate ? reinterpret_cast<const float4*>(out)[i] : zero;
+#pragma unroll 8
+    for (int r = 0; r < world; ++r) {
+      float4* src = reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[r]) + lo) + i;
+      const float4 v = *src;
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      *src = zero;  // this thread is the only reader of the element: clear it for the next step's accumulation
+    }
+    reinterpret_cast<float4*>(out)[i] = s;
+  }
+}
+
 __global__ void adamw_publish_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                                      const float* __restrict__ grad, PeerPtrs params, int world, int64_t lo, int64_t n,
                                      float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
@@ -125,6 +172,14 @@ void grad_pull_reduce(const PeerPtrs& grads, int rank, int world, int64_t lo, in
                       cudaStream_t stream) {
   if (n == 0) return;
   grad_pull_reduce_kernel<<<148 * 8, 256, 0, stream>>>(grads, rank, world, lo, n, out, sumsq);
+}
+
+void grad_pull_bucket(const PeerPtrs& grads, const PeerPtrs& flags, int rank, int world, int bucket, int seq, int64_t lo,
+                      int64_t n, float* out, bool accumulate, int blocks, int* status, cudaStream_t stream) {
+  if (n == 0 || bucket < 0 || bucket >= kBucketSlots) return;
+  if (blocks <= 0) blocks = 148 * 4;
+  grad_pull_bucket_kernel<<<blocks, 512, 0, stream>>>(grads, flags, rank, world, bucket, seq, lo, n, out,
+                                                      accumulate ? 1 : 0, status);
 }
 
 void adamw_publish(float* master, float* m, float* v, const float* grad, const PeerPtrs& params, int world, int64_t lo,

@@ -382,6 +382,7 @@ __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, cons
 }
 
 // out[n, :] = sum_k w[n,k] * y[pos[n,k], :]  (w == nullptr: plain sum); dw[n,k] = <y[pos[n,k], :], g[n, :]> if asked.
+// A negative position marks a dropped (token, slot): its row is never read, it adds nothing and its dw is 0.
 template <int KMAX>
 __global__ void moe_combine_rows_kernel(const __nv_bfloat16* __restrict__ y, const int64_t* __restrict__ pos,
                                         const float* __restrict__ w, __nv_bfloat16* __restrict__ out,
@@ -402,7 +403,7 @@ __global__ void moe_combine_rows_kernel(const __nv_bfloat16* __restrict__ y, con
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
         for (int k = 0; k < KMAX; ++k) {
-          if (k < K) {
+          if (k < K && pk[k] >= 0) {
             Pack8 a;
             a.u = reinterpret_cast<const uint4*>(y + pk[k] * D)[v];
 #pragma unroll
@@ -420,7 +421,7 @@ __global__ void moe_combine_rows_kernel(const __nv_bfloat16* __restrict__ y, con
       for (int k = 0; k < KMAX; ++k) {
         if (k < K) {
           float dot = 0.f;
-          for (int v = lane; v < vecs; v += 32) {
+          for (int v = lane; v < vecs && pk[k] >= 0; v += 32) {
             Pack8 a, b;
             a.u = reinterpret_cast<const uint4*>(y + pk[k] * D)[v];
             b.u = reinterpret_cast<const uint4*>(g + (int64_t)n * D)[v];

@@ -151,7 +151,11 @@ class CheckpointManager:
         if self._writer is None:
             self._writer = _make_writer()
         meta: dict[str, dict] = {}
-        for path, value in tree.items():
+        flat_items = []
+        for path, value in tree.items():  # a list holds several chunks of the same entry written by this rank
+            for v in (value if isinstance(value, list) else [value]):
+                flat_items.append((path, v))
+        for path, value in flat_items:
             entry = value if isinstance(value, dict) else {"tensor": value}
             writer_rank = entry.get("writer_rank", 0)
             t = entry.get("tensor")

@@ -41,6 +41,31 @@ REMAT_POLICIES: dict[str, tuple[frozenset[str], bool] | None] = {
 }
 
 
+_BACKWARD_LAYER_HOOK = None
+
+
+def set_backward_layer_hook(fn) -> None:
+    """Install (or clear, with None) a callback ``fn(layer_index)`` that a forward pass arms on every decoder
+    layer's input: it fires during the backward pass when the gradient of that input is complete, i.e. once every
+    gradient kernel of the layer has been launched.  The training engine uses it on the last micro-batch of a step
+    to start the layer's gradient reduce-scatter while the rest of the backward pass is still running."""
+    global _BACKWARD_LAYER_HOOK
+    _BACKWARD_LAYER_HOOK = fn
+
+
+def _arm_layer_hook(x: torch.Tensor, layer_index: int) -> None:
+    if _BACKWARD_LAYER_HOOK is None or not (torch.is_grad_enabled() and x.requires_grad):
+        return
+
+    def fire(grad, li=layer_index):
+        hook = _BACKWARD_LAYER_HOOK
+        if hook is not None:
+            hook(li)
+        return None
+
+    x.register_hook(fire)
+
+
 def make_causal_mask(seq_len: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """Additive ``[1,1,S,S]`` causal mask (0 / -1e10)."""
     return causal_mask(seq_len, dtype)
@@ -251,6 +276,7 @@ class Transformer(nn.Module):
         pending = None
         fuse = REMAT_POLICIES[self.remat_policy] is None or not torch.is_grad_enabled()
         for li, layer in enumerate(self.layers):
+            _arm_layer_hook(x, li)
             with nvtx_range(f"layer{li}"):
                 if fuse:  # carry the last residual add into the next norm kernel
                     x, aux, pending = layer(x, positions, mask, default_positions, pending=pending, defer_residual=True)

@@ -43,6 +43,7 @@ class _Slot:
     param: torch.nn.Parameter
     offset: int
     numel: int
+    bucket: int = 0  # index into the engine's bucket list (sharded group only)
 
 
 class FlatGroup:
@@ -55,6 +56,35 @@ class FlatGroup:
 
 def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
+
+
+def bucket_of(name: str) -> int:
+    """Gradient bucket of a parameter: decoder layer ``i`` is bucket ``i + 1``; everything else (embedding, output
+    head, final norm) is bucket 0, whose gradients are complete only when the whole backward pass is."""
+    parts = name.split(".")
+    if len(parts) > 2 and parts[0] == "layers" and parts[1].isdigit():
+        return int(parts[1]) + 1
+    return 0
+
+
+def plan_buckets(sizes: list[tuple[int, int]], world: int, align: int = _ALIGN, quantum: int = 1024):
+    """Lay parameters out bucket by bucket.  ``sizes`` lists ``(bucket id, numel)`` per parameter in model order.
+    Returns ``(offsets, buckets, total)``: the flat offset of every parameter, and per bucket (ascending id)
+    ``(bucket id, flat offset, length)`` with every length a multiple of ``world * quantum``, so that each rank owns
+    one contiguous, vector-aligned ``length / world`` slice of every bucket."""
+    ids = sorted({b for b, _ in sizes})
+    cursor = {b: 0 for b in ids}
+    rel = []
+    for b, n in sizes:
+        rel.append((b, cursor[b]))
+        cursor[b] = _round_up(cursor[b] + n, align)
+    buckets, start, base = [], {}, 0
+    for b in ids:
+        length = _round_up(max(cursor[b], 1), world * quantum)
+        buckets.append((b, base, length))
+        start[b] = base
+        base += length
+    return [start[b] + off for b, off in rel], buckets, base
 
 
 class TrainEngine:
@@ -97,6 +127,11 @@ class TrainEngine:
         self._sumsq_shard = torch.zeros(1, device=self.device, dtype=torch.float32)
         self._clip = torch.ones(1, device=self.device, dtype=torch.float32)
         self.kernel_launches = 0
+        self._flat_cleared_by_pull = False
+        self._pulled: set[int] = set()   # buckets whose reduction has been issued in this step
+        self._late: set[int] = set()     # ... and that received further gradients afterwards
+        self._slots_of_bucket = None
+        self._has_tp_replicated = None
 
     # ------------------------------------------------------------------ storage
     def _build_storage(self) -> None:
@@ -123,15 +158,33 @@ class TrainEngine:
             else:
                 small.append(_Slot(name, p, off_s, p.numel()))
                 off_s = _round_up(off_s + p.numel(), _ALIGN)
-        shard_quantum = self.world * 1024
-        total_b = _round_up(max(off_b, 1), shard_quantum)
         self.use_muon = cfg.optimizer == "muon"
+        # Flat layout of the sharded group.  One bucket per decoder layer (plus one for the rest), each split 1/N
+        # over the ranks: a rank's optimizer shard is the concatenation of its slice of every bucket, and a bucket's
+        # gradients can be reduced as soon as the backward pass has left its layer.  Muon keeps whole matrices on
+        # one rank instead (one bucket, bin-packed).
         if self.use_muon and self.world > 1 and big:
             total_b = self._matrix_aligned_layout(big)
+            buckets = [(0, 0, total_b)]
+        elif self.compute_dtype == torch.bfloat16 and big and self.world > 1:
+            offs, buckets, total_b = plan_buckets([(bucket_of(s.name), s.numel) for s in big], self.world)
+            for s, o in zip(big, offs):
+                s.offset = o
+        else:
+            total_b = _round_up(max(off_b, 1), self.world * 1024)
+            buckets = [(0, 0, total_b)]
         self.big = FlatGroup(big, total_b)
         self.small = FlatGroup(small, _round_up(max(off_s, 1), _ALIGN))
         self.shard_size = total_b // self.world
-        lo = self.rank * self.shard_size
+        # (bucket id, flat range of this rank's slice, offset of the slice in the rank's shard arrays)
+        self.segments: list[tuple[int, int, int, int]] = []
+        local = 0
+        for bid, boff, blen in buckets:
+            sl = blen // self.world
+            self.segments.append((bid, boff + self.rank * sl, boff + (self.rank + 1) * sl, local))
+            local += sl
+        self.buckets = buckets
+        self._bucket_index = {bid: i for i, (bid, _, _) in enumerate(buckets)}
 
         # fp32 master values come from the model's initialisation.  Parameters are consumed one at a time (they may
         # already live on the device): the bf16 compute copy and this rank's slice of the fp32 master are filled
@@ -144,17 +197,16 @@ class TrainEngine:
         self.exp_avg = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
         self.exp_avg_sq = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
         self.grad_shard = torch.empty(self.shard_size, device=dev, dtype=torch.float32)
-        hi = lo + self.shard_size
         # per-element weight decay is uniform over the big group (only the router bias is exempt and it is frozen)
         for s in big:
             src = s.param.detach().reshape(-1)
             self.param_flat[s.offset:s.offset + s.numel].copy_(src)
-            a, b = max(s.offset, lo), min(s.offset + s.numel, hi)
-            if a < b:
-                self.master[a - lo:b - lo].copy_(src[a - s.offset:b - s.offset])
+            for a, b, loc in self._overlaps(s.offset, s.offset + s.numel):
+                self.master[loc:loc + (b - a)].copy_(src[a - s.offset:b - s.offset])
             del src
             s.param.data = self.param_flat[s.offset:s.offset + s.numel].view(s.param.shape)
             s.param.main_grad = self.grad_flat[s.offset:s.offset + s.numel].view(s.param.shape)
+            s.bucket = self._bucket_index.get(bucket_of(s.name), 0) if len(buckets) > 1 else 0
 
         # expert-parallel parameters: every rank owns its experts outright (compute copy, master, moments, grads)
         self.exp = FlatGroup(exp, _round_up(max(off_e, 4), _ALIGN))
@@ -189,6 +241,25 @@ class TrainEngine:
             if not weight_decay_mask(s.name):
                 self.small_wd[s.offset:s.offset + s.numel] = 0.0
 
+    def _overlaps(self, lo: int, hi: int):
+        """Parts of the flat range ``[lo, hi)`` that this rank's shard holds: ``(flat_a, flat_b, local offset)``."""
+        for _, a, b, loc in self.segments:
+            x, y = max(a, lo), min(b, hi)
+            if x < y:
+                yield x, y, loc + (x - a)
+
+    def _gather_flat(self, local: torch.Tensor) -> torch.Tensor:
+        """All ranks' shard arrays reassembled into the flat layout (bucket by bucket, rank slices in rank order)."""
+        if self.world == 1:
+            return local
+        every = torch.empty(self.world, self.shard_size, device=self.device, dtype=local.dtype)
+        dist.all_gather_into_tensor(every.view(-1), local.contiguous(), group=self.group)
+        full = torch.empty(self.big.total, device=self.device, dtype=local.dtype)
+        for (_, boff, blen), (_, _, _, loc) in zip(self.buckets, self.segments):
+            sl = blen // self.world
+            full[boff:boff + blen].view(self.world, sl).copy_(every[:, loc:loc + sl])
+        return full
+
     def _matrix_aligned_layout(self, big: list) -> int:
         """Muon orthogonalises whole matrices, so under Muon no parameter may straddle two optimizer shards:
         parameters are packed greedily (largest first) into one bin per rank, a bin being that rank's contiguous
@@ -218,11 +289,7 @@ class TrainEngine:
     # ------------------------------------------------------------------ helpers
     def named_master_parameters(self) -> dict[str, torch.Tensor]:
         """Full fp32 master tensors by name (gathers the shards; used by checkpointing and tests)."""
-        if self.world > 1:
-            full = torch.empty(self.big.total, device=self.device, dtype=torch.float32)
-            dist.all_gather_into_tensor(full, self.master, group=self.group)
-        else:
-            full = self.master
+        full = self._gather_flat(self.master)
         out = {s.name: full[s.offset:s.offset + s.numel].view(s.param.shape).clone() for s in self.big.slots}
         for s in self.small.slots:
             out[s.name] = s.param.detach().clone()
@@ -231,25 +298,75 @@ class TrainEngine:
                 out[n] = p.detach().clone()
         return out
 
-    def zero_grad(self) -> None:
-        self.grad_flat.zero_()
+    def zero_grad(self, force: bool = False) -> None:
+        """Clear the gradient accumulators.  The flat buffer of the sharded group is skipped when the previous
+        step's bucket pulls have already cleared it (each owner zeroes what it has consumed, on every rank)."""
+        if force or not self._flat_cleared_by_pull:
+            self.grad_flat.zero_()
+        self._flat_cleared_by_pull = False
         self.small_grad.zero_()
         if self.exp.slots:
             self.exp_grad.zero_()
 
-    def _fold_autograd_grads(self) -> None:
-        """Parameters whose ops returned ordinary autograd gradients: add them into the flat buffers."""
-        for grp in (self.big, self.small, self.exp):
-            for s in grp.slots:
+    def _fold_autograd_grads(self, slots=None) -> None:
+        """Parameters whose ops returned ordinary autograd gradients: add them into the flat buffers.  A gradient
+        that arrives for a bucket whose reduction has already been issued marks the bucket for a second,
+        accumulating pull."""
+        groups = (slots,) if slots is not None else (self.big.slots, self.small.slots, self.exp.slots)
+        for grp in groups:
+            for s in grp:
                 g = s.param.grad
                 if g is not None:
                     s.param.main_grad.add_(g.to(torch.float32))
                     s.param.grad = None
+                    if grp is self.big.slots and s.bucket in self._pulled:
+                        self._late.add(s.bucket)
 
     # ------------------------------------------------------------------ step
     def backward(self, loss: torch.Tensor) -> None:
         loss.backward()
         self._fold_autograd_grads()
+
+    def _micro_batch(self, micro: dict, last: bool):
+        """Forward + backward of one micro-batch.  On the last one of a step (peer-memory path) every decoder layer
+        reports when the backward pass has left it, and its bucket's reduce-scatter starts on the side stream right
+        away; the hook has to be in place during the forward pass, which arms it on the layers' inputs."""
+        from mintext_b200.models import transformer as tfm
+        from mintext_b200.trainer import compute_loss
+
+        overlap = last and self._overlap_ok()
+        if overlap:
+            tfm.set_backward_layer_hook(self._on_layer_backward_done)
+        try:
+            loss, aux = compute_loss(None, self.model, self.config, micro)
+            self.backward(loss)
+        finally:
+            if overlap:
+                tfm.set_backward_layer_hook(None)
+        return aux
+
+    def _overlap_ok(self) -> bool:
+        if not (self.use_fused and len(self.buckets) > 1) or os.environ.get("MT_OVERLAP_GRAD_REDUCE", "1") == "0":
+            return False
+        if self._has_tp_replicated is None:
+            self._has_tp_replicated = any(getattr(s.param, "tp_replicated_compute", False) for s in self.big.slots)
+        return not self._has_tp_replicated  # those gradients are rescaled before the reduction
+
+    def _on_layer_backward_done(self, layer: int) -> None:
+        b = self._bucket_index.get(layer + 1)
+        if b is None or b in self._pulled:
+            return
+        if self._slots_of_bucket is None:
+            self._slots_of_bucket = {}
+            for s in self.big.slots:
+                self._slots_of_bucket.setdefault(s.bucket, []).append(s)
+        for s in self._slots_of_bucket.get(b, ()):  # gradients that came back through autograd so far
+            g = s.param.grad
+            if g is not None:
+                s.param.main_grad.add_(g.to(torch.float32))
+                s.param.grad = None
+        self._comm.pull_bucket_async(b)
+        self._pulled.add(b)
 
     def optimizer_step(self, num_micro: int = 1) -> dict:
         """Reduce gradients, clip, update, re-publish bf16 weights.  Returns device scalars."""
@@ -275,16 +392,22 @@ class TrainEngine:
                         s.param.main_grad.mul_(1.0 / tp.size)
         # 1. gradient reduction
         if W > 1:
-            if self.use_fused:
+            if self.use_fused and len(self.buckets) > 1:
+                self._comm.finish_bucket_pulls(self._pulled, self._late)
+                self._pulled, self._late = set(), set()
+                self._flat_cleared_by_pull = True
+            elif self.use_fused:
                 self._comm.reduce_scatter_grads(self.grad_shard)
             else:
-                dist.reduce_scatter_tensor(self.grad_shard, self.grad_flat, group=self.group)
+                for (_, boff, blen), (_, _, _, loc) in zip(self.buckets, self.segments):
+                    dist.reduce_scatter_tensor(self.grad_shard[loc:loc + blen // W], self.grad_flat[boff:boff + blen],
+                                               group=self.group)
             dist.all_reduce(self.small_grad, group=self.group)
             gshard = self.grad_shard
         else:
             gshard = self.grad_flat
         # 2. global norm of the averaged gradient
-        if W > 1 and self.use_fused:
+        if W > 1 and self.use_fused and len(self.buckets) == 1:
             self._sumsq.copy_(self._sumsq_shard)  # produced by the pull-reduce kernel
         else:
             self._sumsq.zero_()
@@ -306,20 +429,25 @@ class TrainEngine:
         else:
             self._clip.fill_(1.0)
         # 3. fused AdamW on the shard (+ 4. publication of the bf16 copy)
-        lo = self.rank * self.shard_size
-        pshard = self.param_flat[lo:lo + self.shard_size]
         if self.use_muon:
+            lo = self.rank * self.shard_size
+            pshard = self.param_flat[lo:lo + self.shard_size]
             self._muon_group(self.big.slots, lo, lo + self.shard_size, self.master, self.exp_avg, self.exp_avg_sq,
                              gshard, pshard, lr, bc1, bc2, inv, t)
             if W > 1:
                 dist.all_gather_into_tensor(self.param_flat, pshard, group=self.group)
         elif W > 1 and self.use_fused:
             self._comm.adamw_and_publish(gshard, lr, bc1, bc2, inv, self._clip)
+        elif W > 1:
+            for (_, boff, blen), (_, a, b, loc) in zip(self.buckets, self.segments):
+                sl = slice(loc, loc + (b - a))
+                pslice = self.param_flat[a:b]
+                e.adamw_step(self.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], gshard[sl], pslice, lr, cfg.adam_b1,
+                             cfg.adam_b2, cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)
+                dist.all_gather_into_tensor(self.param_flat[boff:boff + blen], pslice, group=self.group)
         else:
-            e.adamw_step(self.master, self.exp_avg, self.exp_avg_sq, gshard, pshard, lr, cfg.adam_b1, cfg.adam_b2,
-                         cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)
-            if W > 1:
-                dist.all_gather_into_tensor(self.param_flat, pshard, group=self.group)
+            e.adamw_step(self.master, self.exp_avg, self.exp_avg_sq, gshard, self.param_flat, lr, cfg.adam_b1,
+                         cfg.adam_b2, cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)
         if self.exp.slots and self.use_muon:
             self._muon_group(self.exp.slots, 0, self.exp.total, self.exp_master, self.exp_m, self.exp_v, self.exp_grad,
                              self.exp_param, lr, bc1, bc2, inv, t)
@@ -399,8 +527,7 @@ class TrainEngine:
         counts = None
         for i in range(n):
             micro = {k: v[i * mb:(i + 1) * mb] for k, v in batch.items()}
-            loss, aux = compute_loss(None, self.model, cfg, micro)
-            self.backward(loss)
+            aux = self._micro_batch(micro, last=(i == n - 1))
             loss_sum += aux["loss"].float()
             if aux.get("moe_expert_counts") is not None:
                 counts = aux["moe_expert_counts"] if counts is None else counts + aux["moe_expert_counts"]
@@ -416,7 +543,7 @@ class TrainEngine:
 
             # the all-reduced loss is the same on every rank, so all ranks take the same decision
             if apply_nan_policy(cfg.nan_policy, float(loss_mean), self.step_count):
-                self.zero_grad()
+                self._abandon_step()
                 return {"loss": loss_mean, "param_norm": pnorm, "moe_expert_counts": None, "z_loss": aux["z_loss"],
                         "grad_norm": torch.full((), float("nan"), device=self.device),
                         "learning_rate": float(self.schedule(self.step_count)), "skipped": True}
@@ -424,6 +551,15 @@ class TrainEngine:
             out = self.optimizer_step(n)
         out.update({"loss": loss_mean, "param_norm": pnorm, "moe_expert_counts": counts, "z_loss": aux["z_loss"]})
         return out
+
+    def _abandon_step(self) -> None:
+        """Drop the gradients of a skipped step.  Bucket reductions that were already issued are left to finish (every
+        rank takes the same decision), then everything is cleared."""
+        if self._comm is not None and self._pulled:
+            self._comm.wait_side_stream()
+            self._comm.barrier()  # no peer is still pulling from (or clearing) this rank's buffer
+        self._pulled, self._late = set(), set()
+        self.zero_grad(force=True)
 
     def check(self) -> None:
         """Raise if any kernel recorded a bounded-wait expiry since the last check (synchronises)."""
@@ -459,16 +595,17 @@ class TrainEngine:
     def checkpoint_tree(self) -> dict:
         """Flat fp32 master / moment buffers are saved as one chunk per rank (``flat_range`` = the rank's slice
         of the flat layout); small replicated and frozen parameters are saved by name from rank 0."""
-        lo = self.rank * self.shard_size
-        rng = (lo, lo + self.shard_size)
-        suffix = f".{lo}-{lo + self.shard_size}"
-        common = {"writer_rank": self.rank, "flat_range": rng, "flat_total": self.big.total, "suffix": suffix}
+        def chunks(local: torch.Tensor) -> list[dict]:
+            # one chunk per bucket slice this rank holds: (flat range, the matching part of the shard array)
+            return [{"tensor": local[loc:loc + (b - a)], "writer_rank": self.rank, "flat_range": (a, b),
+                     "flat_total": self.big.total, "suffix": f".{a}-{b}"} for _, a, b, loc in self.segments]
+
         tree: dict = {
             "step": self.step_count,
             "layout/big": {"tensor": json.dumps([[s.name, s.offset, s.numel, list(s.param.shape)] for s in self.big.slots])},
-            "opt_state/flat_master": {"tensor": self.master, **common},
-            "opt_state/flat_exp_avg": {"tensor": self.exp_avg, **common},
-            "opt_state/flat_exp_avg_sq": {"tensor": self.exp_avg_sq, **common},
+            "opt_state/flat_master": chunks(self.master),
+            "opt_state/flat_exp_avg": chunks(self.exp_avg),
+            "opt_state/flat_exp_avg_sq": chunks(self.exp_avg_sq),
         }
         # expert- / tensor-parallel parameters: this rank's slice along the parameter's shard dimension; of the
         # data-parallel replicas that hold the same slice only the first writes it
@@ -492,8 +629,6 @@ class TrainEngine:
 
     @torch.no_grad()
     def load_checkpoint_tree(self, read) -> None:
-        lo = self.rank * self.shard_size
-        hi = lo + self.shard_size
         paths = set(getattr(read, "paths", []))
         if "opt_state/flat_master" in paths:
             saved = {row[0]: row for row in json.loads(read("layout/big"))}
@@ -507,23 +642,22 @@ class TrainEngine:
                 kinds += [("opt_state/flat_exp_avg", self.exp_avg), ("opt_state/flat_exp_avg_sq", self.exp_avg_sq)]
             if same:
                 for path, dst in kinds:
-                    dst.copy_(read(path, (lo, hi)))
+                    for _, a, b, loc in self.segments:
+                        dst[loc:loc + (b - a)].copy_(read(path, (a, b)))
             else:
-                # the flat layout depends on the optimizer and the rank count (Muon packs whole matrices per rank):
-                # look every parameter up by name in the saved layout and copy the part this rank holds
+                # the flat layout depends on the optimizer and the rank count (bucket lengths are rounded to the
+                # rank count; Muon packs whole matrices per rank): look every parameter up by name in the saved
+                # layout and copy the parts this rank holds
                 for s in self.big.slots:
-                    a, b = max(s.offset, lo), min(s.offset + s.numel, hi)
-                    if a >= b:
-                        continue
                     so = saved[s.name][1]
-                    for path, dst in kinds:
-                        dst[a - lo:b - lo] = read(path, (so + a - s.offset, so + b - s.offset)).to(self.device)
+                    for a, b, loc in self._overlaps(s.offset, s.offset + s.numel):
+                        for path, dst in kinds:
+                            dst[loc:loc + (b - a)] = read(path, (so + a - s.offset, so + b - s.offset)).to(self.device)
         else:  # a per-name checkpoint written by the CPU trainer
             for s in self.big.slots:
                 full = read(f"params/{s.name}").float().reshape(-1)
-                a, b = max(s.offset, lo), min(s.offset + s.numel, hi)
-                if a < b:
-                    self.master[a - lo:b - lo] = full[a - s.offset:b - s.offset].to(self.device)
+                for a, b, loc in self._overlaps(s.offset, s.offset + s.numel):
+                    self.master[loc:loc + (b - a)] = full[a - s.offset:b - s.offset].to(self.device)
         for s in self.exp.slots:
             spec = tuple(getattr(s.param, "shard_spec", (0, self.rank, self.world)))
             sl = slice(s.offset, s.offset + s.numel)
@@ -547,11 +681,12 @@ class TrainEngine:
 
     def _publish_master(self) -> None:
         """Rebuild the resident bf16 compute copy from the fp32 master shards."""
-        lo = self.rank * self.shard_size
-        pshard = self.param_flat[lo:lo + self.shard_size]
-        pshard.copy_(self.master.to(torch.bfloat16))
-        if self.world > 1:
-            dist.all_gather_into_tensor(self.param_flat, pshard.clone(), group=self.group)
+        for (_, boff, blen), (_, a, b, loc) in zip(self.buckets, self.segments):
+            mine = self.master[loc:loc + (b - a)].to(torch.bfloat16)
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.param_flat[boff:boff + blen], mine, group=self.group)
+            else:
+                self.param_flat[a:b].copy_(mine)
 
     def reset_step(self) -> None:
         self.step_count = 0
@@ -564,8 +699,8 @@ class TrainEngine:
     def refresh_from_model(self) -> None:
         """Parameters were overwritten in place (e.g. by an HF import into the bf16 views): re-derive the master
         shards from them."""
-        lo = self.rank * self.shard_size
-        self.master.copy_(self.param_flat[lo:lo + self.shard_size].float())
+        for _, a, b, loc in self.segments:
+            self.master[loc:loc + (b - a)].copy_(self.param_flat[a:b].float())
 
 
 def local_batch_rows(global_batch: int, world: int, rank: int) -> tuple[int, int]:

@@ -44,6 +44,7 @@ class ExpertParallel:
         self._bufs = None  # (cap_rows, dim) -> symmetric buffers
         self.seq = 0
         self.overflow = None
+        self._dropped = None
 
     def local_expert_range(self, num_experts: int) -> tuple[int, int]:
         if num_experts % self.size != 0:
@@ -65,17 +66,26 @@ class ExpertParallel:
         flags.zero_()
         # one 16-byte record per received row: (sender rank + 1, the row's flat (token, slot) index, 0, 0)
         tagb = symm.empty(cap_rows * 8, dtype=torch.bfloat16, device=self.device)
+        tagb.zero_()  # each dispatch clears the records it has consumed, so the buffer is clean between exchanges
+        # per-expert row counts of every rank, double buffered by call parity: int32 [2][8][slots]
+        from mintext_b200.ops._ext import ext
+
+        countb = symm.empty(2 * 8 * int(ext().ep_count_slots()), dtype=torch.int32, device=self.device)
+        countb.zero_()
+        h_cnt = symm.rendezvous(countb, self.group)
         h_in, h_out, h_fl, h_tag = (symm.rendezvous(t, self.group) for t in (inb, outb, flags, tagb))
         self._bufs = {
             "cap": cap_rows, "dim": dim, "in": inb.view(cap_rows, dim), "out": outb.view(cap_rows, dim),
             "in_ptrs": [int(p) for p in h_in.buffer_ptrs], "out_ptrs": [int(p) for p in h_out.buffer_ptrs],
             "flag_ptrs": [int(p) for p in h_fl.buffer_ptrs], "handles": (h_in, h_out, h_fl, h_tag), "flags": flags,
             "tag": tagb.view(cap_rows, 8), "tag_ptrs": [int(p) for p in h_tag.buffer_ptrs],
+            "counts": countb, "count_ptrs": [int(p) for p in h_cnt.buffer_ptrs], "h_cnt": h_cnt,
             "out_ptr_table": torch.tensor([int(p) for p in h_out.buffer_ptrs], dtype=torch.int64, device=self.device),
             "in_ptr_table": torch.tensor([int(p) for p in h_in.buffer_ptrs], dtype=torch.int64, device=self.device),
         }
         self.overflow = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.seq = 0
+        self.calls = 0
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
         status_word(self.device)
@@ -87,7 +97,21 @@ class ExpertParallel:
         self.seq += 1
         ext().symm_barrier(self._bufs["flag_ptrs"], self.rank, self.seq, status_word(self.device))
 
+    def dropped_counter(self) -> torch.Tensor:
+        """Device counter of routed rows dropped because a destination's receive capacity was exhausted."""
+        if self._dropped is None:
+            self._dropped = torch.zeros(1, dtype=torch.int64, device=self.device)
+        return self._dropped
+
+    def dropped_rows(self, reset: bool = True) -> int:
+        """Routed rows dropped for lack of receive capacity since the last call (synchronises)."""
+        n = 0 if self._dropped is None else int(self._dropped.item())
+        if reset and self._dropped is not None:
+            self._dropped.zero_()
+        return n
+
     def check_overflow(self) -> None:
+        """Raise if a push kernel met a row beyond the receive capacity that the plan had not already dropped."""
         if self.overflow is not None and int(self.overflow.item()) != 0:
             self.overflow.zero_()
             raise RuntimeError("expert-parallel dispatch overflowed a receive buffer; raise moe capacity_factor")
@@ -156,75 +180,67 @@ def experts_forward_collective(ep: ExpertParallel, x, topk_idx, topk_w, gate_up_
 
 
 # ------------------------------------------------------------------------------------------ peer-memory path
-def _plan(ep: ExpertParallel, topk_idx: torch.Tensor, num_experts: int, cap: int):
+def _plan(ep: ExpertParallel, topk_idx: torch.Tensor, topk_w: torch.Tensor, num_experts: int, cap: int, dim: int):
     """Device-side routing plan, in flat (token, slot) order: for every local entry its destination rank and its
     row in that rank's expert-contiguous, 128-padded buffer, plus the padded offsets of this rank's own experts.
-    The per-expert counts and the stable rank of every entry inside its expert come from the counting-sort kernel
-    (no host synchronisation); the only collective is the all-gather of the counts."""
+    The per-expert counts and the stable rank of every entry inside its expert come from the counting-sort kernel;
+    the ranks exchange their counts by peer stores into a small symmetric table, and one kernel derives the plan
+    from it.  No host synchronisation, no library collective.
+
+    Capacity: a destination rank holds at most ``cap`` rows.  Rows that would land beyond it are dropped (they
+    contribute nothing to the token's output and receive no gradient, as in capacity-factor routing): the sender
+    marks them with rank -1 / home position -1, and every rank truncates its own expert offsets at ``cap``, so no
+    kernel on either side ever indexes past a buffer."""
     from mintext_b200.ops import moe as moe_ops
     from mintext_b200.ops._ext import ext
 
     N, K = topk_idx.shape
     E, R = num_experts, ep.size
-    El = E // R
     flat = topk_idx.reshape(-1).contiguous()
     counts, off_l, pos_l, _ = ext().moe_sort(flat, E, moe_ops.capacity(flat.numel(), E))
-    within = pos_l - off_l.long()[flat]                         # stable rank of the entry among its expert's entries
-    all_counts = torch.empty(R, E, dtype=counts.dtype, device=counts.device)
-    dist.all_gather_into_tensor(all_counts, counts, group=ep.group)
-    total = all_counts.sum(0)                                   # rows per global expert
-    padded = (total + 127) // 128 * 128
-    off = torch.zeros(R, El + 1, dtype=torch.int64, device=flat.device)
-    off[:, 1:] = torch.cumsum(padded.view(R, El), dim=1)        # padded offsets inside each destination rank
-    before = torch.cumsum(all_counts, 0) - all_counts           # rows of earlier source ranks, per expert
-    dst_rank = torch.div(flat, El, rounding_mode="floor")
-    dst_pos = off[dst_rank, flat % El] + before[ep.rank][flat] + within
-    idx = torch.arange(flat.numel(), device=flat.device)
-    dst_rank32 = dst_rank.to(torch.int32)
-    return {
-        "src_token": torch.div(idx, K, rounding_mode="floor"), "sort_idx": idx, "dst_rank": dst_rank32, "dst_pos": dst_pos,
-        "rank_flat": dst_rank32, "pos_flat": dst_pos,
-        "off_local": off[ep.rank].to(torch.int32).contiguous(), "cap": cap, "N": N, "K": K,
-    }
+    b = ep.buffers(cap, dim)
+    parity = ep.calls & 1
+    ep.calls += 1
+    ext().ep_push_counts(counts, b["count_ptrs"], ep.rank, parity)
+    # every rank's counts are in every table; also: no peer still uses this rank's buffers from an earlier exchange
+    ep.barrier()
+    w = topk_w.detach().reshape(-1).float().contiguous()
+    dst_rank, dst_pos, home_pos, off_local, tags = ext().ep_plan(flat, pos_l, off_l, w, b["counts"], parity, ep.rank, R,
+                                                                 E, cap, K, ep.dropped_counter())
+    return {"dst_rank": dst_rank, "dst_pos": dst_pos, "rank_flat": dst_rank, "pos_flat": dst_pos, "home_pos": home_pos,
+            "off_local": off_local, "send_tags": tags, "cap": cap, "N": N, "K": K}
+
+
+def _src_token(plan) -> torch.Tensor:
+    """Token row of every flat (token, slot) entry (only the unfused fallbacks need it as a tensor)."""
+    if "src_token" not in plan:
+        idx = torch.arange(plan["N"] * plan["K"], device=plan["dst_pos"].device)
+        plan["src_token"] = torch.div(idx, plan["K"], rounding_mode="floor")
+    return plan["src_token"]
 
 
 def _dispatch_rows(x, ep, plan):
     """Forward half of the dispatch.  Every rank publishes its tokens in its symmetric buffer and sends each expert
     rank one 16-byte record per routed (token, slot): (sender + 1, flat (token, slot) index, token row, routing
     weight).  The expert rank then pulls the rows it was promised with one table-driven gather that also lays them
-    out expert-contiguous and 128-padded (zero rows in the padding).  Returns those rows; the records stay in
-    ``plan["tags"]`` as the rows' return addresses."""
+    out expert-contiguous and 128-padded (zero rows in the padding).  Returns those rows; the addresses derived from
+    the records stay in the plan (``row_src``: where a row came from, ``row_dst``: where its result goes back to,
+    ``row_scale``: its routing weight).  The barrier that opens the exchange is the one inside :func:`_plan`."""
     from mintext_b200.ops._ext import ext
 
     N, D = x.shape
     b = ep.buffers(plan["cap"], D)
-    R = plan["dst_rank"].numel()
-    tags = torch.empty(R, 4, dtype=torch.int32, device=x.device)
-    tags[:, 0] = ep.rank + 1
-    tags[:, 1] = plan["sort_idx"].to(torch.int32)
-    tags[:, 2] = plan["src_token"].to(torch.int32)
-    tags[:, 3] = plan["w_sorted"].view(torch.int32)
-    ep.barrier()  # nobody still reads this rank's buffers from an earlier exchange
     b["in"][:N].copy_(x)
-    b["tag"].zero_()
-    ep.barrier()  # tokens published, record buffers cleared everywhere
-    ext().ep_push_rows(tags.view(torch.bfloat16), plan["dst_rank"], plan["dst_pos"], b["tag_ptrs"], b["cap"], ep.overflow)
-    ep.barrier()  # records have landed
+    ext().ep_push_rows(plan["send_tags"].view(torch.bfloat16), plan["dst_rank"], plan["dst_pos"], b["tag_ptrs"], b["cap"],
+                       ep.overflow)
+    ep.barrier()  # records have landed, tokens are published
     got = b["tag"][: plan["cap"]].view(torch.int32).clone()
-    plan["tags"] = got
-    home = got[:, 0].long()
-    src = b["in_ptr_table"][(home - 1).clamp_min(0)] + got[:, 2].long() * (D * 2)
+    b["tag"].zero_()  # cleared before this rank passes the closing barrier, i.e. before any peer's next records
+    plan["row_src"], plan["row_dst"], plan["row_scale"] = ext().ep_resolve(got, b["in_ptrs"], b["out_ptrs"], D * 2)
     rows = torch.empty(plan["cap"], D, device=x.device, dtype=x.dtype)
-    ext().ep_gather_rows(rows, torch.where(home > 0, src, torch.zeros_like(src)).contiguous(), torch.empty(0, device=x.device))
+    ext().ep_gather_rows(rows, plan["row_src"], torch.empty(0, device=x.device))
     ep.barrier()  # every rank has its rows: the token buffers may be reused
     return rows
-
-
-def _return_addresses(b, tags: torch.Tensor, column: int, dim: int) -> torch.Tensor:
-    """Byte address, in the sender's receive buffer, of the row that each padded local row answers (0 = padding)."""
-    home = tags[:, 0].long()
-    dst = b["out_ptr_table"][(home - 1).clamp_min(0)] + tags[:, column].long() * (dim * 2)
-    return torch.where(home > 0, dst, torch.zeros_like(dst)).contiguous()
 
 
 class _Dispatch(torch.autograd.Function):
@@ -245,7 +261,7 @@ class _Dispatch(torch.autograd.Function):
         ext().ep_pull_rows(pulled, plan["dst_rank"], plan["dst_pos"], b["out_ptrs"], b["cap"])
         ep.barrier()
         dx = torch.zeros(ctx.n, d_rows.shape[1], device=d_rows.device, dtype=torch.float32)
-        dx.index_add_(0, plan["src_token"], pulled.float())
+        dx.index_add_(0, _src_token(plan), pulled.float())
         return dx.to(d_rows.dtype), None, None
 
 
@@ -296,16 +312,16 @@ class _GroupedCombine(torch.autograd.Function):
         D = w.shape[2]
         N, K = plan["N"], plan["K"]
         b = ep.buffers(plan["cap"], D)
-        row_dst = _return_addresses(b, plan["tags"], 1, D)
-        ep.barrier()  # nobody still reads its receive buffer from an earlier layer
-        ext().grouped_gemm_scatter(h, w, row_dst, plan["off_local"], True, status_word(h.device))
+        # no barrier in front: a rank's last read of its receive buffer (the previous exchange) precedes, in stream
+        # order, its arrival at this layer's dispatch barriers, which every peer has passed before it gets here
+        ext().grouped_gemm_scatter(h, w, plan["row_dst"], plan["off_local"], True, status_word(h.device))
         ep.fused_combines = getattr(ep, "fused_combines", 0) + 1
         ep.barrier()  # every rank's rows have landed
         picked = b["out"][: N * K].clone()
         ctx.save_for_backward(h, w, picked, topk_w)
         ctx.ep, ctx.plan, ctx.main_grad = ep, plan, main_grad
         # weighted sum of each token's K adjacent rows (row-reduction kernel of the single-GPU path, identity index)
-        out, _ = ext().moe_combine_rows(picked, plan["sort_idx"], topk_w.detach().float().contiguous(), N, K, True, None)
+        out, _ = ext().moe_combine_rows(picked, plan["home_pos"], topk_w.detach().float().contiguous(), N, K, True, None)
         return out
 
     @staticmethod
@@ -318,20 +334,16 @@ class _GroupedCombine(torch.autograd.Function):
         st = status_word(h.device)
         D = dy.shape[1]
         dy = dy.contiguous()
-        _, dtw = ext().moe_combine_rows(picked, plan["sort_idx"], None, N, K, False, dy)
+        _, dtw = ext().moe_combine_rows(picked, plan["home_pos"], None, N, K, False, dy)
         dtw = dtw.to(topk_w.dtype)
         b = ep.buffers(plan["cap"], D)
         # the expert ranks pull dy[token] * routing weight for each of their rows (weights came with the dispatch
-        # records), so the weighted [N*K, D] gradient is never materialised on the home rank
-        tags = plan["tags"]
-        home = tags[:, 0].long()
-        src = b["in_ptr_table"][(home - 1).clamp_min(0)] + torch.div(tags[:, 1], K, rounding_mode="floor").long() * (D * 2)
-        ep.barrier()  # nobody still reads this rank's token buffer
+        # records), so the weighted [N*K, D] gradient is never materialised on the home rank.  The token buffer is
+        # free: its last readers (the previous exchange) finished before that exchange's closing barrier.
         b["in"][:N].copy_(dy)
         ep.barrier()  # every rank's output gradient is published
         dy_p = torch.empty(plan["cap"], D, device=dy.device, dtype=dy.dtype)
-        ext().ep_gather_rows(dy_p, torch.where(home > 0, src, torch.zeros_like(src)).contiguous(),
-                             tags[:, 3].contiguous().view(torch.float32))
+        ext().ep_gather_rows(dy_p, plan["row_src"], plan["row_scale"])
         ep.barrier()  # all pulls done: the buffers may be reused
         dh = torch.empty_like(h)
         ext().grouped_gemm(dy_p, w, dh, plan["off_local"], False, st)
@@ -380,12 +392,12 @@ class _DispatchGrouped(torch.autograd.Function):
         b = ep.buffers(plan["cap"], D)
         # rows go home to their flat (token, slot) position, so a token's K gradient rows are adjacent and the
         # reduction over slots needs no atomics
-        row_dst = _return_addresses(b, plan["tags"], 1, D)
-        ep.barrier()  # nobody still reads its receive buffer
-        ext().grouped_gemm_scatter(dy, w, row_dst, plan["off_local"], False, st)  # dy @ w[e]^T, rows sent home
+        # (no barrier in front, as in the fused combine: the combine-gradient barriers of this layer lie in between)
+        ext().grouped_gemm_scatter(dy, w, plan["row_dst"], plan["off_local"], False, st)  # dy @ w[e]^T, rows sent home
         ep.barrier()
         N, K = plan["N"], plan["K"]
-        dx = b["out"][: N * K].view(N, K, D).sum(dim=1, dtype=torch.float32).to(dy.dtype)
+        # sum of each token's K adjacent gradient rows; rows of dropped slots were never written and are skipped
+        dx, _ = ext().moe_combine_rows(b["out"][: N * K], plan["home_pos"], None, N, K, True, None)
         return dx, dw, None, None, None
 
 
@@ -407,8 +419,7 @@ def experts_forward_peer(ep: ExpertParallel, x, topk_idx, topk_w, gate_up_local,
     N, K = topk_idx.shape
     El = num_experts // ep.size
     cap = moe_ops.capacity(int(ep.capacity_factor * N * K), El)
-    plan = _plan(ep, topk_idx, num_experts, cap)
-    plan["w_sorted"] = topk_w.detach().reshape(-1)[plan["sort_idx"]].float().contiguous()
+    plan = _plan(ep, topk_idx, topk_w, num_experts, cap, x.shape[1])
     fused = _fused_combine_ok(ep, plan, down_local)
     if fused and x.shape[1] > 128 and x.dtype == torch.bfloat16:
         h = _DispatchGrouped.apply(x.contiguous(), gate_up_local, getattr(gate_up_local, "main_grad", None), ep, plan)

@@ -15,6 +15,8 @@ produces a recorded timeout status on the others instead of a hang.
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -39,6 +41,18 @@ class SymmetricOptimizerComm:
         self.grad_ptrs = [int(p) for p in self._h_grad.buffer_ptrs]
         self.param_ptrs = [int(p) for p in self._h_param.buffer_ptrs]
         self.seq = 0
+        # per-bucket readiness flags for the overlapped gradient reduction, and the stream it runs on
+        self.bucket_slots = int(ext().bucket_flag_slots())
+        if len(engine.buckets) > self.bucket_slots:
+            raise RuntimeError(f"{len(engine.buckets)} gradient buckets exceed the {self.bucket_slots} flag slots")
+        self.bucket_flags = symm.empty(self.world * self.bucket_slots, dtype=torch.int32, device=engine.device)
+        self.bucket_flags.zero_()
+        self._h_bflags = symm.rendezvous(self.bucket_flags, group)
+        self.bflag_ptrs = [int(p) for p in self._h_bflags.buffer_ptrs]
+        self.side = torch.cuda.Stream(device=engine.device)
+        self.round = 0            # one per optimizer step; flags carry 2 * round (+ 1 for second pulls)
+        self._round_open = False
+        self.side_blocks = int(os.environ.get("MT_GRAD_PULL_BLOCKS", "32"))
         torch.cuda.synchronize(engine.device)
         dist.barrier(group=group)  # flags are zeroed everywhere before the first in-kernel barrier
 
@@ -54,8 +68,46 @@ class SymmetricOptimizerComm:
         e._sumsq_shard.zero_()
         ext().grad_pull_reduce(self.grad_ptrs, self.rank, self.rank * e.shard_size, out, e._sumsq_shard)
 
+    # -- bucketed reduction, overlapped with the backward pass ---------------------------------------------------
+    def _pull(self, bucket: int, accumulate: bool, blocks: int) -> None:
+        e = self.engine
+        _, a, b, loc = e.segments[bucket]
+        seq = 2 * self.round + (1 if accumulate else 0)
+        ext().grad_pull_bucket(self.grad_ptrs, self.bflag_ptrs, self.rank, bucket, seq, a, e.grad_shard[loc:loc + (b - a)],
+                               accumulate, blocks, status_word(e.device))
+
+    def _open_round(self) -> None:
+        if not self._round_open:
+            self.round += 1
+            self._round_open = True
+
+    def pull_bucket_async(self, bucket: int) -> None:
+        """Called from inside the backward pass once every gradient kernel of ``bucket`` has been launched: the
+        bucket's reduction is queued on the side stream behind those kernels, on a few SMs."""
+        self._open_round()
+        self.side.wait_stream(torch.cuda.current_stream(self.engine.device))
+        with torch.cuda.stream(self.side):
+            self._pull(bucket, False, self.side_blocks)
+
+    def wait_side_stream(self) -> None:
+        torch.cuda.current_stream(self.engine.device).wait_stream(self.side)
+
+    def finish_bucket_pulls(self, pulled: set, late: set) -> None:
+        """After the backward pass: reduce the buckets that were not started early, and run a second, accumulating
+        pull for buckets that received gradients after theirs had been issued (the same set on every rank)."""
+        self._open_round()
+        self.wait_side_stream()
+        for b in range(len(self.engine.buckets)):
+            if b not in pulled:
+                self._pull(b, False, 0)
+        for b in sorted(late):
+            self._pull(b, True, 0)
+        self._round_open = False
+
     def adamw_and_publish(self, grad_shard: torch.Tensor, lr, bc1, bc2, grad_scale, clip: torch.Tensor) -> None:
         e, cfg = self.engine, self.engine.config
-        ext().adamw_publish(e.master, e.exp_avg, e.exp_avg_sq, grad_shard, self.param_ptrs, self.rank * e.shard_size,
-                            lr, cfg.adam_b1, cfg.adam_b2, cfg.adam_eps, cfg.weight_decay, bc1, bc2, grad_scale, clip)
+        for _, a, b, loc in e.segments:
+            sl = slice(loc, loc + (b - a))
+            ext().adamw_publish(e.master[sl], e.exp_avg[sl], e.exp_avg_sq[sl], grad_shard[sl], self.param_ptrs, a,
+                                lr, cfg.adam_b1, cfg.adam_b2, cfg.adam_eps, cfg.weight_decay, bc1, bc2, grad_scale, clip)
         self.barrier()  # all shards published everywhere, all peers done reading this rank's gradients

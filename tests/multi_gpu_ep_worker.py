@@ -40,10 +40,13 @@ def main(out_path: str) -> None:
     results = {}
     # "peer": dispatch by peer stores, down projection fused with the combine all-to-all (one kernel);
     # "peer_unfused": the same exchange with the combine as a separate pull kernel; "collective": NCCL baseline
-    for name, fused, fuse_combine in (("peer", True, "1"), ("peer_unfused", True, "0"), ("collective", False, "1")):
+    # "peer_tight": receive buffers smaller than the rows routed to a rank - the excess rows are dropped cleanly
+    for name, fused, fuse_combine in (("peer", True, "1"), ("peer_unfused", True, "0"), ("collective", False, "1"),
+                                      ("peer_tight", True, "1")):
         os.environ["MT_EP_FUSED_COMBINE"] = fuse_combine
         cfg = moe_config(fused, world)
-        ep = ExpertParallel(dist.group.WORLD, dev, cfg.moe_capacity_factor, fused=fused)
+        capacity = 0.62 if name == "peer_tight" else cfg.moe_capacity_factor
+        ep = ExpertParallel(dist.group.WORLD, dev, capacity, fused=fused)
         set_current_ep(ep)
         eng = TrainEngine(Transformer(cfg, rngs=0), cfg, device=dev)
         assert len(eng.exp.slots) == 2, [s.name for s in eng.exp.slots]
@@ -55,7 +58,9 @@ def main(out_path: str) -> None:
         ep.check_overflow()
         if fused:  # the fused expert-GEMM + combine kernel ran exactly where it was asked for
             assert (getattr(ep, "fused_combines", 0) > 0) == (fuse_combine == "1"), (name, getattr(ep, "fused_combines", 0))
-        results[name] = {"losses": losses, "grad_norm": float(out["grad_norm"])}
+        dropped = torch.tensor([ep.dropped_rows() if fused else 0], device=dev)
+        dist.all_reduce(dropped)
+        results[name] = {"losses": losses, "grad_norm": float(out["grad_norm"]), "dropped": int(dropped.item())}
         set_current_ep(None)
     if rank == 0:
         Path(out_path).write_text(json.dumps(results))

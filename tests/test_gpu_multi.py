@@ -82,6 +82,11 @@ def test_expert_parallel_matches_single_gpu(tmp_path):
     for name in ("peer", "peer_unfused", "collective"):
         for a, b in zip(res[name]["losses"], single):
             assert abs(a - b) < 3e-2, (name, res[name]["losses"], single)
+        assert res[name]["dropped"] == 0, (name, res[name])
+    # receive capacity below the routed rows: rows are dropped (counted), nothing faults, training still moves
+    tight = res["peer_tight"]
+    assert tight["dropped"] > 0 and all(l == l and 0.0 < l < 12.0 for l in tight["losses"]), tight
+    assert tight["losses"][-1] < tight["losses"][0], tight
 
 
 def test_barrier_with_absent_peer_times_out_cleanly():

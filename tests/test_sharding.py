@@ -162,3 +162,45 @@ def _mesh_groups(rank, world):
 def test_mesh_process_groups_on_gloo():
     out = run_ranks(_mesh_groups, 4, 29611)
     assert out == {0: (1.0, 2.0), 1: (1.0, 4.0), 2: (5.0, 2.0), 3: (5.0, 4.0)}
+
+
+# ------------------------------------------------------------------ gradient bucket layout of the engine
+def test_bucket_plan_gives_every_rank_an_aligned_slice_of_every_bucket():
+    from mintext_b200.parallel.engine import bucket_of, plan_buckets
+
+    assert bucket_of("layers.3.mlp.gate.kernel") == 4 and bucket_of("token_embedder") == 0
+    assert bucket_of("output_proj.kernel") == 0 and bucket_of("layers.x.y") == 0
+    sizes = [(0, 70000), (1, 5000), (1, 130), (2, 4097), (2, 64), (0, 9000)]   # model order, buckets interleaved
+    for world in (1, 2, 4, 8):
+        offsets, buckets, total = plan_buckets(sizes, world)
+        assert [b for b, _, _ in buckets] == [0, 1, 2]
+        spans = {b: (off, off + length) for b, off, length in buckets}
+        assert sum(length for _, _, length in buckets) == total
+        seen = []
+        for (b, n), off in zip(sizes, offsets):
+            lo, hi = spans[b]
+            assert lo <= off and off + n <= hi and off % 64 == 0      # inside its bucket, TMA-aligned
+            seen.append((off, off + n))
+        seen.sort()
+        assert all(a[1] <= b[0] for a, b in zip(seen, seen[1:]))       # parameters do not overlap
+        for _, off, length in buckets:
+            assert length % (world * 1024) == 0 and off % 1024 == 0    # every rank's slice is vector-aligned
+
+
+def test_engine_segments_cover_the_flat_buffer_once():
+    """The shard arrays of all ranks, laid back into the flat order, tile it exactly (pure index arithmetic)."""
+    from mintext_b200.parallel.engine import plan_buckets
+
+    world = 4
+    _, buckets, total = plan_buckets([(0, 3000), (1, 9000), (2, 100), (3, 4096)], world)
+    covered = [0] * (total // 1024)
+    per_rank = total // world
+    for rank in range(world):
+        local = 0
+        for _, boff, blen in buckets:
+            sl = blen // world
+            for k in range((boff + rank * sl) // 1024, (boff + (rank + 1) * sl) // 1024):
+                covered[k] += 1
+            local += sl
+        assert local == per_rank
+    assert set(covered) == {1}
