@@ -146,7 +146,10 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--impl", default="own", choices=["own", "reference", "library"],
+                    help="own: this framework; reference: the unmodified reference (reports why it cannot run here); "
+                         "library: the same step composed from stock torch / cuBLAS / SDPA / NCCL pieces "
+                         "(baseline/library_llama.py) - a same-box comparator, not the reference")
     ap.add_argument("--model", default="llama1b", choices=["llama1b"] + sorted(BENCH_MODELS))
     ap.add_argument("--global-batch", type=int, default=None)
     ap.add_argument("--seq-len", type=int, default=None)
@@ -180,7 +183,23 @@ def main() -> None:
     from mintext_b200.utils.pytree import model_flops_per_token_batch
 
     warmup = max(args.warmup, 3)
-    if args.model == "llama1b":
+    if args.impl == "library":
+        if args.model != "llama1b":
+            raise SystemExit("--impl library covers the headline model only")
+        sys.path.insert(0, str(ROOT / "baseline"))
+        import library_llama
+
+        args.global_batch = args.global_batch or 64
+        args.seq_len = args.seq_len or 4096
+        args.micro_batch = args.micro_batch or 8
+        cfg = llama_1b_config(args.global_batch, args.seq_len, world, args.micro_batch, args.steps + warmup)
+        eng = library_llama.LibraryTrainer(library_llama.LLAMA_1B, dev, world, args.micro_batch,
+                                           total_steps=max(args.steps + warmup, 10))
+        tp = 1
+        metric = "train tokens/s (Llama-3.2-1B-shaped, bf16, AdamW)"
+        model_desc = "llama-3.2-1b-shaped (16L, d2048, 32/8 heads, ffn 8192, vocab 128256, tied)"
+        parallelism = eng.parallel
+    elif args.model == "llama1b":
         args.global_batch = args.global_batch or 64
         args.seq_len = args.seq_len or 4096
         args.micro_batch = args.micro_batch or 8
@@ -298,7 +317,7 @@ def main() -> None:
             "higher_is_better": True, "scaling": "strong",
             # the reference publishes a number for the Llama-3.2-1B run only
             "vs_baseline": value / (PUBLISHED_TOKENS_PER_SEC_PER_DEVICE * world) if args.model == "llama1b" else None,
-            "dtype": ("bf16 (mxfp8 MLP projections)" if args.fp8_recipe == "mx_block" else "bf16 (fp8 e4m3/e5m2 MLP projections)") if args.fp8_mlp else "bf16", "data": "synthetic uniform-random token ids, random-init weights", "impl": "own",
+            "dtype": ("bf16 (mxfp8 MLP projections)" if args.fp8_recipe == "mx_block" else "bf16 (fp8 e4m3/e5m2 MLP projections)") if args.fp8_mlp else "bf16", "data": "synthetic uniform-random token ids, random-init weights", "impl": args.impl,
             "tokens_per_sec_per_gpu": value / world, "tflops_per_gpu": tflops_per_gpu,
             "mfu_vs_nominal_2250": tflops_per_gpu / 2250.0, "final_loss": final_loss,
             "peak_memory_gb": peak_gb, "moe_dropped_rows": dropped,
@@ -308,7 +327,8 @@ def main() -> None:
                        "micro_batch": args.micro_batch, "grad_accum_per_rank": n_micro,
                        "l2": "inputs and weights per step exceed L2 (126 MB) by >20x; no explicit flush"},
             "clocks": clocks.summary(), "e2e": e2e,
-            "gpu_launches": int(n_launches),
+            # own arm: launches of this repository's kernels; library arm: none of them run, by construction
+            "gpu_launches": int(n_launches) if args.impl == "own" else 0,
         }
         print(json.dumps(line))
     if world > 1:

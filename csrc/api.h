@@ -21,6 +21,9 @@ void grouped_gemm_bf16(const void* X, const void* W, void* Y, const int* offsets
 // Experts without rows are skipped (clear dW beforehand when not accumulating).
 void grouped_wgrad_bf16(const void* X, const void* G, void* dW, const int* offsets, int E, int M_cap, int N, int K,
                         bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream);
+// Kernel choice for this thread's next grouped launches: 0 = default, 1 = single-CTA tiles (128 x 256), 2 = CTA pairs
+// (256 x 256).  Shapes the pair kernels do not cover fall back to the single-CTA kernels either way.
+void set_grouped_variant(int variant);
 // the same two products on CTA pairs (gemm/grouped_bf16_2cta.cu); the functions above route to these by default
 void grouped_gemm_bf16_pair(const void* X, const void* W, void* Y, const int* offsets, int E, int M_cap, int N, int K,
                             bool w_mn_major, int* status, int num_sms, cudaStream_t stream);

@@ -748,6 +748,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grad_pull_bucket", &grad_pull_bucket);
   m.def("bucket_flag_slots", &bucket_flag_slots);
   m.def("adamw_publish", &adamw_publish);
+  m.def("set_grouped_variant", [](int64_t v) { mt::set_grouped_variant((int)v); });
   m.def("grouped_gemm", &grouped_gemm);
   m.def("grouped_wgrad", &grouped_wgrad);
   m.def("grouped_gemm_scatter", &grouped_gemm_scatter);

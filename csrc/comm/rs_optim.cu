@@ -107,15 +107,20 @@ __global__ void grad_pull_bucket_kernel(PeerPtrs grads, PeerPtrs flags, int rank
   const int64_t nvec = n >> 2;
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    // all peers' loads are issued before any of them is consumed or cleared, so they overlap in flight (a store
+    // between two loads would pin their order: the buffers may alias as far as the compiler can tell)
+    float4 v[kMaxPeers];
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < world) v[r] = *(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo) + i);
     float4 s = accumulate ? reinterpret_cast<const float4*>(out)[i] : zero;
-#pragma unroll 8
-    for (int r = 0; r < world; ++r) {
-      float4* src = reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[r]) + lo) + i;
-      const float4 v = *src;
-      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-      *src = zero;  // this thread is the only reader of the element: clear it for the next step's accumulation
-    }
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)  // fixed summation order: the result is the same on every run
+      if (r < world) { s.x += v[r].x; s.y += v[r].y; s.z += v[r].z; s.w += v[r].w; }
     reinterpret_cast<float4*>(out)[i] = s;
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)  // this thread is the only reader of these elements: clear them for the next step
+      if (r < world) *(reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[r]) + lo) + i) = zero;
   }
 }
 

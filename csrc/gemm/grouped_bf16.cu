@@ -26,6 +26,12 @@ bool single_cta_only() {  // MT_GEMM_SINGLE_CTA=1 keeps the single-CTA kernels (
   return v;
 }
 
+// Kernel choice of the calling thread for the next grouped launches: 0 = default (CTA pairs unless
+// MT_GEMM_SINGLE_CTA=1), 1 = single-CTA 128 x 256 tiles, 2 = CTA-pair 256 x 256 tiles.  The autotuner times both.
+thread_local int g_variant = 0;
+
+bool use_pair_kernels() { return g_variant == 2 || (g_variant == 0 && !single_cta_only()); }
+
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
@@ -303,10 +309,12 @@ void configure(Kern k) {
 
 }  // namespace
 
+void set_grouped_variant(int v) { g_variant = (v == 1 || v == 2) ? v : 0; }
+
 void grouped_gemm_bf16(const void* X, const void* W, void* Y, const int* offsets, int E, int M_cap, int N, int K,
                        bool w_mn_major, int* status, int num_sms, cudaStream_t stream) {
   if (M_cap <= 0 || E <= 0) return;
-  if (!single_cta_only() && N > 128 && E <= 256)
+  if (use_pair_kernels() && N > 128 && E <= 256)
     return grouped_gemm_bf16_pair(X, W, Y, offsets, E, M_cap, N, K, w_mn_major, status, num_sms, stream);
   if (E > kMaxExperts) throw std::runtime_error("grouped_gemm_bf16: too many experts");
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -332,7 +340,7 @@ void grouped_gemm_bf16(const void* X, const void* W, void* Y, const int* offsets
 void grouped_wgrad_bf16(const void* X, const void* G, void* dW, const int* offsets, int E, int M_cap, int N, int K,
                         bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream) {
   if (M_cap <= 0 || E <= 0) return;
-  if (!single_cta_only() && N > 128 && K > 128 && E <= 256)
+  if (use_pair_kernels() && N > 128 && K > 128 && E <= 256)
     return grouped_wgrad_bf16_pair(X, G, dW, offsets, E, M_cap, N, K, out_f32, accumulate, status, num_sms, stream);
   if (E > kMaxExperts) throw std::runtime_error("grouped_wgrad_bf16: too many experts");
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;

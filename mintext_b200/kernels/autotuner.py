@@ -1,11 +1,13 @@
 """Grouped-GEMM autotuner with an on-disk cache (reference: mintext/kernels/autotuner.py).
 
-The reference sweeps XLA ``ragged_dot`` tile hints.  Here the tcgen05 grouped GEMM has a fixed tile, so what is
-tuned is the choice that still matters at run time: candidate (tm, tk, tn) triples are timed on the machine's
-actual backend (this repository's grouped kernel on a GPU, the loop oracle on CPU) for the gate/up and the down
-projection, the best triple per projection is recorded together with the achieved GFLOP/s, and the result is
-cached as JSON keyed by a hash of the problem (dims, dtype, device).  The cache semantics (key, file per
-problem, reuse on the next call) are the reference's.
+The reference sweeps XLA ``ragged_dot`` tile hints.  The tcgen05 grouped GEMM exists in two tilings -
+``(128, 64, 256)``: single-CTA tiles, and ``(256, 64, 256)``: CTA-pair tiles on two SMs (``cta_group::2``) - and
+which one wins depends on the rows per expert and the projection's width, so those are the candidates on a GPU:
+each is timed forward + backward (data and weight gradient) with CUDA events for the gate/up and the down
+projection on expert-balanced rows, the faster one per projection is recorded together with its GFLOP/s, and the
+result is cached as JSON keyed by a hash of the problem (dims, dtype, device).  ``MoEExperts`` passes the chosen
+triples to the kernels (``grouped_matmul(..., tiling=...)``).  On CPU there is one implementation, so the sweep
+collapses to a single candidate.  Cache semantics (key, file per problem, reuse on the next call) are the reference's.
 """
 
 from __future__ import annotations
@@ -18,7 +20,7 @@ from pathlib import Path
 
 import torch
 
-_TILE_CHOICES = (32, 64, 128, 256, 512)
+GPU_TILINGS = ((128, 64, 256), (256, 64, 256))  # single-CTA tiles, CTA-pair tiles
 
 
 @dataclass(frozen=True)
@@ -47,30 +49,36 @@ def _cache_key(cfg: MoETuningConfig) -> str:
     return hashlib.sha256(blob.encode()).hexdigest()[:16]
 
 
-def _candidate_tilings(m: int, k: int, n: int) -> list[tuple[int, int, int]]:
-    return [(tm, tk, tn) for tm in _TILE_CHOICES if tm <= m for tk in _TILE_CHOICES if tk <= k
-            for tn in _TILE_CHOICES if tn <= n]
-
-
-def _sample(cands, max_trials):
-    if len(cands) <= max_trials:
-        return cands
-    step = len(cands) / max_trials
-    return [cands[int(i * step)] for i in range(max_trials)]
+def _candidate_tilings(on_gpu: bool) -> list[tuple[int, int, int]]:
+    return list(GPU_TILINGS) if on_gpu else [GPU_TILINGS[0]]
 
 
 def _time_grouped(x, w, sizes, tiling, warmup, iters) -> float:
+    """Seconds per forward + backward of ``grouped_matmul`` with ``tiling`` (device-timed on a GPU)."""
     from mintext_b200.kernels import grouped_matmul
 
+    x = x.detach().requires_grad_(True)
+    w = w.detach().requires_grad_(True)
+
+    def run():
+        y = grouped_matmul(x, w, sizes, tiling=tiling)
+        y.backward(y.detach())
+        x.grad = w.grad = None
+
     for _ in range(warmup):
-        grouped_matmul(x, w, sizes, tiling=tiling)
+        run()
     if x.is_cuda:
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        start.record()
+        for _ in range(iters):
+            run()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / 1e3 / iters
     t0 = time.perf_counter()
     for _ in range(iters):
-        grouped_matmul(x, w, sizes, tiling=tiling)
-    if x.is_cuda:
-        torch.cuda.synchronize()
+        run()
     return (time.perf_counter() - t0) / iters
 
 
@@ -95,12 +103,16 @@ def autotune_moe(cfg: MoETuningConfig, cache_dir: str | None = None, max_trials:
         x = torch.randn(M, k, device=dev, dtype=dt)
         w = torch.randn(E, k, n, device=dev, dtype=dt)
         best, best_t = None, float("inf")
-        for tiling in _sample(_candidate_tilings(M, k, n), max_trials):
+        timings = {}
+        for tiling in _candidate_tilings(dev == "cuda")[:max_trials]:
             t = _time_grouped(x, w, sizes, tiling, warmup_iters, bench_iters)
+            timings["x".join(map(str, tiling))] = t
             if t < best_t:
                 best, best_t = tiling, t
-        result[name] = best or (128, 64, 256)
-        gflops[name] = 2.0 * M * k * n / best_t / 1e9 if best_t < float("inf") else 0.0
+        result[name] = best or GPU_TILINGS[0]
+        # forward + data gradient + weight gradient: three products of 2*M*k*n FLOPs
+        gflops[name] = 6.0 * M * k * n / best_t / 1e9 if best_t < float("inf") else 0.0
+        gflops[name + "_candidates_ms"] = {k_: round(v * 1e3, 4) for k_, v in timings.items()}
     res = MoETuningResult(tuple(result["gate_up"]), tuple(result["down"]),
                           "tcgen05_grouped" if dev == "cuda" else "loop_oracle", gflops)
     if cache_file is not None:

@@ -7,8 +7,9 @@
   one-hot einsum that costs E times the FLOPs).
 * ``tgmm(lhs[M,K], rhs[M,N], group_sizes[E]) -> [E,K,N]``
 
-The ``tiling`` arguments of the reference (XLA/Mosaic hints) are accepted and ignored: tile shapes are fixed by
-the tcgen05 kernel (128 x 256 x 64).
+``tiling = (tile_m, tile_k, tile_n)`` selects between the two tilings the tcgen05 grouped kernel exists in:
+``(128, 64, 256)`` single-CTA tiles, ``(256, 64, 256)`` CTA-pair tiles on two SMs (``cta_group::2``); other values,
+or None, keep the default.  On CPU the argument has no effect.
 """
 
 from __future__ import annotations
@@ -25,7 +26,7 @@ def _cuda(x: torch.Tensor) -> bool:
 
 
 def grouped_matmul(x: torch.Tensor, w: torch.Tensor, group_sizes: torch.Tensor, *, tiling=None) -> torch.Tensor:
-    return grouped_matmul_vjp(x, w, group_sizes)
+    return grouped_matmul_vjp(x, w, group_sizes, tiling=tiling)
 
 
 def tgmm(lhs: torch.Tensor, rhs: torch.Tensor, group_sizes: torch.Tensor, *, tiling=None) -> torch.Tensor:
@@ -55,5 +56,5 @@ def grouped_matmul_vjp(x: torch.Tensor, w: torch.Tensor, group_sizes: torch.Tens
     if _cuda(x):
         from mintext_b200.ops import moe as moe_ops
 
-        return moe_ops.grouped_matmul_cuda(x, w, group_sizes)
+        return moe_ops.grouped_matmul_cuda(x, w, group_sizes, tiling)
     return _GroupedMatmulFn.apply(x, w.to(x.dtype), group_sizes)

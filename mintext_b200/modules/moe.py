@@ -79,6 +79,9 @@ class MoEExperts(nn.Module):
         self.num_experts = E
         self.dtype = config.torch_dtype
         self.act_name = config.hidden_activation
+        # grouped-GEMM tilings per projection: from the config, or set later by the autotuner (train.py)
+        self.gate_up_tiling = tuple(config.moe_gate_up_tiling) or None
+        self.down_tiling = tuple(config.moe_down_tiling) or None
         self.ep = current_ep()
         lo, hi = self.ep.local_expert_range(E) if self.ep is not None else (0, E)
         self.local_range = (lo, hi)
@@ -109,11 +112,12 @@ class MoEExperts(nn.Module):
             return ep_mod.experts_forward_collective(self.ep, x, topk_indices, topk_weights, self.gate_up_proj,
                                                      self.down_proj, self.act_name, self.num_experts, self.dtype)
         if moe_ops.cuda_path(x) and gu is self.gate_up_proj:
-            return moe_ops.experts_forward(x, topk_indices, topk_weights, gu, dn, self.act_name)
+            return moe_ops.experts_forward(x, topk_indices, topk_weights, gu, dn, self.act_name, self.gate_up_tiling,
+                                           self.down_tiling)
         rows, sort_idx, sizes = kernels.route(x, topk_indices, self.num_experts)
-        h = kernels.grouped_matmul_vjp(rows, gu, sizes)
+        h = kernels.grouped_matmul_vjp(rows, gu, sizes, tiling=self.gate_up_tiling)
         h = F.gated_act(h, self.act_name)
-        y = kernels.grouped_matmul_vjp(h, dn, sizes)
+        y = kernels.grouped_matmul_vjp(h, dn, sizes, tiling=self.down_tiling)
         return kernels.unroute(y, sort_idx, topk_weights, topk_indices.shape[1])
 
 

@@ -43,20 +43,52 @@ def row_destinations(sorted_experts: torch.Tensor, off_p: torch.Tensor, off_u: t
     return off_p.long()[sorted_experts] + (r - off_u[sorted_experts])
 
 
+def tiling_variant(tiling) -> int:
+    """Kernel variant a ``(tile_m, tile_k, tile_n)`` triple selects: tile_m 128 = the single-CTA grouped kernel
+    (128 x 256 x 64 tiles), 256 = the CTA-pair kernel (256 x 256 x 64 on two SMs); anything else (or None) leaves
+    the default choice.  These are the two tilings the tcgen05 grouped GEMM exists in, and what the autotuner picks
+    between per projection."""
+    if not tiling:
+        return 0
+    return {128: 1, 256: 2}.get(int(tiling[0]), 0)
+
+
+class _variant:
+    """Selects the grouped-kernel variant for the launches issued inside the block (per calling thread)."""
+
+    def __init__(self, v: int):
+        self.v = int(v)
+
+    def __enter__(self):
+        if self.v:
+            ext().set_grouped_variant(self.v)
+
+    def __exit__(self, *exc):
+        if self.v:
+            ext().set_grouped_variant(0)
+
+
 class _GroupedPaddedFn(torch.autograd.Function):
     """``y = x @ w[e]`` on a padded, expert-contiguous row buffer (forward, data gradient and weight gradient all
     run the tcgen05 grouped kernel)."""
 
     @staticmethod
-    def forward(ctx, x, w, off_p, main_grad):
+    def forward(ctx, x, w, off_p, main_grad, variant=0):
         y = torch.empty(x.shape[0], w.shape[2], device=x.device, dtype=torch.bfloat16)
-        ext().grouped_gemm(x, w, y, off_p, True, status_word(x.device))
+        with _variant(variant):
+            ext().grouped_gemm(x, w, y, off_p, True, status_word(x.device))
         ctx.save_for_backward(x, w, off_p)
         ctx.main_grad = main_grad
+        ctx.variant = variant
         return y
 
     @staticmethod
     def backward(ctx, dy):
+        with _variant(ctx.variant):
+            return _GroupedPaddedFn._backward(ctx, dy) + (None,)
+
+    @staticmethod
+    def _backward(ctx, dy):
         x, w, off_p = ctx.saved_tensors
         dy = dy.contiguous()
         st = status_word(x.device)
@@ -75,8 +107,8 @@ class _GroupedPaddedFn(torch.autograd.Function):
         return dx, dw, None, None
 
 
-def grouped_padded(x_p: torch.Tensor, w: torch.Tensor, off_p: torch.Tensor) -> torch.Tensor:
-    return _GroupedPaddedFn.apply(x_p, w, off_p, getattr(w, "main_grad", None))
+def grouped_padded(x_p: torch.Tensor, w: torch.Tensor, off_p: torch.Tensor, tiling=None) -> torch.Tensor:
+    return _GroupedPaddedFn.apply(x_p, w, off_p, getattr(w, "main_grad", None), tiling_variant(tiling))
 
 
 def _pad_rows(x: torch.Tensor, group_sizes: torch.Tensor):
@@ -89,10 +121,10 @@ def _pad_rows(x: torch.Tensor, group_sizes: torch.Tensor):
     return x_p, off_p, dest
 
 
-def grouped_matmul_cuda(x, w, group_sizes):
+def grouped_matmul_cuda(x, w, group_sizes, tiling=None):
     """Public ragged form: rows grouped by expert without padding."""
     x_p, off_p, dest = _pad_rows(x.contiguous(), group_sizes)
-    return grouped_padded(x_p, w, off_p).index_select(0, dest)
+    return grouped_padded(x_p, w, off_p, tiling).index_select(0, dest)
 
 
 def tgmm_cuda(lhs, rhs, group_sizes):
@@ -216,7 +248,7 @@ def sort_by_expert(topk_idx: torch.Tensor, num_experts: int):
 
 
 def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, gate_up: torch.Tensor,
-                    down: torch.Tensor, act: str) -> torch.Tensor:
+                    down: torch.Tensor, act: str, gate_up_tiling=None, down_tiling=None) -> torch.Tensor:
     """Routed-expert MLP for ``x [N, D]``: counting-sort dispatch into the padded layout, two grouped GEMMs around
     the gated activation, weighted combine back to token order.  Differentiable end to end; every step is a kernel
     of this package."""
@@ -224,7 +256,7 @@ def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tenso
     E = gate_up.shape[0]
     sizes, off_p, pos, src = sort_by_expert(topk_idx, E)
     rows = _DispatchFn.apply(x.contiguous(), src, pos, K)
-    h = grouped_padded(rows, gate_up, off_p)
+    h = grouped_padded(rows, gate_up, off_p, gate_up_tiling)
     h = F.gated_act(h, act)
-    y = grouped_padded(h, down, off_p)
+    y = grouped_padded(h, down, off_p, down_tiling)
     return _CombineFn.apply(y, topk_w, pos, src, K)

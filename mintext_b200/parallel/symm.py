@@ -86,8 +86,12 @@ class SymmetricOptimizerComm:
         bucket's reduction is queued on the side stream behind those kernels, on a few SMs."""
         self._open_round()
         self.side.wait_stream(torch.cuda.current_stream(self.engine.device))
+        _, a, b, _ = self.engine.segments[bucket]
+        # a few SMs' worth of blocks for a layer of a small model, more for slices of hundreds of megabytes, so that
+        # the pull finishes under the rest of the backward pass without crowding it
+        blocks = max(self.side_blocks, min(296, (b - a) * 4 // (2 << 20)))
         with torch.cuda.stream(self.side):
-            self._pull(bucket, False, self.side_blocks)
+            self._pull(bucket, False, blocks)
 
     def wait_side_stream(self) -> None:
         torch.cuda.current_stream(self.engine.device).wait_stream(self.side)

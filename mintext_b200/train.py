@@ -70,9 +70,15 @@ class _SyntheticStream:
         return {"input_tokens": tok, "target_tokens": tgt}
 
 
-def _apply_moe_tiling(config, result) -> MinTextConfig:
-    """Copy autotuned grouped-GEMM tilings into the config (kept for parity; tile shapes are fixed by the
-    tcgen05 kernels, so the values are informational)."""
+def _apply_moe_tiling(config, result, model=None) -> MinTextConfig:
+    """Copy autotuned grouped-GEMM tilings into the config and, when the model is already built, into its expert
+    modules, which hand them to the grouped kernels (single-CTA or CTA-pair tiles per projection)."""
+    if model is not None:
+        from mintext_b200.modules.moe import MoEExperts
+
+        for m in model.modules():
+            if isinstance(m, MoEExperts):
+                m.gate_up_tiling, m.down_tiling = tuple(result.gate_up_tiling), tuple(result.down_tiling)
     return config.model_copy(update={"moe_gate_up_tiling": list(result.gate_up_tiling),
                                      "moe_down_tiling": list(result.down_tiling)})
 
@@ -173,7 +179,7 @@ def train(config: MinTextConfig) -> dict:
         tokens = config.per_device_batch_size * config.seq_length * config.num_experts_per_tok
         res = autotune_moe(MoETuningConfig(config.num_experts, config.hidden_size, config.moe_intermediate_size,
                                            tokens, config.dtype), cache_dir=config.moe_autotune_cache_dir or None)
-        config = _apply_moe_tiling(config, res)
+        config = _apply_moe_tiling(config, res, model)
 
     world = mesh.size
     tp = mesh.shape["tensor"]
@@ -264,6 +270,10 @@ def train(config: MinTextConfig) -> dict:
 
         dist.barrier()
         heartbeat.close()
+    if use_gpu:
+        free_b, total_b = torch.cuda.mem_get_info(device)  # includes symmetric-memory and communicator buffers
+        last["peak_memory_gb"] = round(max(torch.cuda.max_memory_reserved(device), total_b - free_b) / 2 ** 30, 2)
+        logger.info("peak device memory on rank %d: %.2f GB", rank, last["peak_memory_gb"])
     profiler.stop()
     metric_logger.close()
     if train_iter is not None:

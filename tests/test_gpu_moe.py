@@ -213,3 +213,34 @@ def test_grouped_gemm_with_row_scatter_epilogue():
     want[perm[keep]] = y[keep]
     assert torch.equal(out, want)
 
+
+
+def test_grouped_tilings_select_both_kernel_variants_and_agree():
+    """`tiling` picks the single-CTA or the CTA-pair grouped kernel; both give the fp32 product, values and gradients."""
+    from mintext_b200 import kernels
+
+    torch.manual_seed(0)
+    E, M, K, N = 4, 1024, 256, 512
+    sizes = torch.tensor([300, 0, 500, 224], device="cuda")
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(E, K, N, device="cuda") * 0.05).bfloat16()
+    outs = []
+    for tiling in ((128, 64, 256), (256, 64, 256), None):
+        xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        y = kernels.grouped_matmul(xa, wa, sizes, tiling=tiling)
+        y.backward(torch.ones_like(y))
+        outs.append((y.float(), xa.grad.float(), wa.grad.float()))
+    ref = torch.cat([x[a:b].float() @ w[e].float() for e, (a, b) in
+                     enumerate(zip([0, 300, 300, 800], [300, 300, 800, 1024]))])
+    for y, dx, dw in outs:
+        assert ((y - ref).norm() / ref.norm()).item() < 1e-2
+        assert ((dx - outs[0][1]).norm() / outs[0][1].norm()).item() < 1e-2
+        assert ((dw - outs[0][2]).norm() / outs[0][2].norm()).item() < 1e-2
+
+
+def test_autotuner_times_real_variants_on_gpu(tmp_path):
+    from mintext_b200.kernels.autotuner import GPU_TILINGS, MoETuningConfig, autotune_moe
+
+    r = autotune_moe(MoETuningConfig(8, 512, 256, 4096), cache_dir=str(tmp_path), warmup_iters=2, bench_iters=3)
+    assert tuple(r.gate_up_tiling) in GPU_TILINGS and tuple(r.down_tiling) in GPU_TILINGS
+    assert len(r.throughput_gflops["gate_up_candidates_ms"]) == 2 and r.backend == "tcgen05_grouped"

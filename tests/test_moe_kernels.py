@@ -118,11 +118,16 @@ def test_moe_block_forward_backward():
 def test_autotuner_candidates_and_cache(tmp_path):
     from mintext_b200.kernels.autotuner import MoETuningConfig, MoETuningResult, _cache_key, _candidate_tilings, autotune_moe
 
-    cands = _candidate_tilings(256, 512, 384)
-    assert cands and all(tm <= 256 and tk <= 512 and tn <= 384 for tm, tk, tn in cands)
+    from mintext_b200.ops.moe import tiling_variant
+
+    # the two tilings the tcgen05 grouped kernel exists in, mapped to its two kernel variants; one candidate on CPU
+    assert _candidate_tilings(True) == [(128, 64, 256), (256, 64, 256)] and _candidate_tilings(False) == [(128, 64, 256)]
+    assert [tiling_variant(t) for t in _candidate_tilings(True)] == [1, 2]
+    assert tiling_variant(None) == 0 and tiling_variant(()) == 0 and tiling_variant((64, 64, 64)) == 0
     tc = MoETuningConfig(num_experts=4, hidden_size=32, moe_intermediate_size=16, num_tokens=64, dtype="float32")
     r = autotune_moe(tc, cache_dir=str(tmp_path), max_trials=2, warmup_iters=1, bench_iters=1)
     assert isinstance(r, MoETuningResult) and len(r.gate_up_tiling) == 3 and r.backend
+    assert r.throughput_gflops["gate_up"] > 0 and "128x64x256" in r.throughput_gflops["gate_up_candidates_ms"]
     files = list(tmp_path.glob("*.json"))
     assert len(files) == 1
     r2 = autotune_moe(tc, cache_dir=str(tmp_path))
