@@ -81,9 +81,9 @@ void threefry_randint(int64_t* out, int64_t count, uint32_t a0, uint32_t a1, uin
                       uint32_t span, cudaStream_t stream);
 
 // ---- elementwise/embedding.cu
-void embedding_fwd(const void* table, const int64_t* ids, void* out, int64_t tokens, int dim, float scale,
+void embedding_fwd(const void* table, const int64_t* ids, void* out, int64_t tokens, int dim, float scale, int64_t vocab,
                    cudaStream_t stream);
-void embedding_bwd(const void* dout, const int64_t* ids, float* dtable, int64_t tokens, int dim, float scale,
+void embedding_bwd(const void* dout, const int64_t* ids, float* dtable, int64_t tokens, int dim, float scale, int64_t vocab,
                    cudaStream_t stream);
 
 // ---- optim/adamw.cu
@@ -163,6 +163,12 @@ void mxfp8_quantize(const void* x_bf16, int R, int C, void* q, void* sf, bool q_
                     bool qt_b_operand, cudaStream_t stream);
 void gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K, int* status,
                 int num_sms, cudaStream_t stream);
+// Stack of expert matrices w [E, R, C] bf16 -> q [E, R, C] (groups along C) and / or qt [E, C, R] (groups along R),
+// each matrix with its own B-operand scale tiling (E * mxfp8_sf_bytes(...) bytes per scale buffer).
+void mxfp8_quantize_stack(const void* w, int E, int R, int C, void* q, void* sf, void* qt, void* sft, cudaStream_t stream);
+// Block-scaled grouped product: rows of X grouped by expert at 128-aligned `offsets`; B = [E, N, K] e4m3.
+void grouped_gemm_mxfp8(const void* X, const void* sfa, const void* B, const void* sfb, void* Y, const int* offsets, int E,
+                        int M_cap, int N, int K, int* status, int num_sms, cudaStream_t stream);
 
 // ---- gemm/fp8_gemm.cu: per-tensor-scaled FP8 GEMM (both operands K-major) and its quantisation kernels
 void fp8_amax(const void* x_bf16, int64_t n, float* amax, cudaStream_t stream);
@@ -201,9 +207,9 @@ int moe_sort_chunks(int M);
 void moe_sort(const int64_t* experts, int M, int E, int64_t cap, int* chunk_counts, int64_t* sizes, int* off_p,
               int64_t* pos, int* src, cudaStream_t stream);
 void moe_gather_rows(const void* x, const int* src, const float* w, void* rows, int64_t cap, int K, int D,
-                     cudaStream_t stream);
+                     int64_t entries, cudaStream_t stream);
 void moe_combine_rows(const void* y, const int64_t* pos, const float* w, void* out, const void* g, float* dw, int N,
-                      int K, int D, cudaStream_t stream);
+                      int K, int D, int64_t y_rows, cudaStream_t stream);
 
 // ---- attention/flash_fwd.cu, flash_bwd.cu
 struct AttnParams {

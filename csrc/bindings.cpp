@@ -4,6 +4,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include "api.h"
+#include "common/bounds.cuh"
 
 namespace {
 
@@ -175,7 +176,7 @@ void embedding_fwd(const torch::Tensor& table, const torch::Tensor& ids, torch::
   TORCH_CHECK(dim % 8 == 0);
   c10::cuda::CUDAGuard guard(table.device());
   mt::embedding_fwd(table.data_ptr(), ids.data_ptr<int64_t>(), out.data_ptr(), ids.numel(), dim, (float)scale,
-                    cur_stream());
+                    table.size(0), cur_stream());
 }
 
 void embedding_bwd(const torch::Tensor& dout, const torch::Tensor& ids, torch::Tensor& dtable, double scale) {
@@ -184,7 +185,7 @@ void embedding_bwd(const torch::Tensor& dout, const torch::Tensor& ids, torch::T
   const int dim = (int)dtable.size(1);
   c10::cuda::CUDAGuard guard(dout.device());
   mt::embedding_bwd(dout.data_ptr(), ids.data_ptr<int64_t>(), dtable.data_ptr<float>(), ids.numel(), dim,
-                    (float)scale, cur_stream());
+                    (float)scale, dtable.size(0), cur_stream());
 }
 
 void adamw_step(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, const torch::Tensor& grad,
@@ -485,6 +486,43 @@ torch::Tensor gemm_mxfp8(const torch::Tensor& a, const torch::Tensor& sfa, const
   return out;
 }
 
+// w [E,R,C] bf16 -> (q [E,R,C], sf, qt [E,C,R], sft) with per-matrix B-operand scale tilings (expert weights)
+std::vector<torch::Tensor> mxfp8_quantize_stack(const torch::Tensor& w, bool want_q, bool want_qt) {
+  TORCH_CHECK(w.is_cuda() && w.is_contiguous() && w.dim() == 3 && w.scalar_type() == torch::kBFloat16);
+  c10::cuda::CUDAGuard guard(w.device());
+  auto u8 = w.options().dtype(torch::kUInt8);
+  const int E = (int)w.size(0), R = (int)w.size(1), C = (int)w.size(2);
+  torch::Tensor q, sf, qt, sft;
+  if (want_q) {
+    q = torch::empty({E, R, C}, u8);
+    sf = torch::zeros({E * mt::mxfp8_sf_bytes(R, C, true)}, u8);
+  }
+  if (want_qt) {
+    qt = torch::empty({E, C, R}, u8);
+    sft = torch::zeros({E * mt::mxfp8_sf_bytes(C, R, true)}, u8);
+  }
+  mt::mxfp8_quantize_stack(w.data_ptr(), E, R, C, want_q ? q.data_ptr() : nullptr, want_q ? sf.data_ptr() : nullptr,
+                           want_qt ? qt.data_ptr() : nullptr, want_qt ? sft.data_ptr() : nullptr, cur_stream());
+  return {q, sf, qt, sft};
+}
+
+// y [M_cap, N] bf16 = x [M_cap, K] . b[e] [N, K]^T per expert row group, block scales applied by the tensor core
+torch::Tensor grouped_gemm_mxfp8(const torch::Tensor& x, const torch::Tensor& sfx, const torch::Tensor& b,
+                                 const torch::Tensor& sfb, const torch::Tensor& offsets, torch::Tensor& status) {
+  TORCH_CHECK(x.is_contiguous() && b.is_contiguous() && x.scalar_type() == torch::kUInt8 && b.scalar_type() == torch::kUInt8);
+  TORCH_CHECK(x.dim() == 2 && b.dim() == 3 && x.size(1) == b.size(2) && x.size(1) % 128 == 0 && b.size(1) % 8 == 0 &&
+              x.size(0) % 128 == 0);
+  TORCH_CHECK(offsets.scalar_type() == torch::kInt32 && offsets.is_contiguous() && offsets.numel() == b.size(0) + 1);
+  TORCH_CHECK(sfx.numel() == mt::mxfp8_sf_bytes((int)x.size(0), (int)x.size(1), false), "row scales: wrong tiling");
+  TORCH_CHECK(sfb.numel() == b.size(0) * mt::mxfp8_sf_bytes((int)b.size(1), (int)b.size(2), true), "expert scales: wrong tiling");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = torch::empty({x.size(0), b.size(1)}, x.options().dtype(torch::kBFloat16));
+  mt::grouped_gemm_mxfp8(x.data_ptr(), sfx.data_ptr(), b.data_ptr(), sfb.data_ptr(), y.data_ptr(), offsets.data_ptr<int>(),
+                         (int)b.size(0), (int)x.size(0), (int)b.size(1), (int)x.size(2 - 1), status.data_ptr<int>(),
+                         sm_count(), cur_stream());
+  return y;
+}
+
 // W, QG, KD [BH, C, 64, dk]; U [BH, C, 64, dv]; M [BH, C, 64, 64]; GL [BH, C]  ->  (O [BH, C, 64, dv], Sstart [BH, C, dk, dv])
 std::vector<torch::Tensor> gdn_scan_fwd(const torch::Tensor& W, const torch::Tensor& U, const torch::Tensor& QG,
                                         const torch::Tensor& M, const torch::Tensor& KD, const torch::Tensor& GL) {
@@ -600,7 +638,7 @@ torch::Tensor moe_gather_rows(const torch::Tensor& x, const torch::Tensor& src, 
   c10::cuda::CUDAGuard guard(x.device());
   auto rows = torch::empty({src.numel(), x.size(1)}, x.options());
   mt::moe_gather_rows(x.data_ptr(), src.data_ptr<int>(), w ? w->data_ptr<float>() : nullptr, rows.data_ptr(), src.numel(),
-                      (int)K, (int)x.size(1), cur_stream());
+                      (int)K, (int)x.size(1), x.size(0) * K, cur_stream());
   return rows;
 }
 
@@ -671,7 +709,7 @@ std::vector<torch::Tensor> moe_combine_rows(const torch::Tensor& y, const torch:
   if (g) dw = torch::empty({N, K}, y.options().dtype(torch::kFloat32));
   mt::moe_combine_rows(y.data_ptr(), pos.data_ptr<int64_t>(), w ? w->data_ptr<float>() : nullptr,
                        want_out ? out.data_ptr() : nullptr, g ? g->data_ptr() : nullptr,
-                       g ? dw.data_ptr<float>() : nullptr, (int)N, (int)K, (int)y.size(1), cur_stream());
+                       g ? dw.data_ptr<float>() : nullptr, (int)N, (int)K, (int)y.size(1), y.size(0), cur_stream());
   return {out, dw};
 }
 
@@ -727,6 +765,36 @@ void tp_reduce_slots(const torch::Tensor& staging, torch::Tensor& y) {
 
 }  // namespace
 
+// ---- debug-bounds registry (common/bounds.cuh): translation units built with -DMINTEXT_DEBUG_BOUNDS register here
+namespace mt {
+namespace {
+struct BoundsUnit { std::string file; BoundsReadFn read; BoundsResetFn reset; };
+std::vector<BoundsUnit>& bounds_units() {
+  static std::vector<BoundsUnit> units;
+  return units;
+}
+}  // namespace
+void register_bounds_unit(const char* file, BoundsReadFn read, BoundsResetFn reset) {
+  bounds_units().push_back({std::string(file), read, reset});
+}
+}  // namespace mt
+
+// [(file, line, index, limit)] for every translation unit that recorded an out-of-range index; empty = clean.
+// In the ordinary build no unit registers and the list is always empty.
+std::vector<std::tuple<std::string, int64_t, int64_t, int64_t>> debug_bounds_report() {
+  std::vector<std::tuple<std::string, int64_t, int64_t, int64_t>> out;
+  for (auto& u : mt::bounds_units()) {
+    mt::BoundsRecord r{0, 0, 0, 0};
+    if (u.read(&r) != 0) throw std::runtime_error("debug_bounds_report: could not read the record of " + u.file);
+    if (r.code != 0) out.emplace_back(u.file, (int64_t)r.line, (int64_t)r.index, (int64_t)r.limit);
+  }
+  return out;
+}
+void debug_bounds_reset() {
+  for (auto& u : mt::bounds_units()) u.reset();
+}
+int64_t debug_bounds_units() { return (int64_t)mt::bounds_units().size(); }
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM");
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
@@ -738,6 +806,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gate_mul_fwd", &gate_mul_fwd);
   m.def("gate_mul_bwd", &gate_mul_bwd);
   m.def("cross_entropy", &cross_entropy);
+  m.def("debug_bounds_report", &debug_bounds_report);
+  m.def("debug_bounds_reset", &debug_bounds_reset);
+  m.def("debug_bounds_units", &debug_bounds_units);
   m.def("threefry_randint", &threefry_randint);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
@@ -762,6 +833,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_fp8", &gemm_fp8);
   m.def("mxfp8_quantize", &mxfp8_quantize);
   m.def("gemm_mxfp8", &gemm_mxfp8);
+  m.def("mxfp8_quantize_stack", &mxfp8_quantize_stack);
+  m.def("grouped_gemm_mxfp8", &grouped_gemm_mxfp8);
   m.def("gdn_scan_fwd", &gdn_scan_fwd);
   m.def("gdn_scan_bwd", &gdn_scan_bwd);
   m.def("conv1d_silu_fwd", &conv1d_silu_fwd);

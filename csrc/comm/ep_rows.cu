@@ -25,6 +25,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include "../api.h"
+#include "../common/bounds.cuh"
 
 namespace mt {
 namespace {
@@ -142,10 +143,12 @@ __global__ void ep_plan_kernel(const int64_t* __restrict__ flat, const int64_t* 
   __syncthreads();
   unsigned int my_drop = 0;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < NK; i += (int64_t)gridDim.x * blockDim.x) {
-    const int e = (int)flat[i];
+    int e = (int)flat[i];
+    const bool valid = MT_IN_BOUNDS(e, E);  // debug-bounds build: a bad expert id is reported and its row dropped
+    if (!valid) e = 0;
     const int r = e / El;
     const int64_t pos = s_start[e] + (pos_l[i] - off_l[e]);
-    const bool keep = pos < cap;
+    const bool keep = valid && pos < cap;
     dst_rank[i] = keep ? r : -1;
     dst_pos[i] = keep ? pos : 0;
     home_pos[i] = keep ? i : -1;

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include "../api.h"
+#include "../common/bounds.cuh"
 
 namespace mt {
 namespace {
@@ -15,7 +16,7 @@ union Pack8 {
 
 __global__ void embedding_fwd_kernel(const __nv_bfloat16* __restrict__ table, const int64_t* __restrict__ ids,
                                      __nv_bfloat16* __restrict__ out, int64_t tokens, int dim, float scale,
-                                     int use_scale) {
+                                     int use_scale, int64_t vocab) {
   const int nvec = dim >> 3;
   const int64_t total = tokens * nvec;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -23,6 +24,7 @@ __global__ void embedding_fwd_kernel(const __nv_bfloat16* __restrict__ table, co
     const int64_t t = idx / nvec;
     const int c = (int)(idx % nvec);
     Pack8 a;
+    if (!MT_IN_BOUNDS(ids[t], vocab)) continue;  // debug-bounds build: a bad token id is reported, not dereferenced
     a.u = reinterpret_cast<const uint4*>(table + ids[t] * dim)[c];
     if (use_scale) {
       const __nv_bfloat16 s = __float2bfloat16(scale);
@@ -34,7 +36,7 @@ __global__ void embedding_fwd_kernel(const __nv_bfloat16* __restrict__ table, co
 }
 
 __global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const int64_t* __restrict__ ids,
-                                     float* __restrict__ dtable, int64_t tokens, int dim, float scale) {
+                                     float* __restrict__ dtable, int64_t tokens, int dim, float scale, int64_t vocab) {
   const int nvec = dim >> 3;
   const int64_t total = tokens * nvec;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -43,6 +45,7 @@ __global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout, con
     const int c = (int)(idx % nvec);
     Pack8 a;
     a.u = reinterpret_cast<const uint4*>(dout + t * dim)[c];
+    if (!MT_IN_BOUNDS(ids[t], vocab)) continue;
     float* dst = dtable + ids[t] * dim + c * 8;
 #pragma unroll
     for (int j = 0; j < 8; ++j) atomicAdd(dst + j, __bfloat162float(a.h[j]) * scale);
@@ -57,19 +60,19 @@ inline int grid_for(int64_t total) {
 }  // namespace
 
 void embedding_fwd(const void* table, const int64_t* ids, void* out, int64_t tokens, int dim, float scale,
-                   cudaStream_t stream) {
+                   int64_t vocab, cudaStream_t stream) {
   const int64_t total = tokens * (dim / 8);
   if (total == 0) return;
   embedding_fwd_kernel<<<grid_for(total), 256, 0, stream>>>((const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out,
-                                                           tokens, dim, scale, scale != 1.0f);
+                                                           tokens, dim, scale, scale != 1.0f, vocab);
 }
 
 void embedding_bwd(const void* dout, const int64_t* ids, float* dtable, int64_t tokens, int dim, float scale,
-                   cudaStream_t stream) {
+                   int64_t vocab, cudaStream_t stream) {
   const int64_t total = tokens * (dim / 8);
   if (total == 0) return;
   embedding_bwd_kernel<<<grid_for(total), 256, 0, stream>>>((const __nv_bfloat16*)dout, ids, dtable, tokens, dim,
-                                                           scale);
+                                                           scale, vocab);
 }
 
 }  // namespace mt

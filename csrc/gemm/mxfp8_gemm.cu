@@ -266,6 +266,190 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
+
+// ---------------------------------------------------------------------------------------- grouped (expert) product
+// Y[rows, N] = X[rows, K] * W[e]^T-view for the rows of expert e, block-scaled like the dense kernel above.  Rows are
+// grouped by expert at 128-aligned offsets (`offsets`, device int32[E+1]), so every 128-row A tile belongs to one
+// expert and its scale atoms are indexed by the global row block exactly as in the dense case.  The B operand is the
+// stack of per-expert matrices [E, N, K] (K-major, e4m3) with per-expert scale tiling (192-row tiles inside each
+// expert; rows beyond N are zero-filled by the 3-D tile load, never the next expert's).  Tiles are (row block,
+// 192-column block); the expert of a row block comes from a table built in shared memory at kernel start.
+constexpr int kMaxRowBlocks = 4096;
+
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmC, const uint8_t* __restrict__ sfa,
+                     const uint8_t* __restrict__ sfb, const int* __restrict__ offsets, int E, int N, int K, int* status) {
+  using C = XCfg;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, MT_ERR_BAD_ARGS);
+    return;
+  }
+  uint8_t* sf_base = smem + C::OFF_SF;
+  uint8_t* epi_base = smem + C::OFF_EPI;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* tmem_full = bars + 2 * kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint16_t* mb2e = reinterpret_cast<uint16_t*>(smem + C::SMEM_BYTES);  // expert of every 128-row block
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_n = (N + BN - 1) / BN;
+  const int num_kb = K / BK;
+  int total_rows = offsets[E];
+  if (total_rows > kMaxRowBlocks * BM) total_rows = kMaxRowBlocks * BM;
+  const int num_mb = total_rows / BM;
+  const int num_tiles = num_mb * num_n;
+  for (int e = 0; e < E; ++e) {  // every thread fills its share of each expert's row blocks
+    const int b0 = offsets[e] / BM, b1 = min(offsets[e + 1] / BM, num_mb);
+    for (int mb = b0 + (int)threadIdx.x; mb < b1; mb += blockDim.x) mb2e[mb] = (uint16_t)e;
+  }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], kEpiWarps);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    prefetch_tmap(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int mb = tile / num_n, n_idx = tile % num_n;
+        const int e = mb2e[mb];
+        const uint8_t* sfa_row = sfa + static_cast<int64_t>(mb) * num_kb * C::SFA_BYTES;
+        const uint8_t* sfb_row = sfb + (static_cast<int64_t>(e) * num_n + n_idx) * num_kb * C::SFB_BYTES;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          if (!mbar_wait(&empty_bar[s], ((it / kStages) & 1) ^ 1, abort_flag, status, MT_ERR_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + s * C::STAGE_BYTES;
+          uint8_t* sf_dst = sf_base + s * C::SF_STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], C::STAGE_BYTES + C::SF_STAGE_BYTES);
+          tma_load_2d(a_dst, &tmA, &full_bar[s], kb * BK, mb * BM);
+          tma_load_3d(a_dst + C::A_BYTES, &tmB, &full_bar[s], kb * BK, n_idx * BN, e);
+          bulk_g2s(sf_dst, sfa_row + kb * C::SFA_BYTES, C::SFA_BYTES, &full_bar[s]);
+          bulk_g2s(sf_dst + C::SFA_BYTES, sfb_row + kb * C::SFB_BYTES, C::SFB_BYTES, &full_bar[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+        const int buf = tcount & 1;
+        if (!mbar_wait(&tmem_empty[buf], ((tcount >> 1) & 1) ^ 1, abort_flag, status, MT_ERR_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          if (!mbar_wait(&full_bar[s], (it / kStages) & 1, abort_flag, status, MT_ERR_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + C::A_BYTES;
+          const uint32_t sf_addr = smem_u32(sf_base + s * C::SF_STAGE_BYTES);
+          const uint32_t t_sfa = tmem_base + C::COL_SFA + (it & 1) * 4;
+          const uint32_t t_sfb = tmem_base + C::COL_SFB + (it & 1) * 8;
+          tc_cp_32x128b_warpx4(t_sfa, make_smem_desc_plain(sf_addr, 16, 128));
+          tc_cp_32x128b_warpx4(t_sfb, make_smem_desc_plain(sf_addr + C::SFA_BYTES, 16, 128));
+          tc_cp_32x128b_warpx4(t_sfb + 4, make_smem_desc_plain(sf_addr + C::SFA_BYTES + kAtomBytes, 16, 128));
+          const uint64_t da = make_smem_desc_sw128(a_addr, 16, 1024), db = make_smem_desc_sw128(b_addr, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tc_mma_mxf8(d_tmem, da + k * (UMMA_K >> 4), db + k * (UMMA_K >> 4), make_idesc_mxf8(BM, BN, k), t_sfa, t_sfb,
+                        (kb | k) != 0 ? 1u : 0u);
+          tc_commit(&empty_bar[s]);
+        }
+        if (ok) tc_commit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint8_t* stage0 = epi_base + (warp - 2) * 2 * kEpiStageBytes;
+    int tcount = 0, nstores = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+      const int mb = tile / num_n, n_idx = tile % num_n;
+      const int buf = tcount & 1;
+      if (!mbar_wait_warp(&tmem_full[buf], (tcount >> 1) & 1, abort_flag, status, MT_ERR_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after_sync();
+      const int row0 = mb * BM + q * 32;
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      for (int c = 0; c < BN / 64; ++c) {
+        const int col0 = n_idx * BN + c * 64;
+        if (col0 >= N) break;
+        uint8_t* sbuf = stage0 + (nstores & 1) * kEpiStageBytes;
+        if (lane == 0) tma_wait_group_read<1>();
+        __syncwarp();
+        uint8_t* srow = sbuf + lane * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_lane + c * 64 + h * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            *reinterpret_cast<uint4*>(srow + (((h * 4 + j) ^ (lane & 7)) << 4)) = v;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmC, sbuf, col0, row0);
+          tma_commit_group();
+        }
+        ++nstores;
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+    }
+    if (lane == 0) tma_wait_group<0>();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    __syncwarp();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
 // ---------------------------------------------------------------------------------------- quantisation
 // Byte offset of the scale of (row, 32-element group `g32`) in a scale buffer whose row tiles are `T` rows
 // (`atoms` = ceil(T / 128) atoms per tile and k-block), for a contraction length of `kb128` 128-element k-blocks.
@@ -297,10 +481,19 @@ __device__ __forceinline__ uint4 quantise16(const float (&v)[16], float inv) {
 
 // x [R, C] bf16 -> q [R, C] e4m3 with scales over 32-element groups along C (tile rows T), and / or the transposed
 // copy qt [C, R] with scales over 32-element groups along R (tile rows Tt).  One 64 x 64 tile per block.
+// blockIdx.z selects one matrix of a stack of `gridDim.z` equally shaped matrices (per-expert weights): element
+// buffers advance by R*C per matrix, scale buffers by `sf_stride` / `sft_stride` bytes (each matrix has its own
+// scale tiling, so a scale tile never spans two experts).
 __global__ void mx_quantize_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* __restrict__ q,
                                    uint8_t* __restrict__ sf, int T, uint8_t* __restrict__ qt, uint8_t* __restrict__ sft,
-                                   int Tt) {
+                                   int Tt, int64_t sf_stride, int64_t sft_stride) {
   __shared__ float tile[64][65];
+  {
+    const int64_t z = blockIdx.z, elems = static_cast<int64_t>(R) * C;
+    x += z * elems;
+    if (q != nullptr) { q += z * elems; sf += z * sf_stride; }
+    if (qt != nullptr) { qt += z * elems; sft += z * sft_stride; }
+  }
   const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
   const int sub = threadIdx.x >> 2, seg = threadIdx.x & 3;  // 64 rows (columns) x four 16-element segments
   {
@@ -376,7 +569,49 @@ void mxfp8_quantize(const void* x, int R, int C, void* q, void* sf, bool q_b_ope
   mx_quantize_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), R, C, static_cast<uint8_t*>(q),
                                                static_cast<uint8_t*>(sf), q_b_operand ? BN : BM,
                                                static_cast<uint8_t*>(qt), static_cast<uint8_t*>(sft),
-                                               qt_b_operand ? BN : BM);
+                                               qt_b_operand ? BN : BM, 0, 0);
+  MT_CUDA_CHECK(cudaGetLastError());
+}
+
+// The same for a stack w [E, R, C] (expert weights), every matrix with its own B-operand scale tiling:
+// q [E, R, C] with groups along C and scales sf (E * mxfp8_sf_bytes(R, C, true) bytes), and / or qt [E, C, R] with
+// groups along R and scales sft (E * mxfp8_sf_bytes(C, R, true) bytes).
+void mxfp8_quantize_stack(const void* w, int E, int R, int C, void* q, void* sf, void* qt, void* sft,
+                          cudaStream_t stream) {
+  if (E == 0 || R == 0 || C == 0) return;
+  if (C % 16 != 0) throw std::runtime_error("mxfp8_quantize_stack: columns must be a multiple of 16");
+  if (q != nullptr && C % BK != 0) throw std::runtime_error("mxfp8_quantize_stack: row-wise groups need columns % 128 == 0");
+  if (qt != nullptr && R % BK != 0) throw std::runtime_error("mxfp8_quantize_stack: transposed groups need rows % 128 == 0");
+  dim3 grid((C + 63) / 64, (R + 63) / 64, E);
+  mx_quantize_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(w), R, C, static_cast<uint8_t*>(q),
+                                               static_cast<uint8_t*>(sf), BN, static_cast<uint8_t*>(qt),
+                                               static_cast<uint8_t*>(sft), BN, mxfp8_sf_bytes(R, C, true),
+                                               mxfp8_sf_bytes(C, R, true));
+  MT_CUDA_CHECK(cudaGetLastError());
+}
+
+// Y [M_cap, N] bf16 = X [M_cap, K] (e4m3 + scales sfa, 128-row tiles) times, per expert, B[e] [N, K] (e4m3 + per-expert
+// scales sfb); rows grouped by expert at the 128-aligned `offsets` (device int32[E+1]).
+void grouped_gemm_mxfp8(const void* X, const void* sfa, const void* B, const void* sfb, void* Y, const int* offsets, int E,
+                        int M_cap, int N, int K, int* status, int num_sms, cudaStream_t stream) {
+  if (M_cap <= 0 || E <= 0) return;
+  if (K % BK != 0 || N % 8 != 0) throw std::runtime_error("grouped_gemm_mxfp8: K must be a multiple of 128 and N of 8");
+  if (M_cap % BM != 0 || M_cap / BM > kMaxRowBlocks || E > 65535)
+    throw std::runtime_error("grouped_gemm_mxfp8: row capacity must be a multiple of 128 and at most 524288 rows");
+  const auto u8 = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  CUtensorMap tA = make_tmap_2d(X, u8, 1, M_cap, K, K, BM, BK, sw);
+  CUtensorMap tB = make_tmap_3d(B, u8, 1, E, N, K, (uint64_t)N * K, K, 1, BN, BK, sw);
+  CUtensorMap tC = make_tmap_2d(Y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M_cap, N, N, 32, 64, sw);
+  const int smem_bytes = XCfg::SMEM_BYTES + kMaxRowBlocks * (int)sizeof(uint16_t);
+  static bool configured = false;
+  if (!configured) {
+    MT_CUDA_CHECK(cudaFuncSetAttribute(grouped_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    configured = true;
+  }
+  grouped_mxfp8_kernel<<<num_sms, kThreads, smem_bytes, stream>>>(tA, tB, tC, static_cast<const uint8_t*>(sfa),
+                                                                  static_cast<const uint8_t*>(sfb), offsets, E, N, K,
+                                                                  status);
   MT_CUDA_CHECK(cudaGetLastError());
 }
 

@@ -17,6 +17,7 @@
 #include <cstdint>
 #include <stdexcept>
 #include "../api.h"
+#include "../common/bounds.cuh"
 
 namespace mt {
 namespace {
@@ -286,7 +287,8 @@ __global__ void moe_count_kernel(const int64_t* __restrict__ experts, int M, int
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
   const int base = blockIdx.x * kChunk;
-  for (int i = threadIdx.x; i < kChunk && base + i < M; i += blockDim.x) atomicAdd(&cnt[(int)experts[base + i]], 1);
+  for (int i = threadIdx.x; i < kChunk && base + i < M; i += blockDim.x)
+    if (MT_IN_BOUNDS(experts[base + i], E)) atomicAdd(&cnt[(int)experts[base + i]], 1);
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) chunk_counts[blockIdx.x * E + e] = cnt[e];
 }
@@ -329,7 +331,7 @@ __global__ void moe_rank_kernel(const int64_t* __restrict__ experts, int M, int 
   const int base = blockIdx.x * kChunk;
   for (int i0 = 0; i0 < kChunk && base + i0 < M; i0 += 32) {
     const int i = base + i0 + lane;
-    const bool live = i < M;
+    const bool live = i < M && MT_IN_BOUNDS(experts[i < M ? i : 0], E);
     const int e = live ? (int)experts[i] : -1 - lane;  // dead lanes match nobody
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     const int before = __popc(peers & ((1u << lane) - 1u));
@@ -355,13 +357,13 @@ union Pack8 {
 // scale = w[src[p]] when w is given.
 __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src,
                                        const float* __restrict__ w, __nv_bfloat16* __restrict__ rows, int64_t cap,
-                                       int K, int D) {
+                                       int K, int D, int64_t entries) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int vecs = D >> 3;
   for (int64_t p = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp; p < cap; p += (int64_t)gridDim.x * (blockDim.x >> 5)) {
     const int s = src[p];
     uint4* dst = reinterpret_cast<uint4*>(rows + p * D);
-    if (s < 0) {
+    if (s < 0 || !MT_IN_BOUNDS(s, entries)) {
       for (int v = lane; v < vecs; v += 32) dst[v] = make_uint4(0, 0, 0, 0);
       continue;
     }
@@ -387,7 +389,7 @@ template <int KMAX>
 __global__ void moe_combine_rows_kernel(const __nv_bfloat16* __restrict__ y, const int64_t* __restrict__ pos,
                                         const float* __restrict__ w, __nv_bfloat16* __restrict__ out,
                                         const __nv_bfloat16* __restrict__ g, float* __restrict__ dw, int N, int K,
-                                        int D) {
+                                        int D, int64_t y_rows) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int vecs = D >> 3;
   for (int n = blockIdx.x * (blockDim.x >> 5) + warp; n < N; n += gridDim.x * (blockDim.x >> 5)) {
@@ -396,6 +398,7 @@ __global__ void moe_combine_rows_kernel(const __nv_bfloat16* __restrict__ y, con
 #pragma unroll
     for (int k = 0; k < KMAX; ++k) {
       pk[k] = k < K ? pos[(int64_t)n * K + k] : 0;
+      if (pk[k] >= 0 && !MT_IN_BOUNDS(pk[k], y_rows)) pk[k] = -1;  // reported; treated like a dropped slot
       wk[k] = k < K ? (w ? w[(int64_t)n * K + k] : 1.f) : 0.f;
     }
     if (out != nullptr) {
@@ -499,15 +502,16 @@ void moe_sort(const int64_t* experts, int M, int E, int64_t cap, int* chunk_coun
 }
 
 void moe_gather_rows(const void* x, const int* src, const float* w, void* rows, int64_t cap, int K, int D,
-                     cudaStream_t stream) {
+                     int64_t entries, cudaStream_t stream) {
   if (cap == 0) return;
   int64_t blocks = (cap + 7) / 8;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  moe_gather_rows_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, src, w, (__nv_bfloat16*)rows, cap, K, D);
+  moe_gather_rows_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, src, w, (__nv_bfloat16*)rows, cap, K, D,
+                                                          entries);
 }
 
 void moe_combine_rows(const void* y, const int64_t* pos, const float* w, void* out, const void* g, float* dw, int N,
-                      int K, int D, cudaStream_t stream) {
+                      int K, int D, int64_t y_rows, cudaStream_t stream) {
   if (N == 0) return;
   if (K > 16) throw std::runtime_error("moe_combine_rows: top_k must be <= 16");
   int blocks = (N + 7) / 8;
@@ -515,10 +519,10 @@ void moe_combine_rows(const void* y, const int64_t* pos, const float* w, void* o
   auto y_ = (const __nv_bfloat16*)y;
   auto o_ = (__nv_bfloat16*)out;
   auto g_ = (const __nv_bfloat16*)g;
-  if (K <= 2) moe_combine_rows_kernel<2><<<blocks, 256, 0, stream>>>(y_, pos, w, o_, g_, dw, N, K, D);
-  else if (K <= 4) moe_combine_rows_kernel<4><<<blocks, 256, 0, stream>>>(y_, pos, w, o_, g_, dw, N, K, D);
-  else if (K <= 8) moe_combine_rows_kernel<8><<<blocks, 256, 0, stream>>>(y_, pos, w, o_, g_, dw, N, K, D);
-  else moe_combine_rows_kernel<16><<<blocks, 256, 0, stream>>>(y_, pos, w, o_, g_, dw, N, K, D);
+  if (K <= 2) moe_combine_rows_kernel<2><<<blocks, 256, 0, stream>>>(y_, pos, w, o_, g_, dw, N, K, D, y_rows);
+  else if (K <= 4) moe_combine_rows_kernel<4><<<blocks, 256, 0, stream>>>(y_, pos, w, o_, g_, dw, N, K, D, y_rows);
+  else if (K <= 8) moe_combine_rows_kernel<8><<<blocks, 256, 0, stream>>>(y_, pos, w, o_, g_, dw, N, K, D, y_rows);
+  else moe_combine_rows_kernel<16><<<blocks, 256, 0, stream>>>(y_, pos, w, o_, g_, dw, N, K, D, y_rows);
 }
 
 }  // namespace mt

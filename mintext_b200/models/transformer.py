@@ -156,7 +156,7 @@ class DecoderLayer(nn.Module):
 
         tp = tpm.current_tp()
         tp_on = tp is not None and tp.size > 1
-        self.attn_replicated = tp_on and (self.is_linear or config.attention_type == "mla")
+        self.attn_replicated = tp_on and self.is_linear  # multi-head-latent attention shards its heads (modules/mla.py)
         self.mlp_replicated = tp_on and self.has_moe
         if self.attn_replicated:
             tpm.set_current_tp(None)

@@ -47,11 +47,45 @@ class MLAttention(nn.Module):
                                 ("embed", "heads", "kv"), rngs=rngs, name="value_proj")
         self.out = Linear((H, self.v_head_dim), D, dt, wdt, ("heads", "kv", "embed"), rngs=rngs, name="out_proj")
         self.rope = RotaryEmbedding(config, rope_dim=self.qk_rope_head_dim)
+        # Tensor parallelism: the per-head expansions (q_b / q, kv_b) are column-parallel over heads and the output
+        # projection row-parallel; the low-rank down-projections and their norms stay whole on every rank and see
+        # the gathered tokens, so each rank's gradient for them is the contribution of its own heads - a partial
+        # sum that the engine's cross-rank gradient sum completes.
+        from mintext_b200.parallel.tp import current_tp
+
+        self.tp = current_tp() if (current_tp() is not None and current_tp().size > 1) else None
+        self.local_heads = H
+        if self.tp is not None:
+            lo, hi = self.tp.shard(H, "num_attention_heads")
+            self.local_heads = hi - lo
+            heads_out = [self.q_b_proj if self.q_lora_rank > 0 else self.q_proj, self.kv_b_proj]
+            for lin, dim in [(m, 1) for m in heads_out] + [(self.out, 0)]:
+                full = lin.kernel.data
+                axes = lin.kernel.logical_axes
+                lin.kernel = nn.Parameter((full[:, lo:hi] if dim == 1 else full[lo:hi]).clone().contiguous())
+                lin.kernel.logical_axes = axes
+                lin.kernel.tensor_parallel = True
+                lin.kernel.shard_spec = (dim, self.tp.rank, self.tp.size)
+                lin.out_shape = tuple(lin.kernel.shape[len(lin.in_shape):])
+                lin.in_shape = tuple(lin.kernel.shape[:len(lin.in_shape)])
 
     def forward(self, x: torch.Tensor, positions: torch.Tensor | None, mask: torch.Tensor | None = None,
                 default_positions: bool = False) -> torch.Tensor:
+        tp = self.tp
+        if tp is not None:
+            # token-sharded input [1, T/t, D]: gather the group's tokens, attend with the local heads over the full
+            # sequences, scatter the output projection's partial sums back to the token shards
+            from mintext_b200.parallel import tp as tpm
+
+            if mask is not None:
+                raise NotImplementedError("explicit attention masks are not supported under tensor parallelism")
+            B, S = tp.batch_shape
+            Tl, D = x.shape[-2], x.shape[-1]
+            x = tpm.all_gather_tokens(x.reshape(Tl, D), tp).view(B, S, D)
+            if positions is None or positions.shape[-1] != S:
+                positions = torch.arange(S, device=x.device)[None].expand(B, -1)
         B, S, _ = x.shape
-        H = self.num_attention_heads
+        H = self.local_heads
         if self.q_lora_rank > 0:
             q = self.q_b_proj(self.q_a_norm(self.q_a_proj(x)))
         else:
@@ -70,4 +104,9 @@ class MLAttention(nn.Module):
             o = F.attention(qf, kf, v, self.scale, causal=False, mask=mask)
         else:
             o = F.attention(qf, kf, v, self.scale, causal=self.causal)
-        return self.out(o)
+        y = self.out(o)
+        if tp is not None:
+            from mintext_b200.parallel import tp as tpm
+
+            return tpm.reduce_scatter_tokens(y.reshape(B * S, -1), tp).view(1, -1, y.shape[-1])
+        return y

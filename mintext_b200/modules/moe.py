@@ -82,6 +82,7 @@ class MoEExperts(nn.Module):
         # grouped-GEMM tilings per projection: from the config, or set later by the autotuner (train.py)
         self.gate_up_tiling = tuple(config.moe_gate_up_tiling) or None
         self.down_tiling = tuple(config.moe_down_tiling) or None
+        self.use_fp8 = bool(config.moe_use_fp8)  # expert GEMMs (forward, data gradient) in block-scaled FP8
         self.ep = current_ep()
         lo, hi = self.ep.local_expert_range(E) if self.ep is not None else (0, E)
         self.local_range = (lo, hi)
@@ -108,12 +109,12 @@ class MoEExperts(nn.Module):
 
             if self.ep.fused and moe_ops.cuda_path(x) and gu is self.gate_up_proj:
                 return ep_mod.experts_forward_peer(self.ep, x, topk_indices, topk_weights, gu, dn, self.act_name,
-                                                   self.num_experts)
+                                                   self.num_experts, fp8=self.use_fp8)
             return ep_mod.experts_forward_collective(self.ep, x, topk_indices, topk_weights, self.gate_up_proj,
                                                      self.down_proj, self.act_name, self.num_experts, self.dtype)
         if moe_ops.cuda_path(x) and gu is self.gate_up_proj:
             return moe_ops.experts_forward(x, topk_indices, topk_weights, gu, dn, self.act_name, self.gate_up_tiling,
-                                           self.down_tiling)
+                                           self.down_tiling, self.use_fp8)
         rows, sort_idx, sizes = kernels.route(x, topk_indices, self.num_experts)
         h = kernels.grouped_matmul_vjp(rows, gu, sizes, tiling=self.gate_up_tiling)
         h = F.gated_act(h, self.act_name)

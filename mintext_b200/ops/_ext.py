@@ -7,6 +7,7 @@ The CUDA path is mandatory on a GPU machine: if a CUDA device is present and the
 from __future__ import annotations
 
 import importlib.util
+import os
 import threading
 from pathlib import Path
 
@@ -36,11 +37,14 @@ def _load(name: str):
         if not path.exists():
             from . import build
 
-            (build.build_cuda if name == "_mt_C" else build.build_io)()
+            if name == "_mt_C_dbg":
+                build.build_cuda(debug_bounds=True)
+            else:
+                (build.build_cuda if name == "_mt_C" else build.build_io)()
         spec = importlib.util.spec_from_file_location(name, path)
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
-        if name == "_mt_C":
+        if name in ("_mt_C", "_mt_C_dbg"):
             from . import launch_counter
 
             launch_counter.install(mod)
@@ -48,9 +52,27 @@ def _load(name: str):
         return mod
 
 
+def debug_bounds_enabled() -> bool:
+    """True when ``MT_DEBUG_BOUNDS=1`` selects the range-checked build of the kernels."""
+    return os.environ.get("MT_DEBUG_BOUNDS", "0") == "1"
+
+
 def ext():
-    """The CUDA extension module (built on first use when the shared object is missing)."""
-    return _load("_mt_C")
+    """The CUDA extension module (built on first use when the shared object is missing).  With
+    ``MT_DEBUG_BOUNDS=1`` this is the build whose kernels range-check every index they read from memory."""
+    return _load("_mt_C_dbg" if debug_bounds_enabled() else "_mt_C")
+
+
+def check_bounds(reset: bool = True) -> None:
+    """Debug-bounds build: raise if any kernel met an out-of-range index (the access itself was skipped); a no-op
+    report in the ordinary build.  Synchronises."""
+    torch.cuda.synchronize()
+    rep = ext().debug_bounds_report()
+    if rep:
+        if reset:
+            ext().debug_bounds_reset()
+        msgs = [f"{Path(f).name}:{line}: index {idx} outside [0, {lim})" for f, line, idx, lim in rep]
+        raise IndexError("out-of-range index in a kernel: " + "; ".join(msgs))
 
 
 def io_ext():

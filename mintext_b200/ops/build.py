@@ -1,8 +1,9 @@
 """In-tree build of the CUDA/C++ extension for sm_100a.
 
 ``python -m mintext_b200.ops.build`` compiles every source under ``csrc/`` into
-``mintext_b200/_mt_C.so`` (CUDA kernels + torch bindings) and ``mintext_b200/_mt_io.so`` (host-only C++
-runtime pieces).  nvcc cross-compiles without a GPU, so this also serves as the "does it build" check.
+``mintext_b200/_mt_C.so`` (CUDA kernels + torch bindings), ``mintext_b200/_mt_C_dbg.so`` (the same sources with
+``-DMINTEXT_DEBUG_BOUNDS``: data-dependent indices are range-checked, violations are recorded and skipped; selected
+at run time with ``MT_DEBUG_BOUNDS=1``) and ``mintext_b200/_mt_io.so`` (host-only C++ runtime pieces).  nvcc cross-compiles without a GPU, so this also serves as the "does it build" check.
 """
 
 from __future__ import annotations
@@ -28,26 +29,28 @@ def _cuda_sources() -> list[str]:
     return sorted(str(p) for p in CSRC.rglob("*.cu"))
 
 
-def build_cuda(verbose: bool = False) -> Path:
+def build_cuda(verbose: bool = False, debug_bounds: bool = False) -> Path:
     from torch.utils import cpp_extension
 
-    build_dir = REPO_ROOT / "build" / "_mt_C"
+    name = "_mt_C_dbg" if debug_bounds else "_mt_C"
+    build_dir = REPO_ROOT / "build" / name
     build_dir.mkdir(parents=True, exist_ok=True)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     os.environ.setdefault("MAX_JOBS", str(os.cpu_count() or 4))
     sources = [str(CSRC / "bindings.cpp")] + _cuda_sources()
+    define = ["-DMINTEXT_DEBUG_BOUNDS"] if debug_bounds else []
     cpp_extension.load(
-        name="_mt_C",
+        name=name,
         sources=sources,
-        extra_cflags=["-O3", "-std=c++17"],
-        extra_cuda_cflags=CUDA_FLAGS,
+        extra_cflags=["-O3", "-std=c++17"] + define,
+        extra_cuda_cflags=CUDA_FLAGS + define,
         extra_include_paths=[str(CSRC)],
         build_directory=str(build_dir),
         verbose=verbose,
         is_python_module=True,
     )
-    out = PKG / "_mt_C.so"
-    shutil.copyfile(build_dir / "_mt_C.so", out)
+    out = PKG / f"{name}.so"
+    shutil.copyfile(build_dir / f"{name}.so", out)
     return out
 
 
@@ -75,6 +78,7 @@ def build_io(verbose: bool = False) -> Path | None:
 
 def build_all(verbose: bool = False) -> None:
     build_cuda(verbose)
+    build_cuda(verbose, debug_bounds=True)
     build_io(verbose)
 
 

@@ -107,7 +107,54 @@ class _GroupedPaddedFn(torch.autograd.Function):
         return dx, dw, None, None
 
 
-def grouped_padded(x_p: torch.Tensor, w: torch.Tensor, off_p: torch.Tensor, tiling=None) -> torch.Tensor:
+class _GroupedMxfp8Fn(torch.autograd.Function):
+    """``y = x @ w[e]`` on the padded expert layout with MXFP8 operands (e4m3 elements, one power-of-two scale per
+    32 elements along the contraction, applied inside the tensor core: csrc/gemm/mxfp8_gemm.cu, grouped kernel).
+    Forward and data gradient run in 8 bits - each operand quantised along the dimension its product contracts, the
+    expert weights per expert with their own scale tiling; the weight gradient stays a bf16 grouped GEMM accumulating
+    in fp32, as on the dense FP8 paths (mintext/modules/linear.py:37-57 for the layer semantics)."""
+
+    @staticmethod
+    def forward(ctx, x, w, off_p, main_grad):
+        e, st = ext(), status_word(x.device)
+        xq, xs, _, _ = e.mxfp8_quantize(x, True, False, False, False)
+        # w [E, K, N]: the forward contracts K (transposed copy [E, N, K]), the data gradient contracts N (w as stored)
+        wq, ws, wqt, wst = e.mxfp8_quantize_stack(w, True, True)
+        ctx.save_for_backward(x, w, wq, ws, off_p)
+        ctx.main_grad = main_grad
+        return e.grouped_gemm_mxfp8(xq, xs, wqt, wst, off_p, st)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, wq, ws, off_p = ctx.saved_tensors
+        e, st = ext(), status_word(x.device)
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dyq, dys, _, _ = e.mxfp8_quantize(dy, True, False, False, False)
+            dx = e.grouped_gemm_mxfp8(dyq, dys, wq, ws, off_p, st)   # dy [rows, N] . w[e] [K, N]^T
+        if ctx.needs_input_grad[1]:
+            mg = ctx.main_grad
+            if mg is not None:
+                e.grouped_wgrad(x, dy, mg.view(w.shape), off_p, True, st)
+            else:
+                dwf = torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+                e.grouped_wgrad(x, dy, dwf, off_p, False, st)
+                dw = dwf.to(w.dtype)
+        return dx, dw, None, None
+
+
+def mxfp8_grouped_path(x_p: torch.Tensor, w: torch.Tensor) -> bool:
+    """Shapes the block-scaled grouped kernel covers: both contraction lengths (forward K, data gradient N) in
+    whole 128-element blocks."""
+    return (x_p.is_cuda and x_p.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 3
+            and hasattr(ext(), "grouped_gemm_mxfp8") and w.shape[1] % 128 == 0 and w.shape[2] % 128 == 0
+            and x_p.shape[0] % 128 == 0 and x_p.shape[0] // 128 <= 4096)
+
+
+def grouped_padded(x_p: torch.Tensor, w: torch.Tensor, off_p: torch.Tensor, tiling=None, fp8: bool = False) -> torch.Tensor:
+    if fp8 and mxfp8_grouped_path(x_p, w):
+        return _GroupedMxfp8Fn.apply(x_p, w, off_p, getattr(w, "main_grad", None))
     return _GroupedPaddedFn.apply(x_p, w, off_p, getattr(w, "main_grad", None), tiling_variant(tiling))
 
 
@@ -248,7 +295,7 @@ def sort_by_expert(topk_idx: torch.Tensor, num_experts: int):
 
 
 def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, gate_up: torch.Tensor,
-                    down: torch.Tensor, act: str, gate_up_tiling=None, down_tiling=None) -> torch.Tensor:
+                    down: torch.Tensor, act: str, gate_up_tiling=None, down_tiling=None, fp8: bool = False) -> torch.Tensor:
     """Routed-expert MLP for ``x [N, D]``: counting-sort dispatch into the padded layout, two grouped GEMMs around
     the gated activation, weighted combine back to token order.  Differentiable end to end; every step is a kernel
     of this package."""
@@ -256,7 +303,7 @@ def experts_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tenso
     E = gate_up.shape[0]
     sizes, off_p, pos, src = sort_by_expert(topk_idx, E)
     rows = _DispatchFn.apply(x.contiguous(), src, pos, K)
-    h = grouped_padded(rows, gate_up, off_p, gate_up_tiling)
+    h = grouped_padded(rows, gate_up, off_p, gate_up_tiling, fp8)
     h = F.gated_act(h, act)
-    y = grouped_padded(h, down, off_p, down_tiling)
+    y = grouped_padded(h, down, off_p, down_tiling, fp8)
     return _CombineFn.apply(y, topk_w, pos, src, K)

@@ -298,6 +298,25 @@ class _Combine(torch.autograd.Function):
         return b["in"][: plan["cap"]].clone(), dw, None, None
 
 
+def _grouped_plain(x, w, off, w_is_ekn: bool, fp8: bool):
+    """Grouped product that stays on this rank (no row scatter): ``x @ w[e]`` (``w_is_ekn``) or ``x @ w[e]^T``; in
+    block-scaled FP8 when asked for and the shapes allow it, else bf16."""
+    from mintext_b200.ops import moe as moe_ops
+    from mintext_b200.ops._ext import ext, status_word
+
+    e, st = ext(), status_word(x.device)
+    if fp8 and moe_ops.mxfp8_grouped_path(x, w):
+        xq, xs, _, _ = e.mxfp8_quantize(x, True, False, False, False)
+        if w_is_ekn:   # contraction over K: the kernel wants [E, N, K]
+            _, _, wq, ws = e.mxfp8_quantize_stack(w, False, True)
+        else:          # contraction over N: w as stored is [E, K(out), N(contraction)]
+            wq, ws, _, _ = e.mxfp8_quantize_stack(w, True, False)
+        return e.grouped_gemm_mxfp8(xq, xs, wq, ws, off, st)
+    y = torch.empty(x.shape[0], w.shape[2] if w_is_ekn else w.shape[1], device=x.device, dtype=torch.bfloat16)
+    e.grouped_gemm(x, w, y, off, w_is_ekn, st)
+    return y
+
+
 class _GroupedCombine(torch.autograd.Function):
     """Down projection of the local experts fused with the combine all-to-all: ONE kernel multiplies the expert
     tiles and writes every output row from its epilogue straight into the home rank's receive buffer over NVLink
@@ -306,9 +325,10 @@ class _GroupedCombine(torch.autograd.Function):
     expert ranks, then the grouped data- and weight-gradient GEMMs."""
 
     @staticmethod
-    def forward(ctx, h, w, topk_w, main_grad, ep, plan):
+    def forward(ctx, h, w, topk_w, main_grad, ep, plan, fp8=False):
         from mintext_b200.ops._ext import ext, status_word
 
+        ctx.fp8 = fp8
         D = w.shape[2]
         N, K = plan["N"], plan["K"]
         b = ep.buffers(plan["cap"], D)
@@ -345,8 +365,7 @@ class _GroupedCombine(torch.autograd.Function):
         dy_p = torch.empty(plan["cap"], D, device=dy.device, dtype=dy.dtype)
         ext().ep_gather_rows(dy_p, plan["row_src"], plan["row_scale"])
         ep.barrier()  # all pulls done: the buffers may be reused
-        dh = torch.empty_like(h)
-        ext().grouped_gemm(dy_p, w, dh, plan["off_local"], False, st)
+        dh = _grouped_plain(dy_p, w, plan["off_local"], False, ctx.fp8)
         dw = None
         if ctx.main_grad is not None:
             ext().grouped_wgrad(h, dy_p, ctx.main_grad.view(w.shape), plan["off_local"], True, st)
@@ -354,7 +373,7 @@ class _GroupedCombine(torch.autograd.Function):
             dwf = torch.zeros(w.shape, device=w.device, dtype=torch.float32)
             ext().grouped_wgrad(h, dy_p, dwf, plan["off_local"], False, st)
             dw = dwf.to(w.dtype)
-        return dh, dw, dtw, None, None, None
+        return dh, dw, dtw, None, None, None, None
 
 
 class _DispatchGrouped(torch.autograd.Function):
@@ -363,12 +382,9 @@ class _DispatchGrouped(torch.autograd.Function):
     straight back to the rank the token came from (same SCATTER kernel as the fused combine)."""
 
     @staticmethod
-    def forward(ctx, x, w, main_grad, ep, plan):
-        from mintext_b200.ops._ext import ext, status_word
-
+    def forward(ctx, x, w, main_grad, ep, plan, fp8=False):
         rows = _dispatch_rows(x, ep, plan)
-        y = torch.empty(rows.shape[0], w.shape[2], device=x.device, dtype=torch.bfloat16)
-        ext().grouped_gemm(rows, w, y, plan["off_local"], True, status_word(x.device))
+        y = _grouped_plain(rows, w, plan["off_local"], True, fp8)
         ctx.save_for_backward(rows, w)
         ctx.ep, ctx.plan, ctx.main_grad, ctx.n = ep, plan, main_grad, x.shape[0]
         return y
@@ -398,7 +414,7 @@ class _DispatchGrouped(torch.autograd.Function):
         N, K = plan["N"], plan["K"]
         # sum of each token's K adjacent gradient rows; rows of dropped slots were never written and are skipped
         dx, _ = ext().moe_combine_rows(b["out"][: N * K], plan["home_pos"], None, N, K, True, None)
-        return dx, dw, None, None, None
+        return dx, dw, None, None, None, None
 
 
 def _fused_combine_ok(ep: ExpertParallel, plan, down_local) -> bool:
@@ -412,7 +428,9 @@ def _fused_combine_ok(ep: ExpertParallel, plan, down_local) -> bool:
 
 
 def experts_forward_peer(ep: ExpertParallel, x, topk_idx, topk_w, gate_up_local, down_local, act: str,
-                         num_experts: int):
+                         num_experts: int, fp8: bool = False):
+    """``fp8``: the expert GEMMs that stay on the rank (gate/up forward, down data gradient) run block-scaled; the two
+    fused with a row scatter over NVLink (down forward, gate/up data gradient) stay bf16."""
     from mintext_b200.ops import functional as F
     from mintext_b200.ops import moe as moe_ops
 
@@ -422,12 +440,14 @@ def experts_forward_peer(ep: ExpertParallel, x, topk_idx, topk_w, gate_up_local,
     plan = _plan(ep, topk_idx, topk_w, num_experts, cap, x.shape[1])
     fused = _fused_combine_ok(ep, plan, down_local)
     if fused and x.shape[1] > 128 and x.dtype == torch.bfloat16:
-        h = _DispatchGrouped.apply(x.contiguous(), gate_up_local, getattr(gate_up_local, "main_grad", None), ep, plan)
+        h = _DispatchGrouped.apply(x.contiguous(), gate_up_local, getattr(gate_up_local, "main_grad", None), ep, plan,
+                                   fp8)
     else:
         rows = _Dispatch.apply(x, ep, plan)
-        h = moe_ops.grouped_padded(rows, gate_up_local, plan["off_local"])
+        h = moe_ops.grouped_padded(rows, gate_up_local, plan["off_local"], None, fp8)
     h = F.gated_act(h, act)
     if fused:
-        return _GroupedCombine.apply(h.contiguous(), down_local, topk_w, getattr(down_local, "main_grad", None), ep, plan)
-    y = moe_ops.grouped_padded(h, down_local, plan["off_local"])
+        return _GroupedCombine.apply(h.contiguous(), down_local, topk_w, getattr(down_local, "main_grad", None), ep, plan,
+                                     fp8)
+    y = moe_ops.grouped_padded(h, down_local, plan["off_local"], None, fp8)
     return _Combine.apply(y, topk_w, ep, plan)

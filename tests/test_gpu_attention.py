@@ -10,6 +10,16 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
+def _assert_blocks_close(got, ref, rel, what):
+    """Per (batch, 128-token block, head) error: a single bad tile of one head must not hide in the global norm."""
+    B, S, H, D = ref.shape
+    nb = max(S // 128, 1)
+    d = (got.float() - ref.float()).reshape(B, nb, S // nb, H, D).permute(0, 1, 3, 2, 4).reshape(B, nb, H, -1)
+    r = ref.float().reshape(B, nb, S // nb, H, D).permute(0, 1, 3, 2, 4).reshape(B, nb, H, -1)
+    err = d.norm(dim=-1) / (r.norm(dim=-1) + 1e-3 * r.norm() / (B * nb * H) ** 0.5 + 1e-12)
+    assert err.max().item() < rel, (what, "worst block", err.max().item())
+
+
 def _run(B, S, H, Hkv, d, causal=True, window=None, softcap=None, grad=True, dv=None):
     from mintext_b200.ops import oracle
     from mintext_b200.ops._ext import check_status
@@ -26,6 +36,7 @@ def _run(B, S, H, Hkv, d, causal=True, window=None, softcap=None, grad=True, dv=
     torch.cuda.synchronize()
     check_status()
     assert _rel(o, ref) < 2e-2, _rel(o, ref)
+    _assert_blocks_close(o, ref, 4e-2, "o")
     if grad:
         do = torch.randn_like(o)
         o.backward(do)
@@ -35,6 +46,9 @@ def _run(B, S, H, Hkv, d, causal=True, window=None, softcap=None, grad=True, dv=
         assert _rel(v.grad, vf.grad) < 3e-2, ("dv", _rel(v.grad, vf.grad))
         assert _rel(k.grad, kf.grad) < 3e-2, ("dk", _rel(k.grad, kf.grad))
         assert _rel(q.grad, qf.grad) < 3e-2, ("dq", _rel(q.grad, qf.grad))
+        _assert_blocks_close(v.grad, vf.grad, 6e-2, "dv")
+        _assert_blocks_close(k.grad, kf.grad, 6e-2, "dk")
+        _assert_blocks_close(q.grad, qf.grad, 6e-2, "dq")
 
 
 def test_flash_fwd_single_block():

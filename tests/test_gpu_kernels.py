@@ -29,6 +29,28 @@ def _rel_err(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
+def _tiles(t, tile):
+    """[M, N] -> [ceil(M/tile), ceil(N/tile), tile*tile] with zero padding at ragged edges."""
+    M, N = t.shape
+    Mp, Np = -(-M // tile) * tile, -(-N // tile) * tile
+    p = torch.zeros(Mp, Np, device=t.device, dtype=torch.float32)
+    p[:M, :N] = t.float()
+    return p.view(Mp // tile, tile, Np // tile, tile).permute(0, 2, 1, 3).reshape(Mp // tile, Np // tile, -1)
+
+
+def _assert_tiles_close(got, ref, tile=128, rel=1e-2, max_abs=2.0 ** -6):
+    """Every ``tile x tile`` block of the output on its own: relative Frobenius error below ``rel`` and largest
+    absolute error below ``max_abs`` times the block's largest reference magnitude.  A whole-tensor norm hides one
+    misplaced epilogue box (a 32 x 64 box is 0.01 % of a 4096 x 2048 output); a per-block bound does not."""
+    d, r = _tiles(got.float() - ref.float(), tile), _tiles(ref, tile)
+    fro = d.norm(dim=-1) / (r.norm(dim=-1) + 1e-6)
+    worst = d.abs().amax(-1) / (r.abs().amax(-1) + 1e-6)
+    i = int(fro.argmax())
+    assert fro.max().item() < rel, ("tile frobenius", divmod(i, fro.shape[1]), fro.max().item())
+    j = int(worst.argmax())
+    assert worst.max().item() < max_abs, ("tile max-abs", divmod(j, worst.shape[1]), worst.max().item())
+
+
 @pytest.mark.parametrize("a_km,b_kn", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (384, 512, 320), (200, 136, 72), (1024, 2048, 1024)])
 def test_gemm_layouts(a_km, b_kn, M, N, K):
@@ -42,6 +64,7 @@ def test_gemm_layouts(a_km, b_kn, M, N, K):
     _ext().gemm(A, B, c, a_km, b_kn, False, _status())
     _check()
     assert _rel_err(c, ref) < 1e-2
+    _assert_tiles_close(c, ref)
 
 
 @pytest.mark.parametrize("accumulate", [False, True])
@@ -56,6 +79,7 @@ def test_gemm_fp32_out_and_accumulate(accumulate):
     _check()
     ref = a.float() @ b.float().t() + (c0 if accumulate else 0)
     assert _rel_err(c, ref) < 1e-5
+    _assert_tiles_close(c, ref, rel=1e-5, max_abs=1e-5)
 
 
 @pytest.mark.parametrize("M,N,K,b_kn", [(256, 256, 64, False), (512, 768, 320, True), (384, 520, 1024, False),
@@ -71,6 +95,7 @@ def test_gemm_on_cta_pairs(M, N, K, b_kn):
     _ext().gemm_pair(a, B, c, b_kn, _status())
     _check()
     assert _rel_err(c, ref) < 1e-2
+    _assert_tiles_close(c, ref)
 
 
 def test_gemm_weight_gradient_layout_with_split_k():

@@ -244,3 +244,71 @@ def test_autotuner_times_real_variants_on_gpu(tmp_path):
     r = autotune_moe(MoETuningConfig(8, 512, 256, 4096), cache_dir=str(tmp_path), warmup_iters=2, bench_iters=3)
     assert tuple(r.gate_up_tiling) in GPU_TILINGS and tuple(r.down_tiling) in GPU_TILINGS
     assert len(r.throughput_gflops["gate_up_candidates_ms"]) == 2 and r.backend == "tcgen05_grouped"
+
+
+def _mx_qdq(t):
+    """Quantise-dequantise along the last dim in 32-element blocks: e4m3 elements, power-of-two block scale."""
+    shape = t.shape
+    tf = t.float().reshape(-1, shape[-1] // 32, 32)
+    amax = tf.abs().amax(-1, keepdim=True)
+    e = torch.ceil(torch.log2(amax.clamp_min(2.0 ** -120) / 448.0)).clamp(-127, 127)
+    scale = torch.exp2(e)
+    return ((tf / scale).clamp(-448, 448).to(torch.float8_e4m3fn).float() * scale).reshape(shape)
+
+
+def test_grouped_mxfp8_matches_dequantised_product():
+    """Block-scaled expert GEMM: forward and data gradient equal the fp32 product of the de-quantised operands (each
+    quantised along the dimension that product contracts); the weight gradient is the bf16 one."""
+    from mintext_b200.ops import moe as moe_ops
+    from mintext_b200.ops._ext import check_status
+
+    torch.manual_seed(0)
+    E, K, N = 4, 256, 384          # N is not a multiple of the 192-row B tile: the ragged tile must not read the next expert
+    sizes = [256, 0, 128, 384]
+    off = torch.tensor([0, 256, 256, 384, 768], device="cuda", dtype=torch.int32)
+    cap = 1024                     # rows beyond the last offset stay unused
+    x = (torch.randn(cap, K, device="cuda") * 0.7).bfloat16()
+    x[768:] = 0
+    w = (torch.randn(E, K, N, device="cuda") * 0.05).bfloat16()
+    xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    assert moe_ops.mxfp8_grouped_path(xa, wa)
+    y = moe_ops.grouped_padded(xa, wa, off, None, True)
+    dy = (torch.randn_like(y.float()) * 0.3).bfloat16()
+    dy[768:] = 0
+    y.backward(dy)
+    torch.cuda.synchronize()
+    check_status()
+    xq = _mx_qdq(x)                                  # activations: blocks along K
+    wq_fwd = _mx_qdq(w.transpose(1, 2)).transpose(1, 2)   # weights for the forward: blocks along K
+    wq_bwd = _mx_qdq(w)                              # weights for the data gradient: blocks along N
+    dyq = _mx_qdq(dy)
+    ref_y = torch.zeros(cap, N, device="cuda")
+    ref_dx = torch.zeros(cap, K, device="cuda")
+    ref_dw = torch.zeros(E, K, N, device="cuda")
+    for e in range(E):
+        a, b = int(off[e]), int(off[e + 1])
+        ref_y[a:b] = xq[a:b] @ wq_fwd[e]
+        ref_dx[a:b] = dyq[a:b] @ wq_bwd[e].t()
+        ref_dw[e] = x[a:b].float().t() @ dy[a:b].float()
+    rel = lambda g, r: ((g.float() - r).norm() / (r.norm() + 1e-9)).item()
+    assert rel(y[:768], ref_y[:768]) < 1e-2, rel(y[:768], ref_y[:768])
+    assert rel(xa.grad[:768], ref_dx[:768]) < 1e-2, rel(xa.grad[:768], ref_dx[:768])
+    assert rel(wa.grad, ref_dw) < 1e-2, rel(wa.grad, ref_dw)
+    # and close to the unquantised bf16 path (quantisation noise only)
+    yb = moe_ops.grouped_padded(x, w, off, None, False)
+    assert rel(y[:768], yb[:768].float()) < 6e-2
+
+
+def test_experts_forward_with_fp8_tracks_the_bf16_path():
+    from mintext_b200.ops import moe as moe_ops
+
+    torch.manual_seed(1)
+    n_tok, E, K, D, I = 512, 8, 2, 256, 128
+    x = torch.randn(n_tok, D, device="cuda", dtype=torch.bfloat16)
+    idx = torch.randint(0, E, (n_tok, K), device="cuda")
+    wts = torch.rand(n_tok, K, device="cuda")
+    gu = (torch.randn(E, D, 2 * I, device="cuda") * 0.05).bfloat16()
+    dn = (torch.randn(E, I, D, device="cuda") * 0.05).bfloat16()
+    a = moe_ops.experts_forward(x, idx, wts, gu, dn, "silu", fp8=False).float()
+    b = moe_ops.experts_forward(x, idx, wts, gu, dn, "silu", fp8=True).float()
+    assert ((a - b).norm() / a.norm()).item() < 8e-2

@@ -140,3 +140,53 @@ def test_tensor_parallel_with_replicated_mla_and_experts():
 
 def test_tensor_parallel_with_replicated_gdn_experts_and_aux_loss():
     _check_mixed("qwen3_next", _qwen3_next_worker, 29635)
+
+
+def _mla_cfg():
+    return MinTextConfig(dtype="float32", vocab_size=64, num_hidden_layers=2, hidden_size=32, num_attention_heads=4,
+                         intermediate_size=64, seq_length=16, model_type="deepseek_v3", attention_type="mla",
+                         q_lora_rank=16, kv_lora_rank=16, qk_nope_head_dim=8, qk_rope_head_dim=4, v_head_dim=8)
+
+
+def _mla_tp_worker(rank, world):
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.tp import TensorParallel, set_current_tp
+
+    set_current_tp(TensorParallel(dist.group.WORLD, torch.device("cpu"), fused=False))
+    try:
+        cfg = _mla_cfg()
+        m = Transformer(cfg, rngs=0)
+        att = m.layers[0].attention
+        assert att.q_b_proj.kernel.shape == (16, 2, 12) and att.kv_b_proj.kernel.shape == (16, 2, 16)
+        assert att.out.kernel.shape == (2, 8, 32) and att.q_a_proj.kernel.shape == (32, 16)
+        assert not getattr(att.q_a_proj.kernel, "tp_replicated_compute", False)
+        loss, _ = trainer.compute_loss(None, m, cfg, _batch())
+        names = [n for n, _ in m.named_parameters()]
+        grads = torch.autograd.grad(loss, list(m.parameters()))
+        return float(loss), {n: g.clone() for n, g in zip(names, grads)}
+    finally:
+        set_current_tp(None)
+
+
+def test_head_sharded_mla_matches_single_process():
+    """Multi-head-latent attention with its heads split over two ranks: the loss and every gradient equal the
+    single-process model's (whole low-rank projections collect partial sums, one per rank's heads)."""
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+
+    world = 2
+    res = run_ranks(_mla_tp_worker, world, 29633)
+    cfg = _mla_cfg()
+    m = Transformer(cfg, rngs=0)
+    loss, _ = trainer.compute_loss(None, m, cfg, _batch())
+    ref = dict(zip([n for n, _ in m.named_parameters()], torch.autograd.grad(loss, list(m.parameters()))))
+    assert abs(sum(res[r][0] for r in range(world)) / world - float(loss)) < 1e-5
+    for name, g in ref.items():
+        parts = [res[r][1][name] for r in range(world)]
+        if parts[0].shape == g.shape:
+            got = sum(parts) / world
+        else:
+            dim = next(i for i, (a, b) in enumerate(zip(parts[0].shape, g.shape)) if a != b)
+            got = torch.cat(parts, dim=dim) / world
+        assert torch.allclose(got, g, atol=2e-5), name
