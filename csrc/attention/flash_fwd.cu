@@ -77,9 +77,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* v_empty = bars + 7;   // [2]
   uint64_t* s_full = bars + 9;    // [2]  scores of a block are in buffer b
   uint64_t* p_full = bars + 11;   // [2]  probabilities of a block are in buffer b (four warp arrivals)
-  uint64_t* pv_done = bars + 13;  //      O holds every block up to the committed one
+  uint64_t* pv_done = bars + 13;  //      O holds every block up to the committed one (one phase per block)
   uint64_t* o_staged = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* o_final = bars + 15;  //      the last block's second MMA has completed (single phase)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -118,6 +119,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     mbar_init(pv_done, 1);
     mbar_init(o_staged, 4);
+    mbar_init(o_final, 1);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&tmQ);
@@ -209,6 +211,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         make_smem_desc_sw128(v_addr + k * (16 * 128), BN * 128, 1024), idesc_pv, (i | k) != 0 ? 1u : 0u);
         tc_commit(&v_empty[s]);
         tc_commit(pv_done);
+        if (i == n_blocks - 1) tc_commit(o_final);
         // the tensor pipe executes in issue order: the scores of block i+2 overwrite buffer s only after P(i) was read
         if (i + 2 < n_blocks) ok = issue_qk(i + 2);
       }
@@ -269,7 +272,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
           // O must hold every earlier block before it is rescaled; the second MMA of THIS block cannot start before
-          // this warp has arrived on p_full, so the accumulator is quiet in between
+          // this warp has arrived on p_full, so the accumulator is quiet in between.  The parity wait is sound here:
+          // the scores of block i were issued behind the second MMA of block i-2, so at this point pv_done has
+          // completed i-1 or i phases, never fewer (a waiter two phases behind would read a stale parity).
           if (!mbar_wait_warp(pv_done, (i - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL)) return false;
           tc_fence_after_sync();
 #pragma unroll
@@ -326,9 +331,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0) mbar_arrive(&p_full[i & 1]);
     }
     // epilogue: O / l -> bf16 -> staging (the Q tile: every score MMA has completed by now) -> TMA store ; lse
-    if (ok && n_blocks > 0) {
-      ok = mbar_wait_warp(pv_done, (n_blocks - 1) & 1, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL);
-    }
+    // (its own single-phase barrier: after the last softmax block pv_done may still be two phases short, where a
+    // parity wait would pass on the stale phase)
+    if (ok && n_blocks > 0) ok = mbar_wait_warp(o_final, 0, abort_flag, args.status, MT_ERR_TIMEOUT_TMEM_FULL);
     if (ok) {
       tc_fence_after_sync();
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
