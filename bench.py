@@ -156,6 +156,9 @@ def main() -> None:
     ap.add_argument("--micro-batch", type=int, default=None)
     ap.add_argument("--set", nargs="*", default=[], metavar="KEY=VALUE", help="config overrides (not for llama1b)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--profile-out", default=None, metavar="FILE",
+                    help="after the measurement, run one more step under torch.profiler and write rank 0's "
+                         "per-kernel time shares to FILE (outside every timed region)")
     ap.add_argument("--fp8-mlp", action="store_true",
                     help="side measurement, not the headline: MLP projections through the FP8 GEMM (per-tensor scales)")
     ap.add_argument("--fp8-recipe", choices=("per_tensor", "mx_block"), default="per_tensor",
@@ -331,6 +334,15 @@ def main() -> None:
             "gpu_launches": int(n_launches) if args.impl == "own" else 0,
         }
         print(json.dumps(line))
+    if args.profile_out:
+        from mintext_b200.utils.profiling import kernel_share_table
+
+        text = kernel_share_table(lambda: step_device(0), header=f"model={args.model} gpus={world} global_batch="
+                                  f"{args.global_batch} micro_batch={args.micro_batch} n_micro={n_micro} "
+                                  f"plain step {ms_per_step:.1f} ms")
+        if rank == 0:
+            Path(args.profile_out).parent.mkdir(parents=True, exist_ok=True)
+            Path(args.profile_out).write_text(text + "\n")
     if world > 1:
         dist.destroy_process_group()
 

@@ -100,6 +100,10 @@ struct PeerPtrs {
   void* p[kMaxPeers];
 };
 void symm_barrier(const PeerPtrs& flags, int rank, int world, int seq, int* status, cudaStream_t stream);
+// dst[r * n_bytes + i] = shards[r][lo_bytes + i] for every rank r (byte offsets / sizes, multiples of 16): the
+// parameter all-gather of the parameter-sharded engine mode, by plain peer loads
+void peer_gather(const PeerPtrs& shards, int world, int64_t lo_bytes, int64_t n_bytes, void* dst, int blocks,
+                 cudaStream_t stream);
 // out[0..n) = sum over ranks of grads[r][lo..lo+n) ; *sumsq += |out|^2   (n multiple of 4, lo multiple of 4)
 void grad_pull_reduce(const PeerPtrs& grads, int rank, int world, int64_t lo, int64_t n, float* out, float* sumsq,
                       cudaStream_t stream);
@@ -192,6 +196,23 @@ void gdn_scan_fwd(const float* W, const float* U, const float* QG, const float* 
 void gdn_scan_bwd(const float* W, const float* U, const float* QG, const float* M, const float* KD, const float* GL,
                   const float* Sstart, const float* dO, float* dW, float* dU, float* dQG, float* dM, float* dKD,
                   float* dGL, int BH, int C, int dk, int dv, cudaStream_t stream);
+
+// ---- gdn/gdn_prep.cu: chunk-parallel stage of the chunked Gated Delta Rule (fp32, chunk length 64): from raw
+// q, k [B,H,S,dk], v [B,H,S,dv], beta, g [B,H,S] (any batch / head / token strides, unit inner stride, 16-byte aligned
+// rows) to the scan operands W, QG, KD [B*H, C, 64, dk], U [B*H, C, 64, dv], M, T [B*H, C, 64, 64], GL [B*H, C] with
+// C = ceil(S / 64); the backward takes the operand gradients to dq, dk [B,H,S,dk], dv [B,H,S,dv], dbeta, dg [B,H,S].
+struct GdnStrided {
+  const float* p;
+  int64_t sb, sh, ss;  // element strides of the batch, head and token axes
+};
+bool gdn_prep_supported(int dk, int dv);
+void gdn_prep_fwd(const GdnStrided& q, const GdnStrided& k, const GdnStrided& v, const GdnStrided& beta, const GdnStrided& g,
+                  float* W, float* U, float* QG, float* M, float* KD, float* GL, float* T, int B, int H, int S, int dk, int dv,
+                  cudaStream_t stream);
+void gdn_prep_bwd(const GdnStrided& q, const GdnStrided& k, const GdnStrided& v, const GdnStrided& beta, const GdnStrided& g,
+                  const float* T, const float* dW, const float* dU, const float* dQG, const float* dM, const float* dKD,
+                  const float* dGL, float* dq, float* dk, float* dv_, float* dbeta, float* dg, int B, int H, int S, int dk_dim,
+                  int dv, cudaStream_t stream);
 
 // ---- moe/route.cu
 void router_sigmoid_group(const void* logits, bool logits_bf16, const float* bias, float* scores, int64_t* topk_idx,

@@ -288,6 +288,15 @@ void grad_pull_bucket(const std::vector<int64_t>& grad_ptrs, const std::vector<i
 
 int64_t bucket_flag_slots() { return mt::kBucketSlots; }
 
+// dst (flat, world * n elements) <- slice [lo, lo + n) of every rank's shard buffer, rank by rank
+void peer_gather(const std::vector<int64_t>& shard_ptrs, int64_t lo, int64_t n, torch::Tensor& dst, int64_t blocks) {
+  const int64_t es = dst.element_size();
+  TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && dst.numel() == n * (int64_t)shard_ptrs.size());
+  TORCH_CHECK((lo * es) % 16 == 0 && (n * es) % 16 == 0 && reinterpret_cast<uintptr_t>(dst.data_ptr()) % 16 == 0);
+  c10::cuda::CUDAGuard guard(dst.device());
+  mt::peer_gather(to_peers(shard_ptrs), (int)shard_ptrs.size(), lo * es, n * es, dst.data_ptr(), (int)blocks, cur_stream());
+}
+
 void adamw_publish(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, const torch::Tensor& grad,
                    const std::vector<int64_t>& param_ptrs, int64_t lo, double lr, double b1, double b2, double eps,
                    double wd, double bc1, double bc2, double grad_scale, const c10::optional<torch::Tensor>& clip_coef) {
@@ -555,6 +564,54 @@ std::vector<torch::Tensor> gdn_scan_bwd(const torch::Tensor& W, const torch::Ten
   return {dW, dU, dQG, dM, dKD, dGL};
 }
 
+static mt::GdnStrided gdn_strided(const torch::Tensor& t, bool rows) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.dim() == (rows ? 4 : 3), "gdn_prep wants fp32 [B,H,S(,d)]");
+  if (rows)
+    TORCH_CHECK(t.stride(3) == 1 && t.stride(0) % 4 == 0 && t.stride(1) % 4 == 0 && t.stride(2) % 4 == 0 &&
+                    reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0,
+                "gdn_prep wants unit inner stride and 16-byte aligned rows");
+  return {t.data_ptr<float>(), t.stride(0), t.stride(1), t.stride(2)};
+}
+
+// q, k [B,H,S,dk], v [B,H,S,dv], beta, g [B,H,S] (strided views allowed) -> (W, U, QG, M, KD, GL, T)
+std::vector<torch::Tensor> gdn_prep_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v,
+                                        const torch::Tensor& beta, const torch::Tensor& g) {
+  const int64_t B = q.size(0), H = q.size(1), S = q.size(2), dk = q.size(3), dv = v.size(3), C = (S + 63) / 64;
+  TORCH_CHECK(k.sizes() == q.sizes() && v.size(0) == B && v.size(1) == H && v.size(2) == S && beta.size(2) == S &&
+              g.size(2) == S && mt::gdn_prep_supported((int)dk, (int)dv));
+  c10::cuda::CUDAGuard guard(q.device());
+  auto o = q.options();
+  auto W = torch::empty({B * H, C, 64, dk}, o), QG = torch::empty({B * H, C, 64, dk}, o), KD = torch::empty({B * H, C, 64, dk}, o);
+  auto U = torch::empty({B * H, C, 64, dv}, o), M = torch::empty({B * H, C, 64, 64}, o), T = torch::empty({B * H, C, 64, 64}, o);
+  auto GL = torch::empty({B * H, C}, o);
+  mt::gdn_prep_fwd(gdn_strided(q, true), gdn_strided(k, true), gdn_strided(v, true), gdn_strided(beta, false),
+                   gdn_strided(g, false), W.data_ptr<float>(), U.data_ptr<float>(), QG.data_ptr<float>(), M.data_ptr<float>(),
+                   KD.data_ptr<float>(), GL.data_ptr<float>(), T.data_ptr<float>(), (int)B, (int)H, (int)S, (int)dk, (int)dv,
+                   cur_stream());
+  return {W, U, QG, M, KD, GL, T};
+}
+
+// -> (dq, dk, dv, dbeta, dg), contiguous [B,H,S,...]
+std::vector<torch::Tensor> gdn_prep_bwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v,
+                                        const torch::Tensor& beta, const torch::Tensor& g, const torch::Tensor& T,
+                                        const torch::Tensor& dW, const torch::Tensor& dU, const torch::Tensor& dQG,
+                                        const torch::Tensor& dM, const torch::Tensor& dKD, const torch::Tensor& dGL) {
+  const int64_t B = q.size(0), H = q.size(1), S = q.size(2), dk = q.size(3), dv = v.size(3);
+  for (const auto* t : {&T, &dW, &dU, &dQG, &dM, &dKD, &dGL})
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == torch::kFloat32, "gdn_prep_bwd wants contiguous fp32");
+  TORCH_CHECK(mt::gdn_prep_supported((int)dk, (int)dv) && dW.size(0) == B * H && dW.size(3) == dk && dU.size(3) == dv);
+  c10::cuda::CUDAGuard guard(q.device());
+  auto o = q.options();
+  auto dq = torch::empty({B, H, S, dk}, o), dkk = torch::empty({B, H, S, dk}, o), dvv = torch::empty({B, H, S, dv}, o);
+  auto dbeta = torch::empty({B, H, S}, o), dg = torch::empty({B, H, S}, o);
+  mt::gdn_prep_bwd(gdn_strided(q, true), gdn_strided(k, true), gdn_strided(v, true), gdn_strided(beta, false),
+                   gdn_strided(g, false), T.data_ptr<float>(), dW.data_ptr<float>(), dU.data_ptr<float>(),
+                   dQG.data_ptr<float>(), dM.data_ptr<float>(), dKD.data_ptr<float>(), dGL.data_ptr<float>(),
+                   dq.data_ptr<float>(), dkk.data_ptr<float>(), dvv.data_ptr<float>(), dbeta.data_ptr<float>(),
+                   dg.data_ptr<float>(), (int)B, (int)H, (int)S, (int)dk, (int)dv, cur_stream());
+  return {dq, dkk, dvv, dbeta, dg};
+}
+
 torch::Tensor conv1d_silu_fwd(const torch::Tensor& x, const torch::Tensor& w) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 3 && x.scalar_type() == torch::kBFloat16);
   TORCH_CHECK(w.is_contiguous() && w.scalar_type() == torch::kBFloat16 && w.numel() % x.size(2) == 0);
@@ -818,6 +875,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grad_pull_reduce", &grad_pull_reduce);
   m.def("grad_pull_bucket", &grad_pull_bucket);
   m.def("bucket_flag_slots", &bucket_flag_slots);
+  m.def("peer_gather", &peer_gather);
   m.def("adamw_publish", &adamw_publish);
   m.def("set_grouped_variant", [](int64_t v) { mt::set_grouped_variant((int)v); });
   m.def("grouped_gemm", &grouped_gemm);
@@ -837,6 +895,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm_mxfp8", &grouped_gemm_mxfp8);
   m.def("gdn_scan_fwd", &gdn_scan_fwd);
   m.def("gdn_scan_bwd", &gdn_scan_bwd);
+  m.def("gdn_prep_fwd", &gdn_prep_fwd);
+  m.def("gdn_prep_bwd", &gdn_prep_bwd);
   m.def("conv1d_silu_fwd", &conv1d_silu_fwd);
   m.def("conv1d_silu_bwd", &conv1d_silu_bwd);
   m.def("moe_router", &moe_router);

@@ -233,6 +233,9 @@ class MinTextConfig(BaseModel):
     nan_policy: str = "ignore"
     logical_axis_rules: list[tuple[str, str | None]] = []
     fused_collectives: bool = True  # peer-memory kernels for the sharded optimizer step; False: NCCL composition
+    # layer weights and layer gradients sharded 1/N over data x fsdp (gathered one layer ahead, reduce-scattered per
+    # layer) instead of resident on every rank: parallel/fsdp.py
+    fsdp_shard_params: bool = False
 
     # checkpoints
     enable_checkpointing: bool = True

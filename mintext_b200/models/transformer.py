@@ -53,7 +53,20 @@ def set_backward_layer_hook(fn) -> None:
     _BACKWARD_LAYER_HOOK = fn
 
 
+_FORWARD_LAYER_HOOK = None
+
+
+def set_forward_layer_hook(fn) -> None:
+    """Install (or clear, with None) a callback ``fn(layer_index)`` that every forward pass calls right before it
+    enters a decoder layer.  The parameter-sharded engine mode uses it to make sure the layer's gathered weights
+    have arrived and to start the gather of the next layer."""
+    global _FORWARD_LAYER_HOOK
+    _FORWARD_LAYER_HOOK = fn
+
+
 def _arm_layer_hook(x: torch.Tensor, layer_index: int) -> None:
+    if _FORWARD_LAYER_HOOK is not None:
+        _FORWARD_LAYER_HOOK(layer_index)
     if _BACKWARD_LAYER_HOOK is None or not (torch.is_grad_enabled() and x.requires_grad):
         return
 

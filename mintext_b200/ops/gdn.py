@@ -1,13 +1,17 @@
 """CUDA path of the chunked Gated Delta Rule (reference: mintext/modules/linear_attention.py:49-205).
 
-The chunk-parallel part (L2 normalisation, decay matrices, the unit-lower-triangular WY inverse, the per-chunk
-operands) is batched tensor algebra over all chunks at once and stays in PyTorch; the sequential walk over the chunks
-with the ``[dk, dv]`` state, which the plain implementation runs as a Python loop of small matmuls, is one kernel
-forward and one backward (``csrc/gdn/gdn_scan.cu``): the state slice of 32 value columns lives in shared memory for
-the whole sequence and the per-chunk operands are staged once.
+Two kernels each way.  The chunk-parallel part (L2 normalisation, decay matrices, the unit-lower-triangular WY
+inverse, the per-chunk operands) is one CTA per (batch, head, chunk) working in shared memory
+(``csrc/gdn/gdn_prep.cu``; its backward takes the operand gradients back to q, k, v, beta, g).  The sequential walk over
+the chunks with the ``[dk, dv]`` state, which the plain implementation runs as a Python loop of small matmuls, is
+``csrc/gdn/gdn_scan.cu``: the state slice of 32 value columns lives in shared memory for the whole sequence and the
+per-chunk operands are staged once.  Value head dims above 128 keep the chunk-parallel part as batched tensor algebra
+(``MT_GDN_PREP=torch`` selects that path everywhere).
 """
 
 from __future__ import annotations
+
+import os
 
 import torch
 import torch.nn.functional as TF
@@ -44,8 +48,39 @@ class _ScanFn(torch.autograd.Function):
         return dW, dU, dQG, dM, dKD, dGL
 
 
-def chunk_gated_delta_rule_cuda(q, k, v, beta, g, chunk_size: int = _L) -> torch.Tensor:
-    """q,k ``[B,H,S,dk]``, v ``[B,H,S,dv]``, beta,g ``[B,H,S]`` -> ``[B,H,S,dv]`` (fp32)."""
+def prep_kernel_path(dk: int, dv: int) -> bool:
+    """True when the chunk-parallel stage runs as the ``gdn_prep`` kernels."""
+    return (os.environ.get("MT_GDN_PREP", "kernel") != "torch" and hasattr(ext(), "gdn_prep_fwd")
+            and dk in (64, 128) and dv % 32 == 0 and 0 < dv <= 128)
+
+
+def _rows_ok(t: torch.Tensor) -> torch.Tensor:
+    """The kernels read rows as 16-byte vectors through arbitrary batch / head / token strides."""
+    if t.stride(-1) == 1 and all(s % 4 == 0 for s in t.stride()[:-1]) and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
+
+
+class _PrepFn(torch.autograd.Function):
+    """Raw ``q, k, v, beta, g`` -> the scan operands ``W, U, QG, M, KD, GL`` (``[B*H, C, 64, ...]``)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, beta, g):
+        q, k, v = _rows_ok(q), _rows_ok(k), _rows_ok(v)
+        W, U, QG, M, KD, GL, T = ext().gdn_prep_fwd(q, k, v, beta, g)
+        ctx.save_for_backward(q, k, v, beta, g, T)
+        return W, U, QG, M, KD, GL
+
+    @staticmethod
+    def backward(ctx, dW, dU, dQG, dM, dKD, dGL):
+        q, k, v, beta, g, T = ctx.saved_tensors
+        grads = [t.contiguous() for t in (dW, dU, dQG, dM, dKD, dGL)]
+        return tuple(ext().gdn_prep_bwd(q, k, v, beta, g, T, *grads))
+
+
+def prep_torch(q, k, v, beta, g, chunk_size: int = _L):
+    """The chunk-parallel stage as batched tensor algebra (one triangular solve for the WY inverse): the scan operands
+    ``W, U, QG, M, KD, GL`` of :class:`_ScanFn`.  Fallback for shapes the kernel does not cover, and its test oracle."""
     B, H, S, dk = q.shape
     dv = v.shape[-1]
     L = chunk_size
@@ -78,6 +113,18 @@ def chunk_gated_delta_rule_cuda(q, k, v, beta, g, chunk_size: int = _L) -> torch
     KD = k * k_decay[..., None]
     GL = g_exp[..., -1]
     BH = B * H
-    O = _ScanFn.apply(W.reshape(BH, C, L, dk), U.reshape(BH, C, L, dv), QG.reshape(BH, C, L, dk), M.reshape(BH, C, L, L),
-                      KD.reshape(BH, C, L, dk), GL.reshape(BH, C))
-    return O.reshape(B, H, C * L, dv)[:, :, :S]
+    return (W.reshape(BH, C, L, dk), U.reshape(BH, C, L, dv), QG.reshape(BH, C, L, dk), M.reshape(BH, C, L, L),
+            KD.reshape(BH, C, L, dk), GL.reshape(BH, C))
+
+
+def chunk_gated_delta_rule_cuda(q, k, v, beta, g, chunk_size: int = _L) -> torch.Tensor:
+    """q,k ``[B,H,S,dk]``, v ``[B,H,S,dv]``, beta,g ``[B,H,S]`` -> ``[B,H,S,dv]`` (fp32)."""
+    B, H, S, dk = q.shape
+    dv = v.shape[-1]
+    L = chunk_size
+    if prep_kernel_path(dk, dv):
+        W, U, QG, M, KD, GL = _PrepFn.apply(q.float(), k.float(), v.float(), beta.float(), g.float())
+        O = _ScanFn.apply(W, U, QG, M, KD, GL)
+        return O.reshape(B, H, -1, dv)[:, :, :S]
+    O = _ScanFn.apply(*prep_torch(q, k, v, beta, g, L))
+    return O.reshape(B, H, -1, dv)[:, :, :S]

@@ -113,7 +113,7 @@ class TrainEngine:
         self._build_storage()
         self.use_fused = bool(config.fused_collectives) and self.world > 1 and config.optimizer == "adamw"
         self._comm = None
-        if self.use_fused:
+        if self.use_fused and self._use_symmetric_optimizer_comm():
             try:
                 from mintext_b200.parallel.symm import SymmetricOptimizerComm
 
@@ -132,6 +132,11 @@ class TrainEngine:
         self._late: set[int] = set()     # ... and that received further gradients afterwards
         self._slots_of_bucket = None
         self._has_tp_replicated = None
+
+    sharded_params = False  # True in the subclass that shards layer weights and gradients (parallel/fsdp.py)
+
+    def _use_symmetric_optimizer_comm(self) -> bool:
+        return True
 
     # ------------------------------------------------------------------ storage
     def _build_storage(self) -> None:
@@ -186,27 +191,7 @@ class TrainEngine:
         self.buckets = buckets
         self._bucket_index = {bid: i for i, (bid, _, _) in enumerate(buckets)}
 
-        # fp32 master values come from the model's initialisation.  Parameters are consumed one at a time (they may
-        # already live on the device): the bf16 compute copy and this rank's slice of the fp32 master are filled
-        # from a parameter, then its own storage is released by re-pointing it at the flat buffer.
-        self.param_flat = self._alloc_symmetric(total_b, torch.bfloat16)
-        self.param_flat.zero_()
-        self.grad_flat = self._alloc_symmetric(total_b, torch.float32)
-        self.grad_flat.zero_()
-        self.master = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
-        self.exp_avg = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
-        self.exp_avg_sq = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
-        self.grad_shard = torch.empty(self.shard_size, device=dev, dtype=torch.float32)
-        # per-element weight decay is uniform over the big group (only the router bias is exempt and it is frozen)
-        for s in big:
-            src = s.param.detach().reshape(-1)
-            self.param_flat[s.offset:s.offset + s.numel].copy_(src)
-            for a, b, loc in self._overlaps(s.offset, s.offset + s.numel):
-                self.master[loc:loc + (b - a)].copy_(src[a - s.offset:b - s.offset])
-            del src
-            s.param.data = self.param_flat[s.offset:s.offset + s.numel].view(s.param.shape)
-            s.param.main_grad = self.grad_flat[s.offset:s.offset + s.numel].view(s.param.shape)
-            s.bucket = self._bucket_index.get(bucket_of(s.name), 0) if len(buckets) > 1 else 0
+        self._alloc_sharded_group(big, buckets, total_b)
 
         # expert-parallel parameters: every rank owns its experts outright (compute copy, master, moments, grads)
         self.exp = FlatGroup(exp, _round_up(max(off_e, 4), _ALIGN))
@@ -240,6 +225,32 @@ class TrainEngine:
         for s in small:
             if not weight_decay_mask(s.name):
                 self.small_wd[s.offset:s.offset + s.numel] = 0.0
+
+    def _alloc_sharded_group(self, big: list, buckets: list, total_b: int) -> None:
+        """Device storage of the sharded group: resident bf16 compute copy and fp32 gradient accumulator (full, flat),
+        fp32 master / moments / reduced gradient (this rank's slices)."""
+        dev = self.device
+        # fp32 master values come from the model's initialisation.  Parameters are consumed one at a time (they may
+        # already live on the device): the bf16 compute copy and this rank's slice of the fp32 master are filled
+        # from a parameter, then its own storage is released by re-pointing it at the flat buffer.
+        self.param_flat = self._alloc_symmetric(total_b, torch.bfloat16)
+        self.param_flat.zero_()
+        self.grad_flat = self._alloc_symmetric(total_b, torch.float32)
+        self.grad_flat.zero_()
+        self.master = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
+        self.exp_avg = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
+        self.exp_avg_sq = torch.zeros(self.shard_size, device=dev, dtype=torch.float32)
+        self.grad_shard = torch.empty(self.shard_size, device=dev, dtype=torch.float32)
+        # per-element weight decay is uniform over the big group (only the router bias is exempt and it is frozen)
+        for s in big:
+            src = s.param.detach().reshape(-1)
+            self.param_flat[s.offset:s.offset + s.numel].copy_(src)
+            for a, b, loc in self._overlaps(s.offset, s.offset + s.numel):
+                self.master[loc:loc + (b - a)].copy_(src[a - s.offset:b - s.offset])
+            del src
+            s.param.data = self.param_flat[s.offset:s.offset + s.numel].view(s.param.shape)
+            s.param.main_grad = self.grad_flat[s.offset:s.offset + s.numel].view(s.param.shape)
+            s.bucket = self._bucket_index.get(bucket_of(s.name), 0) if len(buckets) > 1 else 0
 
     def _overlaps(self, lo: int, hi: int):
         """Parts of the flat range ``[lo, hi)`` that this rank's shard holds: ``(flat_a, flat_b, local offset)``."""
@@ -368,6 +379,34 @@ class TrainEngine:
         self._comm.pull_bucket_async(b)
         self._pulled.add(b)
 
+    def _reduce_sharded_group(self) -> None:
+        """``grad_shard`` <- this rank's slices of the gradients summed over all ranks."""
+        W = self.world
+        if self.use_fused and len(self.buckets) > 1:
+            self._comm.finish_bucket_pulls(self._pulled, self._late)
+            self._pulled, self._late = set(), set()
+            self._flat_cleared_by_pull = True
+        elif self.use_fused:
+            self._comm.reduce_scatter_grads(self.grad_shard)
+        else:
+            for (_, boff, blen), (_, _, _, loc) in zip(self.buckets, self.segments):
+                dist.reduce_scatter_tensor(self.grad_shard[loc:loc + blen // W], self.grad_flat[boff:boff + blen],
+                                           group=self.group)
+
+    def _update_sharded_group(self, gshard: torch.Tensor, lr: float, bc1: float, bc2: float, inv: float) -> None:
+        """AdamW on this rank's slices and publication of the updated bf16 values to every rank (multi-rank runs)."""
+        cfg = self.config
+        e = ext()
+        if self.use_fused:
+            self._comm.adamw_and_publish(gshard, lr, bc1, bc2, inv, self._clip)
+            return
+        for (_, boff, blen), (_, a, b, loc) in zip(self.buckets, self.segments):
+            sl = slice(loc, loc + (b - a))
+            pslice = self.param_flat[a:b]
+            e.adamw_step(self.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], gshard[sl], pslice, lr, cfg.adam_b1,
+                         cfg.adam_b2, cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)
+            dist.all_gather_into_tensor(self.param_flat[boff:boff + blen], pslice, group=self.group)
+
     def optimizer_step(self, num_micro: int = 1) -> dict:
         """Reduce gradients, clip, update, re-publish bf16 weights.  Returns device scalars."""
         cfg = self.config
@@ -392,16 +431,7 @@ class TrainEngine:
                         s.param.main_grad.mul_(1.0 / tp.size)
         # 1. gradient reduction
         if W > 1:
-            if self.use_fused and len(self.buckets) > 1:
-                self._comm.finish_bucket_pulls(self._pulled, self._late)
-                self._pulled, self._late = set(), set()
-                self._flat_cleared_by_pull = True
-            elif self.use_fused:
-                self._comm.reduce_scatter_grads(self.grad_shard)
-            else:
-                for (_, boff, blen), (_, _, _, loc) in zip(self.buckets, self.segments):
-                    dist.reduce_scatter_tensor(self.grad_shard[loc:loc + blen // W], self.grad_flat[boff:boff + blen],
-                                               group=self.group)
+            self._reduce_sharded_group()
             dist.all_reduce(self.small_grad, group=self.group)
             gshard = self.grad_shard
         else:
@@ -436,15 +466,8 @@ class TrainEngine:
                              gshard, pshard, lr, bc1, bc2, inv, t)
             if W > 1:
                 dist.all_gather_into_tensor(self.param_flat, pshard, group=self.group)
-        elif W > 1 and self.use_fused:
-            self._comm.adamw_and_publish(gshard, lr, bc1, bc2, inv, self._clip)
         elif W > 1:
-            for (_, boff, blen), (_, a, b, loc) in zip(self.buckets, self.segments):
-                sl = slice(loc, loc + (b - a))
-                pslice = self.param_flat[a:b]
-                e.adamw_step(self.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], gshard[sl], pslice, lr, cfg.adam_b1,
-                             cfg.adam_b2, cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)
-                dist.all_gather_into_tensor(self.param_flat[boff:boff + blen], pslice, group=self.group)
+            self._update_sharded_group(gshard, lr, bc1, bc2, inv)
         else:
             e.adamw_step(self.master, self.exp_avg, self.exp_avg_sq, gshard, self.param_flat, lr, cfg.adam_b1,
                          cfg.adam_b2, cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)

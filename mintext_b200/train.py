@@ -129,9 +129,11 @@ def setup_training(config: MinTextConfig):
     init_device = device if (use_gpu and _device_init_wanted(config)) else None
     model = create_sharded_model(config, mesh, init_device=init_device)
     if use_gpu:
-        from mintext_b200.parallel.engine import TrainEngine
-
-        state = TrainEngine(model, config, device=device, local_reduce_group=local_reduce_group)
+        if config.fsdp_shard_params:
+            from mintext_b200.parallel.fsdp import ParamShardedEngine as Engine
+        else:
+            from mintext_b200.parallel.engine import TrainEngine as Engine
+        state = Engine(model, config, device=device, local_reduce_group=local_reduce_group)
     else:
         from mintext_b200 import trainer
 

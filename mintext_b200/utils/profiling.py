@@ -82,3 +82,35 @@ class Profiler:
         global _NVTX
         _NVTX = False
         logger.info("Profiler stopped")
+
+
+def kernel_share_table(step_fn, header: str = "", top: int = 40) -> str:
+    """Run ``step_fn()`` once under ``torch.profiler`` and return a text table of the device kernels by total time
+    (calls, milliseconds, share of the summed kernel time).  Times taken under the profiler are for shares only."""
+    import time
+    from collections import defaultdict
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+        t0 = time.time()
+        step_fn()
+        host_ms = (time.time() - t0) * 1e3
+        torch.cuda.synchronize()
+        wall_ms = (time.time() - t0) * 1e3
+    agg = defaultdict(lambda: [0, 0.0])
+    for ev in prof.events():
+        if ev.device_type == torch.autograd.DeviceType.CUDA:
+            a = agg[ev.name]
+            a[0] += 1
+            a[1] += ev.device_time
+    total = sum(v[1] for v in agg.values()) or 1.0
+    lines = [header] if header else []
+    lines.append(f"under profiler: wall {wall_ms:.1f} ms, host issue time {host_ms:.1f} ms, sum of kernel time "
+                 f"{total / 1e3:.1f} ms, launches {sum(v[0] for v in agg.values())}")
+    lines.append(f"{'kernel':90s} {'calls':>6s} {'ms':>9s} {'share':>7s}")
+    for name, (n, us) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:top]:
+        lines.append(f"{name[:90]:90s} {n:6d} {us / 1e3:9.2f} {us / total * 100:6.1f}%")
+    return "\n".join(lines)

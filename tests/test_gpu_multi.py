@@ -206,3 +206,32 @@ def test_checkpoint_saved_on_two_gpus_restores_on_one(tmp_path, optimizer):
     eng.check()
     for a, b in zip(got, res["after"]):
         assert abs(a - b) < 2e-2, (got, res["after"])
+
+
+def test_parameter_sharded_mode_matches_resident_mode(tmp_path):
+    """Layer weights and layer gradients sharded 1/N (gathered one layer ahead, reduce-scattered per layer) train
+    like the resident mode: same losses, gradient norms and final master weights, with one and two micro-batches per
+    step and under full rematerialisation."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    out = tmp_path / "fsdp.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29681", str(ROOT / "tests" / "multi_gpu_fsdp_worker.py"),
+           str(out)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.loads(out.read_text())
+    for case, runs in res.items():
+        a, b = runs["resident"], runs["sharded"]
+        for x, y in zip(a["losses"], b["losses"]):
+            assert abs(x - y) < 2e-3, (case, a["losses"], b["losses"])
+        for x, y in zip(a["grad_norms"], b["grad_norms"]):
+            assert abs(x - y) < 2e-3 * max(1.0, abs(x)), (case, a["grad_norms"], b["grad_norms"])
+        assert abs(a["eval_loss"] - b["eval_loss"]) < 2e-3, case
+        # Adam turns a reordered sum of near-zero gradients into a full-size step for single elements: bound the mean
+        # tightly and the maximum by the five steps' learning rate
+        assert runs["mean_master_diff"] < 2e-5, (case, runs["mean_master_diff"])
+        assert runs["max_master_diff"] < 6e-3, (case, runs["max_master_diff"])
+        assert a["losses"][-1] < a["losses"][0]
