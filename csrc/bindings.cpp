@@ -276,13 +276,13 @@ void grad_pull_reduce(const std::vector<int64_t>& grad_ptrs, int64_t rank, int64
 }
 
 void grad_pull_bucket(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& flag_ptrs, int64_t rank,
-                      int64_t bucket, int64_t seq, int64_t lo, torch::Tensor& out, bool accumulate, int64_t blocks,
-                      torch::Tensor& status) {
+                      int64_t bucket, int64_t seq, int64_t lo, torch::Tensor& out, bool accumulate, bool clear,
+                      int64_t blocks, torch::Tensor& status) {
   TORCH_CHECK(out.scalar_type() == torch::kFloat32 && out.is_contiguous() && out.numel() % 4 == 0 && lo % 4 == 0);
   TORCH_CHECK(grad_ptrs.size() == flag_ptrs.size() && bucket >= 0 && bucket < mt::kBucketSlots);
   c10::cuda::CUDAGuard guard(out.device());
   mt::grad_pull_bucket(to_peers(grad_ptrs), to_peers(flag_ptrs), (int)rank, (int)grad_ptrs.size(), (int)bucket, (int)seq,
-                       lo, out.numel(), out.data_ptr<float>(), accumulate, (int)blocks, status.data_ptr<int>(),
+                       lo, out.numel(), out.data_ptr<float>(), accumulate, clear, (int)blocks, status.data_ptr<int>(),
                        cur_stream());
 }
 

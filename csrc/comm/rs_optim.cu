@@ -9,8 +9,11 @@
 //                       backward pass is still running: the kernel first posts "my gradients for bucket b are
 //                       final" (a sequence number) into every peer's flag table, waits (bounded) until every peer
 //                       has posted the same, then pulls and sums its slice of the bucket from all ranks and
-//                       stores zeros back into the slices it has consumed, so that no separate clearing pass over the
-//                       gradient buffers is needed.  Runs on a capped grid so that it hides under the backward
+//                       stores zeros back into the slices it has consumed (`clear`), so that no separate clearing pass
+//                       over the gradient buffers is needed.  Those are remote stores: a rank may write the cleared
+//                       range again only after a later synchronisation point that is far behind them (the step-end
+//                       barrier); a caller that reuses the buffer right away passes clear = false and clears its own
+//                       memory once every peer has finished reading.  Runs on a capped grid so that it hides under the backward
 //                       kernels instead of competing with them.
 //   adamw_publish       fused AdamW on the shard (clip factor, moments, fp32 master) whose bf16 result is written
 //                       straight into the shard's slot of every rank's resident parameter buffer (peer stores),
@@ -86,7 +89,8 @@ __global__ void grad_pull_reduce_kernel(PeerPtrs grads, int rank, int world, int
 // flags: per rank an int[world * kBucketSlots] table in symmetric memory; entry [src * kBucketSlots + bucket] of rank d
 // is the last sequence number rank src posted for that bucket.
 __global__ void grad_pull_bucket_kernel(PeerPtrs grads, PeerPtrs flags, int rank, int world, int bucket, int seq,
-                                        int64_t lo, int64_t n, float* __restrict__ out, int accumulate, int* status) {
+                                        int64_t lo, int64_t n, float* __restrict__ out, int accumulate, int clear,
+                                        int* status) {
   __shared__ int give_up;
   if (threadIdx.x == 0) give_up = 0;
   __syncthreads();
@@ -122,9 +126,11 @@ __global__ void grad_pull_bucket_kernel(PeerPtrs grads, PeerPtrs flags, int rank
     for (int r = 0; r < kMaxPeers; ++r)  // fixed summation order: the result is the same on every run
       if (r < world) { s.x += v[r].x; s.y += v[r].y; s.z += v[r].z; s.w += v[r].w; }
     reinterpret_cast<float4*>(out)[i] = s;
+    if (clear) {
 #pragma unroll
-    for (int r = 0; r < kMaxPeers; ++r)  // this thread is the only reader of these elements: clear them for the next step
-      if (r < world) *(reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[r]) + lo) + i) = zero;
+      for (int r = 0; r < kMaxPeers; ++r)  // this thread is the only reader of these elements: clear them for the next step
+        if (r < world) *(reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[r]) + lo) + i) = zero;
+    }
   }
 }
 
@@ -204,11 +210,11 @@ void grad_pull_reduce(const PeerPtrs& grads, int rank, int world, int64_t lo, in
 }
 
 void grad_pull_bucket(const PeerPtrs& grads, const PeerPtrs& flags, int rank, int world, int bucket, int seq, int64_t lo,
-                      int64_t n, float* out, bool accumulate, int blocks, int* status, cudaStream_t stream) {
+                      int64_t n, float* out, bool accumulate, bool clear, int blocks, int* status, cudaStream_t stream) {
   if (n == 0 || bucket < 0 || bucket >= kBucketSlots) return;
   if (blocks <= 0) blocks = 148 * 4;
   grad_pull_bucket_kernel<<<blocks, 512, 0, stream>>>(grads, flags, rank, world, bucket, seq, lo, n, out,
-                                                      accumulate ? 1 : 0, status);
+                                                      accumulate ? 1 : 0, clear ? 1 : 0, status);
 }
 
 void adamw_publish(float* master, float* m, float* v, const float* grad, const PeerPtrs& params, int world, int64_t lo,

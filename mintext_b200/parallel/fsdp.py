@@ -12,10 +12,10 @@ decoder layer, only the rank's ``1/N`` slice of both:
   left layer ``L`` (backward), so the consuming GEMMs find their weights in place.  Autograd's saved weight tensors
   are views of the slot, and the layer is always gathered into the same slot again before its backward runs.
 * **Gradients.**  Weight-gradient epilogues add into a two-slot fp32 staging buffer (symmetric memory).  When the
-  backward pass has left layer ``L`` its slot is reduce-scattered on the side stream by ``grad_pull_bucket`` (every rank
-  sums its slice from all peers, accumulates it into its persistent ``grad_shard`` and stores zeros back), followed by
-  a barrier after which the slot may be written again; the compute stream waits for that event only before the layer
-  that reuses the slot, two layers later.  With gradient accumulation every micro-batch reduces every layer.
+  backward pass has left layer ``L`` its slot is reduce-scattered by ``grad_pull_bucket`` (every rank sums its slice
+  from all peers and accumulates it into its persistent ``grad_shard``), followed by a barrier (every peer has read
+  this rank's slot) and a local clearing of the slot, after which the layer two below may write it.  With gradient
+  accumulation every micro-batch reduces every layer.
 * **Bucket 0** (embedding, output head, final norm: used at both ends of the step) stays resident and follows the
   resident mode's path.
 
@@ -71,6 +71,10 @@ class _ShardedComm:
         self.gather = torch.cuda.Stream(device=dev)    # weight gathers
         self.gather_blocks = int(os.environ.get("MT_PARAM_GATHER_BLOCKS", "32"))
         self.pull_blocks = int(os.environ.get("MT_GRAD_PULL_BLOCKS", "32"))
+        # The per-layer reduce-scatter runs on the compute stream, between two layers' backward passes.  Running it
+        # on the side stream under the next layer's backward (MT_FSDP_OVERLAP_REDUCE=1) is wired but off: on some
+        # 2-GPU boxes it produced intermittently different updates whose cause has not been found.
+        self.overlap_reduce = os.environ.get("MT_FSDP_OVERLAP_REDUCE", "0") == "1"
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)
 
@@ -230,14 +234,18 @@ class ParamShardedEngine(TrainEngine):
         _, _, blen = self.buckets[bidx]
         _, _, _, loc = self.segments[bidx]
         sl = blen // self.world
-        with torch.cuda.stream(sc.side):
+        with torch.cuda.stream(sc.side if sc.overlap_reduce else cur):
+            # the slot is written again two layers later: no remote clearing stores (their arrival at the peer is not
+            # ordered with the barrier that follows); every rank clears its own slot once all peers have read it
             ext().grad_pull_bucket(sc.stage_grad_ptrs, sc.bflag_ptrs, self.rank, bidx, self._pull_seq(),
                                    slot * self.stage_len + self.rank * sl, self.grad_shard[loc:loc + sl],
-                                   self._micro_index > 0, max(sc.pull_blocks, min(296, sl * 4 // (2 << 20))),
+                                   self._micro_index > 0, False,
+                                   max(sc.pull_blocks, min(296, sl * 4 // (2 << 20))) if sc.overlap_reduce else 0,
                                    status_word(self.device))
-            sc.barrier_side()  # every rank has pulled (and cleared) its slice of this slot
+            sc.barrier_side()  # every rank has pulled its slice of this slot
+            self.stage_grad[slot * self.stage_len:slot * self.stage_len + blen].zero_()
             ev = torch.cuda.Event()
-            ev.record(sc.side)
+            ev.record(torch.cuda.current_stream(self.device))
         self._grad_event[slot] = ev
         self._pulled.add(bidx)
         self.kernel_launches += 2
@@ -312,7 +320,7 @@ class ParamShardedEngine(TrainEngine):
             _, _, _, loc = self.segments[self._res_index]
             sl = blen // self.world
             ext().grad_pull_bucket(sc.res_grad_ptrs, sc.bflag_ptrs, self.rank, self._res_index, self._round,
-                                   self.rank * sl, self.grad_shard[loc:loc + sl], False, 0, status_word(self.device))
+                                   self.rank * sl, self.grad_shard[loc:loc + sl], False, True, 0, status_word(self.device))
             self._flat_cleared_by_pull = True
         self._pulled, self._late = set(), set()
 

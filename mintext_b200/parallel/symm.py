@@ -74,7 +74,7 @@ class SymmetricOptimizerComm:
         _, a, b, loc = e.segments[bucket]
         seq = 2 * self.round + (1 if accumulate else 0)
         ext().grad_pull_bucket(self.grad_ptrs, self.bflag_ptrs, self.rank, bucket, seq, a, e.grad_shard[loc:loc + (b - a)],
-                               accumulate, blocks, status_word(e.device))
+                               accumulate, True, blocks, status_word(e.device))
 
     def _open_round(self) -> None:
         if not self._round_open:
