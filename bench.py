@@ -159,6 +159,9 @@ def main() -> None:
     ap.add_argument("--profile-out", default=None, metavar="FILE",
                     help="after the measurement, run one more step under torch.profiler and write rank 0's "
                          "per-kernel time shares to FILE (outside every timed region)")
+    ap.add_argument("--shard-params", action="store_true",
+                    help="side measurement: layer weights and gradients sharded 1/N (fsdp_shard_params) instead of "
+                         "resident on every rank; needs more than one GPU")
     ap.add_argument("--fp8-mlp", action="store_true",
                     help="side measurement, not the headline: MLP projections through the FP8 GEMM (per-tensor scales)")
     ap.add_argument("--fp8-recipe", choices=("per_tensor", "mx_block"), default="per_tensor",
@@ -209,11 +212,16 @@ def main() -> None:
         cfg = llama_1b_config(args.global_batch, args.seq_len, world, args.micro_batch, args.steps + warmup,
                               args.fp8_mlp, args.fp8_recipe)
         model = Transformer(cfg, rngs=0)
-        eng = TrainEngine(model, cfg, device=dev)
+        if args.shard_params:
+            from mintext_b200.parallel.fsdp import ParamShardedEngine
+
+            eng = ParamShardedEngine(model, cfg.model_copy(update={"fsdp_shard_params": True}), device=dev)
+        else:
+            eng = TrainEngine(model, cfg, device=dev)
         tp = 1
         metric = "train tokens/s (Llama-3.2-1B-shaped, bf16, AdamW)"
         model_desc = "llama-3.2-1b-shaped (16L, d2048, 32/8 heads, ffn 8192, vocab 128256, tied)"
-        parallelism = f"fsdp{world}" if world > 1 else "single"
+        parallelism = (f"fsdp{world}" if world > 1 else "single") + (" (parameters sharded)" if args.shard_params else "")
     else:
         from mintext_b200.train import setup_training
 

@@ -14,7 +14,6 @@ import argparse
 import os
 import sys
 import time
-from collections import defaultdict
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parents[1]
@@ -37,7 +36,6 @@ def main() -> None:
 
     import torch
     import torch.distributed as dist
-    from torch.profiler import ProfilerActivity, profile
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -76,29 +74,14 @@ def main() -> None:
     eng.train_step(batch, num_micro=n_micro)
     torch.cuda.synchronize()
     plain_ms = (time.time() - t0) * 1e3
-    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
-        t0 = time.time()
-        eng.train_step(batch, num_micro=n_micro)
-        host_ms = (time.time() - t0) * 1e3
-        torch.cuda.synchronize()
-        wall_ms = (time.time() - t0) * 1e3
+    from mintext_b200.utils.profiling import kernel_share_table
+
+    text = kernel_share_table(lambda: eng.train_step(batch, num_micro=n_micro), top=args.top,
+                              header=f"model={args.model} gpus={world} global_batch={gb} micro_batch="
+                                     f"{cfg.per_device_batch_size} n_micro={n_micro} overrides={args.set}\n"
+                                     f"step without profiler: {plain_ms:.1f} ms")
     eng.check()
-    agg = defaultdict(lambda: [0, 0.0])
-    for ev in prof.events():
-        if ev.device_type == torch.autograd.DeviceType.CUDA:
-            a = agg[ev.name]
-            a[0] += 1
-            a[1] += ev.device_time
-    total = sum(v[1] for v in agg.values())
-    lines = [f"model={args.model} gpus={world} global_batch={gb} micro_batch={cfg.per_device_batch_size} "
-             f"n_micro={n_micro} overrides={args.set}",
-             f"step without profiler: {plain_ms:.1f} ms;  under profiler: wall {wall_ms:.1f} ms, host issue time "
-             f"{host_ms:.1f} ms, sum of kernel time {total / 1e3:.1f} ms, launches {sum(v[0] for v in agg.values())}",
-             f"{'kernel':90s} {'calls':>6s} {'ms':>9s} {'share':>7s}"]
-    for name, (n, us) in sorted(agg.items(), key=lambda kv: -kv[1][1])[: args.top]:
-        lines.append(f"{name[:90]:90s} {n:6d} {us / 1e3:9.2f} {us / total * 100:6.1f}%")
     if rank == 0:
-        text = "\n".join(lines)
         print(text)
         if args.out:
             Path(args.out).parent.mkdir(parents=True, exist_ok=True)

@@ -100,10 +100,12 @@ struct PeerPtrs {
   void* p[kMaxPeers];
 };
 void symm_barrier(const PeerPtrs& flags, int rank, int world, int seq, int* status, cudaStream_t stream);
-// dst[r * n_bytes + i] = shards[r][lo_bytes + i] for every rank r (byte offsets / sizes, multiples of 16): the
-// parameter all-gather of the parameter-sharded engine mode, by plain peer loads
-void peer_gather(const PeerPtrs& shards, int world, int64_t lo_bytes, int64_t n_bytes, void* dst, int blocks,
-                 cudaStream_t stream);
+// dst[r * n_bytes + i] = shards[r][lo_bytes + r * rank_stride_bytes + i] for every rank r (byte offsets / sizes,
+// multiples of 16): an all-gather by plain peer loads (parameter-sharded engine mode: stride 0, every rank's slice
+// sits at the same offset of its shard buffer; Muon's publication: stride = slice size, rank r's slice sits at
+// its place in the flat buffer)
+void peer_gather(const PeerPtrs& shards, int world, int64_t lo_bytes, int64_t rank_stride_bytes, int64_t n_bytes, void* dst,
+                 int blocks, cudaStream_t stream);
 // out[0..n) = sum over ranks of grads[r][lo..lo+n) ; *sumsq += |out|^2   (n multiple of 4, lo multiple of 4)
 void grad_pull_reduce(const PeerPtrs& grads, int rank, int world, int64_t lo, int64_t n, float* out, float* sumsq,
                       cudaStream_t stream);

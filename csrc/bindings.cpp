@@ -288,13 +288,16 @@ void grad_pull_bucket(const std::vector<int64_t>& grad_ptrs, const std::vector<i
 
 int64_t bucket_flag_slots() { return mt::kBucketSlots; }
 
-// dst (flat, world * n elements) <- slice [lo, lo + n) of every rank's shard buffer, rank by rank
-void peer_gather(const std::vector<int64_t>& shard_ptrs, int64_t lo, int64_t n, torch::Tensor& dst, int64_t blocks) {
+// dst (flat, world * n elements) <- elements [lo + r * rank_stride, + n) of rank r's buffer, rank by rank
+void peer_gather(const std::vector<int64_t>& shard_ptrs, int64_t lo, int64_t rank_stride, int64_t n, torch::Tensor& dst,
+                 int64_t blocks) {
   const int64_t es = dst.element_size();
   TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && dst.numel() == n * (int64_t)shard_ptrs.size());
-  TORCH_CHECK((lo * es) % 16 == 0 && (n * es) % 16 == 0 && reinterpret_cast<uintptr_t>(dst.data_ptr()) % 16 == 0);
+  TORCH_CHECK((lo * es) % 16 == 0 && (n * es) % 16 == 0 && (rank_stride * es) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(dst.data_ptr()) % 16 == 0);
   c10::cuda::CUDAGuard guard(dst.device());
-  mt::peer_gather(to_peers(shard_ptrs), (int)shard_ptrs.size(), lo * es, n * es, dst.data_ptr(), (int)blocks, cur_stream());
+  mt::peer_gather(to_peers(shard_ptrs), (int)shard_ptrs.size(), lo * es, rank_stride * es, n * es, dst.data_ptr(),
+                  (int)blocks, cur_stream());
 }
 
 void adamw_publish(torch::Tensor& master, torch::Tensor& m, torch::Tensor& v, const torch::Tensor& grad,

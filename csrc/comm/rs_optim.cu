@@ -177,13 +177,15 @@ __global__ void adamw_publish_kernel(float* __restrict__ master, float* __restri
   }
 }
 
-// dst[r * n16 + i] = shards[r][lo16 + i] in 16-byte units; the loads of all ranks are issued before the stores
-__global__ void peer_gather_kernel(PeerPtrs shards, int world, int64_t lo16, int64_t n16, uint4* __restrict__ dst) {
+// dst[r * n16 + i] = shards[r][lo16 + r * stride16 + i] in 16-byte units; the loads of all ranks are issued before
+// the stores
+__global__ void peer_gather_kernel(PeerPtrs shards, int world, int64_t lo16, int64_t stride16, int64_t n16,
+                                   uint4* __restrict__ dst) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
     uint4 v[kMaxPeers];
 #pragma unroll
     for (int r = 0; r < kMaxPeers; ++r)
-      if (r < world) v[r] = *(reinterpret_cast<const uint4*>(shards.p[r]) + lo16 + i);
+      if (r < world) v[r] = *(reinterpret_cast<const uint4*>(shards.p[r]) + lo16 + r * stride16 + i);
 #pragma unroll
     for (int r = 0; r < kMaxPeers; ++r)
       if (r < world) dst[(int64_t)r * n16 + i] = v[r];
@@ -196,11 +198,12 @@ void symm_barrier(const PeerPtrs& flags, int rank, int world, int seq, int* stat
   symm_barrier_kernel<<<1, 32, 0, stream>>>(flags, rank, world, seq, status);
 }
 
-void peer_gather(const PeerPtrs& shards, int world, int64_t lo_bytes, int64_t n_bytes, void* dst, int blocks,
-                 cudaStream_t stream) {
+void peer_gather(const PeerPtrs& shards, int world, int64_t lo_bytes, int64_t rank_stride_bytes, int64_t n_bytes, void* dst,
+                 int blocks, cudaStream_t stream) {
   if (n_bytes == 0) return;
   if (blocks <= 0) blocks = 64;
-  peer_gather_kernel<<<blocks, 512, 0, stream>>>(shards, world, lo_bytes / 16, n_bytes / 16, reinterpret_cast<uint4*>(dst));
+  peer_gather_kernel<<<blocks, 512, 0, stream>>>(shards, world, lo_bytes / 16, rank_stride_bytes / 16, n_bytes / 16,
+                                                 reinterpret_cast<uint4*>(dst));
 }
 
 void grad_pull_reduce(const PeerPtrs& grads, int rank, int world, int64_t lo, int64_t n, float* out, float* sumsq,

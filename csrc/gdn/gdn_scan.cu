@@ -83,26 +83,41 @@ gdn_scan_fwd_kernel(const float* __restrict__ W, const float* __restrict__ U, co
       v_s[l * VP + lane] = u_s[l * DVB + lane] - acc[i];
     }
     __syncthreads();
-    // O[l, lane] = QG S + M V'
+    // O[l, lane] = QG S + M V' : the warp's eight rows share every V' load (32 FMAs per 12 shared-memory loads)
+    for (int m = 0; m < L; m += 4) {
+      const float v0 = v_s[(m + 0) * VP + lane], v1 = v_s[(m + 1) * VP + lane], v2 = v_s[(m + 2) * VP + lane],
+                  v3 = v_s[(m + 3) * VP + lane];
 #pragma unroll
-    for (int i = 0; i < L / kWarps; ++i) {
-      const int l = warp + kWarps * i;
-      float o = accq[i];
-      for (int m = 0; m < L; m += 4) {
-        const float4 m4 = *reinterpret_cast<const float4*>(m_s + l * L + m);
-        o = fmaf(m4.x, v_s[(m + 0) * VP + lane],
-                 fmaf(m4.y, v_s[(m + 1) * VP + lane], fmaf(m4.z, v_s[(m + 2) * VP + lane], fmaf(m4.w, v_s[(m + 3) * VP + lane], o))));
+      for (int i = 0; i < L / kWarps; ++i) {
+        const float4 m4 = *reinterpret_cast<const float4*>(m_s + (warp + kWarps * i) * L + m);
+        accq[i] = fmaf(m4.x, v0, fmaf(m4.y, v1, fmaf(m4.z, v2, fmaf(m4.w, v3, accq[i]))));
       }
-      O[(cb * L + l) * dv + j0 + lane] = o;
     }
-    // S[k, lane] = gl * S + sum_l KD[l, k] V'[l, lane] ; rows k = warp + 8 i (each thread owns its own S entries)
-    const float gl = GL[cb];
-    for (int i = 0; i < DK / kWarps; ++i) {
-      const int k = warp + kWarps * i;
-      float a = gl * s_s[k * SP + lane];
-#pragma unroll 8
-      for (int l = 0; l < L; ++l) a = fmaf(kd_s[l * DK + k], v_s[l * VP + lane], a);
-      s_s[k * SP + lane] = a;
+#pragma unroll
+    for (int i = 0; i < L / kWarps; ++i) O[(cb * L + warp + kWarps * i) * dv + j0 + lane] = accq[i];
+    // S[k, lane] = gl * S + sum_l KD[l, k] V'[l, lane] ; a warp owns DK / 8 adjacent key rows, so that one V' load
+    // and DK / 32 vector loads of KD feed DK / 8 FMAs (each thread owns its own S entries)
+    {
+      constexpr int KW = DK / kWarps;
+      const int k0 = warp * KW;
+      const float gl = GL[cb];
+      float a[KW];
+#pragma unroll
+      for (int i = 0; i < KW; ++i) a[i] = gl * s_s[(k0 + i) * SP + lane];
+#pragma unroll 4
+      for (int l = 0; l < L; ++l) {
+        const float v = v_s[l * VP + lane];
+#pragma unroll
+        for (int i = 0; i < KW; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kd_s + l * DK + k0 + i);
+          a[i] = fmaf(k4.x, v, a[i]);
+          a[i + 1] = fmaf(k4.y, v, a[i + 1]);
+          a[i + 2] = fmaf(k4.z, v, a[i + 2]);
+          a[i + 3] = fmaf(k4.w, v, a[i + 3]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < KW; ++i) s_s[(k0 + i) * SP + lane] = a[i];
     }
     __syncthreads();
   }
@@ -177,42 +192,70 @@ gdn_scan_bwd_kernel(const float* __restrict__ W, const float* __restrict__ U, co
       }
     }
     __syncthreads();
-    // (3) dV'[m, lane] += sum_l M[l, m] dO[l, lane] ; then dU = dV'
+    // (3) dV'[m, lane] += sum_l M[l, m] dO[l, lane] ; then dU = dV'.  A warp owns the eight adjacent rows
+    //     m = 8 warp .. 8 warp + 7: one dO load and two vector loads of M feed eight FMAs.
+    {
+      const int m0 = warp * (L / kWarps);
+      float a[L / kWarps];
 #pragma unroll
-    for (int i = 0; i < L / kWarps; ++i) {
-      const int m = warp + kWarps * i;
-      float a = dv_s[m * VP + lane];
-#pragma unroll 8
-      for (int l = 0; l < L; ++l) a = fmaf(m_s[l * L + m], do_s[l * VP + lane], a);
-      dv_s[m * VP + lane] = a;
-      dU[(cb * L + m) * dv + j0 + lane] = a;
+      for (int i = 0; i < L / kWarps; ++i) a[i] = dv_s[(m0 + i) * VP + lane];
+#pragma unroll 4
+      for (int l = 0; l < L; ++l) {
+        const float d = do_s[l * VP + lane];
+        const float4 ma = *reinterpret_cast<const float4*>(m_s + l * L + m0);
+        const float4 mb = *reinterpret_cast<const float4*>(m_s + l * L + m0 + 4);
+        a[0] = fmaf(ma.x, d, a[0]); a[1] = fmaf(ma.y, d, a[1]); a[2] = fmaf(ma.z, d, a[2]); a[3] = fmaf(ma.w, d, a[3]);
+        a[4] = fmaf(mb.x, d, a[4]); a[5] = fmaf(mb.y, d, a[5]); a[6] = fmaf(mb.z, d, a[6]); a[7] = fmaf(mb.w, d, a[7]);
+      }
+      __syncthreads();  // every warp has read the dV' rows it needs before any row changes
+#pragma unroll
+      for (int i = 0; i < L / kWarps; ++i) {
+        dv_s[(m0 + i) * VP + lane] = a[i];
+        dU[(cb * L + m0 + i) * dv + j0 + lane] = a[i];
+      }
     }
     __syncthreads();
-    // (4) outputs that reduce over this CTA's 32 columns; a thread owns key rows k = lane + 32 x (conflict-free in the
-    //     padded state tiles) and the rows l = warp + 8 r, walks the 32 columns, then adds into global memory
-    //     (the dv/32 column slices of a head all contribute):
+    // (4) outputs that reduce over this CTA's 32 columns; a thread owns the key rows k = lane + 32 x (all of them:
+    //     conflict-free in the padded state tiles) and, per pass, four of its rows l = warp + 8 r; it walks the 32
+    //     columns and then adds into global memory (the dv/32 column slices of a head all contribute):
     //     dQG[l,k] = <dO[l,:], Sc[k,:]>   dW[l,k] = -<dV'[l,:], Sc[k,:]>   dKD[l,k] = <V'[l,:], dS[k,:]>
-    for (int x = 0; x < DK / 32; ++x) {
-      const int k = lane + 32 * x;
-      float aq[L / kWarps], aw[L / kWarps], ak[L / kWarps];
+    {
+      constexpr int KX = DK / 32;
+      for (int rp = 0; rp < L / kWarps; rp += 4) {
+        float aq[4][KX], aw[4][KX], ak[4][KX];
 #pragma unroll
-      for (int r = 0; r < L / kWarps; ++r) aq[r] = aw[r] = ak[r] = 0.f;
-      for (int j = 0; j < DVB; ++j) {
-        const float sv = sc_s[k * SP + j], dsv = ds_s[k * SP + j];
+        for (int r = 0; r < 4; ++r)
 #pragma unroll
-        for (int r = 0; r < L / kWarps; ++r) {
-          const int l = warp + kWarps * r;
-          aq[r] = fmaf(do_s[l * VP + j], sv, aq[r]);
-          aw[r] = fmaf(dv_s[l * VP + j], sv, aw[r]);
-          ak[r] = fmaf(v_s[l * VP + j], dsv, ak[r]);
+          for (int x = 0; x < KX; ++x) aq[r][x] = aw[r][x] = ak[r][x] = 0.f;
+#pragma unroll 2
+        for (int j = 0; j < DVB; ++j) {
+          float sv[KX], dsv[KX];
+#pragma unroll
+          for (int x = 0; x < KX; ++x) {
+            sv[x] = sc_s[(lane + 32 * x) * SP + j];
+            dsv[x] = ds_s[(lane + 32 * x) * SP + j];
+          }
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int l = warp + kWarps * (rp + r);
+            const float d = do_s[l * VP + j], g = dv_s[l * VP + j], v = v_s[l * VP + j];
+#pragma unroll
+            for (int x = 0; x < KX; ++x) {
+              aq[r][x] = fmaf(d, sv[x], aq[r][x]);
+              aw[r][x] = fmaf(g, sv[x], aw[r][x]);
+              ak[r][x] = fmaf(v, dsv[x], ak[r][x]);
+            }
+          }
         }
-      }
 #pragma unroll
-      for (int r = 0; r < L / kWarps; ++r) {
-        const int64_t g = (cb * L + warp + kWarps * r) * DK + k;
-        atomicAdd(dQG + g, aq[r]);
-        atomicAdd(dW + g, -aw[r]);
-        atomicAdd(dKD + g, ak[r]);
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int x = 0; x < KX; ++x) {
+            const int64_t g = (cb * L + warp + kWarps * (rp + r)) * DK + lane + 32 * x;
+            atomicAdd(dQG + g, aq[r][x]);
+            atomicAdd(dW + g, -aw[r][x]);
+            atomicAdd(dKD + g, ak[r][x]);
+          }
       }
     }
     //     dM[l, m] = <dO[l,:], V'[m,:]>
@@ -243,14 +286,30 @@ gdn_scan_bwd_kernel(const float* __restrict__ W, const float* __restrict__ U, co
       for (int w = 0; w < kWarps; ++w) a += red[w];
       atomicAdd(dGL + cb, a);
     }
-    // (6) dS_prev[k, lane] = gl * dS + sum_l QG[l,k] dO[l,lane] - sum_l W[l,k] dV'[l,lane]
-    for (int i = 0; i < DK / kWarps; ++i) {
-      const int k = warp + kWarps * i;
-      float a = gl * ds_s[k * SP + lane];
-#pragma unroll 8
-      for (int l = 0; l < L; ++l)
-        a = fmaf(qg_s[l * DK + k], do_s[l * VP + lane], fmaf(-w_s[l * DK + k], dv_s[l * VP + lane], a));
-      ds_s[k * SP + lane] = a;
+    // (6) dS_prev[k, lane] = gl * dS + sum_l QG[l,k] dO[l,lane] - sum_l W[l,k] dV'[l,lane] ; a warp owns DK / 8
+    //     adjacent key rows (two loads of dO / dV' and DK / 16 vector loads feed DK / 4 FMAs)
+    {
+      constexpr int KW = DK / kWarps;
+      const int k0 = warp * KW;
+      float a[KW];
+#pragma unroll
+      for (int i = 0; i < KW; ++i) a[i] = gl * ds_s[(k0 + i) * SP + lane];
+#pragma unroll 2
+      for (int l = 0; l < L; ++l) {
+        const float d = do_s[l * VP + lane], g = -dv_s[l * VP + lane];
+#pragma unroll
+        for (int i = 0; i < KW; i += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qg_s + l * DK + k0 + i);
+          const float4 w4 = *reinterpret_cast<const float4*>(w_s + l * DK + k0 + i);
+          a[i] = fmaf(q4.x, d, fmaf(w4.x, g, a[i]));
+          a[i + 1] = fmaf(q4.y, d, fmaf(w4.y, g, a[i + 1]));
+          a[i + 2] = fmaf(q4.z, d, fmaf(w4.z, g, a[i + 2]));
+          a[i + 3] = fmaf(q4.w, d, fmaf(w4.w, g, a[i + 3]));
+        }
+      }
+      __syncthreads();  // (4) and (5) on other warps have finished reading dS
+#pragma unroll
+      for (int i = 0; i < KW; ++i) ds_s[(k0 + i) * SP + lane] = a[i];
     }
     __syncthreads();
   }

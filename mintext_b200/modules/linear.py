@@ -135,7 +135,9 @@ class Linear(nn.Module):
         w2 = self.kernel.reshape(fan_in, -1) if self.kernel.dim() != 2 else self.kernel
         if self.use_fp8 and self.kernel.dim() == 2 and self.fp8_recipe == "mx_block":
             if F.mxfp8_kernel_path(x2, w2):
-                y = F.linear_mxfp8(x2, w2)
+                if not hasattr(self, "_mx_cache"):
+                    self._mx_cache = F.QuantisedWeightCache()
+                y = F.linear_mxfp8(x2, w2, self._mx_cache)
             else:
                 y = mxfp8_matmul_reference(x2.reshape(-1, fan_in), w2, self.dtype).reshape(*lead, -1)
             if self.bias is not None:
@@ -170,6 +172,8 @@ class MLP(nn.Module):
         self.act_name = config.hidden_activation
         fp8 = bool(config.use_fp8)
         rec = str(getattr(config, "fp8_recipe", "per_tensor"))
+        # block-scaled copies of [gate | up] and down, re-made when the optimizer has changed the weights
+        self._mx_gate_up, self._mx_down = F.QuantisedWeightCache(), F.QuantisedWeightCache()
         self.gate = Linear(D, M, dt, wdt, ("embed", "mlp"), use_fp8=fp8, rngs=rngs, name="mlp_gate_proj", fp8_recipe=rec)
         self.up = Linear(D, M, dt, wdt, ("embed", "mlp"), use_fp8=fp8, rngs=rngs, name="mlp_up", fp8_recipe=rec)
         self.down = Linear(M, D, dt, wdt, ("mlp", "embed"), use_fp8=fp8, rngs=rngs, name="mlp_down", fp8_recipe=rec)
@@ -197,9 +201,9 @@ class MLP(nn.Module):
                 # block-scaled FP8 on the rank's column / row slices: the gathered tokens are quantised once for
                 # gate|up; the collectives around the two GEMMs are the group's all-gather and reduce-scatter
                 xg = tpm.all_gather_tokens(x2, self.tp)
-                gu = F.linear_mxfp8(xg, torch.cat([self.gate.kernel, self.up.kernel], dim=1))
+                gu = F.gate_up_mxfp8(xg, self.gate.kernel, self.up.kernel, self._mx_gate_up)
                 h = F.gated_act(gu, self.act_name)
-                return tpm.reduce_scatter_tokens(F.linear_mxfp8(h, self.down.kernel), self.tp).view(*lead, D)
+                return tpm.reduce_scatter_tokens(F.linear_mxfp8(h, self.down.kernel, self._mx_down), self.tp).view(*lead, D)
             _, (g, u) = tpm.column_linear(x.reshape(-1, D), [self.gate.kernel, self.up.kernel], self.tp, self.gate.dtype)
             h = F.gated_act(torch.cat([g, u], dim=-1), self.act_name)
             return tpm.row_linear(h, self.down.kernel, self.tp, self.gate.dtype).view(*lead, D)
@@ -207,8 +211,10 @@ class MLP(nn.Module):
             x2 = x.reshape(-1, x.shape[-1])
             if self.act_name in oracle.ACT_CODES and F.mxfp8_kernel_path(x2, self.gate.kernel):
                 # one block-scaled GEMM for gate|up (the activation is quantised once), then the gated-act kernel
-                gu = F.linear_mxfp8(x, torch.cat([self.gate.kernel, self.up.kernel], dim=1))
+                gu = F.gate_up_mxfp8(x, self.gate.kernel, self.up.kernel, self._mx_gate_up)
                 h = F.gated_act(gu, self.act_name)
+                if self.down.bias is None and F.mxfp8_kernel_path(h.reshape(-1, h.shape[-1]), self.down.kernel):
+                    return F.linear_mxfp8(h, self.down.kernel, self._mx_down)
             else:
                 h = oracle.activation(self.act_name)(self.gate(x)) * self.up(x)
         elif self.gate.use_fp8 and self.act_name in oracle.ACT_CODES and \

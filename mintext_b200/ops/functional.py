@@ -266,6 +266,32 @@ def linear_fp8(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return y.reshape(*lead, w.shape[1])
 
 
+_WEIGHT_VERSION = 0
+
+
+def bump_weight_version() -> None:
+    """The parameters have changed (optimizer step, checkpoint restore): quantised weight copies are stale."""
+    global _WEIGHT_VERSION
+    _WEIGHT_VERSION += 1
+
+
+class QuantisedWeightCache:
+    """Block-scaled FP8 copies of one layer's weights (both contraction orientations), kept until the parameters next
+    change: with gradient accumulation and rematerialisation a weight is used many times per optimizer step but only
+    changes once, so it is quantised once per step instead of once per use."""
+
+    def __init__(self):
+        self.key = None
+        self.entry = None
+
+    def get(self, tensors, make):
+        key = (_WEIGHT_VERSION,) + tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in tensors)
+        if key != self.key:
+            self.entry = make()
+            self.key = key
+        return self.entry
+
+
 class _LinearMxfp8Fn(torch.autograd.Function):
     """``y = x @ W`` with MXFP8 operands: e4m3 elements with one power-of-two scale per 32 elements along the
     contraction, applied inside the tensor core (csrc/gemm/mxfp8_gemm.cu).  Forward and data gradient run in 8
@@ -273,11 +299,12 @@ class _LinearMxfp8Fn(torch.autograd.Function):
     accumulating in fp32, as on the per-tensor FP8 path (mintext/modules/linear.py:37-57 for the layer semantics)."""
 
     @staticmethod
-    def forward(ctx, x, w, main_grad):
+    def forward(ctx, x, w, main_grad, cache):
         e, st = ext(), status_word(x.device)
         xq, xs, _, _ = e.mxfp8_quantize(x, True, False, False, False)
         # w is [K, N]: the forward contracts K (transposed copy [N, K]), the data gradient contracts N (w as stored)
-        wq, ws, wqt, wst = e.mxfp8_quantize(w, True, True, True, True)
+        quantise = lambda: e.mxfp8_quantize(w, True, True, True, True)
+        wq, ws, wqt, wst = cache.get((w,), quantise) if cache is not None else quantise()
         ctx.save_for_backward(x, wq, ws)
         ctx.main_grad, ctx.wmeta = main_grad, (w.shape, w.dtype, w.device)
         return e.gemm_mxfp8(xq, xs, wqt, wst, st)
@@ -299,7 +326,47 @@ class _LinearMxfp8Fn(torch.autograd.Function):
             else:
                 dw = torch.empty(shape, device=dev, dtype=torch.float32)
                 dw = _gemm(x, dy, dw, True, True).to(wdt)
-        return dx, dw, None
+        return dx, dw, None, None
+
+
+class _GateUpMxfp8Fn(torch.autograd.Function):
+    """``[gate | up] = x @ [Wg | Wu]`` as one block-scaled GEMM: the activation is quantised once, the concatenated
+    weight is quantised once per optimizer step (``cache``), and the two weight gradients are bf16 GEMMs on the column
+    halves of ``dy`` that add straight into each parameter's fp32 accumulator."""
+
+    @staticmethod
+    def forward(ctx, x, wg, wu, mg_g, mg_u, cache):
+        e, st = ext(), status_word(x.device)
+        xq, xs, _, _ = e.mxfp8_quantize(x, True, False, False, False)
+        quantise = lambda: e.mxfp8_quantize(torch.cat([wg, wu], dim=1), True, True, True, True)
+        wq, ws, wqt, wst = cache.get((wg, wu), quantise) if cache is not None else quantise()
+        ctx.save_for_backward(x, wq, ws)
+        ctx.grads = (mg_g, mg_u)
+        ctx.wmeta = (wg.shape, wu.shape, wg.dtype, wg.device)
+        return e.gemm_mxfp8(xq, xs, wqt, wst, st)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, wq, ws = ctx.saved_tensors
+        e, st = ext(), status_word(x.device)
+        dy = dy.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dyq, dys, _, _ = e.mxfp8_quantize(dy, True, False, False, False)
+            dx = e.gemm_mxfp8(dyq, dys, wq, ws, st)
+        sg, su, wdt, dev = ctx.wmeta
+        M = sg[1]
+        dws = [None, None]
+        for i, (need, mg, shape, cols) in enumerate(((ctx.needs_input_grad[1], ctx.grads[0], sg, slice(0, M)),
+                                                     (ctx.needs_input_grad[2], ctx.grads[1], su, slice(M, M + su[1])))):
+            if not need:
+                continue
+            if mg is not None:
+                _gemm(x, dy[:, cols], mg.view(shape), True, True, accumulate=True)
+            else:
+                dw = torch.empty(shape, device=dev, dtype=torch.float32)
+                dws[i] = _gemm(x, dy[:, cols], dw, True, True).to(wdt)
+        return dx, dws[0], dws[1], None, None, None
 
 
 def mxfp8_kernel_path(x: torch.Tensor, w2: torch.Tensor) -> bool:
@@ -307,14 +374,25 @@ def mxfp8_kernel_path(x: torch.Tensor, w2: torch.Tensor) -> bool:
             and w2.shape[0] % 128 == 0 and w2.shape[1] % 128 == 0)
 
 
-def linear_mxfp8(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+def linear_mxfp8(x: torch.Tensor, w: torch.Tensor, cache: QuantisedWeightCache | None = None) -> torch.Tensor:
     """``x[..., K] @ w[K, N]`` through the block-scaled FP8 GEMM (callers check :func:`mxfp8_kernel_path`)."""
     lead, K = x.shape[:-1], w.shape[0]
     x2 = x.reshape(-1, K)
     if not x2.is_contiguous():
         x2 = x2.contiguous()
-    y = _LinearMxfp8Fn.apply(x2, w, getattr(w, "main_grad", None))
+    y = _LinearMxfp8Fn.apply(x2, w, getattr(w, "main_grad", None), cache)
     return y.reshape(*lead, w.shape[1])
+
+
+def gate_up_mxfp8(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor,
+                  cache: QuantisedWeightCache | None = None) -> torch.Tensor:
+    """``x[..., K] @ [wg | wu]`` -> ``[..., 2M]`` through one block-scaled FP8 GEMM."""
+    lead, K = x.shape[:-1], wg.shape[0]
+    x2 = x.reshape(-1, K)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = _GateUpMxfp8Fn.apply(x2, wg, wu, getattr(wg, "main_grad", None), getattr(wu, "main_grad", None), cache)
+    return y.reshape(*lead, wg.shape[1] + wu.shape[1])
 
 
 class _LinearNTFn(torch.autograd.Function):

@@ -1,9 +1,11 @@
 """Muon's Newton-Schulz orthogonalisation on the tcgen05 GEMM kernel (bf16 operands, fp32 accumulation).
 
-Per iteration three GEMMs of this repository's dense kernel: ``A = X X^T``, ``A2 = A A`` and
-``X <- a X + (b A + c A2) X`` (the last one accumulates into an fp32 copy of ``a X`` through the kernel's TMA-add
-epilogue).  Semantics follow ``optax.contrib.muon`` as used by the reference (mintext/optim/optimizer.py:117-168):
-wide orientation, Frobenius normalisation, coefficients (3.4445, -4.7750, 2.0315).
+Per iteration three GEMMs of this repository's dense kernel and three scalings, everything in bf16 between the GEMMs:
+``A = X X^T``; ``B = b A`` prefilled and ``(c A) A`` added into it by the kernel's TMA-add epilogue; ``X' = a X``
+prefilled and ``B X`` added into it.  No fp32 <-> bf16 cast passes; only the last iteration accumulates into an fp32
+copy of ``a X`` so that the returned update keeps the accumulator's precision.  Semantics follow
+``optax.contrib.muon`` as used by the reference (mintext/optim/optimizer.py:117-168): wide orientation, Frobenius
+normalisation, coefficients (3.4445, -4.7750, 2.0315).
 """
 
 from __future__ import annotations
@@ -30,21 +32,31 @@ def newton_schulz(x: torch.Tensor, steps: int = 5, eps: float = 1e-8, coeffs=ora
         return oracle.newton_schulz(x, steps, eps, coeffs)
     ca, cb, cc = coeffs
     out = torch.empty_like(x)
+    bf = torch.bfloat16
     for i in range(bsz):
         m = x[i]
         transposed = r > c
         if transposed:
             m = m.t()
         m = m / (m.norm() + eps)
-        X = m.to(torch.bfloat16).contiguous()
-        n = X.shape[0]
+        X = m.to(bf).contiguous()
+        n, w = X.shape
+        A, Ac, Bm = (torch.empty(n, n, device=x.device, dtype=bf) for _ in range(3))
+        Xn = torch.empty(n, w, device=x.device, dtype=bf)
         Xf = None
-        for _ in range(steps):
-            A = _gemm(X, X, torch.empty(n, n, device=x.device, dtype=torch.bfloat16), False, False)   # X X^T
-            A2 = _gemm(A, A, torch.empty_like(A), False, True)                                         # A A
-            Bm = A.float().mul_(cb).add_(A2.float(), alpha=cc).to(torch.bfloat16)
-            Xf = X.float().mul_(ca)
-            _gemm(Bm, X, Xf, False, True, accumulate=True)                                             # += B X
-            X = Xf.to(torch.bfloat16)
+        for it in range(steps):
+            _gemm(X, X, A, False, False)                         # A = X X^T
+            torch.mul(A, cb, out=Bm)
+            torch.mul(A, cc, out=Ac)
+            _gemm(Ac, A, Bm, False, True, accumulate=True)       # B = b A + (c A) A
+            if it == steps - 1:
+                Xf = X.float().mul_(ca)
+                _gemm(Bm, X, Xf, False, True, accumulate=True)   # fp32: a X + B X
+            else:
+                torch.mul(X, ca, out=Xn)
+                _gemm(Bm, X, Xn, False, True, accumulate=True)   # X' = a X + B X
+                X, Xn = Xn, X
+        if Xf is None:
+            Xf = X.float()
         out[i] = Xf.t() if transposed else Xf
     return out

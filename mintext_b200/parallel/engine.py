@@ -123,6 +123,16 @@ class TrainEngine:
 
                 logging.getLogger(__name__).warning("peer-memory optimizer path unavailable (%s); using NCCL", e)
                 self.use_fused = False
+        self._muon_comm = None
+        if self.use_muon and self.world > 1 and bool(config.fused_collectives) and self.param_flat is not None:
+            try:
+                from mintext_b200.parallel.symm import MuonPublishComm
+
+                self._muon_comm = MuonPublishComm(self)
+            except Exception as e:  # fall back to the NCCL all-gather, loudly
+                import logging
+
+                logging.getLogger(__name__).warning("peer-memory Muon publication unavailable (%s); using NCCL", e)
         self._sumsq = torch.zeros(1, device=self.device, dtype=torch.float32)
         self._sumsq_shard = torch.zeros(1, device=self.device, dtype=torch.float32)
         self._clip = torch.ones(1, device=self.device, dtype=torch.float32)
@@ -464,7 +474,9 @@ class TrainEngine:
             pshard = self.param_flat[lo:lo + self.shard_size]
             self._muon_group(self.big.slots, lo, lo + self.shard_size, self.master, self.exp_avg, self.exp_avg_sq,
                              gshard, pshard, lr, bc1, bc2, inv, t)
-            if W > 1:
+            if W > 1 and self._muon_comm is not None:
+                self._muon_comm.publish()
+            elif W > 1:
                 dist.all_gather_into_tensor(self.param_flat, pshard, group=self.group)
         elif W > 1:
             self._update_sharded_group(gshard, lr, bc1, bc2, inv)
@@ -479,6 +491,9 @@ class TrainEngine:
                          cfg.adam_b2, cfg.adam_eps, cfg.weight_decay, bc1, bc2, inv, self._clip)
         self._small_adamw(lr, bc1, bc2, inv)
         self.kernel_launches += 4
+        from mintext_b200.ops import functional as F
+
+        F.bump_weight_version()  # quantised weight copies kept by the layers are stale now
         return {"grad_norm": grad_norm, "learning_rate": lr}
 
     def _muon_group(self, slots, lo, hi, master, mom, second, grad, param_out, lr, bc1, bc2, inv, t) -> None:
@@ -704,6 +719,9 @@ class TrainEngine:
 
     def _publish_master(self) -> None:
         """Rebuild the resident bf16 compute copy from the fp32 master shards."""
+        from mintext_b200.ops import functional as F
+
+        F.bump_weight_version()
         for (_, boff, blen), (_, a, b, loc) in zip(self.buckets, self.segments):
             mine = self.master[loc:loc + (b - a)].to(torch.bfloat16)
             if self.world > 1:
@@ -722,6 +740,9 @@ class TrainEngine:
     def refresh_from_model(self) -> None:
         """Parameters were overwritten in place (e.g. by an HF import into the bf16 views): re-derive the master
         shards from them."""
+        from mintext_b200.ops import functional as F
+
+        F.bump_weight_version()
         for _, a, b, loc in self.segments:
             self.master[loc:loc + (b - a)].copy_(self.param_flat[a:b].float())
 

@@ -195,7 +195,7 @@ class ParamShardedEngine(TrainEngine):
         sl = blen // self.world
         dst = self.stage_param[slot * self.stage_len:slot * self.stage_len + blen]
         with torch.cuda.stream(sc.gather):
-            ext().peer_gather(sc.shard_ptrs, loc, sl, dst, sc.gather_blocks)
+            ext().peer_gather(sc.shard_ptrs, loc, 0, sl, dst, sc.gather_blocks)
             done = torch.cuda.Event()
             done.record(sc.gather)
         self._slot_layer[slot] = layer
@@ -355,6 +355,9 @@ class ParamShardedEngine(TrainEngine):
 
     # ------------------------------------------------------------------ whole-tensor access
     def _publish_master(self) -> None:
+        from mintext_b200.ops import functional as F
+
+        F.bump_weight_version()
         self.param_shard.copy_(self.master)
         if self._res_index is not None:
             _, a, b, loc = self.segments[self._res_index]

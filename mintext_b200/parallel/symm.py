@@ -115,3 +115,38 @@ class SymmetricOptimizerComm:
             ext().adamw_publish(e.master[sl], e.exp_avg[sl], e.exp_avg_sq[sl], grad_shard[sl], self.param_ptrs, a,
                                 lr, cfg.adam_b1, cfg.adam_b2, cfg.adam_eps, cfg.weight_decay, bc1, bc2, grad_scale, clip)
         self.barrier()  # all shards published everywhere, all peers done reading this rank's gradients
+
+
+class MuonPublishComm:
+    """Publication of Muon's updated bf16 shards without a library collective: every rank owns one contiguous
+    ``1/N`` bin of the flat parameter buffer (symmetric memory); after its update it waits at a flag barrier, pulls the
+    other ranks' bins from their buffers into its own (``peer_gather``: plain peer loads) and waits again, so that no
+    rank overwrites its bin in the next step while a peer still reads it."""
+
+    def __init__(self, engine):
+        import torch.distributed._symmetric_memory as symm
+
+        self.engine = engine
+        group = engine.group or dist.group.WORLD
+        self.rank, self.world = engine.rank, engine.world
+        if self.world > 8:
+            raise RuntimeError("the peer-memory path covers a single NVSwitch domain of at most 8 GPUs")
+        self.flags = symm.empty(64, dtype=torch.int32, device=engine.device)
+        self.flags.zero_()
+        self._h_flags = symm.rendezvous(self.flags, group)
+        self._h_param = symm.rendezvous(engine.param_flat, group)
+        self.flag_ptrs = [int(p) for p in self._h_flags.buffer_ptrs]
+        self.param_ptrs = [int(p) for p in self._h_param.buffer_ptrs]
+        self.seq = 0
+        torch.cuda.synchronize(engine.device)
+        dist.barrier(group=group)
+
+    def _barrier(self) -> None:
+        self.seq += 1
+        ext().symm_barrier(self.flag_ptrs, self.rank, self.seq, status_word(self.engine.device))
+
+    def publish(self) -> None:
+        e = self.engine
+        self._barrier()  # every rank's bin holds its updated weights
+        ext().peer_gather(self.param_ptrs, 0, e.shard_size, e.shard_size, e.param_flat, 0)
+        self._barrier()  # every rank has read every bin

@@ -87,11 +87,18 @@ def estimate_param_count(config) -> float:
     return float(emb + attn * L + ffn)
 
 
+def _tensor_parallel_degree(config) -> int:
+    return max(int(getattr(config, "ici_tensor_parallelism", 1) or 1), 1)
+
+
 def calculate_tflops_per_device(config) -> float:
-    """TFLOP per device per optimizer step, assuming each device processes ``per_device_batch_size`` sequences
-    per micro-step."""
-    return model_flops_per_token_batch(config, config.per_device_batch_size) * config.gradient_accumulation_steps / 1e12
+    """TFLOP per device per optimizer step.  ``per_device_batch_size`` sequences per micro-step are processed by one
+    data-parallel rank, i.e. by a whole tensor-parallel group: a device's share is 1 / tensor-parallel degree of it
+    (the reference replicates work under its sharding instead and counts it in full, mintext/utils/pytree.py:35-37)."""
+    per_group = model_flops_per_token_batch(config, config.per_device_batch_size) * config.gradient_accumulation_steps
+    return per_group / _tensor_parallel_degree(config) / 1e12
 
 
-def calculate_tokens_per_device(config) -> int:
-    return config.per_device_batch_size * config.seq_length * config.gradient_accumulation_steps
+def calculate_tokens_per_device(config) -> float:
+    per_group = config.per_device_batch_size * config.seq_length * config.gradient_accumulation_steps
+    return per_group / _tensor_parallel_degree(config)

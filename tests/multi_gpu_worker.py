@@ -31,15 +31,18 @@ def main(out_path: str) -> None:
     global_tok = torch.randint(0, 1024, (8, 128), generator=g)
     lo, hi = local_batch_rows(8, world, rank)
     tok = global_tok[lo:hi].to(dev)
-    for name, fused in (("fused", True), ("nccl", False), ("muon", False)):
-        cfg = MinTextConfig(optimizer="muon" if name == "muon" else "adamw",
+    for name, fused in (("fused", True), ("nccl", False), ("muon", False), ("muon_peer", True)):
+        cfg = MinTextConfig(optimizer="muon" if name.startswith("muon") else "adamw",
                             num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2,
                             head_dim=64, intermediate_size=512, vocab_size=1024, seq_length=128, steps=20,
                             learning_rate=1e-3, enable_tensorboard=False, enable_checkpointing=False,
                             fused_collectives=fused)
         eng = TrainEngine(Transformer(cfg, rngs=0), cfg, device=dev)
-        assert eng.use_fused == fused, (name, eng.use_fused)
-        if name == "muon":  # matrix-aligned shards: no parameter straddles two ranks' optimizer shards
+        if name.startswith("muon"):  # Muon's own publication: peer loads (fused collectives) or the NCCL all-gather
+            assert (eng._muon_comm is not None) == fused, name
+        else:
+            assert eng.use_fused == fused, (name, eng.use_fused)
+        if name.startswith("muon"):  # matrix-aligned shards: no parameter straddles two ranks' optimizer shards
             for sl in eng.big.slots:
                 assert sl.offset // eng.shard_size == (sl.offset + sl.numel - 1) // eng.shard_size, sl.name
         losses, norms = [], []
