@@ -328,7 +328,7 @@ def main() -> None:
             "higher_is_better": True, "scaling": "strong",
             # the reference publishes a number for the Llama-3.2-1B run only
             "vs_baseline": value / (PUBLISHED_TOKENS_PER_SEC_PER_DEVICE * world) if args.model == "llama1b" else None,
-            "dtype": ("bf16 (mxfp8 MLP projections)" if args.fp8_recipe == "mx_block" else "bf16 (fp8 e4m3/e5m2 MLP projections)") if args.fp8_mlp else "bf16", "data": "synthetic uniform-random token ids, random-init weights", "impl": args.impl,
+            "dtype": ("bf16 (mxfp8 MLP projections)" if args.fp8_recipe == "mx_block" else "bf16 (fp8 e4m3/e5m2 MLP projections)") if args.fp8_mlp else ("bf16 (mxfp8 expert GEMMs)" if getattr(cfg, "moe_use_fp8", False) else "bf16"), "data": "synthetic uniform-random token ids, random-init weights", "impl": args.impl,
             "tokens_per_sec_per_gpu": value / world, "tflops_per_gpu": tflops_per_gpu,
             "mfu_vs_nominal_2250": tflops_per_gpu / 2250.0, "final_loss": final_loss,
             "peak_memory_gb": peak_gb, "moe_dropped_rows": dropped,

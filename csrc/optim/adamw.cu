@@ -66,12 +66,41 @@ __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, 
   }
 }
 
+// Sum of squares.  A thread keeps four 16-byte loads in flight per iteration (the kernel is a pure read stream);
+// the ragged tail (and a misaligned base) falls back to scalar loads.
 template <bool F32>
 __global__ void sumsq_kernel(const void* __restrict__ x, int64_t n, float* __restrict__ out) {
+  constexpr int EPV = F32 ? 4 : 8;  // elements per 16-byte vector
   float s = 0.f;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    const float f = F32 ? reinterpret_cast<const float*>(x)[i]
-                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[i]);
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (int64_t)gridDim.x * blockDim.x;
+  const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  const int64_t nvec = aligned ? n / EPV : 0;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  auto add_vec = [&s](const uint4& v) {
+    if (F32) {
+      const float a = __uint_as_float(v.x), b = __uint_as_float(v.y), c = __uint_as_float(v.z), d = __uint_as_float(v.w);
+      s += a * a + b * b + c * c + d * d;
+    } else {
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xffff0000u);
+        s += lo * lo + hi * hi;
+      }
+    }
+  };
+  int64_t i = tid;
+  for (; i + 3 * nthreads < nvec; i += 4 * nthreads) {
+    const uint4 v0 = xv[i], v1 = xv[i + nthreads], v2 = xv[i + 2 * nthreads], v3 = xv[i + 3 * nthreads];
+    add_vec(v0);
+    add_vec(v1);
+    add_vec(v2);
+    add_vec(v3);
+  }
+  for (; i < nvec; i += nthreads) add_vec(xv[i]);
+  for (int64_t k = nvec * EPV + tid; k < n; k += nthreads) {
+    const float f = F32 ? reinterpret_cast<const float*>(x)[k]
+                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[k]);
     s += f * f;
   }
 #pragma unroll
@@ -110,7 +139,7 @@ void adamw_step(float* master, float* m, float* v, const void* grad, bool grad_f
 
 void sumsq(const void* x, bool is_f32, int64_t n, float* out_accum, cudaStream_t stream) {
   if (n == 0) return;
-  const int g = grid_for(n);
+  const int g = grid_for(n / 16 + 1);
   if (is_f32) sumsq_kernel<true><<<g, 256, 0, stream>>>(x, n, out_accum);
   else sumsq_kernel<false><<<g, 256, 0, stream>>>(x, n, out_accum);
 }

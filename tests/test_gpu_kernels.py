@@ -542,3 +542,38 @@ def test_threefry_randint_kernel_equals_the_tensor_path():
         got = tf.randint_rows(k, row_lo, rows, cols, span, device="cuda", use_kernel=True)
         want = tf.randint_rows(k, row_lo, rows, cols, span, device="cpu", use_kernel=False)
         assert got.dtype == torch.int64 and torch.equal(got.cpu(), want)
+
+
+def test_gate_up_mxfp8_matches_the_concatenated_linear_and_reuses_quantised_weights():
+    """One block-scaled GEMM for [gate | up]: same values as the block-scaled linear on the concatenated weight, weight
+    gradients added straight into each parameter's fp32 accumulator, and the quantised weight copy kept until the
+    parameters are declared changed."""
+    from mintext_b200.ops import functional as F
+
+    torch.manual_seed(11)
+    T, K, M = 256, 256, 384
+    x = (torch.randn(T, K, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    wg = (torch.randn(K, M, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_(True)
+    wu = (torch.randn(K, M, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_(True)
+    wg.main_grad = torch.zeros(K, M, device="cuda")
+    wu.main_grad = torch.zeros(K, M, device="cuda")
+    cache = F.QuantisedWeightCache()
+    y = F.gate_up_mxfp8(x, wg, wu, cache)
+    first = cache.entry
+    x2 = x.detach().clone().requires_grad_(True)
+    wcat = torch.cat([wg.detach(), wu.detach()], dim=1).requires_grad_(True)
+    ref = F.linear_mxfp8(x2, wcat)
+    assert torch.equal(y, ref)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ref.backward(dy)
+    _check()
+    assert torch.equal(x.grad, x2.grad)
+    assert wg.grad is None and wu.grad is None
+    assert _rel_err(wg.main_grad, wcat.grad[:, :M].float()) < 1e-2
+    assert _rel_err(wu.main_grad, wcat.grad[:, M:].float()) < 1e-2
+    F.gate_up_mxfp8(x, wg, wu, cache)
+    assert cache.entry is first          # same parameters: no second quantisation
+    F.bump_weight_version()
+    F.gate_up_mxfp8(x, wg, wu, cache)
+    assert cache.entry is not first      # the optimizer has stepped: quantised again
