@@ -91,3 +91,13 @@ def test_parse_file_size_errors():
     for bad in ("abc", "5X", ""):
         with pytest.raises(ValueError):
             parse_file_size(bad)
+
+
+def test_per_device_throughput_counts_a_tensor_parallel_group_once():
+    """``per_device_batch_size`` sequences belong to one data-parallel rank, i.e. to a whole tensor-parallel group."""
+    base = dict(per_device_batch_size=2, seq_length=64, gradient_accumulation_steps=3)
+    one = MinTextConfig(**base)
+    two = MinTextConfig(**base, ici_tensor_parallelism=2, ici_fsdp_parallelism=1)
+    assert calculate_tokens_per_device(one) == 2 * 64 * 3
+    assert calculate_tokens_per_device(two) == 2 * 64 * 3 / 2
+    assert abs(calculate_tflops_per_device(two) - calculate_tflops_per_device(one) / 2) < 1e-12

@@ -220,3 +220,27 @@ def test_moe_counts_bias_update_and_aux_loss():
     la, _ = trainer.compute_loss(None, ma, ca, b)
     l0, _ = trainer.compute_loss(None, ma, ca.model_copy(update={"router_aux_loss_coef": 0.0}), b)
     assert float(la) > float(l0)
+
+
+def test_quantised_weight_cache_is_keyed_on_the_parameter_version():
+    """The block-scaled weight copies are rebuilt when the optimizer declares the parameters changed, when a tensor
+    is modified in place, and when another tensor is passed; otherwise the cached entry is returned."""
+    from mintext_b200.ops import functional as F
+
+    made = []
+
+    def make():
+        made.append(1)
+        return object()
+
+    cache = F.QuantisedWeightCache()
+    w = torch.zeros(4, 4)
+    a = cache.get((w,), make)
+    assert cache.get((w,), make) is a and len(made) == 1
+    F.bump_weight_version()
+    b = cache.get((w,), make)
+    assert b is not a and len(made) == 2
+    w.add_(1.0)  # an in-place change moves the tensor's version counter
+    c = cache.get((w,), make)
+    assert c is not b and len(made) == 3
+    assert cache.get((torch.zeros(4, 4),), make) is not c and len(made) == 4
