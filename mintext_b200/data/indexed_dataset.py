@@ -51,8 +51,11 @@ def write_mmap_dataset(path_prefix: str, documents, dtype=np.uint16, parts: int 
         return
     per = max((len(docs) + parts - 1) // parts, 1)
     for p in range(parts):
+        chunk = docs[p * per:(p + 1) * per]
+        if not chunk and p > 0:  # fewer documents than parts: no empty trailing files (they cannot be mapped)
+            break
         with open(f"{path_prefix}.bin.{p:05d}", "wb") as f:
-            for d in docs[p * per:(p + 1) * per]:
+            for d in chunk:
                 f.write(d.tobytes())
 
 
@@ -95,7 +98,8 @@ class MMapIndexedDataset:
                 paths.append(p)
             if not paths:
                 raise FileNotFoundError(f"Data file not found: {single} (also tried {path_prefix}.bin.00000)")
-        self._bin_parts = [np.memmap(p, mode="r", dtype=np.uint8) for p in paths]
+        self._bin_parts = [np.memmap(p, mode="r", dtype=np.uint8) if p.stat().st_size > 0 else np.zeros(0, dtype=np.uint8)
+                           for p in paths]
         self._part_cumulative = np.concatenate([[0], np.cumsum([len(m) for m in self._bin_parts])]).astype(np.int64)
         self._num_docs = len(self._document_indices) - 1
         cs = np.zeros(seq_count + 1, dtype=np.int64)

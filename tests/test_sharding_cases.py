@@ -1,0 +1,309 @@
+"""Single-behaviour tests of the mesh, the logical sharding rules and the scan eligibility (after the cases of the
+reference's tests/test_sharding.py), plus the expert axis and the rank arithmetic this build adds."""
+
+import os
+from unittest import mock
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from mintext_b200 import MinTextConfig
+from mintext_b200.parallel import (add_data_axis_to_sharding, create_mesh, create_named_sharding, create_sharded_model,
+                                   get_input_data_sharding, get_logical_axis_rules, get_model_param_shardings,
+                                   logical_to_pspec, setup_mesh)
+from mintext_b200.parallel.mesh import _resolve_auto_parallelism, get_global_mesh
+from mintext_b200.parallel.sharding import NamedSharding
+
+
+# ---- auto axis ---------------------------------------------------------------------------------------------------
+def test_auto_all_explicit_passes_through():
+    assert _resolve_auto_parallelism({"data": 2, "fsdp": 2, "tensor": 2}, 8) == {"data": 2, "fsdp": 2, "tensor": 2}
+
+
+def test_auto_fsdp():
+    assert _resolve_auto_parallelism({"data": 1, "fsdp": -1, "tensor": 1}, 8)["fsdp"] == 8
+
+
+def test_auto_data():
+    assert _resolve_auto_parallelism({"data": -1, "fsdp": 2, "tensor": 2}, 8)["data"] == 2
+
+
+def test_auto_tensor():
+    assert _resolve_auto_parallelism({"data": 2, "fsdp": 1, "tensor": -1}, 8)["tensor"] == 4
+
+
+def test_auto_product_mismatch():
+    with pytest.raises(ValueError, match="product"):
+        _resolve_auto_parallelism({"data": 2, "fsdp": 2, "tensor": 1}, 8)
+
+
+def test_auto_two_unknowns():
+    with pytest.raises(ValueError, match="At most one"):
+        _resolve_auto_parallelism({"data": -1, "fsdp": -1, "tensor": 1}, 8)
+
+
+def test_auto_not_divisible():
+    with pytest.raises(ValueError, match="not divisible"):
+        _resolve_auto_parallelism({"data": 3, "fsdp": -1, "tensor": 1}, 8)
+
+
+def test_auto_rejects_zero_and_other_negatives():
+    with pytest.raises(ValueError):
+        _resolve_auto_parallelism({"data": 0, "fsdp": -1, "tensor": 1}, 8)
+    with pytest.raises(ValueError):
+        _resolve_auto_parallelism({"data": -2, "fsdp": 4, "tensor": 1}, 8)
+
+
+# ---- mesh --------------------------------------------------------------------------------------------------------
+def test_mesh_on_one_device():
+    m = create_mesh(MinTextConfig(), devices=[0])
+    assert m.size == 1 and m.shape == {"data": 1, "fsdp": 1, "tensor": 1, "expert": 1}
+
+
+def test_mesh_auto_fsdp_takes_all_devices():
+    assert create_mesh(MinTextConfig(), devices=list(range(4))).shape["fsdp"] == 4
+
+
+def test_mesh_tensor_is_the_fastest_axis():
+    m = create_mesh(MinTextConfig(ici_fsdp_parallelism=2, ici_tensor_parallelism=2), devices=list(range(4)))
+    assert m.ranks_along("tensor", 0) == [0, 1] and m.ranks_along("fsdp", 0) == [0, 2]
+
+
+def test_mesh_coords_round_trip():
+    m = create_mesh(MinTextConfig(ici_data_parallelism=2, ici_fsdp_parallelism=2, ici_tensor_parallelism=2),
+                    devices=list(range(8)))
+    for r in range(8):
+        c = m.coords(r)
+        assert r == (c["data"] * 2 + c["fsdp"]) * 2 + c["tensor"]
+
+
+def test_mesh_ranks_along_contains_the_rank_itself():
+    m = create_mesh(MinTextConfig(ici_data_parallelism=2, ici_fsdp_parallelism=2, ici_tensor_parallelism=2),
+                    devices=list(range(8)))
+    for r in range(8):
+        for axes in ("data", "fsdp", "tensor", ("data", "fsdp")):
+            assert r in m.ranks_along(axes, r)
+
+
+def test_mesh_data_parallel_groups_partition_the_job():
+    m = create_mesh(MinTextConfig(ici_fsdp_parallelism=4, ici_tensor_parallelism=2), devices=list(range(8)))
+    groups = {tuple(m.ranks_along(("data", "fsdp"), r)) for r in range(8)}
+    assert sorted(sum(map(list, groups), [])) == list(range(8)) and len(groups) == 2
+
+
+def test_expert_axis_is_carved_out_of_data_and_fsdp():
+    m = create_mesh(MinTextConfig(ici_expert_parallelism=4), devices=list(range(8)))
+    assert m.shape["expert"] == 4 and m.shape["fsdp"] == 8
+    assert len(m.expert_group_ranks(0)) == 4
+
+
+def test_expert_groups_partition_the_data_parallel_ranks():
+    m = create_mesh(MinTextConfig(ici_expert_parallelism=2), devices=list(range(8)))
+    groups = {tuple(m.expert_group_ranks(r)) for r in range(8)}
+    assert sorted(sum(map(list, groups), [])) == list(range(8)) and all(len(g) == 2 for g in groups)
+
+
+def test_expert_axis_must_divide_the_data_parallel_ranks():
+    with pytest.raises(ValueError, match="ici_expert_parallelism"):
+        create_mesh(MinTextConfig(ici_expert_parallelism=3), devices=list(range(8)))
+
+
+def test_expert_axis_with_tensor_parallelism_counts_only_data_ranks():
+    with pytest.raises(ValueError, match="ici_expert_parallelism"):
+        create_mesh(MinTextConfig(ici_tensor_parallelism=2, ici_expert_parallelism=8), devices=list(range(8)))
+
+
+def test_multi_slice_meshes_are_refused():
+    with pytest.raises(ValueError, match="multi-slice"):
+        create_mesh(MinTextConfig(num_slices=2), devices=[0])
+    with pytest.raises(ValueError, match="multi-slice"):
+        create_mesh(MinTextConfig(dcn_data_parallelism=2), devices=[0, 1])
+
+
+def test_setup_mesh_sets_the_global_mesh():
+    m = setup_mesh(MinTextConfig())
+    assert get_global_mesh() is m
+
+
+# ---- rules and specs ---------------------------------------------------------------------------------------------
+def test_default_rules_cover_the_reference_axes():
+    rules = dict(get_logical_axis_rules(MinTextConfig()))
+    for axis, target in (("batch", "data"), ("embed", "fsdp"), ("mlp", "tensor"), ("heads", "tensor"), ("vocab", "tensor")):
+        assert rules[axis] == target, axis
+
+
+def test_rules_come_from_the_config():
+    c = MinTextConfig(logical_axis_rules=[["embed", "tensor"], ["mlp", None]])
+    assert get_logical_axis_rules(c) == [("embed", "tensor"), ("mlp", None)]
+
+
+@pytest.fixture
+def mesh42():
+    return create_mesh(MinTextConfig(ici_fsdp_parallelism=4, ici_tensor_parallelism=2), devices=list(range(8)))
+
+
+def test_spec_of_a_weight(mesh42):
+    assert logical_to_pspec(("embed", "mlp"), get_logical_axis_rules(MinTextConfig()), mesh42) == ("fsdp", "tensor")
+
+
+def test_spec_with_unsharded_axes(mesh42):
+    assert logical_to_pspec((None, None), get_logical_axis_rules(MinTextConfig()), mesh42) == (None, None)
+
+
+def test_spec_of_a_norm_scale(mesh42):
+    assert logical_to_pspec(("norm",), get_logical_axis_rules(MinTextConfig()), mesh42) == (None,)
+
+
+def test_spec_drops_axes_of_size_one(mesh42):
+    assert logical_to_pspec(("batch",), get_logical_axis_rules(MinTextConfig()), mesh42) == (None,)
+
+
+def test_spec_of_an_unknown_logical_axis(mesh42):
+    assert logical_to_pspec(("no_such_axis",), get_logical_axis_rules(MinTextConfig()), mesh42) == (None,)
+
+
+def test_named_sharding_shard_shape(mesh42):
+    sh = create_named_sharding(mesh42, ("embed", "mlp"), get_logical_axis_rules(MinTextConfig()))
+    assert isinstance(sh, NamedSharding) and sh.shard_shape((64, 32)) == (16, 16)
+
+
+def test_named_sharding_rejects_indivisible_shapes(mesh42):
+    sh = create_named_sharding(mesh42, ("embed", "mlp"), get_logical_axis_rules(MinTextConfig()))
+    with pytest.raises(ValueError):
+        sh.shard_shape((66, 32))
+
+
+def test_named_sharding_slices_tile_the_tensor(mesh42):
+    sh = create_named_sharding(mesh42, ("embed", "mlp"), get_logical_axis_rules(MinTextConfig()))
+    t = torch.arange(16 * 8).view(16, 8)
+    seen = torch.zeros_like(t)
+    for r in range(8):
+        sl = sh.local_slices(t.shape, r)
+        seen[sl] += 1
+        assert torch.equal(sh.shard(t, r), t[sl])
+    assert bool((seen == 1).all())
+
+
+def test_input_sharding_follows_the_batch_rule():
+    c = MinTextConfig(ici_data_parallelism=2, ici_fsdp_parallelism=2)
+    m = create_mesh(c, devices=list(range(4)))
+    assert get_input_data_sharding(c, m).spec[0] == "data"
+
+
+def test_zero1_adds_data_to_an_unsharded_dimension():
+    m = create_mesh(MinTextConfig(ici_data_parallelism=2, ici_fsdp_parallelism=2), devices=list(range(4)))
+    assert add_data_axis_to_sharding(NamedSharding(m, ("fsdp", None))).spec == ("fsdp", "data")
+
+
+def test_zero1_leaves_data_sharded_specs_alone():
+    m = create_mesh(MinTextConfig(ici_data_parallelism=2, ici_fsdp_parallelism=2), devices=list(range(4)))
+    assert add_data_axis_to_sharding(NamedSharding(m, ("data", None))).spec == ("data", None)
+
+
+def test_zero1_compounds_when_every_dimension_is_sharded():
+    m = create_mesh(MinTextConfig(ici_data_parallelism=2, ici_fsdp_parallelism=2), devices=list(range(4)))
+    assert add_data_axis_to_sharding(NamedSharding(m, ("fsdp", "tensor"))).spec == (("data", "fsdp"), "tensor")
+
+
+def test_zero1_on_a_scalar_spec():
+    m = create_mesh(MinTextConfig(ici_data_parallelism=2, ici_fsdp_parallelism=2), devices=list(range(4)))
+    assert add_data_axis_to_sharding(NamedSharding(m, ())).spec == ()
+
+
+def test_zero1_without_a_data_axis_is_the_identity():
+    m = create_mesh(MinTextConfig(), devices=[0])
+    assert add_data_axis_to_sharding(NamedSharding(m, (None, "fsdp"))).spec == (None, "fsdp")
+
+
+# ---- model creation ----------------------------------------------------------------------------------------------
+def test_create_sharded_model_runs():
+    c = MinTextConfig(dtype="float32")
+    model = create_sharded_model(c, setup_mesh(c))
+    out, _ = model(torch.randint(0, c.vocab_size, (2, 6)))
+    assert out.shape == (2, 6, c.vocab_size) and bool(torch.isfinite(out).all())
+
+
+def test_param_shardings_cover_every_parameter():
+    c = MinTextConfig(dtype="float32")
+    mesh = setup_mesh(c)
+    model = create_sharded_model(c, mesh)
+    sh = get_model_param_shardings(model, c, mesh)
+    assert set(sh) == {n for n, _ in model.named_parameters()}
+
+
+def test_param_shardings_follow_the_rules():
+    c = MinTextConfig(dtype="float32")
+    model = create_sharded_model(c, setup_mesh(c))
+    big = create_mesh(MinTextConfig(ici_fsdp_parallelism=2, ici_tensor_parallelism=2), devices=list(range(4)))
+    sh = get_model_param_shardings(model, c, big)
+    assert sh["layers.0.mlp.down.kernel"].spec == ("tensor", "fsdp")
+    assert sh["final_norm.scale"].spec == (None,)
+
+
+# ---- distributed bootstrap ---------------------------------------------------------------------------------------
+def test_initialize_distributed_without_a_launcher():
+    from mintext_b200.parallel.mesh import initialize_distributed
+
+    clean = {k: v for k, v in os.environ.items()
+             if k not in ("WORLD_SIZE", "RANK", "NNODES", "NODE_RANK", "JAX_COORDINATOR_IP", "MASTER_ADDR")}
+    with mock.patch.dict(os.environ, clean, clear=True), mock.patch.object(dist, "is_initialized", return_value=False), \
+            mock.patch.object(dist, "init_process_group") as init:
+        assert initialize_distributed() is False
+        init.assert_not_called()
+
+
+def test_initialize_distributed_when_already_joined():
+    from mintext_b200.parallel.mesh import initialize_distributed
+
+    with mock.patch.object(dist, "is_initialized", return_value=True), \
+            mock.patch.object(dist, "get_world_size", return_value=4), \
+            mock.patch.object(dist, "init_process_group") as init:
+        assert initialize_distributed() is True
+        init.assert_not_called()
+
+
+def test_initialize_distributed_world_of_one_is_not_joined():
+    from mintext_b200.parallel.mesh import initialize_distributed
+
+    with mock.patch.dict(os.environ, {"WORLD_SIZE": "1", "RANK": "0"}), \
+            mock.patch.object(dist, "is_initialized", return_value=False), \
+            mock.patch.object(dist, "init_process_group") as init:
+        assert initialize_distributed() is False
+        init.assert_not_called()
+
+
+# ---- layer scan key ----------------------------------------------------------------------------------------------
+def test_scan_homogeneous_layers():
+    from mintext_b200.models import _all_layers_scannable
+
+    assert _all_layers_scannable(MinTextConfig(num_hidden_layers=4))
+
+
+def test_scan_disabled_by_the_config():
+    from mintext_b200.models import _all_layers_scannable
+
+    assert not _all_layers_scannable(MinTextConfig(scan_layers=False))
+
+
+def test_scan_mixture_of_experts_layers():
+    from mintext_b200.models import _all_layers_scannable
+
+    assert not _all_layers_scannable(MinTextConfig(num_experts=4))
+
+
+def test_scan_mixed_layer_types():
+    from mintext_b200.models import _all_layers_scannable
+
+    assert not _all_layers_scannable(MinTextConfig(model_type="gemma3", num_hidden_layers=6))
+
+
+def test_scanned_and_looped_forward_agree():
+    tok = torch.randint(0, 256, (2, 8))
+    outs = []
+    for scan in (True, False):
+        c = MinTextConfig(dtype="float32", scan_layers=scan, num_hidden_layers=3, vocab_size=256)
+        from mintext_b200.models import Transformer
+
+        outs.append(Transformer(c, rngs=0)(tok)[0])
+    assert outs[0].shape == (2, 8, 256) and torch.allclose(outs[0], outs[1], atol=1e-6)
