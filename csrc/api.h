@@ -114,7 +114,11 @@ void grad_pull_reduce(const PeerPtrs& grads, int rank, int world, int64_t lo, in
 // consumed source elements are cleared on every rank when `clear` is set.  `blocks` caps the grid (<= 0: full device).
 constexpr int kBucketSlots = 1024;
 void grad_pull_bucket(const PeerPtrs& grads, const PeerPtrs& flags, int rank, int world, int bucket, int seq, int64_t lo,
-                      int64_t n, float* out, bool accumulate, bool clear, int blocks, int* status, cudaStream_t stream);
+                      int64_t n, float* out, bool accumulate, bool clear, bool handshake, int blocks, int* status,
+                      cudaStream_t stream);
+// The handshake alone (one warp): post `seq` for `bucket` to every peer and wait for theirs; a reduction launched
+// behind it on the same stream passes handshake = false
+void bucket_ready(const PeerPtrs& flags, int rank, int world, int bucket, int seq, int* status, cudaStream_t stream);
 // AdamW on the local shard, bf16 result stored to params[r][lo..lo+n) of every rank r   (n multiple of 8)
 void adamw_publish(float* master, float* m, float* v, const float* grad, const PeerPtrs& params, int world, int64_t lo,
                    int64_t n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,

@@ -277,13 +277,20 @@ void grad_pull_reduce(const std::vector<int64_t>& grad_ptrs, int64_t rank, int64
 
 void grad_pull_bucket(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& flag_ptrs, int64_t rank,
                       int64_t bucket, int64_t seq, int64_t lo, torch::Tensor& out, bool accumulate, bool clear,
-                      int64_t blocks, torch::Tensor& status) {
+                      bool handshake, int64_t blocks, torch::Tensor& status) {
   TORCH_CHECK(out.scalar_type() == torch::kFloat32 && out.is_contiguous() && out.numel() % 4 == 0 && lo % 4 == 0);
   TORCH_CHECK(grad_ptrs.size() == flag_ptrs.size() && bucket >= 0 && bucket < mt::kBucketSlots);
   c10::cuda::CUDAGuard guard(out.device());
   mt::grad_pull_bucket(to_peers(grad_ptrs), to_peers(flag_ptrs), (int)rank, (int)grad_ptrs.size(), (int)bucket, (int)seq,
-                       lo, out.numel(), out.data_ptr<float>(), accumulate, clear, (int)blocks, status.data_ptr<int>(),
-                       cur_stream());
+                       lo, out.numel(), out.data_ptr<float>(), accumulate, clear, handshake, (int)blocks,
+                       status.data_ptr<int>(), cur_stream());
+}
+
+void bucket_ready(const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t bucket, int64_t seq, torch::Tensor& status) {
+  TORCH_CHECK(bucket >= 0 && bucket < mt::kBucketSlots);
+  c10::cuda::CUDAGuard guard(status.device());
+  mt::bucket_ready(to_peers(flag_ptrs), (int)rank, (int)flag_ptrs.size(), (int)bucket, (int)seq, status.data_ptr<int>(),
+                   cur_stream());
 }
 
 int64_t bucket_flag_slots() { return mt::kBucketSlots; }
@@ -878,6 +885,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grad_pull_reduce", &grad_pull_reduce);
   m.def("grad_pull_bucket", &grad_pull_bucket);
   m.def("bucket_flag_slots", &bucket_flag_slots);
+  m.def("bucket_ready", &bucket_ready);
   m.def("peer_gather", &peer_gather);
   m.def("adamw_publish", &adamw_publish);
   m.def("set_grouped_variant", [](int64_t v) { mt::set_grouped_variant((int)v); });

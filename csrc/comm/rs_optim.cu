@@ -86,15 +86,35 @@ __global__ void grad_pull_reduce_kernel(PeerPtrs grads, int rank, int world, int
   }
 }
 
+// The readiness handshake of one bucket on its own: posts this rank's sequence number to every peer and waits (bounded)
+// for theirs.  One warp: while it waits it holds no shared memory and next to no registers, so it never keeps a compute
+// kernel's blocks off an SM, which a waiting multi-block reduction grid does.
+__global__ void bucket_ready_kernel(PeerPtrs flags, int rank, int world, int bucket, int seq, int* status) {
+  const int peer = threadIdx.x;
+  if (peer >= world) return;
+  __threadfence_system();  // this rank's gradient writes (earlier kernels of the stream) before the post
+  st_release_sys(reinterpret_cast<int*>(flags.p[peer]) + rank * kBucketSlots + bucket, seq);
+  const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + peer * kBucketSlots + bucket;
+  const long long t0 = clock64();
+  while (ld_acquire_sys(mine) < seq) {
+    if (clock64() - t0 > kMaxWaitCycles) {
+      if (status) atomicCAS(status, 0, MT_ERR_TIMEOUT_FLAG);
+      return;
+    }
+  }
+}
+
 // flags: per rank an int[world * kBucketSlots] table in symmetric memory; entry [src * kBucketSlots + bucket] of rank d
 // is the last sequence number rank src posted for that bucket.
 __global__ void grad_pull_bucket_kernel(PeerPtrs grads, PeerPtrs flags, int rank, int world, int bucket, int seq,
                                         int64_t lo, int64_t n, float* __restrict__ out, int accumulate, int clear,
-                                        int* status) {
+                                        int handshake, int* status) {
   __shared__ int give_up;
-  if (threadIdx.x == 0) give_up = 0;
+  // without the handshake a bucket_ready_kernel ran before this one on the same stream; if its wait expired the
+  // status word is set and nothing may be read
+  if (threadIdx.x == 0) give_up = (!handshake && status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
   __syncthreads();
-  if (threadIdx.x < world) {
+  if (handshake && threadIdx.x < world) {
     const int peer = threadIdx.x;
     if (blockIdx.x == 0) {
       __threadfence_system();  // this rank's gradient writes (earlier kernels of the stream) before the post
@@ -213,11 +233,17 @@ void grad_pull_reduce(const PeerPtrs& grads, int rank, int world, int64_t lo, in
 }
 
 void grad_pull_bucket(const PeerPtrs& grads, const PeerPtrs& flags, int rank, int world, int bucket, int seq, int64_t lo,
-                      int64_t n, float* out, bool accumulate, bool clear, int blocks, int* status, cudaStream_t stream) {
+                      int64_t n, float* out, bool accumulate, bool clear, bool handshake, int blocks, int* status,
+                      cudaStream_t stream) {
   if (n == 0 || bucket < 0 || bucket >= kBucketSlots) return;
   if (blocks <= 0) blocks = 148 * 4;
   grad_pull_bucket_kernel<<<blocks, 512, 0, stream>>>(grads, flags, rank, world, bucket, seq, lo, n, out,
-                                                      accumulate ? 1 : 0, clear ? 1 : 0, status);
+                                                      accumulate ? 1 : 0, clear ? 1 : 0, handshake ? 1 : 0, status);
+}
+
+void bucket_ready(const PeerPtrs& flags, int rank, int world, int bucket, int seq, int* status, cudaStream_t stream) {
+  if (bucket < 0 || bucket >= kBucketSlots) return;
+  bucket_ready_kernel<<<1, 32, 0, stream>>>(flags, rank, world, bucket, seq, status);
 }
 
 void adamw_publish(float* master, float* m, float* v, const float* grad, const PeerPtrs& params, int world, int64_t lo,

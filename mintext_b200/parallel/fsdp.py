@@ -239,7 +239,7 @@ class ParamShardedEngine(TrainEngine):
             # ordered with the barrier that follows); every rank clears its own slot once all peers have read it
             ext().grad_pull_bucket(sc.stage_grad_ptrs, sc.bflag_ptrs, self.rank, bidx, self._pull_seq(),
                                    slot * self.stage_len + self.rank * sl, self.grad_shard[loc:loc + sl],
-                                   self._micro_index > 0, False,
+                                   self._micro_index > 0, False, True,
                                    max(sc.pull_blocks, min(296, sl * 4 // (2 << 20))) if sc.overlap_reduce else 0,
                                    status_word(self.device))
             sc.barrier_side()  # every rank has pulled its slice of this slot
@@ -320,7 +320,8 @@ class ParamShardedEngine(TrainEngine):
             _, _, _, loc = self.segments[self._res_index]
             sl = blen // self.world
             ext().grad_pull_bucket(sc.res_grad_ptrs, sc.bflag_ptrs, self.rank, self._res_index, self._round,
-                                   self.rank * sl, self.grad_shard[loc:loc + sl], False, True, 0, status_word(self.device))
+                                   self.rank * sl, self.grad_shard[loc:loc + sl], False, True, True, 0,
+                                   status_word(self.device))
             self._flat_cleared_by_pull = True
         self._pulled, self._late = set(), set()
 

@@ -53,6 +53,7 @@ class SymmetricOptimizerComm:
         self.round = 0            # one per optimizer step; flags carry 2 * round (+ 1 for second pulls)
         self._round_open = False
         self.side_blocks = int(os.environ.get("MT_GRAD_PULL_BLOCKS", "32"))
+        self.split_handshake = os.environ.get("MT_GRAD_PULL_SPLIT_HANDSHAKE", "1") != "0"
         torch.cuda.synchronize(engine.device)
         dist.barrier(group=group)  # flags are zeroed everywhere before the first in-kernel barrier
 
@@ -69,12 +70,17 @@ class SymmetricOptimizerComm:
         ext().grad_pull_reduce(self.grad_ptrs, self.rank, self.rank * e.shard_size, out, e._sumsq_shard)
 
     # -- bucketed reduction, overlapped with the backward pass ---------------------------------------------------
-    def _pull(self, bucket: int, accumulate: bool, blocks: int) -> None:
+    def _pull(self, bucket: int, accumulate: bool, blocks: int, split_handshake: bool = False) -> None:
+        """``split_handshake``: wait for the peers in a one-warp kernel of its own in front of the reduction, so that
+        no multi-block grid sits on SMs while it waits (under the backward pass a waiting block can keep an
+        attention-backward block, which needs the whole register file, off its SM)."""
         e = self.engine
         _, a, b, loc = e.segments[bucket]
         seq = 2 * self.round + (1 if accumulate else 0)
+        if split_handshake:
+            ext().bucket_ready(self.bflag_ptrs, self.rank, bucket, seq, status_word(e.device))
         ext().grad_pull_bucket(self.grad_ptrs, self.bflag_ptrs, self.rank, bucket, seq, a, e.grad_shard[loc:loc + (b - a)],
-                               accumulate, True, blocks, status_word(e.device))
+                               accumulate, True, not split_handshake, blocks, status_word(e.device))
 
     def _open_round(self) -> None:
         if not self._round_open:
@@ -91,7 +97,7 @@ class SymmetricOptimizerComm:
         # the pull finishes under the rest of the backward pass without crowding it
         blocks = max(self.side_blocks, min(296, (b - a) * 4 // (2 << 20)))
         with torch.cuda.stream(self.side):
-            self._pull(bucket, False, blocks)
+            self._pull(bucket, False, blocks, split_handshake=self.split_handshake)
 
     def wait_side_stream(self) -> None:
         torch.cuda.current_stream(self.engine.device).wait_stream(self.side)
