@@ -163,16 +163,13 @@ class DecoderLayer(nn.Module):
             self.post_ffw_norm = RMSNorm(D, eps, dt)
         self.is_linear = layer_type == "linear_attention"
         self.has_moe = config.num_experts > 0 and layer_idx >= config.first_k_dense_replace
-        # Under tensor parallelism the dense attention and MLP shard their weights; sub-layers without a sharded
-        # kernel path are built unsharded and computed in full on every rank of the group (parallel/tp.py).
-        from mintext_b200.parallel import tp as tpm
-
-        tp = tpm.current_tp()
-        tp_on = tp is not None and tp.size > 1
-        self.attn_replicated = tp_on and self.is_linear  # multi-head-latent attention shards its heads (modules/mla.py)
-        self.mlp_replicated = tp_on and self.has_moe
-        if self.attn_replicated:
-            tpm.set_current_tp(None)
+        # Under tensor parallelism the residual stream is sharded over tokens.  Dense attention, multi-head-latent
+        # attention and the Gated Delta Rule shard their heads, dense MLPs (and a mixture-of-experts block's shared
+        # expert) their hidden columns; the router and the routed experts simply work on the rank's own token shard
+        # (the group acts as data parallelism for them).  A sub-layer without any of these paths could still be
+        # computed in full on every rank of the group (parallel/tp.py::run_replicated); none is at present.
+        self.attn_replicated = False
+        self.mlp_replicated = False
         if self.is_linear:
             self.attention = GatedDeltaRuleAttention(config, rngs=rngs)
         elif config.attention_type == "mla":
@@ -184,13 +181,7 @@ class DecoderLayer(nn.Module):
                 config, rngs=rngs, mesh=mesh, use_qk_norm=config.use_qk_norm, sliding_window=sliding,
                 use_gate=(config.model_type == "qwen3_next" and layer_type == "full_attention"),
                 rope_local_theta=local_theta)
-        tpm.set_current_tp(None if self.mlp_replicated else tp)
         self.mlp = MoEBlock(config, rngs=rngs) if self.has_moe else MLP(config, rngs=rngs, mesh=mesh)
-        tpm.set_current_tp(tp)
-        if self.attn_replicated:
-            tpm.mark_replicated(self.attention)
-        if self.mlp_replicated:
-            tpm.mark_replicated(self.mlp)
 
     def _attend(self, h, positions, mask, default_positions):
         if self.attn_replicated:
@@ -254,6 +245,7 @@ class Transformer(nn.Module):
         self.token_embedder.logical_axes = ("vocab", "embed")
         self.layers = nn.ModuleList(
             [DecoderLayer(config, i, rngs=rngs, mesh=mesh) for i in range(config.num_hidden_layers)])
+        self.has_tp_replicated = any(l.attn_replicated or l.mlp_replicated for l in self.layers)
         self.remat_policy = config.remat_policy
         self.final_norm = RMSNorm(D, config.rms_norm_eps, dt)
         self.tie_word_embeddings = config.tie_word_embeddings

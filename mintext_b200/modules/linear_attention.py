@@ -46,39 +46,85 @@ class GatedDeltaRuleAttention(nn.Module):
         self.dt_bias.logical_axes = (None,)
         self.norm = RMSNorm(dv, config.rms_norm_eps, dt)
         self.out_proj = Linear(value_dim, D, dt, wdt, ("mlp", "embed"), rngs=rngs)
+        # Tensor parallelism: key heads (with their value-head groups) are split over the group.  The two input
+        # projections are column-parallel in the grouped per-key-head layout, the output projection row-parallel; the
+        # depth-wise conv weights, A_log, dt_bias and the output norm stay whole on every rank, which uses the rows of
+        # its own heads - its gradient for them is a partial sum that the engine's cross-rank gradient sum completes.
+        from mintext_b200.parallel.tp import current_tp
+
+        self.tp = current_tp() if (current_tp() is not None and current_tp().size > 1) else None
+        self.k_head_lo, self.local_k_heads = 0, Hk
+        if self.tp is not None:
+            lo, hi = self.tp.shard(Hk, "linear_num_key_heads")
+            self.k_head_lo, self.local_k_heads = lo, hi - lo
+            g = self.v_heads_per_k_group
+            per_qkvz, per_ba, per_out = 2 * dk + 2 * g * dv, 2 * g, g * dv
+            for lin, dim, per in ((self.in_proj_qkvz, 1, per_qkvz), (self.in_proj_ba, 1, per_ba), (self.out_proj, 0, per_out)):
+                full = lin.kernel.data
+                axes = lin.kernel.logical_axes
+                a, b = lo * per, hi * per
+                lin.kernel = nn.Parameter((full[:, a:b] if dim == 1 else full[a:b]).clone().contiguous())
+                lin.kernel.logical_axes = axes
+                lin.kernel.tensor_parallel = True
+                lin.kernel.shard_spec = (dim, self.tp.rank, self.tp.size)
+                lin.out_shape = tuple(lin.kernel.shape[len(lin.in_shape):])
+                lin.in_shape = tuple(lin.kernel.shape[:len(lin.in_shape)])
 
     def _split_qkvz(self, qkvz: torch.Tensor):
-        """HF grouped layout: per key head ``[q(dk) | k(dk) | v(g*dv) | z(g*dv)]``."""
+        """HF grouped layout: per key head ``[q(dk) | k(dk) | v(g*dv) | z(g*dv)]`` (this rank's key heads)."""
         B, S, _ = qkvz.shape
+        Hk, Hv = self.local_k_heads, self.local_k_heads * self.v_heads_per_k_group
         vg = self.v_heads_per_k_group * self.value_head_dim
-        grouped = qkvz.reshape(B, S, self.num_k_heads, 2 * self.key_head_dim + 2 * vg)
+        grouped = qkvz.reshape(B, S, Hk, 2 * self.key_head_dim + 2 * vg)
         q, k, v, z = grouped.split([self.key_head_dim, self.key_head_dim, vg, vg], dim=-1)
-        v = v.reshape(B, S, self.num_v_heads, self.value_head_dim)
-        z = z.reshape(B, S, self.num_v_heads, self.value_head_dim)
+        v = v.reshape(B, S, Hv, self.value_head_dim)
+        z = z.reshape(B, S, Hv, self.value_head_dim)
         return q, k, v, z
 
     def _split_ba(self, ba: torch.Tensor):
         B, S, _ = ba.shape
         g = self.v_heads_per_k_group
-        grouped = ba.reshape(B, S, self.num_k_heads, 2 * g)
+        grouped = ba.reshape(B, S, self.local_k_heads, 2 * g)
         b, a = grouped.split([g, g], dim=-1)
-        return b.reshape(B, S, self.num_v_heads), a.reshape(B, S, self.num_v_heads)
+        Hv = self.local_k_heads * g
+        return b.reshape(B, S, Hv), a.reshape(B, S, Hv)
+
+    def _local_head_params(self):
+        """Conv weights, A_log and dt_bias of this rank's heads (all of them without tensor parallelism)."""
+        if self.tp is None:
+            return self.conv_weight, self.A_log, self.dt_bias
+        g, dk, dv = self.v_heads_per_k_group, self.key_head_dim, self.value_head_dim
+        lo, hi = self.k_head_lo, self.k_head_lo + self.local_k_heads
+        key_total = self.num_k_heads * dk
+        cw = self.conv_weight
+        conv = torch.cat([cw[lo * dk:hi * dk], cw[key_total + lo * dk:key_total + hi * dk],
+                          cw[2 * key_total + lo * g * dv:2 * key_total + hi * g * dv]], dim=0)
+        return conv, self.A_log[lo * g:hi * g], self.dt_bias[lo * g:hi * g]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        tp = self.tp
+        if tp is not None:
+            # token-sharded input [1, T/t, D]: gather the group's tokens, run this rank's heads over the full
+            # sequences, scatter the output projection's partial sums back to the token shards
+            from mintext_b200.parallel import tp as tpm
+
+            B, S = tp.batch_shape
+            x = tpm.all_gather_tokens(x.reshape(-1, x.shape[-1]), tp).view(B, S, x.shape[-1])
         B, S, _ = x.shape
+        Hk, Hv = self.local_k_heads, self.local_k_heads * self.v_heads_per_k_group
+        conv_weight, A_log, dt_bias = self._local_head_params()
         q, k, v, z = self._split_qkvz(self.in_proj_qkvz(x))
         b_raw, a = self._split_ba(self.in_proj_ba(x))
         beta = torch.sigmoid(b_raw.float())
-        key_total = self.num_k_heads * self.key_head_dim
-        value_total = self.num_v_heads * self.value_head_dim
+        key_total = Hk * self.key_head_dim
+        value_total = Hv * self.value_head_dim
         qkv = torch.cat([q.reshape(B, S, key_total), k.reshape(B, S, key_total), v.reshape(B, S, value_total)], dim=-1)
-        qkv = F.causal_conv1d_silu(qkv, self.conv_weight if self.conv_weight.dtype == self.dtype
-                                   else self.conv_weight.to(self.dtype))
+        qkv = F.causal_conv1d_silu(qkv, conv_weight if conv_weight.dtype == self.dtype else conv_weight.to(self.dtype))
         qc, kc, vc = qkv.split([key_total, key_total, value_total], dim=-1)
-        qh = qc.reshape(B, S, self.num_k_heads, self.key_head_dim)
-        kh = kc.reshape(B, S, self.num_k_heads, self.key_head_dim)
-        vh = vc.reshape(B, S, self.num_v_heads, self.value_head_dim)
-        g = -torch.exp(self.A_log.float()) * torch.nn.functional.softplus(a.float() + self.dt_bias.float())
+        qh = qc.reshape(B, S, Hk, self.key_head_dim)
+        kh = kc.reshape(B, S, Hk, self.key_head_dim)
+        vh = vc.reshape(B, S, Hv, self.value_head_dim)
+        g = -torch.exp(A_log.float()) * torch.nn.functional.softplus(a.float() + dt_bias.float())
         if self.v_heads_per_k_group > 1:
             qh = qh.repeat_interleave(self.v_heads_per_k_group, dim=2)
             kh = kh.repeat_interleave(self.v_heads_per_k_group, dim=2)
@@ -87,4 +133,9 @@ class GatedDeltaRuleAttention(nn.Module):
             beta.transpose(1, 2), g.transpose(1, 2), chunk_size=self.chunk_size)
         out = out.transpose(1, 2).to(self.dtype)
         out = F.gate_mul(self.norm(out.contiguous()), z.to(self.dtype), "silu")
-        return self.out_proj(out.reshape(B, S, value_total))
+        y = self.out_proj(out.reshape(B, S, value_total))
+        if tp is not None:
+            from mintext_b200.parallel import tp as tpm
+
+            return tpm.reduce_scatter_tokens(y.reshape(B * S, -1), tp).view(1, -1, y.shape[-1])
+        return y

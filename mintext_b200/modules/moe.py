@@ -44,6 +44,21 @@ class MoERouter(nn.Module):
                                                    self.n_group) else oracle
         if self.router_type == "softmax_topk":
             idx, w, probs, aux = impl.router_softmax_topk(logits, self.num_experts_per_tok, self.norm_topk_prob)
+            from mintext_b200.parallel.tp import current_tp
+
+            tp = current_tp()
+            if tp is not None and tp.size > 1:
+                # Token-sharded activations: this rank routed its own share of the group's tokens.  With the
+                # assignment fractions f_e taken over the whole group (a small all-reduce of counts, no gradient) and
+                # the mean probabilities P_e over the rank's tokens, the mean of the ranks' terms is exactly the
+                # auxiliary loss E * sum_e f_e P_e of the group's batch.
+                import torch.distributed as dist
+
+                N, E = probs.shape
+                counts = oracle.histogram(idx, E).float()
+                dist.all_reduce(counts, group=tp.group)
+                f = counts / (N * tp.size * self.num_experts_per_tok)
+                aux = E * (f * probs.mean(0)).sum()
             self.last_aux_loss = aux
             return idx, w, probs
         self.last_aux_loss = None

@@ -117,8 +117,9 @@ def setup_training(config: MinTextConfig):
         from mintext_b200.parallel.tp import TensorParallel, set_current_tp
 
         if config.ici_expert_parallelism > 1:
-            raise NotImplementedError("expert parallelism and tensor parallelism cannot be combined: experts are "
-                                      "computed in full on every rank of a tensor-parallel group")
+            raise NotImplementedError("expert parallelism and tensor parallelism cannot be combined: the engine reduces "
+                                      "tensor-parallel slices and expert slices over one replica group, and the two "
+                                      "would need different ones")
         set_current_tp(TensorParallel(mesh.group(("tensor",)), device, fused=config.fused_collectives))
         if mesh.shape["data"] * mesh.shape["fsdp"] > 1:
             local_reduce_group = mesh.group(("data", "fsdp"))

@@ -154,13 +154,16 @@ def compute_loss(params, model, config, batch, loss_scale: float | None = None):
         if "aux_loss" in aux and config.router_aux_loss_coef > 0:
             aux_loss = aux["aux_loss"] if aux_loss is None else aux_loss + aux["aux_loss"]
     if aux_loss is not None:
-        # under tensor parallelism the router runs on the whole batch on every rank of the group while the token
-        # loss is this rank's share; the engine averages the ranks' gradients, so the replicated term counts
-        # group-size times here
-        from mintext_b200.parallel.tp import current_tp
+        # Sub-layers that a tensor-parallel group computes in full on every rank (parallel/tp.py::run_replicated;
+        # none at present) form the auxiliary loss of the whole batch on every rank while the token loss is the rank's
+        # share; the engine averages the ranks' gradients, so such a replicated term counts group-size times here.
+        # Token-sharded routers contribute their own share, like the token loss.
+        rep = 1.0
+        if getattr(model, "has_tp_replicated", False):
+            from mintext_b200.parallel.tp import current_tp
 
-        tp = current_tp()
-        rep = float(tp.size) if (tp is not None and tp.size > 1) else 1.0
+            tp = current_tp()
+            rep = float(tp.size) if (tp is not None and tp.size > 1) else 1.0
         term = config.router_aux_loss_coef * aux_loss * (scale * ntok)
         reported = (loss + term).detach()          # what a single process would report
         loss = loss + term * rep

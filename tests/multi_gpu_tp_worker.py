@@ -14,7 +14,7 @@ import torch.distributed as dist
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 
-MIXED = {  # families whose attention / feed-forward has no sharded path: computed in full on every rank
+MIXED = {  # families with multi-head-latent attention / Gated Delta Rule layers and mixture-of-experts blocks
     "deepseek": dict(model_type="deepseek_v3", attention_type="mla", q_lora_rank=128, kv_lora_rank=128,
                      qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, num_experts=8, num_experts_per_tok=2,
                      moe_intermediate_size=128, n_group=4, topk_group=2, first_k_dense_replace=1, n_shared_experts=1),

@@ -145,10 +145,10 @@ def test_tensor_parallel_fused_kernels(tmp_path):
 
 
 @pytest.mark.parametrize("kind", ["deepseek", "qwen3_next"])
-def test_tensor_parallel_with_replicated_sublayers_matches_single_gpu(tmp_path, kind):
-    """Families whose attention (multi-head latent, Gated Delta Rule) or feed-forward (mixture of experts) has no
-    sharded path train under tensor parallelism with those sub-layers computed in full on every rank; the dense
-    attention / MLP layers between them stay sharded.  Losses follow the single-GPU run."""
+def test_tensor_parallel_mla_gdn_and_expert_families_match_single_gpu(tmp_path, kind):
+    """Families with multi-head-latent attention, Gated Delta Rule layers and mixture-of-experts blocks train under
+    tensor parallelism: heads split over the group, routers and routed experts on each rank's token shard, shared
+    experts column / row parallel.  Losses follow the single-GPU run."""
     world = 2
     if torch.cuda.device_count() < world:
         pytest.skip("needs 2 GPUs")

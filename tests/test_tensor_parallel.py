@@ -103,9 +103,10 @@ def _qwen3_next_worker(rank, world):
 
 
 def _check_mixed(kind, worker, port):
-    """Sub-layers without a sharded path (MLA, Gated Delta Rule, experts) run in full on every rank: their gradients
-    are the same on all ranks and count once after the 1/tp scaling the engine applies; everything else follows the
-    token-sharded rules.  Together they give the single-process gradient of mean loss (+ auxiliary loss)."""
+    """Attention variants shard their heads, routers and routed experts work on each rank's token shard (their
+    gradients are per-shard contributions like a norm scale's), shared experts shard their hidden columns.  Together
+    they give the single-process gradient of mean loss (+ auxiliary loss).  A sub-layer computed in full on every rank
+    (none at present) would show identical gradients that count once after the engine's 1/tp scaling."""
     from mintext_b200 import trainer
     from mintext_b200.models import Transformer
 
@@ -117,7 +118,7 @@ def _check_mixed(kind, worker, port):
     named = [(n, p) for n, p in m.named_parameters() if p.requires_grad]
     ref = dict(zip([n for n, _ in named], torch.autograd.grad(loss, [p for _, p in named], allow_unused=True)))
     replicated = res[0][2]
-    assert replicated, "some sub-layer should have been computed replicated"
+    assert not replicated, f"no sub-layer should need the replicated fallback: {sorted(replicated)}"
     for name, g in ref.items():
         parts = [res[r][1][name] for r in range(world)]
         if g is None:
@@ -134,11 +135,11 @@ def _check_mixed(kind, worker, port):
         assert torch.allclose(got, g, atol=5e-5), (name, (got - g).abs().max())
 
 
-def test_tensor_parallel_with_replicated_mla_and_experts():
+def test_tensor_parallel_with_head_sharded_mla_and_token_sharded_experts():
     _check_mixed("deepseek", _deepseek_worker, 29633)
 
 
-def test_tensor_parallel_with_replicated_gdn_experts_and_aux_loss():
+def test_tensor_parallel_with_head_sharded_gdn_token_sharded_experts_and_aux_loss():
     _check_mixed("qwen3_next", _qwen3_next_worker, 29635)
 
 
@@ -190,3 +191,57 @@ def test_head_sharded_mla_matches_single_process():
             dim = next(i for i, (a, b) in enumerate(zip(parts[0].shape, g.shape)) if a != b)
             got = torch.cat(parts, dim=dim) / world
         assert torch.allclose(got, g, atol=2e-5), name
+
+
+def _gdn_cfg():
+    return MinTextConfig(dtype="float32", vocab_size=64, num_hidden_layers=2, hidden_size=32, num_attention_heads=4,
+                         num_key_value_heads=2, intermediate_size=64, seq_length=16, model_type="qwen3_next",
+                         use_qk_norm=True, full_attention_interval=2, partial_rotary_factor=0.5, linear_key_head_dim=8,
+                         linear_value_head_dim=8, linear_num_key_heads=2, linear_num_value_heads=4)
+
+
+def _gdn_tp_worker(rank, world):
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.tp import TensorParallel, set_current_tp
+
+    set_current_tp(TensorParallel(dist.group.WORLD, torch.device("cpu"), fused=False))
+    try:
+        cfg = _gdn_cfg()
+        m = Transformer(cfg, rngs=0)
+        att = m.layers[0].attention
+        # one of two key heads (with its two value heads) per rank: q 8 + k 8 + v 16 + z 16 columns, 2 x (b, a), 16 rows
+        assert att.in_proj_qkvz.kernel.shape == (32, 48) and att.in_proj_ba.kernel.shape == (32, 4)
+        assert att.out_proj.kernel.shape == (16, 32)
+        assert att.conv_weight.shape[0] == 2 * 16 + 32 and att.A_log.shape == (4,)   # whole on every rank
+        assert not any(getattr(p, "tp_replicated_compute", False) for p in m.parameters())
+        loss, _ = trainer.compute_loss(None, m, cfg, _batch())
+        names = [n for n, _ in m.named_parameters()]
+        grads = torch.autograd.grad(loss, list(m.parameters()))
+        return float(loss), {n: g.clone() for n, g in zip(names, grads)}
+    finally:
+        set_current_tp(None)
+
+
+def test_head_sharded_gated_delta_rule_matches_single_process():
+    """Gated Delta Rule layers with their key heads (and value-head groups) split over two ranks: the loss and every
+    gradient equal the single-process model's; conv weights, A_log, dt_bias and the output norm stay whole and collect
+    one partial sum per rank's heads."""
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+
+    world = 2
+    res = run_ranks(_gdn_tp_worker, world, 29637)
+    cfg = _gdn_cfg()
+    m = Transformer(cfg, rngs=0)
+    loss, _ = trainer.compute_loss(None, m, cfg, _batch())
+    ref = dict(zip([n for n, _ in m.named_parameters()], torch.autograd.grad(loss, list(m.parameters()))))
+    assert abs(sum(res[r][0] for r in range(world)) / world - float(loss)) < 1e-5
+    for name, g in ref.items():
+        parts = [res[r][1][name] for r in range(world)]
+        if parts[0].shape == g.shape:
+            got = sum(parts) / world
+        else:
+            dim = next(i for i, (a, b) in enumerate(zip(parts[0].shape, g.shape)) if a != b)
+            got = torch.cat(parts, dim=dim) / world
+        assert torch.allclose(got, g, atol=2e-5), (name, float((got - g).abs().max()))
