@@ -71,3 +71,12 @@ def test_model_configs_shrink_and_train(tmp_path, model):
         over.update(sliding_window=8)
     last = train(load_config(paths, over))
     assert last["loss"] == last["loss"]
+
+
+def test_cpu_plumbing_config_runs_ten_steps_and_learns():
+    """The shipped CPU plumbing config (tiny Llama-style decoder, fp32, batch 8 x 128, AdamW, 10 steps)."""
+    cfg = load_config(ROOT / "configs" / "benchmarks" / "test-tiny-cpu.yml")
+    assert (cfg.num_hidden_layers, cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads) == (2, 128, 4, 2)
+    assert (cfg.vocab_size, cfg.per_device_batch_size, cfg.seq_length, cfg.steps) == (1024, 8, 128, 10)
+    last = train(cfg)
+    assert last["step"] == 9 and last["loss"] == last["loss"] and last["loss"] < 7.5
