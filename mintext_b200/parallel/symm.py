@@ -23,6 +23,16 @@ import torch.distributed as dist
 from mintext_b200.ops._ext import ext, status_word
 
 
+def multicast_available(handle) -> bool:
+    """Whether the symmetric-memory rendezvous bound the buffer to an NVLink multicast object (NVLS): the handle then
+    carries a multicast address that `multimem` instructions could use.  This repository's kernels do not (they use
+    plain peer loads and stores); the probe only reports what the platform offers, once, at start-up."""
+    try:
+        return bool(int(getattr(handle, "multicast_ptr", 0) or 0))
+    except Exception:
+        return False
+
+
 class SymmetricOptimizerComm:
     def __init__(self, engine):
         import torch.distributed._symmetric_memory as symm
@@ -54,6 +64,13 @@ class SymmetricOptimizerComm:
         self._round_open = False
         self.side_blocks = int(os.environ.get("MT_GRAD_PULL_BLOCKS", "32"))
         self.split_handshake = os.environ.get("MT_GRAD_PULL_SPLIT_HANDSHAKE", "1") != "0"
+        self.multicast = multicast_available(self._h_grad)
+        if self.rank == 0:
+            import logging
+
+            logging.getLogger(__name__).info("peer-memory optimizer path: %d ranks, NVLink multicast %s (not used: "
+                                             "peer loads / stores only)", self.world,
+                                             "available" if self.multicast else "not available")
         torch.cuda.synchronize(engine.device)
         dist.barrier(group=group)  # flags are zeroed everywhere before the first in-kernel barrier
 

@@ -307,3 +307,22 @@ def test_scanned_and_looped_forward_agree():
 
         outs.append(Transformer(c, rngs=0)(tok)[0])
     assert outs[0].shape == (2, 8, 256) and torch.allclose(outs[0], outs[1], atol=1e-6)
+
+
+# ---- NVLink multicast probe --------------------------------------------------------------------------------------
+def test_multicast_probe_reads_the_handle_and_never_raises():
+    from mintext_b200.parallel.symm import multicast_available
+
+    class Plain:
+        multicast_ptr = 0
+
+    class Bound:
+        multicast_ptr = 0x7F0000000000
+
+    class Broken:
+        @property
+        def multicast_ptr(self):
+            raise RuntimeError("driver says no")
+
+    assert not multicast_available(Plain()) and multicast_available(Bound())
+    assert not multicast_available(object()) and not multicast_available(Broken())

@@ -279,3 +279,26 @@ def test_gradient_accumulation_needs_divisible_batches(setup):
     params = {n: p for n, p in m.named_parameters() if p.requires_grad}
     with pytest.raises(ValueError):
         accumulate_gradients(lambda _p, mb: trainer.compute_loss(_p, m, c, mb), params, batch(c, B=6), 4)
+
+
+# ---- determinism -------------------------------------------------------------------------------------------------
+def test_same_seed_gives_the_same_run_bit_for_bit():
+    """Two runs of the plain-PyTorch trainer from the same seeds produce identical losses and parameters."""
+    runs = []
+    for _ in range(2):
+        c = cfg(learning_rate=1e-2)
+        m = Transformer(c, rngs=0)
+        st = trainer.create_train_state(m, c)
+        losses = []
+        for s in range(4):
+            st, met = trainer.train_step(st, batch(c, seed=s), m, c)
+            losses.append(float(met["loss"]))
+        runs.append((losses, {n: p.detach().clone() for n, p in st.params.items()}))
+    assert runs[0][0] == runs[1][0]
+    assert all(torch.equal(runs[0][1][n], runs[1][1][n]) for n in runs[0][1])
+
+
+def test_a_different_seed_gives_a_different_model():
+    c = cfg()
+    a, b = Transformer(c, rngs=0), Transformer(c, rngs=1)
+    assert not torch.equal(a.token_embedder, b.token_embedder)
