@@ -23,7 +23,6 @@ The rule for which GPU holds which batch rows: the global batch is split evenly 
 from __future__ import annotations
 
 import json
-import math
 import os
 from dataclasses import dataclass
 

@@ -122,7 +122,6 @@ class ParamShardedEngine(TrainEngine):
 
     def _alloc_sharded_group(self, big: list, buckets: list, total_b: int) -> None:
         dev = self.device
-        W = self.world
         if len(buckets) < 2:
             raise ValueError("fsdp_shard_params needs per-layer buckets (a decoder with at least one layer)")
         self.param_flat = None
@@ -173,9 +172,6 @@ class ParamShardedEngine(TrainEngine):
         import torch.distributed._symmetric_memory as symm
 
         return symm.empty(numel, dtype=dtype, device=self.device)
-
-    def memory_per_parameter_note(self) -> str:
-        return "layer weights and layer gradients sharded 1/N; two staging slots of one layer each"
 
     # ------------------------------------------------------------------ weight gathers
     def _issue_gather(self, layer: int) -> None:
