@@ -94,13 +94,19 @@ class TrainEngine:
     """
 
     def __init__(self, model: torch.nn.Module, config, device: torch.device | str = "cuda", group=None,
-                 local_reduce_group=None):
+                 local_reduce_group=None, expert_reduce_group=None):
         """``group``: ranks over which replicated parameters are reduced and the optimizer state is sharded
         (default: all ranks).  ``local_reduce_group``: ranks that hold *the same* slice of the expert- or
-        tensor-parallel parameters (their data-parallel replicas); None when every rank's slice is unique."""
+        tensor-parallel parameters (their data-parallel replicas); None when every rank's slice is unique.
+        ``expert_reduce_group``: given when tensor and expert parallelism are combined, where the two kinds of
+        slices have different replicas (tensor slices: the ranks of the same tensor coordinate; expert slices: the
+        ranks at the same expert position, across the tensor axis): then ``local_reduce_group`` serves the tensor
+        slices and this group the expert slices."""
         self.config = config
         self.local_reduce_group = local_reduce_group
         self.local_reduce_size = dist.get_world_size(local_reduce_group) if local_reduce_group is not None else 1
+        self.expert_reduce_group = expert_reduce_group
+        self.expert_reduce_size = dist.get_world_size(expert_reduce_group) if expert_reduce_group is not None else 1
         self.model = model
         self.device = torch.device(device)
         self.group = group
@@ -203,6 +209,18 @@ class TrainEngine:
         self._alloc_sharded_group(big, buckets, total_b)
 
         # expert-parallel parameters: every rank owns its experts outright (compute copy, master, moments, grads)
+        self._exp_split = None
+        if exp and self.expert_reduce_group is not None:
+            # tensor slices first, expert slices behind them: two contiguous ranges with their own replica groups
+            exp.sort(key=lambda sl: bool(getattr(sl.param, "expert_parallel", False)))
+            off_e = 0
+            for sl in exp:
+                if self._exp_split is None and getattr(sl.param, "expert_parallel", False):
+                    self._exp_split = off_e
+                sl.offset = off_e
+                off_e = _round_up(off_e + sl.numel, _ALIGN)
+            if self._exp_split is None:
+                self._exp_split = off_e
         self.exp = FlatGroup(exp, _round_up(max(off_e, 4), _ALIGN))
         if exp:
             self.exp_master = torch.zeros(self.exp.total, device=dev, dtype=torch.float32)
@@ -452,12 +470,14 @@ class TrainEngine:
             self._sumsq.zero_()
             e.sumsq(gshard, self._sumsq)
         if self.exp.slots:
-            # slices are disjoint across ranks up to their data-parallel replicas: count each slice once
-            if self.local_reduce_group is not None:
-                dist.all_reduce(self.exp_grad, group=self.local_reduce_group)
-            tmp = torch.zeros_like(self._sumsq)
-            e.sumsq(self.exp_grad, tmp)
-            self._sumsq.add_(tmp / self.local_reduce_size)
+            # slices are disjoint across ranks up to their replicas: sum over the replicas, count each slice once
+            for lo, hi, grp, size in self._exp_ranges():
+                seg = self.exp_grad[lo:hi]
+                if grp is not None:
+                    dist.all_reduce(seg, group=grp)
+                tmp = torch.zeros_like(self._sumsq)
+                e.sumsq(seg, tmp)
+                self._sumsq.add_(tmp / size)
         if W > 1:
             dist.all_reduce(self._sumsq, group=self.group)
         e.sumsq(self.small_grad, self._sumsq)
@@ -538,13 +558,26 @@ class TrainEngine:
         upd = (self.small_m / bc1) / ((self.small_v / bc2).sqrt() + cfg.adam_eps)
         self.small_param.add_(upd + cfg.weight_decay * self.small_wd * self.small_param, alpha=-lr)
 
+    def _exp_ranges(self):
+        """Ranges of the rank-local (tensor- / expert-parallel) flat buffers with the group that holds replicas of
+        them and its size: one range normally, two when tensor and expert parallelism are combined."""
+        total = self.exp.total
+        if self._exp_split is None:
+            return [(0, total, self.local_reduce_group, self.local_reduce_size)]
+        out = []
+        if self._exp_split > 0:
+            out.append((0, self._exp_split, self.local_reduce_group, self.local_reduce_size))
+        if self._exp_split < total:
+            out.append((self._exp_split, total, self.expert_reduce_group, self.expert_reduce_size))
+        return out
+
     def param_norm(self) -> torch.Tensor:
         s = torch.zeros(1, device=self.device, dtype=torch.float32)
         ext().sumsq(self.master, s)
-        if self.exp.slots:
+        for lo, hi, _, size in (self._exp_ranges() if self.exp.slots else ()):
             tmp = torch.zeros_like(s)
-            ext().sumsq(self.exp_master, tmp)
-            s.add_(tmp / self.local_reduce_size)
+            ext().sumsq(self.exp_master[lo:hi], tmp)
+            s.add_(tmp / size)
         if self.world > 1:
             dist.all_reduce(s, group=self.group)
         ext().sumsq(self.small_param, s)
@@ -646,10 +679,15 @@ class TrainEngine:
         }
         # expert- / tensor-parallel parameters: this rank's slice along the parameter's shard dimension; of the
         # data-parallel replicas that hold the same slice only the first writes it
-        first_replica = self.local_reduce_group is None or dist.get_rank(self.local_reduce_group) == 0
+        def first_replica(slot) -> bool:
+            grp = self.local_reduce_group
+            if self._exp_split is not None and slot.offset >= self._exp_split:
+                grp = self.expert_reduce_group
+            return grp is None or dist.get_rank(grp) == 0
+
         for s in self.exp.slots:
             dim, idx, cnt = getattr(s.param, "shard_spec", (0, self.rank, self.world))
-            meta = {"writer_rank": self.rank if first_replica else -1, "shard": (int(dim), int(idx), int(cnt)),
+            meta = {"writer_rank": self.rank if first_replica(s) else -1, "shard": (int(dim), int(idx), int(cnt)),
                     "suffix": f".shard{idx}of{cnt}"}
             sl = slice(s.offset, s.offset + s.numel)
             tree[f"params/{s.name}"] = {"tensor": self.exp_master[sl].view(s.param.shape), **meta}

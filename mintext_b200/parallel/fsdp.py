@@ -92,7 +92,7 @@ class ParamShardedEngine(TrainEngine):
 
     sharded_params = True
 
-    def __init__(self, model, config, device="cuda", group=None, local_reduce_group=None):
+    def __init__(self, model, config, device="cuda", group=None, local_reduce_group=None, expert_reduce_group=None):
         if not (dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1):
             raise ValueError("fsdp_shard_params needs more than one rank")
         if config.optimizer != "adamw" or not bool(config.fused_collectives) or config.torch_dtype != torch.bfloat16:
@@ -102,7 +102,8 @@ class ParamShardedEngine(TrainEngine):
 
         if current_tp() is not None and current_tp().size > 1:
             raise ValueError("fsdp_shard_params is not combined with tensor parallelism")
-        super().__init__(model, config, device=device, group=group, local_reduce_group=local_reduce_group)
+        super().__init__(model, config, device=device, group=group, local_reduce_group=local_reduce_group,
+                         expert_reduce_group=expert_reduce_group)
         from mintext_b200.models import transformer as tfm
 
         self._sc = _ShardedComm(self)

@@ -112,21 +112,27 @@ def setup_training(config: MinTextConfig):
 
         set_current_ep(ExpertParallel(mesh.group(("expert",)), device, config.moe_capacity_factor,
                                       fused=config.fused_collectives))
-    local_reduce_group = None
-    if config.ici_tensor_parallelism > 1:
+    # Replica groups for the parameters a rank holds a slice of: tensor slices are replicated on the ranks of the same
+    # tensor coordinate, expert slices on the ranks at the same expert position (across the tensor axis too, since the
+    # routed experts treat a tensor-parallel group as data parallelism).
+    local_reduce_group = expert_reduce_group = None
+    tp_on = config.ici_tensor_parallelism > 1
+    ep_on = config.ici_expert_parallelism > 1 and config.num_experts > 0
+    dp = mesh.shape["data"] * mesh.shape["fsdp"]
+    if tp_on:
         from mintext_b200.parallel.tp import TensorParallel, set_current_tp
 
-        if config.ici_expert_parallelism > 1:
-            raise NotImplementedError("expert parallelism and tensor parallelism cannot be combined: the engine reduces "
-                                      "tensor-parallel slices and expert slices over one replica group, and the two "
-                                      "would need different ones")
         set_current_tp(TensorParallel(mesh.group(("tensor",)), device, fused=config.fused_collectives))
-        if mesh.shape["data"] * mesh.shape["fsdp"] > 1:
+        if dp > 1:
             local_reduce_group = mesh.group(("data", "fsdp"))
-    elif config.ici_expert_parallelism > 1 and config.num_experts > 0:
-        dp = mesh.shape["data"] * mesh.shape["fsdp"]
-        if dp > config.ici_expert_parallelism:
-            local_reduce_group = _expert_replica_group(mesh, config.ici_expert_parallelism)
+    if ep_on:
+        replicas = dp // config.ici_expert_parallelism * mesh.shape["tensor"]
+        if replicas > 1:
+            group = _expert_replica_group(mesh, config.ici_expert_parallelism)
+            if tp_on:
+                expert_reduce_group = group
+            else:
+                local_reduce_group = group
     init_device = device if (use_gpu and _device_init_wanted(config)) else None
     model = create_sharded_model(config, mesh, init_device=init_device)
     if use_gpu:
@@ -134,7 +140,8 @@ def setup_training(config: MinTextConfig):
             from mintext_b200.parallel.fsdp import ParamShardedEngine as Engine
         else:
             from mintext_b200.parallel.engine import TrainEngine as Engine
-        state = Engine(model, config, device=device, local_reduce_group=local_reduce_group)
+        state = Engine(model, config, device=device, local_reduce_group=local_reduce_group,
+                       expert_reduce_group=expert_reduce_group)
     else:
         from mintext_b200 import trainer
 
@@ -142,17 +149,26 @@ def setup_training(config: MinTextConfig):
     return mesh, model, state, device, use_gpu
 
 
+def _expert_replica_ranks(mesh, ep: int, rank: int) -> tuple[int, ...]:
+    """Ranks that hold the same experts as ``rank``: the rank at the same position of every expert-parallel block of
+    the batch-sharding ranks, in every tensor column."""
+    dp = mesh.ranks_along(("data", "fsdp"), rank)
+    pos = dp.index(rank) % ep
+    members = []
+    for column_peer in mesh.ranks_along("tensor", rank):
+        members.extend(mesh.ranks_along(("data", "fsdp"), column_peer)[pos::ep])
+    return tuple(sorted(members))
+
+
 def _expert_replica_group(mesh, ep: int):
-    """Ranks that hold the same experts: one from every expert-parallel block of the batch-sharding ranks."""
+    """Process group of :func:`_expert_replica_ranks` for the calling rank (every rank creates every group)."""
     import torch.distributed as dist
 
     rank = dist.get_rank()
     mine = None
     seen = set()
     for r in range(mesh.size):
-        dp = mesh.ranks_along(("data", "fsdp"), r)
-        pos = dp.index(r) % ep
-        members = tuple(dp[pos::ep])
+        members = _expert_replica_ranks(mesh, ep, r)
         if members in seen:
             continue
         seen.add(members)

@@ -326,3 +326,65 @@ def test_multicast_probe_reads_the_handle_and_never_raises():
 
     assert not multicast_available(Plain()) and multicast_available(Bound())
     assert not multicast_available(object()) and not multicast_available(Broken())
+
+
+# ---- replica groups of expert slices -----------------------------------------------------------------------------
+def test_expert_replicas_without_tensor_parallelism():
+    from mintext_b200.train import _expert_replica_ranks
+
+    m = create_mesh(MinTextConfig(ici_expert_parallelism=2), devices=list(range(8)))
+    # expert-parallel blocks (0,1) (2,3) (4,5) (6,7): position 0 of each block holds the same experts
+    assert _expert_replica_ranks(m, 2, 0) == (0, 2, 4, 6) and _expert_replica_ranks(m, 2, 5) == (1, 3, 5, 7)
+
+
+def test_expert_replicas_span_the_tensor_axis():
+    from mintext_b200.train import _expert_replica_ranks
+
+    m = create_mesh(MinTextConfig(ici_fsdp_parallelism=4, ici_tensor_parallelism=2, ici_expert_parallelism=2),
+                    devices=list(range(8)))
+    # tensor column 0 = ranks 0,2,4,6 with expert blocks (0,2) (4,6); column 1 = ranks 1,3,5,7 likewise
+    assert m.expert_group_ranks(0) == [0, 2] and m.expert_group_ranks(5) == [5, 7]
+    assert _expert_replica_ranks(m, 2, 0) == (0, 1, 4, 5)      # position 0 of every block, both columns
+    assert _expert_replica_ranks(m, 2, 6) == (2, 3, 6, 7)
+    groups = {_expert_replica_ranks(m, 2, r) for r in range(8)}
+    assert sorted(sum(map(list, groups), [])) == list(range(8))
+
+
+def test_expert_replicas_when_every_data_rank_is_its_own_expert_position():
+    from mintext_b200.train import _expert_replica_ranks
+
+    m = create_mesh(MinTextConfig(ici_fsdp_parallelism=2, ici_tensor_parallelism=2, ici_expert_parallelism=2),
+                    devices=list(range(4)))
+    assert _expert_replica_ranks(m, 2, 0) == (0, 1) and _expert_replica_ranks(m, 2, 3) == (2, 3)
+
+
+def test_engine_lays_tensor_slices_before_expert_slices_when_both_have_replica_groups():
+    """With tensor and expert parallelism combined the rank-local flat buffers hold the tensor slices first and the
+    expert slices behind them, so that each range is reduced over its own replica group (storage layout only: runs on
+    the CPU with stand-in groups)."""
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.engine import TrainEngine
+
+    c = MinTextConfig(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, vocab_size=128,
+                      intermediate_size=128, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, n_group=2,
+                      topk_group=1, first_k_dense_replace=1, n_shared_experts=1)
+    model = Transformer(c, rngs=0)
+    for n, p in model.named_parameters():
+        if ".experts." in n:
+            p.expert_parallel = True
+        elif ".attention." in n and p.dim() >= 2:
+            p.tensor_parallel = True
+    with mock.patch.object(dist, "get_world_size", side_effect=lambda g=None: {"tp_replicas": 2, "ep_replicas": 4}[g]):
+        eng = TrainEngine(model, c, device="cpu", local_reduce_group="tp_replicas", expert_reduce_group="ep_replicas")
+    kinds = [bool(getattr(s.param, "expert_parallel", False)) for s in eng.exp.slots]
+    assert kinds == sorted(kinds) and any(kinds) and not all(kinds)
+    first_expert = next(s for s in eng.exp.slots if getattr(s.param, "expert_parallel", False))
+    assert eng._exp_split == first_expert.offset
+    ranges = eng._exp_ranges()
+    assert [(lo, hi) for lo, hi, _, _ in ranges] == [(0, eng._exp_split), (eng._exp_split, eng.exp.total)]
+    assert [(g, n) for _, _, g, n in ranges] == [("tp_replicas", 2), ("ep_replicas", 4)]
+    # offsets are back to back and every parameter views its own range of the flat buffers
+    for s in eng.exp.slots:
+        assert s.param.data_ptr() == eng.exp_param[s.offset:].data_ptr()
+    plain = TrainEngine(Transformer(c, rngs=0), c, device="cpu")
+    assert plain._exp_split is None and plain._exp_ranges() == [(0, plain.exp.total, None, 1)]

@@ -245,3 +245,76 @@ def test_head_sharded_gated_delta_rule_matches_single_process():
             dim = next(i for i, (a, b) in enumerate(zip(parts[0].shape, g.shape)) if a != b)
             got = torch.cat(parts, dim=dim) / world
         assert torch.allclose(got, g, atol=2e-5), (name, float((got - g).abs().max()))
+
+
+def _tp_ep_cfg():
+    return MinTextConfig(dtype="float32", vocab_size=64, num_hidden_layers=2, hidden_size=32, num_attention_heads=4,
+                         num_key_value_heads=2, intermediate_size=64, seq_length=16, model_type="deepseek_v3",
+                         attention_type="mla", q_lora_rank=16, kv_lora_rank=16, qk_nope_head_dim=8, qk_rope_head_dim=8,
+                         v_head_dim=8, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=16, n_group=2,
+                         topk_group=1, first_k_dense_replace=1, n_shared_experts=1, ici_fsdp_parallelism=2,
+                         ici_tensor_parallelism=2, ici_expert_parallelism=2)
+
+
+def _global_batch():
+    t = torch.randint(0, 64, (4, 16), generator=torch.Generator().manual_seed(5))
+    return {"input_tokens": t, "target_tokens": t.roll(-1, 1)}
+
+
+def _tp_ep_worker(rank, world):
+    """4 ranks = 2 data-parallel groups x 2 tensor-parallel ranks; experts split over the 2 ranks of each tensor
+    column (expert parallelism inside the data-parallel ranks)."""
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.ep import ExpertParallel, set_current_ep
+    from mintext_b200.parallel.mesh import create_mesh
+    from mintext_b200.parallel.tp import TensorParallel, set_current_tp
+
+    cfg = _tp_ep_cfg()
+    mesh = create_mesh(cfg)
+    set_current_ep(ExpertParallel(mesh.group(("expert",)), torch.device("cpu"), fused=False))
+    set_current_tp(TensorParallel(mesh.group(("tensor",)), torch.device("cpu"), fused=False))
+    try:
+        m = Transformer(cfg, rngs=0)
+        assert m.layers[1].mlp.experts.gate_up_proj.shape[0] == 2          # half of the experts
+        assert m.layers[1].mlp.shared_expert.gate.kernel.shape == (32, 8)  # half of the shared expert's columns
+        dp = rank // 2
+        b = {k: v[2 * dp:2 * dp + 2] for k, v in _global_batch().items()}
+        loss, _ = trainer.compute_loss(None, m, cfg, b)
+        named = [(n, p) for n, p in m.named_parameters() if p.requires_grad]
+        grads = torch.autograd.grad(loss, [p for _, p in named], allow_unused=True)
+        return float(loss), {n: (g.clone() if g is not None else None) for (n, _), g in zip(named, grads)}
+    finally:
+        set_current_tp(None)
+        set_current_ep(None)
+
+
+def test_tensor_and_expert_parallelism_together_match_single_process():
+    """Token-sharded tensor parallelism with the routed experts split over the data-parallel ranks of each tensor
+    column: the mean of the ranks' losses and the assembled gradients equal the single-process model on the global
+    batch (expert slices are replicated across the tensor axis, tensor slices across the data axis)."""
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+
+    res = run_ranks(_tp_ep_worker, 4, 29641)
+    cfg = _tp_ep_cfg().model_copy(update={"ici_fsdp_parallelism": 1, "ici_tensor_parallelism": 1,
+                                          "ici_expert_parallelism": 1})
+    m = Transformer(cfg, rngs=0)
+    loss, _ = trainer.compute_loss(None, m, cfg, _global_batch())
+    named = [(n, p) for n, p in m.named_parameters() if p.requires_grad]
+    ref = dict(zip([n for n, _ in named], torch.autograd.grad(loss, [p for _, p in named], allow_unused=True)))
+    assert abs(sum(res[r][0] for r in range(4)) / 4 - float(loss)) < 1e-5
+    rank_of = lambda dp, j: 2 * dp + j
+    for name, g in ref.items():
+        parts = [res[r][1][name] for r in range(4)]
+        if g is None:
+            assert all(p is None for p in parts), name
+            continue
+        if parts[0].shape == g.shape:                       # whole on every rank: per-rank contributions
+            got = sum(parts) / 4
+        elif ".experts." in name:                           # expert block p lives on data rank p of both tensor columns
+            got = torch.cat([sum(parts[rank_of(p, j)] for j in range(2)) / 4 for p in range(2)], dim=0)
+        else:                                               # tensor slice j lives on tensor rank j of both data ranks
+            dim = next(i for i, (a, b) in enumerate(zip(parts[0].shape, g.shape)) if a != b)
+            got = torch.cat([sum(parts[rank_of(dp, j)] for dp in range(2)) / 4 for j in range(2)], dim=dim)
+        assert torch.allclose(got, g, atol=5e-5), (name, float((got - g).abs().max()))
