@@ -159,6 +159,7 @@ __global__ void adamw_publish_kernel(float* __restrict__ master, float* __restri
                                      float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
                                      float grad_scale, const float* __restrict__ clip_coef) {
   const float gs = clip_coef ? grad_scale * (*clip_coef) : grad_scale;
+  const float rbc1 = __fdiv_rn(1.f, bc1), rbc2 = __fdiv_rn(1.f, bc2);  // IEEE-rounded, as in optim/adamw.cu
   const int64_t nvec = n >> 3;  // 8 elements = one 16-byte bf16 store per peer
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
     float g[8], mm[8], vv[8], pp[8];
@@ -178,7 +179,7 @@ __global__ void adamw_publish_kernel(float* __restrict__ master, float* __restri
       const float gj = g[j] * gs;
       mm[j] = b1 * mm[j] + (1.f - b1) * gj;
       vv[j] = b2 * vv[j] + (1.f - b2) * gj * gj;
-      pp[j] -= lr * ((mm[j] / bc1) / (sqrtf(vv[j] / bc2) + eps) + wd * pp[j]);
+      pp[j] -= lr * (__fdiv_rn(mm[j] * rbc1, __fsqrt_rn(vv[j] * rbc2) + eps) + wd * pp[j]);
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {

@@ -2,6 +2,8 @@
 // One pass reads grad (fp32 or bf16), m, v, master and writes m, v, master and the bf16 compute copy, so the
 // separate fp32->bf16 weight cast of a mixed-precision step disappears.  Update rule (optax.adamw semantics):
 //   m <- b1 m + (1-b1) g ; v <- b2 v + (1-b2) g^2 ; p <- p - lr * ( (m/bc1) / (sqrt(v/bc2) + eps) + wd * p )
+// The square root and the division of the update are the IEEE-rounded intrinsics: the build's fast-math flag would
+// otherwise turn them into approximations, and the optimizer is where an error repeats every step.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <cstdint>
@@ -16,6 +18,7 @@ __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, 
                              float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
                              const float* __restrict__ clip_coef) {
   const float gs = clip_coef ? grad_scale * (*clip_coef) : grad_scale;
+  const float rbc1 = __fdiv_rn(1.f, bc1), rbc2 = __fdiv_rn(1.f, bc2);
   const int64_t nvec = n >> 2;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
     float g[4];
@@ -37,7 +40,7 @@ __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, 
       const float gj = g[j] * gs;
       mp[j] = b1 * mp[j] + (1.f - b1) * gj;
       vp[j] = b2 * vp[j] + (1.f - b2) * gj * gj;
-      const float upd = (mp[j] / bc1) / (sqrtf(vp[j] / bc2) + eps) + wd * ppp[j];
+      const float upd = __fdiv_rn(mp[j] * rbc1, __fsqrt_rn(vp[j] * rbc2) + eps) + wd * ppp[j];
       ppp[j] -= lr * upd;
     }
     reinterpret_cast<float4*>(m)[i] = mm;
@@ -59,7 +62,7 @@ __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, 
                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(grad)[i])) * gs;
     const float mj = b1 * m[i] + (1.f - b1) * gj;
     const float vj = b2 * v[i] + (1.f - b2) * gj * gj;
-    const float upd = (mj / bc1) / (sqrtf(vj / bc2) + eps) + wd * master[i];
+    const float upd = __fdiv_rn(mj * rbc1, __fsqrt_rn(vj * rbc2) + eps) + wd * master[i];
     const float p = master[i] - lr * upd;
     m[i] = mj; v[i] = vj; master[i] = p;
     if (pbf) pbf[i] = __float2bfloat16(p);
