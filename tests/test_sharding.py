@@ -204,3 +204,48 @@ def test_engine_segments_cover_the_flat_buffer_once():
             local += sl
         assert local == per_rank
     assert set(covered) == {1}
+
+
+# ------------------------------------------------------------------ process groups of the shipped benchmark configs
+def _benchmark_groups(rank, world):
+    """What ``setup_training`` builds between the mesh and the engine for every shipped benchmark config, on 8 ranks:
+    tensor group, expert group and the replica groups of rank-local slices; one all-reduce per group proves it works."""
+    from pathlib import Path
+
+    from mintext_b200.config import load_config
+    from mintext_b200.train import _expert_replica_group
+
+    out = {}
+    root = Path(__file__).resolve().parents[1] / "configs" / "benchmarks"
+    for f in sorted(root.glob("*.yml")):
+        c = load_config(f)
+        m = create_mesh(c)
+        sizes = {}
+        dp = m.shape["data"] * m.shape["fsdp"]
+        groups = {}
+        if c.ici_tensor_parallelism > 1:
+            groups["tensor"] = m.group(("tensor",))
+            if dp > 1:
+                groups["tensor_replicas"] = m.group(("data", "fsdp"))
+        if c.ici_expert_parallelism > 1 and c.num_experts > 0:
+            groups["expert"] = m.group(("expert",))
+            if dp // c.ici_expert_parallelism * m.shape["tensor"] > 1:
+                groups["expert_replicas"] = _expert_replica_group(m, c.ici_expert_parallelism)
+        for name, g in groups.items():
+            t = torch.ones(1)
+            dist.all_reduce(t, group=g)
+            sizes[name] = int(t.item())
+        out[f.name] = (dict(m.shape), sizes)
+    return out
+
+
+def test_benchmark_configs_build_their_process_groups_on_eight_ranks():
+    res = run_ranks(_benchmark_groups, 8, 29651)
+    for r in range(8):
+        assert res[r] == res[0]  # every rank sees groups of the same sizes
+    got = res[0]
+    assert got["llama-3-8b-b200.yml"] == ({"data": 1, "fsdp": 4, "tensor": 2, "expert": 1},
+                                          {"tensor": 2, "tensor_replicas": 4})
+    assert got["qwen3-30b-a3b-b200.yml"] == ({"data": 1, "fsdp": 8, "tensor": 1, "expert": 8}, {"expert": 8})
+    assert got["deepseek-v3-4l-b200.yml"] == ({"data": 1, "fsdp": 8, "tensor": 1, "expert": 8}, {"expert": 8})
+    assert got["llama-3.2-1b-b200.yml"] == ({"data": 1, "fsdp": 8, "tensor": 1, "expert": 1}, {})
