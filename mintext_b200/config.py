@@ -234,8 +234,10 @@ class MinTextConfig(BaseModel):
     logical_axis_rules: list[tuple[str, str | None]] = []
     fused_collectives: bool = True  # peer-memory kernels for the sharded optimizer step; False: NCCL composition
     # layer weights and layer gradients sharded 1/N over data x fsdp (gathered one layer ahead, reduce-scattered per
-    # layer) instead of resident on every rank: parallel/fsdp.py
-    fsdp_shard_params: bool = False
+    # layer) instead of resident on every rank: parallel/fsdp.py.  "auto": sharded when the resident copies (2 + 4 bytes
+    # per parameter a rank holds) would exceed `fsdp_resident_budget_gb` per GPU.
+    fsdp_shard_params: bool | str = False
+    fsdp_resident_budget_gb: float = 60.0
 
     # checkpoints
     enable_checkpointing: bool = True
@@ -281,6 +283,20 @@ class MinTextConfig(BaseModel):
     @classmethod
     def _rope_alias(cls, v: Any) -> Any:
         return "llama3" if v == "llama3_1" else v
+
+    @field_validator("fsdp_shard_params", mode="before")
+    @classmethod
+    def _normalise_shard_mode(cls, v):
+        if isinstance(v, str):
+            low = v.strip().lower()
+            if low in ("true", "1", "yes"):
+                return True
+            if low in ("false", "0", "no", ""):
+                return False
+            if low == "auto":
+                return "auto"
+            raise ValueError(f"fsdp_shard_params must be true, false or auto, got '{v}'")
+        return v
 
     @field_validator(*_POSITIVE)
     @classmethod
@@ -374,6 +390,8 @@ def _reject_unknown(keys: Iterable[str]) -> None:
 
 
 def _coerce_env(key: str, raw: str, current: Any, present: bool) -> Any:
+    if key == "fsdp_shard_params" and raw.strip().lower() == "auto":
+        return "auto"
     if isinstance(current, bool) or (current is None and present):
         low = raw.lower()
         if low in ("true", "1", "yes"):

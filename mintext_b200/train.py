@@ -136,7 +136,9 @@ def setup_training(config: MinTextConfig):
     init_device = device if (use_gpu and _device_init_wanted(config)) else None
     model = create_sharded_model(config, mesh, init_device=init_device)
     if use_gpu:
-        if config.fsdp_shard_params:
+        from mintext_b200.utils.pytree import wants_sharded_params
+
+        if wants_sharded_params(config, mesh.size):
             from mintext_b200.parallel.fsdp import ParamShardedEngine as Engine
         else:
             from mintext_b200.parallel.engine import TrainEngine as Engine

@@ -87,6 +87,39 @@ def estimate_param_count(config) -> float:
     return float(emb + attn * L + ffn)
 
 
+def resident_param_bytes_per_rank(config) -> float:
+    """Bytes a rank holds in the resident engine mode for the bf16 compute copy and the fp32 gradient accumulator
+    (6 per parameter): dense parameters in full (divided by the tensor-parallel degree where they are sliced: an
+    upper bound, embeddings are not), routed experts divided by the expert-parallel degree."""
+    total = estimate_param_count(config)
+    experts = 0.0
+    if config.num_experts > 0:
+        moe_layers = max(0, config.num_hidden_layers - config.first_k_dense_replace)
+        experts = 3.0 * config.hidden_size * config.moe_intermediate_size * config.num_experts * moe_layers
+    ep = max(int(getattr(config, "ici_expert_parallelism", 1) or 1), 1)
+    dense = (total - experts) / _tensor_parallel_degree(config)
+    return 6.0 * (dense + experts / ep)
+
+
+def wants_sharded_params(config, world: int) -> bool:
+    """Decision behind ``fsdp_shard_params``: explicit true / false, or ``"auto"``: shard when there is more than one
+    data-parallel rank to shard over, the configuration is one the sharded mode covers (AdamW, bf16, peer-memory
+    collectives, no tensor parallelism) and the resident copies would take more than ``fsdp_resident_budget_gb``."""
+    mode = config.fsdp_shard_params
+    if isinstance(mode, str):
+        low = mode.strip().lower()
+        if low in ("true", "1", "yes"):
+            return True
+        if low in ("false", "0", "no", ""):
+            return False
+        if low != "auto":
+            raise ValueError(f"fsdp_shard_params must be true, false or auto, got '{mode}'")
+        covered = (world > 1 and str(config.optimizer) == "adamw" and bool(config.fused_collectives)
+                   and str(config.dtype) == "bfloat16" and _tensor_parallel_degree(config) == 1)
+        return covered and resident_param_bytes_per_rank(config) > float(config.fsdp_resident_budget_gb) * 2 ** 30
+    return bool(mode)
+
+
 def _tensor_parallel_degree(config) -> int:
     return max(int(getattr(config, "ici_tensor_parallelism", 1) or 1), 1)
 

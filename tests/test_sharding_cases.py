@@ -388,3 +388,76 @@ def test_engine_lays_tensor_slices_before_expert_slices_when_both_have_replica_g
         assert s.param.data_ptr() == eng.exp_param[s.offset:].data_ptr()
     plain = TrainEngine(Transformer(c, rngs=0), c, device="cpu")
     assert plain._exp_split is None and plain._exp_ranges() == [(0, plain.exp.total, None, 1)]
+
+
+# ---- resident or parameter-sharded engine ------------------------------------------------------------------------
+def _llama8b(**kw):
+    base = dict(num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                intermediate_size=14336, vocab_size=128256)
+    base.update(kw)
+    return MinTextConfig(**base)
+
+
+def test_resident_bytes_count_six_per_parameter():
+    from mintext_b200.utils.pytree import estimate_param_count, resident_param_bytes_per_rank
+
+    c = _llama8b()
+    assert resident_param_bytes_per_rank(c) == pytest.approx(6 * estimate_param_count(c))
+    halved = resident_param_bytes_per_rank(_llama8b(ici_tensor_parallelism=2, ici_fsdp_parallelism=1))
+    assert halved == pytest.approx(3 * estimate_param_count(c))
+
+
+def test_resident_bytes_divide_the_experts_by_the_expert_axis():
+    from mintext_b200.utils.pytree import resident_param_bytes_per_rank
+
+    moe = dict(num_experts=64, num_experts_per_tok=4, moe_intermediate_size=1024, first_k_dense_replace=0)
+    one = resident_param_bytes_per_rank(_llama8b(**moe))
+    eight = resident_param_bytes_per_rank(_llama8b(**moe, ici_expert_parallelism=8))
+    experts = 6.0 * 3 * 4096 * 1024 * 64 * 32
+    assert one - eight == pytest.approx(experts * 7 / 8)
+
+
+def test_explicit_flag_decides():
+    from mintext_b200.utils.pytree import wants_sharded_params
+
+    assert wants_sharded_params(_llama8b(fsdp_shard_params=True), 8)
+    assert not wants_sharded_params(_llama8b(fsdp_shard_params=False), 8)
+    assert _llama8b(fsdp_shard_params="true").fsdp_shard_params is True
+    assert _llama8b(fsdp_shard_params="No").fsdp_shard_params is False
+
+
+def test_auto_shards_when_the_resident_copy_exceeds_the_budget():
+    from mintext_b200.utils.pytree import wants_sharded_params
+
+    big = _llama8b(fsdp_shard_params="auto", fsdp_resident_budget_gb=40.0)     # 8 B parameters x 6 bytes = 45 GB
+    roomy = _llama8b(fsdp_shard_params="auto", fsdp_resident_budget_gb=60.0)
+    assert wants_sharded_params(big, 8) and not wants_sharded_params(roomy, 8)
+
+
+def test_auto_stays_resident_where_the_sharded_mode_does_not_apply():
+    from mintext_b200.utils.pytree import wants_sharded_params
+
+    tight = dict(fsdp_shard_params="auto", fsdp_resident_budget_gb=1.0)
+    assert not wants_sharded_params(_llama8b(**tight), 1)                                   # nothing to shard over
+    assert not wants_sharded_params(_llama8b(**tight, optimizer="muon"), 8)
+    assert not wants_sharded_params(_llama8b(**tight, fused_collectives=False), 8)
+    assert not wants_sharded_params(_llama8b(**tight, ici_tensor_parallelism=2, ici_fsdp_parallelism=4), 8)
+    assert wants_sharded_params(_llama8b(**tight), 8)
+
+
+def test_unknown_mode_is_rejected():
+    with pytest.raises(ValueError, match="true, false or auto"):
+        _llama8b(fsdp_shard_params="sometimes")
+
+
+def test_auto_from_the_environment(tmp_path, monkeypatch):
+    import yaml
+
+    from mintext_b200.config import load_config
+
+    p = tmp_path / "c.yml"
+    p.write_text(yaml.safe_dump({"steps": 1}))
+    monkeypatch.setenv("MINTEXT_FSDP_SHARD_PARAMS", "auto")
+    assert load_config(p).fsdp_shard_params == "auto"
+    monkeypatch.setenv("MINTEXT_FSDP_SHARD_PARAMS", "true")
+    assert load_config(p).fsdp_shard_params is True
