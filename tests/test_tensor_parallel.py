@@ -318,3 +318,38 @@ def test_tensor_and_expert_parallelism_together_match_single_process():
             dim = next(i for i, (a, b) in enumerate(zip(parts[0].shape, g.shape)) if a != b)
             got = torch.cat([sum(parts[rank_of(dp, j)] for dp in range(2)) / 4 for j in range(2)], dim=dim)
         assert torch.allclose(got, g, atol=5e-5), (name, float((got - g).abs().max()))
+
+
+def _setup_training_worker(rank, world):
+    """``setup_training`` on 4 CPU ranks with tensor x expert parallelism: contexts, replica groups, model; then one
+    loss evaluation through the trainer."""
+    from mintext_b200 import trainer
+    from mintext_b200.parallel.ep import current_ep, set_current_ep
+    from mintext_b200.parallel.tp import current_tp, set_current_tp
+    from mintext_b200.train import setup_training
+
+    cfg = _tp_ep_cfg().model_copy(update={"kernel_backend": "oracle", "enable_tensorboard": False,
+                                          "enable_checkpointing": False})
+    try:
+        mesh, model, state, device, use_gpu = setup_training(cfg)
+        assert not use_gpu and device.type == "cpu"
+        assert current_tp().size == 2 and current_ep().size == 2
+        assert dict(mesh.shape) == {"data": 1, "fsdp": 2, "tensor": 2, "expert": 2}
+        dp = rank // 2
+        b = {k: v[2 * dp:2 * dp + 2] for k, v in _global_batch().items()}
+        loss, _ = trainer.compute_loss(None, model, cfg, b)
+        return float(loss)
+    finally:
+        set_current_tp(None)
+        set_current_ep(None)
+
+
+def test_setup_training_builds_tensor_and_expert_contexts_together():
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+
+    res = run_ranks(_setup_training_worker, 4, 29645)
+    cfg = _tp_ep_cfg().model_copy(update={"ici_fsdp_parallelism": 1, "ici_tensor_parallelism": 1,
+                                          "ici_expert_parallelism": 1})
+    loss, _ = trainer.compute_loss(None, Transformer(cfg, rngs=0), cfg, _global_batch())
+    assert abs(sum(res.values()) / 4 - float(loss)) < 1e-5
