@@ -238,6 +238,10 @@ class MinTextConfig(BaseModel):
     # per parameter a rank holds) would exceed `fsdp_resident_budget_gb` per GPU.
     fsdp_shard_params: bool | str = False
     fsdp_resident_budget_gb: float = 60.0
+    # under tensor parallelism: shard the embedding table and the output head over the vocabulary as well (the
+    # reference's `vocab -> tensor` rule): parallel/vocab_parallel.py.  Off: both are whole on every rank of the group
+    # and work on the rank's token shard through the fused projection + loss kernel.
+    tp_vocab_parallel: bool = False
 
     # checkpoints
     enable_checkpointing: bool = True

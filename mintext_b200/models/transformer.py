@@ -252,6 +252,25 @@ class Transformer(nn.Module):
         if not config.tie_word_embeddings:
             self.output_proj = Linear(D, V, dt, wdt, ("embed", "vocab"), rngs=rngs)
         self._use_scan = _all_layers_scannable(config)
+        # vocabulary-parallel ends (parallel/vocab_parallel.py): this rank keeps rows [v_lo, v_hi) of the embedding
+        # table and the same columns of the output projection
+        from mintext_b200.parallel.tp import current_tp
+
+        tp = current_tp()
+        self.vocab_parallel = bool(getattr(config, "tp_vocab_parallel", False)) and tp is not None and tp.size > 1
+        if self.vocab_parallel:
+            from mintext_b200.parallel.vocab_parallel import shard_vocab_rows
+
+            owners = [(self, "token_embedder", 0)]
+            if not config.tie_word_embeddings:
+                owners.append((self.output_proj, "kernel", 1))
+            for owner, attr, dim in owners:
+                full = getattr(owner, attr)
+                local = nn.Parameter(shard_vocab_rows(full.data, tp, dim))
+                local.logical_axes = full.logical_axes
+                local.tensor_parallel = True
+                local.shard_spec = (dim, tp.rank, tp.size)
+                setattr(owner, attr, local)
 
     # the output head as (weight, weight_is_[vocab, hidden]) for the fused projection + loss path
     def output_weight(self) -> tuple[torch.Tensor, bool]:
@@ -276,7 +295,12 @@ class Transformer(nn.Module):
             tp.batch_shape = (B, S)
             lo, hi = tp.shard(B * S, "tokens per batch")
             tokens = tokens.reshape(1, B * S)[:, lo:hi]
-        x = F.embedding(self.token_embedder, tokens, dt, self.embedding_scale)
+        if self.vocab_parallel:
+            from mintext_b200.parallel import vocab_parallel as vp
+
+            x = vp.embedding(self.token_embedder, tokens, tp, dt, self.embedding_scale)
+        else:
+            x = F.embedding(self.token_embedder, tokens, dt, self.embedding_scale)
         all_aux = []
         pending = None
         fuse = REMAT_POLICIES[self.remat_policy] is None or not torch.is_grad_enabled()
@@ -294,6 +318,10 @@ class Transformer(nn.Module):
             x = self.final_norm(x)
         if return_hidden:
             return x, all_aux
+        if self.vocab_parallel:
+            raise NotImplementedError("with tp_vocab_parallel no rank holds the whole output head: ask for the hidden "
+                                      "states (return_hidden=True) and score them with "
+                                      "parallel.vocab_parallel.linear_cross_entropy, as trainer.compute_loss does")
         if self.tie_word_embeddings:
             logits = F.linear_nt(x, self.token_embedder, dtype=dt)
         else:

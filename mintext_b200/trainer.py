@@ -110,18 +110,28 @@ def compute_loss(params, model, config, batch, loss_scale: float | None = None):
     if config.attn_logit_softcapping is not None and not tokens.is_cuda:
         mask = make_causal_mask(S).to(tokens.device)
     fused = F.use_cuda(model.final_norm.scale.new_empty(0, dtype=config.torch_dtype)) and tokens.is_cuda
-    hidden_mode = fused or config.num_vocab_tiles > 1
-    out, aux_list = model(tokens, None, mask, return_hidden=hidden_mode)
     from mintext_b200.parallel.tp import current_tp
 
     tp = current_tp()
+    vocab_parallel = bool(getattr(model, "vocab_parallel", False))
+    hidden_mode = fused or config.num_vocab_tiles > 1 or vocab_parallel
+    out, aux_list = model(tokens, None, mask, return_hidden=hidden_mode)
     if tp is not None and tp.size > 1:  # the model returned this rank's token shard
         lo, hi = tp.shard(B * S, "tokens per batch")
         targets = targets.reshape(1, B * S)[:, lo:hi]
         B, S = 1, hi - lo
     ntok = B * S
     scale = loss_scale if loss_scale is not None else 1.0 / ntok
-    if fused:
+    if vocab_parallel:  # the head is sharded over the vocabulary: softmax statistics are reduced over the group
+        from mintext_b200.parallel.vocab_parallel import linear_cross_entropy as vp_linear_cross_entropy
+
+        w, is_vd = model.output_weight()
+        per_tok, z = vp_linear_cross_entropy(
+            out.reshape(ntok, -1), w, targets.reshape(-1), tp, is_vd, config.label_smoothing, config.z_loss_weight,
+            config.final_logit_softcapping, chunks=max(int(config.num_vocab_tiles), 1))
+        per_tok, z = per_tok.view(B, S), z.view(B, S)
+        loss = per_tok.sum() * scale
+    elif fused:
         w, is_vd = model.output_weight()
         per_tok, z = F.linear_cross_entropy(
             out.reshape(ntok, -1), w, targets.reshape(-1), weight_is_vd=is_vd,

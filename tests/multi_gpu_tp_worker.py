@@ -23,6 +23,8 @@ MIXED = {  # families with multi-head-latent attention / Gated Delta Rule layers
                        linear_num_value_heads=4, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
                        n_group=1, topk_group=1, first_k_dense_replace=0, router_type="softmax_topk",
                        shared_expert_gate=True, n_shared_experts=1, router_aux_loss_coef=0.01),
+    # embedding table and output head sharded over the vocabulary as well (z-loss on, so every softmax reduction counts)
+    "vocab_parallel": dict(tp_vocab_parallel=True, z_loss_weight=1e-4),
 }
 
 

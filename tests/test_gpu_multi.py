@@ -144,11 +144,12 @@ def test_tensor_parallel_fused_kernels(tmp_path):
         assert abs(a - b) < 1e-2
 
 
-@pytest.mark.parametrize("kind", ["deepseek", "qwen3_next"])
+@pytest.mark.parametrize("kind", ["deepseek", "qwen3_next", "vocab_parallel"])
 def test_tensor_parallel_mla_gdn_and_expert_families_match_single_gpu(tmp_path, kind):
     """Families with multi-head-latent attention, Gated Delta Rule layers and mixture-of-experts blocks train under
     tensor parallelism: heads split over the group, routers and routed experts on each rank's token shard, shared
-    experts column / row parallel.  Losses follow the single-GPU run."""
+    experts column / row parallel.  Losses follow the single-GPU run.  ``vocab_parallel``: a dense model whose
+    embedding table and output head are sharded over the vocabulary too."""
     world = 2
     if torch.cuda.device_count() < world:
         pytest.skip("needs 2 GPUs")

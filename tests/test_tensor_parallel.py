@@ -353,3 +353,83 @@ def test_setup_training_builds_tensor_and_expert_contexts_together():
                                           "ici_expert_parallelism": 1})
     loss, _ = trainer.compute_loss(None, Transformer(cfg, rngs=0), cfg, _global_batch())
     assert abs(sum(res.values()) / 4 - float(loss)) < 1e-5
+
+
+VOCAB_PARALLEL = {
+    "plain": dict(),
+    "tied_smoothing_zloss": dict(tie_word_embeddings=True, label_smoothing=0.1, z_loss_weight=1e-3, num_vocab_tiles=3),
+    "softcap_scaled": dict(final_logit_softcapping=5.0, scale_embeddings=True, z_loss_weight=1e-3,
+                           num_key_value_heads=4),
+}
+
+
+def _vp_cfg(kind):
+    return _cfg().model_copy(update=dict(tp_vocab_parallel=True, **VOCAB_PARALLEL[kind]))
+
+
+def _vp_worker(rank, world, kind):
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+    from mintext_b200.parallel.tp import TensorParallel, set_current_tp
+
+    set_current_tp(TensorParallel(dist.group.WORLD, torch.device("cpu"), fused=False))
+    try:
+        cfg = _vp_cfg(kind)
+        m = Transformer(cfg, rngs=0)
+        assert m.vocab_parallel and m.token_embedder.shape == (64 // world, 32)
+        assert m.token_embedder.shard_spec == (0, rank, world) and m.token_embedder.tensor_parallel
+        if not cfg.tie_word_embeddings:
+            assert m.output_proj.kernel.shape == (32, 64 // world) and m.output_proj.kernel.shard_spec == (1, rank, world)
+        loss, aux = trainer.compute_loss(None, m, cfg, _batch())
+        names = [n for n, _ in m.named_parameters()]
+        grads = torch.autograd.grad(loss, list(m.parameters()))
+        return float(loss), {n: g.clone() for n, g in zip(names, grads)}, float(aux["z_loss"])
+    finally:
+        set_current_tp(None)
+
+
+def _vp_plain(rank, world):
+    return _vp_worker(rank, world, "plain")
+
+
+def _vp_tied(rank, world):
+    return _vp_worker(rank, world, "tied_smoothing_zloss")
+
+
+def _vp_softcap(rank, world):
+    return _vp_worker(rank, world, "softcap_scaled")
+
+
+def _check_vocab_parallel(kind, worker, world, port):
+    from mintext_b200 import trainer
+    from mintext_b200.models import Transformer
+
+    res = run_ranks(worker, world, port)
+    cfg = _vp_cfg(kind).model_copy(update={"tp_vocab_parallel": False})
+    m = Transformer(cfg, rngs=0)
+    loss, aux = trainer.compute_loss(None, m, cfg, _batch())
+    ref = dict(zip([n for n, _ in m.named_parameters()], torch.autograd.grad(loss, list(m.parameters()))))
+    assert abs(sum(res[r][0] for r in range(world)) / world - float(loss)) < 1e-5
+    assert abs(sum(res[r][2] for r in range(world)) / world - float(aux["z_loss"])) < 1e-6
+    for name, g in ref.items():
+        parts = [res[r][1][name] for r in range(world)]
+        if parts[0].shape == g.shape:
+            got = sum(parts) / world
+        else:
+            dim = next(i for i, (a, b) in enumerate(zip(parts[0].shape, g.shape)) if a != b)
+            got = torch.cat(parts, dim=dim) / world
+        assert torch.allclose(got, g, atol=2e-5), (name, (got - g).abs().max())
+    for name in ("token_embedder",) + (() if cfg.tie_word_embeddings else ("output_proj.kernel",)):
+        assert res[0][1][name].shape != ref[name].shape, f"{name} should be sharded over the vocabulary"
+
+
+def test_vocab_parallel_embedding_and_head_match_single_process():
+    _check_vocab_parallel("plain", _vp_plain, 2, 29651)
+
+
+def test_vocab_parallel_tied_weights_label_smoothing_z_loss_and_token_chunks():
+    _check_vocab_parallel("tied_smoothing_zloss", _vp_tied, 2, 29653)
+
+
+def test_vocab_parallel_soft_capped_logits_on_four_ranks():
+    _check_vocab_parallel("softcap_scaled", _vp_softcap, 4, 29655)
