@@ -302,3 +302,24 @@ def test_a_different_seed_gives_a_different_model():
     c = cfg()
     a, b = Transformer(c, rngs=0), Transformer(c, rngs=1)
     assert not torch.equal(a.token_embedder, b.token_embedder)
+
+
+def test_quantised_weight_cache_follows_parameter_changes():
+    """The cache of quantised weight copies is reused while the weights are unchanged and rebuilt after an in-place
+    write, after a declared change (optimizer kernels write through raw pointers) and for another tensor."""
+    from mintext_b200.ops import functional as F
+
+    cache, made = F.QuantisedWeightCache(), []
+
+    def make():
+        made.append(len(made))
+        return made[-1]
+
+    w = torch.zeros(4, 4)
+    assert cache.get((w,), make) == 0 and cache.get((w,), make) == 0 and len(made) == 1
+    w.add_(1.0)                       # in-place write through torch: the tensor's version counter moves
+    assert cache.get((w,), make) == 1
+    F.bump_weight_version()           # a kernel wrote the parameters through raw pointers
+    assert cache.get((w,), make) == 2 and cache.get((w,), make) == 2
+    assert cache.get((torch.zeros(4, 4),), make) == 3          # another tensor
+    assert cache.get((w, w), make) == 4                        # another set of tensors
