@@ -3,7 +3,8 @@
 Parity target: ``mintext/config.py`` of the reference (field names, defaults, derived fields, validation
 messages, override priority CLI > ``MINTEXT_<KEY>`` environment > YAML with recursive ``base_config``).
 Differences: the YAML layer is PyYAML (no OmegaConf), several config files can be merged left to right,
-``torch_dtype`` / ``torch_weight_dtype`` replace the jnp dtype properties, and there are extra keys for the
+``torch_dtype`` / ``torch_weight_dtype`` (also under the reference's names ``jnp_dtype`` / ``jnp_weight_dtype``) return
+torch dtypes, and there are extra keys for the
 parallel modes the reference does not have (expert parallelism, router type, fp8 recipe ...).
 """
 
@@ -281,6 +282,10 @@ class MinTextConfig(BaseModel):
         import torch
 
         return getattr(torch, self.weight_dtype)
+
+    # the reference's property names (mintext/config.py: jnp_dtype / jnp_weight_dtype); the values are torch dtypes
+    jnp_dtype = torch_dtype
+    jnp_weight_dtype = torch_weight_dtype
 
     # ------------------------------------------------------------------ validation
     @field_validator("rope_type", mode="before")

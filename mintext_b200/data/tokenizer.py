@@ -5,7 +5,11 @@ from __future__ import annotations
 
 
 class Tokenizer:
-    def __init__(self, name_or_path: str, tokenizer_type: str = "auto"):
+    def __init__(self, path: str, type: str = "auto"):  # noqa: A002 - the reference's argument names
+        """``type``: ``huggingface`` | ``sentencepiece`` | ``auto`` (a ``.model`` file is SentencePiece)."""
+        name_or_path, tokenizer_type = path, type
+        if tokenizer_type not in ("auto", "huggingface", "sentencepiece"):
+            raise ValueError(f"Unknown tokenizer type: {tokenizer_type}")
         self._sp = None
         self._hf = None
         if tokenizer_type == "sentencepiece" or (tokenizer_type == "auto" and str(name_or_path).endswith(".model")):

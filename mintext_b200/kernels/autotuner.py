@@ -82,19 +82,19 @@ def _time_grouped(x, w, sizes, tiling, warmup, iters) -> float:
     return (time.perf_counter() - t0) / iters
 
 
-def autotune_moe(cfg: MoETuningConfig, cache_dir: str | None = None, max_trials: int = 20, warmup_iters: int = 3,
+def autotune_moe(config: MoETuningConfig, cache_dir: str | None = None, max_trials: int = 20, warmup_iters: int = 3,
                  bench_iters: int = 10) -> MoETuningResult:
     cache_file = None
     if cache_dir:
         Path(cache_dir).mkdir(parents=True, exist_ok=True)
-        cache_file = Path(cache_dir) / f"moe_tuning_{_cache_key(cfg)}.json"
+        cache_file = Path(cache_dir) / f"moe_tuning_{_cache_key(config)}.json"
         if cache_file.exists():
             d = json.loads(cache_file.read_text())
             return MoETuningResult(tuple(d["gate_up_tiling"]), tuple(d["down_tiling"]), d["backend"],
                                    d.get("throughput_gflops", {}))
     dev = "cuda" if torch.cuda.is_available() else "cpu"
-    dt = getattr(torch, cfg.dtype) if dev == "cuda" else torch.float32
-    E, D, I, M = cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_tokens
+    dt = getattr(torch, config.dtype) if dev == "cuda" else torch.float32
+    E, D, I, M = config.num_experts, config.hidden_size, config.moe_intermediate_size, config.num_tokens
     sizes = torch.full((E,), M // E, dtype=torch.int64, device=dev)
     sizes[: M % E] += 1
     result = {}
@@ -118,5 +118,5 @@ def autotune_moe(cfg: MoETuningConfig, cache_dir: str | None = None, max_trials:
     if cache_file is not None:
         cache_file.write_text(json.dumps({"gate_up_tiling": list(res.gate_up_tiling),
                                           "down_tiling": list(res.down_tiling), "backend": res.backend,
-                                          "throughput_gflops": res.throughput_gflops, "config": asdict(cfg)}))
+                                          "throughput_gflops": res.throughput_gflops, "config": asdict(config)}))
     return res

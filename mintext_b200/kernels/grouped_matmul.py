@@ -25,8 +25,8 @@ def _cuda(x: torch.Tensor) -> bool:
     return moe_ops.cuda_path(x)
 
 
-def grouped_matmul(x: torch.Tensor, w: torch.Tensor, group_sizes: torch.Tensor, *, tiling=None) -> torch.Tensor:
-    return grouped_matmul_vjp(x, w, group_sizes, tiling=tiling)
+def grouped_matmul(x: torch.Tensor, weights: torch.Tensor, group_sizes: torch.Tensor, *, tiling=None) -> torch.Tensor:
+    return grouped_matmul_vjp(x, weights, group_sizes, tiling=tiling)
 
 
 def tgmm(lhs: torch.Tensor, rhs: torch.Tensor, group_sizes: torch.Tensor, *, tiling=None) -> torch.Tensor:
@@ -51,10 +51,10 @@ class _GroupedMatmulFn(torch.autograd.Function):
         return dx, dw, None
 
 
-def grouped_matmul_vjp(x: torch.Tensor, w: torch.Tensor, group_sizes: torch.Tensor, *, tiling=None,
+def grouped_matmul_vjp(x: torch.Tensor, weights: torch.Tensor, group_sizes: torch.Tensor, *, tiling=None,
                        mosaic_fusion: bool = True) -> torch.Tensor:
     if _cuda(x):
         from mintext_b200.ops import moe as moe_ops
 
-        return moe_ops.grouped_matmul_cuda(x, w, group_sizes, tiling)
-    return _GroupedMatmulFn.apply(x, w.to(x.dtype), group_sizes)
+        return moe_ops.grouped_matmul_cuda(x, weights, group_sizes, tiling)
+    return _GroupedMatmulFn.apply(x, weights.to(x.dtype), group_sizes)

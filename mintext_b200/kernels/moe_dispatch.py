@@ -22,11 +22,11 @@ def route(tokens: torch.Tensor, topk_indices: torch.Tensor, num_experts: int):
     return oracle.route(tokens, topk_indices, num_experts)
 
 
-def unroute(sorted_outputs: torch.Tensor, sort_indices: torch.Tensor, topk_weights: torch.Tensor,
+def unroute(sorted_output: torch.Tensor, sort_indices: torch.Tensor, topk_weights: torch.Tensor,
             num_experts_per_tok: int) -> torch.Tensor:
-    """sorted_outputs ``[N*K,D]`` -> ``[N,D]`` = ``sum_k w[n,k] * y[n,k]``."""
+    """sorted_output ``[N*K,D]`` -> ``[N,D]`` = ``sum_k w[n,k] * y[n,k]``."""
     from mintext_b200.ops import moe as moe_ops
 
-    if moe_ops.cuda_path(sorted_outputs):
-        return moe_ops.unroute_cuda(sorted_outputs, sort_indices, topk_weights, num_experts_per_tok)
-    return oracle.unroute(sorted_outputs, sort_indices, topk_weights, num_experts_per_tok)
+    if moe_ops.cuda_path(sorted_output):
+        return moe_ops.unroute_cuda(sorted_output, sort_indices, topk_weights, num_experts_per_tok)
+    return oracle.unroute(sorted_output, sort_indices, topk_weights, num_experts_per_tok)

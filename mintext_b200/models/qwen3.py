@@ -2,8 +2,11 @@
 set, all others full attention (reference: mintext/models/qwen3.py:8-17)."""
 
 
-def layer_types(num_layers: int, cfg: dict) -> list[str]:
-    if not cfg.get("use_sliding_window", False):
-        return ["full_attention"] * num_layers
-    cut = cfg.get("max_window_layers", 28)
-    return ["sliding_attention" if i < cut else "full_attention" for i in range(num_layers)]
+def layer_types(num_hidden_layers: int, data: dict) -> list[str]:
+    if not data.get("use_sliding_window", False):
+        return ["full_attention"] * num_hidden_layers
+    cut = data.get("max_window_layers", 28)
+    return ["sliding_attention" if i < cut else "full_attention" for i in range(num_hidden_layers)]
+
+
+get_layer_types = layer_types  # the reference's name for the per-family function

@@ -20,9 +20,9 @@ from .norm import RMSNorm
 from .rope import RotaryEmbedding
 
 
-def make_sliding_window_mask(seq_len: int, window: int, dtype=torch.float32) -> torch.Tensor:
-    """Additive ``[1,1,S,S]`` mask that keeps ``0 <= i - j < window``."""
-    return sliding_window_mask(seq_len, window, dtype)
+def make_sliding_window_mask(seq_len: int, window_size: int, dtype=torch.float32) -> torch.Tensor:
+    """Additive ``[1,1,S,S]`` mask that keeps ``0 <= i - j < window_size``."""
+    return sliding_window_mask(seq_len, window_size, dtype)
 
 
 class Attention(nn.Module):

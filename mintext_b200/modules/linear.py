@@ -74,6 +74,24 @@ def truncated_normal_init(shape: Sequence[int], fan_in: int, generator: torch.Ge
     return (t / math.sqrt(max(fan_in, 1))).to(dtype)
 
 
+def variance_scaling_init(scale: float = 1.0):
+    """Initialiser factory with the reference's calling convention (mintext/modules/linear.py:18-30):
+    ``init(generator, shape, dtype, in_axis, out_axis)`` draws a standard normal truncated to [-2, 2] and multiplies
+    it by ``scale / sqrt(fan_in)``, where ``fan_in`` is the product of the dims that are not output axes.
+    ``in_axis`` is accepted for signature parity; the fan-in follows from ``out_axis`` as in the reference."""
+
+    def init(generator, shape, dtype=torch.float32, in_axis=0, out_axis=-1):
+        outs = out_axis if isinstance(out_axis, (tuple, list)) else (out_axis,)
+        fan_out = 1
+        for a in outs:
+            fan_out *= int(shape[a])
+        fan_in = max(math.prod(int(d) for d in shape) // max(fan_out, 1), 1)
+        t = truncated_normal_init(shape, fan_in, generator, torch.float32)
+        return (t * float(scale)).to(dtype)
+
+    return init
+
+
 def fp8_matmul_reference(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """Per-tensor dynamically scaled fp8 product: activations to e4m3 with ``448/amax``, weights to e5m2 with
     ``57344/amax``, fp32 accumulation, rescale (mintext/modules/linear.py:37-57)."""

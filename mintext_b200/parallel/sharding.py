@@ -21,9 +21,9 @@ def get_logical_axis_rules(config) -> list[tuple[str, str | None]]:
     return [tuple(r) for r in config.logical_axis_rules]
 
 
-def logical_to_pspec(logical_axes, rules, mesh: Mesh | None = None) -> PartitionSpec:
+def logical_to_pspec(logical_names, rules, mesh: Mesh | None = None) -> PartitionSpec:
     out = []
-    for name in logical_axes:
+    for name in logical_names:
         target = None
         for logical, physical in rules:
             if logical == name:
@@ -78,8 +78,8 @@ class NamedSharding:
         return tensor[self.local_slices(tensor.shape, rank)]
 
 
-def create_named_sharding(mesh: Mesh, logical_axes, rules) -> NamedSharding:
-    return NamedSharding(mesh, logical_to_pspec(logical_axes, rules, mesh))
+def create_named_sharding(mesh: Mesh, logical_names, rules) -> NamedSharding:
+    return NamedSharding(mesh, logical_to_pspec(logical_names, rules, mesh))
 
 
 def add_data_axis_to_sharding(sharding: NamedSharding, mesh: Mesh | None = None) -> NamedSharding:
@@ -110,8 +110,16 @@ def get_input_data_sharding(config, mesh: Mesh) -> NamedSharding:
     return create_named_sharding(mesh, ("batch", "length"), get_logical_axis_rules(config))
 
 
-def get_model_param_shardings(model: torch.nn.Module, config, mesh: Mesh) -> dict[str, NamedSharding]:
-    rules = get_logical_axis_rules(config)
+def get_model_param_shardings(model: torch.nn.Module, mesh, rules=None, *, config=None) -> dict[str, NamedSharding]:
+    """``{parameter name: NamedSharding}`` from every parameter's logical axes
+    (mintext/distributed/sharding.py:130-165: ``(model, mesh, rules=None)``, default rules when none are given).
+    ``(model, config, mesh)`` is accepted as well: the rules then come from the config."""
+    if not isinstance(mesh, Mesh) and isinstance(rules, Mesh):   # (model, config, mesh)
+        config, mesh, rules = mesh, rules, None
+    if rules is None:
+        from mintext_b200.config import DEFAULT_LOGICAL_AXIS_RULES
+
+        rules = get_logical_axis_rules(config) if config is not None else list(DEFAULT_LOGICAL_AXIS_RULES)
     out = {}
     for name, p in model.named_parameters():
         axes = getattr(p, "logical_axes", (None,) * p.dim())

@@ -76,10 +76,11 @@ def cross_entropy_loss(logits: torch.Tensor, targets: torch.Tensor, label_smooth
     return oracle.cross_entropy(logits, targets, label_smoothing, z_loss_weight)
 
 
-def chunked_cross_entropy_loss(hidden: torch.Tensor, targets: torch.Tensor, output_proj, num_tiles: int,
+def chunked_cross_entropy_loss(hidden_states: torch.Tensor, targets: torch.Tensor, output_proj, num_tiles: int,
                                label_smoothing: float = 0.0, z_loss_weight: float = 0.0):
     """Project-and-score ``num_tiles`` token chunks one at a time so the full ``[N,V]`` logits never exist.
     ``output_proj`` maps ``[n,D] -> [n,V]``."""
+    hidden = hidden_states
     N = hidden.shape[0]
     step = N // num_tiles
     losses, zs = [], []

@@ -9,7 +9,8 @@ _UNITS = {"": 1, "B": 1, "K": 1024, "KB": 1024, "M": 1024 ** 2, "MB": 1024 ** 2,
 _PATTERN = re.compile(r"^\s*([0-9]*\.?[0-9]+)\s*([A-Za-z]*)\s*$")
 
 
-def parse_file_size(size) -> int:
+def parse_file_size(size_str) -> int:
+    size = size_str
     if isinstance(size, (int, float)) and not isinstance(size, bool):
         if size < 0:
             raise ValueError(f"File size must be non-negative, got {size}")

@@ -30,8 +30,10 @@ def count_params(params) -> int:
     return sum(int(t.numel()) for t in _leaves(params) if isinstance(t, torch.Tensor))
 
 
-def check_nan(params) -> bool:
-    """True when any leaf holds a NaN or an infinity."""
+def check_nan(tree, label: str = "params") -> bool:
+    """True when any leaf holds a NaN or an infinity (``label`` is accepted for signature parity and unused, as in
+    mintext/utils/pytree.py:16-25)."""
+    params = tree
     return any(not bool(torch.isfinite(t.float()).all()) for t in _leaves(params) if isinstance(t, torch.Tensor))
 
 
