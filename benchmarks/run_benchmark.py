@@ -2,6 +2,8 @@
 (reference: benchmarks/run_benchmark.py; this logger prints the ``MFU=`` token the parser keys on).
 
     python benchmarks/run_benchmark.py --config configs/benchmarks/llama-3.2-1b-b200.yml [--gpus 8] [--skip 2] [key=value ...]
+
+``--warmup_steps`` and ``--extra_args k=v ...`` are the reference's spellings of ``--skip`` and the bare overrides.
 """
 
 from __future__ import annotations
@@ -31,12 +33,14 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", required=True)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--skip", type=int, default=2, help="leading steps excluded from the averages")
+    ap.add_argument("--skip", "--warmup_steps", dest="skip", type=int, default=2,
+                    help="leading steps excluded from the averages")
+    ap.add_argument("--extra_args", nargs="*", default=[], help="further key=value overrides (also accepted bare)")
     ap.add_argument("--out", default="benchmark_results.json")
     args, rest = ap.parse_known_args()
     root = Path(__file__).resolve().parents[1]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
-           "--master-addr", "127.0.0.1", "--master-port", "29510", "-m", "mintext_b200.train", "--config", args.config, *rest]
+           "--master-addr", "127.0.0.1", "--master-port", "29510", "-m", "mintext_b200.train", "--config", args.config, *args.extra_args, *rest]
     proc = subprocess.run(cmd, cwd=root, capture_output=True, text=True)
     rows = parse(proc.stdout + proc.stderr, args.skip)
     if not rows:

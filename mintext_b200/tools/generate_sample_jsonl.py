@@ -16,12 +16,12 @@ _WORDS = ("the quick brown fox jumps over the lazy dog while a curious model lea
           "gradients flow backward through many layers of attention and feed forward blocks").split()
 
 
-def generate(path: str, num_docs: int, min_words: int, max_words: int, seed: int) -> None:
+def generate(path: str, num_docs: int, min_words: int, max_words: int, seed: int, text_key: str = "text") -> None:
     rng = random.Random(seed)
     with open(path, "w") as f:
         for i in range(num_docs):
             n = rng.randint(min_words, max_words)
-            f.write(json.dumps({"id": i, "text": " ".join(rng.choice(_WORDS) for _ in range(n))}) + "\n")
+            f.write(json.dumps({"id": i, text_key: " ".join(rng.choice(_WORDS) for _ in range(n))}) + "\n")
 
 
 def main(argv=None) -> None:
@@ -31,8 +31,9 @@ def main(argv=None) -> None:
     ap.add_argument("--min-words", type=int, default=20)
     ap.add_argument("--max-words", type=int, default=400)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--text-key", default="text", help="JSON key of the text field")
     a = ap.parse_args(argv)
-    generate(a.output, a.num_docs, a.min_words, a.max_words, a.seed)
+    generate(a.output, a.num_docs, a.min_words, a.max_words, a.seed, a.text_key)
     print(f"wrote {a.num_docs} documents to {a.output}")
 
 

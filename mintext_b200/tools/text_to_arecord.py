@@ -124,7 +124,7 @@ def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description="text -> tokenised record shards")
     ap.add_argument("--input", nargs="+", required=True)
     ap.add_argument("--output", required=True)
-    ap.add_argument("--tokenizer", required=True)
+    ap.add_argument("--tokenizer", "--tokenizer-path", dest="tokenizer", required=True)
     ap.add_argument("--tokenizer-type", default="auto", choices=["auto", "huggingface", "sentencepiece"])
     ap.add_argument("--text-key", default="text")
     ap.add_argument("--workers", type=int, default=1)
