@@ -433,3 +433,56 @@ def test_vocab_parallel_tied_weights_label_smoothing_z_loss_and_token_chunks():
 
 def test_vocab_parallel_soft_capped_logits_on_four_ranks():
     _check_vocab_parallel("softcap_scaled", _vp_softcap, 4, 29655)
+
+
+def _vp_embedding_worker(rank, world):
+    """bf16 table: the reduce-scatter adds one non-zero row and zeros per token, so the result is the plain lookup."""
+    from mintext_b200.parallel import vocab_parallel as vp
+    from mintext_b200.parallel.tp import TensorParallel
+
+    tp = TensorParallel(dist.group.WORLD, torch.device("cpu"), fused=False)
+    g = torch.Generator().manual_seed(5)
+    table = torch.randn(64, 16, generator=g).to(torch.bfloat16)
+    tokens = torch.randint(0, 64, (1, 8 * world), generator=g)
+    per = 64 // world
+    local = table[rank * per:(rank + 1) * per].clone().requires_grad_(True)
+    mine = tokens[:, rank * 8:(rank + 1) * 8]
+    x = vp.embedding(local, mine, tp, torch.bfloat16, scale=2.0)
+    assert torch.equal(x, (table[mine] * 2.0).to(torch.bfloat16))
+    x.float().sum().backward()
+    # every occurrence of a row in the group's tokens adds `scale` to each of its elements
+    counts = torch.bincount(tokens.reshape(-1), minlength=64)[rank * per:(rank + 1) * per]
+    assert torch.equal(local.grad.float(), (counts[:, None] * 2.0).expand(-1, 16).to(torch.float32))
+    return True
+
+
+def test_vocab_parallel_embedding_is_an_exact_lookup_in_bf16():
+    assert all(run_ranks(_vp_embedding_worker, 4, 29657).values())
+
+
+def _vp_bf16_worker(rank, world):
+    """bf16 hidden states and head (the GPU engine's dtypes): loss close to the fp32 oracle, gradient dtypes kept."""
+    from mintext_b200.ops import oracle
+    from mintext_b200.parallel import vocab_parallel as vp
+    from mintext_b200.parallel.tp import TensorParallel
+
+    tp = TensorParallel(dist.group.WORLD, torch.device("cpu"), fused=False)
+    g = torch.Generator().manual_seed(9)
+    h_all = (torch.randn(8 * world, 32, generator=g) * 0.5).to(torch.bfloat16)
+    w_all = (torch.randn(32, 96, generator=g) / 6).to(torch.bfloat16)
+    t_all = torch.randint(0, 96, (8 * world,), generator=g)
+    per = 96 // world
+    h = h_all[rank * 8:(rank + 1) * 8].clone().requires_grad_(True)
+    w = w_all[:, rank * per:(rank + 1) * per].clone().requires_grad_(True)
+    loss, z = vp.linear_cross_entropy(h, w, t_all[rank * 8:(rank + 1) * 8], tp, False, 0.05, 1e-3, None, chunks=3)
+    loss.sum().backward()
+    assert h.grad.dtype == torch.bfloat16 and w.grad.dtype == torch.bfloat16 and w.grad.shape == w.shape
+    ref, zref = oracle.cross_entropy((h_all.float() @ w_all.float()), t_all, 0.05, 1e-3)
+    sl = slice(rank * 8, (rank + 1) * 8)
+    return float((loss - ref[sl]).abs().max()), float((z - zref[sl]).abs().max())
+
+
+def test_vocab_parallel_loss_in_bf16_stays_close_to_the_fp32_oracle():
+    res = run_ranks(_vp_bf16_worker, 2, 29659)
+    for err, zerr in res.values():
+        assert err < 3e-2 and zerr < 1e-3
