@@ -143,12 +143,14 @@ class Optimizer:
 
     @torch.no_grad()
     def update(self, params: dict[str, torch.Tensor], grads: dict[str, torch.Tensor], state: OptState,
-               step: int) -> None:
-        """In-place update of ``params`` for schedule position ``step`` (the pre-increment step counter)."""
+               step: int, grad_norm: float | None = None) -> None:
+        """In-place update of ``params`` for schedule position ``step`` (the pre-increment step counter).
+        ``grad_norm``: the norm to clip by when it is not that of ``grads`` alone (a multi-process run, where a rank
+        holds slices of some gradients)."""
         cfg = self.config
         lr = self.schedule(step)
         if self.clip > 0:
-            gn = float(global_norm(grads.values()))
+            gn = float(grad_norm) if grad_norm is not None else float(global_norm(grads.values()))
             factor = self.clip / max(gn, self.clip)  # optax.clip_by_global_norm
         else:
             factor = 1.0

@@ -147,7 +147,11 @@ def setup_training(config: MinTextConfig):
     else:
         from mintext_b200 import trainer
 
-        state = trainer.create_train_state(model, config)
+        # several CPU processes: gradients are averaged as the GPU engine would (replicas, slices and their groups)
+        groups = None
+        if mesh.size > 1:
+            groups = trainer.ReduceGroups(slice_group=local_reduce_group, expert_group=expert_reduce_group)
+        state = trainer.create_train_state(model, config, groups)
     return mesh, model, state, device, use_gpu
 
 

@@ -30,6 +30,8 @@ class TrainState:
     tx: Any
 
     params_only_restore: bool = False
+    # process groups of a multi-process run (None: single process, or every rank trains on its own)
+    groups: "ReduceGroups | None" = None
 
     # ---- checkpoint protocol (see mintext_b200.checkpoint.manager)
     def checkpoint_tree(self) -> dict:
@@ -61,6 +63,84 @@ class TrainState:
 
     def refresh_from_model(self) -> None:
         """Parameters are shared with the model, nothing to copy."""
+
+
+# ------------------------------------------------------------------------------------------ multi-process runs
+@dataclass
+class ReduceGroups:
+    """Who averages what in a multi-process run of this trainer (the CPU statement of what the GPU engine does).
+
+    Every rank's loss is the mean over its own tokens, so the job's loss is the mean over ranks.  A replicated
+    parameter's gradient is therefore the sum over all ranks divided by the rank count.  A parameter of which a rank
+    holds a slice (tensor-, vocabulary- or expert-parallel) already receives, through the backward pass of the
+    collectives, the contributions of every rank that used the slice; what is left is the sum over the ranks that hold
+    *the same* slice (``slice_group``; ``expert_group`` for expert slices when tensor and expert parallelism are
+    combined; None: the slice is unique) and the same division by the rank count."""
+
+    world: Any = None          # all ranks (None: the default group)
+    slice_group: Any = None
+    expert_group: Any = None
+
+    def replica_group(self, p):
+        if getattr(p, "expert_parallel", False) and self.expert_group is not None:
+            return self.expert_group
+        return self.slice_group
+
+
+def _is_slice(p) -> bool:
+    return bool(getattr(p, "tensor_parallel", False) or getattr(p, "expert_parallel", False))
+
+
+def _group_size(group) -> int:
+    import torch.distributed as dist
+
+    return dist.get_world_size(group) if group is not None else 1
+
+
+@torch.no_grad()
+def sync_gradients(grads: dict, params: dict, groups: ReduceGroups) -> dict:
+    """Average ``grads`` over the job as :class:`ReduceGroups` describes (missing gradients count as zeros, so every
+    rank takes part in every collective).  Returns the new dict."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(groups.world)
+    out = {n: (g if g is not None else torch.zeros_like(params[n])) for n, g in grads.items()}
+    by_group: dict[int, tuple] = {}
+    for n, g in out.items():
+        p = params[n]
+        grp = groups.replica_group(p) if _is_slice(p) else groups.world
+        if _is_slice(p) and grp is None:
+            continue  # a slice nobody else holds
+        by_group.setdefault(id(grp), (grp, []))[1].append(n)
+    for grp, names in by_group.values():  # one collective per group, over a flat copy
+        flat = torch.cat([out[n].reshape(-1).float() for n in names])
+        dist.all_reduce(flat, group=grp)
+        off = 0
+        for n in names:
+            k = out[n].numel()
+            out[n] = flat[off:off + k].view(out[n].shape).to(out[n].dtype)
+            off += k
+    return {n: g / world for n, g in out.items()}
+
+
+@torch.no_grad()
+def global_l2_norm(tensors: dict, params: dict, groups: ReduceGroups) -> torch.Tensor:
+    """L2 norm of a job-wide tree of which ranks hold replicas and slices: replicated tensors count once, every
+    distinct slice once."""
+    import torch.distributed as dist
+
+    rep = torch.zeros((), dtype=torch.float32)
+    sl = torch.zeros((), dtype=torch.float32)
+    for n, t in tensors.items():
+        if t is None:
+            continue
+        s = (t.detach().float() ** 2).sum()
+        if _is_slice(params[n]):
+            sl += s / _group_size(groups.replica_group(params[n]))
+        else:
+            rep += s
+    dist.all_reduce(sl, group=groups.world)
+    return torch.sqrt(rep + sl)
 
 
 # ------------------------------------------------------------------------------------------ losses
@@ -190,11 +270,22 @@ def compute_loss(params, model, config, batch, loss_scale: float | None = None):
 
 
 # ------------------------------------------------------------------------------------------ steps
-def create_train_state(model, config) -> TrainState:
+def create_train_state(model, config, groups: ReduceGroups | None = None) -> TrainState:
     params = dict(model.named_parameters())
     tx = create_optimizer(config)
     trainable = {n: p for n, p in params.items() if p.requires_grad}
-    return TrainState(step=0, params=params, opt_state=tx.init(trainable), tx=tx)
+    return TrainState(step=0, params=params, opt_state=tx.init(trainable), tx=tx, groups=groups)
+
+
+def _active_groups(state) -> ReduceGroups | None:
+    groups = getattr(state, "groups", None)
+    if groups is None:
+        return None
+    import torch.distributed as dist
+
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(groups.world) < 2:
+        return None
+    return groups
 
 
 def train_step(state: TrainState, batch, model, config):
@@ -210,8 +301,26 @@ def train_step(state: TrainState, batch, model, config):
         got = torch.autograd.grad(loss, list(trainable.values()), allow_unused=True)
         grads = dict(zip(trainable, got))
         loss = loss.detach()
-    grad_norm = _l2_norm(grads.values())
-    param_norm = _l2_norm(state.params.values())
+    groups = _active_groups(state)
+    if groups is not None:
+        import torch.distributed as dist
+
+        grads = sync_gradients(grads, trainable, groups)
+        grad_norm = global_l2_norm(grads, trainable, groups)
+        param_norm = global_l2_norm(state.params, state.params, groups)
+        loss = loss.clone()
+        dist.all_reduce(loss, group=groups.world)
+        loss /= dist.get_world_size(groups.world)
+        zl = aux["z_loss"].clone()
+        dist.all_reduce(zl, group=groups.world)
+        aux["z_loss"] = zl / dist.get_world_size(groups.world)
+        if aux.get("moe_expert_counts") is not None:  # the load-balancing update looks at the whole job's tokens
+            counts = aux["moe_expert_counts"].clone()
+            dist.all_reduce(counts, group=groups.world)
+            aux["moe_expert_counts"] = counts
+    else:
+        grad_norm = _l2_norm(grads.values())
+        param_norm = _l2_norm(state.params.values())
     lr = create_lr_schedule(config)(state.step)
     skipped = False
     if getattr(config, "nan_policy", "ignore") != "ignore":
@@ -219,7 +328,8 @@ def train_step(state: TrainState, batch, model, config):
 
         skipped = apply_nan_policy(config.nan_policy, float(loss), state.step)
     if not skipped:
-        state.tx.update(trainable, grads, state.opt_state, state.step)
+        state.tx.update(trainable, grads, state.opt_state, state.step,
+                        grad_norm=float(grad_norm) if groups is not None else None)
         state.step += 1
     metrics = {
         "skipped": skipped,

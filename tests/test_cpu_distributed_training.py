@@ -1,0 +1,139 @@
+"""Several CPU processes (gloo) train through ``setup_training`` + ``trainer.train_step`` and end with the weights a
+single process gets from the same global batches: data parallelism, tensor parallelism (with vocabulary-parallel ends),
+expert parallelism and their combination, over several optimizer steps with global-norm clipping."""
+
+import pytest
+import torch
+
+from mintext_b200 import MinTextConfig
+from tests.test_sharding import run_ranks
+
+STEPS = 3
+BASE = dict(dtype="float32", vocab_size=64, num_hidden_layers=2, hidden_size=32, num_attention_heads=4,
+            num_key_value_heads=2, intermediate_size=64, seq_length=16, use_qk_norm=True, model_type="qwen3",
+            kernel_backend="oracle", enable_tensorboard=False, enable_checkpointing=False, learning_rate=1e-2,
+            gradient_clip_threshold=0.5, per_device_batch_size=2, steps=STEPS, warmup_steps_fraction=0.0)
+MOE = dict(model_type="deepseek_v3", use_qk_norm=False, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=16,
+           n_group=2, topk_group=1, first_k_dense_replace=1, n_shared_experts=1, moe_capacity_factor=8.0)
+CASES = {
+    # name: (ranks, parallelism, extra model settings)
+    "data_parallel": (2, dict(ici_fsdp_parallelism=2), {}),
+    "tensor_and_vocab_parallel": (4, dict(ici_fsdp_parallelism=2, ici_tensor_parallelism=2),
+                                  dict(tp_vocab_parallel=True, z_loss_weight=1e-3)),
+    "expert_parallel": (2, dict(ici_fsdp_parallelism=2, ici_expert_parallelism=2), MOE),
+    "tensor_and_expert_parallel": (4, dict(ici_fsdp_parallelism=2, ici_tensor_parallelism=2, ici_expert_parallelism=2),
+                                   MOE),
+}
+
+
+def _config(case: str, parallel: bool) -> MinTextConfig:
+    ranks, par, extra = CASES[case]
+    cfg = dict(BASE, **extra)
+    if parallel:
+        cfg.update(par)
+    else:  # one process sees the whole global batch
+        dp = ranks // par.get("ici_tensor_parallelism", 1)
+        cfg["per_device_batch_size"] = BASE["per_device_batch_size"] * dp
+    return MinTextConfig(**cfg)
+
+
+def _global_batches(case: str):
+    ranks, par, _ = CASES[case]
+    rows = BASE["per_device_batch_size"] * (ranks // par.get("ici_tensor_parallelism", 1))
+    g = torch.Generator().manual_seed(11)
+    out = []
+    for _ in range(STEPS):
+        t = torch.randint(0, 64, (rows, 16), generator=g)
+        out.append({"input_tokens": t, "target_tokens": t.roll(-1, 1)})
+    return out
+
+
+def _train_worker(rank, world, case):
+    from mintext_b200 import trainer
+    from mintext_b200.parallel.ep import set_current_ep
+    from mintext_b200.parallel.tp import set_current_tp
+    from mintext_b200.train import setup_training
+
+    cfg = _config(case, parallel=True)
+    try:
+        mesh, model, state, device, use_gpu = setup_training(cfg)
+        assert not use_gpu and state.groups is not None
+        tp = mesh.shape["tensor"]
+        b = cfg.per_device_batch_size
+        dp = rank // tp
+        log = []
+        for batch in _global_batches(case):
+            mine = {k: v[dp * b:(dp + 1) * b] for k, v in batch.items()}
+            state, m = trainer.train_step(state, mine, model, cfg)
+            if m.get("moe_expert_counts") is not None:
+                state = trainer.update_expert_biases(state, m["moe_expert_counts"], cfg)
+            log.append((float(m["loss"]), float(m["grad_norm"]), float(m["param_norm"])))
+        params = {n: (p.detach().clone(), tuple(getattr(p, "shard_spec", ()))) for n, p in model.named_parameters()}
+        return log, params
+    finally:
+        set_current_tp(None)
+        set_current_ep(None)
+
+
+def _worker(case):
+    # run_ranks pickles the function: module-level closures per case
+    return globals()[f"_worker_{case}"]
+
+
+def _worker_data_parallel(rank, world):
+    return _train_worker(rank, world, "data_parallel")
+
+
+def _worker_tensor_and_vocab_parallel(rank, world):
+    return _train_worker(rank, world, "tensor_and_vocab_parallel")
+
+
+def _worker_expert_parallel(rank, world):
+    return _train_worker(rank, world, "expert_parallel")
+
+
+def _worker_tensor_and_expert_parallel(rank, world):
+    return _train_worker(rank, world, "tensor_and_expert_parallel")
+
+
+def _single_process(case):
+    from mintext_b200 import trainer
+    from mintext_b200.train import setup_training
+
+    cfg = _config(case, parallel=False)
+    mesh, model, state, device, use_gpu = setup_training(cfg)
+    assert state.groups is None
+    log = []
+    for batch in _global_batches(case):
+        state, m = trainer.train_step(state, batch, model, cfg)
+        if m.get("moe_expert_counts") is not None:
+            state = trainer.update_expert_biases(state, m["moe_expert_counts"], cfg)
+        log.append((float(m["loss"]), float(m["grad_norm"]), float(m["param_norm"])))
+    return log, {n: p.detach().clone() for n, p in model.named_parameters()}
+
+
+@pytest.mark.parametrize("case,port", [("data_parallel", 29661), ("tensor_and_vocab_parallel", 29663),
+                                       ("expert_parallel", 29665), ("tensor_and_expert_parallel", 29667)])
+def test_cpu_processes_train_to_the_single_process_weights(case, port):
+    ranks = CASES[case][0]
+    res = run_ranks(_worker(case), ranks, port)
+    ref_log, ref = _single_process(case)
+    for r in range(ranks):
+        for got, want in zip(res[r][0], ref_log):   # loss, gradient norm and parameter norm of every step
+            assert got == pytest.approx(want, rel=2e-4, abs=2e-5), (case, r, res[r][0], ref_log)
+    for name, full in ref.items():
+        pieces = {}
+        for r in range(ranks):
+            t, spec = res[r][1][name]
+            if not spec:
+                assert torch.allclose(t, full, atol=2e-5), (case, name, r, float((t - full).abs().max()))
+                continue
+            dim, idx, cnt = spec
+            if idx in pieces:  # replicas of one slice hold the same values
+                assert torch.allclose(t, pieces[idx][1], atol=1e-6), (case, name, r)
+            pieces[idx] = (dim, t)
+        if pieces:
+            dim = next(iter(pieces.values()))[0]
+            got = torch.cat([pieces[i][1] for i in sorted(pieces)], dim=dim)
+            assert got.shape == full.shape and torch.allclose(got, full, atol=2e-5), \
+                (case, name, float((got - full).abs().max()))
