@@ -34,28 +34,53 @@ class TrainState:
     groups: "ReduceGroups | None" = None
 
     # ---- checkpoint protocol (see mintext_b200.checkpoint.manager)
+    def _slice_entry(self, name: str, tensor: torch.Tensor):
+        """A parameter of which this rank holds a slice is saved as one shard per slice (same entry format as the GPU
+        engine's), written by the first of the ranks that hold the slice; whole tensors by rank 0."""
+        p = self.params[name]
+        spec = getattr(p, "shard_spec", None)
+        if spec is None or not _is_slice(p):
+            return tensor
+        import torch.distributed as dist
+
+        grp = self.groups.replica_group(p) if self.groups is not None else None
+        first = grp is None or dist.get_rank(grp) == 0
+        me = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+        dim, idx, cnt = (int(v) for v in spec)
+        return {"tensor": tensor, "writer_rank": me if first else -1, "shard": (dim, idx, cnt),
+                "suffix": f".shard{idx}of{cnt}"}
+
+    def _shard_of(self, name: str):
+        p = self.params[name]
+        spec = getattr(p, "shard_spec", None)
+        return tuple(int(v) for v in spec) if (spec is not None and _is_slice(p)) else None
+
     def checkpoint_tree(self) -> dict:
         tree: dict = {"step": self.step, "opt_state/count": self.opt_state.count}
         for n, p in self.params.items():
-            tree[f"params/{n}"] = p.detach()
+            tree[f"params/{n}"] = self._slice_entry(n, p.detach())
         for n, t in self.opt_state.mu.items():
-            tree[f"opt_state/mu/{n}"] = t
+            tree[f"opt_state/mu/{n}"] = self._slice_entry(n, t)
         for n, t in self.opt_state.nu.items():
-            tree[f"opt_state/nu/{n}"] = t
+            tree[f"opt_state/nu/{n}"] = self._slice_entry(n, t)
         return tree
 
     @torch.no_grad()
     def load_checkpoint_tree(self, read) -> None:
+        def get(path, name):
+            spec = self._shard_of(name)
+            return read(path, shard=spec) if spec is not None else read(path)
+
         for n, p in self.params.items():
-            p.copy_(read(f"params/{n}").to(p.dtype))
+            p.copy_(get(f"params/{n}", n).to(p.dtype))
         if self.params_only_restore:
             return
         self.step = int(read("step"))
         self.opt_state.count = int(read("opt_state/count"))
         for n in self.opt_state.mu:
-            self.opt_state.mu[n].copy_(read(f"opt_state/mu/{n}"))
+            self.opt_state.mu[n].copy_(get(f"opt_state/mu/{n}", n))
         for n in self.opt_state.nu:
-            self.opt_state.nu[n].copy_(read(f"opt_state/nu/{n}"))
+            self.opt_state.nu[n].copy_(get(f"opt_state/nu/{n}", n))
 
     def reset_step(self) -> None:
         self.step = 0

@@ -137,3 +137,65 @@ def test_cpu_processes_train_to_the_single_process_weights(case, port):
             got = torch.cat([pieces[i][1] for i in sorted(pieces)], dim=dim)
             assert got.shape == full.shape and torch.allclose(got, full, atol=2e-5), \
                 (case, name, float((got - full).abs().max()))
+
+
+# ------------------------------------------------------------------ checkpoints of sliced parameters
+def _ckpt_worker(rank, world):
+    """Two steps on 4 ranks (fsdp 2 x tensor 2, vocabulary-parallel), save, one more step; then restore the saved
+    step into the same layout and repeat the third step: same weights."""
+    import os
+
+    from mintext_b200 import trainer
+    from mintext_b200.checkpoint import CheckpointManager
+    from mintext_b200.parallel.tp import set_current_tp
+    from mintext_b200.train import setup_training
+
+    case = "tensor_and_vocab_parallel"
+    cfg = _config(case, parallel=True)
+    try:
+        mesh, model, state, _, _ = setup_training(cfg)
+        b, dp = cfg.per_device_batch_size, rank // mesh.shape["tensor"]
+        batches = [{k: v[dp * b:(dp + 1) * b] for k, v in gb.items()} for gb in _global_batches(case)]
+        for mine in batches[:2]:
+            state, _ = trainer.train_step(state, mine, model, cfg)
+        mgr = CheckpointManager(os.environ["MT_TEST_CKPT_DIR"], save_interval_steps=1, max_to_keep=2, enable_async=False)
+        assert mgr.save(2, state, force=True)
+        mgr.wait_until_finished()
+        state, _ = trainer.train_step(state, batches[2], model, cfg)
+        after3 = {n: p.detach().clone() for n, p in model.named_parameters()}
+        mgr.restore(2, state)
+        assert state.step == 2
+        state, _ = trainer.train_step(state, batches[2], model, cfg)
+        for n, p in model.named_parameters():
+            assert torch.allclose(p, after3[n], atol=1e-7), n
+        return True
+    finally:
+        set_current_tp(None)
+
+
+def test_sliced_parameters_checkpoint_on_four_cpu_ranks_and_restore_in_one_process(tmp_path, monkeypatch):
+    from mintext_b200 import trainer
+    from mintext_b200.checkpoint import CheckpointManager
+    from mintext_b200.train import setup_training
+
+    monkeypatch.setenv("MT_TEST_CKPT_DIR", str(tmp_path))
+    assert all(run_ranks(_ckpt_worker, 4, 29669).values())
+    files = sorted(p.name for p in (tmp_path / "2" / "default").iterdir())
+    assert "params__token_embedder.shard0of2.bin" in files and "params__token_embedder.shard1of2.bin" in files
+    assert "params__final_norm.scale.bin" in files
+    # one process restores the whole tensors from the shards and continues as the four ranks did
+    case = "tensor_and_vocab_parallel"
+    cfg = _config(case, parallel=False)
+    _, model, state, _, _ = setup_training(cfg)
+    CheckpointManager(str(tmp_path), save_interval_steps=1, max_to_keep=2, enable_async=False).restore(2, state)
+    assert state.step == 2
+    ref_cfg = cfg
+    _, ref_model, ref_state, _, _ = setup_training(ref_cfg)
+    batches = _global_batches(case)
+    for gb in batches[:2]:
+        ref_state, _ = trainer.train_step(ref_state, gb, ref_model, ref_cfg)
+    for (n, p), (_, q) in zip(model.named_parameters(), ref_model.named_parameters()):
+        assert torch.allclose(p, q, atol=2e-5), (n, float((p - q).abs().max()))
+    state, m = trainer.train_step(state, batches[2], model, cfg)
+    ref_state, mr = trainer.train_step(ref_state, batches[2], ref_model, ref_cfg)
+    assert float(m["loss"]) == pytest.approx(float(mr["loss"]), rel=1e-4)
