@@ -215,8 +215,7 @@ def _create_iterator(config, mesh, split_index: int, shuffle: bool) -> BatchIter
             world = dist.get_world_size()
             rank = dist.get_rank()
             if mesh is not None:
-                tp = mesh.shape.get("tensor", 1)
-                rank, world = rank // tp, world // tp  # tensor-parallel peers read the same rows
+                rank, world = mesh.batch_rank(rank)  # tensor-parallel peers read the same rows
     except Exception:
         pass
     batch = config.per_device_batch_size * config.gradient_accumulation_steps

@@ -5,6 +5,11 @@ One process drives one GPU.  The mesh has the reference's three axes plus ``expe
 optimizer state); ``tensor`` splits heads / MLP width / vocabulary inside a layer; ``expert`` distributes MoE
 experts and is carved out of the data-parallel ranks (a rank's expert-parallel peers are data-parallel peers
 for the dense parts of the model).
+
+Several NVSwitch domains (nodes) form a hybrid mesh as the reference's multi-slice meshes do
+(mintext/distributed/mesh.py:133-199): a slice is a node, ``dcn_*_parallelism`` says how the nodes are laid out on
+the axes and ``ici_*_parallelism`` how the GPUs of one node are; along every axis the node index is the slow one,
+so the peers a rank has along the fast part of an axis sit on its own NVSwitch.
 """
 
 from __future__ import annotations
@@ -55,6 +60,8 @@ class Mesh:
     devices: np.ndarray
     axis_names: tuple[str, ...] = AXES
     expert: int = 1
+    num_slices: int = 1                                   # NVSwitch domains (nodes) the mesh spans
+    dcn_shape: tuple[int, ...] = (1, 1, 1)                # nodes along each axis (the slow part of the axis)
     _groups: dict = field(default_factory=dict, repr=False)
 
     @property
@@ -79,6 +86,21 @@ class Mesh:
         c = self.coords(rank)
         index = tuple(slice(None) if n in axes else c[n] for n in self.axis_names)
         return [int(r) for r in np.asarray(self.devices[index]).reshape(-1)]
+
+    def batch_rank(self, rank: int) -> tuple[int, int]:
+        """``(index, count)`` of ``rank`` among the batch-sharding positions (``data x fsdp``): which rows of the
+        global batch it reads.  The ranks of a tensor-parallel group share an index."""
+        c = self.coords(rank)
+        shape = dict(zip(self.axis_names, self.devices.shape))
+        return c["data"] * shape["fsdp"] + c["fsdp"], shape["data"] * shape["fsdp"]
+
+    def slice_of(self, rank: int) -> int:
+        """NVSwitch domain of ``rank`` (ranks are numbered slice by slice)."""
+        return int(rank) // (self.size // self.num_slices)
+
+    def within_one_slice(self, ranks) -> bool:
+        """Whether ``ranks`` share an NVSwitch domain, i.e. may use the peer-memory kernels among themselves."""
+        return len({self.slice_of(r) for r in ranks}) <= 1
 
     def expert_group_ranks(self, rank: int) -> list[int]:
         """Expert-parallel peers: consecutive blocks of ``expert`` ranks inside the batch-sharding ranks."""
@@ -129,17 +151,44 @@ def create_mesh(config, devices=None) -> Mesh:
             n = 1
         devices = list(range(n))
     n = len(devices)
-    if config.num_slices != 1 or config.dcn_data_parallelism * config.dcn_fsdp_parallelism * config.dcn_tensor_parallelism != 1:
-        raise ValueError("multi-slice (DCN) meshes are not supported: this build targets a single NVSwitch domain")
-    sizes = _resolve_auto_parallelism(
+    dcn_cfg = {"data": int(config.dcn_data_parallelism), "fsdp": int(config.dcn_fsdp_parallelism),
+               "tensor": int(config.dcn_tensor_parallelism)}
+    slices = _num_slices(config, dcn_cfg, n)
+    if slices > 1:
+        if n % slices != 0:
+            raise ValueError(f"multi-slice mesh: {n} devices do not split into {slices} slices")
+        dcn = _resolve_auto_parallelism(dcn_cfg, slices, "DCN")
+    else:
+        dcn = {"data": 1, "fsdp": 1, "tensor": 1}
+    ici = _resolve_auto_parallelism(
         {"data": config.ici_data_parallelism, "fsdp": config.ici_fsdp_parallelism,
-         "tensor": config.ici_tensor_parallelism}, n)
+         "tensor": config.ici_tensor_parallelism}, n // slices)
+    sizes = {k: dcn[k] * ici[k] for k in AXES}
     ep = int(getattr(config, "ici_expert_parallelism", 1))
     dp = sizes["data"] * sizes["fsdp"]
     if ep < 1 or dp % ep != 0:
         raise ValueError(f"ici_expert_parallelism ({ep}) must divide data x fsdp ({dp})")
-    grid = np.asarray(devices).reshape(sizes["data"], sizes["fsdp"], sizes["tensor"])
-    return Mesh(devices=grid, expert=ep)
+    # ranks are numbered slice by slice; on every axis the slice index is the slow part and the index inside the
+    # slice the fast part
+    grid = np.asarray(devices).reshape(*(dcn[k] for k in AXES), *(ici[k] for k in AXES))
+    grid = grid.transpose(0, 3, 1, 4, 2, 5).reshape(sizes["data"], sizes["fsdp"], sizes["tensor"])
+    return Mesh(devices=grid, expert=ep, num_slices=slices, dcn_shape=tuple(dcn[k] for k in AXES))
+
+
+def _num_slices(config, dcn_cfg: dict[str, int], num_devices: int) -> int:
+    """Slices (NVSwitch domains) of the job: ``num_slices`` when set above 1, else the product of the
+    ``dcn_*_parallelism`` values when that is above 1.  The reference reads the slice of every device from the
+    runtime (mintext/distributed/mesh.py:76-81); here the configuration says it, and a job whose DCN settings are all 1
+    is laid out as one slice however many nodes it runs on."""
+    if int(config.num_slices) > 1:
+        return int(config.num_slices)
+    known = 1
+    for v in dcn_cfg.values():
+        if v != -1:
+            known *= v
+    if -1 in dcn_cfg.values():
+        raise ValueError("a DCN parallelism axis of -1 (auto) needs num_slices > 1 to resolve against")
+    return known if known > 1 else 1
 
 
 def setup_mesh(config) -> Mesh:

@@ -107,22 +107,29 @@ def setup_training(config: MinTextConfig):
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_gpu else torch.device("cpu")
     if use_gpu:
         torch.cuda.set_device(device)
+    rank = 0
+    if mesh.size > 1:
+        import torch.distributed as dist
+
+        rank = dist.get_rank()
+    # peer-memory kernels only among ranks of one NVSwitch domain; a group that spans nodes composes NCCL collectives
+    fused_ok = lambda ranks: bool(config.fused_collectives) and mesh.within_one_slice(ranks)  # noqa: E731
     if config.ici_expert_parallelism > 1 and config.num_experts > 0:
         from mintext_b200.parallel.ep import ExpertParallel, set_current_ep
 
         set_current_ep(ExpertParallel(mesh.group(("expert",)), device, config.moe_capacity_factor,
-                                      fused=config.fused_collectives))
+                                      fused=fused_ok(mesh.expert_group_ranks(rank))))
     # Replica groups for the parameters a rank holds a slice of: tensor slices are replicated on the ranks of the same
     # tensor coordinate, expert slices on the ranks at the same expert position (across the tensor axis too, since the
     # routed experts treat a tensor-parallel group as data parallelism).
     local_reduce_group = expert_reduce_group = None
-    tp_on = config.ici_tensor_parallelism > 1
+    tp_on = mesh.shape["tensor"] > 1
     ep_on = config.ici_expert_parallelism > 1 and config.num_experts > 0
     dp = mesh.shape["data"] * mesh.shape["fsdp"]
     if tp_on:
         from mintext_b200.parallel.tp import TensorParallel, set_current_tp
 
-        set_current_tp(TensorParallel(mesh.group(("tensor",)), device, fused=config.fused_collectives))
+        set_current_tp(TensorParallel(mesh.group(("tensor",)), device, fused=fused_ok(mesh.ranks_along("tensor", rank))))
         if dp > 1:
             local_reduce_group = mesh.group(("data", "fsdp"))
     if ep_on:
@@ -138,11 +145,16 @@ def setup_training(config: MinTextConfig):
     if use_gpu:
         from mintext_b200.utils.pytree import wants_sharded_params
 
-        if wants_sharded_params(config, mesh.size):
+        engine_config = config
+        if mesh.num_slices > 1 and config.fused_collectives:
+            # the optimizer's reduce-scatter / all-gather span every rank, hence every node: NCCL composition
+            logger.info("mesh spans %d NVSwitch domains: the sharded optimizer step uses NCCL collectives", mesh.num_slices)
+            engine_config = config.model_copy(update={"fused_collectives": False})
+        if wants_sharded_params(engine_config, mesh.size):
             from mintext_b200.parallel.fsdp import ParamShardedEngine as Engine
         else:
             from mintext_b200.parallel.engine import TrainEngine as Engine
-        state = Engine(model, config, device=device, local_reduce_group=local_reduce_group,
+        state = Engine(model, engine_config, device=device, local_reduce_group=local_reduce_group,
                        expert_reduce_group=expert_reduce_group)
     else:
         from mintext_b200 import trainer
@@ -220,7 +232,7 @@ def train(config: MinTextConfig) -> dict:
         if config.eval_period > 0:
             eval_iter = create_eval_iterator(config, mesh)
     rank = int(os.environ.get("RANK", "0"))
-    synthetic = _SyntheticStream(config, rows, rank // tp, device)
+    synthetic = _SyntheticStream(config, rows, mesh.batch_rank(rank)[0] if world > 1 else 0, device)
     if train_iter is None:
         synthetic.skip(start_step)  # resume: past the batches already consumed
 

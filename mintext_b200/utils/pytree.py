@@ -123,7 +123,8 @@ def wants_sharded_params(config, world: int) -> bool:
 
 
 def _tensor_parallel_degree(config) -> int:
-    return max(int(getattr(config, "ici_tensor_parallelism", 1) or 1), 1)
+    dcn = int(getattr(config, "dcn_tensor_parallelism", 1) or 1)
+    return max(int(getattr(config, "ici_tensor_parallelism", 1) or 1), 1) * max(dcn, 1)
 
 
 def calculate_tflops_per_device(config) -> float:

@@ -23,6 +23,8 @@ CASES = {
     "expert_parallel": (2, dict(ici_fsdp_parallelism=2, ici_expert_parallelism=2), MOE),
     "tensor_and_expert_parallel": (4, dict(ici_fsdp_parallelism=2, ici_tensor_parallelism=2, ici_expert_parallelism=2),
                                    MOE),
+    # two slices (nodes) of four ranks: data parallel across them, fsdp x tensor inside each
+    "two_slices": (8, dict(num_slices=2, dcn_data_parallelism=2, ici_fsdp_parallelism=2, ici_tensor_parallelism=2), {}),
 }
 
 
@@ -96,6 +98,10 @@ def _worker_tensor_and_expert_parallel(rank, world):
     return _train_worker(rank, world, "tensor_and_expert_parallel")
 
 
+def _worker_two_slices(rank, world):
+    return _train_worker(rank, world, "two_slices")
+
+
 def _single_process(case):
     from mintext_b200 import trainer
     from mintext_b200.train import setup_training
@@ -113,7 +119,8 @@ def _single_process(case):
 
 
 @pytest.mark.parametrize("case,port", [("data_parallel", 29661), ("tensor_and_vocab_parallel", 29663),
-                                       ("expert_parallel", 29665), ("tensor_and_expert_parallel", 29667)])
+                                       ("expert_parallel", 29665), ("tensor_and_expert_parallel", 29667),
+                                       ("two_slices", 29671)])
 def test_cpu_processes_train_to_the_single_process_weights(case, port):
     ranks = CASES[case][0]
     res = run_ranks(_worker(case), ranks, port)

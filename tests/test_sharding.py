@@ -40,7 +40,7 @@ def test_mesh_shapes_and_groups():
     one = setup_mesh(MinTextConfig())
     assert one.size == 1 and get_global_mesh() is one
     with pytest.raises(ValueError, match="multi-slice"):
-        create_mesh(MinTextConfig(num_slices=2), devices=[0])
+        create_mesh(MinTextConfig(num_slices=2), devices=[0])       # one device does not split into two slices
 
 
 def test_logical_rules_and_specs():

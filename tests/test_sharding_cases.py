@@ -114,11 +114,42 @@ def test_expert_axis_with_tensor_parallelism_counts_only_data_ranks():
         create_mesh(MinTextConfig(ici_tensor_parallelism=2, ici_expert_parallelism=8), devices=list(range(8)))
 
 
-def test_multi_slice_meshes_are_refused():
+def test_multi_slice_mesh_puts_the_slice_index_on_the_slow_part_of_every_axis():
+    """Two nodes of 8 (ranks numbered node by node): data across the nodes, fsdp x tensor inside each."""
+    m = create_mesh(MinTextConfig(num_slices=2, dcn_data_parallelism=2, ici_fsdp_parallelism=4, ici_tensor_parallelism=2),
+                    devices=list(range(16)))
+    assert dict(m.shape) == {"data": 2, "fsdp": 4, "tensor": 2, "expert": 1}
+    assert m.num_slices == 2 and m.dcn_shape == (2, 1, 1)
+    assert m.ranks_along("tensor", 9) == [8, 9] and m.within_one_slice(m.ranks_along("tensor", 9))
+    assert m.ranks_along("fsdp", 9) == [9, 11, 13, 15] and m.within_one_slice(m.ranks_along("fsdp", 9))
+    assert m.ranks_along("data", 9) == [1, 9] and not m.within_one_slice(m.ranks_along("data", 9))
+    assert [m.slice_of(r) for r in (0, 7, 8, 15)] == [0, 0, 1, 1]
+
+
+def test_multi_slice_axis_split_over_nodes_and_gpus():
+    """fsdp 2 (nodes) x 4 (GPUs): the node index is the slow part of the axis; tensor pairs stay inside a node."""
+    m = create_mesh(MinTextConfig(num_slices=2, dcn_fsdp_parallelism=-1, ici_fsdp_parallelism=-1, ici_tensor_parallelism=2),
+                    devices=list(range(16)))
+    assert dict(m.shape) == {"data": 1, "fsdp": 8, "tensor": 2, "expert": 1} and m.dcn_shape == (1, 2, 1)
+    assert m.ranks_along("fsdp", 0) == [0, 2, 4, 6, 8, 10, 12, 14]
+    assert all(m.within_one_slice(m.ranks_along("tensor", r)) for r in range(16))
+    # expert-parallel blocks of 4 are consecutive batch-sharding ranks: inside one node
+    e = create_mesh(MinTextConfig(num_slices=2, dcn_fsdp_parallelism=2, ici_fsdp_parallelism=8, ici_expert_parallelism=4),
+                    devices=list(range(16)))
+    assert e.expert_group_ranks(9) == [8, 9, 10, 11] and e.within_one_slice(e.expert_group_ranks(9))
+
+
+def test_slices_follow_from_the_dcn_settings_and_are_validated():
+    m = create_mesh(MinTextConfig(dcn_data_parallelism=2), devices=[0, 1])        # num_slices left at 1
+    assert m.num_slices == 2 and dict(m.shape)["data"] == 2
     with pytest.raises(ValueError, match="multi-slice"):
-        create_mesh(MinTextConfig(num_slices=2), devices=[0])
-    with pytest.raises(ValueError, match="multi-slice"):
-        create_mesh(MinTextConfig(dcn_data_parallelism=2), devices=[0, 1])
+        create_mesh(MinTextConfig(num_slices=2), devices=[0])                       # 1 device, 2 slices
+    with pytest.raises(ValueError, match="DCN"):
+        create_mesh(MinTextConfig(num_slices=4, dcn_data_parallelism=2), devices=list(range(8)))   # product != slices
+    with pytest.raises(ValueError, match="num_slices"):
+        create_mesh(MinTextConfig(dcn_data_parallelism=-1), devices=list(range(8)))
+    flat = create_mesh(MinTextConfig(ici_fsdp_parallelism=-1), devices=list(range(16)))  # all DCN settings 1: one slice
+    assert flat.num_slices == 1 and dict(flat.shape)["fsdp"] == 16
 
 
 def test_setup_mesh_sets_the_global_mesh():
