@@ -18,6 +18,7 @@ MOE = dict(model_type="deepseek_v3", use_qk_norm=False, num_experts=4, num_exper
 CASES = {
     # name: (ranks, parallelism, extra model settings)
     "data_parallel": (2, dict(ici_fsdp_parallelism=2), {}),
+    "data_parallel_with_accumulation": (2, dict(ici_data_parallelism=2), dict(gradient_accumulation_steps=2)),
     "tensor_and_vocab_parallel": (4, dict(ici_fsdp_parallelism=2, ici_tensor_parallelism=2),
                                   dict(tp_vocab_parallel=True, z_loss_weight=1e-3)),
     "expert_parallel": (2, dict(ici_fsdp_parallelism=2, ici_expert_parallelism=2), MOE),
@@ -41,7 +42,8 @@ def _config(case: str, parallel: bool) -> MinTextConfig:
 
 def _global_batches(case: str):
     ranks, par, _ = CASES[case]
-    rows = BASE["per_device_batch_size"] * (ranks // par.get("ici_tensor_parallelism", 1))
+    accum = CASES[case][2].get("gradient_accumulation_steps", 1)
+    rows = BASE["per_device_batch_size"] * accum * (ranks // par.get("ici_tensor_parallelism", 1))
     g = torch.Generator().manual_seed(11)
     out = []
     for _ in range(STEPS):
@@ -61,7 +63,7 @@ def _train_worker(rank, world, case):
         mesh, model, state, device, use_gpu = setup_training(cfg)
         assert not use_gpu and state.groups is not None
         tp = mesh.shape["tensor"]
-        b = cfg.per_device_batch_size
+        b = cfg.per_device_batch_size * cfg.gradient_accumulation_steps
         dp = rank // tp
         log = []
         for batch in _global_batches(case):
@@ -84,6 +86,10 @@ def _worker(case):
 
 def _worker_data_parallel(rank, world):
     return _train_worker(rank, world, "data_parallel")
+
+
+def _worker_data_parallel_with_accumulation(rank, world):
+    return _train_worker(rank, world, "data_parallel_with_accumulation")
 
 
 def _worker_tensor_and_vocab_parallel(rank, world):
@@ -118,7 +124,8 @@ def _single_process(case):
     return log, {n: p.detach().clone() for n, p in model.named_parameters()}
 
 
-@pytest.mark.parametrize("case,port", [("data_parallel", 29661), ("tensor_and_vocab_parallel", 29663),
+@pytest.mark.parametrize("case,port", [("data_parallel", 29661), ("data_parallel_with_accumulation", 29673),
+                                       ("tensor_and_vocab_parallel", 29663),
                                        ("expert_parallel", 29665), ("tensor_and_expert_parallel", 29667),
                                        ("two_slices", 29671)])
 def test_cpu_processes_train_to_the_single_process_weights(case, port):
