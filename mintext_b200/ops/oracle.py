@@ -391,3 +391,26 @@ def newton_schulz(x: torch.Tensor, steps: int = 5, eps: float = 1e-8, coeffs=NS_
         A = x @ x.transpose(-1, -2)
         x = a * x + (b * A + c * (A @ A)) @ x
     return x.transpose(-1, -2) if transposed else x
+
+
+def newton_schulz_sliced(x: torch.Tensor, axis: int, all_reduce, steps: int = 5, eps: float = 1e-8,
+                         coeffs=NS_COEFFS) -> torch.Tensor:
+    """:func:`newton_schulz` for a matrix of which every rank of a group holds a slice: ``x`` ``[b, r, c]`` is the
+    local slice, ``axis`` the sliced dimension (-2 rows, -1 columns) and ``all_reduce(t)`` sums ``t`` over the group in
+    place.  The iteration is written on the Gram matrix of the *unsliced* dimension, which is a plain sum of the
+    ranks' local Gram matrices (``X X^T = sum_l X_l X_l^T`` for column slices, ``X^T X`` for row slices); the
+    polynomial then acts on each slice locally.  Equal to the whole-matrix iteration (``p(X X^T) X = X p(X^T X)``)."""
+    a, b, c = coeffs
+    ss = (x.float() ** 2).sum(dim=(-2, -1), keepdim=True)
+    all_reduce(ss)
+    x = x / (ss.sqrt() + eps)
+    for _ in range(steps):
+        if axis == -1:
+            A = x @ x.transpose(-1, -2)
+            all_reduce(A)
+            x = a * x + (b * A + c * (A @ A)) @ x
+        else:
+            A = x.transpose(-1, -2) @ x
+            all_reduce(A)
+            x = a * x + x @ (b * A + c * (A @ A))
+    return x

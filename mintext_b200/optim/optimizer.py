@@ -99,6 +99,40 @@ def muon_matrix_view(name: str, shape: tuple[int, ...]) -> tuple[int, int, int] 
     return None
 
 
+def muon_slice_axis(name: str, param) -> int | None:
+    """For a parameter of which a tensor-parallel rank holds a slice: which dimension of its Muon matrix view is
+    sliced (-2 rows, -1 columns); None for whole matrices (expert stacks are whole matrices per expert)."""
+    spec = getattr(param, "shard_spec", None)
+    if spec is None or not getattr(param, "tensor_parallel", False) or int(spec[2]) < 2:
+        return None
+    shape = tuple(param.shape)
+    if muon_matrix_view(name, shape) is None:
+        return None
+    dim = int(spec[0])
+    if len(shape) == 2:
+        return -2 if dim == 0 else -1
+    if "experts" in name or name.endswith("gate_up_proj") or name.endswith("down_proj"):
+        return None if dim == 0 else (-2 if dim == 1 else -1)
+    if ".out." in name or name.endswith("out.kernel"):
+        return -2 if dim in (0, 1) else -1
+    return -2 if dim == 0 else -1
+
+
+def muon_sliced_update(mu_hat: torch.Tensor, view: tuple[int, int, int], axis: int, group, steps: int, eps: float,
+                       consistent_rms: float | None):
+    """Orthogonalised update of a sliced matrix and its shape factor (that of the whole matrix)."""
+    import torch.distributed as dist
+
+    from mintext_b200.ops import oracle
+
+    b, r, c = view
+    n = dist.get_world_size(group)
+    upd = oracle.newton_schulz_sliced(mu_hat.reshape(b, r, c).float(), axis,
+                                      lambda t: dist.all_reduce(t, group=group), steps, eps)
+    full = (r * n, c) if axis == -2 else (r, c * n)
+    return upd, muon_shape_scale(full[0], full[1], consistent_rms)
+
+
 def muon_shape_scale(fan_in: int, fan_out: int, consistent_rms: float | None = None) -> float:
     """Factor applied to an orthogonalised ``[fan_in, fan_out]`` update: ``sqrt(max(1, fan_out / fan_in))`` (the
     update of a matrix that widens its input is scaled up, one that narrows it is left alone), or
@@ -156,6 +190,12 @@ class Optimizer:
             factor = 1.0
         state.count += 1
         t = state.count
+        tp_group = None
+        if self.kind == "muon":
+            from mintext_b200.parallel.tp import current_tp
+
+            tp = current_tp()
+            tp_group = tp.group if (tp is not None and tp.size > 1) else None
         for n, p in params.items():
             g = grads.get(n)
             if g is None:
@@ -173,9 +213,15 @@ class Optimizer:
                 mu.mul_(beta).add_(g, alpha=1 - beta)
                 # Nesterov look-ahead with optax's bias correction of both terms
                 mu_hat = (beta * mu / (1 - beta ** (t + 1))) + ((1 - beta) * g / (1 - beta ** t))
-                upd = oracle.newton_schulz(mu_hat.reshape(b, r, c), cfg.muon_newton_schulz_steps,
-                                           cfg.adam_eps).reshape(p.shape)
-                scale = muon_shape_scale(r, c, cfg.muon_consistent_rms)
+                axis = muon_slice_axis(n, p) if tp_group is not None else None
+                if axis is not None:  # this rank holds a slice: the Gram matrices are summed over the group
+                    upd, scale = muon_sliced_update(mu_hat, view, axis, tp_group, cfg.muon_newton_schulz_steps,
+                                                    cfg.adam_eps, cfg.muon_consistent_rms)
+                    upd = upd.reshape(p.shape)
+                else:
+                    upd = oracle.newton_schulz(mu_hat.reshape(b, r, c), cfg.muon_newton_schulz_steps,
+                                               cfg.adam_eps).reshape(p.shape)
+                    scale = muon_shape_scale(r, c, cfg.muon_consistent_rms)
                 pf.add_(upd * scale + wd * pf, alpha=-lr)
             if pf is not p:
                 p.copy_(pf)

@@ -520,11 +520,15 @@ class TrainEngine:
         (mintext/optim/optimizer.py:117-168: Nesterov momentum with optax's bias correction, Newton-Schulz,
         shape-dependent scale, decoupled weight decay)."""
         from mintext_b200.ops import muon as muon_ops
-        from mintext_b200.optim.optimizer import muon_matrix_view, muon_shape_scale
+        from mintext_b200.optim.optimizer import (muon_matrix_view, muon_shape_scale, muon_slice_axis,
+                                                  muon_sliced_update)
+        from mintext_b200.parallel.tp import current_tp
 
         cfg = self.config
         e = ext()
         beta = cfg.muon_beta
+        tp = current_tp()
+        tp_group = tp.group if (tp is not None and tp.size > 1) else None
         for s in slots:
             if s.offset < lo or s.offset + s.numel > hi:
                 continue
@@ -543,8 +547,17 @@ class TrainEngine:
             mu = mom[sl]
             mu.mul_(beta).add_(g, alpha=1 - beta)
             mu_hat = mu * (beta / (1 - beta ** (t + 1))) + g * ((1 - beta) / (1 - beta ** t))
-            upd = muon_ops.newton_schulz(mu_hat.view(b, r, c), cfg.muon_newton_schulz_steps, cfg.adam_eps).reshape(-1)
-            scale = muon_shape_scale(r, c, cfg.muon_consistent_rms)
+            axis = muon_slice_axis(s.name, s.param) if tp_group is not None else None
+            if axis is not None:
+                # a tensor-parallel slice (rank-local group: every rank of the group walks the same slots in the same
+                # order): Gram matrices summed over the group, shape factor of the whole matrix
+                upd, scale = muon_sliced_update(mu_hat, view, axis, tp_group, cfg.muon_newton_schulz_steps,
+                                                cfg.adam_eps, cfg.muon_consistent_rms)
+                upd = upd.reshape(-1)
+            else:
+                upd = muon_ops.newton_schulz(mu_hat.view(b, r, c), cfg.muon_newton_schulz_steps,
+                                             cfg.adam_eps).reshape(-1)
+                scale = muon_shape_scale(r, c, cfg.muon_consistent_rms)
             wd = cfg.weight_decay if weight_decay_mask(s.name) else 0.0
             w = master[sl]
             w.add_(upd * scale + wd * w, alpha=-lr)

@@ -24,6 +24,9 @@ CASES = {
     "expert_parallel": (2, dict(ici_fsdp_parallelism=2, ici_expert_parallelism=2), MOE),
     "tensor_and_expert_parallel": (4, dict(ici_fsdp_parallelism=2, ici_tensor_parallelism=2, ici_expert_parallelism=2),
                                    MOE),
+    # Muon on sliced matrices: the Newton-Schulz Gram matrices are summed over the tensor-parallel group
+    "muon_on_tensor_parallel_slices": (4, dict(ici_fsdp_parallelism=2, ici_tensor_parallelism=2),
+                                       dict(optimizer="muon", tp_vocab_parallel=True, learning_rate=2e-3)),
     # two slices (nodes) of four ranks: data parallel across them, fsdp x tensor inside each
     "two_slices": (8, dict(num_slices=2, dcn_data_parallelism=2, ici_fsdp_parallelism=2, ici_tensor_parallelism=2), {}),
 }
@@ -104,6 +107,10 @@ def _worker_tensor_and_expert_parallel(rank, world):
     return _train_worker(rank, world, "tensor_and_expert_parallel")
 
 
+def _worker_muon_on_tensor_parallel_slices(rank, world):
+    return _train_worker(rank, world, "muon_on_tensor_parallel_slices")
+
+
 def _worker_two_slices(rank, world):
     return _train_worker(rank, world, "two_slices")
 
@@ -127,7 +134,7 @@ def _single_process(case):
 @pytest.mark.parametrize("case,port", [("data_parallel", 29661), ("data_parallel_with_accumulation", 29673),
                                        ("tensor_and_vocab_parallel", 29663),
                                        ("expert_parallel", 29665), ("tensor_and_expert_parallel", 29667),
-                                       ("two_slices", 29671)])
+                                       ("two_slices", 29671), ("muon_on_tensor_parallel_slices", 29675)])
 def test_cpu_processes_train_to_the_single_process_weights(case, port):
     ranks = CASES[case][0]
     res = run_ranks(_worker(case), ranks, port)
