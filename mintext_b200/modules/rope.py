@@ -41,7 +41,8 @@ class RotaryEmbedding(nn.Module):
             self._tables = rope_tables(self._inv_freq.float().cpu(), self._attention_factor, n, device=device)
         return self._tables
 
-    def forward(self, inputs: torch.Tensor, positions: torch.Tensor | None, default_positions: bool = False) -> torch.Tensor:
+    def forward(self, inputs: torch.Tensor, positions: torch.Tensor | None,
+                default_positions: bool = False) -> torch.Tensor:
         x = inputs
         tables = self._cuda_tables(x.device, x.shape[1]) if F.use_cuda(x) else None
         return F.rope(x, positions, self._inv_freq, self._attention_factor, self._rot_dim, self.interleave,
