@@ -301,3 +301,12 @@ def test_help_lists_every_field(capsys):
     for name in ("learning_rate", "ici_fsdp_parallelism", "fsdp_shard_params", "remat_policy"):
         assert name in out
     assert f"Total: {len(MinTextConfig.model_fields)}" in out
+
+
+def test_exponent_literals_without_a_dot_load_as_numbers(tmp_path):
+    """PyYAML reads ``1e-5`` (no dot) as a string; the reference's config files are written that way."""
+    f = tmp_path / "c.yml"
+    f.write_text("rms_norm_eps: 1e-5\nlearning_rate: 3e-4\nadam_eps: 1e-8\nrope_theta: 500000.0\n")
+    c = load_config(f)
+    assert c.rms_norm_eps == 1e-5 and c.learning_rate == 3e-4 and c.adam_eps == 1e-8
+    assert isinstance(c.rms_norm_eps, float)
